@@ -1,0 +1,176 @@
+/*
+ * ctb200.h — C ABI of the B200 (sm_100a) elementwise / broadcast / reduction operator path.
+ *
+ * This is the boundary a maintainer of the reference (ZYROS-OFFICIEL/CTensor) binds at the
+ * place the reference already left a hook: the `device().is_cpu()` test followed by
+ * `throw "...: unsupported device"` in src/core/ops_dispatch.cpp:206-212,295-311,362-376.
+ * Every entry point takes plain pointers, sizes and a CUDA stream handle; no C++ or torch
+ * type crosses it.  All pointers inside a `ctb_view` are DEVICE pointers unless the entry
+ * point's name ends in `_host`.
+ *
+ * Conventions
+ *  - Return value: 0 (CTB_OK) or a ctb_status code; ctb_last_error() gives the message of the
+ *    last failing call on this host thread.  The messages equal the reference's exception
+ *    texts ("binary_op: null input", "Shape mismatch in binary op", ...), so a C++ shim can
+ *    re-throw them unchanged.  Nothing in device code aborts, traps or waits on another block.
+ *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ *    default stream).  The caller synchronises.  The `_host` entry points are synchronous.
+ *  - Shapes and strides are in ELEMENTS, strides are non-negative, at most CTB_MAX_DIMS dims —
+ *    the layout of the reference's Tensorimpl (src/core/tensor.h:322-358).
+ *  - `out` views must be contiguous row-major (every reference op writes a fresh contiguous
+ *    tensor: src/core/opsmp.cpp:148,277,607) and must not alias an input.
+ *  - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *    CTB_ERR_CUDA.
+ */
+#ifndef CTB200_H
+#define CTB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CTB_MAX_DIMS 8
+#define CTB_ABI_VERSION 1
+
+/* Element types; numbering follows the reference's DType enum (src/core/tensor.h:23-25). */
+enum ctb_dtype { CTB_F32 = 0, CTB_I32 = 1, CTB_F64 = 2 };
+
+enum ctb_status {
+    CTB_OK = 0,
+    CTB_ERR_NULL = 1,      /* null view / null base pointer            */
+    CTB_ERR_SHAPE = 2,     /* shapes not broadcastable / out mismatch  */
+    CTB_ERR_DTYPE = 3,     /* unsupported dtype for this op            */
+    CTB_ERR_DIM = 4,       /* reduction dim out of range               */
+    CTB_ERR_ARG = 5,       /* bad op code, ndim, negative stride, ...  */
+    CTB_ERR_CUDA = 6,      /* CUDA runtime error (no device, launch)   */
+    CTB_ERR_WORKSPACE = 7, /* caller workspace too small / misaligned  */
+    CTB_ERR_LIMIT = 8      /* size beyond a documented fixed maximum   */
+};
+
+/* A strided N-d view: replaces (Tensorimpl::data, offset, shape, strides, dtype),
+ * src/core/tensor.h:322-337; Gen-1 twin tensor1.h:77-189. */
+typedef struct ctb_view {
+    void*   base;                   /* start of the storage buffer                     */
+    int64_t offset;                 /* element offset of the view's first element      */
+    int32_t dtype;                  /* enum ctb_dtype                                   */
+    int32_t ndim;                   /* 0..CTB_MAX_DIMS (0 = one element)               */
+    int64_t shape[CTB_MAX_DIMS];
+    int64_t stride[CTB_MAX_DIMS];   /* elements; 0 allowed (broadcast)                 */
+} ctb_view;
+
+/* Binary operators: add/sub/mul/div — src/core/ops_dispatch.cpp:219-233 -> add_mp..div_mp
+ * src/core/opsmp.cpp:391-409 (Gen 1: add_/diff_/mult_/div_ ops1.cpp:149-444, *_mp root
+ * opsmp.cpp:178-196); comparisons — src/core/ops_dispatch.cpp:342-347, opsmp.cpp:708-713
+ * (result 1.0/0.0 in the dtype of `a`). */
+enum ctb_binary_op {
+    CTB_ADD = 0, CTB_SUB = 1, CTB_MUL = 2, CTB_DIV = 3,
+    CTB_LT = 4, CTB_LE = 5, CTB_GT = 6, CTB_GE = 7, CTB_EQ = 8, CTB_NE = 9,
+    CTB_BINARY_OP_COUNT
+};
+
+/* Unary operators.  *_S take the `scalar` argument (a double, applied in double precision
+ * and rounded once: src/core/opsmp.cpp:297,418-456); comparisons with a scalar
+ * src/core/opsmp.cpp:701-706; math ops src/core/ops_dispatch.cpp:319-335.
+ * For CTB_F32 the transcendental flavours are the reference's SIMD Cephes polynomials as its
+ * shipped flags compile them: exp/tanh/sigmoid src/cpu/AVX512/ops_avx512_f32.cpp:63-92,
+ * 187-201; log src/cpu/AVX2/ops_avx2_f32.cpp:103-158.  CTB_GELU_TANH is the tanh-form GELU
+ * written as a chain of those primitives with every step rounded to fp32. */
+enum ctb_unary_op {
+    CTB_ADD_S = 0, CTB_SUB_S = 1, CTB_RSUB_S = 2, CTB_MUL_S = 3, CTB_DIV_S = 4, CTB_RDIV_S = 5,
+    CTB_POW_S = 6, CTB_RPOW_S = 7,
+    CTB_LT_S = 8, CTB_LE_S = 9, CTB_GT_S = 10, CTB_GE_S = 11, CTB_EQ_S = 12, CTB_NE_S = 13,
+    CTB_ABS = 14, CTB_RELU = 15, CTB_EXP = 16, CTB_LOG = 17, CTB_TANH = 18, CTB_SIGMOID = 19,
+    CTB_SQRT = 20, CTB_GELU_TANH = 21,
+    CTB_UNARY_OP_COUNT
+};
+
+/* Reductions: sum/mean src/core/ops_dispatch.cpp:360-390, opsmp.cpp:672-677,693-697;
+ * max/min :392-424, opsmp.cpp:679-691; argmax :427-526 (int32 out, first maximum);
+ * var = biased variance, the recipe of src/neuralnet/batchnorm/batchnorm.cpp:54-61. */
+enum ctb_reduce_op {
+    CTB_SUM = 0, CTB_MEAN = 1, CTB_MAX = 2, CTB_MIN = 3, CTB_VAR = 4, CTB_ARGMAX = 5,
+    CTB_REDUCE_OP_COUNT
+};
+
+#define CTB_DIM_FULL (-1)   /* "reduce everything" (the reference's API-level dim = -1) */
+
+/* ---- library ---------------------------------------------------------------------------- */
+int         ctb_abi_version(void);
+const char* ctb_last_error(void);
+/* Number of CUDA devices visible to the library (0 when there is none). */
+int         ctb_device_count(void);
+
+/* ---- memory: replaces Storage::allocate, src/core/tensor.cpp:18-39 (calloc) --------------- */
+/* Stream-ordered allocation from the device's memory pool; `zero` != 0 clears the buffer
+ * (the reference's calloc promise for Tensor::zeros / fresh tensors). */
+int ctb_alloc(void** ptr, size_t bytes, int zero, void* stream);
+int ctb_free(void* ptr, void* stream);
+int ctb_sync(void* stream);
+
+/* ---- elementwise -------------------------------------------------------------------------- */
+/* out = a (op) b with NumPy-style right-aligned broadcasting (src/core/opsmp.cpp:19-40);
+ * `out` has the broadcast shape and the dtype of `a`; `b` must have the dtype of `a`. */
+int ctb_binary(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream);
+
+/* out[i] = f(a[i], scalar); `out` has the shape and dtype of `a`. */
+int ctb_unary(int op, const ctb_view* a, double scalar, const ctb_view* out, void* stream);
+
+/* Strided gather into contiguous storage: Tensor::contiguous()/clone(),
+ * src/core/tensor.cpp:60-116,233-236 (Gen 1 tensor1.cpp:120-178).  Bit copy, any dtype. */
+int ctb_copy_strided(const ctb_view* src, const ctb_view* out, void* stream);
+
+/* ---- reductions --------------------------------------------------------------------------- */
+/* dim >= 0: reduce that dim, `out` has the input shape without it (no keepdim; a 1-d input
+ * gives shape {1}).  dim == CTB_DIM_FULL: reduce everything to one element.  `out` has the
+ * dtype of `a`, except CTB_ARGMAX which writes CTB_I32 and needs dim >= 0.
+ * Accumulation is fp64 with a fixed combine order, so results are run-to-run identical.
+ * Scratch memory for split reductions comes from a per-device workspace the library
+ * allocates on first use (cudaMalloc) and keeps; calls on one device that share it must be
+ * stream-ordered with respect to each other. */
+int ctb_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, void* stream);
+
+/* Same, with caller-provided scratch (256-byte aligned device memory of at least
+ * ctb_reduce_workspace_bytes(a, dim) bytes; may be NULL when that is 0). */
+size_t ctb_reduce_workspace_bytes(const ctb_view* a, int dim);
+int ctb_reduce_ws(int op, const ctb_view* a, int dim, const ctb_view* out,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* Multi-GPU full reductions: the local shard's fp64 partial (sum for CTB_SUM/MEAN, max/min as
+ * double for CTB_MAX/MIN) is written to `partial` (one double in device memory).  The caller
+ * all-reduces the partials (sum / max / min) across ranks and calls ctb_finalize_full, which
+ * applies the reference's rounding: out = (T)partial, and for CTB_MEAN
+ * out = (T)((double)(T)partial * (1.0 / total_count)) (src/core/ops_dispatch.cpp:385-390). */
+int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* stream);
+int ctb_finalize_full(int op, const double* partial, int64_t total_count,
+                      const ctb_view* out, void* stream);
+
+/* ---- fused rows ----------------------------------------------------------------------------
+ * Softmax over the last dim = the chain max -> sub -> exp -> sum -> div of
+ * src/neuralnet/loss.cpp:97-101 in one pass over the rows.  `mask` (may be NULL) is first added
+ * with broadcasting (additive bias / mask tensor).  `causal` != 0 additionally adds -1e9 to
+ * every element whose last-dim index exceeds its second-to-last-dim index.  fp32 only. */
+int ctb_softmax_lastdim(const ctb_view* x, const ctb_view* mask, int causal,
+                        const ctb_view* out, void* stream);
+
+/* LayerNorm over the last dim = the chain of src/neuralnet/batchnorm/batchnorm.cpp:103-113
+ * applied per row: mean, centre, biased variance, (var+eps)^-0.5, scale, shift.
+ * gamma/beta: 1-d views of the row length, or NULL.  fp32 only. */
+int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_view* beta,
+                          double eps, const ctb_view* out, void* stream);
+
+/* ---- host-buffer entry points ---------------------------------------------------------------
+ * Same semantics as ctb_binary / ctb_unary / ctb_reduce, but every view points to HOST memory
+ * (pinned memory gives full PCIe speed).  Inputs are staged to `device`, the kernel runs there
+ * and the result is copied back before the call returns.  Contiguous same-shape inputs are
+ * processed in chunks so that upload, kernel and download overlap. */
+int ctb_binary_host(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, int device);
+int ctb_unary_host(int op, const ctb_view* a, double scalar, const ctb_view* out, int device);
+int ctb_reduce_host(int op, const ctb_view* a, int dim, const ctb_view* out, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTB200_H */

@@ -1,0 +1,87 @@
+#!/usr/bin/env bash
+# TEST INFRASTRUCTURE — builds the real reference (CTensor src tree) as a shared library.
+#
+#   oracle/build_ref.sh [REFERENCE_ROOT]      (default REFERENCE_ROOT=/root/reference)
+#
+# Output: oracle/_ref/libctensor_ref.so  (+ oracle/_ref/BUILD_INFO.txt).  Nothing else is
+# written; no reference source is copied into the repository.
+#
+# The reference's HEAD does not compile (an unfinished CUDA allocator stub).  Two spots are
+# removed on the fly, into a throw-away directory that is deleted on exit:
+#   1. src/core/tensor.h   : the `//Memory pool` / `struct Block` / `class CudaMemoryPool` block
+#   2. src/core/tensor.cpp : `#include <cuda>` and the `else if (dev.type == DeviceType::CUDA)`
+#                            branch of Storage::allocate
+# Every other file is compiled from where it lies under REFERENCE_ROOT, reached through a
+# farm of symbolic links in the same throw-away directory (a quoted #include looks beside the
+# including file first, so the two patched files must sit beside links to their neighbours).
+#
+# Flags: the two SIMD targets use exactly the reference's own per-target flags
+# (CMakeLists.txt:63,71; GCC's default -ffp-contract=fast is part of what is being pinned).
+# The scalar/OpenMP core is built -O2 -fopenmp ("tuned": the shipped CMake build gives it
+# neither -O nor -fopenmp), which changes speed but not results (its arithmetic is plain
+# double-precision + - * / and libm calls).
+set -euo pipefail
+REF="${1:-/root/reference}"
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+OUT="$HERE/_ref"
+[ -d "$REF/src/core" ] || { echo "build_ref: no reference at $REF" >&2; exit 3; }
+mkdir -p "$OUT"
+TMP="$(mktemp -d /tmp/ctref.XXXXXX)"
+trap 'rm -rf "$TMP"' EXIT
+for d in core cpu/AVX2 cpu/AVX512; do
+  mkdir -p "$TMP/src/$d"
+  for f in "$REF/src/$d"/*.h "$REF/src/$d"/*.cpp; do
+    case "$(basename "$f")" in tensor.h|tensor.cpp) [ "$d" = core ] && continue ;; esac
+    ln -s "$f" "$TMP/src/$d/$(basename "$f")"
+  done
+done
+
+# spot 1: drop the CUDA pool block (from the "//Memory pool" marker up to the line before
+# "// STORAGE & INTERNAL IMPLEMENTATION")
+awk '
+  /^\/\/Memory pool/ {skip=1}
+  /^\/\/ STORAGE & INTERNAL IMPLEMENTATION/ {skip=0}
+  !skip {print}
+' "$REF/src/core/tensor.h" > "$TMP/src/core/tensor.h"
+# spot 2: drop "#include <cuda>" and the CUDA branch of Storage::allocate
+awk '
+  /^#include <cuda>/ {next}
+  /else if\(dev\.type == DeviceType::CUDA\)/ {print "    }"; skip=1; next}
+  skip && /^    }$/ {skip=0; next}
+  !skip {print}
+' "$REF/src/core/tensor.cpp" > "$TMP/src/core/tensor.cpp"
+
+S="$TMP/src"
+INC="-I$S -I$S/core -I$S/cpu/AVX2 -I$S/cpu/AVX512"
+CXX="${REF_CXX:-g++}"   # the PATH g++ (13.3 in this image), not $CXX
+STD="-std=gnu++20 -fPIC -w"
+CORE_FLAGS="-O2 -fopenmp"
+AVX2_FLAGS="-O3 -mavx2 -mfma -fopenmp"       # CMakeLists.txt:63
+AVX512_FLAGS="-O3 -mavx512f -mavx512dq"      # CMakeLists.txt:71 (no OpenMP: single-threaded)
+
+mkdir -p "$TMP/obj"
+pids=()
+cc() { # name flags source
+  $CXX $STD $2 $INC -c "$3" -o "$TMP/obj/$1.o" & pids+=($!)
+}
+cc tensor        "$CORE_FLAGS"   "$TMP/src/core/tensor.cpp"
+cc opsmp         "$CORE_FLAGS"   "$S/core/opsmp.cpp"
+cc ops_dispatch  "$CORE_FLAGS"   "$S/core/ops_dispatch.cpp"
+cc autograd      "$CORE_FLAGS"   "$S/core/autograd.cpp"
+cc avx2_f32      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_f32.cpp"
+cc avx2_d64      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_d64.cpp"
+cc avx512_f32    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_f32.cpp"
+cc avx512_d64    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_d64.cpp"
+cc ref_shim      "$CORE_FLAGS"   "$HERE/ref_shim.cpp"
+for p in "${pids[@]}"; do wait "$p"; done
+
+$CXX -shared -o "$OUT/libctensor_ref.so" "$TMP"/obj/*.o -fopenmp
+{
+  echo "reference: $REF"
+  echo "compiler: $($CXX --version | head -1)"
+  echo "core flags: $CORE_FLAGS"
+  echo "avx2 flags: $AVX2_FLAGS"
+  echo "avx512 flags: $AVX512_FLAGS"
+  echo "patched: tensor.h (CudaMemoryPool block removed), tensor.cpp (<cuda> include + CUDA allocate branch removed)"
+} > "$OUT/BUILD_INFO.txt"
+echo "built $OUT/libctensor_ref.so"

@@ -1,0 +1,296 @@
+"""ctypes bindings of the CPU checkers used by the tests (never by the product).
+
+* ``Oracle``    — oracle/libctb_oracle.so, the plain-C restatement (oracle/ctb_oracle.c).
+* ``Reference`` — oracle/_ref/libctensor_ref.so, the real reference compiled by
+  oracle/build_ref.sh (present only where that build ran or was carried along).
+
+Both take ``HostView`` operands: a 1-d numpy storage buffer plus (offset, shape, strides in
+elements), i.e. the reference's (Storage, offset, shape, strides) quadruple.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_SO = os.path.join(ORACLE_DIR, "libctb_oracle.so")
+REF_SO = os.path.join(ORACLE_DIR, "_ref", "libctensor_ref.so")
+
+MAX_DIMS = 8
+F32, I32, F64 = 0, 1, 2
+NP_DTYPES = {F32: np.float32, I32: np.int32, F64: np.float64}
+DT_OF = {np.dtype(np.float32): F32, np.dtype(np.int32): I32, np.dtype(np.float64): F64}
+
+# operator codes (include/ctb200.h)
+ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE = range(10)
+(ADD_S, SUB_S, RSUB_S, MUL_S, DIV_S, RDIV_S, POW_S, RPOW_S, LT_S, LE_S, GT_S, GE_S, EQ_S, NE_S,
+ ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH) = range(22)
+SUM, MEAN, MAX, MIN, VAR, ARGMAX = range(6)
+PATH_MP, PATH_AVX2, PATH_AVX512, PATH_DISPATCH = range(4)
+
+BINARY_NAMES = ["add", "sub", "mul", "div", "lt", "le", "gt", "ge", "eq", "ne"]
+UNARY_NAMES = ["add_s", "sub_s", "rsub_s", "mul_s", "div_s", "rdiv_s", "pow_s", "rpow_s",
+               "lt_s", "le_s", "gt_s", "ge_s", "eq_s", "ne_s", "abs", "relu", "exp", "log",
+               "tanh", "sigmoid", "sqrt", "gelu_tanh"]
+REDUCE_NAMES = ["sum", "mean", "max", "min", "var", "argmax"]
+
+
+class CView(ctypes.Structure):
+    _fields_ = [("base", ctypes.c_void_p), ("offset", ctypes.c_int64),
+                ("dtype", ctypes.c_int32), ("ndim", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * MAX_DIMS), ("stride", ctypes.c_int64 * MAX_DIMS)]
+
+
+@dataclass
+class HostView:
+    buf: np.ndarray                 # 1-d contiguous storage
+    shape: tuple
+    strides: tuple                  # elements
+    offset: int = 0
+
+    @staticmethod
+    def contig(arr: np.ndarray) -> "HostView":
+        arr = np.ascontiguousarray(arr)
+        shape = tuple(int(s) for s in arr.shape)
+        strides, st = [], 1
+        for s in reversed(shape):
+            strides.append(st)
+            st *= s
+        return HostView(arr.reshape(-1), shape, tuple(reversed(strides)), 0)
+
+    @property
+    def dtype(self) -> int:
+        return DT_OF[self.buf.dtype]
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def permute(self, dims: Sequence[int]) -> "HostView":
+        return HostView(self.buf, tuple(self.shape[d] for d in dims),
+                        tuple(self.strides[d] for d in dims), self.offset)
+
+    def narrow(self, dim: int, start: int, length: int) -> "HostView":
+        shape = list(self.shape)
+        shape[dim] = length
+        return HostView(self.buf, tuple(shape), self.strides, self.offset + start * self.strides[dim])
+
+    def step(self, dim: int, k: int) -> "HostView":
+        shape, strides = list(self.shape), list(self.strides)
+        shape[dim] = (shape[dim] + k - 1) // k
+        strides[dim] *= k
+        return HostView(self.buf, tuple(shape), tuple(strides), self.offset)
+
+    def expand(self, shape: Sequence[int]) -> "HostView":
+        """Broadcast view (stride 0 on expanded dims), right-aligned."""
+        shape = tuple(shape)
+        pad = len(shape) - self.ndim
+        st = []
+        for i, s in enumerate(shape):
+            j = i - pad
+            if j < 0 or (self.shape[j] == 1 and s != 1):
+                st.append(0)
+            else:
+                st.append(self.strides[j])
+        return HostView(self.buf, shape, tuple(st), self.offset)
+
+    def numpy(self) -> np.ndarray:
+        """Materialise the logical tensor (numpy strided gather)."""
+        es = self.buf.dtype.itemsize
+        v = np.lib.stride_tricks.as_strided(self.buf[self.offset:], shape=self.shape,
+                                            strides=tuple(s * es for s in self.strides))
+        return np.array(v)
+
+    def cview(self, base_ptr: Optional[int] = None) -> CView:
+        v = CView()
+        v.base = self.buf.ctypes.data if base_ptr is None else base_ptr
+        v.offset = self.offset
+        v.dtype = self.dtype
+        v.ndim = self.ndim
+        for i in range(self.ndim):
+            v.shape[i] = self.shape[i]
+            v.stride[i] = self.strides[i]
+        return v
+
+
+def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
+    nd = max(len(a), len(b))
+    out = []
+    for i in range(nd):
+        da = 1 if i < nd - len(a) else a[i - (nd - len(a))]
+        db = 1 if i < nd - len(b) else b[i - (nd - len(b))]
+        if da != db and da != 1 and db != 1:
+            raise ValueError("Shape mismatch in binary op")
+        out.append(max(da, db))
+    return tuple(out)
+
+
+def reduced_shape(shape: Sequence[int], dim: int) -> tuple:
+    if dim == -1:
+        return (1,)
+    s = tuple(x for i, x in enumerate(shape) if i != dim)
+    return s if s else (1,)
+
+
+def _ptr(v: Optional[HostView]):
+    return None if v is None else ctypes.byref(v.cview())
+
+
+def build_oracle() -> str:
+    subprocess.check_call(["make", "-s", "-C", ORACLE_DIR])
+    return ORACLE_SO
+
+
+class Oracle:
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(
+                os.path.join(ORACLE_DIR, "ctb_oracle.c")):
+            build_oracle()
+        L = self.lib = ctypes.CDLL(ORACLE_SO)
+        vp = ctypes.POINTER(CView)
+        L.orc_binary.restype = ctypes.c_int64
+        L.orc_binary.argtypes = [ctypes.c_int, vp, vp, ctypes.c_void_p]
+        L.orc_unary.restype = ctypes.c_int64
+        L.orc_unary.argtypes = [ctypes.c_int, vp, ctypes.c_double, ctypes.c_void_p]
+        L.orc_reduce.restype = ctypes.c_int64
+        L.orc_reduce.argtypes = [ctypes.c_int, vp, ctypes.c_int, ctypes.c_void_p]
+        L.orc_contiguous.restype = ctypes.c_int64
+        L.orc_contiguous.argtypes = [vp, ctypes.c_void_p]
+        L.orc_softmax_lastdim.restype = ctypes.c_int64
+        L.orc_softmax_lastdim.argtypes = [vp, vp, ctypes.c_int, ctypes.c_void_p]
+        L.orc_layernorm_lastdim.restype = ctypes.c_int64
+        L.orc_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, ctypes.c_void_p]
+        L.orc_unary_sweep_f32.restype = None
+        L.orc_unary_sweep_f32.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                          ctypes.c_int64, ctypes.c_double, ctypes.c_void_p,
+                                          ctypes.c_void_p]
+
+    def binary(self, op, a: HostView, b: HostView) -> np.ndarray:
+        shape = broadcast_shape(a.shape, b.shape)
+        out = np.empty(shape, NP_DTYPES[a.dtype])
+        n = self.lib.orc_binary(op, a.cview(), b.cview(), out.ctypes.data)
+        assert n == out.size, "oracle binary failed"
+        return out
+
+    def unary(self, op, a: HostView, scalar: float = 0.0) -> np.ndarray:
+        out = np.empty(a.shape, NP_DTYPES[a.dtype])
+        n = self.lib.orc_unary(op, a.cview(), float(scalar), out.ctypes.data)
+        assert n == out.size, "oracle unary failed"
+        return out
+
+    def reduce(self, op, a: HostView, dim: int) -> np.ndarray:
+        out = np.empty(reduced_shape(a.shape, dim), np.int32 if op == ARGMAX else NP_DTYPES[a.dtype])
+        n = self.lib.orc_reduce(op, a.cview(), dim, out.ctypes.data)
+        assert n == out.size, "oracle reduce failed"
+        return out
+
+    def contiguous(self, a: HostView) -> np.ndarray:
+        out = np.empty(a.shape, NP_DTYPES[a.dtype])
+        assert self.lib.orc_contiguous(a.cview(), out.ctypes.data) == out.size
+        return out
+
+    def softmax(self, x: HostView, mask: Optional[HostView] = None, causal: bool = False) -> np.ndarray:
+        shape = x.shape if mask is None else broadcast_shape(x.shape, mask.shape)
+        out = np.empty(shape, np.float32)
+        n = self.lib.orc_softmax_lastdim(x.cview(), _ptr(mask), int(causal), out.ctypes.data)
+        assert n == out.size, "oracle softmax failed"
+        return out
+
+    def layernorm(self, x: HostView, gamma: Optional[HostView], beta: Optional[HostView],
+                  eps: float = 1e-5) -> np.ndarray:
+        out = np.empty(x.shape, np.float32)
+        n = self.lib.orc_layernorm_lastdim(x.cview(), _ptr(gamma), _ptr(beta), eps, out.ctypes.data)
+        assert n == out.size, "oracle layernorm failed"
+        return out
+
+    def sweep(self, op, start: int, step: int, count: int, scalar: float = 0.0):
+        xin = np.empty(count, np.float32)
+        out = np.empty(count, np.float32)
+        self.lib.orc_unary_sweep_f32(op, start, step, count, scalar, xin.ctypes.data, out.ctypes.data)
+        return xin, out
+
+
+class Reference:
+    """The real reference (when oracle/_ref/libctensor_ref.so exists and this CPU can run it)."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_SO)
+
+    def __init__(self):
+        L = self.lib = ctypes.CDLL(REF_SO)
+        vp = ctypes.POINTER(CView)
+        i64, vd = ctypes.c_int64, ctypes.c_void_p
+        L.ref_last_error.restype = ctypes.c_char_p
+        L.ref_cpu_features.restype = ctypes.c_int
+        L.ref_max_threads.restype = ctypes.c_int
+        L.ref_set_threads.argtypes = [ctypes.c_int]
+        L.ref_binary.restype = i64
+        L.ref_binary.argtypes = [ctypes.c_int, ctypes.c_int, vp, vp, vd, i64]
+        L.ref_unary.restype = i64
+        L.ref_unary.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.c_double, vd, i64]
+        L.ref_reduce.restype = i64
+        L.ref_reduce.argtypes = [ctypes.c_int, ctypes.c_int, vp, ctypes.c_int, vd, i64]
+        L.ref_contiguous.restype = i64
+        L.ref_contiguous.argtypes = [vp, vd, i64]
+        L.ref_softmax_lastdim.restype = i64
+        L.ref_softmax_lastdim.argtypes = [ctypes.c_int, vp, vp, vd, i64]
+        L.ref_layernorm_lastdim.restype = i64
+        L.ref_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, vd, i64]
+        feats = L.ref_cpu_features()
+        self.has_avx2 = bool(feats & 1)
+        self.has_avx512 = bool(feats & 2)
+
+    def simd_path(self) -> int:
+        """The SIMD back-end this host can execute (AVX-512 preferred, as the dispatcher does)."""
+        if self.has_avx512:
+            return PATH_AVX512
+        if self.has_avx2:
+            return PATH_AVX2
+        raise RuntimeError("host CPU has neither AVX2 nor AVX-512")
+
+    def _check(self, n, out):
+        if n < 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        assert n == out.size, (n, out.size)
+        return out
+
+    def binary(self, op, a, b, path=PATH_MP):
+        out = np.empty(broadcast_shape(a.shape, b.shape), NP_DTYPES[a.dtype])
+        return self._check(self.lib.ref_binary(path, op, a.cview(), b.cview(), out.ctypes.data, out.nbytes), out)
+
+    def unary(self, op, a, scalar=0.0, path=PATH_MP):
+        out = np.empty(a.shape, NP_DTYPES[a.dtype])
+        return self._check(self.lib.ref_unary(path, op, a.cview(), float(scalar), out.ctypes.data, out.nbytes), out)
+
+    def reduce(self, op, a, dim, path=PATH_MP):
+        out = np.empty(reduced_shape(a.shape, dim), np.int32 if op == ARGMAX else NP_DTYPES[a.dtype])
+        return self._check(self.lib.ref_reduce(path, op, a.cview(), dim, out.ctypes.data, out.nbytes), out)
+
+    def contiguous(self, a):
+        out = np.empty(a.shape, NP_DTYPES[a.dtype])
+        return self._check(self.lib.ref_contiguous(a.cview(), out.ctypes.data, out.nbytes), out)
+
+    def softmax(self, x, mask=None, exp_path=None):
+        shape = x.shape if mask is None else broadcast_shape(x.shape, mask.shape)
+        out = np.empty(shape, np.float32)
+        p = self.simd_path() if exp_path is None else exp_path
+        return self._check(self.lib.ref_softmax_lastdim(p, x.cview(), _ptr(mask), out.ctypes.data, out.nbytes), out)
+
+    def layernorm(self, x, gamma, beta, eps=1e-5):
+        out = np.empty(x.shape, np.float32)
+        return self._check(self.lib.ref_layernorm_lastdim(x.cview(), _ptr(gamma), _ptr(beta), eps,
+                                                          out.ctypes.data, out.nbytes), out)
