@@ -1,0 +1,326 @@
+"""ctensor_b200 — B200 (sm_100a) elementwise / broadcast / reduction operators behind a C ABI.
+
+The product is ``libctb200.so`` (sources in ``ctensor_b200/csrc``, interface in
+``include/ctb200.h``).  This module is the thin Python binding used by the tests and the
+benchmark: it loads the library with ctypes, wraps device memory held by torch tensors in
+``ctb_view`` structs and calls the C entry points on torch's current CUDA stream.  torch only
+provides memory, streams and process groups; no torch operator computes a result here.
+
+There is no CPU fallback: importing works anywhere, but every operator call needs the built
+library and a CUDA device and raises otherwise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libctb200.so")
+MAX_DIMS = 8
+
+# dtypes (reference DType numbering)
+F32, I32, F64 = 0, 1, 2
+# binary operators
+ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE = range(10)
+# unary operators
+(ADD_S, SUB_S, RSUB_S, MUL_S, DIV_S, RDIV_S, POW_S, RPOW_S, LT_S, LE_S, GT_S, GE_S, EQ_S, NE_S,
+ ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH) = range(22)
+# reductions
+SUM, MEAN, MAX, MIN, VAR, ARGMAX = range(6)
+DIM_FULL = -1
+
+STATUS_NAMES = {0: "CTB_OK", 1: "CTB_ERR_NULL", 2: "CTB_ERR_SHAPE", 3: "CTB_ERR_DTYPE",
+                4: "CTB_ERR_DIM", 5: "CTB_ERR_ARG", 6: "CTB_ERR_CUDA", 7: "CTB_ERR_WORKSPACE",
+                8: "CTB_ERR_LIMIT"}
+
+# every symbol include/ctb200.h declares
+EXPORTED_SYMBOLS = [
+    "ctb_abi_version", "ctb_last_error", "ctb_device_count", "ctb_alloc", "ctb_free", "ctb_sync",
+    "ctb_binary", "ctb_unary", "ctb_copy_strided", "ctb_reduce", "ctb_reduce_workspace_bytes",
+    "ctb_reduce_ws", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
+    "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
+]
+
+
+class CtbError(RuntimeError):
+    """A C-ABI call returned a non-zero status.  ``code`` is the ctb_status value; the message
+    is the library's, which equals the reference's exception text for the same mistake."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(code, code)}: {message}")
+        self.code = code
+        self.message = message
+
+
+class View(ctypes.Structure):
+    """struct ctb_view."""
+    _fields_ = [("base", ctypes.c_void_p), ("offset", ctypes.c_int64),
+                ("dtype", ctypes.c_int32), ("ndim", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * MAX_DIMS), ("stride", ctypes.c_int64 * MAX_DIMS)]
+
+
+def make_view(base: int, dtype: int, shape: Sequence[int], strides: Sequence[int], offset: int = 0) -> View:
+    if len(shape) > MAX_DIMS:
+        raise CtbError(5, f"ndim {len(shape)} not in 0..{MAX_DIMS}")
+    v = View()
+    v.base = base
+    v.offset = offset
+    v.dtype = dtype
+    v.ndim = len(shape)
+    for i, (s, st) in enumerate(zip(shape, strides)):
+        v.shape[i] = s
+        v.stride[i] = st
+    return v
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load libctb200.so (built in-tree by ``ctensor_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it first (python -c 'import __graft_entry__ as g; g.build()' "
+            "or python -m ctensor_b200.build).  There is no CPU fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, vd, i32, i64 = ctypes.POINTER(View), ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    L.ctb_abi_version.restype = i32
+    L.ctb_last_error.restype = ctypes.c_char_p
+    L.ctb_device_count.restype = i32
+    L.ctb_alloc.argtypes = [ctypes.POINTER(vd), ctypes.c_size_t, i32, vd]
+    L.ctb_free.argtypes = [vd, vd]
+    L.ctb_sync.argtypes = [vd]
+    L.ctb_binary.argtypes = [i32, vp, vp, vp, vd]
+    L.ctb_unary.argtypes = [i32, vp, ctypes.c_double, vp, vd]
+    L.ctb_copy_strided.argtypes = [vp, vp, vd]
+    L.ctb_reduce.argtypes = [i32, vp, i32, vp, vd]
+    L.ctb_reduce_workspace_bytes.restype = ctypes.c_size_t
+    L.ctb_reduce_workspace_bytes.argtypes = [vp, i32]
+    L.ctb_reduce_ws.argtypes = [i32, vp, i32, vp, vd, ctypes.c_size_t, vd]
+    L.ctb_reduce_full_partial.argtypes = [i32, vp, vd, vd]
+    L.ctb_finalize_full.argtypes = [i32, vd, i64, vp, vd]
+    L.ctb_softmax_lastdim.argtypes = [vp, vp, i32, vp, vd]
+    L.ctb_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, vp, vd]
+    L.ctb_binary_host.argtypes = [i32, vp, vp, vp, i32]
+    L.ctb_unary_host.argtypes = [i32, vp, ctypes.c_double, vp, i32]
+    L.ctb_reduce_host.argtypes = [i32, vp, i32, vp, i32]
+    for name in EXPORTED_SYMBOLS:      # AttributeError here = the library lacks a declared symbol
+        getattr(L, name)
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise CtbError(status, lib().ctb_last_error().decode())
+
+
+# ---- torch plumbing (device memory + streams) -------------------------------------------------------
+def _torch():
+    import torch
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    try:
+        return {torch.float32: F32, torch.int32: I32, torch.float64: F64}[t.dtype]
+    except KeyError:
+        raise CtbError(3, f"unsupported dtype {t.dtype}")
+
+
+def _torch_dtype(code: int):
+    torch = _torch()
+    return {F32: torch.float32, I32: torch.int32, F64: torch.float64}[code]
+
+
+@dataclass
+class DView:
+    """A strided view of a torch storage buffer: the (Storage, offset, shape, strides) quadruple
+    of the reference's Tensorimpl.  ``buf`` is a 1-d torch tensor (CUDA for the device entry
+    points, CPU — ideally pinned — for the ``*_host`` ones)."""
+    buf: "object"
+    shape: tuple
+    strides: tuple
+    offset: int = 0
+
+    @staticmethod
+    def of(t) -> "DView":
+        """View of a torch tensor as it is (its own strides; offset folded into data_ptr)."""
+        if any(s < 0 for s in t.stride()):
+            raise CtbError(5, "negative strides are not supported")
+        return DView(t, tuple(t.shape), tuple(t.stride()), 0)
+
+    @property
+    def dtype(self) -> int:
+        return _dtype_code(self.buf)
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def cview(self) -> View:
+        return make_view(self.buf.data_ptr(), self.dtype, self.shape, self.strides, self.offset)
+
+    def permute(self, dims: Sequence[int]) -> "DView":
+        return DView(self.buf, tuple(self.shape[d] for d in dims), tuple(self.strides[d] for d in dims), self.offset)
+
+
+def _as_dview(x) -> DView:
+    return x if isinstance(x, DView) else DView.of(x)
+
+
+def _stream_ptr(x: DView) -> int:
+    torch = _torch()
+    if not x.buf.is_cuda:
+        raise CtbError(6, "device entry point called with host memory (use the *_host functions)")
+    return torch.cuda.current_stream(x.buf.device).cuda_stream
+
+
+def _device_guard(x: DView):
+    return _torch().cuda.device(x.buf.device)
+
+
+def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
+    nd = max(len(a), len(b))
+    out = []
+    for i in range(nd):
+        da = 1 if i < nd - len(a) else a[i - (nd - len(a))]
+        db = 1 if i < nd - len(b) else b[i - (nd - len(b))]
+        if da != db and da != 1 and db != 1:
+            raise CtbError(2, "Shape mismatch in binary op")
+        out.append(max(da, db))
+    return tuple(out)
+
+
+def reduced_shape(shape: Sequence[int], dim: int) -> tuple:
+    if dim == DIM_FULL:
+        return (1,)
+    s = tuple(x for i, x in enumerate(shape) if i != dim)
+    return s if s else (1,)
+
+
+def _new_out(like: DView, shape, dtype_code=None):
+    torch = _torch()
+    return torch.empty(shape, dtype=_torch_dtype(like.dtype if dtype_code is None else dtype_code),
+                       device=like.buf.device)
+
+
+# ---- operators (device memory) ------------------------------------------------------------------------
+def binary(op: int, a, b, out=None):
+    """out = a (op) b with broadcasting; a, b: torch CUDA tensors or DViews."""
+    a, b = _as_dview(a), _as_dview(b)
+    if out is None:
+        out = _new_out(a, broadcast_shape(a.shape, b.shape))
+    with _device_guard(a):
+        check(lib().ctb_binary(op, a.cview(), b.cview(), DView.of(out).cview(), _stream_ptr(a)))
+    return out
+
+
+def unary(op: int, a, scalar: float = 0.0, out=None):
+    a = _as_dview(a)
+    if out is None:
+        out = _new_out(a, a.shape)
+    with _device_guard(a):
+        check(lib().ctb_unary(op, a.cview(), float(scalar), DView.of(out).cview(), _stream_ptr(a)))
+    return out
+
+
+def contiguous(a, out=None):
+    """Strided gather into fresh row-major storage (Tensor::contiguous / clone)."""
+    a = _as_dview(a)
+    if out is None:
+        out = _new_out(a, a.shape)
+    with _device_guard(a):
+        check(lib().ctb_copy_strided(a.cview(), DView.of(out).cview(), _stream_ptr(a)))
+    return out
+
+
+def reduce(op: int, a, dim: int = DIM_FULL, out=None, workspace=None):
+    """sum/mean/max/min/var/argmax along ``dim`` (DIM_FULL = everything)."""
+    a = _as_dview(a)
+    if out is None:
+        out = _new_out(a, reduced_shape(a.shape, dim), I32 if op == ARGMAX else None)
+    with _device_guard(a):
+        if workspace is None:
+            check(lib().ctb_reduce(op, a.cview(), dim, DView.of(out).cview(), _stream_ptr(a)))
+        else:
+            check(lib().ctb_reduce_ws(op, a.cview(), dim, DView.of(out).cview(), workspace.data_ptr(),
+                                      workspace.numel() * workspace.element_size(), _stream_ptr(a)))
+    return out
+
+
+def reduce_workspace_bytes(a, dim: int) -> int:
+    return int(lib().ctb_reduce_workspace_bytes(_as_dview(a).cview(), dim))
+
+
+def reduce_full_partial(op: int, a, partial=None):
+    """fp64 partial of a full reduction over this shard (device tensor with one double)."""
+    torch = _torch()
+    a = _as_dview(a)
+    if partial is None:
+        partial = torch.empty(1, dtype=torch.float64, device=a.buf.device)
+    with _device_guard(a):
+        check(lib().ctb_reduce_full_partial(op, a.cview(), partial.data_ptr(), _stream_ptr(a)))
+    return partial
+
+
+def finalize_full(op: int, partial, total_count: int, out=None, dtype_code: int = F32):
+    torch = _torch()
+    if out is None:
+        out = torch.empty(1, dtype=_torch_dtype(dtype_code), device=partial.device)
+    with torch.cuda.device(partial.device):
+        check(lib().ctb_finalize_full(op, partial.data_ptr(), int(total_count), DView.of(out).cview(),
+                                      torch.cuda.current_stream(partial.device).cuda_stream))
+    return out
+
+
+def softmax(x, mask=None, causal: bool = False, out=None):
+    x = _as_dview(x)
+    m = None if mask is None else _as_dview(mask)
+    if out is None:
+        out = _new_out(x, x.shape)
+    with _device_guard(x):
+        check(lib().ctb_softmax_lastdim(x.cview(), None if m is None else m.cview(), int(causal),
+                                        DView.of(out).cview(), _stream_ptr(x)))
+    return out
+
+
+def layernorm(x, gamma=None, beta=None, eps: float = 1e-5, out=None):
+    x = _as_dview(x)
+    g = None if gamma is None else _as_dview(gamma)
+    b = None if beta is None else _as_dview(beta)
+    if out is None:
+        out = _new_out(x, x.shape)
+    with _device_guard(x):
+        check(lib().ctb_layernorm_lastdim(x.cview(), None if g is None else g.cview(),
+                                          None if b is None else b.cview(), float(eps),
+                                          DView.of(out).cview(), _stream_ptr(x)))
+    return out
+
+
+# ---- operators (host memory in, host memory out) --------------------------------------------------------
+def binary_host(op: int, a, b, out, device: int = 0):
+    a, b, o = _as_dview(a), _as_dview(b), _as_dview(out)
+    check(lib().ctb_binary_host(op, a.cview(), b.cview(), o.cview(), device))
+    return out
+
+
+def unary_host(op: int, a, out, scalar: float = 0.0, device: int = 0):
+    a, o = _as_dview(a), _as_dview(out)
+    check(lib().ctb_unary_host(op, a.cview(), float(scalar), o.cview(), device))
+    return out
+
+
+def reduce_host(op: int, a, dim: int, out, device: int = 0):
+    a, o = _as_dview(a), _as_dview(out)
+    check(lib().ctb_reduce_host(op, a.cview(), dim, o.cview(), device))
+    return out

@@ -1,0 +1,677 @@
+// C ABI of the operator library (declared in include/ctb200.h): argument validation, broadcast
+// and collapse planning on the host, dispatch to the kernels, per-device scratch, and the
+// host-buffer entry points.  Error texts equal the reference's exception messages
+// (src/core/opsmp.cpp:138,144,274,595; src/core/ops_dispatch.cpp:428,433) so a C++ shim can
+// re-throw them unchanged.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "ctb_common.cuh"
+#include "ctb_math.cuh"
+#include "ctb_reduce.cuh"
+
+namespace ctb {
+
+// ---- errors ------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+int set_error(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int cuda_error(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return CTB_OK;
+    return set_error(CTB_ERR_CUDA, "CUDA error in %s: %s", what, cudaGetErrorString(e));
+}
+
+// ---- per-device state ----------------------------------------------------------------------------
+namespace {
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool known = false;
+    int sm_count = 0;
+    void* ws = nullptr;          // reduction scratch
+    size_t ws_bytes = 0;
+    void* stage = nullptr;       // staging for the host-buffer entry points
+    size_t stage_bytes = 0;
+    cudaStream_t streams[3] = {nullptr, nullptr, nullptr};
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+}  // namespace
+
+int current_device_info(DeviceInfo* info) {
+    int dev = -1;
+    CTB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return set_error(CTB_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[dev];
+    if (!s.known) {
+        CTB_CUDA_TRY(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        s.known = true;
+    }
+    info->device = dev;
+    info->sm_count = s.sm_count;
+    return CTB_OK;
+}
+
+namespace {
+
+// Scratch that grows on demand and is zeroed when (re)allocated.
+int ensure_workspace(size_t bytes, void** out) {
+    *out = nullptr;
+    if (bytes == 0) return CTB_OK;
+    DeviceInfo di;
+    int rc = current_device_info(&di);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[di.device];
+    if (s.ws_bytes < bytes) {
+        size_t want = bytes < (size_t(8) << 20) ? (size_t(8) << 20) : bytes;
+        if (s.ws) CTB_CUDA_TRY(cudaFree(s.ws));
+        s.ws = nullptr;
+        s.ws_bytes = 0;
+        CTB_CUDA_TRY(cudaMalloc(&s.ws, want));
+        CTB_CUDA_TRY(cudaMemset(s.ws, 0, want));
+        s.ws_bytes = want;
+    }
+    *out = s.ws;
+    return CTB_OK;
+}
+
+size_t dtype_bytes(int dt) { return dt == CTB_F64 ? 8 : 4; }
+bool dtype_ok(int dt) { return dt == CTB_F32 || dt == CTB_I32 || dt == CTB_F64; }
+
+int64_t view_numel(const ctb_view* v) {
+    int64_t n = 1;
+    for (int i = 0; i < v->ndim; ++i) n *= v->shape[i];
+    return n;
+}
+
+// Largest element index the view can touch + 1, counted from `base` (0 for an empty view).
+int64_t view_span(const ctb_view* v) {
+    int64_t hi = v->offset;
+    for (int i = 0; i < v->ndim; ++i) {
+        if (v->shape[i] == 0) return 0;
+        hi += (v->shape[i] - 1) * v->stride[i];
+    }
+    return hi + 1;
+}
+
+int check_view(const ctb_view* v, const char* null_msg, const char* who) {
+    if (!v) return set_error(CTB_ERR_NULL, "%s", null_msg);
+    if (v->ndim < 0 || v->ndim > CTB_MAX_DIMS) return set_error(CTB_ERR_ARG, "%s: ndim %d not in 0..%d", who, v->ndim, CTB_MAX_DIMS);
+    if (!v->base) {       // an empty tensor may have no storage at all
+        bool empty = false;
+        for (int i = 0; i < v->ndim; ++i) if (v->shape[i] == 0) empty = true;
+        if (!empty) return set_error(CTB_ERR_NULL, "%s", null_msg);
+    }
+    if (!dtype_ok(v->dtype)) return set_error(CTB_ERR_DTYPE, "%s: unsupported dtype", who);
+    if (v->offset < 0) return set_error(CTB_ERR_ARG, "%s: negative offset", who);
+    for (int i = 0; i < v->ndim; ++i)
+        if (v->shape[i] < 0 || v->stride[i] < 0) return set_error(CTB_ERR_ARG, "%s: negative shape or stride", who);
+    return CTB_OK;
+}
+
+// Same rule as Tensor::is_contiguous (src/core/tensor.cpp:244-254): size-1 dims are ignored.
+bool view_contiguous(const ctb_view* v) {
+    int64_t expect = 1;
+    for (int i = v->ndim - 1; i >= 0; --i) {
+        if (v->shape[i] > 1) {
+            if (v->stride[i] != expect) return false;
+            expect *= v->shape[i];
+        }
+    }
+    return true;
+}
+
+int check_out(const ctb_view* out, int64_t numel, int dtype, const char* who) {
+    int rc = check_view(out, "output: null view", who);
+    if (rc) return rc;
+    if (out->dtype != dtype) return set_error(CTB_ERR_DTYPE, "%s: output dtype mismatch", who);
+    if (view_numel(out) != numel) return set_error(CTB_ERR_SHAPE, "%s: output has %lld elements, expected %lld", who, (long long)view_numel(out), (long long)numel);
+    if (!view_contiguous(out)) return set_error(CTB_ERR_SHAPE, "%s: output must be contiguous", who);
+    return CTB_OK;
+}
+
+inline const void* elem_ptr(const ctb_view* v) {
+    return (const char*)v->base + (size_t)v->offset * dtype_bytes(v->dtype);
+}
+inline void* elem_ptr_mut(const ctb_view* v) {
+    return (char*)v->base + (size_t)v->offset * dtype_bytes(v->dtype);
+}
+
+// Right-aligned broadcast of up to kMaxOperands inputs, then collapse.
+// Returns CTB_ERR_SHAPE if the shapes are not broadcastable (src/core/opsmp.cpp:19-28).
+int build_plan(const ctb_view* const* in, int nin, Plan* plan) {
+    int nd = 0;
+    for (int i = 0; i < nin; ++i) nd = in[i]->ndim > nd ? in[i]->ndim : nd;
+    int64_t shape[CTB_MAX_DIMS], stride[kMaxOperands][CTB_MAX_DIMS];
+    for (int d = 0; d < nd; ++d) {
+        int64_t s = 1;
+        for (int i = 0; i < nin; ++i) {
+            int j = d - (nd - in[i]->ndim);
+            int64_t di = j < 0 ? 1 : in[i]->shape[j];
+            if (di != 1) {
+                if (s != 1 && s != di) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+                s = di;
+            }
+        }
+        shape[d] = s;
+        for (int i = 0; i < nin; ++i) {
+            int j = d - (nd - in[i]->ndim);
+            stride[i][d] = (j < 0 || in[i]->shape[j] == 1) ? 0 : in[i]->stride[j];
+        }
+    }
+    // a zero-sized dim anywhere makes the result empty
+    int64_t numel = 1;
+    for (int d = 0; d < nd; ++d) {
+        // broadcasting a size-0 dim against size-1 gives 0
+        for (int i = 0; i < nin; ++i) {
+            int j = d - (nd - in[i]->ndim);
+            if (j >= 0 && in[i]->shape[j] == 0) shape[d] = 0;
+        }
+        numel *= shape[d];
+    }
+    plan->nin = nin;
+    plan->numel = numel;
+    // drop size-1 dims, merge neighbours
+    int k = 0;
+    for (int d = 0; d < nd; ++d) {
+        if (shape[d] == 1) continue;
+        if (k > 0) {
+            bool merge = true;
+            for (int i = 0; i < nin; ++i)
+                if (plan->stride[i][k - 1] != stride[i][d] * shape[d]) merge = false;
+            if (merge) {
+                plan->shape[k - 1] *= shape[d];
+                for (int i = 0; i < nin; ++i) plan->stride[i][k - 1] = stride[i][d];
+                continue;
+            }
+        }
+        plan->shape[k] = shape[d];
+        for (int i = 0; i < nin; ++i) plan->stride[i][k] = stride[i][d];
+        ++k;
+    }
+    if (k == 0) {
+        plan->shape[0] = 1;
+        for (int i = 0; i < nin; ++i) plan->stride[i][0] = 0;
+        k = 1;
+    }
+    plan->ndim = k;
+    return CTB_OK;
+}
+
+// Geometry of a reduction over `dim` (>= 0): outer dims in output order, merged where the
+// input is contiguous across them.
+void reduce_geom_dim(const ctb_view* a, int dim, ReduceGeom* g) {
+    memset(g, 0, sizeof *g);
+    int k = 0;
+    int64_t nout = 1;
+    for (int d = 0; d < a->ndim; ++d) {
+        if (d == dim) continue;
+        nout *= a->shape[d];
+        if (a->shape[d] == 1) continue;
+        if (k > 0 && g->ostride[k - 1] == a->stride[d] * a->shape[d]) {
+            g->oshape[k - 1] *= a->shape[d];
+            g->ostride[k - 1] = a->stride[d];
+            continue;
+        }
+        g->oshape[k] = a->shape[d];
+        g->ostride[k] = a->stride[d];
+        ++k;
+    }
+    g->nouter = k;
+    g->nout = nout;
+    g->rlen = a->shape[dim];
+    g->rstride = a->shape[dim] == 1 ? 1 : a->stride[dim];
+    g->total = g->rlen;
+}
+
+// A view is "dense" when it is some permutation of a gap-free block of memory; a full
+// reduction of it may then run in memory order (sum/mean/var are order-insensitive at the
+// stated tolerance, max/min exactly).
+bool view_dense(const ctb_view* a) {
+    int idx[CTB_MAX_DIMS], k = 0;
+    for (int d = 0; d < a->ndim; ++d) if (a->shape[d] != 1) idx[k++] = d;
+    for (int i = 1; i < k; ++i)
+        for (int j = i; j > 0 && a->stride[idx[j]] > a->stride[idx[j - 1]]; --j) {
+            int t = idx[j]; idx[j] = idx[j - 1]; idx[j - 1] = t;
+        }
+    int64_t expect = 1;
+    for (int i = k - 1; i >= 0; --i) {
+        if (a->stride[idx[i]] != expect) return false;
+        expect *= a->shape[idx[i]];
+    }
+    return true;
+}
+
+void reduce_geom_full_dense(const ctb_view* a, ReduceGeom* g) {
+    memset(g, 0, sizeof *g);
+    g->nouter = 0;
+    g->nout = 1;
+    g->rlen = view_numel(a);
+    g->rstride = 1;
+    g->total = g->rlen;
+}
+
+int reduce_out_check(int op, const ctb_view* a, int dim, const ctb_view* out) {
+    int64_t nout = 1;
+    if (dim != CTB_DIM_FULL)
+        for (int d = 0; d < a->ndim; ++d) if (d != dim) nout *= a->shape[d];
+    return check_out(out, nout, op == CTB_ARGMAX ? CTB_I32 : a->dtype, "reduction");
+}
+
+int reduce_arg_check(int op, const ctb_view* a, int dim) {
+    int rc = check_view(a, "reduction: null input", "reduction");
+    if (rc) return rc;
+    if (op < 0 || op >= CTB_REDUCE_OP_COUNT) return set_error(CTB_ERR_ARG, "reduction: unknown operator code %d", op);
+    if (op == CTB_ARGMAX) {
+        if (dim < 0 || dim >= a->ndim) return set_error(CTB_ERR_DIM, "argmax: dim out of range");
+    } else if (dim != CTB_DIM_FULL && (dim < 0 || dim >= a->ndim)) {
+        return set_error(CTB_ERR_DIM, "reduction: dim out of range");
+    }
+    return CTB_OK;
+}
+
+// Scratch needed by ctb_reduce for (a, dim): kernel scratch, plus a packed copy of the input
+// when a full reduction is asked of a non-dense view.
+size_t reduce_ws_need(const ctb_view* a, int dim, size_t* copy_bytes) {
+    ReduceGeom g;
+    *copy_bytes = 0;
+    if (dim == CTB_DIM_FULL) {
+        if (!view_dense(a)) *copy_bytes = (((size_t)view_numel(a) * dtype_bytes(a->dtype)) + 255) / 256 * 256;
+        reduce_geom_full_dense(a, &g);
+    } else {
+        reduce_geom_dim(a, dim, &g);
+    }
+    return *copy_bytes + reduce_workspace_bytes(g, a->dtype);
+}
+
+int do_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, double* partial,
+              void* ws, size_t ws_bytes, cudaStream_t st) {
+    ReduceGeom g;
+    const void* src = elem_ptr(a);
+    size_t copy_bytes = 0;
+    const size_t need = reduce_ws_need(a, dim, &copy_bytes);
+    if (need > ws_bytes || (need && !ws)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+    if (need && !is_aligned(ws, 256)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace must be 256-byte aligned");
+    if (dim == CTB_DIM_FULL) {
+        if (copy_bytes) {
+            // pack the view first (what the reference does: contiguous() before a full reduction,
+            // src/cpu/AVX2/ops_avx2_f32.cpp:782)
+            const ctb_view* in[1] = {a};
+            Plan p;
+            int rc = build_plan(in, 1, &p);
+            if (rc) return rc;
+            void* packed = (char*)ws + (need - copy_bytes);
+            rc = launch_copy((int)dtype_bytes(a->dtype), p, src, packed, st);
+            if (rc) return rc;
+            src = packed;
+        }
+        reduce_geom_full_dense(a, &g);
+    } else {
+        reduce_geom_dim(a, dim, &g);
+    }
+    void* o = out ? elem_ptr_mut(out) : nullptr;
+    return launch_reduce(op, a->dtype, g, src, o, partial, ws, need - copy_bytes, st);
+}
+
+int rows_geom(const ctb_view* x, const ctb_view* mask, RowsGeom* g, const char* who) {
+    memset(g, 0, sizeof *g);
+    if (x->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "%s: only Float32 is supported", who);
+    if (x->ndim < 1) return set_error(CTB_ERR_SHAPE, "%s: needs at least one dim", who);
+    const int nd = x->ndim;
+    if (x->shape[nd - 1] > 1 && x->stride[nd - 1] != 1) return set_error(CTB_ERR_SHAPE, "%s: the last dim must be contiguous", who);
+    g->cols = x->shape[nd - 1];
+    g->qlen = nd >= 2 ? x->shape[nd - 2] : 1;
+    if (g->qlen == 0) g->qlen = 1;
+    g->rows = 1;
+    g->nouter = nd - 1;
+    for (int d = 0; d < nd - 1; ++d) {
+        g->oshape[d] = x->shape[d];
+        g->xstride[d] = x->shape[d] == 1 ? 0 : x->stride[d];
+        g->rows *= x->shape[d];
+    }
+    if (mask) {
+        if (mask->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "%s: mask must be Float32", who);
+        if (mask->ndim > nd) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+        g->has_mask = 1;
+        const int pad = nd - mask->ndim;
+        for (int d = 0; d < nd; ++d) {
+            const int j = d - pad;
+            const int64_t ms = j < 0 ? 1 : mask->shape[j];
+            if (ms != 1 && ms != x->shape[d]) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+            const int64_t st = (j < 0 || ms == 1) ? 0 : mask->stride[j];
+            if (d == nd - 1) {
+                if (st != 0 && st != 1) return set_error(CTB_ERR_SHAPE, "%s: the mask's last dim must be contiguous or broadcast", who);
+                g->m_inner = (int32_t)st;
+            } else {
+                g->mstride[d] = st;
+            }
+        }
+    }
+    return CTB_OK;
+}
+
+// ---- host-buffer helpers ----------------------------------------------------------------------------
+int ensure_stage(int device, size_t bytes, void** out, cudaStream_t** streams) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_dev[device];
+    for (int i = 0; i < 3; ++i)
+        if (!s.streams[i]) CTB_CUDA_TRY(cudaStreamCreateWithFlags(&s.streams[i], cudaStreamNonBlocking));
+    if (s.stage_bytes < bytes) {
+        if (s.stage) CTB_CUDA_TRY(cudaFree(s.stage));
+        s.stage = nullptr;
+        s.stage_bytes = 0;
+        CTB_CUDA_TRY(cudaMalloc(&s.stage, bytes));
+        s.stage_bytes = bytes;
+    }
+    *out = s.stage;
+    *streams = s.streams;
+    return CTB_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) return;
+        ok = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Upload the storage span a host view touches; returns the device view in *dv.
+int upload_view(const ctb_view* hv, char* dbuf, size_t* used, ctb_view* dv, cudaStream_t st) {
+    const size_t es = dtype_bytes(hv->dtype);
+    const int64_t span = view_span(hv);
+    *dv = *hv;
+    dv->base = dbuf + *used;
+    dv->offset = 0;
+    if (span > hv->offset) {
+        const size_t bytes = (size_t)(span - hv->offset) * es;
+        CTB_CUDA_TRY(cudaMemcpyAsync(dv->base, (const char*)hv->base + (size_t)hv->offset * es, bytes, cudaMemcpyHostToDevice, st));
+        *used += align_up(bytes, 256);
+    }
+    return CTB_OK;
+}
+
+size_t span_bytes(const ctb_view* v) {
+    const int64_t span = view_span(v);
+    return span > v->offset ? align_up((size_t)(span - v->offset) * dtype_bytes(v->dtype), 256) : 0;
+}
+
+constexpr int64_t kHostChunkElems = int64_t(1) << 24;     // 64 MiB of fp32 per pipelined chunk
+
+}  // namespace
+}  // namespace ctb
+
+// ====================================================================================================
+//                                              C ABI
+// ====================================================================================================
+using namespace ctb;
+
+extern "C" {
+
+int ctb_abi_version(void) { return CTB_ABI_VERSION; }
+
+const char* ctb_last_error(void) { return g_last_error.c_str(); }
+
+int ctb_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int ctb_alloc(void** ptr, size_t bytes, int zero, void* stream) {
+    if (!ptr) return set_error(CTB_ERR_NULL, "ctb_alloc: null result pointer");
+    *ptr = nullptr;
+    if (bytes == 0) bytes = 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    CTB_CUDA_TRY(cudaMallocAsync(ptr, bytes, st));
+    if (zero) CTB_CUDA_TRY(cudaMemsetAsync(*ptr, 0, bytes, st));
+    return CTB_OK;
+}
+
+int ctb_free(void* ptr, void* stream) {
+    if (!ptr) return CTB_OK;
+    CTB_CUDA_TRY(cudaFreeAsync(ptr, (cudaStream_t)stream));
+    return CTB_OK;
+}
+
+int ctb_sync(void* stream) {
+    CTB_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return CTB_OK;
+}
+
+int ctb_binary(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(a, "binary_op: null input", "binary_op"))) return rc;
+    if ((rc = check_view(b, "binary_op: null input", "binary_op"))) return rc;
+    if (op < 0 || op >= CTB_BINARY_OP_COUNT) return set_error(CTB_ERR_ARG, "binary_op: unknown operator code %d", op);
+    if (a->dtype != b->dtype) return set_error(CTB_ERR_DTYPE, "binary_op: operands must have the same dtype");
+    const ctb_view* in[2] = {a, b};
+    Plan p;
+    if ((rc = build_plan(in, 2, &p))) return rc;
+    if ((rc = check_out(out, p.numel, a->dtype, "binary_op"))) return rc;
+    return launch_binary(op, a->dtype, p, elem_ptr(a), elem_ptr(b), elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+int ctb_unary(int op, const ctb_view* a, double scalar, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(a, "unary_op: null input", "unary_op"))) return rc;
+    if (op < 0 || op >= CTB_UNARY_OP_COUNT) return set_error(CTB_ERR_ARG, "unary_op: unknown operator code %d", op);
+    const ctb_view* in[1] = {a};
+    Plan p;
+    if ((rc = build_plan(in, 1, &p))) return rc;
+    if ((rc = check_out(out, p.numel, a->dtype, "unary_op"))) return rc;
+    return launch_unary(op, a->dtype, p, elem_ptr(a), scalar, elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+int ctb_copy_strided(const ctb_view* src, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(src, "copy: null input", "copy"))) return rc;
+    const ctb_view* in[1] = {src};
+    Plan p;
+    if ((rc = build_plan(in, 1, &p))) return rc;
+    if ((rc = check_out(out, p.numel, src->dtype, "copy"))) return rc;
+    return launch_copy((int)dtype_bytes(src->dtype), p, elem_ptr(src), elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+size_t ctb_reduce_workspace_bytes(const ctb_view* a, int dim) {
+    if (check_view(a, "reduction: null input", "reduction")) return 0;
+    if (dim != CTB_DIM_FULL && (dim < 0 || dim >= a->ndim)) return 0;
+    size_t copy_bytes;
+    return reduce_ws_need(a, dim, &copy_bytes);
+}
+
+int ctb_reduce_ws(int op, const ctb_view* a, int dim, const ctb_view* out, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    int rc;
+    if ((rc = reduce_arg_check(op, a, dim))) return rc;
+    if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    return do_reduce(op, a, dim, out, nullptr, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int ctb_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = reduce_arg_check(op, a, dim))) return rc;
+    if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    size_t copy_bytes;
+    const size_t need = reduce_ws_need(a, dim, &copy_bytes);
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(need, &ws))) return rc;
+    return do_reduce(op, a, dim, out, nullptr, ws, need, (cudaStream_t)stream);
+}
+
+int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* stream) {
+    int rc;
+    if ((rc = reduce_arg_check(op, a, CTB_DIM_FULL))) return rc;
+    if (!partial) return set_error(CTB_ERR_NULL, "reduction: null partial pointer");
+    if (op != CTB_SUM && op != CTB_MEAN && op != CTB_MAX && op != CTB_MIN)
+        return set_error(CTB_ERR_ARG, "reduction: fp64 partials exist for sum/mean/max/min only");
+    if (a->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "reduction: fp64 partials need a Float32 input");
+    size_t copy_bytes;
+    const size_t need = reduce_ws_need(a, CTB_DIM_FULL, &copy_bytes);
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(need, &ws))) return rc;
+    return do_reduce(op, a, CTB_DIM_FULL, nullptr, partial, ws, need, (cudaStream_t)stream);
+}
+
+int ctb_finalize_full(int op, const double* partial, int64_t total_count, const ctb_view* out, void* stream) {
+    int rc;
+    if (!partial) return set_error(CTB_ERR_NULL, "reduction: null partial pointer");
+    if ((rc = check_view(out, "output: null view", "finalize"))) return rc;
+    if (view_numel(out) != 1) return set_error(CTB_ERR_SHAPE, "finalize: output must hold one element");
+    return launch_finalize_full(op, out->dtype, partial, total_count, elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+int ctb_softmax_lastdim(const ctb_view* x, const ctb_view* mask, int causal, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(x, "softmax: null input", "softmax"))) return rc;
+    if (mask && (rc = check_view(mask, "softmax: null mask", "softmax"))) return rc;
+    RowsGeom g;
+    if ((rc = rows_geom(x, mask, &g, "softmax"))) return rc;
+    if ((rc = check_out(out, g.rows * g.cols, CTB_F32, "softmax"))) return rc;
+    return launch_softmax(g, (const float*)elem_ptr(x), mask ? (const float*)elem_ptr(mask) : nullptr,
+                          causal, (float*)elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_view* beta, double eps,
+                          const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(x, "layernorm: null input", "layernorm"))) return rc;
+    RowsGeom g;
+    if ((rc = rows_geom(x, nullptr, &g, "layernorm"))) return rc;
+    const ctb_view* gb[2] = {gamma, beta};
+    int64_t st[2] = {0, 0};
+    for (int i = 0; i < 2; ++i) {
+        if (!gb[i]) continue;
+        if ((rc = check_view(gb[i], "layernorm: null scale/shift", "layernorm"))) return rc;
+        if (gb[i]->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "layernorm: scale/shift must be Float32");
+        if (view_numel(gb[i]) != g.cols || gb[i]->ndim < 1 || gb[i]->shape[gb[i]->ndim - 1] != g.cols)
+            return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+        st[i] = gb[i]->stride[gb[i]->ndim - 1];
+    }
+    if ((rc = check_out(out, g.rows * g.cols, CTB_F32, "layernorm"))) return rc;
+    return launch_layernorm(g, (const float*)elem_ptr(x), gamma ? (const float*)elem_ptr(gamma) : nullptr, st[0],
+                            beta ? (const float*)elem_ptr(beta) : nullptr, st[1], eps,
+                            (float*)elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+// ---- host-buffer entry points --------------------------------------------------------------------------
+static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* b, double scalar,
+                            const ctb_view* out, int device) {
+    int rc;
+    const char* who = nin == 2 ? "binary_op" : "unary_op";
+    if ((rc = check_view(a, nin == 2 ? "binary_op: null input" : "unary_op: null input", who))) return rc;
+    if (nin == 2 && (rc = check_view(b, "binary_op: null input", who))) return rc;
+    if (nin == 2 && a->dtype != b->dtype) return set_error(CTB_ERR_DTYPE, "binary_op: operands must have the same dtype");
+    const ctb_view* in[2] = {a, b};
+    Plan p;
+    if ((rc = build_plan(in, nin, &p))) return rc;
+    if ((rc = check_out(out, p.numel, a->dtype, who))) return rc;
+    if (p.numel == 0) return CTB_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
+    const size_t es = dtype_bytes(a->dtype);
+    char* stage;
+    cudaStream_t* streams;
+
+    bool flat = p.ndim == 1;
+    for (int i = 0; i < nin; ++i) if (p.stride[i][0] != 1) flat = false;
+    if (flat && p.numel > kHostChunkElems) {
+        // pipelined: chunk c uses stage slot c % 3 on stream c % 3 (upload -> kernel -> download)
+        const int64_t chunk = kHostChunkElems;
+        const size_t slot = align_up((size_t)chunk * es, 256) * (nin + 1);
+        if ((rc = ensure_stage(device, slot * 3, (void**)&stage, &streams))) return rc;
+        const char* ha = (const char*)elem_ptr(a);
+        const char* hb = nin == 2 ? (const char*)elem_ptr(b) : nullptr;
+        char* ho = (char*)elem_ptr_mut(out);
+        int64_t c = 0;
+        for (int64_t lo = 0; lo < p.numel; lo += chunk, ++c) {
+            const int64_t n = p.numel - lo < chunk ? p.numel - lo : chunk;
+            cudaStream_t st = streams[c % 3];
+            char* base = stage + slot * (c % 3);
+            char* da = base;
+            char* db = base + align_up((size_t)chunk * es, 256);
+            char* dout = base + align_up((size_t)chunk * es, 256) * nin;
+            CTB_CUDA_TRY(cudaMemcpyAsync(da, ha + (size_t)lo * es, (size_t)n * es, cudaMemcpyHostToDevice, st));
+            if (nin == 2) CTB_CUDA_TRY(cudaMemcpyAsync(db, hb + (size_t)lo * es, (size_t)n * es, cudaMemcpyHostToDevice, st));
+            Plan cp = p;
+            cp.numel = n;
+            cp.shape[0] = n;
+            rc = nin == 2 ? launch_binary(op, a->dtype, cp, da, db, dout, st)
+                          : launch_unary(op, a->dtype, cp, da, scalar, dout, st);
+            if (rc) return rc;
+            CTB_CUDA_TRY(cudaMemcpyAsync(ho + (size_t)lo * es, dout, (size_t)n * es, cudaMemcpyDeviceToHost, st));
+        }
+        for (int i = 0; i < 3; ++i) CTB_CUDA_TRY(cudaStreamSynchronize(streams[i]));
+        return CTB_OK;
+    }
+    // general case: upload the touched storage spans, run once, download
+    const size_t out_bytes = align_up((size_t)p.numel * es, 256);
+    const size_t total = span_bytes(a) + (nin == 2 ? span_bytes(b) : 0) + out_bytes;
+    if ((rc = ensure_stage(device, total, (void**)&stage, &streams))) return rc;
+    cudaStream_t st = streams[0];
+    size_t used = 0;
+    ctb_view da, db, dout = *out;
+    if ((rc = upload_view(a, stage, &used, &da, st))) return rc;
+    if (nin == 2 && (rc = upload_view(b, stage, &used, &db, st))) return rc;
+    dout.base = stage + used;
+    dout.offset = 0;
+    rc = nin == 2 ? ctb_binary(op, &da, &db, &dout, st) : ctb_unary(op, &da, scalar, &dout, st);
+    if (rc) return rc;
+    CTB_CUDA_TRY(cudaMemcpyAsync(elem_ptr_mut(out), dout.base, (size_t)p.numel * es, cudaMemcpyDeviceToHost, st));
+    CTB_CUDA_TRY(cudaStreamSynchronize(st));
+    return CTB_OK;
+}
+
+int ctb_binary_host(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, int device) {
+    if (op < 0 || op >= CTB_BINARY_OP_COUNT) return set_error(CTB_ERR_ARG, "binary_op: unknown operator code %d", op);
+    return host_elementwise(2, op, a, b, 0.0, out, device);
+}
+
+int ctb_unary_host(int op, const ctb_view* a, double scalar, const ctb_view* out, int device) {
+    if (op < 0 || op >= CTB_UNARY_OP_COUNT) return set_error(CTB_ERR_ARG, "unary_op: unknown operator code %d", op);
+    return host_elementwise(1, op, a, nullptr, scalar, out, device);
+}
+
+int ctb_reduce_host(int op, const ctb_view* a, int dim, const ctb_view* out, int device) {
+    int rc;
+    if ((rc = reduce_arg_check(op, a, dim))) return rc;
+    if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
+    const size_t oes = dtype_bytes(out->dtype);
+    const int64_t nout = view_numel(out);
+    char* stage;
+    cudaStream_t* streams;
+    const size_t total = span_bytes(a) + align_up((size_t)nout * oes, 256);
+    if ((rc = ensure_stage(device, total, (void**)&stage, &streams))) return rc;
+    cudaStream_t st = streams[0];
+    size_t used = 0;
+    ctb_view da, dout = *out;
+    if ((rc = upload_view(a, stage, &used, &da, st))) return rc;
+    dout.base = stage + used;
+    dout.offset = 0;
+    if ((rc = ctb_reduce(op, &da, dim, &dout, st))) return rc;
+    CTB_CUDA_TRY(cudaMemcpyAsync(elem_ptr_mut(out), dout.base, (size_t)nout * oes, cudaMemcpyDeviceToHost, st));
+    CTB_CUDA_TRY(cudaStreamSynchronize(st));
+    return CTB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,374 @@
+// Elementwise kernels of the operator path (binary broadcast ops, unary ops, strided copy).
+//
+// Three kernel shapes, picked by the host from the collapsed iteration plan:
+//   ew_flat  : every operand is contiguous (or a single broadcast element) -> one flat index
+//              space, 128/256-bit streaming loads and stores, several loads in flight per thread.
+//   ew_rows  : [outer dims..., inner] where every operand's inner stride is 0 or 1
+//              (row broadcast [R,C]o[1,C], column broadcast [R,C]o[R,1], permuted views whose
+//              innermost dim is contiguous, bias adds).  Offsets are computed once per
+//              (row, column-chunk) tile, the inner dim is accessed with vector loads when the
+//              alignment allows it.
+//   ew_gather: anything else — one div/mod chain per element (the "strided-gather" path).
+//
+// These replace binary_op_impl / unary_op_impl (src/core/opsmp.cpp:136-385 of the reference),
+// the AVX2 contiguous/general paths (src/cpu/AVX2/ops_avx2_f32.cpp:357-568) and
+// Tensor::clone's odometer copy (src/core/tensor.cpp:84-113).
+#include "ctb_common.cuh"
+#include "ctb_math.cuh"
+
+namespace ctb {
+
+// Tunables (overridable at build time for sweeps).
+#ifndef CTB_EW_THREADS
+#define CTB_EW_THREADS 256
+#endif
+#ifndef CTB_EW_VEC_BYTES
+#define CTB_EW_VEC_BYTES 16
+#endif
+#ifndef CTB_EW_UNROLL
+#define CTB_EW_UNROLL 4
+#endif
+#ifndef CTB_EW_CTAS_PER_SM
+#define CTB_EW_CTAS_PER_SM 8
+#endif
+
+// ------------------------------------------------------------------------------------------------
+// ew_flat: out[i] = f(a[i * sa], b[i * sb]) with sa, sb in {0, 1}.
+// A CTA owns tiles of THREADS*VEC*UNROLL consecutive elements (grid-stride over tiles); within
+// a tile, pass u of thread t touches vector (u*THREADS + t) so every warp-level access is one
+// fully coalesced 512 B / 1 KiB request, and all UNROLL*NIN loads are issued before first use.
+// ------------------------------------------------------------------------------------------------
+template <typename F, typename T, int NIN, int VEC, int UNROLL, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+ew_flat_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
+               int64_t n, int a_bcast, int b_bcast, double scalar) {
+    using V = Vec<T, VEC>;
+    constexpr int64_t TILE = (int64_t)THREADS * VEC * UNROLL;
+    const int64_t full_tiles = n / TILE;
+    T a0 = a_bcast ? a[0] : T(0);
+    T b0 = (NIN == 2 && b_bcast) ? b[0] : T(0);
+
+    for (int64_t tile = blockIdx.x; tile < full_tiles; tile += gridDim.x) {
+        const int64_t base = tile * TILE + (int64_t)threadIdx.x * VEC;
+        V va[UNROLL], vb[UNROLL];
+        if (!a_bcast) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                va[u] = ldg_stream(reinterpret_cast<const V*>(a + base + (int64_t)u * THREADS * VEC));
+        }
+        if (NIN == 2 && !b_bcast) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                vb[u] = ldg_stream(reinterpret_cast<const V*>(b + base + (int64_t)u * THREADS * VEC));
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            V r;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                T x = a_bcast ? a0 : va[u].v[k];
+                if (NIN == 2) {
+                    T y = b_bcast ? b0 : vb[u].v[k];
+                    r.v[k] = F::apply2(x, y);
+                } else {
+                    r.v[k] = F::apply1(x, scalar);
+                }
+            }
+            stg_stream(reinterpret_cast<V*>(out + base + (int64_t)u * THREADS * VEC), r);
+        }
+    }
+    // ragged tail (< TILE elements): scalar, handled by the first CTA
+    if (blockIdx.x == 0) {
+        for (int64_t i = full_tiles * TILE + threadIdx.x; i < n; i += THREADS) {
+            T x = a_bcast ? a0 : a[i];
+            if (NIN == 2) {
+                T y = b_bcast ? b0 : b[i];
+                out[i] = F::apply2(x, y);
+            } else {
+                out[i] = F::apply1(x, scalar);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// ew_rows: plan dims = [outer..., inner]; inner strides are 0/1 for every input.
+// A tile is VEC*THREADS consecutive inner elements of one row.  tile -> (row, chunk) by one
+// 32-bit div, row -> per-operand offsets by ndim-1 div/mods, both once per thread per tile.
+// ------------------------------------------------------------------------------------------------
+struct RowsArgs {
+    int32_t nouter;                         // number of outer dims (plan.ndim - 1)
+    uint32_t oshape[CTB_MAX_DIMS];          // outer shapes, outer -> inner
+    int64_t ostride[2][CTB_MAX_DIMS];       // per input
+    int32_t istride[2];                     // inner stride per input: 0 or 1
+    uint32_t inner;                         // inner length
+    uint32_t tiles_per_row;
+    uint32_t ntiles;                        // rows * tiles_per_row (< 2^32)
+};
+
+template <typename F, typename T, int NIN, int VEC, int UNROLL, int THREADS, bool ALIGNED>
+__global__ void __launch_bounds__(THREADS)
+ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
+               RowsArgs g, double scalar) {
+    using V = Vec<T, VEC>;
+    constexpr uint32_t TILE = THREADS * VEC;
+    for (uint32_t t0 = blockIdx.x * UNROLL; t0 < g.ntiles; t0 += gridDim.x * UNROLL) {
+        V va[UNROLL], vb[UNROLL];
+        int64_t oo[UNROLL];
+        uint32_t cnt[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const uint32_t t = t0 + u;
+            cnt[u] = 0;
+            if (t >= g.ntiles) continue;
+            uint32_t row = t / g.tiles_per_row;
+            const uint32_t col = (t - row * g.tiles_per_row) * TILE + threadIdx.x * VEC;
+            oo[u] = (int64_t)row * g.inner + col;
+            int64_t oa = 0, ob = 0;
+            for (int d = g.nouter - 1; d >= 0; --d) {
+                const uint32_t q = row / g.oshape[d];
+                const uint32_t c = row - q * g.oshape[d];
+                row = q;
+                oa += (int64_t)c * g.ostride[0][d];
+                if (NIN == 2) ob += (int64_t)c * g.ostride[1][d];
+            }
+            if (col >= g.inner) continue;
+            const uint32_t left = g.inner - col;
+            cnt[u] = left < (uint32_t)VEC ? left : (uint32_t)VEC;
+            const T* pa = a + oa + (g.istride[0] ? col : 0);
+            const T* pb = (NIN == 2) ? b + ob + (g.istride[1] ? col : 0) : nullptr;
+            if (ALIGNED && cnt[u] == VEC) {
+                if (g.istride[0]) va[u] = ldg_stream(reinterpret_cast<const V*>(pa));
+                else {
+                    const T s = *pa;
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) va[u].v[k] = s;
+                }
+                if (NIN == 2) {
+                    if (g.istride[1]) vb[u] = ldg_stream(reinterpret_cast<const V*>(pb));
+                    else {
+                        const T s = *pb;
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) vb[u].v[k] = s;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    if ((uint32_t)k < cnt[u]) {
+                        va[u].v[k] = pa[g.istride[0] ? k : 0];
+                        if (NIN == 2) vb[u].v[k] = pb[g.istride[1] ? k : 0];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (cnt[u] == 0) continue;
+            V r;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                if (NIN == 2) r.v[k] = F::apply2(va[u].v[k], vb[u].v[k]);
+                else r.v[k] = F::apply1(va[u].v[k], scalar);
+            }
+            if (ALIGNED && cnt[u] == VEC) {
+                stg_stream(reinterpret_cast<V*>(out + oo[u]), r);
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k)
+                    if ((uint32_t)k < cnt[u]) out[oo[u] + k] = r.v[k];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// ew_gather: fully general strided operands; one output element per thread per step.
+// ------------------------------------------------------------------------------------------------
+template <typename F, typename T, int NIN>
+__global__ void __launch_bounds__(256)
+ew_gather_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
+                 Plan p, double scalar) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.numel; i += step) {
+        int64_t t = i, oa = 0, ob = 0;
+        for (int d = p.ndim - 1; d >= 0; --d) {
+            const int64_t q = t / p.shape[d];
+            const int64_t c = t - q * p.shape[d];
+            t = q;
+            oa += c * p.stride[0][d];
+            if (NIN == 2) ob += c * p.stride[1][d];
+        }
+        if (NIN == 2) out[i] = F::apply2(a[oa], b[ob]);
+        else out[i] = F::apply1(a[oa], scalar);
+    }
+}
+
+// ---- functor adapters ----------------------------------------------------------------------------
+template <int OP, typename T> struct BinAdapter {
+    __device__ __forceinline__ static T apply2(T x, T y) { return BinaryFn<OP, T>::apply(x, y); }
+    __device__ __forceinline__ static T apply1(T x, double) { return x; }
+};
+template <int OP, typename T> struct UnAdapter {
+    __device__ __forceinline__ static T apply2(T x, T) { return x; }
+    __device__ __forceinline__ static T apply1(T x, double s) { return UnaryFn<OP, T>::apply(x, s); }
+};
+template <typename T> struct CopyAdapter {
+    __device__ __forceinline__ static T apply2(T x, T) { return x; }
+    __device__ __forceinline__ static T apply1(T x, double) { return x; }
+};
+
+// ---- host-side shape classification and launch ----------------------------------------------------
+namespace {
+
+int grid_for(int64_t work_items, int ctas_per_sm) {
+    DeviceInfo di;
+    if (current_device_info(&di) != CTB_OK) return -1;
+    int64_t cap = (int64_t)di.sm_count * ctas_per_sm;
+    int64_t g = work_items < cap ? work_items : cap;
+    return (int)(g < 1 ? 1 : g);
+}
+
+bool plan_is_flat(const Plan& p) {
+    if (p.ndim != 1) return false;
+    for (int i = 0; i < p.nin; ++i)
+        if (p.stride[i][0] != 0 && p.stride[i][0] != 1) return false;
+    return true;
+}
+
+bool plan_is_rows(const Plan& p) {
+    if (p.ndim < 2) return false;
+    for (int i = 0; i < p.nin; ++i) {
+        int64_t s = p.stride[i][p.ndim - 1];
+        if (s != 0 && s != 1) return false;
+    }
+    if (p.shape[p.ndim - 1] < 32) return false;              // tiny rows: gather is as good
+    if (p.shape[p.ndim - 1] > 0xFFFFFFFFll) return false;
+    for (int d = 0; d < p.ndim - 1; ++d) if (p.shape[d] > 0xFFFFFFFFll) return false;
+    return true;
+}
+
+template <typename F, typename T, int NIN>
+int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, cudaStream_t st) {
+    constexpr int THREADS = CTB_EW_THREADS;
+    constexpr int VEC = CTB_EW_VEC_BYTES / (int)sizeof(T);
+    constexpr int UNROLL = CTB_EW_UNROLL;
+    if (p.numel == 0) return CTB_OK;
+
+    if (plan_is_flat(p)) {
+        const int a_b = p.stride[0][0] == 0 && p.numel > 1;
+        const int b_b = NIN == 2 && p.stride[1][0] == 0 && p.numel > 1;
+        const bool aligned = is_aligned(out, CTB_EW_VEC_BYTES) && (a_b || is_aligned(a, CTB_EW_VEC_BYTES)) &&
+                             (NIN == 1 || b_b || is_aligned(b, CTB_EW_VEC_BYTES));
+        if (aligned) {
+            constexpr int64_t TILE = (int64_t)THREADS * VEC * UNROLL;
+            int grid = grid_for(p.numel / TILE > 0 ? p.numel / TILE : 1, CTB_EW_CTAS_PER_SM);
+            if (grid < 0) return CTB_ERR_CUDA;
+            ew_flat_kernel<F, T, NIN, VEC, UNROLL, THREADS><<<grid, THREADS, 0, st>>>(a, b, out, p.numel, a_b, b_b, scalar);
+        } else {
+            // misaligned base (an odd view offset): scalar accesses, still coalesced
+            int grid = grid_for(ceil_div(p.numel, (int64_t)THREADS * UNROLL), CTB_EW_CTAS_PER_SM);
+            if (grid < 0) return CTB_ERR_CUDA;
+            ew_flat_kernel<F, T, NIN, 1, UNROLL, THREADS><<<grid, THREADS, 0, st>>>(a, b, out, p.numel, a_b, b_b, scalar);
+        }
+        return cuda_error(cudaGetLastError(), "ew_flat launch");
+    }
+
+    if (plan_is_rows(p)) {
+        RowsArgs g{};
+        const int nd = p.ndim;
+        g.nouter = nd - 1;
+        int64_t rows = 1;
+        bool aligned = is_aligned(out, CTB_EW_VEC_BYTES) && is_aligned(a, CTB_EW_VEC_BYTES) &&
+                       (NIN == 1 || is_aligned(b, CTB_EW_VEC_BYTES)) && (p.shape[nd - 1] % VEC == 0);
+        for (int d = 0; d < nd - 1; ++d) {
+            g.oshape[d] = (uint32_t)p.shape[d];
+            rows *= p.shape[d];
+            for (int i = 0; i < NIN; ++i) {
+                g.ostride[i][d] = p.stride[i][d];
+                if (p.stride[i][d] % VEC != 0) aligned = false;
+            }
+        }
+        for (int i = 0; i < NIN; ++i) g.istride[i] = (int32_t)p.stride[i][nd - 1];
+        g.inner = (uint32_t)p.shape[nd - 1];
+        constexpr int64_t TILE = (int64_t)THREADS * VEC;
+        const int64_t tpr = ceil_div(p.shape[nd - 1], TILE);
+        const int64_t ntiles = rows * tpr;
+        if (ntiles < 0xFFFFFFFFll - 4096) {
+            g.tiles_per_row = (uint32_t)tpr;
+            g.ntiles = (uint32_t)ntiles;
+            int grid = grid_for(ceil_div(ntiles, UNROLL), CTB_EW_CTAS_PER_SM);
+            if (grid < 0) return CTB_ERR_CUDA;
+            if (aligned)
+                ew_rows_kernel<F, T, NIN, VEC, UNROLL, THREADS, true><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
+            else
+                ew_rows_kernel<F, T, NIN, VEC, UNROLL, THREADS, false><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
+            return cuda_error(cudaGetLastError(), "ew_rows launch");
+        }
+    }
+
+    int grid = grid_for(ceil_div(p.numel, 256), 16);
+    if (grid < 0) return CTB_ERR_CUDA;
+    ew_gather_kernel<F, T, NIN><<<grid, 256, 0, st>>>(a, b, out, p, scalar);
+    return cuda_error(cudaGetLastError(), "ew_gather launch");
+}
+
+template <int OP>
+int launch_binary_dt(int dtype, const Plan& p, const void* a, const void* b, void* out, cudaStream_t st) {
+    switch (dtype) {
+    case CTB_F32: return launch_shapes<BinAdapter<OP, float>, float, 2>(p, (const float*)a, (const float*)b, (float*)out, 0.0, st);
+    case CTB_I32: return launch_shapes<BinAdapter<OP, int32_t>, int32_t, 2>(p, (const int32_t*)a, (const int32_t*)b, (int32_t*)out, 0.0, st);
+    case CTB_F64: return launch_shapes<BinAdapter<OP, double>, double, 2>(p, (const double*)a, (const double*)b, (double*)out, 0.0, st);
+    }
+    return set_error(CTB_ERR_DTYPE, "binary op: unsupported dtype or op not registered");
+}
+
+template <int OP>
+int launch_unary_dt(int dtype, const Plan& p, const void* a, double s, void* out, cudaStream_t st) {
+    switch (dtype) {
+    case CTB_F32: return launch_shapes<UnAdapter<OP, float>, float, 1>(p, (const float*)a, nullptr, (float*)out, s, st);
+    case CTB_I32: return launch_shapes<UnAdapter<OP, int32_t>, int32_t, 1>(p, (const int32_t*)a, nullptr, (int32_t*)out, s, st);
+    case CTB_F64: return launch_shapes<UnAdapter<OP, double>, double, 1>(p, (const double*)a, nullptr, (double*)out, s, st);
+    }
+    return set_error(CTB_ERR_DTYPE, "unary op: unsupported dtype");
+}
+
+}  // namespace
+
+int launch_binary(int op, int dtype, const Plan& p, const void* a, const void* b, void* out, cudaStream_t st) {
+    switch (op) {
+#define CASE(OP) case OP: return launch_binary_dt<OP>(dtype, p, a, b, out, st);
+    CASE(CTB_ADD) CASE(CTB_SUB) CASE(CTB_MUL) CASE(CTB_DIV)
+    CASE(CTB_LT) CASE(CTB_LE) CASE(CTB_GT) CASE(CTB_GE) CASE(CTB_EQ) CASE(CTB_NE)
+#undef CASE
+    }
+    return set_error(CTB_ERR_ARG, "binary op: unknown operator code %d", op);
+}
+
+int launch_unary(int op, int dtype, const Plan& p, const void* a, double s, void* out, cudaStream_t st) {
+    if (unary_is_f32_only(op) && dtype != CTB_F32)
+        return set_error(CTB_ERR_DTYPE, "unary op %d: only Float32 has a pinned flavour", op);
+    switch (op) {
+#define CASE(OP) case OP: return launch_unary_dt<OP>(dtype, p, a, s, out, st);
+    CASE(CTB_ADD_S) CASE(CTB_SUB_S) CASE(CTB_RSUB_S) CASE(CTB_MUL_S) CASE(CTB_DIV_S) CASE(CTB_RDIV_S)
+    CASE(CTB_POW_S) CASE(CTB_RPOW_S)
+    CASE(CTB_LT_S) CASE(CTB_LE_S) CASE(CTB_GT_S) CASE(CTB_GE_S) CASE(CTB_EQ_S) CASE(CTB_NE_S)
+    CASE(CTB_ABS) CASE(CTB_RELU) CASE(CTB_SQRT)
+#undef CASE
+    // fp32-only flavours: instantiate for float alone
+#define CASEF(OP) case OP: return launch_shapes<UnAdapter<OP, float>, float, 1>(p, (const float*)a, nullptr, (float*)out, s, st);
+    CASEF(CTB_EXP) CASEF(CTB_LOG) CASEF(CTB_TANH) CASEF(CTB_SIGMOID) CASEF(CTB_GELU_TANH)
+#undef CASEF
+    }
+    return set_error(CTB_ERR_ARG, "unary op: unknown operator code %d", op);
+}
+
+int launch_copy(int elem_bytes, const Plan& p, const void* a, void* out, cudaStream_t st) {
+    if (elem_bytes == 4)
+        return launch_shapes<CopyAdapter<uint32_t>, uint32_t, 1>(p, (const uint32_t*)a, nullptr, (uint32_t*)out, 0.0, st);
+    if (elem_bytes == 8)
+        return launch_shapes<CopyAdapter<uint64_t>, uint64_t, 1>(p, (const uint64_t*)a, nullptr, (uint64_t*)out, 0.0, st);
+    return set_error(CTB_ERR_DTYPE, "copy: unsupported element size %d", elem_bytes);
+}
+
+}  // namespace ctb

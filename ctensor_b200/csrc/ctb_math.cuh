@@ -1,0 +1,207 @@
+// Device-side arithmetic of the operator path.  Every function states the reference code whose
+// results it reproduces bit-for-bit (paths relative to the reference repository).  The library
+// is compiled with -fmad=false -prec-div=true -prec-sqrt=true -ftz=false; fused multiply-adds
+// below are explicit (fmaf) and unfused operations use the _rn intrinsics so that no compiler
+// setting can change a rounding point.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <math.h>
+#include "../../include/ctb200.h"
+
+namespace ctb {
+
+// ---- fp32 transcendental flavours -------------------------------------------------------------
+// exp512_ps, src/cpu/AVX512/ops_avx512_f32.cpp:63-92 (== exp256_ps, src/cpu/AVX2/
+// ops_avx2_f32.cpp:58-100, as GCC contracts it under the shipped -O3 -mfma flags).
+// SSE min/max return the second operand on an unordered compare, hence the selects.
+__device__ __forceinline__ float exp_cephes(float x) {
+    const float HI = 88.3762626647949f, LO = -88.3762626647949f;
+    x = (x < HI) ? x : HI;
+    x = (x > LO) ? x : LO;
+    float fx = fmaf(x, 1.44269504088896341f, 0.5f);
+    // floor(fx) without the conversion pipe: |fx| <= 129, so adding 1.5*2^23 rounds to the
+    // nearest integer (exactly), and one compare corrects nearest -> floor.
+    const float MAGIC = 12582912.0f;
+    float r = __fadd_rn(fx, MAGIC);
+    int32_t n = __float_as_int(r) - 0x4B400000;    // integer nearest to fx
+    r = __fsub_rn(r, MAGIC);
+    if (r > fx) { r = __fsub_rn(r, 1.0f); n -= 1; }
+    fx = r;
+    x = fmaf(-fx, 0.693359375f, x);
+    x = fmaf(-fx, -2.12194440e-4f, x);
+    float z = __fmul_rn(x, x);
+    float y = 1.9875691500E-4f;
+    y = fmaf(y, x, 1.3981999507E-3f);
+    y = fmaf(y, x, 8.3334519073E-3f);
+    y = fmaf(y, x, 4.1665795894E-2f);
+    y = fmaf(y, x, 1.6666665459E-1f);
+    y = fmaf(y, x, 0.5f);
+    y = fmaf(y, z, x);
+    y = __fadd_rn(y, 1.0f);
+    float pow2n = __int_as_float((n + 127) << 23);
+    return __fmul_rn(y, pow2n);
+}
+
+// log256_ps, src/cpu/AVX2/ops_avx2_f32.cpp:103-158 as compiled with the shipped flags:
+// the y*z product is fused into the following add, e*Q1 is rounded on its own.
+__device__ __forceinline__ float log_cephes(float x) {
+    bool invalid = (x <= 0.0f);
+    x = (x > 1.17549435e-38f) ? x : 1.17549435e-38f;
+    uint32_t bits = __float_as_uint(x);
+    int32_t emm0 = (int32_t)(bits >> 23) - 127;
+    x = __uint_as_float((bits & 0x7fffffu) | 0x3f000000u);
+    float e = __fadd_rn(__int2float_rn(emm0), 1.0f);
+    bool m = (x < 0.707106781186547524f);
+    float tmp = m ? x : 0.0f;
+    x = __fsub_rn(x, 1.0f);
+    e = __fsub_rn(e, m ? 1.0f : 0.0f);
+    x = __fadd_rn(x, tmp);
+    float z = __fmul_rn(x, x);
+    float y = 7.0376836292E-2f;
+    y = fmaf(y, x, -1.1514610310E-1f);
+    y = fmaf(y, x, 1.1676998740E-1f);
+    y = fmaf(y, x, -1.2420140846E-1f);
+    y = fmaf(y, x, 1.4249322787E-1f);
+    y = fmaf(y, x, -1.6668057665E-1f);
+    y = fmaf(y, x, 2.0000714765E-1f);
+    y = fmaf(y, x, -2.4999993993E-1f);
+    y = fmaf(y, x, 3.3333331174E-1f);
+    y = __fmul_rn(y, x);
+    float t = __fmul_rn(e, -2.12194440e-4f);
+    y = fmaf(y, z, t);
+    y = fmaf(-z, 0.5f, y);
+    x = __fadd_rn(x, y);
+    x = fmaf(e, 0.693359375f, x);
+    return invalid ? __uint_as_float(0xFFFFFFFFu) : x;
+}
+
+// tanh512_ps, src/cpu/AVX512/ops_avx512_f32.cpp:187-193
+__device__ __forceinline__ float tanh_cephes(float x) {
+    float e = exp_cephes(__fmul_rn(x, 2.0f));
+    return __fdiv_rn(__fsub_rn(e, 1.0f), __fadd_rn(e, 1.0f));
+}
+
+// sigmoid512_ps, src/cpu/AVX512/ops_avx512_f32.cpp:195-201
+__device__ __forceinline__ float sigmoid_cephes(float x) {
+    float e = exp_cephes(__uint_as_float(__float_as_uint(x) ^ 0x80000000u));
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+}
+
+// (float)((double)x * s): mult_scalar_mp, src/core/opsmp.cpp:297,433-436
+__device__ __forceinline__ float mul_scalar_f32(float x, double s) {
+    return __double2float_rn(__dmul_rn((double)x, s));
+}
+
+// Tanh-form GELU as the chain mul, mul, mul_scalar(0.044715), add, mul_scalar(sqrt(2/pi)),
+// tanh, add_scalar(1), mul_scalar(x, 0.5), mul with fp32 rounding after every step.
+// (double)t + 1.0 and (double)x * 0.5 rounded to fp32 equal the fp32 operations: a double
+// holds any fp32 sum/product to more than 2*24+2 bits, so the second rounding is innocuous.
+__device__ __forceinline__ float gelu_tanh_chain(float x) {
+    float u = __fmul_rn(x, x);
+    u = __fmul_rn(u, x);
+    u = mul_scalar_f32(u, 0.044715);
+    u = __fadd_rn(x, u);
+    u = mul_scalar_f32(u, 0.7978845608028654);
+    float t = tanh_cephes(u);
+    t = __fadd_rn(t, 1.0f);
+    float h = __fmul_rn(x, 0.5f);
+    return __fmul_rn(h, t);
+}
+
+// static_cast<int32_t>(double) as x86 cvttsd2si does it (write_scalar_at,
+// src/core/tensor.h:77): truncation, INT32_MIN for NaN / out of range.
+__device__ __forceinline__ int32_t d2i_x86(double v) {
+    return (v > -2147483649.0 && v < 2147483648.0) ? __double2int_rz(v) : INT32_MIN;
+}
+
+// ---- typed load/convert -----------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ double to_double(T v) { return (double)v; }
+template <typename T> __device__ __forceinline__ T from_double(double v);
+template <> __device__ __forceinline__ float from_double<float>(double v) { return __double2float_rn(v); }
+template <> __device__ __forceinline__ double from_double<double>(double v) { return v; }
+template <> __device__ __forceinline__ int32_t from_double<int32_t>(double v) { return d2i_x86(v); }
+
+// ---- binary functors: out = (T) op((double)a, (double)b), src/core/opsmp.cpp:198,249-252 --------
+// For fp32 the four arithmetic ops are evaluated directly in fp32: the double-precision result
+// rounded to fp32 equals the IEEE fp32 operation (double rounding is innocuous for + - * /).
+template <int OP, typename T> struct BinaryFn {
+    __device__ __forceinline__ static T apply(T a, T b) {
+        double x = to_double(a), y = to_double(b), r;
+        if (OP == CTB_ADD) r = __dadd_rn(x, y);
+        else if (OP == CTB_SUB) r = __dsub_rn(x, y);
+        else if (OP == CTB_MUL) r = __dmul_rn(x, y);
+        else if (OP == CTB_DIV) r = __ddiv_rn(x, y);
+        else if (OP == CTB_LT) r = x < y ? 1.0 : 0.0;
+        else if (OP == CTB_LE) r = x <= y ? 1.0 : 0.0;
+        else if (OP == CTB_GT) r = x > y ? 1.0 : 0.0;
+        else if (OP == CTB_GE) r = x >= y ? 1.0 : 0.0;
+        else if (OP == CTB_EQ) r = x == y ? 1.0 : 0.0;
+        else r = x != y ? 1.0 : 0.0;
+        return from_double<T>(r);
+    }
+};
+template <int OP> struct BinaryFn<OP, float> {
+    __device__ __forceinline__ static float apply(float a, float b) {
+        if (OP == CTB_ADD) return __fadd_rn(a, b);
+        if (OP == CTB_SUB) return __fsub_rn(a, b);
+        if (OP == CTB_MUL) return __fmul_rn(a, b);
+        if (OP == CTB_DIV) return __fdiv_rn(a, b);
+        if (OP == CTB_LT) return a < b ? 1.0f : 0.0f;
+        if (OP == CTB_LE) return a <= b ? 1.0f : 0.0f;
+        if (OP == CTB_GT) return a > b ? 1.0f : 0.0f;
+        if (OP == CTB_GE) return a >= b ? 1.0f : 0.0f;
+        if (OP == CTB_EQ) return a == b ? 1.0f : 0.0f;
+        return a != b ? 1.0f : 0.0f;
+    }
+};
+
+// ---- unary functors -----------------------------------------------------------------------------
+// Scalar ops: (T) op((double)x, s), src/core/opsmp.cpp:418-456; scalar comparisons :701-706;
+// abs/sqrt/relu :562,565,581-584.
+template <int OP> __device__ __forceinline__ double unary_double(double x, double s) {
+    if (OP == CTB_ADD_S) return __dadd_rn(x, s);
+    if (OP == CTB_SUB_S) return __dsub_rn(x, s);
+    if (OP == CTB_RSUB_S) return __dsub_rn(s, x);
+    if (OP == CTB_MUL_S) return __dmul_rn(x, s);
+    if (OP == CTB_DIV_S) return __ddiv_rn(x, s);
+    if (OP == CTB_RDIV_S) return __ddiv_rn(s, x);
+    if (OP == CTB_POW_S) return pow(x, s);
+    if (OP == CTB_RPOW_S) return pow(s, x);
+    if (OP == CTB_LT_S) return x < s ? 1.0 : 0.0;
+    if (OP == CTB_LE_S) return x <= s ? 1.0 : 0.0;
+    if (OP == CTB_GT_S) return x > s ? 1.0 : 0.0;
+    if (OP == CTB_GE_S) return x >= s ? 1.0 : 0.0;
+    if (OP == CTB_EQ_S) return x == s ? 1.0 : 0.0;
+    if (OP == CTB_NE_S) return x != s ? 1.0 : 0.0;
+    if (OP == CTB_ABS) return fabs(x);
+    if (OP == CTB_RELU) return x > 0 ? x : 0.0;
+    if (OP == CTB_SQRT) return __dsqrt_rn(x);
+    return x;
+}
+
+template <int OP, typename T> struct UnaryFn {
+    __device__ __forceinline__ static T apply(T x, double s) {
+        return from_double<T>(unary_double<OP>(to_double(x), s));
+    }
+};
+template <int OP> struct UnaryFn<OP, float> {
+    __device__ __forceinline__ static float apply(float x, double s) {
+        if (OP == CTB_ABS) return fabsf(x);
+        if (OP == CTB_RELU) return x > 0.0f ? x : 0.0f;       // NaN -> 0, -0 -> +0
+        if (OP == CTB_SQRT) return __fsqrt_rn(x);             // == (float)sqrt((double)x)
+        if (OP == CTB_EXP) return exp_cephes(x);
+        if (OP == CTB_LOG) return log_cephes(x);
+        if (OP == CTB_TANH) return tanh_cephes(x);
+        if (OP == CTB_SIGMOID) return sigmoid_cephes(x);
+        if (OP == CTB_GELU_TANH) return gelu_tanh_chain(x);
+        return __double2float_rn(unary_double<OP>((double)x, s));
+    }
+};
+
+__host__ __device__ inline bool unary_is_f32_only(int op) {
+    return op == CTB_EXP || op == CTB_LOG || op == CTB_TANH || op == CTB_SIGMOID ||
+           op == CTB_GELU_TANH;
+}
+
+}  // namespace ctb

@@ -1,0 +1,628 @@
+// Reduction kernels of the operator path: sum / mean / max / min / var / argmax along one dim
+// or over the whole tensor.  They replace reduction_op_impl (src/core/opsmp.cpp:593-697 of the
+// reference), the SIMD full reductions (src/cpu/AVX2/ops_avx2_f32.cpp:778-966,
+// src/cpu/AVX512/ops_avx512_f32.cpp:480-566) and argmax (src/core/ops_dispatch.cpp:427-526).
+//
+// Kernel shapes (picked on the host from the geometry):
+//   rows_warp  : reduce dim contiguous, short lines -> one warp per output, shuffle tree.
+//   rows_block : reduce dim contiguous, long lines  -> one CTA per output, shuffle + smem tree.
+//   rows_split : few, very long contiguous lines (full-tensor reductions) -> each line is cut
+//                into `splits` chunks, one CTA per chunk writes an fp64 partial to scratch;
+//                the CTA that takes the last ticket combines the partials IN INDEX ORDER.
+//   cols       : an outer dim is contiguous (e.g. dim 0 of a row-major matrix) -> threads are
+//                coalesced along that dim and walk the reduce dim; row chunks are split over
+//                CTAs and combined by the same ticket scheme.
+//   generic    : any other geometry or dtype: one thread per output.
+// Sums accumulate in fp64.  Every combine order is fixed by the launch geometry alone, so
+// results are identical from run to run.  No kernel waits on another block: the ticket is an
+// atomic counter that is read once, and the block that sees the last value does the combine.
+#include "ctb_reduce.cuh"
+#include "ctb_math.cuh"
+#include <cstring>
+
+namespace ctb {
+
+#ifndef CTB_RED_THREADS
+#define CTB_RED_THREADS 256
+#endif
+#ifndef CTB_RED_UNROLL
+#define CTB_RED_UNROLL 4
+#endif
+#ifndef CTB_RED_SPLIT_CTAS_PER_SM
+#define CTB_RED_SPLIT_CTAS_PER_SM 4
+#endif
+
+constexpr int kCounterSlots = 16384;                 // uint32 tickets at the start of scratch
+constexpr size_t kCounterBytes = kCounterSlots * sizeof(uint32_t);
+
+// ---- accumulation policies ------------------------------------------------------------------------
+// VT is the element type as the policy sees it (float on the fast paths, double on the generic
+// path).  add() receives the element's index along the reduced dim and the line's shift value.
+template <typename VT> struct SumPol {
+    struct Acc { double s; };
+    __device__ __forceinline__ static Acc init() { return {0.0}; }
+    __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double) { a.s = __dadd_rn(a.s, (double)x); }
+    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) { return {__dadd_rn(a.s, b.s)}; }
+    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) { return {__shfl_down_sync(0xffffffffu, a.s, off)}; }
+};
+
+// std::max(acc, val) == (acc < val) ? val : acc — a NaN val never replaces acc
+// (src/core/opsmp.cpp:679-691).
+template <typename VT, bool IS_MAX> struct MinMaxPol {
+    struct Acc { VT m; };
+    __device__ __forceinline__ static VT pick(VT acc, VT v) {
+        if (IS_MAX) return (acc < v) ? v : acc;
+        return (v < acc) ? v : acc;
+    }
+    __device__ __forceinline__ static Acc init() {
+        return {IS_MAX ? -(VT)INFINITY : (VT)INFINITY};
+    }
+    __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double) { a.m = pick(a.m, x); }
+    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) { return {pick(a.m, b.m)}; }
+    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) { return {__shfl_down_sync(0xffffffffu, a.m, off)}; }
+};
+
+// Biased variance from two shifted moments in fp64: with d = x - shift (shift = first element of
+// the line), var = (sum d^2 - (sum d)^2 / n) / n.
+template <typename VT> struct VarPol {
+    struct Acc { double s1, s2; };
+    __device__ __forceinline__ static Acc init() { return {0.0, 0.0}; }
+    __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double shift) {
+        double d = __dsub_rn((double)x, shift);
+        a.s1 = __dadd_rn(a.s1, d);
+        a.s2 = fma(d, d, a.s2);
+    }
+    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) {
+        return {__dadd_rn(a.s1, b.s1), __dadd_rn(a.s2, b.s2)};
+    }
+    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) {
+        return {__shfl_down_sync(0xffffffffu, a.s1, off), __shfl_down_sync(0xffffffffu, a.s2, off)};
+    }
+};
+
+// First index of the maximum; strict '>' against a running maximum that starts at -1e18
+// (src/core/ops_dispatch.cpp:460-472,511-521): NaN and values <= -1e18 never win, an all-
+// losing line yields index 0.  For fp32 the start value is the largest float <= -1e18, which
+// makes the fp32 compare equivalent to the reference's compare in double.
+template <typename VT> struct ArgmaxPol {
+    struct Acc { VT v; int32_t i; };
+    __device__ __forceinline__ static VT floor_value() {
+        if (sizeof(VT) == 4) return (VT)__uint_as_float(0xDD5E0B6Cu);   // -1.00000005e18f
+        return (VT)-1e18;
+    }
+    __device__ __forceinline__ static Acc init() { return {floor_value(), 0}; }
+    __device__ __forceinline__ static void add(Acc& a, VT x, int64_t idx, double) {
+        if (x > a.v) { a.v = x; a.i = (int32_t)idx; }
+    }
+    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) {
+        if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+        return a;
+    }
+    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) {
+        return {__shfl_down_sync(0xffffffffu, a.v, off), __shfl_down_sync(0xffffffffu, a.i, off)};
+    }
+};
+
+// ---- finalisation ------------------------------------------------------------------------------------
+// sum: (T)acc.  mean: the sum is rounded to T first, then multiplied by 1.0/n in double and
+// rounded again (mean = mul_scalar(sum, 1.0/N), src/core/ops_dispatch.cpp:385-390).
+template <typename T, typename Acc>
+__device__ __forceinline__ void finalize_store(int op, const Acc& a, int64_t n, void* out, int64_t oi,
+                                               double* partial_out);
+
+template <typename T> struct Finalize {
+    template <typename VT>
+    __device__ __forceinline__ static void run(int op, const typename SumPol<VT>::Acc& a, int64_t n, void* out, int64_t oi, double* po) {
+        if (po) { po[oi] = a.s; return; }
+        T s = from_double<T>(a.s);
+        if (op == CTB_MEAN) s = from_double<T>(__dmul_rn(to_double(s), 1.0 / (double)n));
+        ((T*)out)[oi] = s;
+    }
+    template <typename VT, bool IS_MAX>
+    __device__ __forceinline__ static void run_mm(const typename MinMaxPol<VT, IS_MAX>::Acc& a, void* out, int64_t oi, double* po) {
+        if (po) { po[oi] = (double)a.m; return; }
+        ((T*)out)[oi] = from_double<T>((double)a.m);
+    }
+    template <typename VT>
+    __device__ __forceinline__ static void run_var(const typename VarPol<VT>::Acc& a, int64_t n, void* out, int64_t oi) {
+        double dn = (double)n;
+        double v = (a.s2 - a.s1 * a.s1 / dn) / dn;
+        if (v < 0.0) v = 0.0;
+        ((T*)out)[oi] = from_double<T>(v);
+    }
+};
+
+template <typename T, typename Pol> struct Fin;
+template <typename T, typename VT> struct Fin<T, SumPol<VT>> {
+    __device__ __forceinline__ static void run(int op, const typename SumPol<VT>::Acc& a, int64_t n, void* out, int64_t oi, double* po) {
+        Finalize<T>::template run<VT>(op, a, n, out, oi, po);
+    }
+};
+template <typename T, typename VT, bool M> struct Fin<T, MinMaxPol<VT, M>> {
+    __device__ __forceinline__ static void run(int, const typename MinMaxPol<VT, M>::Acc& a, int64_t, void* out, int64_t oi, double* po) {
+        Finalize<T>::template run_mm<VT, M>(a, out, oi, po);
+    }
+};
+template <typename T, typename VT> struct Fin<T, VarPol<VT>> {
+    __device__ __forceinline__ static void run(int, const typename VarPol<VT>::Acc& a, int64_t n, void* out, int64_t oi, double*) {
+        Finalize<T>::template run_var<VT>(a, n, out, oi);
+    }
+};
+template <typename T, typename VT> struct Fin<T, ArgmaxPol<VT>> {
+    __device__ __forceinline__ static void run(int, const typename ArgmaxPol<VT>::Acc& a, int64_t, void* out, int64_t oi, double*) {
+        ((int32_t*)out)[oi] = a.i;
+    }
+};
+
+template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
+template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
+
+// ---- helpers -----------------------------------------------------------------------------------------
+struct OuterIdx {
+    int32_t nouter;
+    int64_t oshape[CTB_MAX_DIMS];
+    int64_t ostride[CTB_MAX_DIMS];
+};
+
+__device__ __forceinline__ int64_t outer_offset(const OuterIdx& o, int64_t i) {
+    int64_t off = 0;
+    for (int d = o.nouter - 1; d >= 0; --d) {
+        const int64_t q = i / o.oshape[d];
+        off += (i - q * o.oshape[d]) * o.ostride[d];
+        i = q;
+    }
+    return off;
+}
+
+// L2-coherent load of a scratch accumulator written by another CTA.
+template <typename A>
+__device__ __forceinline__ A load_cg(const A* p) {
+    A r;
+    if constexpr (sizeof(A) == 4) {
+        unsigned u = __ldcg(reinterpret_cast<const unsigned*>(p));
+        memcpy(&r, &u, 4);
+    } else if constexpr (sizeof(A) == 8) {
+        unsigned long long u = __ldcg(reinterpret_cast<const unsigned long long*>(p));
+        memcpy(&r, &u, 8);
+    } else {
+        static_assert(sizeof(A) == 16, "unexpected accumulator size");
+        ulonglong2 u = __ldcg(reinterpret_cast<const ulonglong2*>(p));
+        memcpy(&r, &u, 16);
+    }
+    return r;
+}
+
+template <typename Pol>
+__device__ __forceinline__ typename Pol::Acc warp_reduce(typename Pol::Acc a) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a = Pol::combine(a, Pol::shfl_down(a, off));
+    return a;   // valid in lane 0
+}
+
+// CTA-wide reduce; result valid in thread 0.  smem must hold THREADS/32 accumulators.
+template <typename Pol, int THREADS>
+__device__ __forceinline__ typename Pol::Acc block_reduce(typename Pol::Acc a, typename Pol::Acc* smem) {
+    constexpr int NW = THREADS / 32;
+    a = warp_reduce<Pol>(a);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();                       // smem may still be read from a previous use
+    if (lane == 0) smem[w] = a;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < NW; ++i) a = Pol::combine(a, smem[i]);
+    }
+    return a;
+}
+
+// Accumulate elements [lo, hi) of one contiguous line; `nthr` cooperating threads, this one
+// has rank `tid`.  Vector loads when VEC > 1 (caller guarantees alignment of line + lo).
+template <typename Pol, int VEC, int UNROLL>
+__device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const float* __restrict__ line,
+                                                int64_t lo, int64_t hi, int tid, int nthr, double shift) {
+    using V = Vec<float, VEC>;
+    const int64_t stride = (int64_t)nthr * VEC;
+    int64_t j = lo + (int64_t)tid * VEC;
+    // unrolled main loop: UNROLL vector loads in flight
+    for (; j + (UNROLL - 1) * stride + VEC <= hi; j += UNROLL * stride) {
+        V v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(line + j + u * stride));
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
+    }
+    for (; j + VEC <= hi; j += stride) {
+        V v = ldg_stream(reinterpret_cast<const V*>(line + j));
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) Pol::add(acc, v.v[k], j + k, shift);
+    }
+    if (VEC > 1) {   // ragged end of the line
+        for (int k = 0; k < VEC; ++k)
+            if (j + k < hi) Pol::add(acc, line[j + k], j + k, shift);
+    }
+}
+
+// ---- rows_warp ------------------------------------------------------------------------------------------
+template <typename Pol, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+reduce_rows_warp_kernel(const float* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen, int op) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (THREADS / 32);
+    for (int64_t row = (int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); row < nout; row += warps) {
+        const float* line = a + outer_offset(o, row);
+        const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+        typename Pol::Acc acc = Pol::init();
+        accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, lane, 32, shift);
+        acc = warp_reduce<Pol>(acc);
+        if (lane == 0) Fin<float, Pol>::run(op, acc, rlen, out, row, nullptr);
+    }
+}
+
+// ---- rows_block -----------------------------------------------------------------------------------------
+template <typename Pol, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen, int op) {
+    __shared__ typename Pol::Acc smem[THREADS / 32];
+    for (int64_t row = blockIdx.x; row < nout; row += gridDim.x) {
+        const float* line = a + outer_offset(o, row);
+        const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+        typename Pol::Acc acc = Pol::init();
+        accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
+        acc = block_reduce<Pol, THREADS>(acc, smem);
+        if (threadIdx.x == 0) Fin<float, Pol>::run(op, acc, rlen, out, row, nullptr);
+    }
+}
+
+// ---- rows_split -----------------------------------------------------------------------------------------
+// grid = (splits, nout).  Scratch: tickets[nout] (uint32, zero before and after), then
+// partials[nout][splits].
+template <typename Pol, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial_out, OuterIdx o,
+                         int64_t rlen, int64_t chunk, int op, uint32_t* tickets,
+                         typename Pol::Acc* partials) {
+    __shared__ typename Pol::Acc smem[THREADS / 32];
+    __shared__ bool is_last;
+    const int64_t row = blockIdx.y;
+    const int splits = gridDim.x;
+    const float* line = a + outer_offset(o, row);
+    const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+    const int64_t lo = (int64_t)blockIdx.x * chunk;
+    int64_t hi = lo + chunk;
+    if (hi > rlen) hi = rlen;
+    typename Pol::Acc acc = Pol::init();
+    if (lo < hi) accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, lo, hi, threadIdx.x, THREADS, shift);
+    acc = block_reduce<Pol, THREADS>(acc, smem);
+    if (threadIdx.x == 0) {
+        partials[row * splits + blockIdx.x] = acc;
+        __threadfence();
+        const uint32_t t = atomicAdd(&tickets[row], 1u);
+        is_last = (t == (uint32_t)splits - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // fixed-order combine: thread t folds partials t, t+THREADS, ... then the CTA tree
+    typename Pol::Acc c = Pol::init();
+    const typename Pol::Acc* p = partials + row * splits;
+    for (int i = threadIdx.x; i < splits; i += THREADS) c = Pol::combine(c, load_cg(p + i));
+    c = block_reduce<Pol, THREADS>(c, smem);
+    if (threadIdx.x == 0) {
+        Fin<float, Pol>::run(op, c, rlen, out, row, partial_out);
+        tickets[row] = 0;
+    }
+}
+
+// ---- cols -----------------------------------------------------------------------------------------------
+// Outer dims = [batch..., C] with the last one contiguous.  CTA = 32 x 8 threads: x walks
+// columns (VEC each), y walks rows.  grid = (column tiles, row splits, batch).
+template <typename Pol, int VEC>
+__global__ void __launch_bounds__(256)
+reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64_t ncols, int64_t rlen,
+                   int64_t rstride, int64_t rows_per_split, int op, uint32_t* tickets,
+                   typename Pol::Acc* partials) {
+    using V = Vec<float, VEC>;
+    using Acc = typename Pol::Acc;
+    __shared__ Acc smem[8][32 * VEC + 1];
+    __shared__ bool is_last;
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int64_t col = ((int64_t)blockIdx.x * 32 + x) * VEC;
+    const int64_t b = blockIdx.z;
+    const float* base = a + outer_offset(batch, b);
+    const int splits = gridDim.y;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
+    int64_t r1 = r0 + rows_per_split;
+    if (r1 > rlen) r1 = rlen;
+
+    Acc acc[VEC];
+    double shift[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { acc[k] = Pol::init(); shift[k] = 0.0; }
+    const bool active = col < ncols;     // ncols % VEC == 0 when VEC > 1
+    if (active) {
+        if (NeedsShift<Pol>::value) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) shift[k] = (double)base[col + k];
+        }
+        const float* p = base + col;
+        int64_t r = r0 + y;
+        for (; r + 8 * (CTB_RED_UNROLL - 1) < r1; r += 8 * CTB_RED_UNROLL) {
+            V v[CTB_RED_UNROLL];
+#pragma unroll
+            for (int u = 0; u < CTB_RED_UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
+#pragma unroll
+            for (int u = 0; u < CTB_RED_UNROLL; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
+        }
+        for (; r < r1; r += 8) {
+            V v = ldg_stream(reinterpret_cast<const V*>(p + r * rstride));
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v.v[k], r, shift[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) smem[y][x * VEC + k] = acc[k];
+    __syncthreads();
+    // 32*VEC columns, one thread each (threads 0..32*VEC-1), rows y = 0..7 in order
+    const int ct = threadIdx.x;
+    const int64_t ccol = (int64_t)blockIdx.x * 32 * VEC + ct;
+    const bool cact = ct < 32 * VEC && ccol < ncols;
+    Acc c = Pol::init();
+    if (cact) {
+        c = smem[0][ct];
+#pragma unroll
+        for (int yy = 1; yy < 8; ++yy) c = Pol::combine(c, smem[yy][ct]);
+    }
+    if (splits == 1) {
+        if (cact) Fin<float, Pol>::run(op, c, rlen, out, b * ncols + ccol, nullptr);
+        return;
+    }
+    Acc* part = partials + (b * splits) * ncols;
+    if (cact) part[(int64_t)blockIdx.y * ncols + ccol] = c;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t slot = (uint32_t)(b * gridDim.x + blockIdx.x);
+        const uint32_t t = atomicAdd(&tickets[slot], 1u);
+        is_last = (t == (uint32_t)splits - 1);
+        if (is_last) tickets[slot] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (cact) {
+        Acc f = load_cg(part + ccol);
+        for (int s = 1; s < splits; ++s) f = Pol::combine(f, load_cg(part + (int64_t)s * ncols + ccol));
+        Fin<float, Pol>::run(op, f, rlen, out, b * ncols + ccol, nullptr);
+    }
+}
+
+// ---- generic --------------------------------------------------------------------------------------------
+template <typename Pol, typename T>
+__global__ void __launch_bounds__(256)
+reduce_generic_kernel(const T* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen,
+                      int64_t rstride, int op) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nout; i += step) {
+        const T* line = a + outer_offset(o, i);
+        const double shift = NeedsShift<Pol>::value && rlen > 0 ? to_double(line[0]) : 0.0;
+        typename Pol::Acc acc = Pol::init();
+        for (int64_t k = 0; k < rlen; ++k) Pol::add(acc, to_double(line[k * rstride]), k, shift);
+        Fin<T, Pol>::run(op, acc, rlen, out, i, nullptr);
+    }
+}
+
+// ---- multi-GPU finalisation ---------------------------------------------------------------------------
+template <typename T>
+__global__ void finalize_full_kernel(int op, const double* partial, int64_t total, T* out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    T s = from_double<T>(partial[0]);
+    if (op == CTB_MEAN) s = from_double<T>(__dmul_rn(to_double(s), 1.0 / (double)total));
+    out[0] = s;
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+namespace {
+
+enum Shape { SH_ROWS_WARP, SH_ROWS_BLOCK, SH_ROWS_SPLIT, SH_COLS, SH_GENERIC };
+
+struct Choice {
+    Shape shape;
+    int vec;             // 4 or 1
+    int splits;          // rows_split / cols
+    int64_t chunk;       // rows_split: elements per split; cols: rows per split
+    int64_t coltiles;    // cols
+    int64_t batch;       // cols
+    size_t acc_bytes_max = 16;
+};
+
+bool all_multiple(const int64_t* v, int n, int64_t m) {
+    for (int i = 0; i < n; ++i) if (v[i] % m) return false;
+    return true;
+}
+
+Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
+    Choice c{};
+    c.shape = SH_GENERIC;
+    c.vec = 1;
+    if (dtype != CTB_F32 || g.nout == 0 || g.rlen == 0) return c;
+    const bool base16 = a == nullptr || is_aligned(a, 16);
+    if (g.rstride == 1 || g.rlen == 1) {
+        c.vec = (base16 && all_multiple(g.ostride, g.nouter, 4) && g.rlen % 4 == 0) ? 4 : 1;
+        if (g.nout <= 2 * (int64_t)sm_count && g.rlen >= 65536 && g.nout <= 65535 && g.nout <= kCounterSlots) {
+            c.shape = SH_ROWS_SPLIT;
+            int64_t want = (int64_t)sm_count * CTB_RED_SPLIT_CTAS_PER_SM / g.nout;
+            if (want < 1) want = 1;
+            const int64_t gran = (int64_t)CTB_RED_THREADS * 4 * CTB_RED_UNROLL;     // keeps chunks vector-aligned
+            int64_t chunk = ceil_div(ceil_div(g.rlen, want), gran) * gran;
+            c.chunk = chunk;
+            c.splits = (int)ceil_div(g.rlen, chunk);
+            return c;
+        }
+        c.shape = g.rlen <= 2048 ? SH_ROWS_WARP : SH_ROWS_BLOCK;
+        return c;
+    }
+    // column case: innermost outer dim contiguous
+    if (g.nouter >= 1 && g.ostride[g.nouter - 1] == 1) {
+        const int64_t ncols = g.oshape[g.nouter - 1];
+        int64_t batch = 1;
+        for (int d = 0; d < g.nouter - 1; ++d) batch *= g.oshape[d];
+        if (batch <= 65535 && ncols >= 32) {
+            c.vec = (base16 && ncols % 4 == 0 && g.rstride % 4 == 0 && all_multiple(g.ostride, g.nouter - 1, 4)) ? 4 : 1;
+            c.coltiles = ceil_div(ncols, 32 * c.vec);
+            c.batch = batch;
+            int64_t ctas = c.coltiles * batch;
+            int64_t want = ceil_div((int64_t)sm_count * 8, ctas);
+            int64_t max_splits = g.rlen / 64;
+            if (want > max_splits) want = max_splits;
+            if (want > 64) want = 64;
+            if (want < 1) want = 1;
+            if (want > 1 && ctas > kCounterSlots) want = 1;
+            c.chunk = ceil_div(ceil_div(g.rlen, want), 8) * 8;
+            c.splits = (int)ceil_div(g.rlen, c.chunk);
+            c.shape = SH_COLS;
+            return c;
+        }
+    }
+    return c;
+}
+
+size_t scratch_bytes(const ReduceGeom& g, const Choice& c) {
+    if (c.shape == SH_ROWS_SPLIT) return kCounterBytes + (size_t)g.nout * c.splits * 16;
+    if (c.shape == SH_COLS && c.splits > 1) return kCounterBytes + (size_t)c.batch * c.splits * g.oshape[g.nouter - 1] * 16;
+    return 0;
+}
+
+OuterIdx outer_of(const ReduceGeom& g, int n) {
+    OuterIdx o{};
+    o.nouter = n;
+    for (int d = 0; d < n; ++d) { o.oshape[d] = g.oshape[d]; o.ostride[d] = g.ostride[d]; }
+    return o;
+}
+
+template <typename Pol>
+int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out, double* partial_out,
+                void* ws, int op, int sm_count, cudaStream_t st) {
+    constexpr int T = CTB_RED_THREADS;
+    uint32_t* tickets = (uint32_t*)ws;
+    typename Pol::Acc* partials = (typename Pol::Acc*)((char*)ws + kCounterBytes);
+    static_assert(sizeof(typename Pol::Acc) <= 16, "accumulator larger than the scratch slot");
+    switch (c.shape) {
+    case SH_ROWS_WARP: {
+        int64_t blocks = ceil_div(g.nout, T / 32);
+        int64_t cap = (int64_t)sm_count * 16;
+        int grid = (int)(blocks < cap ? blocks : cap);
+        if (c.vec == 4) reduce_rows_warp_kernel<Pol, 4, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        else reduce_rows_warp_kernel<Pol, 1, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        break;
+    }
+    case SH_ROWS_BLOCK: {
+        int64_t cap = (int64_t)sm_count * 16;
+        int grid = (int)(g.nout < cap ? g.nout : cap);
+        if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        else reduce_rows_block_kernel<Pol, 1, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        break;
+    }
+    case SH_ROWS_SPLIT: {
+        dim3 grid(c.splits, (unsigned)g.nout);
+        if (c.vec == 4) reduce_rows_split_kernel<Pol, 4, T><<<grid, T, 0, st>>>(a, out, partial_out, outer_of(g, g.nouter), g.rlen, c.chunk, op, tickets, partials);
+        else reduce_rows_split_kernel<Pol, 1, T><<<grid, T, 0, st>>>(a, out, partial_out, outer_of(g, g.nouter), g.rlen, c.chunk, op, tickets, partials);
+        break;
+    }
+    case SH_COLS: {
+        dim3 grid((unsigned)c.coltiles, (unsigned)c.splits, (unsigned)c.batch);
+        const int64_t ncols = g.oshape[g.nouter - 1];
+        if (c.vec == 4) reduce_cols_kernel<Pol, 4><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, c.chunk, op, tickets, partials);
+        else reduce_cols_kernel<Pol, 1><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, c.chunk, op, tickets, partials);
+        break;
+    }
+    default: return set_error(CTB_ERR_ARG, "reduce: internal shape error");
+    }
+    return cuda_error(cudaGetLastError(), "reduce launch");
+}
+
+template <typename T>
+int launch_generic_t(int op, const ReduceGeom& g, const T* a, void* out, int sm_count, cudaStream_t st) {
+    int64_t blocks = ceil_div(g.nout, 256);
+    int64_t cap = (int64_t)sm_count * 8;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (grid < 1) grid = 1;
+    OuterIdx o = outer_of(g, g.nouter);
+    switch (op) {
+    case CTB_SUM: case CTB_MEAN:
+        reduce_generic_kernel<SumPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
+    case CTB_MAX:
+        reduce_generic_kernel<MinMaxPol<double, true>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
+    case CTB_MIN:
+        reduce_generic_kernel<MinMaxPol<double, false>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
+    case CTB_VAR:
+        reduce_generic_kernel<VarPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
+    case CTB_ARGMAX:
+        reduce_generic_kernel<ArgmaxPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
+    default: return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+    }
+    return cuda_error(cudaGetLastError(), "reduce_generic launch");
+}
+
+}  // namespace
+
+size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype) {
+    DeviceInfo di;
+    if (current_device_info(&di) != CTB_OK) di.sm_count = 148;
+    Choice c = choose(g, dtype, nullptr, di.sm_count);
+    return scratch_bytes(g, c);
+}
+
+int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
+                  double* partial_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (op < 0 || op >= CTB_REDUCE_OP_COUNT) return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+    DeviceInfo di;
+    int rc = current_device_info(&di);
+    if (rc) return rc;
+    if (g.nout == 0) return CTB_OK;
+    Choice c = choose(g, dtype, a, di.sm_count);
+    if (partial_out && c.shape != SH_ROWS_SPLIT) {
+        // the fp64 partial is only produced by the split kernel; force it (splits may be 1)
+        if (dtype != CTB_F32 || g.rstride != 1 || g.nout != 1)
+            return set_error(CTB_ERR_ARG, "reduce: fp64 partials need a dense Float32 input");
+        c.shape = SH_ROWS_SPLIT;
+        c.vec = (is_aligned(a, 16) && g.rlen % 4 == 0) ? 4 : 1;
+        c.chunk = ceil_div(g.rlen > 0 ? g.rlen : 1, (int64_t)CTB_RED_THREADS * 4 * CTB_RED_UNROLL) * CTB_RED_THREADS * 4 * CTB_RED_UNROLL;
+        c.splits = 1;
+    }
+    const size_t need = scratch_bytes(g, c);
+    if (need > ws_bytes || (need && !ws)) return set_error(CTB_ERR_WORKSPACE, "reduce: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+    if (need && !is_aligned(ws, 256)) return set_error(CTB_ERR_WORKSPACE, "reduce: workspace must be 256-byte aligned");
+
+    if (c.shape == SH_GENERIC) {
+        switch (dtype) {
+        case CTB_F32: return launch_generic_t<float>(op, g, (const float*)a, out, di.sm_count, st);
+        case CTB_I32: return launch_generic_t<int32_t>(op, g, (const int32_t*)a, out, di.sm_count, st);
+        case CTB_F64: return launch_generic_t<double>(op, g, (const double*)a, out, di.sm_count, st);
+        }
+        return set_error(CTB_ERR_DTYPE, "reduce: unsupported dtype");
+    }
+    const float* fa = (const float*)a;
+    switch (op) {
+    case CTB_SUM: case CTB_MEAN: return launch_fast<SumPol<float>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_MAX: return launch_fast<MinMaxPol<float, true>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_MIN: return launch_fast<MinMaxPol<float, false>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_VAR: return launch_fast<VarPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);
+    case CTB_ARGMAX: return launch_fast<ArgmaxPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);
+    }
+    return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+}
+
+int launch_finalize_full(int op, int dtype, const double* partial, int64_t total, void* out, cudaStream_t st) {
+    switch (dtype) {
+    case CTB_F32: finalize_full_kernel<float><<<1, 32, 0, st>>>(op, partial, total, (float*)out); break;
+    case CTB_I32: finalize_full_kernel<int32_t><<<1, 32, 0, st>>>(op, partial, total, (int32_t*)out); break;
+    case CTB_F64: finalize_full_kernel<double><<<1, 32, 0, st>>>(op, partial, total, (double*)out); break;
+    default: return set_error(CTB_ERR_DTYPE, "finalize: unsupported dtype");
+    }
+    return cuda_error(cudaGetLastError(), "finalize launch");
+}
+
+}  // namespace ctb

@@ -1,0 +1,52 @@
+// Host-visible interface of the reduction and fused-row kernels (ctb_reduce.cu, ctb_rows.cu).
+#pragma once
+#include "ctb_common.cuh"
+
+namespace ctb {
+
+// A strided input seen by a reduction: `outer` dims index the outputs, one `reduce` dim
+// (length rlen, stride rstride) is folded.  A full reduction of a dense buffer is planned as
+// outer = {}, rlen = numel, rstride = 1.
+struct ReduceGeom {
+    int32_t nouter;
+    int64_t oshape[CTB_MAX_DIMS];
+    int64_t ostride[CTB_MAX_DIMS];
+    int64_t nout;        // product of oshape (1 when nouter == 0)
+    int64_t rlen;
+    int64_t rstride;
+    int64_t total;       // element count that "mean"/"var" divide by (== rlen)
+};
+
+// Bytes of scratch the chosen kernel shape needs for this geometry (0 when none).
+size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype);
+
+// Launch the reduction.  `out` is T (or int32 for argmax); `partial_out` (may be null) asks for
+// the raw fp64 accumulator instead of the finalised T (full reductions only, used by the
+// multi-GPU path).  `ws` must hold reduce_workspace_bytes() bytes, zero-initialised once at
+// allocation (the kernels leave their tickets at zero again).
+int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
+                  double* partial_out, void* ws, size_t ws_bytes, cudaStream_t stream);
+
+int launch_finalize_full(int op, int dtype, const double* partial, int64_t total, void* out,
+                         cudaStream_t stream);
+
+// Fused rows (fp32).  x: [outer..., cols] with inner stride 1; mask (optional): same outer dims
+// with broadcast strides, inner stride 0 or 1.
+struct RowsGeom {
+    int32_t nouter;
+    int64_t oshape[CTB_MAX_DIMS];
+    int64_t xstride[CTB_MAX_DIMS];
+    int64_t mstride[CTB_MAX_DIMS];
+    int64_t rows;
+    int64_t cols;
+    int64_t qlen;        // size of the second-to-last dim (row index within it drives `causal`)
+    int32_t m_inner;     // mask inner stride (0 or 1)
+    int32_t has_mask;
+};
+int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int causal, float* out,
+                   cudaStream_t stream);
+int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride,
+                     const float* beta, int64_t bstride, double eps, float* out,
+                     cudaStream_t stream);
+
+}  // namespace ctb

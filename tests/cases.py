@@ -1,0 +1,234 @@
+"""The catalogue of small parity cases shared by the golden-vector generator, the oracle tests
+and the GPU tests.  Every case is a dict:
+
+    name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'), op, views (HostViews),
+    scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
+
+Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
+"""
+from __future__ import annotations
+
+import hashlib
+
+import numpy as np
+
+import oracle_lib as ol
+from oracle_lib import HostView
+
+SPECIAL_F32 = np.array(
+    [0.0, -0.0, 1.0, -1.0, 0.5, 0.75, 1.5, 3.0, 2.0, 10.0, -10.0, 88.0, 88.5, -88.0, -88.5, 100.0,
+     -100.0, 1e-40, -1e-40, 1.17549435e-38, 3.4e38, -3.4e38, np.inf, -np.inf, np.nan, 1e-7, -1e-7,
+     0.70710677, 0.707106, 0.70710683, 1e10, -1e10, 1e-20, 44.0, -44.5, 0.34657359, 6.0e-8,
+     16777216.0, 0.1, -0.1, 7.0, -7.0, 1e18, -1e18, -1.5e18], dtype=np.float32)
+
+
+def _rng(seed):
+    return np.random.default_rng(seed)
+
+
+def _u(seed, shape, lo=-1.0, hi=1.0):
+    return _rng(seed).uniform(lo, hi, shape).astype(np.float32)
+
+
+def _n(seed, shape, scale=1.0):
+    return (_rng(seed).standard_normal(shape) * scale).astype(np.float32)
+
+
+def _simd_path(op):
+    """Reference back-end that defines each fp32 unary flavour."""
+    if op == ol.LOG:
+        return ol.PATH_AVX2
+    if op in (ol.EXP, ol.TANH, ol.SIGMOID, ol.GELU_TANH):
+        return ol.PATH_AVX512
+    return ol.PATH_MP
+
+
+def all_cases():
+    cases = []
+
+    def add(**kw):
+        kw.setdefault("scalar", 0.0)
+        kw.setdefault("dim", 0)
+        kw.setdefault("causal", False)
+        kw.setdefault("exact", True)
+        kw.setdefault("path", ol.PATH_MP)
+        cases.append(kw)
+
+    # ---- binary, fp32 -------------------------------------------------------------------------
+    A = HostView.contig(_u(0, (64, 48)))
+    B = HostView.contig(_u(1, (1, 48)))
+    C = HostView.contig(_u(2, (64, 1)))
+    S1 = HostView.contig(_u(3, (1,)))
+    V = HostView.contig(_u(4, (48,)))
+    buf4 = HostView.contig(_n(5, (2, 5, 3, 16)))
+    P4 = buf4.permute([0, 2, 1, 3])                    # scaled version of the permuted 4-d view
+    M4 = HostView.contig(_u(6, (1, 3, 1, 16), -1.0, 0.0))
+    T = A.permute([1, 0])                               # transposed: inner stride != 1
+    big = HostView.contig(_n(7, (3, 2051)))             # ragged length (not a multiple of 4)
+    off = HostView(_n(8, (5000,)), (37, 101), (101, 1), 3)      # odd offset -> misaligned base
+    stepped = HostView(_n(9, (64 * 70,)), (64, 35), (70, 2), 0)  # inner stride 2
+    for op in range(10):
+        nm = ol.BINARY_NAMES[op]
+        add(name=f"bin_{nm}_rowbcast", kind="binary", op=op, views=[A, B])
+        add(name=f"bin_{nm}_colbcast", kind="binary", op=op, views=[A, C])
+        add(name=f"bin_{nm}_same", kind="binary", op=op, views=[A, A.narrow(0, 0, 64)])
+    for op in (ol.ADD, ol.SUB, ol.MUL, ol.DIV):
+        nm = ol.BINARY_NAMES[op]
+        add(name=f"bin_{nm}_bcast_a", kind="binary", op=op, views=[B, A])
+        add(name=f"bin_{nm}_scalar_b", kind="binary", op=op, views=[A, S1])
+        add(name=f"bin_{nm}_scalar_a", kind="binary", op=op, views=[S1, A])
+        add(name=f"bin_{nm}_vec", kind="binary", op=op, views=[A, V])
+        add(name=f"bin_{nm}_perm4d", kind="binary", op=op, views=[P4, M4])
+        add(name=f"bin_{nm}_transposed", kind="binary", op=op, views=[T, HostView.contig(_u(10, (48, 64)))])
+        add(name=f"bin_{nm}_outer", kind="binary", op=op, views=[C, B])        # [64,1] o [1,48]
+        add(name=f"bin_{nm}_ragged", kind="binary", op=op, views=[big, big.narrow(0, 1, 1)])
+        add(name=f"bin_{nm}_offset", kind="binary", op=op, views=[off, off])
+        add(name=f"bin_{nm}_stepped", kind="binary", op=op, views=[stepped, stepped])
+        sp = HostView.contig(SPECIAL_F32)
+        add(name=f"bin_{nm}_special", kind="binary", op=op,
+            views=[HostView.contig(np.repeat(SPECIAL_F32, SPECIAL_F32.size).reshape(SPECIAL_F32.size, -1)), sp])
+    # both operands single elements (the dispatcher's scalar short-circuit computes the same value)
+    add(name="bin_add_1x1", kind="binary", op=ol.ADD, views=[S1, HostView.contig(_u(11, (1, 1)))])
+
+    # ---- binary, int32 and fp64 ------------------------------------------------------------------
+    Ai = HostView.contig(_rng(12).integers(-100, 100, (7, 9)).astype(np.int32))
+    Bi = HostView.contig(_rng(13).integers(1, 9, (9,)).astype(np.int32))
+    edge_a = HostView.contig(np.array([2000000000, -2000000000, 7, -7, 0, 5], np.int32))
+    edge_b = HostView.contig(np.array([2000000000, 2000000000, 2, 2, 0, 0], np.int32))
+    Ad = HostView.contig(_rng(14).standard_normal((5, 6)))
+    Bd = HostView.contig(_rng(15).standard_normal((6,)))
+    for op in range(10):
+        nm = ol.BINARY_NAMES[op]
+        add(name=f"bin_{nm}_i32", kind="binary", op=op, views=[Ai, Bi])
+        add(name=f"bin_{nm}_i32_edge", kind="binary", op=op, views=[edge_a, edge_b])
+        add(name=f"bin_{nm}_f64", kind="binary", op=op, views=[Ad, Bd])
+
+    # ---- unary ---------------------------------------------------------------------------------------
+    X = HostView.contig(_n(16, (37, 53), 3.0))
+    Xp = HostView.contig(np.abs(_n(17, (37, 53), 3.0)) + np.float32(1e-3))
+    sp = HostView.contig(SPECIAL_F32)
+    for op in range(22):
+        nm = ol.UNARY_NAMES[op]
+        path = _simd_path(op)
+        exact = op not in (ol.POW_S, ol.RPOW_S)        # libm pow in double: tolerance only
+        for s in ((0.5, -3.0, 2.0) if op < ol.ABS else (0.0,)):
+            tag = f"{nm}_{s}" if op < ol.ABS else nm
+            src = Xp if op in (ol.POW_S, ol.RPOW_S, ol.LOG, ol.SQRT) else X
+            if op == ol.RPOW_S and s < 0:
+                continue
+            add(name=f"un_{tag}", kind="unary", op=op, views=[src], scalar=s, exact=exact, path=path)
+            if exact:
+                add(name=f"un_{tag}_special", kind="unary", op=op, views=[sp], scalar=s, path=path)
+        if path == ol.PATH_MP and op >= ol.ABS or op in (ol.MUL_S, ol.ADD_S):
+            # strided inputs (the SIMD unary back-ends of the reference are stride-blind)
+            add(name=f"un_{nm}_perm4d", kind="unary", op=op, views=[P4], scalar=1.5, path=ol.PATH_MP)
+            add(name=f"un_{nm}_transposed", kind="unary", op=op, views=[T], scalar=1.5, path=ol.PATH_MP)
+    for op in (ol.ADD_S, ol.MUL_S, ol.DIV_S, ol.RSUB_S, ol.GT_S, ol.ABS, ol.RELU, ol.SQRT):
+        nm = ol.UNARY_NAMES[op]
+        add(name=f"un_{nm}_i32", kind="unary", op=op, views=[Ai], scalar=2.5)
+        add(name=f"un_{nm}_f64", kind="unary", op=op, views=[Ad], scalar=2.5)
+    add(name="un_mul_s_i32_overflow", kind="unary", op=ol.MUL_S, views=[edge_a], scalar=3.0)
+
+    # ---- strided copy -----------------------------------------------------------------------------------
+    for nm, v in (("perm4d", P4), ("transposed", T), ("offset", off), ("stepped", stepped),
+                  ("i32", HostView.contig(Ai.numpy()).permute([1, 0])), ("f64", Ad.permute([1, 0])),
+                  ("narrow", A.narrow(1, 5, 17))):
+        add(name=f"copy_{nm}", kind="copy", op=0, views=[v])
+
+    # ---- reductions ---------------------------------------------------------------------------------------
+    R = HostView.contig(_n(18, (33, 70)))
+    R3 = HostView.contig(_n(19, (6, 20, 36)))
+    Rlong = HostView.contig(_n(20, (3, 5000)))
+    Rtall = HostView.contig(_n(21, (700, 36)))
+    nan_rows = HostView.contig(np.array(
+        [[1, np.nan, 3, 2], [np.nan, 1, 3, 2], [np.nan] * 4, [-np.inf, -2e18, -1e18, -3e18],
+         [5, 7, 7, 1], [-1.0, -1.0, -2.0, -1.0]], np.float32))
+    for op in range(6):
+        nm = ol.REDUCE_NAMES[op]
+        exact = op in (ol.MAX, ol.MIN, ol.ARGMAX)
+        for vn, v in (("2d", R), ("3d", R3), ("long", Rlong), ("tall", Rtall), ("perm4d", P4),
+                      ("transposed", R.permute([1, 0])), ("stepped", stepped), ("i32", Ai), ("f64", Ad)):
+            dims = list(range(v.ndim)) + ([] if op == ol.ARGMAX else [-1])
+            for dim in dims:
+                add(name=f"red_{nm}_{vn}_d{dim}", kind="reduce", op=op, views=[v], dim=dim,
+                    exact=exact or v.dtype == ol.I32)
+        if op in (ol.MAX, ol.MIN, ol.ARGMAX):
+            add(name=f"red_{nm}_nan_rows", kind="reduce", op=op, views=[nan_rows], dim=1)
+    one = HostView.contig(np.array([4.25], np.float32))
+    for op in (ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR):
+        add(name=f"red_{ol.REDUCE_NAMES[op]}_single", kind="reduce", op=op, views=[one], dim=0, exact=True)
+
+    # ---- fused rows ---------------------------------------------------------------------------------------
+    add(name="softmax_2d", kind="softmax", op=0, views=[R], exact=False, path=ol.PATH_AVX512)
+    add(name="softmax_perm4d_mask", kind="softmax", op=0, views=[P4, M4], exact=False, path=ol.PATH_AVX512)
+    add(name="softmax_long", kind="softmax", op=0, views=[Rlong], exact=False, path=ol.PATH_AVX512)
+    sq = HostView.contig(_n(22, (2, 3, 24, 24)))
+    cm = np.where(np.arange(24)[None, :] > np.arange(24)[:, None], np.float32(-1e9), np.float32(0)).astype(np.float32)
+    add(name="softmax_causal_as_mask", kind="softmax", op=0, views=[sq, HostView.contig(cm.reshape(1, 1, 24, 24))],
+        exact=False, path=ol.PATH_AVX512)
+    g = HostView.contig((_n(23, (70,), 0.02) + 1).astype(np.float32))
+    b = HostView.contig(_n(24, (70,), 0.02))
+    add(name="layernorm_2d", kind="layernorm", op=0, views=[R, g, b], scalar=1e-5, exact=False)
+    g36 = HostView.contig((_n(25, (36,), 0.02) + 1).astype(np.float32))
+    b36 = HostView.contig(_n(26, (36,), 0.02))
+    add(name="layernorm_3d", kind="layernorm", op=0, views=[R3, g36, b36], scalar=1e-5, exact=False)
+    return cases
+
+
+def run_case(impl, case):
+    """Evaluate a case on an Oracle- or Reference-like object."""
+    k, v = case["kind"], case["views"]
+    is_ref = isinstance(impl, ol.Reference)
+    if k == "binary":
+        return impl.binary(case["op"], v[0], v[1], ol.PATH_MP) if is_ref else impl.binary(case["op"], v[0], v[1])
+    if k == "unary":
+        return (impl.unary(case["op"], v[0], case["scalar"], case["path"]) if is_ref
+                else impl.unary(case["op"], v[0], case["scalar"]))
+    if k == "copy":
+        return impl.contiguous(v[0])
+    if k == "reduce":
+        return impl.reduce(case["op"], v[0], case["dim"], ol.PATH_MP) if is_ref else impl.reduce(case["op"], v[0], case["dim"])
+    if k == "softmax":
+        mask = v[1] if len(v) > 1 else None
+        return impl.softmax(v[0], mask, case["path"]) if is_ref else impl.softmax(v[0], mask, case["causal"])
+    if k == "layernorm":
+        return impl.layernorm(v[0], v[1], v[2], case["scalar"])
+    raise ValueError(k)
+
+
+def digest(arr: np.ndarray) -> str:
+    """SHA-256 of an output's shape, dtype and bytes, with every NaN mapped to one canonical
+    pattern (x86 and the GPU propagate different NaN payloads)."""
+    a = np.ascontiguousarray(arr).copy()
+    if a.dtype.kind == "f":
+        a[np.isnan(a)] = np.nan
+    h = hashlib.sha256()
+    h.update(str(a.dtype).encode())
+    h.update(str(a.shape).encode())
+    h.update(a.tobytes())
+    return h.hexdigest()
+
+
+GOLDEN_PATH = __import__("os").path.join(__import__("os").path.dirname(__import__("os").path.abspath(__file__)),
+                                         "golden", "golden_cases.npz")
+
+
+def load_golden():
+    """-> dict name -> {'views': [HostView...], 'digest': str | None, 'out': ndarray | None}"""
+    z = np.load(GOLDEN_PATH, allow_pickle=False)
+    res = {}
+    for n in z["__names__"]:
+        n = str(n)
+        views = []
+        i = 0
+        while f"{n}/in{i}/meta" in z:
+            meta = z[f"{n}/in{i}/meta"]
+            nd = int(meta[1])
+            buf = z["buf/" + str(z[f"{n}/in{i}/key"])]
+            views.append(HostView(buf, tuple(int(x) for x in meta[2:2 + nd]),
+                                  tuple(int(x) for x in meta[2 + nd:2 + 2 * nd]), int(meta[0])))
+            i += 1
+        res[n] = {"views": views,
+                  "digest": str(z[f"{n}/digest"]) if f"{n}/digest" in z else None,
+                  "out": z[f"{n}/out"] if f"{n}/out" in z else None}
+    return res

@@ -1,0 +1,284 @@
+"""GPU parity tests: every case goes through the C ABI on cuda:0 and is compared with the
+plain-C oracle and with the golden vectors of the real reference.  Bit-exact for elementwise,
+integer, max/min, argmax and copy cases; sums/means/variances and the fused rows to 1e-5
+relative (the tolerance the operator path states for fp32)."""
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+import oracle_lib as ol
+from oracle_lib import HostView
+from gpu_util import to_device, assert_bits_equal, assert_close
+
+pytestmark = pytest.mark.gpu
+
+CASES = C.all_cases()
+GOLDEN = C.load_golden()
+RTOL = 1e-5
+
+
+def run_gpu(ct, case):
+    k = case["kind"]
+    dv = [to_device(v) for v in case["views"]]
+    if k == "binary":
+        return ct.binary(case["op"], dv[0], dv[1])
+    if k == "unary":
+        return ct.unary(case["op"], dv[0], case["scalar"])
+    if k == "copy":
+        return ct.contiguous(dv[0])
+    if k == "reduce":
+        return ct.reduce(case["op"], dv[0], case["dim"])
+    if k == "softmax":
+        out = ct.softmax(dv[0], dv[1] if len(dv) > 1 else None, case["causal"])
+        return out
+    if k == "layernorm":
+        return ct.layernorm(dv[0], dv[1], dv[2], case["scalar"])
+    raise ValueError(k)
+
+
+def expected_shape(case, ref):
+    return ref.shape
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_case_vs_oracle_and_golden(ct, oracle, case):
+    got = run_gpu(ct, case).cpu().numpy()
+    ref = C.run_case(oracle, case)
+    got = got.reshape(ref.shape)
+    gold = GOLDEN[case["name"]]
+    if case["exact"]:
+        assert_bits_equal(got, ref, case["name"])
+        assert C.digest(got) == gold["digest"], f"{case['name']}: differs from the reference's golden output"
+    else:
+        assert_close(got, ref, RTOL, case["name"])
+        assert_close(got, gold["out"], RTOL, case["name"] + " (golden)")
+
+
+def test_causal_flag(ct, oracle):
+    x = HostView.contig(np.random.default_rng(5).standard_normal((2, 3, 40, 40)).astype(np.float32))
+    got = ct.softmax(to_device(x), None, causal=True).cpu().numpy()
+    ref = oracle.softmax(x, None, causal=True)
+    assert_close(got, ref, RTOL, "causal softmax")
+    assert np.all(got[..., 0, 1:] == 0.0)          # masked entries underflow to exactly 0
+
+
+# ---- the CPU-runnable configuration: A[1024,1024], B[1,1024] ~ U(-1,1), seed 0 -------------------------
+def test_config_cpu_runnable(ct, oracle):
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (1024, 1024)).astype(np.float32)
+    B = rng.uniform(-1, 1, (1, 1024)).astype(np.float32)
+    hA, hB = HostView.contig(A), HostView.contig(B)
+    dA, dB = to_device(hA), to_device(hB)
+    assert_bits_equal(ct.binary(ct.ADD, dA, dB), oracle.binary(ol.ADD, hA, hB), "A+B")
+    assert_bits_equal(ct.binary(ct.MUL, dA, dB), oracle.binary(ol.MUL, hA, hB), "A*B")
+    den_ref = oracle.unary(ol.ADD_S, HostView.contig(oracle.unary(ol.ABS, hB)), 1.0)
+    den = ct.unary(ct.ADD_S, ct.unary(ct.ABS, dB), 1.0)
+    assert_bits_equal(den, den_ref, "|B|+1")
+    assert_bits_equal(ct.binary(ct.DIV, dA, den), oracle.binary(ol.DIV, hA, HostView.contig(den_ref)), "A/(|B|+1)")
+    assert_bits_equal(ct.unary(ct.RELU, dA), oracle.unary(ol.RELU, hA), "relu(A)")
+    for dim in (1, -1):
+        assert_bits_equal(ct.reduce(ct.MAX, dA, dim), oracle.reduce(ol.MAX, hA, dim), f"max {dim}")
+        assert_close(ct.reduce(ct.SUM, dA, dim), oracle.reduce(ol.SUM, hA, dim), RTOL, f"sum {dim}")
+        assert_close(ct.reduce(ct.MEAN, dA, dim), oracle.reduce(ol.MEAN, hA, dim), RTOL, f"mean {dim}")
+
+
+# ---- mid-size cases that exercise every kernel shape (oracle still finishes in seconds) --------------------
+@pytest.mark.parametrize("n", [1, 3, 17, 1025, 4096, 4097, (1 << 20) + 5, 1 << 22])
+@pytest.mark.parametrize("op", [ol.ADD, ol.MUL, ol.DIV])
+def test_flat_binary_sizes(ct, oracle, n, op):
+    rng = np.random.default_rng(n)
+    a = HostView.contig(rng.standard_normal(n).astype(np.float32))
+    b = HostView.contig(rng.standard_normal(n).astype(np.float32))
+    assert_bits_equal(ct.binary(op, to_device(a), to_device(b)), oracle.binary(op, a, b), f"n={n}")
+
+
+@pytest.mark.parametrize("n", [1, 5, 1023, (1 << 20) + 3, 1 << 22])
+@pytest.mark.parametrize("op", [ol.EXP, ol.RELU, ol.GELU_TANH, ol.TANH, ol.LOG, ol.SIGMOID, ol.MUL_S])
+def test_flat_unary_sizes(ct, oracle, n, op):
+    x = np.random.default_rng(n + 1).standard_normal(n).astype(np.float32)
+    if op == ol.LOG:
+        x = np.abs(x) + np.float32(1e-6)
+    h = HostView.contig(x)
+    assert_bits_equal(ct.unary(op, to_device(h), 0.3), oracle.unary(op, h, 0.3), f"n={n}")
+
+
+@pytest.mark.parametrize("op", [ol.EXP, ol.LOG, ol.TANH, ol.SIGMOID, ol.GELU_TANH, ol.SQRT, ol.RELU, ol.ABS])
+def test_bit_pattern_sweep(ct, oracle, op):
+    """Every 521st fp32 bit pattern (8.2 M inputs: NaN, inf, denormals, both signs)."""
+    count = (1 << 32) // 521
+    xin, ref = oracle.sweep(op, 7, 521, count)
+    got = ct.unary(op, torch.from_numpy(xin).cuda())
+    assert_bits_equal(got, ref, ol.UNARY_NAMES[op])
+
+
+@pytest.mark.parametrize("shape,dim", [((2048, 4096), 0), ((2048, 4096), 1), ((4099, 1031), 0), ((4099, 1031), 1),
+                                       ((8, 300000), 1), ((300000, 8), 0), ((3, 700, 1100), 1), ((1 << 22,), 0)])
+@pytest.mark.parametrize("op", [ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR, ol.ARGMAX])
+def test_reduce_shapes(ct, oracle, shape, dim, op):
+    x = HostView.contig(np.random.default_rng(sum(shape) + dim).standard_normal(shape).astype(np.float32))
+    got = ct.reduce(op, to_device(x), dim)
+    ref = oracle.reduce(op, x, dim)
+    if op in (ol.MAX, ol.MIN, ol.ARGMAX):
+        assert_bits_equal(got, ref, f"{shape} dim {dim}")
+    else:
+        assert_close(got, ref, RTOL, f"{shape} dim {dim}")
+
+
+@pytest.mark.parametrize("op", [ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR])
+def test_reduce_full_sizes(ct, oracle, op):
+    for n in (1, 7, 65536, (1 << 22) + 3):
+        x = HostView.contig((np.random.default_rng(n).standard_normal(n) + 0.25).astype(np.float32))
+        got = ct.reduce(op, to_device(x), -1)
+        ref = oracle.reduce(op, x, -1)
+        if op in (ol.MAX, ol.MIN):
+            assert_bits_equal(got, ref, f"full n={n}")
+        else:
+            assert_close(got, ref, RTOL, f"full n={n}")
+
+
+def test_argmax_ties_prefer_first_index(ct, oracle):
+    x = np.zeros((64, 5000), np.float32)
+    x[:, 1234] = 3.0
+    x[:, 4321] = 3.0
+    x[:, 77] = 3.0
+    h = HostView.contig(x)
+    got = ct.reduce(ct.ARGMAX, to_device(h), 1).cpu().numpy()
+    assert np.all(got == 77)
+    assert_bits_equal(ct.reduce(ct.ARGMAX, to_device(h.permute([1, 0])), 0), oracle.reduce(ol.ARGMAX, h.permute([1, 0]), 0))
+
+
+def test_reductions_are_deterministic(ct):
+    x = torch.randn(1 << 24, device="cuda")
+    m = x.view(4096, 4096)
+    for args in ((ct.SUM, x, -1), (ct.SUM, m, 0), (ct.SUM, m, 1), (ct.VAR, m, 0)):
+        a = ct.reduce(*args).cpu().numpy()
+        for _ in range(3):
+            assert np.array_equal(a.view(np.uint32), ct.reduce(*args).cpu().numpy().view(np.uint32))
+
+
+def test_caller_workspace(ct, oracle):
+    x = HostView.contig(np.random.default_rng(3).standard_normal((4096, 512)).astype(np.float32))
+    d = to_device(x)
+    need = ct.reduce_workspace_bytes(d, 0)
+    assert need > 0
+    ws = torch.zeros(need // 4 + 64, dtype=torch.int32, device="cuda")
+    got = ct.reduce(ct.SUM, d, 0, workspace=ws)
+    assert_close(got, oracle.reduce(ol.SUM, x, 0), RTOL)
+    with pytest.raises(ct.CtbError) as e:
+        ct.reduce(ct.SUM, d, 0, workspace=ws[:16])
+    assert e.value.code == 7
+
+
+def test_full_reduce_partials_for_sharding(ct, oracle):
+    """Two shards' fp64 partials summed on the host and finalised == the unsharded result."""
+    x = np.random.default_rng(9).standard_normal(1 << 21).astype(np.float32)
+    d = torch.from_numpy(x).cuda()
+    p0 = ct.reduce_full_partial(ct.SUM, d[: 1 << 20])
+    p1 = ct.reduce_full_partial(ct.SUM, d[1 << 20:])
+    tot = p0 + p1                                   # stands in for the all-reduce
+    for op in (ct.SUM, ct.MEAN):
+        got = ct.finalize_full(op, tot, x.size)
+        assert_close(got, oracle.reduce(op, HostView.contig(x), -1), RTOL)
+    m0 = ct.reduce_full_partial(ct.MAX, d[: 1 << 20])
+    m1 = ct.reduce_full_partial(ct.MAX, d[1 << 20:])
+    got = ct.finalize_full(ct.MAX, torch.maximum(m0, m1), x.size)
+    assert_bits_equal(got, oracle.reduce(ol.MAX, HostView.contig(x), -1))
+
+
+@pytest.mark.parametrize("cols", [1, 3, 32, 768, 1024, 1000, 3072, 8192, 10000])
+def test_fused_rows_widths(ct, oracle, cols):
+    rows = 37
+    rng = np.random.default_rng(cols)
+    x = HostView.contig(rng.standard_normal((rows, cols)).astype(np.float32))
+    g = HostView.contig(rng.normal(1, 0.02, cols).astype(np.float32))
+    b = HostView.contig(rng.normal(0, 0.02, cols).astype(np.float32))
+    assert_close(ct.softmax(to_device(x)), oracle.softmax(x), RTOL, f"softmax cols={cols}")
+    if cols > 1:
+        assert_close(ct.layernorm(to_device(x), to_device(g), to_device(b)), oracle.layernorm(x, g, b), RTOL,
+                     f"layernorm cols={cols}")
+
+
+def test_softmax_chain_equals_unfused_chain(ct):
+    """The fused kernel against the same chain run op by op through the C ABI."""
+    x = torch.randn(64, 12, 1024, device="cuda")
+    m = ct.reduce(ct.MAX, x, 2).view(64, 12, 1)
+    s = ct.binary(ct.SUB, x, m)
+    e = ct.unary(ct.EXP, s)
+    z = ct.reduce(ct.SUM, e, 2).view(64, 12, 1)
+    chain = ct.binary(ct.DIV, e, z)
+    fused = ct.softmax(x)
+    assert_close(fused, chain.cpu().numpy(), RTOL)
+    assert (fused.cpu().numpy().view(np.uint32) != chain.cpu().numpy().view(np.uint32)).mean() < 1e-3
+
+
+# ---- host-buffer entry points ---------------------------------------------------------------------------------
+def test_host_entry_points(ct, oracle):
+    n = (1 << 25) + 12345                       # > one pipeline chunk, ragged
+    rng = np.random.default_rng(1)
+    a = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).pin_memory()
+    b = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).pin_memory()
+    out = torch.empty(n, dtype=torch.float32).pin_memory()
+    ct.binary_host(ct.ADD, a, b, out)
+    ha, hb = HostView.contig(a.numpy()), HostView.contig(b.numpy())
+    assert_bits_equal(out.numpy(), oracle.binary(ol.ADD, ha, hb), "host add")
+    ct.unary_host(ct.GELU_TANH, a, out)
+    assert_bits_equal(out.numpy(), oracle.unary(ol.GELU_TANH, ha), "host gelu")
+    A = torch.from_numpy(rng.standard_normal((512, 300)).astype(np.float32))
+    B = torch.from_numpy(rng.standard_normal((1, 300)).astype(np.float32))
+    o2 = torch.empty(512, 300)
+    ct.binary_host(ct.MUL, A, B, o2)
+    assert_bits_equal(o2.numpy(), oracle.binary(ol.MUL, HostView.contig(A.numpy()), HostView.contig(B.numpy())))
+    r = torch.empty(300)
+    ct.reduce_host(ct.SUM, A, 0, r)
+    assert_close(r.numpy(), oracle.reduce(ol.SUM, HostView.contig(A.numpy()), 0), RTOL)
+
+
+# ---- size-independent properties at benchmark scale -----------------------------------------------------------------
+def test_large_properties(ct):
+    n = 1 << 28                                   # 1 GiB per tensor
+    x = torch.randn(n, device="cuda")
+    y = torch.randn(n, device="cuda")
+    s = ct.binary(ct.ADD, x, y)
+    back = ct.binary(ct.SUB, s, y)                # (x + y) - y == x up to one rounding of x+y
+    err = ct.reduce(ct.MAX, ct.unary(ct.ABS, ct.binary(ct.SUB, back, x)), -1).item()
+    assert err < 1e-5
+    del back
+    # commutativity is exact
+    s2 = ct.binary(ct.ADD, y, x)
+    assert ct.reduce(ct.SUM, ct.binary(ct.NE, s, s2), -1).item() == 0.0
+    del s2
+    # relu is idempotent and equals max(x, 0) expressed through compare+mul
+    r = ct.unary(ct.RELU, x)
+    assert ct.reduce(ct.SUM, ct.binary(ct.NE, ct.unary(ct.RELU, r), r), -1).item() == 0.0
+    assert ct.reduce(ct.MIN, r, -1).item() == 0.0
+    # checksum of checksums: full sum == sum of row sums == sum of column sums (fp64 accumulation)
+    m = x.view(1 << 14, 1 << 14)
+    full = ct.reduce(ct.SUM, x, -1).item()
+    rows = ct.reduce(ct.SUM, ct.reduce(ct.SUM, m, 1), -1).item()
+    cols = ct.reduce(ct.SUM, ct.reduce(ct.SUM, m, 0), -1).item()
+    scale = abs(full) + n ** 0.5
+    assert abs(full - rows) < 1e-5 * scale and abs(full - cols) < 1e-5 * scale
+    # max over everything == max of row maxima == max of column maxima, exactly
+    mx = ct.reduce(ct.MAX, x, -1).item()
+    assert mx == ct.reduce(ct.MAX, ct.reduce(ct.MAX, m, 1), -1).item() == ct.reduce(ct.MAX, ct.reduce(ct.MAX, m, 0), -1).item()
+    # argmax points at the maximum
+    am = ct.reduce(ct.ARGMAX, m, 1)
+    picked = m.gather(1, am.long().view(-1, 1)).view(-1)          # torch used only to index the check
+    assert torch.equal(picked, ct.reduce(ct.MAX, m, 1))
+
+
+def test_errors_on_device(ct):
+    a = torch.zeros(4, 3, device="cuda")
+    b = torch.zeros(4, 2, device="cuda")
+    with pytest.raises(ct.CtbError) as e:
+        ct.binary(ct.ADD, a, b, out=torch.zeros(4, 3, device="cuda"))
+    assert e.value.code == 2 and e.value.message == "Shape mismatch in binary op"
+    with pytest.raises(ct.CtbError) as e:
+        ct.reduce(ct.ARGMAX, a, 2)
+    assert e.value.code == 4
+    with pytest.raises(ct.CtbError) as e:
+        ct.unary(ct.EXP, torch.zeros(4, dtype=torch.int32, device="cuda"))
+    assert e.value.code == 3
+    empty = ct.binary(ct.ADD, torch.zeros(0, 3, device="cuda"), torch.zeros(1, 3, device="cuda"))
+    assert empty.shape == (0, 3)
