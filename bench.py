@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the elementwise operator path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (the "large contiguous fp32 bandwidth sweep" configuration): 1-d fp32 tensors x, y of
+n = 2^30 elements per GPU drawn N(0,1) from a seed; one step = add(x,y), mul(x,y), exp(x),
+relu(x), gelu(x) through the C ABI, i.e. 2 x 12n + 3 x 8n = 48n algorithmic bytes per GPU per
+step.  Every rank owns one shard of a leading-dim split (no data-path collective), so the
+per-GPU work is fixed as N grows ("weak"); `--scaling strong` keeps the total at 2^30 instead.
+
+Keys beyond the base contract:
+  roofline      the kernel with the largest share of the step, timed per launch with CUDA events
+                inside the timed region, against the measured HBM copy bandwidth
+  cpu_baseline  the reference's own CPU code (oracle/_ref) timed on this box's host cores on a
+                bounded sample (N=1, rank 0 only)
+  e2e           the same step through the host-buffer entry points (pinned host memory in,
+                pinned host memory out, copies inside the timed region)
+  per_op        GB/s of every op of the step
+  sweep         GB/s at the other sizes of the configuration (2^20, 2^24, 2^28), N=1 only
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+OPS = [("add", "binary", 12), ("mul", "binary", 12), ("exp", "unary", 8), ("relu", "unary", 8),
+       ("gelu", "unary", 8)]
+BYTES_PER_ELEM_STEP = sum(b for _, _, b in OPS)          # 48
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                smax = float(r[1])
+                for nme, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nme)
+            except Exception:
+                pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_step(ct, x, y, out, events=None):
+    """The five ops of one step; `events` (list of (start, end) pairs) times each launch."""
+    import torch
+    calls = [lambda: ct.binary(ct.ADD, x, y, out=out), lambda: ct.binary(ct.MUL, x, y, out=out),
+             lambda: ct.unary(ct.EXP, x, out=out), lambda: ct.unary(ct.RELU, x, out=out),
+             lambda: ct.unary(ct.GELU_TANH, x, out=out)]
+    for i, c in enumerate(calls):
+        if events is not None:
+            events[i][0].record()
+        c()
+        if events is not None:
+            events[i][1].record()
+
+
+def run_step_host(ct, hx, hy, hout, device):
+    ct.binary_host(ct.ADD, hx, hy, hout, device)
+    ct.binary_host(ct.MUL, hx, hy, hout, device)
+    ct.unary_host(ct.EXP, hx, hout, 0.0, device)
+    ct.unary_host(ct.RELU, hx, hout, 0.0, device)
+    ct.unary_host(ct.GELU_TANH, hx, hout, 0.0, device)
+
+
+def mem_available_bytes():
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable"):
+                return int(line.split()[1]) * 1024
+    except Exception:
+        pass
+    return 0
+
+
+def bench_ours(args):
+    import torch
+    import torch.distributed as dist
+    import ctensor_b200 as ct
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ct.lib()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    n_total = args.n * world if args.scaling == "weak" else args.n
+    n = n_total // world                                  # this rank's shard of the leading dim
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1 + rank)                             # shard i of the seeded tensor
+    x = torch.randn(n, device=dev, generator=gen)
+    y = torch.randn(n, device=dev, generator=gen)
+    out = torch.empty(n, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        run_step(ct, x, y, out)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS]
+          for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        run_step(ct, x, y, out, ev[k])
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+
+    # per-op launch durations (max over ranks of the mean over steps)
+    per_op_ms = torch.tensor([sum(ev[k][i][0].elapsed_time(ev[k][i][1]) for k in range(args.steps)) / args.steps
+                              for i in range(len(OPS))], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(per_op_ms, op=dist.ReduceOp.MAX)
+    per_op_ms = per_op_ms.tolist()
+
+    # ---- end to end through the host-buffer entry points --------------------------------------------
+    e2e = None
+    try:
+        n_e2e = n
+        need = 3 * 4 * n_e2e * max(world, 1)
+        avail = mem_available_bytes()
+        while n_e2e > (1 << 24) and avail and need * 3 > avail:
+            n_e2e //= 2
+            need //= 2
+        n_e2e = min(n_e2e, args.e2e_n) if args.e2e_n else n_e2e
+        hx = torch.empty(n_e2e, dtype=torch.float32).pin_memory()
+        hy = torch.empty(n_e2e, dtype=torch.float32).pin_memory()
+        hout = torch.empty(n_e2e, dtype=torch.float32).pin_memory()
+        hx.copy_(x[:n_e2e])
+        hy.copy_(y[:n_e2e])
+        run_step_host(ct, hx, hy, hout, local)            # warm-up (allocates the staging buffers)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            run_step_host(ct, hx, hy, hout, local)
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        sec = float(dt.item()) / args.e2e_steps
+        e2e = {"value": round(BYTES_PER_ELEM_STEP * n_e2e * world / sec / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": 28 * n_e2e, "d2h_bytes_per_step": 20 * n_e2e,
+               "elements_per_gpu": n_e2e, "ms_per_step": round(sec * 1e3, 3),
+               "note": "ctb_binary_host/ctb_unary_host on pinned host buffers; every op uploads its "
+                       "inputs and downloads its result (chunked, copies overlap the kernels)"}
+        del hx, hy, hout
+    except Exception as exc:                               # report, do not hide
+        e2e = {"value": None, "unit": "GB/s", "error": repr(exc)}
+
+    # ---- extras on rank 0 ------------------------------------------------------------------------------
+    sweep, cpu = None, None
+    if world == 1:
+        sweep = {}
+        for lg in (20, 24, 28):
+            m = 1 << lg
+            if m >= n:
+                continue
+            reps = 8 if lg >= 28 else 50
+            res = {}
+            # rotate over distinct slices so the small sizes are not served from L2
+            nslices = max(1, min(n // m, (1 << 30) // (4 * m) * 3))
+            for (name, kind, bpe), fn in zip(OPS, (
+                    lambda a, b, o: ct.binary(ct.ADD, a, b, out=o), lambda a, b, o: ct.binary(ct.MUL, a, b, out=o),
+                    lambda a, b, o: ct.unary(ct.EXP, a, out=o), lambda a, b, o: ct.unary(ct.RELU, a, out=o),
+                    lambda a, b, o: ct.unary(ct.GELU_TANH, a, out=o))):
+                for r in range(3):
+                    s = (r % nslices) * m
+                    fn(x[s:s + m], y[s:s + m], out[s:s + m])
+                torch.cuda.synchronize()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for r in range(reps):
+                    s = (r % nslices) * m
+                    fn(x[s:s + m], y[s:s + m], out[s:s + m])
+                a1.record()
+                torch.cuda.synchronize()
+                res[name] = round(bpe * m * reps / a0.elapsed_time(a1) / 1e6, 1)
+            sweep[f"2^{lg}"] = res
+        if not args.no_cpu_baseline:
+            cpu = cpu_baseline(sample_log2=args.cpu_log2)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak()
+    top = max(range(len(OPS)), key=lambda i: per_op_ms[i])
+    ach = OPS[top][2] * n / per_op_ms[top] / 1e6
+    value = BYTES_PER_ELEM_STEP * n * world / ms_per_step / 1e6
+    line = {
+        "metric": "op GB/s and % of 8 TB/s HBM peak at 1/2/4/8 B200 vs host-CPU reference",
+        "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"contiguous fp32 sweep, n=2^{n.bit_length() - 1} elements per GPU: add, mul, exp, relu, "
+                               "gelu(tanh) of N(0,1) tensors, sharded along dim 0",
+                   "elements_per_gpu": n, "elements_total": n * world, "parallelism": f"dp{world}",
+                   "algorithmic_bytes_per_step_per_gpu": BYTES_PER_ELEM_STEP * n,
+                   "l2": "inputs (4 GiB per tensor and GPU) exceed the 126 MB L2; no flush needed"},
+        "elements_per_s": round(5 * n * world / (ms_per_step * 1e-3), 1),
+        "pct_of_8TBs_per_gpu": round(100 * value / world / NOMINAL_HBM_GBS, 2),
+        "per_op": {OPS[i][0]: {"ms": round(per_op_ms[i], 4), "GB/s": round(OPS[i][2] * n / per_op_ms[i] / 1e6, 1)}
+                   for i in range(len(OPS))},
+        "roofline": {"bound": "hbm", "kernel": f"ew_flat_kernel<{OPS[top][0]}>", "achieved": round(ach, 1),
+                     "peak": peak, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
+                     "unit": "GB/s", "frac": round(ach / peak, 4), "frac_of_8TBs": round(ach / NOMINAL_HBM_GBS, 4),
+                     "traffic": None},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * args.steps,
+    }
+    if sweep is not None:
+        line["sweep"] = sweep
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            tr = json.load(open(traffic_file))
+            per_elem = tr.get(OPS[top][0], {}).get("dram_bytes_per_element")
+            if per_elem:
+                line["roofline"]["traffic"] = round(per_elem * n)
+        except Exception:
+            pass
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------
+def cpu_baseline(sample_log2=26, reps=3):
+    """The reference's CPU code on a bounded sample: n = 2^sample_log2 elements, the same five ops
+    (gelu as the chain of reference primitives).  Every back-end the reference has for the op is
+    timed; the fastest is the baseline value."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    n = 1 << sample_log2
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(n, dtype=np.float32)
+    y = rng.standard_normal(n, dtype=np.float32)
+    hx, hy = ol.HostView.contig(x), ol.HostView.contig(y)
+    kind, impl, paths = "port", None, {}
+    if ol.Reference.available():
+        try:
+            impl = ol.Reference()
+            kind = "reference"
+        except OSError:
+            impl = None
+    if impl is not None:
+        if impl.has_avx512:
+            paths["dispatch(avx512,1 thread as shipped)"] = ol.PATH_DISPATCH
+        if impl.has_avx2:
+            paths["avx2+openmp"] = ol.PATH_AVX2
+        paths["mp(scalar+openmp)"] = ol.PATH_MP
+    else:
+        impl = ol.Oracle()
+        paths["oracle port (plain C + OpenMP)"] = None
+
+    def step(path):
+        """Seconds for one step."""
+        if path is None:                                   # oracle port
+            t0 = time.perf_counter()
+            impl.binary(ol.ADD, hx, hy); impl.binary(ol.MUL, hx, hy)
+            impl.unary(ol.EXP, hx); impl.unary(ol.RELU, hx); impl.unary(ol.GELU_TANH, hx)
+            return time.perf_counter() - t0
+        return impl.bench_step(path, x, y)                 # timed inside the reference build
+
+    results = {}
+    for name, path in paths.items():
+        try:
+            step(path)
+            best = min(step(path) for _ in range(reps))
+            results[name] = round(BYTES_PER_ELEM_STEP * n / best / 1e9, 2)
+        except Exception as exc:
+            results[name] = f"failed: {exc}"
+    good = {k: v for k, v in results.items() if isinstance(v, float)}
+    best_name = max(good, key=good.get)
+    threads = impl.lib.ref_max_threads() if kind == "reference" else (os.cpu_count() or 1)
+    return {"value": good[best_name], "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"n=2^{sample_log2} elements per tensor, the same 5 ops, best of {reps}; fastest back-end: {best_name}; "
+                      "output allocation is inside every reference op and therefore inside its time",
+            "paths": results, "host_cpus": os.cpu_count()}
+
+
+def bench_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    n = 1 << args.cpu_log2
+    cpu = cpu_baseline(sample_log2=args.cpu_log2, reps=max(1, args.steps))
+    value = cpu["value"]
+    line = {
+        "impl": "reference",
+        "metric": "op GB/s and % of 8 TB/s HBM peak at 1/2/4/8 B200 vs host-CPU reference",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(BYTES_PER_ELEM_STEP * n / value / 1e6, 3), "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "contiguous fp32 sweep: add, mul, exp, relu, gelu(tanh) of N(0,1) tensors; each step a "
+                               f"bounded sample of n=2^{args.cpu_log2} elements on the host cores",
+                   "elements_per_step": n},
+        "cpu_baseline": cpu,
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n", type=int, default=1 << 30, help="elements per GPU (weak) or in total (strong)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-n", type=int, default=0, help="cap on the e2e tensor size (0 = same as --n)")
+    ap.add_argument("--cpu-log2", type=int, default=26)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        bench_reference(args)
+    else:
+        bench_ours(args)
+
+
+if __name__ == "__main__":
+    main()

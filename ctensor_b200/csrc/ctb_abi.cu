@@ -276,6 +276,8 @@ int reduce_arg_check(int op, const ctb_view* a, int dim) {
     int rc = check_view(a, "reduction: null input", "reduction");
     if (rc) return rc;
     if (op < 0 || op >= CTB_REDUCE_OP_COUNT) return set_error(CTB_ERR_ARG, "reduction: unknown operator code %d", op);
+    if (op == CTB_VAR && a->dtype == CTB_I32)
+        return set_error(CTB_ERR_DTYPE, "var: not defined for integer tensors");
     if (op == CTB_ARGMAX) {
         if (dim < 0 || dim >= a->ndim) return set_error(CTB_ERR_DIM, "argmax: dim out of range");
     } else if (dim != CTB_DIM_FULL && (dim < 0 || dim >= a->ndim)) {
@@ -286,7 +288,7 @@ int reduce_arg_check(int op, const ctb_view* a, int dim) {
 
 // Scratch needed by ctb_reduce for (a, dim): kernel scratch, plus a packed copy of the input
 // when a full reduction is asked of a non-dense view.
-size_t reduce_ws_need(const ctb_view* a, int dim, size_t* copy_bytes) {
+size_t reduce_ws_need(const ctb_view* a, int dim, size_t* copy_bytes, bool want_partial = false) {
     ReduceGeom g;
     *copy_bytes = 0;
     if (dim == CTB_DIM_FULL) {
@@ -295,7 +297,12 @@ size_t reduce_ws_need(const ctb_view* a, int dim, size_t* copy_bytes) {
     } else {
         reduce_geom_dim(a, dim, &g);
     }
-    return *copy_bytes + reduce_workspace_bytes(g, a->dtype);
+    size_t kernel_ws = reduce_workspace_bytes(g, a->dtype);
+    // the packed copy must never overlap the ticket region at the start of the scratch
+    if (*copy_bytes && kernel_ws < kTicketBytes) kernel_ws = kTicketBytes;
+    // fp64 partials always come from the split kernel, even for inputs it would not pick itself
+    if (want_partial && kernel_ws < kTicketBytes + 256) kernel_ws = kTicketBytes + 256;
+    return *copy_bytes + kernel_ws;
 }
 
 int do_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, double* partial,
@@ -303,7 +310,7 @@ int do_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, double* p
     ReduceGeom g;
     const void* src = elem_ptr(a);
     size_t copy_bytes = 0;
-    const size_t need = reduce_ws_need(a, dim, &copy_bytes);
+    const size_t need = reduce_ws_need(a, dim, &copy_bytes, partial != nullptr);
     if (need > ws_bytes || (need && !ws)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace of %zu bytes needed, %zu given", need, ws_bytes);
     if (need && !is_aligned(ws, 256)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace must be 256-byte aligned");
     if (dim == CTB_DIM_FULL) {
@@ -503,6 +510,9 @@ int ctb_reduce_ws(int op, const ctb_view* a, int dim, const ctb_view* out, void*
     int rc;
     if ((rc = reduce_arg_check(op, a, dim))) return rc;
     if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    // a caller's buffer has unknown contents: clear the ticket region the split kernels rely on
+    if (workspace && workspace_bytes >= kTicketBytes && ctb_reduce_workspace_bytes(a, dim) > 0)
+        CTB_CUDA_TRY(cudaMemsetAsync(workspace, 0, kTicketBytes, (cudaStream_t)stream));
     return do_reduce(op, a, dim, out, nullptr, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
@@ -525,7 +535,7 @@ int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* st
         return set_error(CTB_ERR_ARG, "reduction: fp64 partials exist for sum/mean/max/min only");
     if (a->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "reduction: fp64 partials need a Float32 input");
     size_t copy_bytes;
-    const size_t need = reduce_ws_need(a, CTB_DIM_FULL, &copy_bytes);
+    const size_t need = reduce_ws_need(a, CTB_DIM_FULL, &copy_bytes, true);
     void* ws = nullptr;
     if ((rc = ensure_workspace(need, &ws))) return rc;
     return do_reduce(op, a, CTB_DIM_FULL, nullptr, partial, ws, need, (cudaStream_t)stream);

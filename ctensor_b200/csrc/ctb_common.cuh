@@ -39,20 +39,20 @@ struct Plan {
 };
 
 // ---- vector access ----------------------------------------------------------------------------
-// Streaming 128-bit and 256-bit global accesses.  Inputs of the elementwise and reduction
-// kernels are read exactly once, so loads bypass L1 allocation; stores are plain (write-back
-// in L2, which coalesces the full lines before they go to HBM).
+// 128-bit and 256-bit global accesses (sm_100 has 256-bit ld/st.global).  Plain loads and stores:
+// on B200 the default cache policy measured faster than .nc, L1::no_allocate or .cs hints for
+// these read-once / write-once streams.
 template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T v[N]; };
 
 __device__ __forceinline__ Vec<float, 4> ldg_stream(const Vec<float, 4>* p) {
     Vec<float, 4> r;
-    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "l"(p));
     return r;
 }
 __device__ __forceinline__ Vec<float, 8> ldg_stream(const Vec<float, 8>* p) {
     Vec<float, 8> r;
-    asm volatile("ld.global.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+    asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]),
                    "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7]) : "l"(p));
     return r;

@@ -32,8 +32,8 @@ namespace ctb {
 #define CTB_RED_SPLIT_CTAS_PER_SM 4
 #endif
 
-constexpr int kCounterSlots = 16384;                 // uint32 tickets at the start of scratch
-constexpr size_t kCounterBytes = kCounterSlots * sizeof(uint32_t);
+constexpr int kCounterSlots = kTicketSlots;           // uint32 tickets at the start of scratch
+constexpr size_t kCounterBytes = kTicketBytes;
 
 // ---- accumulation policies ------------------------------------------------------------------------
 // VT is the element type as the policy sees it (float on the fast paths, double on the generic

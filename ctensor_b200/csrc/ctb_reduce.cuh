@@ -17,6 +17,11 @@ struct ReduceGeom {
     int64_t total;       // element count that "mean"/"var" divide by (== rlen)
 };
 
+// Split reductions keep their tickets (uint32 counters, zero between launches) in the first
+// kTicketBytes of the scratch buffer; nothing else may be written there.
+constexpr int kTicketSlots = 16384;
+constexpr size_t kTicketBytes = kTicketSlots * sizeof(uint32_t);
+
 // Bytes of scratch the chosen kernel shape needs for this geometry (0 when none).
 size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype);
 

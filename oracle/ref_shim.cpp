@@ -17,6 +17,7 @@
 #include <string>
 #include <vector>
 #include <omp.h>
+#include <chrono>
 
 #include "tensor.h"
 #include "opsmp.h"
@@ -333,6 +334,32 @@ int64_t ref_layernorm_lastdim(const RefView* x, const RefView* gamma, const RefV
         if (beta) y = add_mp(y, wrap(beta));
         return emit(y, out, cap);
     });
+}
+
+// Wall time (seconds, std::chrono like the reference's own test/time_avx.cpp:11-24) of one
+// benchmark step on contiguous 1-d inputs of n elements: add, mul, exp, relu and the GELU
+// chain, each through the named back-end, results dropped as soon as they exist (the output
+// allocation every reference op performs is inside the time; no copy-out is).
+double ref_bench_step(int path, const float* x, const float* y, int64_t n) {
+    RefView vx{}, vy{};
+    vx.base = (void*)x; vx.dtype = 0; vx.ndim = 1; vx.shape[0] = n; vx.stride[0] = 1;
+    vy = vx; vy.base = (void*)y;
+    try {
+        g_err.clear();
+        Tensor a = wrap(&vx), b = wrap(&vy);
+        const int tanh_path = (path == PATH_AVX2) ? PATH_AVX2 : PATH_AVX512;
+        auto t0 = std::chrono::high_resolution_clock::now();
+        { Tensor r = do_binary(path, B_ADD, a, b); }
+        { Tensor r = do_binary(path, B_MUL, a, b); }
+        { Tensor r = do_unary(path, U_EXP, a, 0.0); }
+        { Tensor r = do_unary(path, U_RELU, a, 0.0); }
+        { Tensor r = gelu_chain(a, tanh_path); }
+        auto t1 = std::chrono::high_resolution_clock::now();
+        return std::chrono::duration<double>(t1 - t0).count();
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1.0;
+    }
 }
 
 }  // extern "C"

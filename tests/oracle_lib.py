@@ -250,6 +250,8 @@ class Reference:
         L.ref_softmax_lastdim.argtypes = [ctypes.c_int, vp, vp, vd, i64]
         L.ref_layernorm_lastdim.restype = i64
         L.ref_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, vd, i64]
+        L.ref_bench_step.restype = ctypes.c_double
+        L.ref_bench_step.argtypes = [ctypes.c_int, vd, vd, i64]
         feats = L.ref_cpu_features()
         self.has_avx2 = bool(feats & 1)
         self.has_avx512 = bool(feats & 2)
@@ -267,6 +269,13 @@ class Reference:
             raise RuntimeError(self.lib.ref_last_error().decode())
         assert n == out.size, (n, out.size)
         return out
+
+    def bench_step(self, path, x: np.ndarray, y: np.ndarray) -> float:
+        """Seconds for add, mul, exp, relu, gelu-chain on contiguous fp32 arrays (timed in C++)."""
+        t = self.lib.ref_bench_step(path, x.ctypes.data, y.ctypes.data, x.size)
+        if t < 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return t
 
     def binary(self, op, a, b, path=PATH_MP):
         out = np.empty(broadcast_shape(a.shape, b.shape), NP_DTYPES[a.dtype])
