@@ -197,7 +197,7 @@ def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
         db = 1 if i < nd - len(b) else b[i - (nd - len(b))]
         if da != db and da != 1 and db != 1:
             raise CtbError(2, "Shape mismatch in binary op")
-        out.append(max(da, db))
+        out.append(db if da == 1 else da)
     return tuple(out)
 
 

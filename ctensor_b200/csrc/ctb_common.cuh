@@ -78,6 +78,14 @@ __host__ __device__ __forceinline__ bool is_aligned(const void* p, size_t bytes)
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Broadcast lane 0's 64-bit value to the whole warp (index arithmetic with divisions is done
+// by one lane and shared, not repeated by all 32).
+__device__ __forceinline__ int64_t warp_bcast64(int64_t v) {
+    int lo = __shfl_sync(0xffffffffu, (int)(v & 0xffffffffll), 0);
+    int hi = __shfl_sync(0xffffffffu, (int)(v >> 32), 0);
+    return ((int64_t)hi << 32) | (uint32_t)lo;
+}
+
 // ---- launchers implemented in the .cu files ---------------------------------------------------
 // All return a ctb_status and never synchronise.
 int launch_binary(int op, int dtype, const Plan& plan, const void* a, const void* b, void* out,

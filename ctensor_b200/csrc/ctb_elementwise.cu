@@ -35,6 +35,48 @@ namespace ctb {
 #define CTB_ROWS_UNROLL 4
 #endif
 
+// ---- functor adapters ----------------------------------------------------------------------------
+template <int OP, typename T> struct BinAdapter {
+    static constexpr bool kHasPair = false;
+    __device__ __forceinline__ static T apply2(T x, T y) { return BinaryFn<OP, T>::apply(x, y); }
+    __device__ __forceinline__ static T apply1(T x, double) { return x; }
+};
+template <int OP, typename T> struct UnAdapter {
+    static constexpr bool kHasPair = false;
+    __device__ __forceinline__ static T apply2(T x, T) { return x; }
+    __device__ __forceinline__ static T apply1(T x, double s) { return UnaryFn<OP, T>::apply(x, s); }
+};
+template <int OP> struct UnAdapter<OP, float> {
+    static constexpr bool kHasPair = UnaryFn<OP, float>::kHasPair;
+    __device__ __forceinline__ static float apply2(float x, float) { return x; }
+    __device__ __forceinline__ static float apply1(float x, double s) { return UnaryFn<OP, float>::apply(x, s); }
+    __device__ __forceinline__ static float2 apply_pair(float2 x, double s) { return UnaryFn<OP, float>::apply_pair(x, s); }
+};
+template <typename T> struct CopyAdapter {
+    static constexpr bool kHasPair = false;
+    __device__ __forceinline__ static T apply2(T x, T) { return x; }
+    __device__ __forceinline__ static T apply1(T x, double) { return x; }
+};
+
+// r = f(va [, vb]) over one vector; unary functors with a packed form process two lanes at a time.
+template <typename F, typename T, int NIN, int VEC>
+__device__ __forceinline__ void apply_vec(Vec<T, VEC>& r, const Vec<T, VEC>& va, const Vec<T, VEC>& vb, double scalar) {
+    if constexpr (NIN == 1 && F::kHasPair && VEC % 2 == 0) {
+#pragma unroll
+        for (int k = 0; k < VEC; k += 2) {
+            const float2 t = F::apply_pair(make_float2(va.v[k], va.v[k + 1]), scalar);
+            r.v[k] = t.x;
+            r.v[k + 1] = t.y;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            if (NIN == 2) r.v[k] = F::apply2(va.v[k], vb.v[k]);
+            else r.v[k] = F::apply1(va.v[k], scalar);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // ew_flat: out[i] = f(a[i * sa], b[i * sb]) with sa, sb in {0, 1}.
 // One CTA per tile of THREADS*VEC*UNROLL consecutive elements (no grid-stride loop: on B200 a
@@ -67,19 +109,22 @@ ew_flat_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
             for (int u = 0; u < UNROLL; ++u)
                 vb[u] = ldg_stream(reinterpret_cast<const V*>(b + base + (int64_t)u * THREADS * VEC));
         }
+        if (a_bcast) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) va[u].v[k] = a0;
+        }
+        if (NIN == 2 && b_bcast) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) vb[u].v[k] = b0;
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             V r;
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                T x = a_bcast ? a0 : va[u].v[k];
-                if (NIN == 2) {
-                    T y = b_bcast ? b0 : vb[u].v[k];
-                    r.v[k] = F::apply2(x, y);
-                } else {
-                    r.v[k] = F::apply1(x, scalar);
-                }
-            }
+            apply_vec<F, T, NIN, VEC>(r, va[u], vb[u], scalar);
             stg_stream(reinterpret_cast<V*>(out + base + (int64_t)u * THREADS * VEC), r);
         }
     } else {
@@ -99,11 +144,15 @@ ew_flat_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
 // ew_rows: plan dims = [outer..., inner]; inner strides are 0/1 for every input.
 // A tile is VEC*THREADS consecutive inner elements of one row.  tile -> (row, chunk) by one
 // 32-bit div, row -> per-operand offsets by ndim-1 div/mods, both once per thread per tile.
+// Rows are enumerated in the order the host chose (oshape/ostride* are listed in that order):
+// for a permuted input it follows the INPUT's memory order, so reads stream sequentially and
+// the writes form a few sequential streams, instead of reads hopping between distant 4 KiB runs.
 // ------------------------------------------------------------------------------------------------
 struct RowsArgs {
     int32_t nouter;                         // number of outer dims (plan.ndim - 1)
     uint32_t oshape[CTB_MAX_DIMS];          // outer shapes, outer -> inner
     int64_t ostride[2][CTB_MAX_DIMS];       // per input
+    int64_t ostride_out[CTB_MAX_DIMS];      // output stride of each outer dim (elements)
     int32_t istride[2];                     // inner stride per input: 0 or 1
     uint32_t inner;                         // inner length
     uint32_t tiles_per_row;
@@ -116,31 +165,48 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
                RowsArgs g, double scalar) {
     using V = Vec<T, VEC>;
     constexpr uint32_t TILE = THREADS * VEC;
+    // Per-tile offsets are computed by one thread each and shared through smem: the div/mod
+    // chain would otherwise be repeated by all THREADS threads and dominate the kernel.
+    __shared__ int64_t s_oa[UNROLL], s_ob[UNROLL], s_oo[UNROLL];
+    __shared__ uint32_t s_col[UNROLL];
     for (uint32_t t0 = blockIdx.x * UNROLL; t0 < g.ntiles; t0 += gridDim.x * UNROLL) {
+        if (threadIdx.x < UNROLL) {
+            const uint32_t t = t0 + threadIdx.x;
+            uint32_t col0 = 0xFFFFFFFFu;                // "no tile"
+            int64_t oa = 0, ob = 0, oout = 0;
+            if (t < g.ntiles) {
+                uint32_t row = t / g.tiles_per_row;
+                col0 = (t - row * g.tiles_per_row) * TILE;
+                for (int d = g.nouter - 1; d >= 0; --d) {
+                    const uint32_t q = row / g.oshape[d];
+                    const uint32_t c = row - q * g.oshape[d];
+                    row = q;
+                    oa += (int64_t)c * g.ostride[0][d];
+                    if (NIN == 2) ob += (int64_t)c * g.ostride[1][d];
+                    oout += (int64_t)c * g.ostride_out[d];
+                }
+            }
+            s_oa[threadIdx.x] = oa;
+            s_ob[threadIdx.x] = ob;
+            s_oo[threadIdx.x] = oout;
+            s_col[threadIdx.x] = col0;
+        }
+        __syncthreads();
         V va[UNROLL], vb[UNROLL];
         int64_t oo[UNROLL];
         uint32_t cnt[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const uint32_t t = t0 + u;
             cnt[u] = 0;
-            if (t >= g.ntiles) continue;
-            uint32_t row = t / g.tiles_per_row;
-            const uint32_t col = (t - row * g.tiles_per_row) * TILE + threadIdx.x * VEC;
-            oo[u] = (int64_t)row * g.inner + col;
-            int64_t oa = 0, ob = 0;
-            for (int d = g.nouter - 1; d >= 0; --d) {
-                const uint32_t q = row / g.oshape[d];
-                const uint32_t c = row - q * g.oshape[d];
-                row = q;
-                oa += (int64_t)c * g.ostride[0][d];
-                if (NIN == 2) ob += (int64_t)c * g.ostride[1][d];
-            }
+            const uint32_t col0 = s_col[u];
+            if (col0 == 0xFFFFFFFFu) continue;
+            const uint32_t col = col0 + threadIdx.x * VEC;
             if (col >= g.inner) continue;
+            oo[u] = s_oo[u] + col;
             const uint32_t left = g.inner - col;
             cnt[u] = left < (uint32_t)VEC ? left : (uint32_t)VEC;
-            const T* pa = a + oa + (g.istride[0] ? col : 0);
-            const T* pb = (NIN == 2) ? b + ob + (g.istride[1] ? col : 0) : nullptr;
+            const T* pa = a + s_oa[u] + (g.istride[0] ? col : 0);
+            const T* pb = (NIN == 2) ? b + s_ob[u] + (g.istride[1] ? col : 0) : nullptr;
             if (ALIGNED && cnt[u] == VEC) {
                 if (g.istride[0]) va[u] = ldg_stream(reinterpret_cast<const V*>(pa));
                 else {
@@ -170,11 +236,7 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
         for (int u = 0; u < UNROLL; ++u) {
             if (cnt[u] == 0) continue;
             V r;
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                if (NIN == 2) r.v[k] = F::apply2(va[u].v[k], vb[u].v[k]);
-                else r.v[k] = F::apply1(va[u].v[k], scalar);
-            }
+            apply_vec<F, T, NIN, VEC>(r, va[u], vb[u], scalar);
             if (ALIGNED && cnt[u] == VEC) {
                 stg_stream(reinterpret_cast<V*>(out + oo[u]), r);
             } else {
@@ -183,6 +245,7 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
                     if ((uint32_t)k < cnt[u]) out[oo[u] + k] = r.v[k];
             }
         }
+        __syncthreads();      // smem is rewritten by the next pass
     }
 }
 
@@ -207,20 +270,6 @@ ew_gather_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict
         else out[i] = F::apply1(a[oa], scalar);
     }
 }
-
-// ---- functor adapters ----------------------------------------------------------------------------
-template <int OP, typename T> struct BinAdapter {
-    __device__ __forceinline__ static T apply2(T x, T y) { return BinaryFn<OP, T>::apply(x, y); }
-    __device__ __forceinline__ static T apply1(T x, double) { return x; }
-};
-template <int OP, typename T> struct UnAdapter {
-    __device__ __forceinline__ static T apply2(T x, T) { return x; }
-    __device__ __forceinline__ static T apply1(T x, double s) { return UnaryFn<OP, T>::apply(x, s); }
-};
-template <typename T> struct CopyAdapter {
-    __device__ __forceinline__ static T apply2(T x, T) { return x; }
-    __device__ __forceinline__ static T apply1(T x, double) { return x; }
-};
 
 // ---- host-side shape classification and launch ----------------------------------------------------
 namespace {
@@ -288,11 +337,32 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
         int64_t rows = 1;
         bool aligned = is_aligned(out, CTB_ROWS_VEC_BYTES) && is_aligned(a, CTB_ROWS_VEC_BYTES) &&
                        (NIN == 1 || is_aligned(b, CTB_ROWS_VEC_BYTES)) && (p.shape[nd - 1] % RVEC == 0);
-        for (int d = 0; d < nd - 1; ++d) {
-            g.oshape[d] = (uint32_t)p.shape[d];
+        // Enumeration order of the outer dims: by decreasing stride of the first full-size
+        // (non-broadcast) input, i.e. that input's memory order; ties keep the output order.
+        int order[CTB_MAX_DIMS];
+        for (int d = 0; d < nd - 1; ++d) order[d] = d;
+        int lead = 0;
+        for (int i = 0; i < NIN; ++i) {
+            bool full = true;
+            for (int d = 0; d < nd - 1; ++d) if (p.stride[i][d] == 0) full = false;
+            if (full) { lead = i; break; }
+        }
+        for (int i = 1; i < nd - 1; ++i)
+            for (int j = i; j > 0 && p.stride[lead][order[j]] > p.stride[lead][order[j - 1]]; --j) {
+                const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+            }
+        int64_t out_stride[CTB_MAX_DIMS];
+        {
+            int64_t st = p.shape[nd - 1];
+            for (int d = nd - 2; d >= 0; --d) { out_stride[d] = st; st *= p.shape[d]; }
+        }
+        for (int k = 0; k < nd - 1; ++k) {
+            const int d = order[k];
+            g.oshape[k] = (uint32_t)p.shape[d];
+            g.ostride_out[k] = out_stride[d];
             rows *= p.shape[d];
             for (int i = 0; i < NIN; ++i) {
-                g.ostride[i][d] = p.stride[i][d];
+                g.ostride[i][k] = p.stride[i][d];
                 if (p.stride[i][d] % RVEC != 0) aligned = false;
             }
         }

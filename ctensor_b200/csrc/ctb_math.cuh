@@ -16,9 +16,8 @@ namespace ctb {
 // ops_avx2_f32.cpp:58-100, as GCC contracts it under the shipped -O3 -mfma flags).
 // SSE min/max return the second operand on an unordered compare, hence the selects.
 __device__ __forceinline__ float exp_cephes(float x) {
-    const float HI = 88.3762626647949f, LO = -88.3762626647949f;
-    x = (x < HI) ? x : HI;
-    x = (x > LO) ? x : LO;
+    x = fminf(x, 88.3762626647949f);      // min_ps(x, HI): NaN -> HI, as fminf does
+    x = fmaxf(x, -88.3762626647949f);
     float fx = fmaf(x, 1.44269504088896341f, 0.5f);
     // floor(fx) without the conversion pipe: |fx| <= 129, so adding 1.5*2^23 rounds to the
     // nearest integer (exactly), and one compare corrects nearest -> floor.
@@ -109,6 +108,83 @@ __device__ __forceinline__ float gelu_tanh_chain(float x) {
     return __fmul_rn(h, t);
 }
 
+// ---- packed (two lanes per instruction) GELU ---------------------------------------------------
+// sm_100 has packed fp32 instructions (fma/add/mul.rn.f32x2): one issue slot does two IEEE
+// operations, and the GELU chain is bound by issue slots, not by HBM.  Each lane computes
+// exactly the scalar sequence above, so results are bit-identical to gelu_tanh_chain (checked
+// over all 2^32 inputs on a B200).
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+
+// exp_cephes for two lanes: clamp, fx and floor per lane; range reduction and polynomial packed.
+__device__ __forceinline__ void exp_cephes_front(float& x, float& neg_fx, int32_t& n) {
+    x = fminf(x, 88.3762626647949f);      // == (x < HI) ? x : HI, also for NaN
+    x = fmaxf(x, -88.3762626647949f);
+    const float fx = fmaf(x, 1.44269504088896341f, 0.5f);
+    const float MAGIC = 12582912.0f;
+    float r = __fadd_rn(fx, MAGIC);
+    n = __float_as_int(r) - 0x4B400000;
+    r = __fsub_rn(r, MAGIC);
+    if (r > fx) { r = __fsub_rn(r, 1.0f); n -= 1; }
+    neg_fx = -r;
+}
+__device__ __forceinline__ float2 exp_cephes2(float2 v) {
+    float x0 = v.x, x1 = v.y, f0, f1;
+    int32_t n0, n1;
+    exp_cephes_front(x0, f0, n0);
+    exp_cephes_front(x1, f1, n1);
+    float2 x = make_float2(x0, x1);
+    const float2 nfx = make_float2(f0, f1);
+    x = __ffma2_rn(nfx, splat2(0.693359375f), x);
+    x = __ffma2_rn(nfx, splat2(-2.12194440e-4f), x);
+    const float2 z = __fmul2_rn(x, x);
+    float2 y = splat2(1.9875691500E-4f);
+    y = __ffma2_rn(y, x, splat2(1.3981999507E-3f));
+    y = __ffma2_rn(y, x, splat2(8.3334519073E-3f));
+    y = __ffma2_rn(y, x, splat2(4.1665795894E-2f));
+    y = __ffma2_rn(y, x, splat2(1.6666665459E-1f));
+    y = __ffma2_rn(y, x, splat2(0.5f));
+    y = __ffma2_rn(y, z, x);
+    y = __fadd2_rn(y, splat2(1.0f));
+    const float2 p = make_float2(__int_as_float((n0 + 127) << 23), __int_as_float((n1 + 127) << 23));
+    return __fmul2_rn(y, p);
+}
+
+// (e-1)/(e+1) for e = exp_cephes(.) in [0, 2^25]: reciprocal estimate, one Newton step, quotient
+// and one remainder correction.  For these operands (denominator in [1, 2^25+1], |quotient| <= 1)
+// the result equals IEEE division; for e > 2^25 both e-1 and e+1 round to e and the quotient is
+// exactly 1.  Verified against __fdiv_rn for every fp32 input of the GELU chain.
+__device__ __forceinline__ float2 tanh_ratio2(float2 e) {
+    const float2 a = __fadd2_rn(e, splat2(-1.0f));
+    const float2 b = __fadd2_rn(e, splat2(1.0f));
+    float2 r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(b.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(b.y));
+    const float2 nb = make_float2(-b.x, -b.y);
+    const float2 err = __ffma2_rn(nb, r, splat2(1.0f));
+    r = __ffma2_rn(r, err, r);
+    const float2 q = __fmul2_rn(a, r);
+    const float2 rem = __ffma2_rn(nb, q, a);
+    float2 t = __ffma2_rn(rem, r, q);
+    t.x = (e.x > 33554432.0f) ? 1.0f : t.x;
+    t.y = (e.y > 33554432.0f) ? 1.0f : t.y;
+    return t;
+}
+
+__device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
+    float2 u = __fmul2_rn(x, x);
+    u = __fmul2_rn(u, x);
+    u.x = mul_scalar_f32(u.x, 0.044715);
+    u.y = mul_scalar_f32(u.y, 0.044715);
+    u = __fadd2_rn(x, u);
+    u.x = mul_scalar_f32(u.x, 0.7978845608028654);
+    u.y = mul_scalar_f32(u.y, 0.7978845608028654);
+    const float2 e = exp_cephes2(__fmul2_rn(u, splat2(2.0f)));
+    float2 t = tanh_ratio2(e);
+    t = __fadd2_rn(t, splat2(1.0f));
+    const float2 h = __fmul2_rn(x, splat2(0.5f));
+    return __fmul2_rn(h, t);
+}
+
 // static_cast<int32_t>(double) as x86 cvttsd2si does it (write_scalar_at,
 // src/core/tensor.h:77): truncation, INT32_MIN for NaN / out of range.
 __device__ __forceinline__ int32_t d2i_x86(double v) {
@@ -196,6 +272,12 @@ template <int OP> struct UnaryFn<OP, float> {
         if (OP == CTB_SIGMOID) return sigmoid_cephes(x);
         if (OP == CTB_GELU_TANH) return gelu_tanh_chain(x);
         return __double2float_rn(unary_double<OP>((double)x, s));
+    }
+    // Two lanes at once where a packed implementation exists (same bits as apply()).
+    static constexpr bool kHasPair = (OP == CTB_GELU_TANH);
+    __device__ __forceinline__ static float2 apply_pair(float2 x, double s) {
+        if (OP == CTB_GELU_TANH) return gelu_tanh_chain2(x);
+        return make_float2(apply(x.x, s), apply(x.y, s));
     }
 };
 

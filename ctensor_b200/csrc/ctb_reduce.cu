@@ -31,6 +31,15 @@ namespace ctb {
 #ifndef CTB_RED_SPLIT_CTAS_PER_SM
 #define CTB_RED_SPLIT_CTAS_PER_SM 4
 #endif
+#ifndef CTB_RED_BLOCK_THREADS
+#define CTB_RED_BLOCK_THREADS 512          // one CTA per long row: 512 threads measured best on B200
+#endif
+#ifndef CTB_RED_COLS_UNROLL
+#define CTB_RED_COLS_UNROLL 8
+#endif
+#ifndef CTB_RED_COLS_CTAS_PER_SM
+#define CTB_RED_COLS_CTAS_PER_SM 14        // ~2048 CTAs on 148 SMs
+#endif
 
 constexpr int kCounterSlots = kTicketSlots;           // uint32 tickets at the start of scratch
 constexpr size_t kCounterBytes = kTicketBytes;
@@ -192,6 +201,13 @@ __device__ __forceinline__ A load_cg(const A* p) {
     return r;
 }
 
+// outer_offset evaluated by lane 0 and broadcast (all lanes of the warp ask for the same row).
+__device__ __forceinline__ int64_t outer_offset_warp(const OuterIdx& o, int64_t i) {
+    int64_t off = 0;
+    if ((threadIdx.x & 31) == 0) off = outer_offset(o, i);
+    return warp_bcast64(off);
+}
+
 template <typename Pol>
 __device__ __forceinline__ typename Pol::Acc warp_reduce(typename Pol::Acc a) {
 #pragma unroll
@@ -250,7 +266,7 @@ reduce_rows_warp_kernel(const float* __restrict__ a, void* out, OuterIdx o, int6
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (THREADS / 32);
     for (int64_t row = (int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); row < nout; row += warps) {
-        const float* line = a + outer_offset(o, row);
+        const float* line = a + outer_offset_warp(o, row);
         const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, lane, 32, shift);
@@ -265,7 +281,7 @@ __global__ void __launch_bounds__(THREADS)
 reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen, int op) {
     __shared__ typename Pol::Acc smem[THREADS / 32];
     for (int64_t row = blockIdx.x; row < nout; row += gridDim.x) {
-        const float* line = a + outer_offset(o, row);
+        const float* line = a + outer_offset_warp(o, row);
         const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
@@ -286,7 +302,7 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
     __shared__ bool is_last;
     const int64_t row = blockIdx.y;
     const int splits = gridDim.x;
-    const float* line = a + outer_offset(o, row);
+    const float* line = a + outer_offset_warp(o, row);
     const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
     const int64_t lo = (int64_t)blockIdx.x * chunk;
     int64_t hi = lo + chunk;
@@ -329,7 +345,7 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
     const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
     const int64_t col = ((int64_t)blockIdx.x * 32 + x) * VEC;
     const int64_t b = blockIdx.z;
-    const float* base = a + outer_offset(batch, b);
+    const float* base = a + outer_offset_warp(batch, b);
     const int splits = gridDim.y;
     const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
     int64_t r1 = r0 + rows_per_split;
@@ -347,12 +363,12 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
         }
         const float* p = base + col;
         int64_t r = r0 + y;
-        for (; r + 8 * (CTB_RED_UNROLL - 1) < r1; r += 8 * CTB_RED_UNROLL) {
-            V v[CTB_RED_UNROLL];
+        for (; r + 8 * (CTB_RED_COLS_UNROLL - 1) < r1; r += 8 * CTB_RED_COLS_UNROLL) {
+            V v[CTB_RED_COLS_UNROLL];
 #pragma unroll
-            for (int u = 0; u < CTB_RED_UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
+            for (int u = 0; u < CTB_RED_COLS_UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
 #pragma unroll
-            for (int u = 0; u < CTB_RED_UNROLL; ++u)
+            for (int u = 0; u < CTB_RED_COLS_UNROLL; ++u)
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
         }
@@ -474,7 +490,7 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
             c.coltiles = ceil_div(ncols, 32 * c.vec);
             c.batch = batch;
             int64_t ctas = c.coltiles * batch;
-            int64_t want = ceil_div((int64_t)sm_count * 8, ctas);
+            int64_t want = ceil_div((int64_t)sm_count * CTB_RED_COLS_CTAS_PER_SM, ctas);
             int64_t max_splits = g.rlen / 64;
             if (want > max_splits) want = max_splits;
             if (want > 64) want = 64;
@@ -511,18 +527,19 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
     static_assert(sizeof(typename Pol::Acc) <= 16, "accumulator larger than the scratch slot");
     switch (c.shape) {
     case SH_ROWS_WARP: {
+        // one warp per row, one pass per CTA (a persistent grid measured slower)
         int64_t blocks = ceil_div(g.nout, T / 32);
-        int64_t cap = (int64_t)sm_count * 16;
-        int grid = (int)(blocks < cap ? blocks : cap);
+        if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
+        const unsigned grid = (unsigned)blocks;
         if (c.vec == 4) reduce_rows_warp_kernel<Pol, 4, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         else reduce_rows_warp_kernel<Pol, 1, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         break;
     }
     case SH_ROWS_BLOCK: {
-        int64_t cap = (int64_t)sm_count * 16;
-        int grid = (int)(g.nout < cap ? g.nout : cap);
-        if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
-        else reduce_rows_block_kernel<Pol, 1, T><<<grid, T, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        constexpr int TB = CTB_RED_BLOCK_THREADS;
+        const unsigned grid = (unsigned)(g.nout < 0x7FFFFFFFll ? g.nout : 0x7FFFFFFFll);
+        if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        else reduce_rows_block_kernel<Pol, 1, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         break;
     }
     case SH_ROWS_SPLIT: {

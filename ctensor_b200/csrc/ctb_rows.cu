@@ -23,17 +23,21 @@ struct RowIdx {
     int64_t mstride[CTB_MAX_DIMS];
 };
 
+// Offsets of a row's first element in x and in the mask.  All lanes of a warp ask for the same
+// row: lane 0 does the div/mod chain and broadcasts.
 __device__ __forceinline__ void row_offsets(const RowIdx& o, int64_t row, int64_t* xo, int64_t* mo) {
     int64_t x = 0, m = 0;
-    for (int d = o.nouter - 1; d >= 0; --d) {
-        const int64_t q = row / o.oshape[d];
-        const int64_t c = row - q * o.oshape[d];
-        row = q;
-        x += c * o.xstride[d];
-        m += c * o.mstride[d];
+    if ((threadIdx.x & 31) == 0) {
+        for (int d = o.nouter - 1; d >= 0; --d) {
+            const int64_t q = row / o.oshape[d];
+            const int64_t c = row - q * o.oshape[d];
+            row = q;
+            x += c * o.xstride[d];
+            m += c * o.mstride[d];
+        }
     }
-    *xo = x;
-    *mo = m;
+    *xo = warp_bcast64(x);
+    *mo = warp_bcast64(m);
 }
 
 // max with the reference's NaN rule: std::max(acc, v) keeps acc unless acc < v.
@@ -93,7 +97,30 @@ __device__ __forceinline__ void store_vec(float* dst, int64_t col, const float* 
 }
 
 // ---- softmax ---------------------------------------------------------------------------------------------
-// t = x (+ mask) (+ causal -1e9); m = max(t); e = exp(t - m); z = (float)sum_fp64(e); out = e / z.
+// t = x (+ mask); m = max(t); e = exp(t - m); z = (float)sum_fp64(e); out = e / z.
+//
+// `causal`: column j of row q (q = index within the second-to-last dim) is excluded when j > q.
+// This equals adding a -1e9 mask tensor: the masked exponentials are exactly 0 (the exponent
+// clamp of exp_cephes), so they change neither the maximum nor the sum for finite inputs, and
+// their outputs are +0.  Fully masked vectors are therefore neither read nor evaluated.
+//
+// The division uses one reciprocal per row: r ~ 1/z (estimate + Newton step), then per element
+// q = e*r, rem = fma(-z, q, e), out = fma(rem, r, q) — the remainder-corrected quotient, which
+// equals IEEE e/z except in rare last-bit cases; quotients that may be subnormal take the IEEE
+// division.  (The chain's stated tolerance for this step is 1e-5 relative.)
+__device__ __forceinline__ float row_reciprocal(float z) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+    const float err = fmaf(-z, r, 1.0f);
+    return fmaf(r, err, r);
+}
+__device__ __forceinline__ float div_by_row(float e, float z, float r) {
+    const float q = __fmul_rn(e, r);
+    const float rem = fmaf(-z, q, e);
+    const float out = fmaf(rem, r, q);
+    return (e < 1e-30f) ? __fdiv_rn(e, z) : out;
+}
+
 template <int GROUP, int VEC, int NV>
 __global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
 softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
@@ -109,13 +136,13 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
         row_offsets(o, row, &xo, &mo);
         const float* xr = x + xo;
         const float* mr = has_mask ? mask + mo : nullptr;
-        const int64_t q = row % qlen;
+        const int64_t live = causal ? min(cols, row % qlen + 1) : cols;   // columns [0, live) take part
         float t[NV][VEC];
         float m = -INFINITY;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
-            if (col < cols) {
+            if (col < live) {
                 load_vec<VEC>(t[i], xr, col, cols);
                 if (has_mask) {
                     float mv[VEC];
@@ -127,12 +154,11 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
 #pragma unroll
                     for (int k = 0; k < VEC; ++k) t[i][k] = __fadd_rn(t[i][k], mv[k]);
                 }
-                if (causal) {
 #pragma unroll
-                    for (int k = 0; k < VEC; ++k) t[i][k] = __fadd_rn(t[i][k], (col + k > q) ? -1e9f : 0.0f);
+                for (int k = 0; k < VEC; ++k) {
+                    if (col + k < live) m = max_ref(m, t[i][k]);
+                    else t[i][k] = -INFINITY;          // masked lane of a partly live vector
                 }
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) m = max_ref(m, t[i][k]);
             }
         }
         m = group_max<GROUP>(m, smax);
@@ -140,16 +166,25 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
-            if (col < cols) {
+            if (col < live) {
+                if constexpr (VEC % 2 == 0) {
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
-                    z = __dadd_rn(z, (double)t[i][k]);
+                    for (int k = 0; k < VEC; k += 2) {
+                        const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
+                        t[i][k] = e.x;
+                        t[i][k + 1] = e.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
                 }
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) z = __dadd_rn(z, (double)t[i][k]);
             }
         }
         z = group_sum<GROUP>(z, ssum);
         const float zf = __double2float_rn(z);
+        const float rz = row_reciprocal(zf);
         float* orow = out + row * cols;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -157,7 +192,7 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
             if (col < cols) {
                 float r[VEC];
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) r[k] = __fdiv_rn(t[i][k], zf);
+                for (int k = 0; k < VEC; ++k) r[k] = (col < live) ? div_by_row(t[i][k], zf, rz) : 0.0f;
                 store_vec<VEC>(orow, col, r);
             }
         }
@@ -175,26 +210,26 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
         row_offsets(o, row, &xo, &mo);
         const float* xr = x + xo;
         const float* mr = has_mask ? mask + mo : nullptr;
-        const int64_t q = row % qlen;
+        const int64_t live = causal ? min(cols, row % qlen + 1) : cols;
         auto tval = [&](int64_t c) {
             float v = xr[c];
             if (has_mask) v = __fadd_rn(v, mr[m_inner ? c : 0]);
-            if (causal) v = __fadd_rn(v, (c > q) ? -1e9f : 0.0f);
             return v;
         };
         float m = -INFINITY;
-        for (int64_t c = threadIdx.x; c < cols; c += 256) m = max_ref(m, tval(c));
+        for (int64_t c = threadIdx.x; c < live; c += 256) m = max_ref(m, tval(c));
         m = group_max<256>(m, smax);
         double z = 0.0;
         float* orow = out + row * cols;
-        for (int64_t c = threadIdx.x; c < cols; c += 256) {
+        for (int64_t c = threadIdx.x; c < live; c += 256) {
             float e = exp_cephes(__fsub_rn(tval(c), m));
             orow[c] = e;
             z = __dadd_rn(z, (double)e);
         }
         z = group_sum<256>(z, ssum);
         const float zf = __double2float_rn(z);
-        for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = __fdiv_rn(orow[c], zf);
+        const float rz = row_reciprocal(zf);
+        for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = (c < live) ? div_by_row(orow[c], zf, rz) : 0.0f;
     }
 }
 
@@ -319,11 +354,11 @@ bool rows_vec4(const RowsGeom& g, const float* x, const float* m, const float* o
     return true;
 }
 
-int rows_grid(int64_t rows, int groups_per_cta, int sm_count, int ctas_per_sm) {
+// One pass per CTA (a grid of short-lived CTAs measured faster than a persistent one here).
+int rows_grid(int64_t rows, int groups_per_cta, int /*sm_count*/, int /*ctas_per_sm*/) {
     int64_t blocks = ceil_div(rows, groups_per_cta);
-    int64_t cap = (int64_t)sm_count * ctas_per_sm;
-    int64_t g = blocks < cap ? blocks : cap;
-    return (int)(g < 1 ? 1 : g);
+    if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
+    return (int)(blocks < 1 ? 1 : blocks);
 }
 
 }  // namespace
@@ -333,22 +368,23 @@ int rows_grid(int64_t rows, int groups_per_cta, int sm_count, int ctas_per_sm) {
     do {                                                                                       \
         const int64_t per_v = vec4 ? 4 : 1;                                                    \
         const int64_t nv_warp = ceil_div(g.cols, 32 * per_v);                                  \
+        const int64_t nv_128 = ceil_div(g.cols, 128 * per_v);                                  \
         const int64_t nv_cta = ceil_div(g.cols, 256 * per_v);                                  \
         const int gw = rows_grid(g.rows, 8, di.sm_count, 8);                                   \
         const int gc = rows_grid(g.rows, 1, di.sm_count, 8);                                   \
         if (vec4) {                                                                            \
             if (nv_warp <= 1) KERNEL<32, 4, 1><<<gw, 256, 0, st>>> ARGS;                       \
             else if (nv_warp <= 2) KERNEL<32, 4, 2><<<gw, 256, 0, st>>> ARGS;                  \
-            else if (nv_warp <= 4) KERNEL<32, 4, 4><<<gw, 256, 0, st>>> ARGS;                  \
-            else if (nv_warp <= 8) KERNEL<32, 4, 8><<<gw, 256, 0, st>>> ARGS;                  \
-            else if (nv_cta <= 2) KERNEL<256, 4, 2><<<gc, 256, 0, st>>> ARGS;                  \
+            else if (nv_128 <= 1) KERNEL<128, 4, 1><<<gc, 128, 0, st>>> ARGS;                  \
+            else if (nv_128 <= 2) KERNEL<128, 4, 2><<<gc, 128, 0, st>>> ARGS;                  \
+            else if (nv_128 <= 4) KERNEL<128, 4, 4><<<gc, 128, 0, st>>> ARGS;                  \
             else if (nv_cta <= 4) KERNEL<256, 4, 4><<<gc, 256, 0, st>>> ARGS;                  \
             else if (nv_cta <= 8) KERNEL<256, 4, 8><<<gc, 256, 0, st>>> ARGS;                  \
             else launched = false;                                                             \
         } else {                                                                               \
             if (nv_warp <= 4) KERNEL<32, 1, 4><<<gw, 256, 0, st>>> ARGS;                       \
-            else if (nv_warp <= 16) KERNEL<32, 1, 16><<<gw, 256, 0, st>>> ARGS;                \
-            else if (nv_cta <= 8) KERNEL<256, 1, 8><<<gc, 256, 0, st>>> ARGS;                  \
+            else if (nv_128 <= 8) KERNEL<128, 1, 8><<<gc, 128, 0, st>>> ARGS;                  \
+            else if (nv_cta <= 16) KERNEL<256, 1, 16><<<gc, 256, 0, st>>> ARGS;                \
             else if (nv_cta <= 32) KERNEL<256, 1, 32><<<gc, 256, 0, st>>> ARGS;                \
             else launched = false;                                                             \
         }                                                                                      \
