@@ -78,12 +78,68 @@ __host__ __device__ __forceinline__ bool is_aligned(const void* p, size_t bytes)
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// Broadcast lane 0's 64-bit value to the whole warp (index arithmetic with divisions is done
-// by one lane and shared, not repeated by all 32).
-__device__ __forceinline__ int64_t warp_bcast64(int64_t v) {
-    int lo = __shfl_sync(0xffffffffu, (int)(v & 0xffffffffll), 0);
-    int hi = __shfl_sync(0xffffffffu, (int)(v >> 32), 0);
-    return ((int64_t)hi << 32) | (uint32_t)lo;
+// ---- index decomposition --------------------------------------------------------------------------
+// Division by a run-time constant through a precomputed multiplier (Granlund-Montgomery):
+// q = (umulhi(n, mul) + n) >> shr, exact for 0 <= n < 2^31 and 1 <= d < 2^31.  A 32-bit
+// hardware-emulated division costs ~20 issue slots and a 64-bit one ~70; this costs 3.
+struct FastDiv {
+    uint32_t d, mul, shr;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d ? d : 1;
+    uint32_t s = 0;
+    while (s < 32 && (1ull << s) < f.d) ++s;
+    f.shr = s;
+    f.mul = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << s) - f.d)) / f.d + 1);
+    return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+    return (__umulhi(n, f.mul) + n) >> f.shr;
+}
+
+// Mixed-radix decomposition of a linear index over up to CTB_MAX_DIMS dims (outer -> inner)
+// into a weighted sum with per-dim strides.  `fast` says every dim and the index fit 31 bits.
+struct DimSet {
+    int32_t n;
+    int32_t fast;
+    int64_t shape[CTB_MAX_DIMS];
+    FastDiv fd[CTB_MAX_DIMS];
+};
+inline void dimset_init(DimSet* s, int n, const int64_t* shape) {
+    s->n = n;
+    int64_t total = 1;
+    bool fast = true;
+    for (int d = 0; d < n; ++d) {
+        s->shape[d] = shape[d];
+        total *= shape[d] > 0 ? shape[d] : 1;
+        if (shape[d] >= 0x7FFFFFFFll || total >= 0x7FFFFFFFll) fast = false;
+    }
+    s->fast = fast;
+    for (int d = 0; d < n; ++d) s->fd[d] = make_fastdiv(fast ? (uint32_t)shape[d] : 1u);
+}
+// off_k += coord_d * stride_k[d] for NS stride sets at once.
+template <int NS>
+__device__ __forceinline__ void dimset_offsets(const DimSet& s, int64_t i, const int64_t (*stride)[CTB_MAX_DIMS],
+                                               int64_t* off) {
+    if (s.fast) {
+        uint32_t t = (uint32_t)i;
+        for (int d = s.n - 1; d >= 0; --d) {
+            const uint32_t q = fast_div(t, s.fd[d]);
+            const uint32_t c = t - q * s.fd[d].d;
+            t = q;
+#pragma unroll
+            for (int k = 0; k < NS; ++k) off[k] += (int64_t)c * stride[k][d];
+        }
+    } else {
+        for (int d = s.n - 1; d >= 0; --d) {
+            const int64_t q = i / s.shape[d];
+            const int64_t c = i - q * s.shape[d];
+            i = q;
+#pragma unroll
+            for (int k = 0; k < NS; ++k) off[k] += c * stride[k][d];
+        }
+    }
 }
 
 // ---- launchers implemented in the .cu files ---------------------------------------------------

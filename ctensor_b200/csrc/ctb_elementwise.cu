@@ -149,14 +149,12 @@ ew_flat_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
 // the writes form a few sequential streams, instead of reads hopping between distant 4 KiB runs.
 // ------------------------------------------------------------------------------------------------
 struct RowsArgs {
-    int32_t nouter;                         // number of outer dims (plan.ndim - 1)
-    uint32_t oshape[CTB_MAX_DIMS];          // outer shapes, outer -> inner
-    int64_t ostride[2][CTB_MAX_DIMS];       // per input
-    int64_t ostride_out[CTB_MAX_DIMS];      // output stride of each outer dim (elements)
+    DimSet outer;                           // outer dims in enumeration order (all < 2^31)
+    int64_t stride[3][CTB_MAX_DIMS];        // [0], [1] = inputs, [2] = output, per outer dim
     int32_t istride[2];                     // inner stride per input: 0 or 1
     uint32_t inner;                         // inner length
-    uint32_t tiles_per_row;
-    uint32_t ntiles;                        // rows * tiles_per_row (< 2^32)
+    FastDiv tiles_per_row;
+    uint32_t ntiles;                        // rows * tiles_per_row (< 2^31)
 };
 
 template <typename F, typename T, int NIN, int VEC, int UNROLL, int THREADS, bool ALIGNED>
@@ -175,16 +173,13 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
             uint32_t col0 = 0xFFFFFFFFu;                // "no tile"
             int64_t oa = 0, ob = 0, oout = 0;
             if (t < g.ntiles) {
-                uint32_t row = t / g.tiles_per_row;
-                col0 = (t - row * g.tiles_per_row) * TILE;
-                for (int d = g.nouter - 1; d >= 0; --d) {
-                    const uint32_t q = row / g.oshape[d];
-                    const uint32_t c = row - q * g.oshape[d];
-                    row = q;
-                    oa += (int64_t)c * g.ostride[0][d];
-                    if (NIN == 2) ob += (int64_t)c * g.ostride[1][d];
-                    oout += (int64_t)c * g.ostride_out[d];
-                }
+                const uint32_t row = fast_div(t, g.tiles_per_row);
+                col0 = (t - row * g.tiles_per_row.d) * TILE;
+                int64_t off[3] = {0, 0, 0};
+                dimset_offsets<3>(g.outer, row, g.stride, off);
+                oa = off[0];
+                ob = off[1];
+                oout = off[2];
             }
             s_oa[threadIdx.x] = oa;
             s_ob[threadIdx.x] = ob;
@@ -252,35 +247,27 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
 // ------------------------------------------------------------------------------------------------
 // ew_gather: fully general strided operands; one output element per thread per step.
 // ------------------------------------------------------------------------------------------------
+struct GatherArgs {
+    DimSet dims;
+    int64_t stride[2][CTB_MAX_DIMS];
+    int64_t numel;
+};
+
 template <typename F, typename T, int NIN>
 __global__ void __launch_bounds__(256)
 ew_gather_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
-                 Plan p, double scalar) {
+                 GatherArgs g, double scalar) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.numel; i += step) {
-        int64_t t = i, oa = 0, ob = 0;
-        for (int d = p.ndim - 1; d >= 0; --d) {
-            const int64_t q = t / p.shape[d];
-            const int64_t c = t - q * p.shape[d];
-            t = q;
-            oa += c * p.stride[0][d];
-            if (NIN == 2) ob += c * p.stride[1][d];
-        }
-        if (NIN == 2) out[i] = F::apply2(a[oa], b[ob]);
-        else out[i] = F::apply1(a[oa], scalar);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < g.numel; i += step) {
+        int64_t off[2] = {0, 0};
+        dimset_offsets<2>(g.dims, i, g.stride, off);
+        if (NIN == 2) out[i] = F::apply2(a[off[0]], b[off[1]]);
+        else out[i] = F::apply1(a[off[0]], scalar);
     }
 }
 
 // ---- host-side shape classification and launch ----------------------------------------------------
 namespace {
-
-int grid_for(int64_t work_items, int ctas_per_sm) {
-    DeviceInfo di;
-    if (current_device_info(&di) != CTB_OK) return -1;
-    int64_t cap = (int64_t)di.sm_count * ctas_per_sm;
-    int64_t g = work_items < cap ? work_items : cap;
-    return (int)(g < 1 ? 1 : g);
-}
 
 bool plan_is_flat(const Plan& p) {
     if (p.ndim != 1) return false;
@@ -333,10 +320,6 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
         constexpr int RUNROLL = CTB_ROWS_UNROLL;
         RowsArgs g{};
         const int nd = p.ndim;
-        g.nouter = nd - 1;
-        int64_t rows = 1;
-        bool aligned = is_aligned(out, CTB_ROWS_VEC_BYTES) && is_aligned(a, CTB_ROWS_VEC_BYTES) &&
-                       (NIN == 1 || is_aligned(b, CTB_ROWS_VEC_BYTES)) && (p.shape[nd - 1] % RVEC == 0);
         // Enumeration order of the outer dims: by decreasing stride of the first full-size
         // (non-broadcast) input, i.e. that input's memory order; ties keep the output order.
         int order[CTB_MAX_DIMS];
@@ -356,23 +339,28 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
             int64_t st = p.shape[nd - 1];
             for (int d = nd - 2; d >= 0; --d) { out_stride[d] = st; st *= p.shape[d]; }
         }
+        int64_t rows = 1;
+        bool aligned = is_aligned(out, CTB_ROWS_VEC_BYTES) && is_aligned(a, CTB_ROWS_VEC_BYTES) &&
+                       (NIN == 1 || is_aligned(b, CTB_ROWS_VEC_BYTES)) && (p.shape[nd - 1] % RVEC == 0);
+        int64_t oshape[CTB_MAX_DIMS];
         for (int k = 0; k < nd - 1; ++k) {
             const int d = order[k];
-            g.oshape[k] = (uint32_t)p.shape[d];
-            g.ostride_out[k] = out_stride[d];
+            oshape[k] = p.shape[d];
+            g.stride[2][k] = out_stride[d];
             rows *= p.shape[d];
             for (int i = 0; i < NIN; ++i) {
-                g.ostride[i][k] = p.stride[i][d];
+                g.stride[i][k] = p.stride[i][d];
                 if (p.stride[i][d] % RVEC != 0) aligned = false;
             }
         }
+        dimset_init(&g.outer, nd - 1, oshape);
         for (int i = 0; i < NIN; ++i) g.istride[i] = (int32_t)p.stride[i][nd - 1];
         g.inner = (uint32_t)p.shape[nd - 1];
         constexpr int64_t TILE = (int64_t)THREADS * RVEC;
         const int64_t tpr = ceil_div(p.shape[nd - 1], TILE);
         const int64_t ntiles = rows * tpr;
-        if (ntiles < 0xFFFFFFFFll - 4096) {
-            g.tiles_per_row = (uint32_t)tpr;
+        if (ntiles < 0x7FFFFFFFll - 4096 && g.outer.fast) {
+            g.tiles_per_row = make_fastdiv((uint32_t)tpr);
             g.ntiles = (uint32_t)ntiles;
             const unsigned grid = (unsigned)ceil_div(ntiles, RUNROLL);      // one pass per CTA
             if (aligned)
@@ -383,9 +371,14 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
         }
     }
 
-    int grid = grid_for(ceil_div(p.numel, 256), 16);
-    if (grid < 0) return CTB_ERR_CUDA;
-    ew_gather_kernel<F, T, NIN><<<grid, 256, 0, st>>>(a, b, out, p, scalar);
+    GatherArgs ga{};
+    dimset_init(&ga.dims, p.ndim, p.shape);
+    for (int d = 0; d < p.ndim; ++d)
+        for (int i = 0; i < NIN; ++i) ga.stride[i][d] = p.stride[i][d];
+    ga.numel = p.numel;
+    int64_t blocks = ceil_div(p.numel, 256);
+    if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
+    ew_gather_kernel<F, T, NIN><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
     return cuda_error(cudaGetLastError(), "ew_gather launch");
 }
 

@@ -168,19 +168,14 @@ template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool val
 
 // ---- helpers -----------------------------------------------------------------------------------------
 struct OuterIdx {
-    int32_t nouter;
-    int64_t oshape[CTB_MAX_DIMS];
-    int64_t ostride[CTB_MAX_DIMS];
+    DimSet dims;
+    int64_t stride[1][CTB_MAX_DIMS];
 };
 
 __device__ __forceinline__ int64_t outer_offset(const OuterIdx& o, int64_t i) {
-    int64_t off = 0;
-    for (int d = o.nouter - 1; d >= 0; --d) {
-        const int64_t q = i / o.oshape[d];
-        off += (i - q * o.oshape[d]) * o.ostride[d];
-        i = q;
-    }
-    return off;
+    int64_t off[1] = {0};
+    dimset_offsets<1>(o.dims, i, o.stride, off);
+    return off[0];
 }
 
 // L2-coherent load of a scratch accumulator written by another CTA.
@@ -199,13 +194,6 @@ __device__ __forceinline__ A load_cg(const A* p) {
         memcpy(&r, &u, 16);
     }
     return r;
-}
-
-// outer_offset evaluated by lane 0 and broadcast (all lanes of the warp ask for the same row).
-__device__ __forceinline__ int64_t outer_offset_warp(const OuterIdx& o, int64_t i) {
-    int64_t off = 0;
-    if ((threadIdx.x & 31) == 0) off = outer_offset(o, i);
-    return warp_bcast64(off);
 }
 
 template <typename Pol>
@@ -266,7 +254,7 @@ reduce_rows_warp_kernel(const float* __restrict__ a, void* out, OuterIdx o, int6
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (THREADS / 32);
     for (int64_t row = (int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); row < nout; row += warps) {
-        const float* line = a + outer_offset_warp(o, row);
+        const float* line = a + outer_offset(o, row);
         const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, lane, 32, shift);
@@ -281,7 +269,7 @@ __global__ void __launch_bounds__(THREADS)
 reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen, int op) {
     __shared__ typename Pol::Acc smem[THREADS / 32];
     for (int64_t row = blockIdx.x; row < nout; row += gridDim.x) {
-        const float* line = a + outer_offset_warp(o, row);
+        const float* line = a + outer_offset(o, row);
         const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
@@ -302,7 +290,7 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
     __shared__ bool is_last;
     const int64_t row = blockIdx.y;
     const int splits = gridDim.x;
-    const float* line = a + outer_offset_warp(o, row);
+    const float* line = a + outer_offset(o, row);
     const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
     const int64_t lo = (int64_t)blockIdx.x * chunk;
     int64_t hi = lo + chunk;
@@ -345,7 +333,7 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
     const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
     const int64_t col = ((int64_t)blockIdx.x * 32 + x) * VEC;
     const int64_t b = blockIdx.z;
-    const float* base = a + outer_offset_warp(batch, b);
+    const float* base = a + outer_offset(batch, b);
     const int splits = gridDim.y;
     const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
     int64_t r1 = r0 + rows_per_split;
@@ -513,8 +501,8 @@ size_t scratch_bytes(const ReduceGeom& g, const Choice& c) {
 
 OuterIdx outer_of(const ReduceGeom& g, int n) {
     OuterIdx o{};
-    o.nouter = n;
-    for (int d = 0; d < n; ++d) { o.oshape[d] = g.oshape[d]; o.ostride[d] = g.ostride[d]; }
+    dimset_init(&o.dims, n, g.oshape);
+    for (int d = 0; d < n; ++d) o.stride[0][d] = g.ostride[d];
     return o;
 }
 

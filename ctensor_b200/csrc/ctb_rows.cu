@@ -17,27 +17,16 @@ namespace ctb {
 namespace {
 
 struct RowIdx {
-    int32_t nouter;
-    int64_t oshape[CTB_MAX_DIMS];
-    int64_t xstride[CTB_MAX_DIMS];
-    int64_t mstride[CTB_MAX_DIMS];
+    DimSet dims;
+    int64_t stride[2][CTB_MAX_DIMS];      // [0] = x, [1] = mask
 };
 
-// Offsets of a row's first element in x and in the mask.  All lanes of a warp ask for the same
-// row: lane 0 does the div/mod chain and broadcasts.
+// Offsets of a row's first element in x and in the mask.
 __device__ __forceinline__ void row_offsets(const RowIdx& o, int64_t row, int64_t* xo, int64_t* mo) {
-    int64_t x = 0, m = 0;
-    if ((threadIdx.x & 31) == 0) {
-        for (int d = o.nouter - 1; d >= 0; --d) {
-            const int64_t q = row / o.oshape[d];
-            const int64_t c = row - q * o.oshape[d];
-            row = q;
-            x += c * o.xstride[d];
-            m += c * o.mstride[d];
-        }
-    }
-    *xo = warp_bcast64(x);
-    *mo = warp_bcast64(m);
+    int64_t off[2] = {0, 0};
+    dimset_offsets<2>(o.dims, row, o.stride, off);
+    *xo = off[0];
+    *mo = off[1];
 }
 
 // max with the reference's NaN rule: std::max(acc, v) keeps acc unless acc < v.
@@ -117,18 +106,20 @@ __device__ __forceinline__ float row_reciprocal(float z) {
 __device__ __forceinline__ float div_by_row(float e, float z, float r) {
     const float q = __fmul_rn(e, r);
     const float rem = fmaf(-z, q, e);
-    const float out = fmaf(rem, r, q);
-    return (e < 1e-30f) ? __fdiv_rn(e, z) : out;
+    float out = fmaf(rem, r, q);
+    if (e < 1e-30f) out = (e == 0.0f) ? 0.0f : __fdiv_rn(e, z);    // rare: quotient may be subnormal
+    return out;
 }
 
 template <int GROUP, int VEC, int NV>
 __global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
 softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
-                    RowIdx o, int64_t rows, int64_t cols, int64_t qlen, int m_inner, int has_mask, int causal) {
+                    RowIdx o, int64_t rows, int64_t cols64, int64_t qlen, int m_inner, int has_mask, int causal) {
     __shared__ float smax[8];
     __shared__ double ssum[8];
     constexpr int GROUPS_PER_CTA = (GROUP == 32) ? 8 : 1;
     const int tid = (GROUP == 32) ? (threadIdx.x & 31) : threadIdx.x;
+    const int cols = (int)cols64;                       // rows handled here have < 2^31 columns
     const int64_t g0 = (int64_t)blockIdx.x * GROUPS_PER_CTA + ((GROUP == 32) ? (threadIdx.x >> 5) : 0);
     const int64_t gstep = (int64_t)gridDim.x * GROUPS_PER_CTA;
     for (int64_t row = g0; row < rows; row += gstep) {
@@ -136,12 +127,18 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
         row_offsets(o, row, &xo, &mo);
         const float* xr = x + xo;
         const float* mr = has_mask ? mask + mo : nullptr;
-        const int64_t live = causal ? min(cols, row % qlen + 1) : cols;   // columns [0, live) take part
+        int live = cols;                                // columns [0, live) take part
+        if (causal) {
+            int q = 0;
+            if ((threadIdx.x & 31) == 0) q = (int)(row % qlen);
+            q = __shfl_sync(0xffffffffu, q, 0);
+            live = min(cols, q + 1);
+        }
         float t[NV][VEC];
         float m = -INFINITY;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < live) {
                 load_vec<VEC>(t[i], xr, col, cols);
                 if (has_mask) {
@@ -154,18 +151,20 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
 #pragma unroll
                     for (int k = 0; k < VEC; ++k) t[i][k] = __fadd_rn(t[i][k], mv[k]);
                 }
+                if (causal && col + VEC > live) {        // partly live vector: drop the masked lanes
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    if (col + k < live) m = max_ref(m, t[i][k]);
-                    else t[i][k] = -INFINITY;          // masked lane of a partly live vector
+                    for (int k = 0; k < VEC; ++k)
+                        if (col + k >= live) t[i][k] = -INFINITY;
                 }
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);   // == std::max(acc, v): NaN v ignored
             }
         }
         m = group_max<GROUP>(m, smax);
         double z = 0.0;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < live) {
                 if constexpr (VEC % 2 == 0) {
 #pragma unroll
@@ -185,14 +184,19 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
         z = group_sum<GROUP>(z, ssum);
         const float zf = __double2float_rn(z);
         const float rz = row_reciprocal(zf);
-        float* orow = out + row * cols;
+        float* orow = out + row * cols64;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < cols) {
                 float r[VEC];
+                if (col < live) {
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) r[k] = (col < live) ? div_by_row(t[i][k], zf, rz) : 0.0f;
+                    for (int k = 0; k < VEC; ++k) r[k] = div_by_row(t[i][k], zf, rz);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) r[k] = 0.0f;
+                }
                 store_vec<VEC>(orow, col, r);
             }
         }
@@ -241,10 +245,11 @@ template <int GROUP, int VEC, int NV>
 __global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
 layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
                       const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
-                      RowIdx o, int64_t rows, int64_t cols, double inv_cols, double eps) {
+                      RowIdx o, int64_t rows, int64_t cols64, double inv_cols, double eps) {
     __shared__ double ssum[8];
     constexpr int GROUPS_PER_CTA = (GROUP == 32) ? 8 : 1;
     const int tid = (GROUP == 32) ? (threadIdx.x & 31) : threadIdx.x;
+    const int cols = (int)cols64;
     const int64_t g0 = (int64_t)blockIdx.x * GROUPS_PER_CTA + ((GROUP == 32) ? (threadIdx.x >> 5) : 0);
     const int64_t gstep = (int64_t)gridDim.x * GROUPS_PER_CTA;
     for (int64_t row = g0; row < rows; row += gstep) {
@@ -255,7 +260,7 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
         double s = 0.0;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < cols) {
                 load_vec<VEC>(t[i], xr, col, cols);
 #pragma unroll
@@ -267,7 +272,7 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
         double s2 = 0.0;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < cols) {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
@@ -280,10 +285,10 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
         const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
         const float ve = __double2float_rn(__dadd_rn((double)v, eps));
         const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
-        float* orow = out + row * cols;
+        float* orow = out + row * cols64;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int64_t col = ((int64_t)i * GROUP + tid) * VEC;
+            const int col = (i * GROUP + tid) * VEC;
             if (col < cols) {
                 float r[VEC];
 #pragma unroll
@@ -334,11 +339,10 @@ layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict_
 
 RowIdx row_idx(const RowsGeom& g) {
     RowIdx o{};
-    o.nouter = g.nouter;
+    dimset_init(&o.dims, g.nouter, g.oshape);
     for (int d = 0; d < g.nouter; ++d) {
-        o.oshape[d] = g.oshape[d];
-        o.xstride[d] = g.xstride[d];
-        o.mstride[d] = g.mstride[d];
+        o.stride[0][d] = g.xstride[d];
+        o.stride[1][d] = g.mstride[d];
     }
     return o;
 }
