@@ -218,6 +218,32 @@ def bench_ours(args):
     except Exception as exc:                               # report, do not hide
         e2e = {"value": None, "unit": "GB/s", "error": repr(exc)}
 
+    # ---- the one op with an exchange step: full-tensor sum of a sharded tensor ----------------------
+    # (2^28 elements per GPU; local fp64 partial on the GPU, one NCCL all-reduce of a double, finalise)
+    sharded_sum = None
+    try:
+        from ctensor_b200 import sharded
+        m = min(n, 1 << 28)
+        xs = x[:m]
+        for _ in range(3):
+            sharded.full_reduce(ct.SUM, xs, m * world)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 20
+        s0.record()
+        for _ in range(reps):
+            res = sharded.full_reduce(ct.SUM, xs, m * world)
+        s1.record()
+        barrier()
+        tt = torch.tensor([s0.elapsed_time(s1) / reps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        sharded_sum = {"elements_per_gpu": m, "ms": round(float(tt.item()), 4),
+                       "GB/s": round(4.0 * m * world / float(tt.item()) / 1e6, 1), "value": float(res.item()),
+                       "collective": "none (1 rank)" if world == 1 else "1 all-reduce of one fp64 (NCCL)"}
+    except Exception as exc:
+        sharded_sum = {"error": repr(exc)}
+
     # ---- extras on rank 0 ------------------------------------------------------------------------------
     sweep, cpu = None, None
     if world == 1:
@@ -278,6 +304,7 @@ def bench_ours(args):
                      "traffic": None},
         "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * args.steps,
     }
+    line["sharded_full_sum"] = sharded_sum
     if sweep is not None:
         line["sweep"] = sweep
     if cpu is not None:

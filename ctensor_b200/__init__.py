@@ -38,6 +38,7 @@ STATUS_NAMES = {0: "CTB_OK", 1: "CTB_ERR_NULL", 2: "CTB_ERR_SHAPE", 3: "CTB_ERR_
 # every symbol include/ctb200.h declares
 EXPORTED_SYMBOLS = [
     "ctb_abi_version", "ctb_last_error", "ctb_device_count", "ctb_alloc", "ctb_free", "ctb_sync",
+    "ctb_alloc_managed", "ctb_free_managed", "ctb_set_device", "ctb_device_sync",
     "ctb_binary", "ctb_unary", "ctb_copy_strided", "ctb_reduce", "ctb_reduce_workspace_bytes",
     "ctb_reduce_ws", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",

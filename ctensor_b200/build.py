@@ -51,5 +51,24 @@ def build(force: bool = False, extra_flags=(), verbose: bool = False) -> str:
     return LIB
 
 
+HOST_DIR = os.path.join(PKG, "host")
+HOST_LIB = os.path.join(PKG, "libctensor_host.so")
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ host layer (the reference's operator API over the C ABI): plain g++, it needs
+    neither nvcc nor the CUDA headers — everything CUDA is behind libctb200.so."""
+    src = os.path.join(HOST_DIR, "ctensor_host.cpp")
+    deps = [src, os.path.join(os.path.dirname(PKG), "include", "ctb200.h")]
+    deps += [os.path.join(HOST_DIR, "include", f) for f in os.listdir(os.path.join(HOST_DIR, "include"))]
+    if not force and os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(map(os.path.getmtime, deps)) \
+            and os.path.getmtime(HOST_LIB) >= os.path.getmtime(LIB):
+        return HOST_LIB
+    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-o", HOST_LIB, src,
+                           "-I", HOST_DIR, "-L", PKG, "-lctb200", "-Wl,-rpath,$ORIGIN"])
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_host(force="--force" in sys.argv))

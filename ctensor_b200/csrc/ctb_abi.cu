@@ -464,6 +464,31 @@ int ctb_sync(void* stream) {
     return CTB_OK;
 }
 
+int ctb_alloc_managed(void** ptr, size_t bytes, int zero) {
+    if (!ptr) return set_error(CTB_ERR_NULL, "ctb_alloc_managed: null result pointer");
+    *ptr = nullptr;
+    if (bytes == 0) bytes = 1;
+    CTB_CUDA_TRY(cudaMallocManaged(ptr, bytes, cudaMemAttachGlobal));
+    if (zero) CTB_CUDA_TRY(cudaMemset(*ptr, 0, bytes));
+    return CTB_OK;
+}
+
+int ctb_free_managed(void* ptr) {
+    if (!ptr) return CTB_OK;
+    CTB_CUDA_TRY(cudaFree(ptr));
+    return CTB_OK;
+}
+
+int ctb_set_device(int index) {
+    CTB_CUDA_TRY(cudaSetDevice(index));
+    return CTB_OK;
+}
+
+int ctb_device_sync(void) {
+    CTB_CUDA_TRY(cudaDeviceSynchronize());
+    return CTB_OK;
+}
+
 int ctb_binary(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream) {
     int rc;
     if ((rc = check_view(a, "binary_op: null input", "binary_op"))) return rc;

@@ -1,0 +1,449 @@
+// Host layer of the B200 operator library: the reference's C++ operator API (names, shapes,
+// error texts) implemented on top of the C ABI of include/ctb200.h.  No arithmetic happens
+// here: shapes are inferred, the output tensor is allocated, the C entry point is called, and
+// — because callers dereference storage on the CPU (src/neuralnet/loss.cpp:25,
+// src/core/autograd.cpp:97-155 of the reference) — the call waits for the kernel.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "include/ctb_host.h"
+#include "include/ops_dispatch.h"
+#include "include/opsmp.h"
+#include "../../include/ctb200.h"
+
+namespace {
+
+int g_device = 0;
+bool g_device_set = false;
+bool g_sync_after_op = true;
+ctb_host::GradFactory g_grad_factory;
+std::function<void(Tensor&)> g_backward;
+
+[[noreturn]] void raise(int status) {
+    const std::string msg = ctb_last_error();
+    switch (status) {
+    case CTB_ERR_DIM: throw std::out_of_range(msg);                 // argmax: dim out of range
+    case CTB_ERR_ARG: throw std::invalid_argument(msg);
+    default: throw std::runtime_error(msg);                        // what the reference throws
+    }
+}
+inline void check(int status) { if (status != CTB_OK) raise(status); }
+
+void ensure_device() {
+    if (g_device_set) return;
+    if (ctb_device_count() <= 0)
+        throw std::runtime_error("ctensor_b200: no CUDA device (this library has no CPU fallback)");
+    check(ctb_set_device(g_device));
+    g_device_set = true;
+}
+
+int dtype_code(DType dt, const char* who) {
+    switch (dt) {
+    case DType::Float32: return CTB_F32;
+    case DType::Int32: return CTB_I32;
+    case DType::Double64: return CTB_F64;
+    default: throw std::runtime_error(std::string(who) + ": unsupported dtype or op not registered");
+    }
+}
+
+ctb_view view_of(const Tensor& t, const char* who) {
+    ctb_view v;
+    std::memset(&v, 0, sizeof v);
+    v.base = t.impl->data->data.get();
+    v.offset = (int64_t)t.impl->offset;
+    v.dtype = dtype_code(t.impl->dtype, who);
+    v.ndim = (int32_t)t.impl->ndim;
+    for (size_t i = 0; i < t.impl->ndim; ++i) {
+        v.shape[i] = (int64_t)t.impl->shape[i];
+        v.stride[i] = (int64_t)t.impl->strides[i];
+    }
+    return v;
+}
+
+// View for bit copies: only the element size matters to ctb_copy_strided.
+ctb_view view_of_bits(const Tensor& t) {
+    ctb_view v;
+    std::memset(&v, 0, sizeof v);
+    v.base = t.impl->data->data.get();
+    v.offset = (int64_t)t.impl->offset;
+    v.dtype = dtype_size(t.impl->dtype) == 8 ? CTB_F64 : CTB_F32;
+    v.ndim = (int32_t)t.impl->ndim;
+    for (size_t i = 0; i < t.impl->ndim; ++i) {
+        v.shape[i] = (int64_t)t.impl->shape[i];
+        v.stride[i] = (int64_t)t.impl->strides[i];
+    }
+    return v;
+}
+
+void after_op() { if (g_sync_after_op) check(ctb_device_sync()); }
+
+void attach_grad(Tensor& out, const char* op, const std::vector<Tensor>& inputs, double scalar) {
+    bool req = false;
+    for (const Tensor& t : inputs) req = req || t.impl->requires_grad;
+    if (!req) return;
+    out.requires_grad_(true);
+    if (g_grad_factory) out.impl->grad_fn = g_grad_factory(op, inputs, scalar);
+}
+
+std::vector<size_t> broadcast_shape(const Tensor& a, const Tensor& b) {
+    const std::vector<size_t> sa = a.shape(), sb = b.shape();
+    const size_t nd = std::max(sa.size(), sb.size());
+    std::vector<size_t> out(nd);
+    for (size_t i = 0; i < nd; ++i) {
+        const size_t da = i < nd - sa.size() ? 1 : sa[i - (nd - sa.size())];
+        const size_t db = i < nd - sb.size() ? 1 : sb[i - (nd - sb.size())];
+        if (da != db && da != 1 && db != 1) throw std::runtime_error("Shape mismatch in binary op");
+        out[i] = da == 1 ? db : da;
+    }
+    return out;
+}
+
+Tensor binary(int op, const char* name, const Tensor& a, const Tensor& b, bool grad) {
+    if (!a.impl || !b.impl) throw std::runtime_error("binary_op: null input");
+    if (a.device() != b.device()) throw std::runtime_error(std::string(name) + ": tensors must be on same device");
+    ensure_device();
+    // two one-element operands give shape {1} whatever their rank (the reference's scalar
+    // short-circuit, src/core/ops_dispatch.cpp:177-203)
+    std::vector<size_t> shape = (a.numel() == 1 && b.numel() == 1) ? std::vector<size_t>{1} : broadcast_shape(a, b);
+    Tensor out(shape, a._dtype(), false);
+    const ctb_view va = view_of(a, name), vb = view_of(b, name), vo = view_of(out, name);
+    check(ctb_binary(op, &va, &vb, &vo, nullptr));
+    after_op();
+    if (grad) attach_grad(out, name, {a, b}, 0.0);
+    return out;
+}
+
+Tensor unary(int op, const char* name, const Tensor& a, double scalar, bool grad) {
+    if (!a.impl) throw std::runtime_error("unary_op: null input");
+    ensure_device();
+    Tensor out(a.shape(), a._dtype(), false);
+    const ctb_view va = view_of(a, name), vo = view_of(out, name);
+    check(ctb_unary(op, &va, scalar, &vo, nullptr));
+    after_op();
+    if (grad) attach_grad(out, name, {a}, scalar);
+    return out;
+}
+
+Tensor reduce(int op, const char* name, const Tensor& a, int dim, bool grad) {
+    if (!a.impl) throw std::runtime_error("reduction: null input");
+    ensure_device();
+    const int nd = (int)a.impl->ndim;
+    std::vector<size_t> shape;
+    if (dim >= 0 && dim < nd)
+        for (int d = 0; d < nd; ++d) if (d != dim) shape.push_back(a.impl->shape[d]);
+    if (shape.empty()) shape.push_back(1);
+    Tensor out(shape, op == CTB_ARGMAX ? DType::Int32 : a._dtype(), false);
+    const ctb_view va = view_of(a, name), vo = view_of(out, name);
+    check(ctb_reduce(op, &va, dim, &vo, nullptr));
+    after_op();
+    if (grad) attach_grad(out, name, {a}, (double)dim);
+    return out;
+}
+
+}  // namespace
+
+// ---- runtime knobs ------------------------------------------------------------------------------
+namespace ctb_host {
+void set_device(int index) {
+    if (ctb_device_count() <= index || index < 0) throw std::runtime_error("ctensor_b200: no such CUDA device");
+    check(ctb_set_device(index));
+    g_device = index;
+    g_device_set = true;
+}
+int device() { return g_device; }
+void set_sync_after_op(bool on) { g_sync_after_op = on; }
+void sync_for_host_access() { if (g_device_set) check(ctb_device_sync()); }
+void set_grad_factory(GradFactory f) { g_grad_factory = std::move(f); }
+void set_backward_entry(std::function<void(Tensor&)> f) { g_backward = std::move(f); }
+int last_dim_if_negative(const Tensor& t, int dim) {
+    if (!t.impl) throw std::runtime_error("reduction: null input");
+    return dim < 0 ? dim + (int)t.impl->ndim : dim;
+}
+}  // namespace ctb_host
+
+// ---- storage: replaces Storage::allocate (src/core/tensor.cpp:18-39) --------------------------------
+std::shared_ptr<Storage> Storage::allocate(size_t n, DType dt, bool /*requires_grad*/, Device dev) {
+    ensure_device();
+    auto s = std::make_shared<Storage>();
+    s->size = n;
+    s->device = dev;
+    void* p = nullptr;
+    check(ctb_alloc_managed(&p, n * dtype_size(dt), /*zero=*/1));   // zero-filled like calloc
+    s->data = std::shared_ptr<void>(p, [](void* q) { ctb_free_managed(q); });
+    return s;
+}
+
+// ---- Tensor members ------------------------------------------------------------------------------------
+Tensor::Tensor(const std::vector<size_t>& shape_, DType dtype_, bool requires_grad_)
+    : impl(std::make_shared<Tensorimpl>(shape_, dtype_, requires_grad_, Device(DeviceType::CUDA, g_device))) {}
+
+Device Tensor::device() const { return impl ? impl->data->device : Device(DeviceType::CPU); }
+
+Tensor Tensor::to(Device target) {
+    if (!impl || device() == target) return *this;
+    Tensor out = clone();                      // storage is managed memory: reachable from both sides
+    out.impl->data->device = target;
+    return out;
+}
+
+bool Tensor::is_contiguous() const {
+    if (!impl) return true;
+    size_t expect = 1;
+    for (size_t i = impl->ndim; i-- > 0;) {
+        if (impl->shape[i] > 1) {               // size-1 dims never break contiguity
+            if (impl->strides[i] != expect) return false;
+            expect *= impl->shape[i];
+        }
+    }
+    return true;
+}
+
+Tensor Tensor::clone() const {
+    if (!impl) return Tensor();
+    Tensor out(shape(), impl->dtype, impl->requires_grad);
+    const size_t es = dtype_size(impl->dtype);
+    if (es == 4 || es == 8) {                   // strided gather on the GPU, bit copy
+        ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
+        check(ctb_copy_strided(&vs, &vo, nullptr));
+        after_op();
+    } else {                                    // 1- and 2-byte element types: host gather
+        ctb_host::sync_for_host_access();
+        const size_t n = numel(), nd = impl->ndim;
+        const char* src = (const char*)impl->data->data.get();
+        char* dst = (char*)out.impl->data->data.get();
+        for (size_t i = 0; i < n; ++i) {
+            size_t t = i, off = impl->offset;
+            for (size_t d = nd; d-- > 0;) { off += (t % impl->shape[d]) * impl->strides[d]; t /= impl->shape[d]; }
+            std::memcpy(dst + i * es, src + off * es, es);
+        }
+    }
+    return out;
+}
+
+Tensor Tensor::contiguous() const { return is_contiguous() ? *this : clone(); }
+
+Tensor Tensor::detach() const {
+    if (!impl) return Tensor();
+    Tensor out;
+    out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset, impl->shape, impl->strides, impl->dtype, false);
+    return out;
+}
+
+Tensor Tensor::reshape(const std::vector<size_t>& new_shape) const {
+    if (!impl) throw std::runtime_error("Reshape on empty tensor");
+    size_t n = 1;
+    for (size_t s : new_shape) n *= s;
+    if (n != numel()) throw std::runtime_error("Reshape size mismatch");
+    if (!is_contiguous()) return contiguous().reshape(new_shape);    // repack first, as the reference does
+    Tensor out;
+    out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset, DimVec(new_shape), calc_strides(DimVec(new_shape)),
+                                           impl->dtype, impl->requires_grad);
+    if (impl->requires_grad && g_grad_factory) out.impl->grad_fn = g_grad_factory("reshape", {*this}, 0.0);
+    return out;
+}
+
+Tensor Tensor::permute(const std::vector<size_t>& dims) const {
+    if (!impl) throw std::runtime_error("Permute on empty tensor");
+    if (dims.size() != impl->ndim) throw std::runtime_error("Permute dim mismatch");
+    DimVec shape, strides;
+    for (size_t d : dims) {
+        if (d >= impl->ndim) throw std::out_of_range("Permute dimension out of range");
+        shape.push_back(impl->shape[d]);
+        strides.push_back(impl->strides[d]);
+    }
+    Tensor out;
+    out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset, shape, strides, impl->dtype, impl->requires_grad);
+    if (impl->requires_grad && g_grad_factory) out.impl->grad_fn = g_grad_factory("permute", {*this}, 0.0);
+    return out;
+}
+
+Tensor& Tensor::t_() {
+    if (!impl) return *this;
+    if (impl->ndim != 2) throw std::runtime_error("t_() only supports 2D tensors");
+    std::swap(impl->shape[0], impl->shape[1]);
+    std::swap(impl->strides[0], impl->strides[1]);
+    return *this;
+}
+
+Tensor Tensor::select(size_t dim, size_t index) const {
+    if (!impl) throw std::runtime_error("Select on empty tensor");
+    if (dim >= impl->ndim) throw std::out_of_range("Select dimension out of range");
+    if (index >= impl->shape[dim]) throw std::out_of_range("Select index out of range");
+    DimVec shape, strides;
+    for (size_t d = 0; d < impl->ndim; ++d)
+        if (d != dim) { shape.push_back(impl->shape[d]); strides.push_back(impl->strides[d]); }
+    if (shape.empty()) { shape.push_back(1); strides.push_back(1); }
+    Tensor out;
+    out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset + index * impl->strides[dim], shape, strides,
+                                           impl->dtype, impl->requires_grad);
+    return out;
+}
+
+Tensor Tensor::squeeze() const {
+    if (!impl) throw std::runtime_error("Squeeze on empty tensor");
+    std::vector<size_t> s;
+    for (size_t d : impl->shape) if (d != 1) s.push_back(d);
+    if (s.empty()) s.push_back(1);
+    return reshape(s);
+}
+
+Tensor Tensor::unsqueeze(size_t dim) const {
+    std::vector<size_t> s = shape();
+    if (dim > s.size()) dim = s.size();
+    s.insert(s.begin() + (long)dim, 1);
+    return reshape(s);
+}
+
+Tensor Tensor::flatten() const { return reshape({numel()}); }
+
+void Tensor::print_shape() const {
+    std::cout << "(";
+    const auto s = shape();
+    for (size_t i = 0; i < s.size(); ++i) std::cout << s[i] << (i + 1 < s.size() ? ", " : "");
+    std::cout << ")\n";
+}
+
+Tensor Tensor::argmax(int dim) const { return ::argmax(*this, dim); }
+
+Tensor Tensor::astype(DType new_dtype) const {
+    if (_dtype() == new_dtype) return *this;
+    // element-by-element through double, walking storage linearly (the reference's astype,
+    // src/core/tensor.cpp:293-305); host side: this is a conversion utility, not an operator
+    ctb_host::sync_for_host_access();
+    Tensor out(shape(), new_dtype, requires_grad());
+    const size_t n = numel();
+    for (size_t i = 0; i < n; ++i) out.write_scalar(i, read_scalar(i));
+    return out;
+}
+
+void Tensor::to_(DType new_dtype) {
+    if (impl && impl->dtype != new_dtype) *this = astype(new_dtype);
+}
+
+static Tensor filled(const std::vector<size_t>& shape, double value, DType dt, bool req) {
+    Tensor t(shape, dt, req);
+    if (value != 0.0) {
+        const size_t n = t.numel();
+        for (size_t i = 0; i < n; ++i) t.write_scalar(i, value);
+    }
+    return t;
+}
+Tensor Tensor::ones(const std::vector<size_t>& s, DType dt, bool req) { return filled(s, 1.0, dt, req); }
+Tensor Tensor::zeros(const std::vector<size_t>& s, DType dt, bool req) { return Tensor(s, dt, req); }
+Tensor Tensor::empty(const std::vector<size_t>& s, DType dt, bool req) { return Tensor(s, dt, req); }
+Tensor Tensor::full(const std::vector<size_t>& s, double v, DType dt, bool req) { return filled(s, v, dt, req); }
+
+Tensor Tensor::rand(const std::vector<size_t>& s, DType dt, bool req) {
+    Tensor t(s, dt, req);
+    const size_t n = t.numel();
+    for (size_t i = 0; i < n; ++i) t.write_scalar(i, (double)std::rand() / RAND_MAX);
+    return t;
+}
+
+Tensor Tensor::from_vector(const std::vector<double>& data, const std::vector<size_t>& shape, DType dt, bool req) {
+    Tensor t(shape, dt, req);
+    if (t.numel() != data.size()) throw std::runtime_error("from_vector size mismatch");
+    for (size_t i = 0; i < data.size(); ++i) t.write_scalar(i, data[i]);
+    return t;
+}
+
+Tensor Tensor::arange(double start, double end, double step, DType dt) {
+    const size_t steps = (size_t)std::ceil((end - start) / step);
+    Tensor t({steps}, dt);
+    for (size_t i = 0; i < steps; ++i) t.write_scalar(i, start + (double)i * step);
+    return t;
+}
+
+void Tensor::backward() {
+    if (!impl || !impl->requires_grad) return;
+    if (!g_backward) throw std::runtime_error("backward: no autograd library registered (ctb_host::set_backward_entry)");
+    g_backward(*this);
+}
+
+void Tensor::zero_grad() {
+    if (!impl || !impl->grad) return;
+    ctb_host::sync_for_host_access();
+    std::memset(impl->grad->data->data.get(), 0, numel() * dtype_bytes());
+}
+
+// ---- operators ---------------------------------------------------------------------------------------------
+Tensor add(const Tensor& a, const Tensor& b) { return binary(CTB_ADD, "add", a, b, true); }
+Tensor sub(const Tensor& a, const Tensor& b) { return binary(CTB_SUB, "sub", a, b, true); }
+Tensor mul(const Tensor& a, const Tensor& b) { return binary(CTB_MUL, "mul", a, b, true); }
+Tensor div(const Tensor& a, const Tensor& b) { return binary(CTB_DIV, "div", a, b, true); }
+
+Tensor add_scalar(const Tensor& a, double s) { return unary(CTB_ADD_S, "add_scalar", a, s, true); }
+Tensor sub_scalar(const Tensor& a, double s) { return unary(CTB_SUB_S, "sub_scalar", a, s, true); }
+Tensor sub_scalar_rev(double s, const Tensor& a) { return unary(CTB_RSUB_S, "sub_scalar_rev", a, s, true); }
+Tensor mul_scalar(const Tensor& a, double s) { return unary(CTB_MUL_S, "mul_scalar", a, s, true); }
+Tensor div_scalar(const Tensor& a, double s) { return unary(CTB_DIV_S, "div_scalar", a, s, true); }
+Tensor div_scalar_rev(double s, const Tensor& a) { return unary(CTB_RDIV_S, "div_scalar_rev", a, s, true); }
+Tensor pow_scalar(const Tensor& a, double s) { return unary(CTB_POW_S, "pow_scalar", a, s, true); }
+Tensor pow_scalar_rev(double s, const Tensor& a) { return unary(CTB_RPOW_S, "pow_scalar_rev", a, s, true); }
+
+Tensor lt(const Tensor& a, const Tensor& b) { return binary(CTB_LT, "lt", a, b, false); }
+Tensor le(const Tensor& a, const Tensor& b) { return binary(CTB_LE, "le", a, b, false); }
+Tensor gt(const Tensor& a, const Tensor& b) { return binary(CTB_GT, "gt", a, b, false); }
+Tensor ge(const Tensor& a, const Tensor& b) { return binary(CTB_GE, "ge", a, b, false); }
+Tensor eq(const Tensor& a, const Tensor& b) { return binary(CTB_EQ, "eq", a, b, false); }
+Tensor ne(const Tensor& a, const Tensor& b) { return binary(CTB_NE, "ne", a, b, false); }
+Tensor lt(const Tensor& a, double b) { return unary(CTB_LT_S, "lt", a, b, false); }
+Tensor le(const Tensor& a, double b) { return unary(CTB_LE_S, "le", a, b, false); }
+Tensor gt(const Tensor& a, double b) { return unary(CTB_GT_S, "gt", a, b, false); }
+Tensor ge(const Tensor& a, double b) { return unary(CTB_GE_S, "ge", a, b, false); }
+Tensor eq(const Tensor& a, double b) { return unary(CTB_EQ_S, "eq", a, b, false); }
+Tensor ne(const Tensor& a, double b) { return unary(CTB_NE_S, "ne", a, b, false); }
+
+Tensor abs(const Tensor& a) { return unary(CTB_ABS, "abs", a, 0.0, true); }
+Tensor log(const Tensor& a) { return unary(CTB_LOG, "log", a, 0.0, true); }
+Tensor ln(const Tensor& a) { return unary(CTB_LOG, "ln", a, 0.0, true); }
+Tensor exp(const Tensor& a) { return unary(CTB_EXP, "exp", a, 0.0, true); }
+Tensor sqrt(const Tensor& a) { return unary(CTB_SQRT, "sqrt", a, 0.0, true); }
+Tensor tanh(const Tensor& a) { return unary(CTB_TANH, "tanh", a, 0.0, true); }
+Tensor sigmoid(const Tensor& a) { return unary(CTB_SIGMOID, "sigmoid", a, 0.0, true); }
+Tensor relu(const Tensor& a) { return unary(CTB_RELU, "relu", a, 0.0, true); }
+Tensor gelu(const Tensor& a) { return unary(CTB_GELU_TANH, "gelu", a, 0.0, true); }
+
+Tensor sum(const Tensor& a, int dim) { return reduce(CTB_SUM, "sum", a, dim, true); }
+Tensor mean(const Tensor& a, int dim) { return reduce(CTB_MEAN, "mean", a, dim, true); }
+Tensor max(const Tensor& a, int dim) { return reduce(CTB_MAX, "max", a, dim, false); }
+Tensor min(const Tensor& a, int dim) { return reduce(CTB_MIN, "min", a, dim, false); }
+Tensor var(const Tensor& a, int dim) { return reduce(CTB_VAR, "var", a, dim, false); }
+
+Tensor argmax(const Tensor& a, int dim) {
+    if (!a.impl) throw std::runtime_error("argmax: empty tensor");
+    if (dim < 0) dim += (int)a.impl->ndim;          // negative dims wrap (src/core/ops_dispatch.cpp:432)
+    return reduce(CTB_ARGMAX, "argmax", a, dim, false);
+}
+
+static Tensor softmax_impl(const Tensor& a, const Tensor* mask, int causal) {
+    if (!a.impl) throw std::runtime_error("softmax: null input");
+    ensure_device();
+    Tensor out(a.shape(), a._dtype(), false);
+    const ctb_view va = view_of(a, "softmax"), vo = view_of(out, "softmax");
+    ctb_view vm;
+    if (mask) vm = view_of(*mask, "softmax");
+    check(ctb_softmax_lastdim(&va, mask ? &vm : nullptr, causal, &vo, nullptr));
+    after_op();
+    return out;
+}
+Tensor softmax(const Tensor& a) { return softmax_impl(a, nullptr, 0); }
+Tensor softmax(const Tensor& a, const Tensor& additive_mask) {
+    if (!additive_mask.impl) throw std::runtime_error("softmax: null mask");
+    return softmax_impl(a, &additive_mask, 0);
+}
+Tensor causal_softmax(const Tensor& a) { return softmax_impl(a, nullptr, 1); }
+
+Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps) {
+    if (!a.impl) throw std::runtime_error("layernorm: null input");
+    ensure_device();
+    Tensor out(a.shape(), a._dtype(), false);
+    const ctb_view va = view_of(a, "layernorm"), vo = view_of(out, "layernorm");
+    ctb_view vg, vb;
+    if (gamma.impl) vg = view_of(gamma, "layernorm");
+    if (beta.impl) vb = view_of(beta, "layernorm");
+    check(ctb_layernorm_lastdim(&va, gamma.impl ? &vg : nullptr, beta.impl ? &vb : nullptr, eps, &vo, nullptr));
+    after_op();
+    return out;
+}

@@ -1,0 +1,34 @@
+// Runtime knobs of the host layer (nothing here exists in the reference).
+#pragma once
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+#include "tensor.h"
+
+namespace ctb_host {
+
+// CUDA device that new tensors and operators use (default 0).  Throws std::runtime_error when
+// no CUDA device is present: there is no CPU fallback.
+void set_device(int index);
+int device();
+
+// Callers dereference tensor storage on the host right after an operator returns, so by
+// default every operator waits for its kernel.  A caller that keeps data on the GPU across a
+// chain of operators can switch this off and call sync_for_host_access() before touching
+// storage (the index proxies and print_t do so themselves).
+void set_sync_after_op(bool on);
+void sync_for_host_access();
+
+// Autograd hook.  The reference attaches a GradFn node to every result whose inputs require
+// grad (src/core/ops_dispatch.cpp:159-167,247-255,312-315,378-381).  Those node classes belong
+// to the caller's autograd library, so it registers a factory once; `op` is the operator name
+// ("add", "mul_scalar", "relu", "sum", ...), `inputs` the operands, `scalar` the scalar or dim.
+using GradFactory = std::function<std::shared_ptr<GradFn>(const std::string& op, const std::vector<Tensor>& inputs,
+                                                          double scalar)>;
+void set_grad_factory(GradFactory f);
+
+// Hook behind Tensor::backward(); the autograd library installs its backward(root) here.
+void set_backward_entry(std::function<void(Tensor&)> f);
+
+}  // namespace ctb_host

@@ -109,6 +109,14 @@ int         ctb_device_count(void);
 int ctb_alloc(void** ptr, size_t bytes, int zero, void* stream);
 int ctb_free(void* ptr, void* stream);
 int ctb_sync(void* stream);
+/* Host-dereferenceable storage for callers that read tensor memory on the CPU between
+ * operators (the reference's own unfinished CUDA allocator chose cudaMallocManaged too:
+ * src/core/tensor.h:274).  Synchronous; `zero` != 0 clears the buffer. */
+int ctb_alloc_managed(void** ptr, size_t bytes, int zero);
+int ctb_free_managed(void* ptr);
+/* Select the CUDA device of the calling host thread / wait for all work on it. */
+int ctb_set_device(int index);
+int ctb_device_sync(void);
 
 /* ---- elementwise -------------------------------------------------------------------------- */
 /* out = a (op) b with NumPy-style right-aligned broadcasting (src/core/opsmp.cpp:19-40);

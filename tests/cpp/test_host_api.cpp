@@ -1,0 +1,142 @@
+// Tests of the C++ host layer, written the way the reference's own unit tests are
+// (test/test_ops.cpp and test/test.cpp there: plain main(), known answers), against the same
+// operator names.  Needs a CUDA device; prints "ALL PASSED" and exits 0 on success.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+
+#include "ctb_host.h"
+#include "ops_dispatch.h"
+#include "opsmp.h"
+
+static int g_checks = 0;
+#define CHECK(cond)                                                                  \
+    do {                                                                             \
+        ++g_checks;                                                                  \
+        if (!(cond)) { std::fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); std::exit(1); } \
+    } while (0)
+#define CHECK_NEAR(a, b, eps) CHECK(std::fabs(double(a) - double(b)) <= (eps))
+#define CHECK_THROWS(expr, type, text)                                               \
+    do {                                                                             \
+        bool ok = false;                                                             \
+        try { (void)(expr); } catch (const type& e) { ok = std::string(e.what()) == (text); } \
+        CHECK(ok);                                                                   \
+    } while (0)
+
+struct GradFn { std::string op; size_t n_inputs; double scalar; };   // a stand-in autograd node
+
+int main() {
+    // factories and shapes (reference test/test_ops.cpp:41-61)
+    Tensor ones = Tensor::ones({2, 3});
+    CHECK(ones.numel() == 6);
+    CHECK_NEAR(ones[0][0], 1.0, 1e-5);
+    CHECK_NEAR(ones[1][2], 1.0, 1e-5);
+    Tensor f = Tensor::full({2, 2}, 3.14);
+    CHECK_NEAR(f[1][1], 3.14, 1e-5);
+    Tensor r = Tensor::arange(0, 5, 1, DType::Float32);
+    CHECK(r.numel() == 5);
+    CHECK_NEAR(r[4], 4.0, 1e-5);
+
+    // arithmetic (test/test_ops.cpp:63-85)
+    Tensor a = Tensor::full({2, 2}, 2.0), b = Tensor::full({2, 2}, 3.0);
+    CHECK_NEAR((a + b)[0][0], 5.0, 1e-5);
+    CHECK_NEAR((b - a)[1][1], 1.0, 1e-5);
+    CHECK_NEAR((a * b)[0][1], 6.0, 1e-5);
+    CHECK_NEAR((a / b)[1][0], 2.0 / 3.0, 1e-5);
+    CHECK_NEAR((a / 4.0)[0][0], 0.5, 1e-6);
+    CHECK_NEAR((1.0 - a)[0][0], -1.0, 1e-6);
+
+    // reductions (test/test_ops.cpp:113-128): dim = -1 reduces everything to shape {1}
+    Tensor t = Tensor::from_vector({1, 2, 3, 4}, {2, 2});
+    CHECK(sum(t).numel() == 1);
+    CHECK_NEAR(sum(t).item<double>(), 10.0, 1e-5);
+    CHECK_NEAR(mean(t).item<double>(), 2.5, 1e-5);
+    CHECK_NEAR(max(t).item<double>(), 4.0, 1e-5);
+    CHECK_NEAR(min(t).item<double>(), 1.0, 1e-5);
+    Tensor s1 = sum(t, 1);
+    CHECK(s1.shape() == std::vector<size_t>({2}));
+    CHECK_NEAR(s1[0], 3.0, 1e-6);
+    CHECK_NEAR(s1[1], 7.0, 1e-6);
+    CHECK_NEAR(sum_mp(t)[1], 7.0, 1e-6);                 // *_mp: -1 means the last dim
+    CHECK_NEAR(var(t, 0)[0], 1.0, 1e-6);
+    Tensor am = argmax(Tensor::from_vector({5, 7, 7, 1}, {1, 4}), 1);
+    CHECK(am._dtype() == DType::Int32 && (int)double(am[0]) == 1);
+    CHECK((int)double(argmax(t, -1)[0]) == 1);           // negative dim wraps
+
+    // broadcasting (test/test_ops.cpp:130-149)
+    Tensor br = Tensor::ones({2, 2}) + Tensor::full({1, 2}, 2.0);
+    CHECK(br.shape() == std::vector<size_t>({2, 2}));
+    CHECK_NEAR(br[1][1], 3.0, 1e-6);
+    CHECK((Tensor::full({1, 1}, 2.0) + Tensor::full({1}, 1.0)).shape() == std::vector<size_t>({1}));
+
+    // views (test/test_ops.cpp:151-173, test/test.cpp:54-115)
+    Tensor m = Tensor::from_vector({0, 1, 2, 3, 4, 5}, {2, 3});
+    Tensor p = m.permute({1, 0});
+    CHECK(p.shape() == std::vector<size_t>({3, 2}) && !p.is_contiguous());
+    CHECK_NEAR(p[2][1], 5.0, 1e-6);
+    CHECK(p.impl->data.get() == m.impl->data.get());     // a view: same storage
+    Tensor pc = p.contiguous();
+    CHECK(pc.is_contiguous());
+    CHECK_NEAR(pc[1][0], 1.0, 1e-6);
+    CHECK_NEAR(pc[1][1], 4.0, 1e-6);
+    CHECK_NEAR(p.reshape({6})[3], 4.0, 1e-6);            // reshape of a permuted view repacks
+    CHECK_NEAR(m.flatten()[5], 5.0, 1e-6);
+    CHECK_NEAR((p + Tensor::full({3, 2}, 1.0))[2][0], 3.0, 1e-6);   // strided operand through the GPU
+    CHECK_NEAR(sum(p, 0)[1], 12.0, 1e-6);
+    CHECK_NEAR(m.select(0, 1)[2], 5.0, 1e-6);
+    CHECK(m.unsqueeze(0).shape() == std::vector<size_t>({1, 2, 3}));
+    CHECK(m.unsqueeze(0).squeeze().shape() == std::vector<size_t>({2, 3}));
+    m[0][0] = 9.0;
+    CHECK_NEAR(p[0][0], 9.0, 1e-6);                      // writes through the proxy hit shared storage
+
+    // unary flavours and edge values
+    Tensor x = Tensor::from_vector({-1.0, 0.0, 0.5, 100.0}, {4});
+    CHECK_NEAR(relu(x)[0], 0.0, 0.0);
+    CHECK_NEAR(exp(x)[2], std::exp(0.5), 1e-6);
+    CHECK(double(exp(x)[3]) > 2.4e38 && double(exp(x)[3]) < 2.41e38);   // the Cephes clamp, not inf
+    CHECK_NEAR(tanh(x)[0], std::tanh(-1.0), 1e-6);
+    CHECK_NEAR(ln(Tensor::full({1}, 1.5))[0], 0.405465, 1e-6);
+    CHECK_NEAR(gelu(x)[2], 0.345714, 1e-5);
+    CHECK_NEAR((x > 0.25)[2], 1.0, 0.0);
+    CHECK((x > 0.25)._dtype() == DType::Float32);        // comparisons answer in the input dtype
+
+    // integer semantics (test/test_ops.cpp:203-213): truncation
+    Tensor i3 = Tensor::from_vector({3, 5}, {2}, DType::Int32);
+    CHECK((int)double((i3 / 2.0)[0]) == 1 && (int)double((i3 / 2.0)[1]) == 2);
+    CHECK((int)double(Tensor::from_vector({1.5, 2.5}, {2}).astype(DType::Int32)[1]) == 2);
+
+    // fused rows
+    Tensor sm = softmax(Tensor::from_vector({1, 2, 3, 1, 1, 1}, {2, 3}));
+    CHECK_NEAR(double(sm[0][0]) + double(sm[0][1]) + double(sm[0][2]), 1.0, 1e-6);
+    CHECK_NEAR(sm[1][2], 1.0 / 3.0, 1e-6);
+    Tensor cs = causal_softmax(Tensor::ones({2, 2}));
+    CHECK_NEAR(cs[0][0], 1.0, 0.0);
+    CHECK_NEAR(cs[0][1], 0.0, 0.0);
+    CHECK_NEAR(cs[1][1], 0.5, 1e-6);
+    Tensor ln_ = layer_norm(Tensor::from_vector({1, 2, 3, 4}, {1, 4}), Tensor::ones({4}), Tensor::zeros({4}));
+    CHECK_NEAR(ln_[0][3], 1.5 / std::sqrt(1.25 + 1e-5), 1e-5);
+
+    // errors: the reference's exception types and texts
+    CHECK_THROWS(Tensor::ones({2, 3}) + Tensor::ones({2, 2}), std::runtime_error, "Shape mismatch in binary op");
+    CHECK_THROWS(add(Tensor(), a), std::runtime_error, "binary_op: null input");
+    CHECK_THROWS(relu(Tensor()), std::runtime_error, "unary_op: null input");
+    CHECK_THROWS(argmax(t, 5), std::out_of_range, "argmax: dim out of range");
+    CHECK_THROWS(t.reshape({5}), std::runtime_error, "Reshape size mismatch");
+    CHECK_THROWS(t[2], std::out_of_range, "Index out of bounds");
+
+    // autograd hook: requires_grad propagates and the registered factory builds the node
+    ctb_host::set_grad_factory([](const std::string& op, const std::vector<Tensor>& in, double s) {
+        return std::make_shared<GradFn>(GradFn{op, in.size(), s});
+    });
+    Tensor w = Tensor::full({2, 2}, 3.0, DType::Float32, true);
+    Tensor y = mul(w, a);
+    CHECK(y.requires_grad() && y.impl->grad_fn && y.impl->grad_fn->op == "mul" && y.impl->grad_fn->n_inputs == 2);
+    Tensor z = mul_scalar(y, 2.0);
+    CHECK(z.impl->grad_fn->op == "mul_scalar" && z.impl->grad_fn->scalar == 2.0);
+    CHECK(!add(a, b).requires_grad() && !max(w).requires_grad());
+
+    std::printf("ALL PASSED (%d checks)\n", g_checks);
+    return 0;
+}
