@@ -40,7 +40,7 @@ EXPORTED_SYMBOLS = [
     "ctb_abi_version", "ctb_last_error", "ctb_device_count", "ctb_alloc", "ctb_free", "ctb_sync",
     "ctb_alloc_managed", "ctb_free_managed", "ctb_set_device", "ctb_device_sync",
     "ctb_binary", "ctb_unary", "ctb_copy_strided", "ctb_reduce", "ctb_reduce_workspace_bytes",
-    "ctb_reduce_ws", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
+    "ctb_reduce_ws", "ctb_reduce_dim_noalloc", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
 ]
 
@@ -103,6 +103,7 @@ def lib() -> ctypes.CDLL:
     L.ctb_reduce_workspace_bytes.restype = ctypes.c_size_t
     L.ctb_reduce_workspace_bytes.argtypes = [vp, i32]
     L.ctb_reduce_ws.argtypes = [i32, vp, i32, vp, vd, ctypes.c_size_t, vd]
+    L.ctb_reduce_dim_noalloc.argtypes = [i32, vp, i32, vp, vd]
     L.ctb_reduce_full_partial.argtypes = [i32, vp, vd, vd]
     L.ctb_finalize_full.argtypes = [i32, vd, i64, vp, vd]
     L.ctb_softmax_lastdim.argtypes = [vp, vp, i32, vp, vd]
@@ -256,6 +257,21 @@ def reduce(op: int, a, dim: int = DIM_FULL, out=None, workspace=None):
         else:
             check(lib().ctb_reduce_ws(op, a.cview(), dim, DView.of(out).cview(), workspace.data_ptr(),
                                       workspace.numel() * workspace.element_size(), _stream_ptr(a)))
+    return out
+
+
+NOALLOC_SCRATCH_BYTES = 4 * 1024 * 1024 + 64 * 1024
+
+
+def reduce_dim_noalloc(op: int, a, dim: int, out):
+    """ctb_reduce_dim_noalloc: the dim-wise reduction for callers that must not allocate device
+    memory (allocator callbacks, fully budgeted or real-time processes).  Scratch comes from a
+    fixed array inside the library; `out` must be provided; shapes that need more than
+    NOALLOC_SCRATCH_BYTES of scratch raise CtbError(CTB_ERR_LIMIT).  Calls on one device share
+    that array: keep them stream-ordered, and make the first call outside stream capture."""
+    a = _as_dview(a)
+    with _device_guard(a):
+        check(lib().ctb_reduce_dim_noalloc(op, a.cview(), dim, DView.of(out).cview(), _stream_ptr(a)))
     return out
 
 

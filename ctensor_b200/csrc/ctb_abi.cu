@@ -552,6 +552,17 @@ int ctb_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, void* st
     return do_reduce(op, a, dim, out, nullptr, ws, need, (cudaStream_t)stream);
 }
 
+int ctb_reduce_dim_noalloc(int op, const ctb_view* a, int dim, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = reduce_arg_check(op, a, dim))) return rc;
+    if (dim == CTB_DIM_FULL)
+        return set_error(CTB_ERR_DIM, "reduction without allocation: a dim >= 0 is required");
+    if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    ReduceGeom g;
+    reduce_geom_dim(a, dim, &g);
+    return launch_reduce_static_scratch(op, a->dtype, g, elem_ptr(a), elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
 int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* stream) {
     int rc;
     if ((rc = reduce_arg_check(op, a, CTB_DIM_FULL))) return rc;

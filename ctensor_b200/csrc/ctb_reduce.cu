@@ -19,6 +19,7 @@
 #include "ctb_reduce.cuh"
 #include "ctb_math.cuh"
 #include <cstring>
+#include <mutex>
 
 namespace ctb {
 
@@ -618,6 +619,49 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
     case CTB_ARGMAX: return launch_fast<ArgmaxPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);
     }
     return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+}
+
+// ---- scratch that needs no allocation ---------------------------------------------------------------
+// Part of the library's device image: present on every GPU that loads it, for the life of the
+// process.  In host code this name is only a handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[CTB_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_addr[64] = {};
+
+int static_scratch_address(void** ptr) {
+    int dev = -1;
+    CTB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(CTB_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) {
+        void* p = nullptr;
+        CTB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return set_error(CTB_ERR_CUDA, "static scratch has no device address");
+        g_static_addr[dev] = p;
+    }
+    *ptr = g_static_addr[dev];
+    return CTB_OK;
+}
+}  // namespace
+
+int launch_reduce_static_scratch(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
+                                 cudaStream_t st) {
+    const size_t need = reduce_workspace_bytes(g, dtype);
+    if (need > CTB_NOALLOC_SCRATCH_BYTES)
+        return set_error(CTB_ERR_LIMIT,
+                         "reduction without allocation: this shape needs %zu bytes of scratch, the fixed buffer holds %u",
+                         need, (unsigned)CTB_NOALLOC_SCRATCH_BYTES);
+    void* ws = nullptr;
+    if (need) {
+        int rc = static_scratch_address(&ws);
+        if (rc) return rc;
+        // the array keeps the previous call's contents; the tickets must start at zero
+        CTB_CUDA_TRY(cudaMemsetAsync(ws, 0, kTicketBytes, st));
+    }
+    return launch_reduce(op, dtype, g, a, out, nullptr, ws, need ? CTB_NOALLOC_SCRATCH_BYTES : 0, st);
 }
 
 int launch_finalize_full(int op, int dtype, const double* partial, int64_t total, void* out, cudaStream_t st) {

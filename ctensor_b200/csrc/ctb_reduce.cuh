@@ -32,6 +32,11 @@ size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype);
 int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
                   double* partial_out, void* ws, size_t ws_bytes, cudaStream_t stream);
 
+// The same launch with scratch taken from the library's fixed device array (no allocation).
+// Fails with CTB_ERR_LIMIT when the geometry needs more than CTB_NOALLOC_SCRATCH_BYTES.
+int launch_reduce_static_scratch(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
+                                 cudaStream_t stream);
+
 int launch_finalize_full(int op, int dtype, const double* partial, int64_t total, void* out,
                          cudaStream_t stream);
 

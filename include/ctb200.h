@@ -146,6 +146,32 @@ size_t ctb_reduce_workspace_bytes(const ctb_view* a, int dim);
 int ctb_reduce_ws(int op, const ctb_view* a, int dim, const ctb_view* out,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* Dim-wise reduction for callers that must not allocate device memory.
+ * (No counterpart in the reference, which has no GPU path and therefore no scratch memory.)
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits — inside a memory-pool or
+ * allocator callback, in a real-time or pre-provisioned process whose device memory is fully
+ * budgeted at start-up, or in a host that forbids the library's lazily grown workspace
+ * because an allocation may synchronise the device or fail late.  ctb_reduce() grows a
+ * per-device workspace with cudaMalloc on first use; ctb_reduce_ws() avoids that only if the
+ * caller can provide scratch, which such callers cannot.
+ *
+ * Same semantics and results as ctb_reduce(op, a, dim, out, stream) for dim >= 0.  The scratch
+ * of the split reduction kernels (tickets + fp64 partials) lives in a fixed array inside the
+ * library's device image, CTB_NOALLOC_SCRATCH_BYTES large; every GPU that loads the library
+ * holds that much until the process exits.  A reduction that needs more scratch (a column
+ * reduction of more than about 2^18 / splits columns) is refused with CTB_ERR_LIMIT and a
+ * message that states both sizes.  Full reductions (CTB_DIM_FULL) are not offered here.
+ *
+ * The call performs no cudaMalloc/cudaFree and calls no allocating library routine.  The
+ * first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call outside any stream capture.  All calls on a device share the one array and
+ * it keeps whatever the previous call left: the part that must start at zero (the tickets) is
+ * cleared on `stream` before every launch, and two calls that overlap on the GPU (different
+ * streams without an ordering between them) race on it — order them. */
+#define CTB_NOALLOC_SCRATCH_BYTES (4u * 1024u * 1024u + 64u * 1024u)
+int ctb_reduce_dim_noalloc(int op, const ctb_view* a, int dim, const ctb_view* out, void* stream);
+
 /* Multi-GPU full reductions: the local shard's fp64 partial (sum for CTB_SUM/MEAN, max/min as
  * double for CTB_MAX/MIN) is written to `partial` (one double in device memory).  The caller
  * all-reduces the partials (sum / max / min) across ranks and calls ctb_finalize_full, which
