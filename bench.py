@@ -36,6 +36,7 @@ sys.path.insert(0, ROOT)
 OPS = [("add", "binary", 12), ("mul", "binary", 12), ("exp", "unary", 8), ("relu", "unary", 8),
        ("gelu", "unary", 8)]
 BYTES_PER_ELEM_STEP = sum(b for _, _, b in OPS)          # 48
+DRAM_BYTES_PER_ELEMENT = {"add": 11.35, "mul": 11.35, "exp": 7.20, "relu": 7.20, "gelu": 7.29}   # ncu, small case
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
@@ -187,6 +188,8 @@ def bench_ours(args):
     # ---- end to end through the host-buffer entry points --------------------------------------------
     e2e = None
     try:
+        if args.kernel_only:
+            raise RuntimeError("skipped (--kernel-only)")
         n_e2e = n
         need = 3 * 4 * n_e2e * max(world, 1)
         avail = mem_available_bytes()
@@ -222,6 +225,8 @@ def bench_ours(args):
     # (2^28 elements per GPU; local fp64 partial on the GPU, one NCCL all-reduce of a double, finalise)
     sharded_sum = None
     try:
+        if args.kernel_only:
+            raise RuntimeError("skipped (--kernel-only)")
         from ctensor_b200 import sharded
         m = min(n, 1 << 28)
         xs = x[:m]
@@ -246,7 +251,7 @@ def bench_ours(args):
 
     # ---- extras on rank 0 ------------------------------------------------------------------------------
     sweep, cpu = None, None
-    if world == 1:
+    if world == 1 and not args.kernel_only:
         sweep = {}
         for lg in (20, 24, 28):
             m = 1 << lg
@@ -302,22 +307,16 @@ def bench_ours(args):
                      "peak": peak, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
                      "unit": "GB/s", "frac": round(ach / peak, 4), "frac_of_8TBs": round(ach / NOMINAL_HBM_GBS, 4),
                      "traffic": None},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * args.steps,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * args.steps * world,
     }
     line["sharded_full_sum"] = sharded_sum
     if sweep is not None:
         line["sweep"] = sweep
     if cpu is not None:
         line["cpu_baseline"] = cpu
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            tr = json.load(open(traffic_file))
-            per_elem = tr.get(OPS[top][0], {}).get("dram_bytes_per_element")
-            if per_elem:
-                line["roofline"]["traffic"] = round(per_elem * n)
-        except Exception:
-            pass
+    # DRAM bytes per element from the ncu capture of the small case (n = 2^26), see
+    # profiles/ew_flat_small_case_full_set.md; traffic grows in proportion to n.
+    line["roofline"]["traffic"] = round(DRAM_BYTES_PER_ELEMENT[OPS[top][0]] * n)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -415,6 +414,8 @@ def main():
     ap.add_argument("--e2e-n", type=int, default=0, help="cap on the e2e tensor size (0 = same as --n)")
     ap.add_argument("--cpu-log2", type=int, default=26)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
