@@ -17,34 +17,44 @@ namespace ctb {
 namespace {
 
 struct RowIdx {
-    DimSet dims;
-    int64_t stride[2][CTB_MAX_DIMS];      // [0] = x, [1] = mask
+    DimSet dims;                          // outer dims in ENUMERATION order (x's memory order)
+    int64_t stride[3][CTB_MAX_DIMS];      // [0] = x, [1] = mask (elements), [2] = output row number
 };
 
-// Offsets of a row's first element in x and in the mask.
-__device__ __forceinline__ void row_offsets(const RowIdx& o, int64_t row, int64_t* xo, int64_t* mo) {
-    int64_t off[2] = {0, 0};
-    dimset_offsets<2>(o.dims, row, o.stride, off);
+// For enumeration index `i`: offsets of the row's first element in x and in the mask, and the
+// row's number in the (row-major) output.  Rows are walked in the order x lies in memory, so a
+// permuted input is read sequentially and the output is written as a few sequential streams.
+__device__ __forceinline__ void row_offsets(const RowIdx& o, int64_t i, int64_t* xo, int64_t* mo, int64_t* orow) {
+    int64_t off[3] = {0, 0, 0};
+    dimset_offsets<3>(o.dims, i, o.stride, off);
     *xo = off[0];
     *mo = off[1];
+    *orow = off[2];
 }
 
-// max with the reference's NaN rule: std::max(acc, v) keeps acc unless acc < v.
-__device__ __forceinline__ float max_ref(float acc, float v) { return (acc < v) ? v : acc; }
+// Row maxima use fmaxf: like std::max(acc, v) of the reference it ignores a NaN v.
 
 // Group-wide reductions whose result is the same bit pattern in every thread of the group.
+// A CTA holds several groups (one row each); groups wider than a warp synchronise on their own
+// named barrier (ids 1..15; id 0 is the CTA barrier), so a group at the ragged end of the grid
+// can leave without stalling its neighbours.
+template <int GROUP>
+__device__ __forceinline__ void group_barrier() {
+    if (GROUP > 32) asm volatile("bar.sync %0, %1;" ::"r"(1 + (int)threadIdx.x / GROUP), "r"(GROUP) : "memory");
+}
+
 template <int GROUP>
 __device__ __forceinline__ float group_max(float v, float* smem) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = max_ref(v, __shfl_xor_sync(0xffffffffu, v, off));
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
     if (GROUP == 32) return v;
-    const int w = threadIdx.x >> 5;
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) smem[w] = v;
-    __syncthreads();
-    float r = smem[0];
+    float* s = smem + (threadIdx.x / GROUP) * (GROUP / 32);
+    group_barrier<GROUP>();                 // the slots may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) s[(threadIdx.x % GROUP) >> 5] = v;
+    group_barrier<GROUP>();
+    float r = s[0];
 #pragma unroll
-    for (int i = 1; i < GROUP / 32; ++i) r = max_ref(r, smem[i]);
+    for (int i = 1; i < GROUP / 32; ++i) r = fmaxf(r, s[i]);
     return r;
 }
 
@@ -53,13 +63,37 @@ __device__ __forceinline__ double group_sum(double v, double* smem) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = __dadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
     if (GROUP == 32) return v;
-    const int w = threadIdx.x >> 5;
+    double* s = smem + (threadIdx.x / GROUP) * (GROUP / 32);
+    group_barrier<GROUP>();
+    if ((threadIdx.x & 31) == 0) s[(threadIdx.x % GROUP) >> 5] = v;
+    group_barrier<GROUP>();
+    double r = s[0];
+#pragma unroll
+    for (int i = 1; i < GROUP / 32; ++i) r = __dadd_rn(r, s[i]);
+    return r;
+}
+
+// CTA-wide variants for the long-row kernels (every thread of the CTA takes part).
+__device__ __forceinline__ float cta_max256(float v, float* smem) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) smem[w] = v;
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = smem[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) r = fmaxf(r, smem[i]);
+    return r;
+}
+__device__ __forceinline__ double cta_sum256(double v, double* smem) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = __dadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
     __syncthreads();
     double r = smem[0];
 #pragma unroll
-    for (int i = 1; i < GROUP / 32; ++i) r = __dadd_rn(r, smem[i]);
+    for (int i = 1; i < 8; ++i) r = __dadd_rn(r, smem[i]);
     return r;
 }
 
@@ -111,94 +145,116 @@ __device__ __forceinline__ float div_by_row(float e, float z, float r) {
     return out;
 }
 
-template <int GROUP, int VEC, int NV>
-__global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
+// Threads per CTA: 8 warp-rows, or 512 threads split into row groups of 128/256 threads.  (CTAs
+// that hold a single 4 KiB row each measured 2.4x slower than 8 rows per CTA: the kernel
+// becomes bound by CTA launch rate.)
+template <int GROUP> struct RowCta { static constexpr int kThreads = GROUP == 32 ? 256 : 512; };
+
+// MODE bits (compile time, so the unrolled load loop has no run-time branch and all loads of a
+// row are in flight together): 1 = additive mask, 2 = the mask's last dim is contiguous
+// (else one value per row), 4 = causal.
+template <int GROUP, int VEC, int NV, int MODE>
+__global__ void __launch_bounds__(RowCta<GROUP>::kThreads)
 softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
-                    RowIdx o, int64_t rows, int64_t cols64, int64_t qlen, int m_inner, int has_mask, int causal) {
-    __shared__ float smax[8];
-    __shared__ double ssum[8];
-    constexpr int GROUPS_PER_CTA = (GROUP == 32) ? 8 : 1;
-    const int tid = (GROUP == 32) ? (threadIdx.x & 31) : threadIdx.x;
-    const int cols = (int)cols64;                       // rows handled here have < 2^31 columns
-    const int64_t g0 = (int64_t)blockIdx.x * GROUPS_PER_CTA + ((GROUP == 32) ? (threadIdx.x >> 5) : 0);
-    const int64_t gstep = (int64_t)gridDim.x * GROUPS_PER_CTA;
-    for (int64_t row = g0; row < rows; row += gstep) {
-        int64_t xo, mo;
-        row_offsets(o, row, &xo, &mo);
-        const float* xr = x + xo;
-        const float* mr = has_mask ? mask + mo : nullptr;
-        int live = cols;                                // columns [0, live) take part
-        if (causal) {
-            int q = 0;
-            if ((threadIdx.x & 31) == 0) q = (int)(row % qlen);
-            q = __shfl_sync(0xffffffffu, q, 0);
-            live = min(cols, q + 1);
-        }
-        float t[NV][VEC];
-        float m = -INFINITY;
+                    RowIdx o, int64_t rows, int cols, int64_t qlen) {
+    constexpr int THREADS = RowCta<GROUP>::kThreads;
+    constexpr int GPC = THREADS / GROUP;                // rows per CTA
+    constexpr bool has_mask = (MODE & 1) != 0, m_inner = (MODE & 2) != 0, causal = (MODE & 4) != 0;
+    __shared__ float smax[THREADS / 32];
+    __shared__ double ssum[THREADS / 32];
+    const int tid = threadIdx.x % GROUP;
+    const int64_t ridx = (int64_t)blockIdx.x * GPC + threadIdx.x / GROUP;
+    if (ridx >= rows) return;                           // whole groups leave together
+    int64_t xo, mo, row;
+    row_offsets(o, ridx, &xo, &mo, &row);
+    const float* xr = x + xo;
+    int live = cols;                                    // columns [0, live) take part
+    if (causal) live = min(cols, (int)(row % qlen) + 1);
+    float t[NV][VEC];
+    float m = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
-            if (col < live) {
-                load_vec<VEC>(t[i], xr, col, cols);
-                if (has_mask) {
-                    float mv[VEC];
-                    if (m_inner) load_vec<VEC>(mv, mr, col, cols);
-                    else {
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < live) {
+            load_vec<VEC>(t[i], xr, col, cols);
+            if (has_mask) {
+                const float* mr = mask + mo;
+                float mv[VEC];
+                if (m_inner) load_vec<VEC>(mv, mr, col, cols);
+                else {
+                    const float m0 = mr[0];
 #pragma unroll
-                        for (int k = 0; k < VEC; ++k) mv[k] = mr[0];
-                    }
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k) t[i][k] = __fadd_rn(t[i][k], mv[k]);
-                }
-                if (causal && col + VEC > live) {        // partly live vector: drop the masked lanes
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k)
-                        if (col + k >= live) t[i][k] = -INFINITY;
+                    for (int k = 0; k < VEC; ++k) mv[k] = m0;
                 }
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);   // == std::max(acc, v): NaN v ignored
+                for (int k = 0; k < VEC; ++k) t[i][k] = __fadd_rn(t[i][k], mv[k]);
             }
-        }
-        m = group_max<GROUP>(m, smax);
-        double z = 0.0;
+            if (causal) {                               // partly live vector: drop the masked lanes
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
+                for (int k = 0; k < VEC; ++k)
+                    if (col + k >= live) t[i][k] = -INFINITY;
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);
+        }
+    }
+    m = group_max<GROUP>(m, smax);
+    double z = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < live) {
+            if constexpr (VEC % 2 == 0) {
+#pragma unroll
+                for (int k = 0; k < VEC; k += 2) {
+                    const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
+                    t[i][k] = e.x;
+                    t[i][k + 1] = e.y;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) z = __dadd_rn(z, (double)t[i][k]);
+        }
+    }
+    z = group_sum<GROUP>(z, ssum);
+    const float zf = __double2float_rn(z);
+    const float rz = row_reciprocal(zf);
+    float* orow = out + row * (int64_t)cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            float r[VEC];
             if (col < live) {
                 if constexpr (VEC % 2 == 0) {
+                    float smallest = t[i][0];
 #pragma unroll
                     for (int k = 0; k < VEC; k += 2) {
-                        const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
-                        t[i][k] = e.x;
-                        t[i][k + 1] = e.y;
+                        const float2 e = make_float2(t[i][k], t[i][k + 1]);
+                        const float2 q = __fmul2_rn(e, splat2(rz));
+                        const float2 rem = __ffma2_rn(splat2(-zf), q, e);
+                        const float2 res = __ffma2_rn(rem, splat2(rz), q);
+                        r[k] = res.x;
+                        r[k + 1] = res.y;
+                        smallest = fminf(smallest, fminf(e.x, e.y));
+                    }
+                    if (smallest < 1e-30f) {            // rare: a quotient may be subnormal (or e == 0)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k)
+                            if (t[i][k] < 1e-30f) r[k] = (t[i][k] == 0.0f) ? 0.0f : __fdiv_rn(t[i][k], zf);
                     }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < VEC; ++k) t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
-                }
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) z = __dadd_rn(z, (double)t[i][k]);
-            }
-        }
-        z = group_sum<GROUP>(z, ssum);
-        const float zf = __double2float_rn(z);
-        const float rz = row_reciprocal(zf);
-        float* orow = out + row * cols64;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
-            if (col < cols) {
-                float r[VEC];
-                if (col < live) {
-#pragma unroll
                     for (int k = 0; k < VEC; ++k) r[k] = div_by_row(t[i][k], zf, rz);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k) r[k] = 0.0f;
                 }
-                store_vec<VEC>(orow, col, r);
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) r[k] = 0.0f;
             }
+            store_vec<VEC>(orow, col, r);
         }
     }
 }
@@ -209,9 +265,9 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
                          RowIdx o, int64_t rows, int64_t cols, int64_t qlen, int m_inner, int has_mask, int causal) {
     __shared__ float smax[8];
     __shared__ double ssum[8];
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        int64_t xo, mo;
-        row_offsets(o, row, &xo, &mo);
+    for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
+        int64_t xo, mo, row;
+        row_offsets(o, ridx, &xo, &mo, &row);
         const float* xr = x + xo;
         const float* mr = has_mask ? mask + mo : nullptr;
         const int64_t live = causal ? min(cols, row % qlen + 1) : cols;
@@ -221,8 +277,8 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
             return v;
         };
         float m = -INFINITY;
-        for (int64_t c = threadIdx.x; c < live; c += 256) m = max_ref(m, tval(c));
-        m = group_max<256>(m, smax);
+        for (int64_t c = threadIdx.x; c < live; c += 256) m = fmaxf(m, tval(c));
+        m = cta_max256(m, smax);
         double z = 0.0;
         float* orow = out + row * cols;
         for (int64_t c = threadIdx.x; c < live; c += 256) {
@@ -230,7 +286,7 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
             orow[c] = e;
             z = __dadd_rn(z, (double)e);
         }
-        z = group_sum<256>(z, ssum);
+        z = cta_sum256(z, ssum);
         const float zf = __double2float_rn(z);
         const float rz = row_reciprocal(zf);
         for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = (c < live) ? div_by_row(orow[c], zf, rz) : 0.0f;
@@ -241,65 +297,76 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
 // mu = mean(x); d = x - mu; v = mean(d*d); r = (v + eps)^-0.5; y = d*r*gamma + beta, with
 // mean(.) = (float)((double)(float)sum_fp64 * (1.0/cols)) and the scalar steps in double,
 // as mul_scalar / add_scalar / pow_scalar do (src/core/opsmp.cpp:297,418-451).
-template <int GROUP, int VEC, int NV>
-__global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
+// MODE (compile time): 0 = no scale/shift, 1 = gamma and beta are contiguous rows (vector
+// loads), 2 = general (either may be absent or strided).
+template <int GROUP, int VEC, int NV, int MODE>
+__global__ void __launch_bounds__(RowCta<GROUP>::kThreads)
 layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
                       const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
-                      RowIdx o, int64_t rows, int64_t cols64, double inv_cols, double eps) {
-    __shared__ double ssum[8];
-    constexpr int GROUPS_PER_CTA = (GROUP == 32) ? 8 : 1;
-    const int tid = (GROUP == 32) ? (threadIdx.x & 31) : threadIdx.x;
-    const int cols = (int)cols64;
-    const int64_t g0 = (int64_t)blockIdx.x * GROUPS_PER_CTA + ((GROUP == 32) ? (threadIdx.x >> 5) : 0);
-    const int64_t gstep = (int64_t)gridDim.x * GROUPS_PER_CTA;
-    for (int64_t row = g0; row < rows; row += gstep) {
-        int64_t xo, mo;
-        row_offsets(o, row, &xo, &mo);
-        const float* xr = x + xo;
-        float t[NV][VEC];
-        double s = 0.0;
+                      RowIdx o, int64_t rows, int cols, double inv_cols, double eps) {
+    constexpr int THREADS = RowCta<GROUP>::kThreads;
+    constexpr int GPC = THREADS / GROUP;
+    __shared__ double ssum[THREADS / 32];
+    const int tid = threadIdx.x % GROUP;
+    const int64_t ridx = (int64_t)blockIdx.x * GPC + threadIdx.x / GROUP;
+    if (ridx >= rows) return;
+    int64_t xo, mo, row;
+    row_offsets(o, ridx, &xo, &mo, &row);
+    const float* xr = x + xo;
+    float t[NV][VEC];
+    double s = 0.0;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
-            if (col < cols) {
-                load_vec<VEC>(t[i], xr, col, cols);
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            load_vec<VEC>(t[i], xr, col, cols);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) s = __dadd_rn(s, (double)t[i][k]);
+            for (int k = 0; k < VEC; ++k) s = __dadd_rn(s, (double)t[i][k]);
+        }
+    }
+    s = group_sum<GROUP>(s, ssum);
+    const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
+    double s2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                t[i][k] = __fsub_rn(t[i][k], mu);
+                s2 = __dadd_rn(s2, (double)__fmul_rn(t[i][k], t[i][k]));
             }
         }
-        s = group_sum<GROUP>(s, ssum);
-        const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
-        double s2 = 0.0;
+    }
+    s2 = group_sum<GROUP>(s2, ssum);
+    const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
+    const float ve = __double2float_rn(__dadd_rn((double)v, eps));
+    const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
+    float* orow = out + row * (int64_t)cols;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
-            if (col < cols) {
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            float r[VEC];
+            if (MODE == 1) {
+                float gv[VEC], bv[VEC];
+                load_vec<VEC>(gv, gamma, col, cols);
+                load_vec<VEC>(bv, beta, col, cols);
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    t[i][k] = __fsub_rn(t[i][k], mu);
-                    s2 = __dadd_rn(s2, (double)__fmul_rn(t[i][k], t[i][k]));
-                }
-            }
-        }
-        s2 = group_sum<GROUP>(s2, ssum);
-        const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
-        const float ve = __double2float_rn(__dadd_rn((double)v, eps));
-        const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
-        float* orow = out + row * cols64;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int col = (i * GROUP + tid) * VEC;
-            if (col < cols) {
-                float r[VEC];
+                for (int k = 0; k < VEC; ++k)
+                    r[k] = __fadd_rn(__fmul_rn(__fmul_rn(t[i][k], rstd), gv[k]), bv[k]);
+            } else {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
                     float y = __fmul_rn(t[i][k], rstd);
-                    if (gamma) y = __fmul_rn(y, gamma[(col + k) * gstride]);
-                    if (beta) y = __fadd_rn(y, beta[(col + k) * bstride]);
+                    if (MODE == 2) {
+                        if (gamma) y = __fmul_rn(y, gamma[(int64_t)(col + k) * gstride]);
+                        if (beta) y = __fadd_rn(y, beta[(int64_t)(col + k) * bstride]);
+                    }
                     r[k] = y;
                 }
-                store_vec<VEC>(orow, col, r);
             }
+            store_vec<VEC>(orow, col, r);
         }
     }
 }
@@ -309,13 +376,13 @@ layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict_
                            const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
                            RowIdx o, int64_t rows, int64_t cols, double inv_cols, double eps) {
     __shared__ double ssum[8];
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        int64_t xo, mo;
-        row_offsets(o, row, &xo, &mo);
+    for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
+        int64_t xo, mo, row;
+        row_offsets(o, ridx, &xo, &mo, &row);
         const float* xr = x + xo;
         double s = 0.0;
         for (int64_t c = threadIdx.x; c < cols; c += 256) s = __dadd_rn(s, (double)xr[c]);
-        s = group_sum<256>(s, ssum);
+        s = cta_sum256(s, ssum);
         const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
         double s2 = 0.0;
         float* orow = out + row * cols;
@@ -324,7 +391,7 @@ layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict_
             orow[c] = d;
             s2 = __dadd_rn(s2, (double)__fmul_rn(d, d));
         }
-        s2 = group_sum<256>(s2, ssum);
+        s2 = cta_sum256(s2, ssum);
         const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
         const float ve = __double2float_rn(__dadd_rn((double)v, eps));
         const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
@@ -339,11 +406,24 @@ layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict_
 
 RowIdx row_idx(const RowsGeom& g) {
     RowIdx o{};
-    dimset_init(&o.dims, g.nouter, g.oshape);
-    for (int d = 0; d < g.nouter; ++d) {
-        o.stride[0][d] = g.xstride[d];
-        o.stride[1][d] = g.mstride[d];
+    int order[CTB_MAX_DIMS];
+    for (int d = 0; d < g.nouter; ++d) order[d] = d;
+    for (int i = 1; i < g.nouter; ++i)          // by decreasing x stride; ties keep the logical order
+        for (int j = i; j > 0 && g.xstride[order[j]] > g.xstride[order[j - 1]]; --j) {
+            const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+        }
+    int64_t out_stride[CTB_MAX_DIMS];
+    int64_t run = 1;
+    for (int d = g.nouter - 1; d >= 0; --d) { out_stride[d] = run; run *= g.oshape[d]; }
+    int64_t shape[CTB_MAX_DIMS];
+    for (int k = 0; k < g.nouter; ++k) {
+        const int d = order[k];
+        shape[k] = g.oshape[d];
+        o.stride[0][k] = g.xstride[d];
+        o.stride[1][k] = g.mstride[d];
+        o.stride[2][k] = out_stride[d];
     }
+    dimset_init(&o.dims, g.nouter, shape);
     return o;
 }
 
@@ -358,8 +438,8 @@ bool rows_vec4(const RowsGeom& g, const float* x, const float* m, const float* o
     return true;
 }
 
-// One pass per CTA (a grid of short-lived CTAs measured faster than a persistent one here).
-int rows_grid(int64_t rows, int groups_per_cta, int /*sm_count*/, int /*ctas_per_sm*/) {
+// One row per group, GPC groups per CTA, one pass per CTA.
+int rows_grid(int64_t rows, int groups_per_cta) {
     int64_t blocks = ceil_div(rows, groups_per_cta);
     if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
     return (int)(blocks < 1 ? 1 : blocks);
@@ -367,29 +447,51 @@ int rows_grid(int64_t rows, int groups_per_cta, int /*sm_count*/, int /*ctas_per
 
 }  // namespace
 
-// Dispatch over (GROUP, VEC, NV): the smallest per-thread footprint that covers the row.
-#define CTB_ROWS_DISPATCH(KERNEL, ARGS)                                                        \
+// Dispatch over (GROUP, VEC, NV): a warp per row up to 8 vectors per lane (1024 floats), then
+// 128- and 256-thread groups; MASKED is a compile-time switch so the plain case carries no
+// mask/causal code.
+#define CTB_MODES_SOFTMAX(KERNEL, G, V, N, ARGS)                                               \
+    switch (mode) {                                                                            \
+    case 0: KERNEL<G, V, N, 0><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 1: KERNEL<G, V, N, 1><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 3: KERNEL<G, V, N, 3><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 4: KERNEL<G, V, N, 4><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 5: KERNEL<G, V, N, 5><<<grid, thr, 0, st>>> ARGS; break;                              \
+    default: KERNEL<G, V, N, 7><<<grid, thr, 0, st>>> ARGS; break;                             \
+    }
+#define CTB_MODES_LAYERNORM(KERNEL, G, V, N, ARGS)                                             \
+    switch (mode) {                                                                            \
+    case 0: KERNEL<G, V, N, 0><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 1: KERNEL<G, V, N, 1><<<grid, thr, 0, st>>> ARGS; break;                              \
+    default: KERNEL<G, V, N, 2><<<grid, thr, 0, st>>> ARGS; break;                             \
+    }
+#define CTB_ROWS_LAUNCH(MODES, KERNEL, G, V, N, ARGS)                                          \
+    do {                                                                                       \
+        const int grid = rows_grid(g.rows, RowCta<G>::kThreads / G);                           \
+        const int thr = RowCta<G>::kThreads;                                                   \
+        MODES(KERNEL, G, V, N, ARGS)                                                           \
+    } while (0)
+
+#define CTB_ROWS_DISPATCH(MODES, KERNEL, ARGS)                                                        \
     do {                                                                                       \
         const int64_t per_v = vec4 ? 4 : 1;                                                    \
         const int64_t nv_warp = ceil_div(g.cols, 32 * per_v);                                  \
         const int64_t nv_128 = ceil_div(g.cols, 128 * per_v);                                  \
-        const int64_t nv_cta = ceil_div(g.cols, 256 * per_v);                                  \
-        const int gw = rows_grid(g.rows, 8, di.sm_count, 8);                                   \
-        const int gc = rows_grid(g.rows, 1, di.sm_count, 8);                                   \
+        const int64_t nv_256 = ceil_div(g.cols, 256 * per_v);                                  \
         if (vec4) {                                                                            \
-            if (nv_warp <= 1) KERNEL<32, 4, 1><<<gw, 256, 0, st>>> ARGS;                       \
-            else if (nv_warp <= 2) KERNEL<32, 4, 2><<<gw, 256, 0, st>>> ARGS;                  \
-            else if (nv_128 <= 1) KERNEL<128, 4, 1><<<gc, 128, 0, st>>> ARGS;                  \
-            else if (nv_128 <= 2) KERNEL<128, 4, 2><<<gc, 128, 0, st>>> ARGS;                  \
-            else if (nv_128 <= 4) KERNEL<128, 4, 4><<<gc, 128, 0, st>>> ARGS;                  \
-            else if (nv_cta <= 4) KERNEL<256, 4, 4><<<gc, 256, 0, st>>> ARGS;                  \
-            else if (nv_cta <= 8) KERNEL<256, 4, 8><<<gc, 256, 0, st>>> ARGS;                  \
+            if (nv_warp <= 1) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 1, ARGS);                         \
+            else if (nv_warp <= 2) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 2, ARGS);                    \
+            else if (nv_warp <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 4, ARGS);                    \
+            else if (nv_warp <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 8, ARGS);                    \
+            else if (nv_128 <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 4, ARGS);                    \
+            else if (nv_128 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 8, ARGS);                    \
+            else if (nv_256 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 256, 4, 8, ARGS);                    \
             else launched = false;                                                             \
         } else {                                                                               \
-            if (nv_warp <= 4) KERNEL<32, 1, 4><<<gw, 256, 0, st>>> ARGS;                       \
-            else if (nv_128 <= 8) KERNEL<128, 1, 8><<<gc, 128, 0, st>>> ARGS;                  \
-            else if (nv_cta <= 16) KERNEL<256, 1, 16><<<gc, 256, 0, st>>> ARGS;                \
-            else if (nv_cta <= 32) KERNEL<256, 1, 32><<<gc, 256, 0, st>>> ARGS;                \
+            if (nv_warp <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 1, 4, ARGS);                         \
+            else if (nv_warp <= 16) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 1, 16, ARGS);                  \
+            else if (nv_128 <= 16) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 1, 16, ARGS);                  \
+            else if (nv_256 <= 32) CTB_ROWS_LAUNCH(MODES, KERNEL, 256, 1, 32, ARGS);                  \
             else launched = false;                                                             \
         }                                                                                      \
     } while (0)
@@ -402,10 +504,13 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     if (rc) return rc;
     const RowIdx o = row_idx(g);
     const bool vec4 = rows_vec4(g, x, mask, out);
-    bool launched = true;
-    CTB_ROWS_DISPATCH(softmax_rows_kernel, (x, mask, out, o, g.rows, g.cols, g.qlen, g.m_inner, g.has_mask, causal));
+    // mode 2 and 6 (contiguous flag without a mask) do not occur
+    const int mode = (g.has_mask ? 1 : 0) | (g.has_mask && g.m_inner ? 2 : 0) | (causal ? 4 : 0);
+    bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
+    if (launched)
+        CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen));
     if (!launched) {
-        const int grid = rows_grid(g.rows, 1, di.sm_count, 8);
+        const int grid = rows_grid(g.rows, 1);
         softmax_rows_long_kernel<<<grid, 256, 0, st>>>(x, mask, out, o, g.rows, g.cols, g.qlen, g.m_inner, g.has_mask, causal);
     }
     return cuda_error(cudaGetLastError(), "softmax launch");
@@ -420,10 +525,14 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     const RowIdx o = row_idx(g);
     const bool vec4 = rows_vec4(g, x, nullptr, out);
     const double inv = 1.0 / (double)g.cols;
-    bool launched = true;
-    CTB_ROWS_DISPATCH(layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps));
+    int mode = 2;
+    if (!gamma && !beta) mode = 0;
+    else if (gamma && beta && gstride == 1 && bstride == 1 && vec4 && is_aligned(gamma, 16) && is_aligned(beta, 16)) mode = 1;
+    bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
+    if (launched)
+        CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
     if (!launched) {
-        const int grid = rows_grid(g.rows, 1, di.sm_count, 8);
+        const int grid = rows_grid(g.rows, 1);
         layernorm_rows_long_kernel<<<grid, 256, 0, st>>>(x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps);
     }
     return cuda_error(cudaGetLastError(), "layernorm launch");
