@@ -317,7 +317,7 @@ def bench_ours(args):
     # DRAM bytes per element from the ncu capture of the small case (n = 2^26), see
     # profiles/ew_flat_small_case_full_set.md; traffic grows in proportion to n.
     line["roofline"]["traffic"] = round(DRAM_BYTES_PER_ELEMENT[OPS[top][0]] * n)
-    print(json.dumps(line), flush=True)
+    _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -399,10 +399,28 @@ def bench_reference(args):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit(line)
+
+
+_REAL_STDOUT = None
+
+
+def _claim_stdout():
+    """Keep stdout for the one JSON line: everything else a library prints there (NCCL's version
+    banner, for one) goes to stderr."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def _emit(line: dict):
+    _REAL_STDOUT.write(json.dumps(line) + "\n")
+    _REAL_STDOUT.flush()
 
 
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
