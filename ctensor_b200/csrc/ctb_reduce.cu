@@ -386,9 +386,9 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
     }
     Acc* part = partials + (b * splits) * ncols;
     if (cact) part[(int64_t)blockIdx.y * ncols + ccol] = c;
-    __threadfence();
-    __syncthreads();
+    __syncthreads();                          // the CTA's partials are ordered before thread 0's fence
     if (threadIdx.x == 0) {
+        __threadfence();                      // cumulative: publishes them device-wide before the ticket
         const uint32_t slot = (uint32_t)(b * gridDim.x + blockIdx.x);
         const uint32_t t = atomicAdd(&tickets[slot], 1u);
         is_last = (t == (uint32_t)splits - 1);

@@ -11,6 +11,11 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # The shared libraries are build products (not in the history): make a fresh checkout
+    # testable.  nvcc cross-compiles sm_100a without a GPU; nothing is rebuilt when up to date.
+    from ctensor_b200 import build as b
+    b.build()
+    b.build_host()
 
 
 @pytest.fixture(scope="session")

@@ -10,6 +10,8 @@
 #include "ctb_host.h"
 #include "ops_dispatch.h"
 #include "opsmp.h"
+#include "ops1.h"
+#include "tensor1.h"
 
 static int g_checks = 0;
 #define CHECK(cond)                                                                  \
@@ -101,6 +103,14 @@ int main() {
     CHECK_NEAR(gelu(x)[2], 0.345714, 1e-5);
     CHECK_NEAR((x > 0.25)[2], 1.0, 0.0);
     CHECK((x > 0.25)._dtype() == DType::Float32);        // comparisons answer in the input dtype
+
+    // legacy names (ops1.h / opsmp.h of the reference's root tree)
+    CHECK_NEAR(add_(a, b)[0][0], 5.0, 1e-6);
+    CHECK_NEAR(diff_mp(b, a)[0][0], 1.0, 1e-6);
+    CHECK_NEAR(mult_(a, b)[1][1], 6.0, 1e-6);
+    CHECK_NEAR(Relu_(x)[0], 0.0, 0.0);
+    CHECK_NEAR(exp_mp(x)[1], 1.0, 0.0);
+    CHECK_NEAR(mult_scalar_mp(a, 1.5)[0][0], 3.0, 1e-6);
 
     // integer semantics (test/test_ops.cpp:203-213): truncation
     Tensor i3 = Tensor::from_vector({3, 5}, {2}, DType::Int32);
