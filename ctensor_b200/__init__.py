@@ -23,10 +23,11 @@ MAX_DIMS = 8
 # dtypes (reference DType numbering)
 F32, I32, F64 = 0, 1, 2
 # binary operators
-ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE = range(10)
+ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE, POW = range(11)
 # unary operators
 (ADD_S, SUB_S, RSUB_S, MUL_S, DIV_S, RDIV_S, POW_S, RPOW_S, LT_S, LE_S, GT_S, GE_S, EQ_S, NE_S,
- ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH) = range(22)
+ ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH,
+ SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, SOFTPLUS) = range(31)
 # reductions
 SUM, MEAN, MAX, MIN, VAR, ARGMAX = range(6)
 DIM_FULL = -1

@@ -408,7 +408,7 @@ int launch_binary(int op, int dtype, const Plan& p, const void* a, const void* b
     switch (op) {
 #define CASE(OP) case OP: return launch_binary_dt<OP>(dtype, p, a, b, out, st);
     CASE(CTB_ADD) CASE(CTB_SUB) CASE(CTB_MUL) CASE(CTB_DIV)
-    CASE(CTB_LT) CASE(CTB_LE) CASE(CTB_GT) CASE(CTB_GE) CASE(CTB_EQ) CASE(CTB_NE)
+    CASE(CTB_LT) CASE(CTB_LE) CASE(CTB_GT) CASE(CTB_GE) CASE(CTB_EQ) CASE(CTB_NE) CASE(CTB_POW)
 #undef CASE
     }
     return set_error(CTB_ERR_ARG, "binary op: unknown operator code %d", op);
@@ -423,6 +423,8 @@ int launch_unary(int op, int dtype, const Plan& p, const void* a, double s, void
     CASE(CTB_POW_S) CASE(CTB_RPOW_S)
     CASE(CTB_LT_S) CASE(CTB_LE_S) CASE(CTB_GT_S) CASE(CTB_GE_S) CASE(CTB_EQ_S) CASE(CTB_NE_S)
     CASE(CTB_ABS) CASE(CTB_RELU) CASE(CTB_SQRT)
+    CASE(CTB_SIN) CASE(CTB_COS) CASE(CTB_TAN) CASE(CTB_ASIN) CASE(CTB_ACOS) CASE(CTB_ATAN)
+    CASE(CTB_SINH) CASE(CTB_COSH) CASE(CTB_SOFTPLUS)
 #undef CASE
     // fp32-only flavours: instantiate for float alone
 #define CASEF(OP) case OP: return launch_shapes<UnAdapter<OP, float>, float, 1>(p, (const float*)a, nullptr, (float*)out, s, st);

@@ -213,6 +213,7 @@ template <int OP, typename T> struct BinaryFn {
         else if (OP == CTB_GT) r = x > y ? 1.0 : 0.0;
         else if (OP == CTB_GE) r = x >= y ? 1.0 : 0.0;
         else if (OP == CTB_EQ) r = x == y ? 1.0 : 0.0;
+        else if (OP == CTB_POW) r = pow(x, y);
         else r = x != y ? 1.0 : 0.0;
         return from_double<T>(r);
     }
@@ -228,6 +229,7 @@ template <int OP> struct BinaryFn<OP, float> {
         if (OP == CTB_GT) return a > b ? 1.0f : 0.0f;
         if (OP == CTB_GE) return a >= b ? 1.0f : 0.0f;
         if (OP == CTB_EQ) return a == b ? 1.0f : 0.0f;
+        if (OP == CTB_POW) return __double2float_rn(pow((double)a, (double)b));
         return a != b ? 1.0f : 0.0f;
     }
 };
@@ -253,6 +255,15 @@ template <int OP> __device__ __forceinline__ double unary_double(double x, doubl
     if (OP == CTB_ABS) return fabs(x);
     if (OP == CTB_RELU) return x > 0 ? x : 0.0;
     if (OP == CTB_SQRT) return __dsqrt_rn(x);
+    if (OP == CTB_SIN) return sin(x);
+    if (OP == CTB_COS) return cos(x);
+    if (OP == CTB_TAN) return tan(x);
+    if (OP == CTB_ASIN) return asin(x);
+    if (OP == CTB_ACOS) return acos(x);
+    if (OP == CTB_ATAN) return atan(x);
+    if (OP == CTB_SINH) return sinh(x);
+    if (OP == CTB_COSH) return cosh(x);
+    if (OP == CTB_SOFTPLUS) return log(1.0 + exp(x));
     return x;
 }
 

@@ -372,6 +372,7 @@ Tensor add(const Tensor& a, const Tensor& b) { return binary(CTB_ADD, "add", a, 
 Tensor sub(const Tensor& a, const Tensor& b) { return binary(CTB_SUB, "sub", a, b, true); }
 Tensor mul(const Tensor& a, const Tensor& b) { return binary(CTB_MUL, "mul", a, b, true); }
 Tensor div(const Tensor& a, const Tensor& b) { return binary(CTB_DIV, "div", a, b, true); }
+Tensor pow(const Tensor& a, const Tensor& b) { return binary(CTB_POW, "pow", a, b, true); }
 
 Tensor add_scalar(const Tensor& a, double s) { return unary(CTB_ADD_S, "add_scalar", a, s, true); }
 Tensor sub_scalar(const Tensor& a, double s) { return unary(CTB_SUB_S, "sub_scalar", a, s, true); }
@@ -400,6 +401,15 @@ Tensor log(const Tensor& a) { return unary(CTB_LOG, "log", a, 0.0, true); }
 Tensor ln(const Tensor& a) { return unary(CTB_LOG, "ln", a, 0.0, true); }
 Tensor exp(const Tensor& a) { return unary(CTB_EXP, "exp", a, 0.0, true); }
 Tensor sqrt(const Tensor& a) { return unary(CTB_SQRT, "sqrt", a, 0.0, true); }
+Tensor sin(const Tensor& a) { return unary(CTB_SIN, "sin", a, 0.0, true); }
+Tensor cos(const Tensor& a) { return unary(CTB_COS, "cos", a, 0.0, true); }
+Tensor tan(const Tensor& a) { return unary(CTB_TAN, "tan", a, 0.0, true); }
+Tensor asin(const Tensor& a) { return unary(CTB_ASIN, "asin", a, 0.0, true); }
+Tensor acos(const Tensor& a) { return unary(CTB_ACOS, "acos", a, 0.0, true); }
+Tensor atan(const Tensor& a) { return unary(CTB_ATAN, "atan", a, 0.0, true); }
+Tensor sinh(const Tensor& a) { return unary(CTB_SINH, "sinh", a, 0.0, true); }
+Tensor cosh(const Tensor& a) { return unary(CTB_COSH, "cosh", a, 0.0, true); }
+Tensor softplus(const Tensor& a) { return unary(CTB_SOFTPLUS, "softplus", a, 0.0, true); }
 Tensor tanh(const Tensor& a) { return unary(CTB_TANH, "tanh", a, 0.0, true); }
 Tensor sigmoid(const Tensor& a) { return unary(CTB_SIGMOID, "sigmoid", a, 0.0, true); }
 Tensor relu(const Tensor& a) { return unary(CTB_RELU, "relu", a, 0.0, true); }

@@ -19,6 +19,16 @@ inline Tensor abs_(const Tensor& a) { return abs(a); }
 inline Tensor ln_(const Tensor& a) { return ln(a); }
 inline Tensor exp_(const Tensor& a) { return exp(a); }
 inline Tensor sqrt_(const Tensor& a) { return sqrt(a); }
+inline Tensor pow_(const Tensor& a, const Tensor& b) { return pow(a, b); }
+inline Tensor sin_(const Tensor& a) { return sin(a); }
+inline Tensor asin_(const Tensor& a) { return asin(a); }
+inline Tensor sinh_(const Tensor& a) { return sinh(a); }
+inline Tensor cos_(const Tensor& a) { return cos(a); }
+inline Tensor acos_(const Tensor& a) { return acos(a); }
+inline Tensor cosh_(const Tensor& a) { return cosh(a); }
+inline Tensor tan_(const Tensor& a) { return tan(a); }
+inline Tensor atan_(const Tensor& a) { return atan(a); }
+inline Tensor softplus_(const Tensor& a) { return softplus(a); }
 inline Tensor tanh_(const Tensor& a) { return tanh(a); }
 inline Tensor sigmoid_(const Tensor& a) { return sigmoid(a); }
 inline Tensor Relu_(const Tensor& a) { return relu(a); }

@@ -13,6 +13,7 @@ Tensor add(const Tensor& a, const Tensor& b);
 Tensor sub(const Tensor& a, const Tensor& b);
 Tensor mul(const Tensor& a, const Tensor& b);
 Tensor div(const Tensor& a, const Tensor& b);
+Tensor pow(const Tensor& a, const Tensor& b);
 
 // tensor (op) scalar: evaluated in double, rounded once to the tensor's dtype
 Tensor add_scalar(const Tensor& a, double scalar);
@@ -44,6 +45,15 @@ Tensor log(const Tensor& a);
 Tensor ln(const Tensor& a);
 Tensor exp(const Tensor& a);
 Tensor sqrt(const Tensor& a);
+Tensor sin(const Tensor& a);
+Tensor cos(const Tensor& a);
+Tensor tan(const Tensor& a);
+Tensor asin(const Tensor& a);
+Tensor acos(const Tensor& a);
+Tensor atan(const Tensor& a);
+Tensor sinh(const Tensor& a);
+Tensor cosh(const Tensor& a);
+Tensor softplus(const Tensor& a);
 Tensor tanh(const Tensor& a);
 Tensor sigmoid(const Tensor& a);
 Tensor relu(const Tensor& a);
@@ -79,6 +89,7 @@ inline Tensor operator/(const Tensor& a, const Tensor& b) { return div(a, b); }
 // typo there); this library divides.
 inline Tensor operator/(const Tensor& a, double s) { return div_scalar(a, s); }
 inline Tensor operator/(double s, const Tensor& a) { return div_scalar_rev(s, a); }
+inline Tensor operator^(const Tensor& a, const Tensor& b) { return pow(a, b); }
 inline Tensor operator^(const Tensor& a, double s) { return pow_scalar(a, s); }
 inline Tensor operator^(double s, const Tensor& a) { return pow_scalar_rev(s, a); }
 

@@ -11,6 +11,7 @@ inline Tensor add_mp(const Tensor& a, const Tensor& b) { return add(a, b); }
 inline Tensor diff_mp(const Tensor& a, const Tensor& b) { return sub(a, b); }
 inline Tensor mult_mp(const Tensor& a, const Tensor& b) { return mul(a, b); }
 inline Tensor div_mp(const Tensor& a, const Tensor& b) { return div(a, b); }
+inline Tensor pow_mp(const Tensor& a, const Tensor& b) { return pow(a, b); }
 
 inline Tensor add_scalar_mp(const Tensor& a, double s) { return add_scalar(a, s); }
 inline Tensor sub_scalar_mp(const Tensor& a, double s) { return sub_scalar(a, s); }
@@ -25,6 +26,15 @@ inline Tensor abs_mp(const Tensor& a) { return abs(a); }
 inline Tensor ln_mp(const Tensor& a) { return ln(a); }
 inline Tensor exp_mp(const Tensor& a) { return exp(a); }
 inline Tensor sqrt_mp(const Tensor& a) { return sqrt(a); }
+inline Tensor sin_mp(const Tensor& a) { return sin(a); }
+inline Tensor asin_mp(const Tensor& a) { return asin(a); }
+inline Tensor cos_mp(const Tensor& a) { return cos(a); }
+inline Tensor acos_mp(const Tensor& a) { return acos(a); }
+inline Tensor tan_mp(const Tensor& a) { return tan(a); }
+inline Tensor atan_mp(const Tensor& a) { return atan(a); }
+inline Tensor sinh_mp(const Tensor& a) { return sinh(a); }
+inline Tensor cosh_mp(const Tensor& a) { return cosh(a); }
+inline Tensor softplus_mp(const Tensor& a) { return softplus(a); }
 inline Tensor tanh_mp(const Tensor& a) { return tanh(a); }
 inline Tensor sigmoid_mp(const Tensor& a) { return sigmoid(a); }
 inline Tensor Relu_mp(const Tensor& a) { return relu(a); }

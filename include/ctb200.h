@@ -68,6 +68,7 @@ typedef struct ctb_view {
 enum ctb_binary_op {
     CTB_ADD = 0, CTB_SUB = 1, CTB_MUL = 2, CTB_DIV = 3,
     CTB_LT = 4, CTB_LE = 5, CTB_GT = 6, CTB_GE = 7, CTB_EQ = 8, CTB_NE = 9,
+    CTB_POW = 10,          /* pow_mp, src/core/opsmp.cpp:411-414: std::pow in double, rounded once */
     CTB_BINARY_OP_COUNT
 };
 
@@ -84,6 +85,14 @@ enum ctb_unary_op {
     CTB_LT_S = 8, CTB_LE_S = 9, CTB_GT_S = 10, CTB_GE_S = 11, CTB_EQ_S = 12, CTB_NE_S = 13,
     CTB_ABS = 14, CTB_RELU = 15, CTB_EXP = 16, CTB_LOG = 17, CTB_TANH = 18, CTB_SIGMOID = 19,
     CTB_SQRT = 20, CTB_GELU_TANH = 21,
+    /* The remaining unary set of the reference (src/core/opsmp.cpp:566-589): evaluated like its
+     * scalar path, i.e. the double-precision libm function of (double)x rounded once to the
+     * tensor's dtype.  CUDA's and glibc's libm can differ in the last bit of a double, so these
+     * agree with the reference to ~1e-7 relative rather than bit for bit.  (The reference's SIMD
+     * sin/cos polynomials, src/cpu/AVX512/ops_avx512_f32.cpp:143-185, compute x*cos(x)-like
+     * values and are not followed.) */
+    CTB_SIN = 22, CTB_COS = 23, CTB_TAN = 24, CTB_ASIN = 25, CTB_ACOS = 26, CTB_ATAN = 27,
+    CTB_SINH = 28, CTB_COSH = 29, CTB_SOFTPLUS = 30,
     CTB_UNARY_OP_COUNT
 };
 

@@ -7,7 +7,7 @@
  *
  * Pinning: every function here is compared bit-for-bit (sums/means/variances: to 1e-6
  * relative) with the reference's own compiled code (oracle/_ref/libctensor_ref.so, built
- * by oracle/build_ref.sh from the reference sources) by tests/test_oracle_vs_reference.py,
+ * by oracle/build_ref.sh from the reference sources) by tests/test_oracle.py,
  * and with the committed golden vectors under tests/golden/ that the same reference
  * build generated (tests/golden/make_golden.py).
  *
@@ -34,11 +34,12 @@ typedef struct orc_view {       /* same layout as struct ctb_view (include/ctb20
 } orc_view;
 
 enum { ORC_F32 = 0, ORC_I32 = 1, ORC_F64 = 2 };
-enum { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_LT, B_LE, B_GT, B_GE, B_EQ, B_NE };
+enum { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_LT, B_LE, B_GT, B_GE, B_EQ, B_NE, B_POW };
 enum {
     U_ADD_S = 0, U_SUB_S, U_RSUB_S, U_MUL_S, U_DIV_S, U_RDIV_S, U_POW_S, U_RPOW_S,
     U_LT_S, U_LE_S, U_GT_S, U_GE_S, U_EQ_S, U_NE_S,
-    U_ABS, U_RELU, U_EXP, U_LOG, U_TANH, U_SIGMOID, U_SQRT, U_GELU_TANH
+    U_ABS, U_RELU, U_EXP, U_LOG, U_TANH, U_SIGMOID, U_SQRT, U_GELU_TANH,
+    U_SIN, U_COS, U_TAN, U_ASIN, U_ACOS, U_ATAN, U_SINH, U_COSH, U_SOFTPLUS
 };
 enum { R_SUM = 0, R_MEAN, R_MAX, R_MIN, R_VAR, R_ARGMAX };
 
@@ -189,6 +190,7 @@ static inline double bin_apply(int op, double x, double y) {
     case B_GT: return x > y ? 1.0 : 0.0;
     case B_GE: return x >= y ? 1.0 : 0.0;
     case B_EQ: return x == y ? 1.0 : 0.0;
+    case B_POW: return pow(x, y);                 /* pow_mp, src/core/opsmp.cpp:411-414 */
     default:   return x != y ? 1.0 : 0.0;
     }
 }
@@ -259,6 +261,16 @@ static inline double un_apply(int op, double x, double s) {
     case U_ABS:  return fabs(x);
     case U_RELU: return x > 0 ? x : 0.0;
     case U_SQRT: return sqrt(x);
+    /* libm in double, src/core/opsmp.cpp:566-574,586-589 */
+    case U_SIN:  return sin(x);
+    case U_COS:  return cos(x);
+    case U_TAN:  return tan(x);
+    case U_ASIN: return asin(x);
+    case U_ACOS: return acos(x);
+    case U_ATAN: return atan(x);
+    case U_SINH: return sinh(x);
+    case U_COSH: return cosh(x);
+    case U_SOFTPLUS: return log(1.0 + exp(x));
     default:     return x;
     }
 }

@@ -70,11 +70,12 @@ int64_t emit(const Tensor& r, void* out, int64_t out_capacity_bytes) {
 enum Path { PATH_MP = 0, PATH_AVX2 = 1, PATH_AVX512 = 2, PATH_DISPATCH = 3 };
 
 // Operator codes shared with include/ctb200.h.
-enum BinOp { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_LT, B_LE, B_GT, B_GE, B_EQ, B_NE };
+enum BinOp { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_LT, B_LE, B_GT, B_GE, B_EQ, B_NE, B_POW };
 enum UnOp {
     U_ADD_S = 0, U_SUB_S, U_RSUB_S, U_MUL_S, U_DIV_S, U_RDIV_S, U_POW_S, U_RPOW_S,
     U_LT_S, U_LE_S, U_GT_S, U_GE_S, U_EQ_S, U_NE_S,
-    U_ABS, U_RELU, U_EXP, U_LOG, U_TANH, U_SIGMOID, U_SQRT, U_GELU_TANH
+    U_ABS, U_RELU, U_EXP, U_LOG, U_TANH, U_SIGMOID, U_SQRT, U_GELU_TANH,
+    U_SIN, U_COS, U_TAN, U_ASIN, U_ACOS, U_ATAN, U_SINH, U_COSH, U_SOFTPLUS
 };
 enum RedOp { R_SUM = 0, R_MEAN, R_MAX, R_MIN, R_VAR, R_ARGMAX };
 
@@ -87,6 +88,7 @@ Tensor do_binary(int path, int op, const Tensor& a, const Tensor& b) {
         case B_LT: return lt_mp(a, b);     case B_LE: return le_mp(a, b);
         case B_GT: return gt_mp(a, b);     case B_GE: return ge_mp(a, b);
         case B_EQ: return eq_mp(a, b);     case B_NE: return ne_mp(a, b);
+        case B_POW: return pow_mp(a, b);
         } break;
     case PATH_AVX2:     // src/cpu/AVX2/ops_avx2_f32.cpp:574-604
         switch (op) {
@@ -148,6 +150,9 @@ Tensor do_unary(int path, int op, const Tensor& a, double s) {
         case U_EXP: return exp_mp(a);   case U_LOG: return ln_mp(a);
         case U_TANH: return tanh_mp(a); case U_SIGMOID: return sigmoid_mp(a);
         case U_SQRT: return sqrt_mp(a);
+        case U_SIN: return sin_mp(a);   case U_COS: return cos_mp(a);   case U_TAN: return tan_mp(a);
+        case U_ASIN: return asin_mp(a); case U_ACOS: return acos_mp(a); case U_ATAN: return atan_mp(a);
+        case U_SINH: return sinh_mp(a); case U_COSH: return cosh_mp(a); case U_SOFTPLUS: return softplus_mp(a);
         } break;
     case PATH_AVX2:     // src/cpu/AVX2/ops_avx2_f32.cpp:606-641
         switch (op) {

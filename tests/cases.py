@@ -87,6 +87,9 @@ def all_cases():
         sp = HostView.contig(SPECIAL_F32)
         add(name=f"bin_{nm}_special", kind="binary", op=op,
             views=[HostView.contig(np.repeat(SPECIAL_F32, SPECIAL_F32.size).reshape(SPECIAL_F32.size, -1)), sp])
+    pw_e = HostView.contig(_u(28, (1, 53), -2.0, 3.0))
+    add(name="bin_pow_rowbcast", kind="binary", op=ol.POW, views=[HostView.contig(np.abs(_n(17, (37, 53), 3.0)) + np.float32(1e-3)), pw_e],
+        exact=False)
     # both operands single elements (the dispatcher's scalar short-circuit computes the same value)
     add(name="bin_add_1x1", kind="binary", op=ol.ADD, views=[S1, HostView.contig(_u(11, (1, 1)))])
 
@@ -107,13 +110,15 @@ def all_cases():
     X = HostView.contig(_n(16, (37, 53), 3.0))
     Xp = HostView.contig(np.abs(_n(17, (37, 53), 3.0)) + np.float32(1e-3))
     sp = HostView.contig(SPECIAL_F32)
-    for op in range(22):
+    U1 = HostView.contig(_u(27, (37, 53)))            # |x| <= 1 for asin/acos
+    for op in range(31):
         nm = ol.UNARY_NAMES[op]
         path = _simd_path(op)
-        exact = op not in (ol.POW_S, ol.RPOW_S)        # libm pow in double: tolerance only
+        # libm functions evaluated in double (pow, trig, hyperbolic, softplus): tolerance only
+        exact = op not in (ol.POW_S, ol.RPOW_S) and op < ol.SIN
         for s in ((0.5, -3.0, 2.0) if op < ol.ABS else (0.0,)):
             tag = f"{nm}_{s}" if op < ol.ABS else nm
-            src = Xp if op in (ol.POW_S, ol.RPOW_S, ol.LOG, ol.SQRT) else X
+            src = Xp if op in (ol.POW_S, ol.RPOW_S, ol.LOG, ol.SQRT) else (U1 if op in (ol.ASIN, ol.ACOS) else X)
             if op == ol.RPOW_S and s < 0:
                 continue
             add(name=f"un_{tag}", kind="unary", op=op, views=[src], scalar=s, exact=exact, path=path)

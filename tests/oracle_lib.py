@@ -28,16 +28,18 @@ NP_DTYPES = {F32: np.float32, I32: np.int32, F64: np.float64}
 DT_OF = {np.dtype(np.float32): F32, np.dtype(np.int32): I32, np.dtype(np.float64): F64}
 
 # operator codes (include/ctb200.h)
-ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE = range(10)
+ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE, POW = range(11)
 (ADD_S, SUB_S, RSUB_S, MUL_S, DIV_S, RDIV_S, POW_S, RPOW_S, LT_S, LE_S, GT_S, GE_S, EQ_S, NE_S,
- ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH) = range(22)
+ ABS, RELU, EXP, LOG, TANH, SIGMOID, SQRT, GELU_TANH,
+ SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, SOFTPLUS) = range(31)
 SUM, MEAN, MAX, MIN, VAR, ARGMAX = range(6)
 PATH_MP, PATH_AVX2, PATH_AVX512, PATH_DISPATCH = range(4)
 
-BINARY_NAMES = ["add", "sub", "mul", "div", "lt", "le", "gt", "ge", "eq", "ne"]
+BINARY_NAMES = ["add", "sub", "mul", "div", "lt", "le", "gt", "ge", "eq", "ne", "pow"]
 UNARY_NAMES = ["add_s", "sub_s", "rsub_s", "mul_s", "div_s", "rdiv_s", "pow_s", "rpow_s",
                "lt_s", "le_s", "gt_s", "ge_s", "eq_s", "ne_s", "abs", "relu", "exp", "log",
-               "tanh", "sigmoid", "sqrt", "gelu_tanh"]
+               "tanh", "sigmoid", "sqrt", "gelu_tanh", "sin", "cos", "tan", "asin", "acos", "atan",
+               "sinh", "cosh", "softplus"]
 REDUCE_NAMES = ["sum", "mean", "max", "min", "var", "argmax"]
 
 
