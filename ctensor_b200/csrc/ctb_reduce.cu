@@ -27,7 +27,10 @@ namespace ctb {
 #define CTB_RED_THREADS 256
 #endif
 #ifndef CTB_RED_UNROLL
-#define CTB_RED_UNROLL 4
+#define CTB_RED_UNROLL 8
+#endif
+#ifndef CTB_RED_SPLIT_UNROLL
+#define CTB_RED_SPLIT_UNROLL 16            // full-tensor reductions: 16 x 16 B in flight per thread
 #endif
 #ifndef CTB_RED_SPLIT_CTAS_PER_SM
 #define CTB_RED_SPLIT_CTAS_PER_SM 4
@@ -221,27 +224,39 @@ __device__ __forceinline__ typename Pol::Acc block_reduce(typename Pol::Acc a, t
 
 // Accumulate elements [lo, hi) of one contiguous line; `nthr` cooperating threads, this one
 // has rank `tid`.  Vector loads when VEC > 1 (caller guarantees alignment of line + lo).
+// U vector loads issued back to back, then consumed.
+template <typename Pol, int VEC, int U>
+__device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const float* __restrict__ line,
+                                                 int64_t j, int64_t stride, double shift) {
+    using V = Vec<float, VEC>;
+    V v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(line + j + u * stride));
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
+}
+
 template <typename Pol, int VEC, int UNROLL>
 __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const float* __restrict__ line,
                                                 int64_t lo, int64_t hi, int tid, int nthr, double shift) {
-    using V = Vec<float, VEC>;
     const int64_t stride = (int64_t)nthr * VEC;
     int64_t j = lo + (int64_t)tid * VEC;
-    // unrolled main loop: UNROLL vector loads in flight
-    for (; j + (UNROLL - 1) * stride + VEC <= hi; j += UNROLL * stride) {
-        V v[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(line + j + u * stride));
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
+    // main loop: UNROLL loads in flight; the remainder keeps as many in flight as it has
+    // (UNROLL/2, UNROLL/4, ... 1) instead of degrading to one load at a time
+    for (; j + (UNROLL - 1) * stride + VEC <= hi; j += UNROLL * stride)
+        accumulate_batch<Pol, VEC, UNROLL>(acc, line, j, stride, shift);
+    if constexpr (UNROLL >= 16) {
+        if (j + 7 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 8>(acc, line, j, stride, shift); j += 8 * stride; }
     }
-    for (; j + VEC <= hi; j += stride) {
-        V v = ldg_stream(reinterpret_cast<const V*>(line + j));
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) Pol::add(acc, v.v[k], j + k, shift);
+    if constexpr (UNROLL >= 8) {
+        if (j + 3 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 4>(acc, line, j, stride, shift); j += 4 * stride; }
     }
+    if constexpr (UNROLL >= 4) {
+        if (j + 1 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 2>(acc, line, j, stride, shift); j += 2 * stride; }
+    }
+    for (; j + VEC <= hi; j += stride) accumulate_batch<Pol, VEC, 1>(acc, line, j, stride, shift);
     if (VEC > 1) {   // ragged end of the line
         for (int k = 0; k < VEC; ++k)
             if (j + k < hi) Pol::add(acc, line[j + k], j + k, shift);
@@ -297,7 +312,7 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
     int64_t hi = lo + chunk;
     if (hi > rlen) hi = rlen;
     typename Pol::Acc acc = Pol::init();
-    if (lo < hi) accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, lo, hi, threadIdx.x, THREADS, shift);
+    if (lo < hi) accumulate_line<Pol, VEC, CTB_RED_SPLIT_UNROLL>(acc, line, lo, hi, threadIdx.x, THREADS, shift);
     acc = block_reduce<Pol, THREADS>(acc, smem);
     if (threadIdx.x == 0) {
         partials[row * splits + blockIdx.x] = acc;
@@ -460,7 +475,7 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
             c.shape = SH_ROWS_SPLIT;
             int64_t want = (int64_t)sm_count * CTB_RED_SPLIT_CTAS_PER_SM / g.nout;
             if (want < 1) want = 1;
-            const int64_t gran = (int64_t)CTB_RED_THREADS * 4 * CTB_RED_UNROLL;     // keeps chunks vector-aligned
+            const int64_t gran = (int64_t)CTB_RED_THREADS * 4 * CTB_RED_SPLIT_UNROLL;   // whole unrolled passes, vector-aligned
             int64_t chunk = ceil_div(ceil_div(g.rlen, want), gran) * gran;
             c.chunk = chunk;
             c.splits = (int)ceil_div(g.rlen, chunk);
@@ -595,7 +610,7 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
             return set_error(CTB_ERR_ARG, "reduce: fp64 partials need a dense Float32 input");
         c.shape = SH_ROWS_SPLIT;
         c.vec = (is_aligned(a, 16) && g.rlen % 4 == 0) ? 4 : 1;
-        c.chunk = ceil_div(g.rlen > 0 ? g.rlen : 1, (int64_t)CTB_RED_THREADS * 4 * CTB_RED_UNROLL) * CTB_RED_THREADS * 4 * CTB_RED_UNROLL;
+        c.chunk = ceil_div(g.rlen > 0 ? g.rlen : 1, (int64_t)CTB_RED_THREADS * 4 * CTB_RED_SPLIT_UNROLL) * CTB_RED_THREADS * 4 * CTB_RED_SPLIT_UNROLL;
         c.splits = 1;
     }
     const size_t need = scratch_bytes(g, c);
