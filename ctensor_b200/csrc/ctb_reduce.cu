@@ -167,6 +167,11 @@ template <typename T, typename VT> struct Fin<T, ArgmaxPol<VT>> {
     }
 };
 
+// Row loads kept in flight per thread by the column kernel: 16 measured best where the
+// per-element work is heavier (fp64 sums, variance, arg-reduction), 8 for plain max/min.
+template <typename Pol> struct ColsUnroll { static constexpr int value = 2 * CTB_RED_COLS_UNROLL; };
+template <typename VT, bool M> struct ColsUnroll<MinMaxPol<VT, M>> { static constexpr int value = CTB_RED_COLS_UNROLL; };
+
 template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
 template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
 
@@ -367,12 +372,13 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
         }
         const float* p = base + col;
         int64_t r = r0 + y;
-        for (; r + 8 * (CTB_RED_COLS_UNROLL - 1) < r1; r += 8 * CTB_RED_COLS_UNROLL) {
-            V v[CTB_RED_COLS_UNROLL];
+        constexpr int CU = ColsUnroll<Pol>::value;
+        for (; r + 8 * (CU - 1) < r1; r += 8 * CU) {
+            V v[CU];
 #pragma unroll
-            for (int u = 0; u < CTB_RED_COLS_UNROLL; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
+            for (int u = 0; u < CU; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
 #pragma unroll
-            for (int u = 0; u < CTB_RED_COLS_UNROLL; ++u)
+            for (int u = 0; u < CU; ++u)
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
         }
