@@ -172,17 +172,32 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
     if (causal) live = min(cols, (int)(row % qlen) + 1);
     float t[NV][VEC];
     float m = -INFINITY;
+    // Pass A issues every load of the row back to back (nothing else in the loop body, so all
+    // of them are in flight together); pass B applies mask / causal cut-off and takes the max.
+    float m0 = 0.0f;
+    if (has_mask && !m_inner) m0 = mask[mo];
+    // (Which loop shape keeps all loads of the row in flight is decided by the instruction
+    // scheduler; measured on B200: one loop for the plain case, two passes as soon as a mask or
+    // the causal cut-off adds work between the loads.)
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int col = (i * GROUP + tid) * VEC;
         if (col < live) {
             load_vec<VEC>(t[i], xr, col, cols);
+            if (MODE == 0) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (MODE != 0 && col < live) {
             if (has_mask) {
-                const float* mr = mask + mo;
                 float mv[VEC];
-                if (m_inner) load_vec<VEC>(mv, mr, col, cols);
+                if (m_inner) load_vec<VEC>(mv, mask + mo, col, cols);     // L1/L2 resident: short latency
                 else {
-                    const float m0 = mr[0];
 #pragma unroll
                     for (int k = 0; k < VEC; ++k) mv[k] = m0;
                 }
