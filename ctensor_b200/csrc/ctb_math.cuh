@@ -14,21 +14,30 @@ namespace ctb {
 // ---- fp32 transcendental flavours -------------------------------------------------------------
 // exp512_ps, src/cpu/AVX512/ops_avx512_f32.cpp:63-92 (== exp256_ps, src/cpu/AVX2/
 // ops_avx2_f32.cpp:58-100, as GCC contracts it under the shipped -O3 -mfma flags).
-// SSE min/max return the second operand on an unordered compare, hence the selects.
+// SSE min/max return the second operand on an unordered compare: min_ps(x, HI) gives HI for NaN,
+// as fminf does.
+constexpr float kExpHi = 88.3762626647949f;
+
+// Clamp, fx = x*log2(e) + 0.5 and floor(fx) for exp_cephes.  |fx| <= 129, so adding 1.5*2^23
+// with rounding toward minus infinity gives floor(fx) + 1.5*2^23 exactly: no conversion, no
+// compare.  Returns -floor(fx) and the bit pattern of 2^floor(fx); x is clamped in place.
+__device__ __forceinline__ void exp_cephes_front(float& x, float& neg_fx, int32_t& pow2n_bits,
+                                                 float hi = kExpHi) {
+    x = fminf(x, hi);
+    x = fmaxf(x, -kExpHi);
+    const float fx = fmaf(x, 1.44269504088896341f, 0.5f);
+    const float MAGIC = 12582912.0f;                // 0x4B400000, ulp 1
+    const float r = __fadd_rd(fx, MAGIC);
+    pow2n_bits = (__float_as_int(r) - (0x4B400000 - 127)) << 23;
+    neg_fx = __fsub_rn(MAGIC, r);
+}
+
 __device__ __forceinline__ float exp_cephes(float x) {
-    x = fminf(x, 88.3762626647949f);      // min_ps(x, HI): NaN -> HI, as fminf does
-    x = fmaxf(x, -88.3762626647949f);
-    float fx = fmaf(x, 1.44269504088896341f, 0.5f);
-    // floor(fx) without the conversion pipe: |fx| <= 129, so adding 1.5*2^23 rounds to the
-    // nearest integer (exactly), and one compare corrects nearest -> floor.
-    const float MAGIC = 12582912.0f;
-    float r = __fadd_rn(fx, MAGIC);
-    int32_t n = __float_as_int(r) - 0x4B400000;    // integer nearest to fx
-    r = __fsub_rn(r, MAGIC);
-    if (r > fx) { r = __fsub_rn(r, 1.0f); n -= 1; }
-    fx = r;
-    x = fmaf(-fx, 0.693359375f, x);
-    x = fmaf(-fx, -2.12194440e-4f, x);
+    float neg_fx;
+    int32_t pbits;
+    exp_cephes_front(x, neg_fx, pbits);
+    x = fmaf(neg_fx, 0.693359375f, x);
+    x = fmaf(neg_fx, -2.12194440e-4f, x);
     float z = __fmul_rn(x, x);
     float y = 1.9875691500E-4f;
     y = fmaf(y, x, 1.3981999507E-3f);
@@ -38,8 +47,7 @@ __device__ __forceinline__ float exp_cephes(float x) {
     y = fmaf(y, x, 0.5f);
     y = fmaf(y, z, x);
     y = __fadd_rn(y, 1.0f);
-    float pow2n = __int_as_float((n + 127) << 23);
-    return __fmul_rn(y, pow2n);
+    return __fmul_rn(y, __int_as_float(pbits));
 }
 
 // log256_ps, src/cpu/AVX2/ops_avx2_f32.cpp:103-158 as compiled with the shipped flags:
@@ -108,30 +116,20 @@ __device__ __forceinline__ float gelu_tanh_chain(float x) {
     return __fmul_rn(h, t);
 }
 
-// ---- packed (two lanes per instruction) GELU ---------------------------------------------------
+// ---- packed (two lanes per instruction) variants ------------------------------------------------
 // sm_100 has packed fp32 instructions (fma/add/mul.rn.f32x2): one issue slot does two IEEE
-// operations, and the GELU chain is bound by issue slots, not by HBM.  Each lane computes
-// exactly the scalar sequence above, so results are bit-identical to gelu_tanh_chain (checked
-// over all 2^32 inputs on a B200).
+// operations, and exp/tanh/sigmoid/GELU are bound by issue slots, not by HBM.  Each lane computes
+// exactly the scalar sequence above, so results are bit-identical to the scalar functions (each
+// pair function was compared with its scalar twin over all 2^32 inputs on a B200).
 __device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
 
 // exp_cephes for two lanes: clamp, fx and floor per lane; range reduction and polynomial packed.
-__device__ __forceinline__ void exp_cephes_front(float& x, float& neg_fx, int32_t& n) {
-    x = fminf(x, 88.3762626647949f);      // == (x < HI) ? x : HI, also for NaN
-    x = fmaxf(x, -88.3762626647949f);
-    const float fx = fmaf(x, 1.44269504088896341f, 0.5f);
-    const float MAGIC = 12582912.0f;
-    float r = __fadd_rn(fx, MAGIC);
-    n = __float_as_int(r) - 0x4B400000;
-    r = __fsub_rn(r, MAGIC);
-    if (r > fx) { r = __fsub_rn(r, 1.0f); n -= 1; }
-    neg_fx = -r;
-}
-__device__ __forceinline__ float2 exp_cephes2(float2 v) {
+// `hi` may lower the upper clamp for callers that saturate earlier (tanh).
+__device__ __forceinline__ float2 exp_cephes2(float2 v, float hi = kExpHi) {
     float x0 = v.x, x1 = v.y, f0, f1;
-    int32_t n0, n1;
-    exp_cephes_front(x0, f0, n0);
-    exp_cephes_front(x1, f1, n1);
+    int32_t p0, p1;
+    exp_cephes_front(x0, f0, p0, hi);
+    exp_cephes_front(x1, f1, p1, hi);
     float2 x = make_float2(x0, x1);
     const float2 nfx = make_float2(f0, f1);
     x = __ffma2_rn(nfx, splat2(0.693359375f), x);
@@ -145,31 +143,51 @@ __device__ __forceinline__ float2 exp_cephes2(float2 v) {
     y = __ffma2_rn(y, x, splat2(0.5f));
     y = __ffma2_rn(y, z, x);
     y = __fadd2_rn(y, splat2(1.0f));
-    const float2 p = make_float2(__int_as_float((n0 + 127) << 23), __int_as_float((n1 + 127) << 23));
-    return __fmul2_rn(y, p);
+    return __fmul2_rn(y, make_float2(__int_as_float(p0), __int_as_float(p1)));
 }
 
-// (e-1)/(e+1) for e = exp_cephes(.) in [0, 2^25]: reciprocal estimate, one Newton step, quotient
-// and one remainder correction.  For these operands (denominator in [1, 2^25+1], |quotient| <= 1)
-// the result equals IEEE division; for e > 2^25 both e-1 and e+1 round to e and the quotient is
-// exactly 1.  Verified against __fdiv_rn for every fp32 input of the GELU chain.
-__device__ __forceinline__ float2 tanh_ratio2(float2 e) {
-    const float2 a = __fadd2_rn(e, splat2(-1.0f));
-    const float2 b = __fadd2_rn(e, splat2(1.0f));
+// Reciprocal estimate refined by one Newton step, for b in [1, 2^26].
+__device__ __forceinline__ float2 rcp_newton2(float2 b, float2 nb) {
     float2 r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(b.x));
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(b.y));
-    const float2 nb = make_float2(-b.x, -b.y);
     const float2 err = __ffma2_rn(nb, r, splat2(1.0f));
-    r = __ffma2_rn(r, err, r);
+    return __ffma2_rn(r, err, r);
+}
+
+// tanh_cephes for two lanes.  (e-1)/(e+1) equals 1 for every e >= 2^25 (both e-1 and e+1 round
+// to e), so the argument of exp is clamped at 17.4 (exp_cephes(17.4) > 2^25) instead of 88.38;
+// that keeps the denominator in the range where reciprocal + Newton + one remainder correction
+// equals IEEE division.
+constexpr float kTanhExpHi = 17.4f;
+__device__ __forceinline__ float2 tanh_cephes2(float2 x) {
+    const float2 e = exp_cephes2(__fmul2_rn(x, splat2(2.0f)), kTanhExpHi);
+    const float2 a = __fadd2_rn(e, splat2(-1.0f));
+    const float2 b = __fadd2_rn(e, splat2(1.0f));
+    const float2 nb = make_float2(-b.x, -b.y);
+    const float2 r = rcp_newton2(b, nb);
     const float2 q = __fmul2_rn(a, r);
     const float2 rem = __ffma2_rn(nb, q, a);
-    float2 t = __ffma2_rn(rem, r, q);
-    t.x = (e.x > 33554432.0f) ? 1.0f : t.x;
-    t.y = (e.y > 33554432.0f) ? 1.0f : t.y;
+    return __ffma2_rn(rem, r, q);
+}
+
+// sigmoid_cephes for two lanes: 1/(1+e) through the corrected reciprocal; IEEE division where
+// the quotient can be subnormal (e beyond 1e18; never reached for x > -41).
+__device__ __forceinline__ float2 sigmoid_cephes2(float2 x) {
+    const float2 e = exp_cephes2(make_float2(-x.x, -x.y));
+    const float2 b = __fadd2_rn(e, splat2(1.0f));
+    const float2 nb = make_float2(-b.x, -b.y);
+    const float2 r = rcp_newton2(b, nb);
+    const float2 rem = __ffma2_rn(nb, r, splat2(1.0f));
+    float2 t = __ffma2_rn(rem, r, r);
+    if (e.x > 1.0e18f) t.x = __fdiv_rn(1.0f, b.x);
+    if (e.y > 1.0e18f) t.y = __fdiv_rn(1.0f, b.y);
     return t;
 }
 
+// The two double-precision scalar multiplies stay in double: an fp32 two-product emulation with a
+// near-tie check was bit-exact too but slower (it moves work from the conversion and fp64 pipes,
+// which otherwise idle, to the fp32 pipe, which is the busy one).
 __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
     float2 u = __fmul2_rn(x, x);
     u = __fmul2_rn(u, x);
@@ -178,8 +196,7 @@ __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
     u = __fadd2_rn(x, u);
     u.x = mul_scalar_f32(u.x, 0.7978845608028654);
     u.y = mul_scalar_f32(u.y, 0.7978845608028654);
-    const float2 e = exp_cephes2(__fmul2_rn(u, splat2(2.0f)));
-    float2 t = tanh_ratio2(e);
+    float2 t = tanh_cephes2(u);
     t = __fadd2_rn(t, splat2(1.0f));
     const float2 h = __fmul2_rn(x, splat2(0.5f));
     return __fmul2_rn(h, t);
@@ -285,9 +302,11 @@ template <int OP> struct UnaryFn<OP, float> {
         return __double2float_rn(unary_double<OP>((double)x, s));
     }
     // Two lanes at once where a packed implementation exists (same bits as apply()).
-    static constexpr bool kHasPair = (OP == CTB_GELU_TANH);
+    static constexpr bool kHasPair = (OP == CTB_GELU_TANH || OP == CTB_TANH || OP == CTB_SIGMOID);
     __device__ __forceinline__ static float2 apply_pair(float2 x, double s) {
         if (OP == CTB_GELU_TANH) return gelu_tanh_chain2(x);
+        if (OP == CTB_TANH) return tanh_cephes2(x);
+        if (OP == CTB_SIGMOID) return sigmoid_cephes2(x);
         return make_float2(apply(x.x, s), apply(x.y, s));
     }
 };
