@@ -39,12 +39,13 @@ namespace ctb {
 #define CTB_RED_BLOCK_THREADS 512          // one CTA per long row: 512 threads measured best on B200
 #endif
 #ifndef CTB_RED_COLS_UNROLL
-#define CTB_RED_COLS_UNROLL 8
+#define CTB_RED_COLS_UNROLL 16             // row loads in flight per thread of the column kernel
 #endif
 #ifndef CTB_RED_COLS_CTAS_PER_SM
-#define CTB_RED_COLS_CTAS_PER_SM 14        // ~2048 CTAs on 148 SMs
+#define CTB_RED_COLS_CTAS_PER_SM 3         // register budget of the column kernel: at least this many CTAs per SM
 #endif
 
+constexpr int64_t kRowsWarpMax = 8192;
 constexpr int kCounterSlots = kTicketSlots;           // uint32 tickets at the start of scratch
 constexpr size_t kCounterBytes = kTicketBytes;
 
@@ -169,8 +170,7 @@ template <typename T, typename VT> struct Fin<T, ArgmaxPol<VT>> {
 
 // Row loads kept in flight per thread by the column kernel: 16 measured best where the
 // per-element work is heavier (fp64 sums, variance, arg-reduction), 8 for plain max/min.
-template <typename Pol> struct ColsUnroll { static constexpr int value = 2 * CTB_RED_COLS_UNROLL; };
-template <typename VT, bool M> struct ColsUnroll<MinMaxPol<VT, M>> { static constexpr int value = CTB_RED_COLS_UNROLL; };
+template <typename Pol> struct ColsUnroll { static constexpr int value = CTB_RED_COLS_UNROLL; };
 
 template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
 template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
@@ -212,17 +212,21 @@ __device__ __forceinline__ typename Pol::Acc warp_reduce(typename Pol::Acc a) {
     return a;   // valid in lane 0
 }
 
-// CTA-wide reduce; result valid in thread 0.  smem must hold THREADS/32 accumulators.
+// CTA-wide reduce; result valid in thread 0.  smem must hold THREADS/32 accumulators.  The warp
+// results are folded by a second shuffle tree in warp 0 (a serial loop in thread 0 kept the whole
+// CTA resident for THREADS/32 dependent fp64 additions).
 template <typename Pol, int THREADS>
 __device__ __forceinline__ typename Pol::Acc block_reduce(typename Pol::Acc a, typename Pol::Acc* smem) {
     constexpr int NW = THREADS / 32;
+    static_assert(NW <= 32, "one warp folds the warp results");
     a = warp_reduce<Pol>(a);
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     __syncthreads();                       // smem may still be read from a previous use
     if (lane == 0) smem[w] = a;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int i = 1; i < NW; ++i) a = Pol::combine(a, smem[i]);
+    if (w == 0) {
+        a = lane < NW ? smem[lane] : Pol::init();
+        a = warp_reduce<Pol>(a);
     }
     return a;
 }
@@ -342,8 +346,21 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
 // ---- cols -----------------------------------------------------------------------------------------------
 // Outer dims = [batch..., C] with the last one contiguous.  CTA = 32 x 8 threads: x walks
 // columns (VEC each), y walks rows.  grid = (column tiles, row splits, batch).
+template <typename Pol, int VEC, int U>
+__device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const float* __restrict__ q,
+                                           int64_t step, int64_t r, const double (&shift)[VEC]) {
+    using V = Vec<float, VEC>;
+    V v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(q + u * step));
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
+}
+
 template <typename Pol, int VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, CTB_RED_COLS_CTAS_PER_SM)
 reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64_t ncols, int64_t rlen,
                    int64_t rstride, int64_t rows_per_split, int op, uint32_t* tickets,
                    typename Pol::Acc* partials) {
@@ -370,23 +387,20 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
 #pragma unroll
             for (int k = 0; k < VEC; ++k) shift[k] = (double)base[col + k];
         }
-        const float* p = base + col;
-        int64_t r = r0 + y;
+        // CU row loads in flight; the remainder keeps as many in flight as it has (CU/2, ... 1)
         constexpr int CU = ColsUnroll<Pol>::value;
-        for (; r + 8 * (CU - 1) < r1; r += 8 * CU) {
-            V v[CU];
-#pragma unroll
-            for (int u = 0; u < CU; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(p + (r + 8 * u) * rstride));
-#pragma unroll
-            for (int u = 0; u < CU; ++u)
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
+        const int64_t step = 8 * rstride;
+        int64_t r = r0 + y;
+        const float* q = base + col + r * rstride;
+        for (; r + 8 * (CU - 1) < r1; r += 8 * CU, q += CU * step) cols_batch<Pol, VEC, CU>(acc, q, step, r, shift);
+        if constexpr (CU >= 16) {
+            if (r + 8 * 7 < r1) { cols_batch<Pol, VEC, 8>(acc, q, step, r, shift); r += 64; q += 8 * step; }
         }
-        for (; r < r1; r += 8) {
-            V v = ldg_stream(reinterpret_cast<const V*>(p + r * rstride));
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v.v[k], r, shift[k]);
+        if constexpr (CU >= 8) {
+            if (r + 8 * 3 < r1) { cols_batch<Pol, VEC, 4>(acc, q, step, r, shift); r += 32; q += 4 * step; }
         }
+        if (r + 8 < r1) { cols_batch<Pol, VEC, 2>(acc, q, step, r, shift); r += 16; q += 2 * step; }
+        if (r < r1) cols_batch<Pol, VEC, 1>(acc, q, step, r, shift);
     }
 #pragma unroll
     for (int k = 0; k < VEC; ++k) smem[y][x * VEC + k] = acc[k];
@@ -461,12 +475,37 @@ struct Choice {
     int64_t chunk;       // rows_split: elements per split; cols: rows per split
     int64_t coltiles;    // cols
     int64_t batch;       // cols
+    int splits_bound;    // cols: most splits any operator's kernel may use (sizes the scratch)
     size_t acc_bytes_max = 16;
 };
 
 bool all_multiple(const int64_t* v, int n, int64_t m) {
     for (int i = 0; i < n; ++i) if (v[i] % m) return false;
     return true;
+}
+
+// Row splits of the column kernel for a grid of `tiles` CTAs per split when `slots` CTAs can be
+// resident at once.  Up to one wave: as many splits as fit in it (a second, partly filled wave
+// measured 25 % slower than a single one that is 86 % full).  More tiles than slots: enough
+// splits for about four waves of small CTAs, so that the last wave's tail stays short.
+int cols_splits(int64_t tiles, int64_t slots, int64_t rlen) {
+    int64_t want = tiles <= slots ? slots / tiles : ceil_div(4 * slots, tiles);
+    const int64_t max_splits = rlen / 64;
+    if (want > max_splits) want = max_splits;
+    if (want > 64) want = 64;
+    if (want > 1 && tiles > kCounterSlots) want = 1;
+    return want < 1 ? 1 : (int)want;
+}
+
+// Upper bound over every occupancy a column kernel can have (1..8 CTAs of 256 threads per SM):
+// the workspace size must not depend on the operator.
+int cols_splits_bound(int64_t tiles, int sm_count, int64_t rlen) {
+    int s = 1;
+    for (int occ = 1; occ <= 8; ++occ) {
+        const int v = cols_splits(tiles, (int64_t)sm_count * occ, rlen);
+        if (v > s) s = v;
+    }
+    return s;
 }
 
 Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
@@ -487,7 +526,9 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
             c.splits = (int)ceil_div(g.rlen, chunk);
             return c;
         }
-        c.shape = g.rlen <= 2048 ? SH_ROWS_WARP : SH_ROWS_BLOCK;
+        // a warp per row up to 8192 elements (no CTA barrier per row; a 512-thread CTA per 4096-element
+        // row measured 3.7 TB/s against the warp's 6.6), a CTA per row beyond
+        c.shape = g.rlen <= kRowsWarpMax ? SH_ROWS_WARP : SH_ROWS_BLOCK;
         return c;
     }
     // column case: innermost outer dim contiguous
@@ -499,15 +540,10 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
             c.vec = (base16 && ncols % 4 == 0 && g.rstride % 4 == 0 && all_multiple(g.ostride, g.nouter - 1, 4)) ? 4 : 1;
             c.coltiles = ceil_div(ncols, 32 * c.vec);
             c.batch = batch;
-            int64_t ctas = c.coltiles * batch;
-            int64_t want = ceil_div((int64_t)sm_count * CTB_RED_COLS_CTAS_PER_SM, ctas);
-            int64_t max_splits = g.rlen / 64;
-            if (want > max_splits) want = max_splits;
-            if (want > 64) want = 64;
-            if (want < 1) want = 1;
-            if (want > 1 && ctas > kCounterSlots) want = 1;
-            c.chunk = ceil_div(ceil_div(g.rlen, want), 8) * 8;
-            c.splits = (int)ceil_div(g.rlen, c.chunk);
+            // splits and rows per split depend on the kernel's occupancy: set at launch (cols_splits)
+            c.splits = 0;
+            c.chunk = 0;
+            c.splits_bound = cols_splits_bound(c.coltiles * batch, sm_count, g.rlen);
             c.shape = SH_COLS;
             return c;
         }
@@ -517,7 +553,7 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
 
 size_t scratch_bytes(const ReduceGeom& g, const Choice& c) {
     if (c.shape == SH_ROWS_SPLIT) return kCounterBytes + (size_t)g.nout * c.splits * 16;
-    if (c.shape == SH_COLS && c.splits > 1) return kCounterBytes + (size_t)c.batch * c.splits * g.oshape[g.nouter - 1] * 16;
+    if (c.shape == SH_COLS && c.splits_bound > 1) return kCounterBytes + (size_t)c.batch * c.splits_bound * g.oshape[g.nouter - 1] * 16;
     return 0;
 }
 
@@ -526,6 +562,14 @@ OuterIdx outer_of(const ReduceGeom& g, int n) {
     dimset_init(&o.dims, n, g.oshape);
     for (int d = 0; d < n; ++d) o.stride[0][d] = g.ostride[d];
     return o;
+}
+
+// Resident CTAs per SM of a kernel (1..8); 4 if the runtime cannot say.
+int kernel_occupancy(const void* kernel, int threads) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (n < 1) n = 4;
+    return n > 8 ? 8 : n;
 }
 
 template <typename Pol>
@@ -559,10 +603,16 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
         break;
     }
     case SH_COLS: {
-        dim3 grid((unsigned)c.coltiles, (unsigned)c.splits, (unsigned)c.batch);
+        // resident CTAs per SM of this instantiation, asked once per process
+        static const int occ4 = kernel_occupancy((const void*)reduce_cols_kernel<Pol, 4>, 256);
+        static const int occ1 = kernel_occupancy((const void*)reduce_cols_kernel<Pol, 1>, 256);
+        const int occ = c.vec == 4 ? occ4 : occ1;
+        const int splits = cols_splits(c.coltiles * c.batch, (int64_t)sm_count * occ, g.rlen);
+        const int64_t chunk = ceil_div(ceil_div(g.rlen, (int64_t)splits), 8) * 8;
+        dim3 grid((unsigned)c.coltiles, (unsigned)ceil_div(g.rlen, chunk), (unsigned)c.batch);
         const int64_t ncols = g.oshape[g.nouter - 1];
-        if (c.vec == 4) reduce_cols_kernel<Pol, 4><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, c.chunk, op, tickets, partials);
-        else reduce_cols_kernel<Pol, 1><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, c.chunk, op, tickets, partials);
+        if (c.vec == 4) reduce_cols_kernel<Pol, 4><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, chunk, op, tickets, partials);
+        else reduce_cols_kernel<Pol, 1><<<grid, 256, 0, st>>>(a, out, outer_of(g, g.nouter - 1), ncols, g.rlen, g.rstride, chunk, op, tickets, partials);
         break;
     }
     default: return set_error(CTB_ERR_ARG, "reduce: internal shape error");
@@ -598,8 +648,11 @@ int launch_generic_t(int op, const ReduceGeom& g, const T* a, void* out, int sm_
 size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype) {
     DeviceInfo di;
     if (current_device_info(&di) != CTB_OK) di.sm_count = 148;
-    Choice c = choose(g, dtype, nullptr, di.sm_count);
-    return scratch_bytes(g, c);
+    // the base address is not known here: take the larger of the aligned (vector) and the
+    // unaligned (scalar) layout
+    const size_t vec_need = scratch_bytes(g, choose(g, dtype, nullptr, di.sm_count));
+    const size_t scalar_need = scratch_bytes(g, choose(g, dtype, reinterpret_cast<const void*>(4), di.sm_count));
+    return vec_need > scalar_need ? vec_need : scalar_need;
 }
 
 int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
