@@ -157,12 +157,24 @@ struct RowsArgs {
     uint32_t ntiles;                        // rows * tiles_per_row (< 2^31)
 };
 
-template <typename F, typename T, int NIN, int VEC, int UNROLL, int THREADS, bool ALIGNED>
+// MODE picks the body at compile time, because run-time tests on the operands' inner strides and
+// on the tile's raggedness inside the unrolled load loop made the scheduler wait for each load
+// before issuing the next one:
+//   ROWS_GENERAL     any inner strides 0/1, any alignment, ragged rows: element-wise accesses.
+//   ROWS_VEC         everything 16-byte aligned, inner % VEC == 0, first input inner-contiguous,
+//                    second input (if any) inner-contiguous: unconditional vector loads.
+//   ROWS_VEC_BSCALAR same, but the second input has inner stride 0 (one value per row).
+// In the two vector modes a thread without work loads from a valid dummy address (the row
+// start) instead of branching around the load, and only its store is predicated.
+enum { ROWS_GENERAL = 0, ROWS_VEC = 1, ROWS_VEC_BSCALAR = 2 };
+
+template <typename F, typename T, int NIN, int VEC, int UNROLL, int THREADS, int MODE>
 __global__ void __launch_bounds__(THREADS)
 ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
                RowsArgs g, double scalar) {
     using V = Vec<T, VEC>;
     constexpr uint32_t TILE = THREADS * VEC;
+    constexpr bool ALIGNED = false;                     // the general body works element by element
     // Per-tile offsets are computed by one thread each and shared through smem: the div/mod
     // chain would otherwise be repeated by all THREADS threads and dominate the kernel.
     __shared__ int64_t s_oa[UNROLL], s_ob[UNROLL], s_oo[UNROLL];
@@ -187,6 +199,35 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
             s_col[threadIdx.x] = col0;
         }
         __syncthreads();
+        if constexpr (MODE != ROWS_GENERAL) {
+            V va[UNROLL], vb[UNROLL];
+            int64_t oo[UNROLL];
+            bool act[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const uint32_t col0 = s_col[u];
+                const uint32_t col = col0 + threadIdx.x * VEC;          // wraps for "no tile": then >= inner or caught by col0
+                act[u] = col0 != 0xFFFFFFFFu && col < g.inner;
+                const uint32_t c = act[u] ? col : 0u;
+                oo[u] = s_oo[u] + c;
+                va[u] = ldg_stream(reinterpret_cast<const V*>(a + s_oa[u] + c));
+                if constexpr (NIN == 2) {
+                    if constexpr (MODE == ROWS_VEC) {
+                        vb[u] = ldg_stream(reinterpret_cast<const V*>(b + s_ob[u] + c));
+                    } else {
+                        const T sb = b[s_ob[u]];
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) vb[u].v[k] = sb;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                V r;
+                apply_vec<F, T, NIN, VEC>(r, va[u], vb[u], scalar);
+                if (act[u]) stg_stream(reinterpret_cast<V*>(out + oo[u]), r);
+            }
+        } else {
         V va[UNROLL], vb[UNROLL];
         int64_t oo[UNROLL];
         uint32_t cnt[UNROLL];
@@ -239,6 +280,7 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
                 for (int k = 0; k < VEC; ++k)
                     if ((uint32_t)k < cnt[u]) out[oo[u] + k] = r.v[k];
             }
+        }
         }
         __syncthreads();      // smem is rewritten by the next pass
     }
@@ -340,8 +382,12 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
             for (int d = nd - 2; d >= 0; --d) { out_stride[d] = st; st *= p.shape[d]; }
         }
         int64_t rows = 1;
-        bool aligned = is_aligned(out, CTB_ROWS_VEC_BYTES) && is_aligned(a, CTB_ROWS_VEC_BYTES) &&
-                       (NIN == 1 || is_aligned(b, CTB_ROWS_VEC_BYTES)) && (p.shape[nd - 1] % RVEC == 0);
+        // vector accesses need every operand that is read or written as vectors (inner stride 1)
+        // to start on a vector boundary in every row
+        const T* in_ptr[2] = {a, b};
+        bool aligned = is_aligned(out, CTB_ROWS_VEC_BYTES) && (p.shape[nd - 1] % RVEC == 0);
+        for (int i = 0; i < NIN; ++i)
+            if (p.stride[i][nd - 1] == 1 && !is_aligned(in_ptr[i], CTB_ROWS_VEC_BYTES)) aligned = false;
         int64_t oshape[CTB_MAX_DIMS];
         for (int k = 0; k < nd - 1; ++k) {
             const int d = order[k];
@@ -350,7 +396,7 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
             rows *= p.shape[d];
             for (int i = 0; i < NIN; ++i) {
                 g.stride[i][k] = p.stride[i][d];
-                if (p.stride[i][d] % RVEC != 0) aligned = false;
+                if (p.stride[i][nd - 1] == 1 && p.stride[i][d] % RVEC != 0) aligned = false;
             }
         }
         dimset_init(&g.outer, nd - 1, oshape);
@@ -363,10 +409,13 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
             g.tiles_per_row = make_fastdiv((uint32_t)tpr);
             g.ntiles = (uint32_t)ntiles;
             const unsigned grid = (unsigned)ceil_div(ntiles, RUNROLL);      // one pass per CTA
-            if (aligned)
-                ew_rows_kernel<F, T, NIN, RVEC, RUNROLL, THREADS, true><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
+            const bool vec_ok = aligned && g.istride[0] == 1;
+            if (vec_ok && (NIN == 1 || g.istride[1] == 1))
+                ew_rows_kernel<F, T, NIN, RVEC, RUNROLL, THREADS, ROWS_VEC><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
+            else if (NIN == 2 && vec_ok)
+                ew_rows_kernel<F, T, NIN, RVEC, RUNROLL, THREADS, (NIN == 2 ? ROWS_VEC_BSCALAR : ROWS_VEC)><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
             else
-                ew_rows_kernel<F, T, NIN, RVEC, RUNROLL, THREADS, false><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
+                ew_rows_kernel<F, T, NIN, RVEC, RUNROLL, THREADS, ROWS_GENERAL><<<grid, THREADS, 0, st>>>(a, b, out, g, scalar);
             return cuda_error(cudaGetLastError(), "ew_rows launch");
         }
     }
