@@ -43,6 +43,7 @@ EXPORTED_SYMBOLS = [
     "ctb_binary", "ctb_unary", "ctb_copy_strided", "ctb_reduce", "ctb_reduce_workspace_bytes",
     "ctb_reduce_ws", "ctb_reduce_dim_noalloc", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
+    "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad",
 ]
 
 
@@ -109,6 +110,9 @@ def lib() -> ctypes.CDLL:
     L.ctb_finalize_full.argtypes = [i32, vd, i64, vp, vd]
     L.ctb_softmax_lastdim.argtypes = [vp, vp, i32, vp, vd]
     L.ctb_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, vp, vd]
+    L.ctb_log_softmax_lastdim.argtypes = [vp, vp, vp, vd]
+    L.ctb_gather.argtypes = [vp, i32, vp, vp, vd, vd]
+    L.ctb_accumulate_grad.argtypes = [vp, vp, vd]
     L.ctb_binary_host.argtypes = [i32, vp, vp, vp, i32]
     L.ctb_unary_host.argtypes = [i32, vp, ctypes.c_double, vp, i32]
     L.ctb_reduce_host.argtypes = [i32, vp, i32, vp, i32]
@@ -310,6 +314,43 @@ def softmax(x, mask=None, causal: bool = False, out=None):
         check(lib().ctb_softmax_lastdim(x.cview(), None if m is None else m.cview(), int(causal),
                                         DView.of(out).cview(), _stream_ptr(x)))
     return out
+
+
+def log_softmax(x, mask=None, out=None):
+    """(t - max t) - ln(sum exp(t - max t)) over the last dim, t = x (+ mask)."""
+    x = _as_dview(x)
+    m = None if mask is None else _as_dview(mask)
+    if out is None:
+        out = _new_out(x, x.shape)
+    with _device_guard(x):
+        check(lib().ctb_log_softmax_lastdim(x.cview(), None if m is None else m.cview(),
+                                            DView.of(out).cview(), _stream_ptr(x)))
+    return out
+
+
+def gather(x, dim: int, index, out=None):
+    """Tensor::gather: out[i] = x[i with coordinate ``dim`` replaced by index[i]] (index: int32).
+    Raises CtbError(CTB_ERR_DIM) with the reference's text when an index is out of bounds."""
+    torch = _torch()
+    x, idx = _as_dview(x), _as_dview(index)
+    if out is None:
+        out = _new_out(x, idx.shape)
+    bad = torch.zeros(1, dtype=torch.int32, device=x.buf.device)
+    with _device_guard(x):
+        check(lib().ctb_gather(x.cview(), dim, idx.cview(), DView.of(out).cview(), bad.data_ptr(),
+                               _stream_ptr(x)))
+    if int(bad.item()):
+        raise CtbError(4, "Gather index out of bounds")
+    return out
+
+
+def accumulate_grad(grad, src):
+    """grad += src with the broadcast dims of src summed first and non-finite values skipped
+    (accumulate_grad of the reference's autograd); ``grad`` is updated in place."""
+    g, s = _as_dview(grad), _as_dview(src)
+    with _device_guard(g):
+        check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
+    return grad
 
 
 def layernorm(x, gamma=None, beta=None, eps: float = 1e-5, out=None):

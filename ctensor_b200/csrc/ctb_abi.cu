@@ -585,15 +585,24 @@ int ctb_finalize_full(int op, const double* partial, int64_t total_count, const 
     return launch_finalize_full(op, out->dtype, partial, total_count, elem_ptr_mut(out), (cudaStream_t)stream);
 }
 
-int ctb_softmax_lastdim(const ctb_view* x, const ctb_view* mask, int causal, const ctb_view* out, void* stream) {
+static int softmax_entry(const ctb_view* x, const ctb_view* mask, int causal, int log_out, const ctb_view* out,
+                         void* stream, const char* who) {
     int rc;
-    if ((rc = check_view(x, "softmax: null input", "softmax"))) return rc;
-    if (mask && (rc = check_view(mask, "softmax: null mask", "softmax"))) return rc;
+    if ((rc = check_view(x, "softmax: null input", who))) return rc;
+    if (mask && (rc = check_view(mask, "softmax: null mask", who))) return rc;
     RowsGeom g;
-    if ((rc = rows_geom(x, mask, &g, "softmax"))) return rc;
-    if ((rc = check_out(out, g.rows * g.cols, CTB_F32, "softmax"))) return rc;
+    if ((rc = rows_geom(x, mask, &g, who))) return rc;
+    if ((rc = check_out(out, g.rows * g.cols, CTB_F32, who))) return rc;
     return launch_softmax(g, (const float*)elem_ptr(x), mask ? (const float*)elem_ptr(mask) : nullptr,
-                          causal, (float*)elem_ptr_mut(out), (cudaStream_t)stream);
+                          causal, log_out, (float*)elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+int ctb_softmax_lastdim(const ctb_view* x, const ctb_view* mask, int causal, const ctb_view* out, void* stream) {
+    return softmax_entry(x, mask, causal, 0, out, stream, "softmax");
+}
+
+int ctb_log_softmax_lastdim(const ctb_view* x, const ctb_view* mask, const ctb_view* out, void* stream) {
+    return softmax_entry(x, mask, 0, 1, out, stream, "log_softmax");
 }
 
 int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_view* beta, double eps,
@@ -616,6 +625,155 @@ int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_vi
     return launch_layernorm(g, (const float*)elem_ptr(x), gamma ? (const float*)elem_ptr(gamma) : nullptr, st[0],
                             beta ? (const float*)elem_ptr(beta) : nullptr, st[1], eps,
                             (float*)elem_ptr_mut(out), (cudaStream_t)stream);
+}
+
+// ---- gather ------------------------------------------------------------------------------------------
+int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view* out, int32_t* bad, void* stream) {
+    int rc;
+    if ((rc = check_view(x, "Gather on empty tensor", "gather"))) return rc;
+    if ((rc = check_view(index, "Gather with empty index", "gather"))) return rc;
+    if (dim < 0 || dim >= x->ndim) return set_error(CTB_ERR_DIM, "Gather dimension out of range");
+    if (x->ndim != index->ndim) return set_error(CTB_ERR_SHAPE, "Input and index must have same number of dimensions");
+    if (index->dtype != CTB_I32) return set_error(CTB_ERR_DTYPE, "Index tensor must be integer type");
+    for (int d = 0; d < x->ndim; ++d)
+        if (d != dim && index->shape[d] > x->shape[d])
+            return set_error(CTB_ERR_SHAPE, "Index shape dimension mismatch with input");
+    if ((rc = check_out(out, view_numel(index), x->dtype, "gather"))) return rc;
+    if (bad) CTB_CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(int32_t), (cudaStream_t)stream));
+    if (view_numel(index) == 0) return CTB_OK;
+    return launch_gather((int)dtype_bytes(x->dtype), x->ndim, index->shape, x->stride, index->stride, dim,
+                         x->shape[dim], elem_ptr(x), (const int32_t*)elem_ptr(index), elem_ptr_mut(out), bad,
+                         (cudaStream_t)stream);
+}
+
+// ---- accumulate_grad ---------------------------------------------------------------------------------
+namespace {
+
+// Dense row-major strides of `shape` with 0 for size-1 dims.
+void dense_strides(int nd, const int64_t* shape, int64_t* stride) {
+    int64_t run = 1;
+    for (int d = nd - 1; d >= 0; --d) {
+        stride[d] = shape[d] == 1 ? 0 : run;
+        run *= shape[d];
+    }
+}
+
+// `v` with dims [lo, hi] (contiguous across each other) merged into one; returns its index.
+int merge_dims(const ctb_view& v, int lo, int hi, ctb_view* m) {
+    *m = v;
+    int64_t len = 1;
+    for (int d = lo; d <= hi; ++d) len *= v.shape[d];
+    int k = 0;
+    for (int d = 0; d < v.ndim; ++d) {
+        if (d > lo && d <= hi) continue;
+        m->shape[k] = d == lo ? len : v.shape[d];
+        m->stride[k] = d == lo ? v.stride[hi] : v.stride[d];
+        ++k;
+    }
+    m->ndim = k;
+    return lo;
+}
+
+}  // namespace
+
+int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream) {
+    int rc;
+    if ((rc = check_view(grad, "accumulate_grad: null gradient buffer", "accumulate_grad"))) return rc;
+    if ((rc = check_view(src, "accumulate_grad: null source", "accumulate_grad"))) return rc;
+    if (grad->dtype != src->dtype) return set_error(CTB_ERR_DTYPE, "accumulate_grad: dtype mismatch");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nd = grad->ndim > src->ndim ? grad->ndim : src->ndim;
+    if (nd == 0) {
+        const int64_t one = 1, zero = 0;
+        return launch_accumulate_strided(grad->dtype, 1, &one, &zero, &zero, elem_ptr_mut(grad), elem_ptr(src), st);
+    }
+    // right-aligned shapes; which source dims fold (target 1, source > 1)
+    int64_t tshape[CTB_MAX_DIMS], tstride[CTB_MAX_DIMS];
+    bool fold[CTB_MAX_DIMS], src_bcast = false;
+    ctb_view cur = *src;
+    cur.ndim = nd;
+    int nfold = 0;
+    for (int d = 0; d < nd; ++d) {
+        const int jt = d - (nd - grad->ndim), js = d - (nd - src->ndim);
+        tshape[d] = jt < 0 ? 1 : grad->shape[jt];
+        tstride[d] = (jt < 0 || grad->shape[jt] == 1) ? 0 : grad->stride[jt];
+        cur.shape[d] = js < 0 ? 1 : src->shape[js];
+        cur.stride[d] = (js < 0 || src->shape[js] == 1) ? 0 : src->stride[js];
+        if (tshape[d] != cur.shape[d] && tshape[d] != 1 && cur.shape[d] != 1)
+            return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+        fold[d] = tshape[d] == 1 && cur.shape[d] > 1;
+        if (fold[d]) ++nfold;
+        if (cur.shape[d] == 1 && tshape[d] > 1) src_bcast = true;
+    }
+    int64_t tnumel = 1, snumel = 1;
+    for (int d = 0; d < nd; ++d) { tnumel *= tshape[d]; snumel *= cur.shape[d]; }
+    if (tnumel == 0 || snumel == 0) return CTB_OK;
+
+    // groups of neighbouring folded dims the source is contiguous across, last group first
+    struct Group { int lo, hi; };
+    Group groups[CTB_MAX_DIMS];
+    int ngroups = 0;
+    for (int d = nd - 1; d >= 0; --d) {
+        if (!fold[d]) continue;
+        int lo = d;
+        while (lo > 0 && fold[lo - 1] && cur.stride[lo - 1] == cur.stride[lo] * cur.shape[lo]) --lo;
+        groups[ngroups++] = {lo, d};
+        d = lo;
+    }
+    // scratch: kernel scratch of the largest step, then two buffers for intermediate sums
+    const size_t eb = dtype_bytes(src->dtype);
+    size_t kernel_ws = 0, tmp_elems = 0;
+    {
+        ctb_view sim = cur;
+        for (int gi = 0; gi < ngroups; ++gi) {
+            ctb_view m;
+            const int rd = merge_dims(sim, groups[gi].lo, groups[gi].hi, &m);
+            ReduceGeom g;
+            reduce_geom_dim(&m, rd, &g);
+            const size_t need = reduce_workspace_bytes(g, src->dtype);
+            if (need > kernel_ws) kernel_ws = need;
+            for (int d = groups[gi].lo; d <= groups[gi].hi; ++d) sim.shape[d] = 1;
+            dense_strides(nd, sim.shape, sim.stride);
+            int64_t n = 1;
+            for (int d = 0; d < nd; ++d) n *= sim.shape[d];
+            if ((size_t)n > tmp_elems) tmp_elems = (size_t)n;
+        }
+    }
+    kernel_ws = (kernel_ws + 255) / 256 * 256;
+    const size_t tmp_bytes = (tmp_elems * eb + 255) / 256 * 256;
+    void* ws = nullptr;
+    if (ngroups > 0 && (rc = ensure_workspace(kernel_ws + 2 * tmp_bytes, &ws))) return rc;
+
+    const bool grad_dense = view_contiguous(grad);
+    for (int gi = 0; gi < ngroups; ++gi) {
+        ctb_view m;
+        const int rd = merge_dims(cur, groups[gi].lo, groups[gi].hi, &m);
+        ReduceGeom g;
+        reduce_geom_dim(&m, rd, &g);
+        const bool last = gi == ngroups - 1;
+        if (last && grad_dense && !src_bcast) {
+            // the last fold adds straight into the gradient buffer: out[i] += (T)sum
+            return launch_reduce(kOpSumAccumulate, src->dtype, g, elem_ptr(&m), elem_ptr_mut(grad), nullptr, ws, kernel_ws, st);
+        }
+        void* tmp = (char*)ws + kernel_ws + (gi % 2) * tmp_bytes;
+        if ((rc = launch_reduce(CTB_SUM, src->dtype, g, elem_ptr(&m), tmp, nullptr, ws, kernel_ws, st))) return rc;
+        for (int d = groups[gi].lo; d <= groups[gi].hi; ++d) cur.shape[d] = 1;
+        dense_strides(nd, cur.shape, cur.stride);
+        cur.base = tmp;
+        cur.offset = 0;
+    }
+    // element-wise accumulation of `cur` (possibly broadcast) into the gradient buffer
+    if (grad_dense) {
+        ctb_view t = *grad;
+        t.ndim = nd;
+        for (int d = 0; d < nd; ++d) t.shape[d] = tshape[d];
+        dense_strides(nd, t.shape, t.stride);
+        const ctb_view* in[2] = {&t, &cur};
+        Plan p;
+        if ((rc = build_plan(in, 2, &p))) return rc;
+        return launch_binary(kOpAddFinite, grad->dtype, p, elem_ptr(grad), elem_ptr(&cur), elem_ptr_mut(grad), st);
+    }
+    return launch_accumulate_strided(grad->dtype, nd, tshape, tstride, cur.stride, elem_ptr_mut(grad), elem_ptr(&cur), st);
 }
 
 // ---- host-buffer entry points --------------------------------------------------------------------------

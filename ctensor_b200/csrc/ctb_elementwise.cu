@@ -458,6 +458,7 @@ int launch_binary(int op, int dtype, const Plan& p, const void* a, const void* b
 #define CASE(OP) case OP: return launch_binary_dt<OP>(dtype, p, a, b, out, st);
     CASE(CTB_ADD) CASE(CTB_SUB) CASE(CTB_MUL) CASE(CTB_DIV)
     CASE(CTB_LT) CASE(CTB_LE) CASE(CTB_GT) CASE(CTB_GE) CASE(CTB_EQ) CASE(CTB_NE) CASE(CTB_POW)
+    CASE(kOpAddFinite)
 #undef CASE
     }
     return set_error(CTB_ERR_ARG, "binary op: unknown operator code %d", op);

@@ -171,6 +171,46 @@ __device__ __forceinline__ float2 tanh_cephes2(float2 x) {
     return __ffma2_rn(rem, r, q);
 }
 
+// log_cephes for two lanes: mantissa/exponent split per lane, polynomial packed.  The exponent
+// (+1, -1 when the mantissa is below sqrt(1/2)) becomes a float through the 1.5*2^23 bit
+// pattern, which is exact for these small integers and needs no conversion instruction.
+__device__ __forceinline__ void log_cephes_front(float x, float& mant_m1, float& e, bool& invalid) {
+    invalid = (x <= 0.0f);
+    x = fmaxf(x, 1.17549435e-38f);                  // max_ps(x, FLT_MIN): NaN -> FLT_MIN, as fmaxf does
+    const uint32_t bits = __float_as_uint(x);
+    const float m = __uint_as_float((bits & 0x7fffffu) | 0x3f000000u);
+    const bool lo = (m < 0.707106781186547524f);
+    const int32_t ei = (int32_t)(bits >> 23) + (0x4B400000 - 126) - (lo ? 1 : 0);
+    e = __fsub_rn(__int_as_float(ei), 12582912.0f);
+    mant_m1 = __fadd_rn(__fsub_rn(m, 1.0f), lo ? m : 0.0f);
+}
+__device__ __forceinline__ float2 log_cephes2(float2 v) {
+    float x0, x1, e0, e1;
+    bool i0, i1;
+    log_cephes_front(v.x, x0, e0, i0);
+    log_cephes_front(v.y, x1, e1, i1);
+    const float2 x = make_float2(x0, x1), e = make_float2(e0, e1);
+    const float2 z = __fmul2_rn(x, x);
+    float2 y = splat2(7.0376836292E-2f);
+    y = __ffma2_rn(y, x, splat2(-1.1514610310E-1f));
+    y = __ffma2_rn(y, x, splat2(1.1676998740E-1f));
+    y = __ffma2_rn(y, x, splat2(-1.2420140846E-1f));
+    y = __ffma2_rn(y, x, splat2(1.4249322787E-1f));
+    y = __ffma2_rn(y, x, splat2(-1.6668057665E-1f));
+    y = __ffma2_rn(y, x, splat2(2.0000714765E-1f));
+    y = __ffma2_rn(y, x, splat2(-2.4999993993E-1f));
+    y = __ffma2_rn(y, x, splat2(3.3333331174E-1f));
+    y = __fmul2_rn(y, x);
+    const float2 t = __fmul2_rn(e, splat2(-2.12194440e-4f));
+    y = __ffma2_rn(y, z, t);
+    y = __ffma2_rn(z, splat2(-0.5f), y);
+    float2 r = __fadd2_rn(x, y);
+    r = __ffma2_rn(e, splat2(0.693359375f), r);
+    if (i0) r.x = __uint_as_float(0xFFFFFFFFu);
+    if (i1) r.y = __uint_as_float(0xFFFFFFFFu);
+    return r;
+}
+
 // sigmoid_cephes for two lanes: 1/(1+e) through the corrected reciprocal; IEEE division where
 // the quotient can be subnormal (e beyond 1e18; never reached for x > -41).
 __device__ __forceinline__ float2 sigmoid_cephes2(float2 x) {
@@ -218,9 +258,14 @@ template <> __device__ __forceinline__ int32_t from_double<int32_t>(double v) { 
 // ---- binary functors: out = (T) op((double)a, (double)b), src/core/opsmp.cpp:198,249-252 --------
 // For fp32 the four arithmetic ops are evaluated directly in fp32: the double-precision result
 // rounded to fp32 equals the IEEE fp32 operation (double rounding is innocuous for + - * /).
+// Internal operator (not part of the public enum): a + b, or a unchanged when b is NaN or
+// infinite — the accumulation step of accumulate_grad, src/core/autograd.cpp:139-151.
+constexpr int kOpAddFinite = CTB_BINARY_OP_COUNT;
+
 template <int OP, typename T> struct BinaryFn {
     __device__ __forceinline__ static T apply(T a, T b) {
         double x = to_double(a), y = to_double(b), r;
+        if (OP == kOpAddFinite) return isfinite(y) ? from_double<T>(__dadd_rn(x, y)) : a;
         if (OP == CTB_ADD) r = __dadd_rn(x, y);
         else if (OP == CTB_SUB) r = __dsub_rn(x, y);
         else if (OP == CTB_MUL) r = __dmul_rn(x, y);
@@ -237,6 +282,7 @@ template <int OP, typename T> struct BinaryFn {
 };
 template <int OP> struct BinaryFn<OP, float> {
     __device__ __forceinline__ static float apply(float a, float b) {
+        if (OP == kOpAddFinite) return isfinite(b) ? __fadd_rn(a, b) : a;
         if (OP == CTB_ADD) return __fadd_rn(a, b);
         if (OP == CTB_SUB) return __fsub_rn(a, b);
         if (OP == CTB_MUL) return __fmul_rn(a, b);
@@ -302,11 +348,14 @@ template <int OP> struct UnaryFn<OP, float> {
         return __double2float_rn(unary_double<OP>((double)x, s));
     }
     // Two lanes at once where a packed implementation exists (same bits as apply()).
-    static constexpr bool kHasPair = (OP == CTB_GELU_TANH || OP == CTB_TANH || OP == CTB_SIGMOID);
+    static constexpr bool kHasPair = (OP == CTB_GELU_TANH || OP == CTB_TANH || OP == CTB_SIGMOID ||
+                                      OP == CTB_LOG || OP == CTB_EXP);
     __device__ __forceinline__ static float2 apply_pair(float2 x, double s) {
         if (OP == CTB_GELU_TANH) return gelu_tanh_chain2(x);
         if (OP == CTB_TANH) return tanh_cephes2(x);
         if (OP == CTB_SIGMOID) return sigmoid_cephes2(x);
+        if (OP == CTB_LOG) return log_cephes2(x);
+        if (OP == CTB_EXP) return exp_cephes2(x);
         return make_float2(apply(x.x, s), apply(x.y, s));
     }
 };

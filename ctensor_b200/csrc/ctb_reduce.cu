@@ -129,6 +129,10 @@ template <typename T> struct Finalize {
     __device__ __forceinline__ static void run(int op, const typename SumPol<VT>::Acc& a, int64_t n, void* out, int64_t oi, double* po) {
         if (po) { po[oi] = a.s; return; }
         T s = from_double<T>(a.s);
+        if (op == kOpSumAccumulate) {
+            if (isfinite(to_double(s))) ((T*)out)[oi] = from_double<T>(__dadd_rn(to_double(((T*)out)[oi]), to_double(s)));
+            return;
+        }
         if (op == CTB_MEAN) s = from_double<T>(__dmul_rn(to_double(s), 1.0 / (double)n));
         ((T*)out)[oi] = s;
     }
@@ -628,7 +632,7 @@ int launch_generic_t(int op, const ReduceGeom& g, const T* a, void* out, int sm_
     if (grid < 1) grid = 1;
     OuterIdx o = outer_of(g, g.nouter);
     switch (op) {
-    case CTB_SUM: case CTB_MEAN:
+    case CTB_SUM: case CTB_MEAN: case kOpSumAccumulate:
         reduce_generic_kernel<SumPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
     case CTB_MAX:
         reduce_generic_kernel<MinMaxPol<double, true>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
@@ -657,7 +661,7 @@ size_t reduce_workspace_bytes(const ReduceGeom& g, int dtype) {
 
 int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* out,
                   double* partial_out, void* ws, size_t ws_bytes, cudaStream_t st) {
-    if (op < 0 || op >= CTB_REDUCE_OP_COUNT) return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+    if (op < 0 || op > kOpSumAccumulate) return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
     DeviceInfo di;
     int rc = current_device_info(&di);
     if (rc) return rc;
@@ -686,7 +690,7 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
     }
     const float* fa = (const float*)a;
     switch (op) {
-    case CTB_SUM: case CTB_MEAN: return launch_fast<SumPol<float>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_SUM: case CTB_MEAN: case kOpSumAccumulate: return launch_fast<SumPol<float>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
     case CTB_MAX: return launch_fast<MinMaxPol<float, true>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
     case CTB_MIN: return launch_fast<MinMaxPol<float, false>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
     case CTB_VAR: return launch_fast<VarPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);

@@ -19,6 +19,11 @@ struct ReduceGeom {
 
 // Split reductions keep their tickets (uint32 counters, zero between launches) in the first
 // kTicketBytes of the scratch buffer; nothing else may be written there.
+// Internal reduction operator (not part of the public enum): out[i] += (T)sum unless the sum is
+// NaN or infinite — reduction and accumulation of accumulate_grad (src/core/autograd.cpp:84-151)
+// in one kernel.
+constexpr int kOpSumAccumulate = CTB_REDUCE_OP_COUNT;
+
 constexpr int kTicketSlots = 16384;
 constexpr size_t kTicketBytes = kTicketSlots * sizeof(uint32_t);
 
@@ -53,7 +58,7 @@ struct RowsGeom {
     int32_t m_inner;     // mask inner stride (0 or 1)
     int32_t has_mask;
 };
-int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int causal, float* out,
+int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int causal, int log_out, float* out,
                    cudaStream_t stream);
 int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride,
                      const float* beta, int64_t bstride, double eps, float* out,

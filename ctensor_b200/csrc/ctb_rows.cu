@@ -152,7 +152,8 @@ template <int GROUP> struct RowCta { static constexpr int kThreads = GROUP == 32
 
 // MODE bits (compile time, so the unrolled load loop has no run-time branch and all loads of a
 // row are in flight together): 1 = additive mask, 2 = the mask's last dim is contiguous
-// (else one value per row), 4 = causal.
+// (else one value per row), 4 = causal, 8 = log-softmax: out = (t - m) - log((float)sum), the
+// chain of Loss::CrossEntropy (src/neuralnet/loss.cpp:97-104); not combined with causal.
 template <int GROUP, int VEC, int NV, int MODE>
 __global__ void __launch_bounds__(RowCta<GROUP>::kThreads)
 softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
@@ -160,6 +161,7 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
     constexpr int THREADS = RowCta<GROUP>::kThreads;
     constexpr int GPC = THREADS / GROUP;                // rows per CTA
     constexpr bool has_mask = (MODE & 1) != 0, m_inner = (MODE & 2) != 0, causal = (MODE & 4) != 0;
+    constexpr bool log_out = (MODE & 8) != 0;
     __shared__ float smax[THREADS / 32];
     __shared__ double ssum[THREADS / 32];
     const int tid = threadIdx.x % GROUP;
@@ -222,22 +224,41 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
             if constexpr (VEC % 2 == 0) {
 #pragma unroll
                 for (int k = 0; k < VEC; k += 2) {
-                    const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
-                    t[i][k] = e.x;
-                    t[i][k + 1] = e.y;
+                    const float2 sh = __fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m));
+                    const float2 e = exp_cephes2(sh);
+                    t[i][k] = log_out ? sh.x : e.x;           // log-softmax keeps the shifted input
+                    t[i][k + 1] = log_out ? sh.y : e.y;
+                    z = __dadd_rn(__dadd_rn(z, (double)e.x), (double)e.y);
                 }
             } else {
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
+                for (int k = 0; k < VEC; ++k) {
+                    const float sh = __fsub_rn(t[i][k], m);
+                    const float e = exp_cephes(sh);
+                    t[i][k] = log_out ? sh : e;
+                    z = __dadd_rn(z, (double)e);
+                }
             }
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) z = __dadd_rn(z, (double)t[i][k]);
         }
     }
     z = group_sum<GROUP>(z, ssum);
     const float zf = __double2float_rn(z);
-    const float rz = row_reciprocal(zf);
     float* orow = out + row * (int64_t)cols;
+    if constexpr (log_out) {
+        const float lz = log_cephes(zf);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int col = (i * GROUP + tid) * VEC;
+            if (col < cols) {
+                float r[VEC];
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) r[k] = __fsub_rn(t[i][k], lz);
+                store_vec<VEC>(orow, col, r);
+            }
+        }
+        return;
+    }
+    const float rz = row_reciprocal(zf);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int col = (i * GROUP + tid) * VEC;
@@ -277,7 +298,8 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
 // Long rows: one CTA per row, three passes over global memory (the row is re-read from L2).
 __global__ void __launch_bounds__(256)
 softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
-                         RowIdx o, int64_t rows, int64_t cols, int64_t qlen, int m_inner, int has_mask, int causal) {
+                         RowIdx o, int64_t rows, int64_t cols, int64_t qlen, int m_inner, int has_mask, int causal,
+                         int log_out) {
     __shared__ float smax[8];
     __shared__ double ssum[8];
     for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
@@ -297,12 +319,18 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
         double z = 0.0;
         float* orow = out + row * cols;
         for (int64_t c = threadIdx.x; c < live; c += 256) {
-            float e = exp_cephes(__fsub_rn(tval(c), m));
-            orow[c] = e;
+            const float sh = __fsub_rn(tval(c), m);
+            const float e = exp_cephes(sh);
+            orow[c] = log_out ? sh : e;
             z = __dadd_rn(z, (double)e);
         }
         z = cta_sum256(z, ssum);
         const float zf = __double2float_rn(z);
+        if (log_out) {
+            const float lz = log_cephes(zf);
+            for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = __fsub_rn(orow[c], lz);
+            continue;
+        }
         const float rz = row_reciprocal(zf);
         for (int64_t c = threadIdx.x; c < cols; c += 256) orow[c] = (c < live) ? div_by_row(orow[c], zf, rz) : 0.0f;
     }
@@ -472,7 +500,10 @@ int rows_grid(int64_t rows, int groups_per_cta) {
     case 3: KERNEL<G, V, N, 3><<<grid, thr, 0, st>>> ARGS; break;                              \
     case 4: KERNEL<G, V, N, 4><<<grid, thr, 0, st>>> ARGS; break;                              \
     case 5: KERNEL<G, V, N, 5><<<grid, thr, 0, st>>> ARGS; break;                              \
-    default: KERNEL<G, V, N, 7><<<grid, thr, 0, st>>> ARGS; break;                             \
+    case 7: KERNEL<G, V, N, 7><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 8: KERNEL<G, V, N, 8><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 9: KERNEL<G, V, N, 9><<<grid, thr, 0, st>>> ARGS; break;                              \
+    default: KERNEL<G, V, N, 11><<<grid, thr, 0, st>>> ARGS; break;                            \
     }
 #define CTB_MODES_LAYERNORM(KERNEL, G, V, N, ARGS)                                             \
     switch (mode) {                                                                            \
@@ -511,7 +542,7 @@ int rows_grid(int64_t rows, int groups_per_cta) {
         }                                                                                      \
     } while (0)
 
-int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int causal, float* out,
+int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int causal, int log_out, float* out,
                    cudaStream_t st) {
     if (g.rows == 0 || g.cols == 0) return CTB_OK;
     DeviceInfo di;
@@ -520,13 +551,14 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     const RowIdx o = row_idx(g);
     const bool vec4 = rows_vec4(g, x, mask, out);
     // mode 2 and 6 (contiguous flag without a mask) do not occur
-    const int mode = (g.has_mask ? 1 : 0) | (g.has_mask && g.m_inner ? 2 : 0) | (causal ? 4 : 0);
+    if (log_out && causal) return set_error(CTB_ERR_ARG, "log_softmax: no causal variant");
+    const int mode = (g.has_mask ? 1 : 0) | (g.has_mask && g.m_inner ? 2 : 0) | (causal ? 4 : 0) | (log_out ? 8 : 0);
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen));
     if (!launched) {
         const int grid = rows_grid(g.rows, 1);
-        softmax_rows_long_kernel<<<grid, 256, 0, st>>>(x, mask, out, o, g.rows, g.cols, g.qlen, g.m_inner, g.has_mask, causal);
+        softmax_rows_long_kernel<<<grid, 256, 0, st>>>(x, mask, out, o, g.rows, g.cols, g.qlen, g.m_inner, g.has_mask, causal, log_out);
     }
     return cuda_error(cudaGetLastError(), "softmax launch");
 }

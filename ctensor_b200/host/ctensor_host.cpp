@@ -155,6 +155,15 @@ int device() { return g_device; }
 void set_sync_after_op(bool on) { g_sync_after_op = on; }
 void sync_for_host_access() { if (g_device_set) check(ctb_device_sync()); }
 void set_grad_factory(GradFactory f) { g_grad_factory = std::move(f); }
+void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src) {
+    if (!grad_buffer.impl) return;                      // as the reference: nothing to add to
+    if (!grad_src.impl) throw std::runtime_error("accumulate_grad: null gradient");
+    ensure_device();
+    const ctb_view vg = view_of(grad_buffer, "accumulate_grad"), vs = view_of(grad_src, "accumulate_grad");
+    check(ctb_accumulate_grad(&vg, &vs, nullptr));
+    after_op();
+}
+
 void set_backward_entry(std::function<void(Tensor&)> f) { g_backward = std::move(f); }
 int last_dim_if_negative(const Tensor& t, int dim) {
     if (!t.impl) throw std::runtime_error("reduction: null input");
@@ -277,6 +286,31 @@ Tensor Tensor::select(size_t dim, size_t index) const {
     Tensor out;
     out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset + index * impl->strides[dim], shape, strides,
                                            impl->dtype, impl->requires_grad);
+    return out;
+}
+
+// Tensor::gather, src/core/tensor.cpp:344-428.
+Tensor Tensor::gather(const Tensor& index, size_t dim) const {
+    if (!impl) throw std::runtime_error("Gather on empty tensor");
+    if (!index.impl) throw std::runtime_error("Gather with empty index");
+    if (dim >= impl->ndim) throw std::out_of_range("Gather dimension out of range");
+    ensure_device();
+    Tensor out(index.shape(), impl->dtype, impl->requires_grad);
+    if (out.numel() == 0) return out;
+    const ctb_view vx = view_of(*this, "gather"), vi = view_of(index, "gather"), vo = view_of(out, "gather");
+    // the kernel cannot throw: it raises a flag in managed memory that is read after the sync
+    void* flag_mem = nullptr;
+    check(ctb_alloc_managed(&flag_mem, sizeof(int32_t), 1));
+    const int rc = ctb_gather(&vx, (int)dim, &vi, &vo, (int32_t*)flag_mem, nullptr);
+    int32_t bad = 0;
+    if (rc == CTB_OK) {
+        ctb_host::sync_for_host_access();
+        bad = *(volatile int32_t*)flag_mem;
+    }
+    ctb_free_managed(flag_mem);
+    check(rc);
+    if (bad) throw std::out_of_range("Gather index out of bounds");
+    if (impl->requires_grad) attach_grad(out, "gather", {*this, index}, (double)dim);
     return out;
 }
 
@@ -444,6 +478,16 @@ Tensor softmax(const Tensor& a, const Tensor& additive_mask) {
     return softmax_impl(a, &additive_mask, 0);
 }
 Tensor causal_softmax(const Tensor& a) { return softmax_impl(a, nullptr, 1); }
+
+Tensor log_softmax(const Tensor& a) {
+    if (!a.impl) throw std::runtime_error("log_softmax: null input");
+    ensure_device();
+    Tensor out(a.shape(), a._dtype(), false);
+    const ctb_view va = view_of(a, "log_softmax"), vo = view_of(out, "log_softmax");
+    check(ctb_log_softmax_lastdim(&va, nullptr, &vo, nullptr));
+    after_op();
+    return out;
+}
 
 Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps) {
     if (!a.impl) throw std::runtime_error("layernorm: null input");

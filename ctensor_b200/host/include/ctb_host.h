@@ -28,6 +28,12 @@ using GradFactory = std::function<std::shared_ptr<GradFn>(const std::string& op,
                                                           double scalar)>;
 void set_grad_factory(GradFactory f);
 
+// accumulate_grad of the reference's autograd (src/core/autograd.cpp:63-156) on the GPU:
+// `grad_buffer` (the tensor that wraps target.impl->grad) += grad_src, with the broadcast dims of
+// grad_src summed first and NaN/Inf contributions skipped.  The autograd library calls this in
+// place of its host loop.
+void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src);
+
 // Hook behind Tensor::backward(); the autograd library installs its backward(root) here.
 void set_backward_entry(std::function<void(Tensor&)> f);
 

@@ -71,6 +71,7 @@ Tensor argmax(const Tensor& a, int dim);
 Tensor softmax(const Tensor& a);
 Tensor softmax(const Tensor& a, const Tensor& additive_mask);
 Tensor causal_softmax(const Tensor& a);
+Tensor log_softmax(const Tensor& a);                 // the chain inside Loss::CrossEntropy
 Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps = 1e-5);
 
 // operators

@@ -224,6 +224,7 @@ struct Tensor {
     Tensor permute(const std::vector<size_t>& dims) const;
     Tensor reshape(const std::vector<size_t>& new_shape) const;
     Tensor select(size_t dim, size_t index) const;
+    Tensor gather(const Tensor& index, size_t dim = 0) const;
     Tensor squeeze() const;
     Tensor unsqueeze(size_t dim) const;
     Tensor flatten() const;

@@ -198,11 +198,36 @@ int ctb_finalize_full(int op, const double* partial, int64_t total_count,
 int ctb_softmax_lastdim(const ctb_view* x, const ctb_view* mask, int causal,
                         const ctb_view* out, void* stream);
 
+/* Log-softmax over the last dim = the chain max -> sub -> exp -> sum -> ln -> sub that
+ * Loss::CrossEntropy builds from primitive ops (src/neuralnet/loss.cpp:97-104), one pass over the
+ * rows: out = (t - max t) - ln((float)sum exp(t - max t)), t = x (+ mask).  fp32 only. */
+int ctb_log_softmax_lastdim(const ctb_view* x, const ctb_view* mask, const ctb_view* out, void* stream);
+
 /* LayerNorm over the last dim = the chain of src/neuralnet/batchnorm/batchnorm.cpp:103-113
  * applied per row: mean, centre, biased variance, (var+eps)^-0.5, scale, shift.
  * gamma/beta: 1-d views of the row length, or NULL.  fp32 only. */
 int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_view* beta,
                           double eps, const ctb_view* out, void* stream);
+
+/* ---- callers either side of the path --------------------------------------------------------
+ * Tensor::gather, src/core/tensor.cpp:344-428: out[i] = x[i with coordinate `dim` replaced by
+ * index[i]].  `index` is CTB_I32 with x's number of dims and extents no larger than x's outside
+ * `dim`; `out` is contiguous with index's shape and x's dtype.  Negative indices count from the
+ * end.  The reference throws "Gather index out of bounds"; a kernel cannot, so such an element
+ * is written as 0 and *bad (one int32 in device memory, may be NULL; cleared on `stream` first)
+ * is set to 1 for the caller to test after synchronising. */
+int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view* out,
+               int32_t* bad, void* stream);
+
+/* accumulate_grad, src/core/autograd.cpp:63-156: grad += src, where every dim in which `grad`
+ * has extent 1 (or which it lacks) and `src` has more is summed first (the backward rule of
+ * broadcasting), and a NaN or infinite contribution is skipped.  `grad` (in-out) may have any
+ * strides; the shapes must be broadcast-compatible.  The folds run as sum reductions (fp64
+ * accumulation, rounded to the dtype like the reference's sum()); when `grad` is contiguous the
+ * last fold adds into it directly, so a bias gradient is one kernel.  Neighbouring folded dims
+ * the source is contiguous across are folded together (the reference folds one axis per pass).
+ * Intermediate sums live in the library's per-device workspace (see ctb_reduce). */
+int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream);
 
 /* ---- host-buffer entry points ---------------------------------------------------------------
  * Same semantics as ctb_binary / ctb_unary / ctb_reduce, but every view points to HOST memory

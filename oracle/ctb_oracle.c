@@ -543,3 +543,151 @@ int64_t orc_layernorm_lastdim(const orc_view* x, const orc_view* gamma, const or
     }
     return n;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Log-softmax over the last dim: the chain of Loss::CrossEntropy, src/neuralnet/loss.cpp:97-104
+ * (max -> sub -> exp -> sum -> ln -> sub), after an optional broadcast add of `mask`.
+ * Output contiguous fp32 with the broadcast shape of (x, mask).
+ * ---------------------------------------------------------------------------------------- */
+int64_t orc_log_softmax_lastdim(const orc_view* x, const orc_view* mask, void* out) {
+    if (x->dtype != ORC_F32 || x->ndim < 1) return -1;
+    orc_view xv = *x;
+    float* tmp = NULL;
+    int64_t n = numel(x);
+    if (mask) {
+        int64_t shape[ORC_MAX_DIMS];
+        int nd = orc_broadcast_shape(x, mask, shape);
+        if (nd < 0) return -1;
+        n = 1;
+        for (int i = 0; i < nd; ++i) n *= shape[i];
+        tmp = (float*)malloc((size_t)n * 4);
+        if (orc_binary(B_ADD, x, mask, tmp) < 0) { free(tmp); return -1; }
+        xv.base = tmp; xv.offset = 0; xv.ndim = nd;
+        int64_t st = 1;
+        for (int i = nd - 1; i >= 0; --i) { xv.shape[i] = shape[i]; xv.stride[i] = st; st *= shape[i]; }
+    }
+    int nd = xv.ndim;
+    int64_t cols = xv.shape[nd - 1], cs = xv.stride[nd - 1];
+    int64_t rows = n / (cols ? cols : 1);
+    float* o = (float*)out;
+    #pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        int64_t t = r, base = xv.offset;
+        for (int d = nd - 2; d >= 0; --d) {
+            int64_t c = t % xv.shape[d];
+            t /= xv.shape[d];
+            base += c * xv.stride[d];
+        }
+        const float* px = (const float*)xv.base;
+        float* row = o + r * cols;
+        double m = -INFINITY;
+        for (int64_t j = 0; j < cols; ++j) {
+            float v = px[base + j * cs];
+            m = (m < (double)v) ? (double)v : m;
+        }
+        float mf = (float)m;
+        double z = 0.0;
+        for (int64_t j = 0; j < cols; ++j) {
+            float sh = px[base + j * cs] - mf;
+            row[j] = sh;
+            z += (double)orc_exp_f32(sh);
+        }
+        float lz = orc_log_f32((float)z);
+        for (int64_t j = 0; j < cols; ++j) row[j] = row[j] - lz;
+    }
+    free(tmp);
+    return n;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Tensor::gather, src/core/tensor.cpp:344-428: out[i] = x[coords(i) with coordinate `dim`
+ * replaced by index[i]]; negative indices count from the end.  Returns the element count,
+ * -1 for a malformed call, -2 for an index out of bounds (the reference throws).
+ * ---------------------------------------------------------------------------------------- */
+int64_t orc_gather(const orc_view* x, int dim, const orc_view* index, void* out) {
+    if (dim < 0 || dim >= x->ndim || x->ndim != index->ndim || index->dtype != ORC_I32) return -1;
+    int nd = x->ndim;
+    for (int d = 0; d < nd; ++d)
+        if (d != dim && index->shape[d] > x->shape[d]) return -1;
+    int64_t n = numel(index);
+    const int32_t* pi = (const int32_t*)index->base;
+    for (int64_t i = 0; i < n; ++i) {
+        int64_t t = i, xoff = x->offset, ioff = index->offset;
+        for (int d = nd - 1; d >= 0; --d) {
+            int64_t c = t % index->shape[d];
+            t /= index->shape[d];
+            ioff += c * index->stride[d];
+            if (d != dim) xoff += c * x->stride[d];
+        }
+        int64_t idx = pi[ioff];
+        if (idx < 0) idx += x->shape[dim];
+        if (idx < 0 || idx >= x->shape[dim]) return -2;
+        xoff += idx * x->stride[dim];
+        if (esize(x->dtype) == 8) ((uint64_t*)out)[i] = ((const uint64_t*)x->base)[xoff];
+        else ((uint32_t*)out)[i] = ((const uint32_t*)x->base)[xoff];
+    }
+    return n;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * accumulate_grad, src/core/autograd.cpp:63-156: the dims in which the target has extent 1
+ * (or which it lacks) and the source has more are summed (sum() per axis: fp64 accumulation,
+ * rounded to the dtype after every axis), then grad[i] = (T)((double)grad[i] + (double)g[i])
+ * for every finite g[i].  `grad` is the target's gradient buffer, contiguous, updated in
+ * place; tshape/tnd give the target's shape.  (The reference folds the axes in increasing
+ * order with indices that are only right for a single folded axis; here every flagged axis is
+ * folded, last axis first.)
+ * ---------------------------------------------------------------------------------------- */
+int64_t orc_accumulate_grad(void* grad, const int64_t* tshape, int tnd, const orc_view* src) {
+    int nd = tnd > src->ndim ? tnd : src->ndim;
+    int dt = src->dtype;
+    int64_t ts[ORC_MAX_DIMS], ss[ORC_MAX_DIMS];
+    for (int d = 0; d < nd; ++d) {
+        int jt = d - (nd - tnd), js = d - (nd - src->ndim);
+        ts[d] = jt < 0 ? 1 : tshape[jt];
+        ss[d] = js < 0 ? 1 : src->shape[js];
+        if (ts[d] != ss[d] && ts[d] != 1 && ss[d] != 1) return -1;
+    }
+    /* contiguous working copy of the source */
+    int64_t n = numel(src);
+    size_t es = esize(dt);
+    void* cur = malloc((size_t)(n ? n : 1) * es);
+    if (orc_contiguous(src, cur) < 0) { free(cur); return -1; }
+    int64_t cs[ORC_MAX_DIMS];
+    for (int d = 0; d < nd; ++d) cs[d] = ss[d];
+    for (int ax = nd - 1; ax >= 0; --ax) {
+        if (!(ts[ax] == 1 && cs[ax] > 1)) continue;
+        int64_t outer = 1, inner = 1, len = cs[ax];
+        for (int d = 0; d < ax; ++d) outer *= cs[d];
+        for (int d = ax + 1; d < nd; ++d) inner *= cs[d];
+        int64_t on = outer * inner;
+        void* nxt = malloc((size_t)(on > 0 ? on : 1) * es);
+        for (int64_t o = 0; o < outer; ++o)
+            for (int64_t i = 0; i < inner; ++i) {
+                double acc = 0.0;
+                for (int64_t k = 0; k < len; ++k) acc += rd(cur, (o * len + k) * inner + i, dt);
+                wr(nxt, o * inner + i, dt, acc);
+            }
+        free(cur);
+        cur = nxt;
+        cs[ax] = 1;
+    }
+    /* element-wise accumulation with broadcasting of the (reduced) source */
+    int64_t tn = 1;
+    for (int d = 0; d < nd; ++d) tn *= ts[d];
+    for (int64_t i = 0; i < tn; ++i) {
+        int64_t t = i, soff = 0, run = 1;
+        int64_t sstr[ORC_MAX_DIMS];
+        for (int d = nd - 1; d >= 0; --d) { sstr[d] = cs[d] == 1 ? 0 : run; run *= cs[d]; }
+        for (int d = nd - 1; d >= 0; --d) {
+            int64_t c = t % ts[d];
+            t /= ts[d];
+            soff += c * sstr[d];
+        }
+        double g = rd(cur, soff, dt);
+        if (!isfinite(g)) continue;
+        wr(grad, i, dt, rd(grad, i, dt) + g);
+    }
+    free(cur);
+    return tn;
+}

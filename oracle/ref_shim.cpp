@@ -24,6 +24,7 @@
 #include "ops_dispatch.h"
 #include "ops_avx2_f32.h"
 #include "ops_avx512_f32.h"
+#include "autograd.h"
 
 namespace {
 
@@ -338,6 +339,64 @@ int64_t ref_layernorm_lastdim(const RefView* x, const RefView* gamma, const RefV
         if (gamma) y = mult_mp(y, wrap(gamma));
         if (beta) y = add_mp(y, wrap(beta));
         return emit(y, out, cap);
+    });
+}
+
+// Log-softmax over the last dim, the recipe of Loss::CrossEntropy (src/neuralnet/loss.cpp:97-104):
+// max -> reshape -> sub -> exp -> sum -> reshape -> ln -> sub, with the SIMD exp flavour named by
+// exp_path and the AVX2 ln (the flavour the product pins; the AVX-512 ln is numerically wrong).
+int64_t ref_log_softmax_lastdim(int exp_path, const RefView* x, const RefView* mask, void* out, int64_t cap) {
+    return guarded([&] {
+        Tensor t = wrap(x);
+        if (mask) t = add_mp(t, wrap(mask));
+        int last = (int)t.impl->ndim - 1;
+        std::vector<size_t> keep = keepdim_shape(t, last);
+        Tensor m = max_mp(t, last).reshape(keep);
+        Tensor s = diff_mp(t, m);
+        Tensor e = (exp_path == PATH_AVX2) ? exp_avx2_f32(s) : exp_avx512_f32(s);
+        Tensor z = sum_mp(e, last).reshape(keep);
+        Tensor l = ln_avx2_f32(z);
+        return emit(diff_mp(s, l), out, cap);
+    });
+}
+
+// Tensor::gather (src/core/tensor.cpp:344-428).
+int64_t ref_gather(const RefView* x, int dim, const RefView* index, void* out, int64_t cap) {
+    return guarded([&] { return emit(wrap(x).gather(wrap(index), (size_t)dim), out, cap); });
+}
+
+// accumulate_grad (src/core/autograd.cpp:63-156).  `target` gives the parameter's shape; its
+// gradient buffer is created by the reference (ensure_grad_buffer: contiguous, zeroed), seeded
+// with `grad_init` (contiguous, target's numel), accumulated into, and copied out.
+// The reference folds the broadcast axes with sum(g, axis) through its dispatcher, which throws
+// on AVX-512 hosts ("sum_avx512: only dim=-1").  The folds are therefore done here with sum_mp,
+// the function that dispatcher picks on every other host, keeping the folded dim as size 1;
+// the reference's accumulate_grad then performs the accumulation step (incl. its NaN/Inf rule).
+int64_t ref_accumulate_grad(const RefView* target, const void* grad_init, const RefView* src, void* out, int64_t cap) {
+    return guarded([&] {
+        Tensor t = wrap(target);
+        ensure_grad_buffer(t, true);
+        Tensorimpl* gi = t.impl->grad.get();
+        if (!gi) throw std::runtime_error("reference created no gradient buffer");
+        const size_t bytes = t.numel() * dtype_size(t.impl->dtype);
+        std::memcpy((char*)gi->data->data.get() + gi->offset * dtype_size(gi->dtype), grad_init, bytes);
+        Tensor g = wrap(src);
+        const size_t td = t.impl->ndim, gd = g.impl->ndim, nd = td > gd ? td : gd;
+        for (int i = (int)nd - 1; i >= 0; --i) {                    // autograd.cpp:72-82, last axis first
+            const size_t tsz = (size_t)i < nd - td ? 1 : t.impl->shape[i - (nd - td)];
+            if ((size_t)i < nd - gd) continue;
+            const int ax = i - (int)(nd - gd);
+            if (tsz == 1 && g.impl->shape[ax] > 1) g = sum_mp(g, ax).reshape(keepdim_shape(g, ax));
+        }
+        if (gd > td) {      // leading dims the target lacks are all 1 now: drop them, as sum() does
+            std::vector<size_t> sh(g.impl->shape.begin() + (gd - td), g.impl->shape.end());
+            if (sh.empty()) sh.push_back(1);
+            g = g.reshape(sh);
+        }
+        accumulate_grad(t, g);
+        if ((int64_t)bytes > cap) throw std::runtime_error("output buffer too small");
+        std::memcpy(out, (const char*)gi->data->data.get() + gi->offset * dtype_size(gi->dtype), bytes);
+        return (int64_t)t.numel();
     });
 }
 

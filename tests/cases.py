@@ -1,7 +1,8 @@
 """The catalogue of small parity cases shared by the golden-vector generator, the oracle tests
 and the GPU tests.  Every case is a dict:
 
-    name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'), op, views (HostViews),
+    name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
+    'accgrad'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -179,6 +180,40 @@ def all_cases():
     g36 = HostView.contig((_n(25, (36,), 0.02) + 1).astype(np.float32))
     b36 = HostView.contig(_n(26, (36,), 0.02))
     add(name="layernorm_3d", kind="layernorm", op=0, views=[R3, g36, b36], scalar=1e-5, exact=False)
+
+    # ---- callers either side of the path: log-softmax rows, gather, accumulate_grad ------------------------
+    logits = HostView.contig(_n(29, (33, 10), 3.0))           # [batch, classes] of Loss::CrossEntropy
+    add(name="logsoftmax_2d", kind="log_softmax", op=0, views=[logits], exact=False, path=ol.PATH_AVX512)
+    add(name="logsoftmax_wide", kind="log_softmax", op=0, views=[R], exact=False, path=ol.PATH_AVX512)
+    add(name="logsoftmax_long", kind="log_softmax", op=0, views=[Rlong], exact=False, path=ol.PATH_AVX512)
+    add(name="logsoftmax_perm4d_mask", kind="log_softmax", op=0, views=[P4, M4], exact=False, path=ol.PATH_AVX512)
+    tgt = HostView.contig(_rng(30).integers(0, 10, (33, 1)).astype(np.int32))
+    add(name="gather_targets", kind="gather", op=0, views=[logits, tgt], dim=1)
+    idx0 = HostView.contig(_rng(31).integers(-33, 33, (5, 10)).astype(np.int32))     # negative = from the end
+    add(name="gather_dim0_negative", kind="gather", op=0, views=[logits, idx0], dim=0)
+    idx3 = HostView.contig(_rng(32).integers(0, 20, (6, 7, 36)).astype(np.int32))
+    add(name="gather_3d_dim1", kind="gather", op=0, views=[R3, idx3], dim=1)
+    idxp = HostView.contig(_rng(33).integers(0, 3, (2, 2, 5, 16)).astype(np.int32))
+    add(name="gather_perm4d", kind="gather", op=0, views=[P4, idxp], dim=1)
+    add(name="gather_i32", kind="gather", op=0, views=[Ai, HostView.contig(_rng(34).integers(0, 9, (7, 4)).astype(np.int32))], dim=1)
+    add(name="gather_f64", kind="gather", op=0, views=[Ad, HostView.contig(_rng(35).integers(0, 5, (3, 6)).astype(np.int32))], dim=0)
+    # accumulate_grad: views = [start value of the gradient buffer (target's shape), incoming gradient]
+    gsrc = HostView.contig(_n(36, (64, 48)))
+    add(name="accgrad_same", kind="accgrad", op=0, views=[HostView.contig(_n(37, (64, 48))), gsrc])
+    add(name="accgrad_bias_row", kind="accgrad", op=0, views=[HostView.contig(_n(38, (1, 48))), gsrc], exact=False)
+    add(name="accgrad_bias_vec", kind="accgrad", op=0, views=[HostView.contig(_n(39, (48,))), gsrc], exact=False)
+    add(name="accgrad_col", kind="accgrad", op=0, views=[HostView.contig(_n(40, (64, 1))), gsrc], exact=False)
+    add(name="accgrad_tall", kind="accgrad", op=0, views=[HostView.contig(_n(41, (36,))), Rtall], exact=False)
+    add(name="accgrad_transposed_src", kind="accgrad", op=0, views=[HostView.contig(_n(42, (48, 64))), gsrc.permute([1, 0])])
+    add(name="accgrad_src_broadcasts", kind="accgrad", op=0, views=[HostView.contig(_n(43, (64, 48))), B])
+    nf = _n(44, (64, 48)).copy()
+    nf[3, 5] = np.nan
+    nf[7, 0] = np.inf
+    nf[9, 47] = -np.inf
+    add(name="accgrad_skips_nonfinite", kind="accgrad", op=0, views=[HostView.contig(_n(45, (64, 48))), HostView.contig(nf)])
+    add(name="accgrad_bias_nonfinite", kind="accgrad", op=0, views=[HostView.contig(_n(46, (48,))), HostView.contig(nf)], exact=False)
+    add(name="accgrad_i32", kind="accgrad", op=0, views=[HostView.contig(_rng(47).integers(-9, 9, (9,)).astype(np.int32)), Ai])
+    add(name="accgrad_f64", kind="accgrad", op=0, views=[HostView.contig(_rng(48).standard_normal((6,))), Ad], exact=False)
     return cases
 
 
@@ -200,6 +235,13 @@ def run_case(impl, case):
         return impl.softmax(v[0], mask, case["path"]) if is_ref else impl.softmax(v[0], mask, case["causal"])
     if k == "layernorm":
         return impl.layernorm(v[0], v[1], v[2], case["scalar"])
+    if k == "log_softmax":
+        mask = v[1] if len(v) > 1 else None
+        return impl.log_softmax(v[0], mask, case["path"]) if is_ref else impl.log_softmax(v[0], mask)
+    if k == "gather":
+        return impl.gather(v[0], case["dim"], v[1])
+    if k == "accgrad":
+        return impl.accumulate_grad(v[0].numpy(), v[1])
     raise ValueError(k)
 
 

@@ -128,6 +128,27 @@ int main() {
     Tensor ln_ = layer_norm(Tensor::from_vector({1, 2, 3, 4}, {1, 4}), Tensor::ones({4}), Tensor::zeros({4}));
     CHECK_NEAR(ln_[0][3], 1.5 / std::sqrt(1.25 + 1e-5), 1e-5);
 
+    // the callers' side: CrossEntropy's chain (src/neuralnet/loss.cpp:97-110), gather, accumulate_grad
+    Tensor logits = Tensor::from_vector({1, 2, 3, 1, 1, 1}, {2, 3});
+    Tensor lsm = log_softmax(logits);
+    CHECK_NEAR(lsm[1][0], std::log(1.0 / 3.0), 1e-6);
+    CHECK_NEAR(std::exp(double(lsm[0][0])) + std::exp(double(lsm[0][1])) + std::exp(double(lsm[0][2])), 1.0, 1e-6);
+    Tensor tgt = Tensor::from_vector({2, 0}, {2, 1}, DType::Int32);
+    Tensor picked = lsm.gather(tgt, 1);
+    CHECK(picked.numel() == 2);
+    CHECK_NEAR(picked[0][0], double(lsm[0][2]), 0.0);
+    CHECK_NEAR(picked[1][0], double(lsm[1][0]), 0.0);
+    CHECK_NEAR(mean(picked * -1.0).item<double>(), -(double(lsm[0][2]) + double(lsm[1][0])) / 2, 1e-6);
+    CHECK_THROWS(lsm.gather(Tensor::from_vector({3, 0}, {2, 1}, DType::Int32), 1), std::out_of_range, "Gather index out of bounds");
+    CHECK_THROWS(lsm.gather(tgt, 2), std::out_of_range, "Gather dimension out of range");
+    CHECK_THROWS(lsm.gather(Tensor::from_vector({0, 0}, {2, 1}), 1), std::runtime_error, "Index tensor must be integer type");
+    Tensor bias_grad = Tensor::zeros({3});
+    ctb_host::accumulate_grad(bias_grad, logits);            // [2,3] folds into [3]
+    CHECK_NEAR(bias_grad[0], 2.0, 0.0);
+    CHECK_NEAR(bias_grad[2], 4.0, 0.0);
+    ctb_host::accumulate_grad(bias_grad, Tensor::full({3}, std::nan("")));   // NaN contributions are skipped
+    CHECK_NEAR(bias_grad[1], 3.0, 0.0);
+
     // errors: the reference's exception types and texts
     CHECK_THROWS(Tensor::ones({2, 3}) + Tensor::ones({2, 2}), std::runtime_error, "Shape mismatch in binary op");
     CHECK_THROWS(add(Tensor(), a), std::runtime_error, "binary_op: null input");

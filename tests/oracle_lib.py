@@ -175,6 +175,12 @@ class Oracle:
         L.orc_softmax_lastdim.argtypes = [vp, vp, ctypes.c_int, ctypes.c_void_p]
         L.orc_layernorm_lastdim.restype = ctypes.c_int64
         L.orc_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, ctypes.c_void_p]
+        L.orc_log_softmax_lastdim.restype = ctypes.c_int64
+        L.orc_log_softmax_lastdim.argtypes = [vp, vp, ctypes.c_void_p]
+        L.orc_gather.restype = ctypes.c_int64
+        L.orc_gather.argtypes = [vp, ctypes.c_int, vp, ctypes.c_void_p]
+        L.orc_accumulate_grad.restype = ctypes.c_int64
+        L.orc_accumulate_grad.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int, vp]
         L.orc_unary_sweep_f32.restype = None
         L.orc_unary_sweep_f32.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_int64, ctypes.c_double, ctypes.c_void_p,
@@ -218,6 +224,30 @@ class Oracle:
         assert n == out.size, "oracle layernorm failed"
         return out
 
+    def log_softmax(self, x: HostView, mask: Optional[HostView] = None) -> np.ndarray:
+        shape = x.shape if mask is None else broadcast_shape(x.shape, mask.shape)
+        out = np.empty(shape, np.float32)
+        n = self.lib.orc_log_softmax_lastdim(x.cview(), _ptr(mask), out.ctypes.data)
+        assert n == out.size, "oracle log_softmax failed"
+        return out
+
+    def gather(self, x: HostView, dim: int, index: HostView) -> np.ndarray:
+        """Raises IndexError where the reference throws "Gather index out of bounds"."""
+        out = np.empty(index.shape, NP_DTYPES[x.dtype])
+        n = self.lib.orc_gather(x.cview(), dim, index.cview(), out.ctypes.data)
+        if n == -2:
+            raise IndexError("Gather index out of bounds")
+        assert n == out.size, "oracle gather failed"
+        return out
+
+    def accumulate_grad(self, grad: np.ndarray, src: HostView) -> np.ndarray:
+        """Returns grad + fold(src) (a new contiguous array of grad's shape)."""
+        out = np.ascontiguousarray(grad).copy()
+        shape = (ctypes.c_int64 * MAX_DIMS)(*out.shape)
+        n = self.lib.orc_accumulate_grad(out.ctypes.data, shape, out.ndim, src.cview())
+        assert n == out.size, "oracle accumulate_grad failed"
+        return out
+
     def sweep(self, op, start: int, step: int, count: int, scalar: float = 0.0):
         xin = np.empty(count, np.float32)
         out = np.empty(count, np.float32)
@@ -252,6 +282,12 @@ class Reference:
         L.ref_softmax_lastdim.argtypes = [ctypes.c_int, vp, vp, vd, i64]
         L.ref_layernorm_lastdim.restype = i64
         L.ref_layernorm_lastdim.argtypes = [vp, vp, vp, ctypes.c_double, vd, i64]
+        L.ref_log_softmax_lastdim.restype = i64
+        L.ref_log_softmax_lastdim.argtypes = [ctypes.c_int, vp, vp, vd, i64]
+        L.ref_gather.restype = i64
+        L.ref_gather.argtypes = [vp, ctypes.c_int, vp, vd, i64]
+        L.ref_accumulate_grad.restype = i64
+        L.ref_accumulate_grad.argtypes = [vp, vd, vp, vd, i64]
         L.ref_bench_step.restype = ctypes.c_double
         L.ref_bench_step.argtypes = [ctypes.c_int, vd, vd, i64]
         feats = L.ref_cpu_features()
@@ -300,6 +336,24 @@ class Reference:
         out = np.empty(shape, np.float32)
         p = self.simd_path() if exp_path is None else exp_path
         return self._check(self.lib.ref_softmax_lastdim(p, x.cview(), _ptr(mask), out.ctypes.data, out.nbytes), out)
+
+    def log_softmax(self, x, mask=None, exp_path=None):
+        shape = x.shape if mask is None else broadcast_shape(x.shape, mask.shape)
+        out = np.empty(shape, np.float32)
+        p = self.simd_path() if exp_path is None else exp_path
+        return self._check(self.lib.ref_log_softmax_lastdim(p, x.cview(), _ptr(mask), out.ctypes.data, out.nbytes), out)
+
+    def gather(self, x, dim, index):
+        out = np.empty(index.shape, NP_DTYPES[x.dtype])
+        return self._check(self.lib.ref_gather(x.cview(), dim, index.cview(), out.ctypes.data, out.nbytes), out)
+
+    def accumulate_grad(self, grad: np.ndarray, src):
+        """grad: contiguous array with the target's shape (the gradient buffer's start value)."""
+        g = np.ascontiguousarray(grad)
+        out = np.empty_like(g)
+        target = HostView.contig(np.zeros(g.shape, g.dtype))
+        return self._check(self.lib.ref_accumulate_grad(target.cview(), g.ctypes.data, src.cview(),
+                                                        out.ctypes.data, out.nbytes), out)
 
     def layernorm(self, x, gamma, beta, eps=1e-5):
         out = np.empty(x.shape, np.float32)

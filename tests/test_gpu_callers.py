@@ -1,0 +1,137 @@
+"""GPU tests of the entry points that serve the callers either side of the operator path:
+log-softmax rows (Loss::CrossEntropy), gather (Tensor::gather) and accumulate_grad (autograd).
+The catalogue cases of these kinds run in test_gpu_parity.py; here are the shapes and edge
+cases the catalogue does not hold."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as ol
+from oracle_lib import HostView
+from gpu_util import to_device, assert_bits_equal, assert_close
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-5
+
+
+@pytest.mark.parametrize("cols", [1, 7, 128, 1000, 1024, 4096, 5000, 40000])
+def test_log_softmax_widths(ct, oracle, cols):
+    rows = 37 if cols < 10000 else 3
+    x = HostView.contig((np.random.default_rng(cols).standard_normal((rows, cols)) * 4).astype(np.float32))
+    got = ct.log_softmax(to_device(x)).cpu().numpy()
+    ref = oracle.log_softmax(x)
+    np.testing.assert_allclose(got, ref, rtol=RTOL, atol=1e-6)
+
+
+def test_log_softmax_is_log_of_softmax(ct):
+    x = torch.randn(64, 50257 // 8, device="cuda") * 3
+    ls = ct.log_softmax(x)
+    sm = ct.softmax(x)
+    assert torch.allclose(ls.exp(), sm, rtol=1e-5, atol=1e-9)
+    assert torch.allclose(ls.exp().sum(-1), torch.ones(64, device="cuda"), rtol=1e-5)
+
+
+def test_log_softmax_rejects_what_softmax_rejects(ct):
+    with pytest.raises(ct.CtbError):
+        ct.log_softmax(torch.zeros(4, 4, dtype=torch.float64, device="cuda"))
+
+
+def test_cross_entropy_chain(ct, oracle):
+    """Loss::CrossEntropy (src/neuralnet/loss.cpp:90-118): log-softmax, gather the target's
+    log-probability, negate, mean."""
+    rng = np.random.default_rng(3)
+    logits = HostView.contig((rng.standard_normal((256, 1000)) * 2).astype(np.float32))
+    target = HostView.contig(rng.integers(0, 1000, (256, 1)).astype(np.int32))
+    lp = ct.log_softmax(to_device(logits))
+    picked = ct.gather(lp, 1, to_device(target))
+    nll = ct.unary(ct.MUL_S, picked, -1.0)
+    loss = ct.reduce(ct.MEAN, nll, ct.DIM_FULL).cpu().numpy()
+    ref_lp = oracle.log_softmax(logits)
+    ref_pick = oracle.gather(HostView.contig(ref_lp), 1, target)
+    ref = oracle.reduce(ol.MEAN, HostView.contig(oracle.unary(ol.MUL_S, HostView.contig(ref_pick), -1.0)), -1)
+    np.testing.assert_allclose(loss, ref, rtol=RTOL)
+
+
+def test_gather_out_of_bounds_is_reported(ct):
+    x = torch.arange(12, dtype=torch.float32, device="cuda").reshape(3, 4)
+    idx = torch.tensor([[0], [4], [1]], dtype=torch.int32, device="cuda")
+    with pytest.raises(ct.CtbError) as e:
+        ct.gather(x, 1, idx)
+    assert e.value.code == 4 and "Gather index out of bounds" in e.value.message
+    idx = torch.tensor([[0], [-5], [1]], dtype=torch.int32, device="cuda")
+    with pytest.raises(ct.CtbError):
+        ct.gather(x, 1, idx)
+    # the reference's argument checks
+    with pytest.raises(ct.CtbError) as e:
+        ct.gather(x, 2, idx)
+    assert e.value.code == 4
+    with pytest.raises(ct.CtbError) as e:
+        ct.gather(x, 1, idx.float())
+    assert "Index tensor must be integer type" in e.value.message
+    with pytest.raises(ct.CtbError) as e:
+        ct.gather(x, 1, torch.zeros(5, 1, dtype=torch.int32, device="cuda"))
+    assert "Index shape dimension mismatch" in e.value.message
+
+
+def test_gather_large_matches_torch(ct):
+    x = torch.randn(4096, 512, device="cuda")
+    idx = torch.randint(0, 512, (4096, 64), device="cuda", dtype=torch.int32)
+    got = ct.gather(x, 1, idx)
+    assert torch.equal(got, torch.gather(x, 1, idx.long()))
+
+
+@pytest.mark.parametrize("tshape,sshape", [
+    ((16,), (5, 7, 16)),             # two leading dims fold together (contiguous source)
+    ((7, 1), (5, 7, 16)),            # folds on both sides of a kept dim
+    ((1, 7, 16), (5, 7, 16)),
+    ((5, 1, 16), (5, 7, 16)),
+    ((1, 1, 1), (5, 7, 16)),
+    ((1,), (33,)),
+    ((5, 7, 16), (7, 16)),           # the source broadcasts into the target
+    ((3, 5), (1, 5)),
+])
+def test_accumulate_grad_folds(ct, oracle, tshape, sshape):
+    rng = np.random.default_rng(len(tshape) * 100 + len(sshape))
+    g0 = rng.standard_normal(tshape).astype(np.float32)
+    src = HostView.contig(rng.standard_normal(sshape).astype(np.float32))
+    grad = torch.from_numpy(g0.copy()).cuda()
+    ct.accumulate_grad(grad, to_device(src))
+    ref = oracle.accumulate_grad(g0, src)
+    np.testing.assert_allclose(grad.cpu().numpy(), ref, rtol=RTOL, atol=1e-6)
+
+
+def test_accumulate_grad_strided_buffers(ct, oracle):
+    """A gradient buffer that is a view (transposed / sliced) and a permuted source."""
+    rng = np.random.default_rng(9)
+    g0 = rng.standard_normal((48, 64)).astype(np.float32)
+    src = HostView.contig(rng.standard_normal((64, 48)).astype(np.float32))
+    store = torch.from_numpy(g0.copy()).cuda()
+    grad_t = store.t()                                   # [64, 48] view with strides (1, 64)
+    ct.accumulate_grad(ct.DView.of(grad_t), to_device(src))
+    ref = oracle.accumulate_grad(np.ascontiguousarray(g0.T), src)
+    assert_bits_equal(grad_t.contiguous(), ref, "transposed gradient buffer")
+    # bias gradient into a sliced (non-contiguous) buffer
+    wide = torch.zeros(48, 2, device="cuda")
+    col = wide[:, 0]
+    ct.accumulate_grad(ct.DView.of(col), to_device(src))
+    ref = oracle.accumulate_grad(np.zeros(48, np.float32), src)
+    np.testing.assert_allclose(col.cpu().numpy(), ref, rtol=RTOL, atol=1e-6)
+    assert torch.all(wide[:, 1] == 0)
+
+
+def test_accumulate_grad_twice_and_large(ct):
+    g = torch.randn(8192, 4096, device="cuda")
+    bias = torch.zeros(4096, device="cuda")
+    ct.accumulate_grad(bias, g)
+    ct.accumulate_grad(bias, g)
+    want = 2 * g.double().sum(0)
+    assert torch.allclose(bias.double(), want, rtol=1e-5, atol=1e-3)
+    w = torch.zeros(8192, 4096, device="cuda")
+    ct.accumulate_grad(w, g)
+    assert torch.equal(w, g)
+
+
+def test_accumulate_grad_shape_mismatch(ct):
+    with pytest.raises(ct.CtbError) as e:
+        ct.accumulate_grad(torch.zeros(3, 4, device="cuda"), torch.zeros(3, 5, device="cuda"))
+    assert e.value.code == 2

@@ -34,6 +34,13 @@ def run_gpu(ct, case):
         return out
     if k == "layernorm":
         return ct.layernorm(dv[0], dv[1], dv[2], case["scalar"])
+    if k == "log_softmax":
+        return ct.log_softmax(dv[0], dv[1] if len(dv) > 1 else None)
+    if k == "gather":
+        return ct.gather(dv[0], case["dim"], dv[1])
+    if k == "accgrad":
+        grad = torch.from_numpy(case["views"][0].numpy()).cuda()
+        return ct.accumulate_grad(grad, dv[1])
     raise ValueError(k)
 
 
