@@ -43,7 +43,7 @@ EXPORTED_SYMBOLS = [
     "ctb_binary", "ctb_unary", "ctb_copy_strided", "ctb_reduce", "ctb_reduce_workspace_bytes",
     "ctb_reduce_ws", "ctb_reduce_dim_noalloc", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
-    "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad",
+    "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
 ]
 
 
@@ -113,6 +113,8 @@ def lib() -> ctypes.CDLL:
     L.ctb_log_softmax_lastdim.argtypes = [vp, vp, vp, vd]
     L.ctb_gather.argtypes = [vp, i32, vp, vp, vd, vd]
     L.ctb_accumulate_grad.argtypes = [vp, vp, vd]
+    L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
+    L.ctb_adam_step.argtypes = [vp, vp, vd, vd] + [ctypes.c_double] * 4 + [i32, ctypes.c_double, i32, vd]
     L.ctb_binary_host.argtypes = [i32, vp, vp, vp, i32]
     L.ctb_unary_host.argtypes = [i32, vp, ctypes.c_double, vp, i32]
     L.ctb_reduce_host.argtypes = [i32, vp, i32, vp, i32]
@@ -351,6 +353,26 @@ def accumulate_grad(grad, src):
     with _device_guard(g):
         check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
     return grad
+
+
+def sgd_step(param, grad, lr: float):
+    """param -= lr * grad in place (SGD::step of the reference)."""
+    p, g = _as_dview(param), _as_dview(grad)
+    with _device_guard(p):
+        check(lib().ctb_sgd_step(p.cview(), g.cview(), float(lr), _stream_ptr(p)))
+    return param
+
+
+def adam_step(param, grad, m, v, lr: float, step: int, beta1: float = 0.9, beta2: float = 0.999,
+              eps: float = 1e-8, weight_decay=None):
+    """One Adam step in place (AdamW when ``weight_decay`` is given); m, v: fp32 CUDA tensors."""
+    p, g = _as_dview(param), _as_dview(grad)
+    with _device_guard(p):
+        check(lib().ctb_adam_step(p.cview(), g.cview(), m.data_ptr(), v.data_ptr(), float(lr), float(beta1),
+                                  float(beta2), float(eps), int(step),
+                                  0.0 if weight_decay is None else float(weight_decay),
+                                  0 if weight_decay is None else 1, _stream_ptr(p)))
+    return param
 
 
 def layernorm(x, gamma=None, beta=None, eps: float = 1e-5, out=None):

@@ -776,6 +776,35 @@ int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream)
     return launch_accumulate_strided(grad->dtype, nd, tshape, tstride, cur.stride, elem_ptr_mut(grad), elem_ptr(&cur), st);
 }
 
+// ---- optimizer steps ---------------------------------------------------------------------------------
+static int optimizer_operands(const ctb_view* param, const ctb_view* grad, const char* who) {
+    int rc;
+    if ((rc = check_view(param, "optimizer step: null parameter", who))) return rc;
+    if ((rc = check_view(grad, "optimizer step: null gradient", who))) return rc;
+    if (param->dtype != grad->dtype) return set_error(CTB_ERR_DTYPE, "%s: parameter and gradient dtypes differ", who);
+    if (view_numel(param) != view_numel(grad)) return set_error(CTB_ERR_SHAPE, "%s: parameter and gradient sizes differ", who);
+    // the reference walks raw storage linearly (train_utils.h:62-68): only contiguous buffers mean the same here
+    if (!view_contiguous(param) || !view_contiguous(grad)) return set_error(CTB_ERR_SHAPE, "%s: parameter and gradient must be contiguous", who);
+    return CTB_OK;
+}
+
+int ctb_sgd_step(const ctb_view* param, const ctb_view* grad, double lr, void* stream) {
+    int rc;
+    if ((rc = optimizer_operands(param, grad, "sgd_step"))) return rc;
+    return launch_sgd(param->dtype, elem_ptr_mut(param), elem_ptr(grad), view_numel(param), lr, (cudaStream_t)stream);
+}
+
+int ctb_adam_step(const ctb_view* param, const ctb_view* grad, float* m, float* v, double lr, double beta1,
+                  double beta2, double eps, int step, double weight_decay, int decoupled_decay, void* stream) {
+    int rc;
+    if ((rc = optimizer_operands(param, grad, "adam_step"))) return rc;
+    if (param->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "adam_step: only Float32 parameters are updated");
+    if (!m || !v) return set_error(CTB_ERR_NULL, "adam_step: null moment buffer");
+    if (step < 1) return set_error(CTB_ERR_ARG, "adam_step: the step count starts at 1");
+    return launch_adam((float*)elem_ptr_mut(param), (const float*)elem_ptr(grad), m, v, view_numel(param), lr, beta1,
+                       beta2, eps, step, weight_decay, decoupled_decay, (cudaStream_t)stream);
+}
+
 // ---- host-buffer entry points --------------------------------------------------------------------------
 static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* b, double scalar,
                             const ctb_view* out, int device) {

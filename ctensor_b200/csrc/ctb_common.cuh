@@ -157,5 +157,11 @@ int launch_gather(int elem_bytes, int ndim, const int64_t* ishape, const int64_t
 int launch_accumulate_strided(int dtype, int ndim, const int64_t* shape, const int64_t* gstride,
                               const int64_t* sstride, void* grad, const void* src, cudaStream_t stream);
 
+// In-place optimizer steps on contiguous buffers of n elements.
+int launch_sgd(int dtype, void* param, const void* grad, int64_t n, double lr, cudaStream_t stream);
+int launch_adam(float* param, const float* grad, float* m, float* v, int64_t n, double lr, double beta1,
+                double beta2, double eps, int step, double weight_decay, int decoupled_decay,
+                cudaStream_t stream);
+
 struct ReducePlan;   // ctb_reduce.cuh
 }  // namespace ctb

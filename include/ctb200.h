@@ -229,6 +229,18 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
  * Intermediate sums live in the library's per-device workspace (see ctb_reduce). */
 int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream);
 
+/* Optimizer steps, src/neuralnet/train_utils.h:50-188, in place on contiguous buffers.
+ * ctb_sgd_step: param -= (float)lr * grad for CTB_F32 (:66-68); (T)(param - lr*grad) in double
+ * for the other dtypes (:72-76).
+ * ctb_adam_step (CTB_F32 only, like the reference, which skips other dtypes): the update of
+ * Adam (:113-127) or, with decoupled_decay != 0, of AdamW (:176-184, which first does
+ * param -= (float)(lr*weight_decay*param)).  `m`, `v`: the moment vectors (device memory,
+ * param's element count, zero before the first step); `step` is the 1-based step count t. */
+int ctb_sgd_step(const ctb_view* param, const ctb_view* grad, double lr, void* stream);
+int ctb_adam_step(const ctb_view* param, const ctb_view* grad, float* m, float* v, double lr,
+                  double beta1, double beta2, double eps, int step, double weight_decay,
+                  int decoupled_decay, void* stream);
+
 /* ---- host-buffer entry points ---------------------------------------------------------------
  * Same semantics as ctb_binary / ctb_unary / ctb_reduce, but every view points to HOST memory
  * (pinned memory gives full PCIe speed).  Inputs are staged to `device`, the kernel runs there

@@ -52,7 +52,9 @@ awk '
 ' "$REF/src/core/tensor.cpp" > "$TMP/src/core/tensor.cpp"
 
 S="$TMP/src"
-INC="-I$S -I$S/core -I$S/cpu/AVX2 -I$S/cpu/AVX512"
+# the reference tree itself comes last: it only supplies header-only callers (the optimizers of
+# src/neuralnet/train_utils.h); "core/tensor.h" still resolves to the patched copy above
+INC="-I$S -I$S/core -I$S/cpu/AVX2 -I$S/cpu/AVX512 -I$REF/src"
 CXX="${REF_CXX:-g++}"   # the PATH g++ (13.3 in this image), not $CXX
 STD="-std=gnu++20 -fPIC -w"
 CORE_FLAGS="-O2 -fopenmp"

@@ -691,3 +691,32 @@ int64_t orc_accumulate_grad(void* grad, const int64_t* tshape, int tnd, const or
     free(cur);
     return tn;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Optimizer steps, src/neuralnet/train_utils.h:50-188, in place on contiguous buffers.
+ * SGD: fp32 fast path p -= (float)lr*g (:66-68), other dtypes through double (:72-76).
+ * Adam / AdamW (fp32): :113-127 / :176-184.  `step` is the 1-based step count.
+ * ---------------------------------------------------------------------------------------- */
+void orc_sgd_step(int dtype, void* p, const void* g, int64_t n, double lr) {
+    if (dtype == ORC_F32) {
+        float* pp = (float*)p;
+        const float* gg = (const float*)g;
+        for (int64_t i = 0; i < n; ++i) pp[i] -= (float)lr * gg[i];
+    } else {
+        for (int64_t i = 0; i < n; ++i) wr(p, i, dtype, rd(p, i, dtype) - lr * rd(g, i, dtype));
+    }
+}
+
+void orc_adam_step(float* theta, const float* grad, float* m, float* v, int64_t n, double lr,
+                   double beta1, double beta2, double eps, int step, double weight_decay,
+                   int decoupled_decay) {
+    double bc1 = 1.0 - pow(beta1, step), bc2 = 1.0 - pow(beta2, step);
+    float lr_t = (float)(lr * sqrt(bc2) / bc1);
+    for (int64_t i = 0; i < n; ++i) {
+        float g = grad[i];
+        if (decoupled_decay) theta[i] -= (float)(lr * weight_decay * theta[i]);
+        m[i] = (float)beta1 * m[i] + (1.0f - (float)beta1) * g;
+        v[i] = (float)beta2 * v[i] + (1.0f - (float)beta2) * g * g;
+        theta[i] -= lr_t * m[i] / (sqrtf(v[i]) + (float)eps);
+    }
+}

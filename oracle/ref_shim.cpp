@@ -25,6 +25,8 @@
 #include "ops_avx2_f32.h"
 #include "ops_avx512_f32.h"
 #include "autograd.h"
+#include "neuralnet/loss.h"          // declares Loss, which train_utils.h uses without including it
+#include "neuralnet/train_utils.h"   // header-only optimizers (SGD, Adam, AdamW)
 
 namespace {
 
@@ -397,6 +399,31 @@ int64_t ref_accumulate_grad(const RefView* target, const void* grad_init, const 
         if ((int64_t)bytes > cap) throw std::runtime_error("output buffer too small");
         std::memcpy(out, (const char*)gi->data->data.get() + gi->offset * dtype_size(gi->dtype), bytes);
         return (int64_t)t.numel();
+    });
+}
+
+// Optimizer steps, src/neuralnet/train_utils.h:50-188 (SGD, Adam, AdamW): `steps` calls of
+// step() on one fp32 parameter whose gradient buffer holds `grad` (the same gradient every
+// step).  The updated parameter is copied to `param_out`; Adam's moment vectors are private to
+// the reference's classes and are pinned through the parameter trajectory.
+// kind: 0 SGD, 1 Adam, 2 AdamW.
+int64_t ref_optimizer_steps(int kind, const float* param, const float* grad, int64_t n, int steps,
+                            double lr, double beta1, double beta2, double eps, double weight_decay,
+                            float* param_out) {
+    return guarded([&] {
+        Tensor p({(size_t)n}, DType::Float32, true);
+        std::memcpy(p.impl->data->data.get(), param, (size_t)n * 4);
+        ensure_grad_buffer(p, true);
+        std::memcpy(p.impl->grad->data->data.get(), grad, (size_t)n * 4);
+        std::vector<Tensor*> params{&p};
+        std::unique_ptr<Optimizer> opt;
+        if (kind == 0) opt.reset(new SGD(params, lr));
+        else if (kind == 1) opt.reset(new Adam(params, lr, beta1, beta2, eps));
+        else if (kind == 2) opt.reset(new AdamW(params, lr, beta1, beta2, eps, weight_decay));
+        else throw std::runtime_error("ref_optimizer_steps: unknown kind");
+        for (int s = 0; s < steps; ++s) opt->step();
+        std::memcpy(param_out, p.impl->data->data.get(), (size_t)n * 4);
+        return n;
     });
 }
 

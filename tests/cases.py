@@ -2,7 +2,7 @@
 and the GPU tests.  Every case is a dict:
 
     name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
-    'accgrad'), op, views (HostViews),
+    'accgrad'|'optim'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -214,6 +214,16 @@ def all_cases():
     add(name="accgrad_bias_nonfinite", kind="accgrad", op=0, views=[HostView.contig(_n(46, (48,))), HostView.contig(nf)], exact=False)
     add(name="accgrad_i32", kind="accgrad", op=0, views=[HostView.contig(_rng(47).integers(-9, 9, (9,)).astype(np.int32)), Ai])
     add(name="accgrad_f64", kind="accgrad", op=0, views=[HostView.contig(_rng(48).standard_normal((6,))), Ad], exact=False)
+
+    # ---- optimizer steps: views = [parameter, gradient]; op = 0 SGD, 1 Adam, 2 AdamW; dim = number of steps ----
+    w0 = HostView.contig(_n(49, (1003,), 0.5))
+    gw = HostView.contig(_n(50, (1003,), 2.0))
+    gsp = SPECIAL_F32[np.isfinite(SPECIAL_F32)]
+    wsp = HostView.contig(np.linspace(-2, 2, gsp.size).astype(np.float32))
+    for kind, nm in enumerate(("sgd", "adam", "adamw")):
+        add(name=f"optim_{nm}_1step", kind="optim", op=kind, views=[w0, gw], dim=1, scalar=0.01)
+        add(name=f"optim_{nm}_7steps", kind="optim", op=kind, views=[w0, gw], dim=7, scalar=0.003)
+        add(name=f"optim_{nm}_special_grads", kind="optim", op=kind, views=[wsp, HostView.contig(gsp)], dim=2, scalar=0.1)
     return cases
 
 
@@ -242,6 +252,8 @@ def run_case(impl, case):
         return impl.gather(v[0], case["dim"], v[1])
     if k == "accgrad":
         return impl.accumulate_grad(v[0].numpy(), v[1])
+    if k == "optim":
+        return impl.optimizer_steps(case["op"], v[0].numpy(), v[1].numpy(), case["dim"], case["scalar"])
     raise ValueError(k)
 
 

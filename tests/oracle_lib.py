@@ -181,6 +181,11 @@ class Oracle:
         L.orc_gather.argtypes = [vp, ctypes.c_int, vp, ctypes.c_void_p]
         L.orc_accumulate_grad.restype = ctypes.c_int64
         L.orc_accumulate_grad.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int, vp]
+        L.orc_sgd_step.restype = None
+        L.orc_sgd_step.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_double]
+        L.orc_adam_step.restype = None
+        L.orc_adam_step.argtypes = ([ctypes.c_void_p] * 4 + [ctypes.c_int64] + [ctypes.c_double] * 4 +
+                                    [ctypes.c_int, ctypes.c_double, ctypes.c_int])
         L.orc_unary_sweep_f32.restype = None
         L.orc_unary_sweep_f32.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_int64, ctypes.c_double, ctypes.c_void_p,
@@ -248,6 +253,22 @@ class Oracle:
         assert n == out.size, "oracle accumulate_grad failed"
         return out
 
+    def optimizer_steps(self, kind: int, param: np.ndarray, grad: np.ndarray, steps: int, lr: float,
+                        beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01) -> np.ndarray:
+        """`steps` updates with the same gradient; kind 0 SGD, 1 Adam, 2 AdamW.  Returns the parameter."""
+        p = np.ascontiguousarray(param).copy()
+        g = np.ascontiguousarray(grad)
+        if kind == 0:
+            for _ in range(steps):
+                self.lib.orc_sgd_step(DT_OF[p.dtype], p.ctypes.data, g.ctypes.data, p.size, lr)
+            return p
+        m = np.zeros(p.size, np.float32)
+        v = np.zeros(p.size, np.float32)
+        for t in range(1, steps + 1):
+            self.lib.orc_adam_step(p.ctypes.data, g.ctypes.data, m.ctypes.data, v.ctypes.data, p.size, lr,
+                                   beta1, beta2, eps, t, weight_decay, 1 if kind == 2 else 0)
+        return p
+
     def sweep(self, op, start: int, step: int, count: int, scalar: float = 0.0):
         xin = np.empty(count, np.float32)
         out = np.empty(count, np.float32)
@@ -288,6 +309,8 @@ class Reference:
         L.ref_gather.argtypes = [vp, ctypes.c_int, vp, vd, i64]
         L.ref_accumulate_grad.restype = i64
         L.ref_accumulate_grad.argtypes = [vp, vd, vp, vd, i64]
+        L.ref_optimizer_steps.restype = i64
+        L.ref_optimizer_steps.argtypes = ([ctypes.c_int, vd, vd, i64, ctypes.c_int] + [ctypes.c_double] * 5 + [vd])
         L.ref_bench_step.restype = ctypes.c_double
         L.ref_bench_step.argtypes = [ctypes.c_int, vd, vd, i64]
         feats = L.ref_cpu_features()
@@ -354,6 +377,13 @@ class Reference:
         target = HostView.contig(np.zeros(g.shape, g.dtype))
         return self._check(self.lib.ref_accumulate_grad(target.cview(), g.ctypes.data, src.cview(),
                                                         out.ctypes.data, out.nbytes), out)
+
+    def optimizer_steps(self, kind, param, grad, steps, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
+        p = np.ascontiguousarray(param, np.float32)
+        g = np.ascontiguousarray(grad, np.float32)
+        out = np.empty_like(p)
+        return self._check(self.lib.ref_optimizer_steps(kind, p.ctypes.data, g.ctypes.data, p.size, steps, lr,
+                                                        beta1, beta2, eps, weight_decay, out.ctypes.data), out)
 
     def layernorm(self, x, gamma, beta, eps=1e-5):
         out = np.empty(x.shape, np.float32)

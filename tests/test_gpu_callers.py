@@ -135,3 +135,53 @@ def test_accumulate_grad_shape_mismatch(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.accumulate_grad(torch.zeros(3, 4, device="cuda"), torch.zeros(3, 5, device="cuda"))
     assert e.value.code == 2
+
+
+def test_sgd_large_and_other_dtypes(ct, oracle):
+    p = torch.randn(1 << 24, device="cuda")
+    g = torch.randn(1 << 24, device="cuda")
+    want = p - g * torch.tensor(0.05, dtype=torch.float32, device="cuda")     # two fp32 roundings, as the reference
+    ct.sgd_step(p, g, 0.05)
+    assert torch.equal(p, want)
+    # odd length and a misaligned start (scalar path)
+    base = torch.randn(1001 + 1, device="cuda")
+    gb = torch.randn(1001 + 1, device="cuda")
+    pv, gv = base[1:], gb[1:]
+    want = pv - gv * torch.tensor(0.5, dtype=torch.float32, device="cuda")
+    ct.sgd_step(ct.DView.of(pv), ct.DView.of(gv), 0.5)
+    assert torch.equal(pv, want)
+    for dt, npdt in ((torch.float64, np.float64), (torch.int32, np.int32)):
+        p0 = (np.random.default_rng(1).standard_normal(77) * 10).astype(npdt)
+        g0 = (np.random.default_rng(2).standard_normal(77) * 10).astype(npdt)
+        pd, gd = torch.from_numpy(p0.copy()).cuda(), torch.from_numpy(g0).cuda()
+        ct.sgd_step(pd, gd, 0.3)
+        assert_bits_equal(pd, oracle.optimizer_steps(0, p0, g0, 1, 0.3), f"sgd {dt}")
+
+
+def test_adam_trajectory_large(ct, oracle):
+    rng = np.random.default_rng(4)
+    p0 = rng.standard_normal(100003).astype(np.float32)
+    g0 = (rng.standard_normal(100003) * 3).astype(np.float32)
+    for kind, wd in ((1, None), (2, 0.05)):
+        p, g = torch.from_numpy(p0.copy()).cuda(), torch.from_numpy(g0).cuda()
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        for t in range(1, 6):
+            ct.adam_step(p, g, m, v, 1e-3, t, weight_decay=wd)
+        ref = oracle.optimizer_steps(kind, p0, g0, 5, 1e-3, weight_decay=0.05)
+        assert_bits_equal(p, ref, f"adam kind {kind}")
+
+
+def test_optimizer_argument_checks(ct):
+    p = torch.zeros(8, device="cuda")
+    with pytest.raises(ct.CtbError) as e:
+        ct.sgd_step(p, torch.zeros(9, device="cuda"), 0.1)
+    assert e.value.code == 2
+    with pytest.raises(ct.CtbError) as e:
+        ct.sgd_step(ct.DView.of(torch.zeros(8, 2, device="cuda")[:, 0]), p, 0.1)
+    assert "contiguous" in e.value.message
+    with pytest.raises(ct.CtbError) as e:
+        ct.adam_step(p.double(), p.double(), p, p, 0.1, 1)
+    assert e.value.code == 3
+    with pytest.raises(ct.CtbError) as e:
+        ct.adam_step(p, p, p, p, 0.1, 0)
+    assert e.value.code == 5

@@ -41,6 +41,16 @@ def run_gpu(ct, case):
     if k == "accgrad":
         grad = torch.from_numpy(case["views"][0].numpy()).cuda()
         return ct.accumulate_grad(grad, dv[1])
+    if k == "optim":
+        p = torch.from_numpy(case["views"][0].numpy()).cuda()
+        g = torch.from_numpy(case["views"][1].numpy()).cuda()
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        for t in range(1, case["dim"] + 1):
+            if case["op"] == 0:
+                ct.sgd_step(p, g, case["scalar"])
+            else:
+                ct.adam_step(p, g, m, v, case["scalar"], t, weight_decay=0.01 if case["op"] == 2 else None)
+        return p
     raise ValueError(k)
 
 
