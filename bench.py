@@ -19,6 +19,8 @@ Keys beyond the base contract:
                 pinned host memory out, copies inside the timed region)
   per_op        GB/s of every op of the step
   sweep         GB/s at the other sizes of the configuration (2^20, 2^24, 2^28), N=1 only
+  other_configs GB/s (algorithmic bytes / CUDA-event time, 20 back-to-back launches) of the
+                reduction, permuted-softmax-chain and GPT-2 non-GEMM configurations, N=1 only
 """
 from __future__ import annotations
 
@@ -250,7 +252,7 @@ def bench_ours(args):
         sharded_sum = {"error": repr(exc)}
 
     # ---- extras on rank 0 ------------------------------------------------------------------------------
-    sweep, cpu = None, None
+    sweep, cpu, other = None, None, None
     if world == 1 and not args.kernel_only:
         sweep = {}
         for lg in (20, 24, 28):
@@ -278,6 +280,11 @@ def bench_ours(args):
                 torch.cuda.synchronize()
                 res[name] = round(bpe * m * reps / a0.elapsed_time(a1) / 1e6, 1)
             sweep[f"2^{lg}"] = res
+        del x, y, out
+        try:
+            other = other_configs(ct, torch, dev)
+        except Exception as exc:                      # never lose the headline line to an extra
+            other = {"error": repr(exc)}
         if not args.no_cpu_baseline:
             cpu = cpu_baseline(sample_log2=args.cpu_log2)
 
@@ -312,6 +319,8 @@ def bench_ours(args):
     line["sharded_full_sum"] = sharded_sum
     if sweep is not None:
         line["sweep"] = sweep
+    if other is not None:
+        line["other_configs"] = other
     if cpu is not None:
         line["cpu_baseline"] = cpu
     # DRAM bytes per element from the ncu capture of the small case (n = 2^26), see
@@ -323,6 +332,69 @@ def bench_ours(args):
 
 
 # ---------------------------------------------------------------------------------------------------
+def other_configs(ct, torch, dev):
+    """GB/s of the other benchmark configurations on one GPU.  Bytes are the algorithmic bytes
+    (each distinct input element read once, each output element written once); every kernel is
+    timed over 20 back-to-back launches with CUDA events on tensors larger than L2 (the GPT-2
+    layer-norm / residual tensors are 24 MiB and L2-resident: reported, not a bandwidth figure)."""
+    def gbs(nbytes, fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(reps):
+            fn()
+        a1.record()
+        torch.cuda.synchronize()
+        return round(nbytes * reps / a0.elapsed_time(a1) / 1e6, 1)
+
+    g = torch.Generator(device=dev)
+    res = {}
+    # reductions: X[8192,16384] ~ N(0,1), seed 2
+    g.manual_seed(2)
+    X = torch.randn(8192, 16384, device=dev, generator=g)
+    red = {}
+    for dim in (0, 1):
+        for name, op in (("sum", ct.SUM), ("mean", ct.MEAN), ("var", ct.VAR), ("max", ct.MAX), ("argmax", ct.ARGMAX)):
+            r = torch.empty(X.shape[1 - dim], device=dev, dtype=torch.int32 if op == ct.ARGMAX else torch.float32)
+            red[f"{name}_dim{dim}"] = gbs(X.numel() * 4 + r.numel() * 4, lambda: ct.reduce(op, X, dim, out=r))
+    res["reductions_8192x16384"] = red
+    del X
+    # permuted 4-d broadcast and softmax chain: S = [32,1024,12,1024].permute(0,2,1,3), M[1,12,1,1024]
+    g.manual_seed(4)
+    buf = torch.randn(32, 1024, 12, 1024, device=dev, generator=g)
+    S = buf.permute(0, 2, 1, 3)
+    g.manual_seed(5)
+    M = -torch.rand(1, 12, 1, 1024, device=dev, generator=g)
+    O = torch.empty(32, 12, 1024, 1024, device=dev)
+    nb = buf.numel() * 4
+    mx = torch.empty(32, 12, 1024, device=dev)
+    res["permuted_softmax_chain"] = {
+        "S_plus_M": gbs(2 * nb + M.numel() * 4, lambda: ct.binary(ct.ADD, S, M, out=O)),
+        "max_last_dim": gbs(nb + mx.numel() * 4, lambda: ct.reduce(ct.MAX, O, 3, out=mx)),
+        "sub_rowmax": gbs(2 * nb + mx.numel() * 4, lambda: ct.binary(ct.SUB, O, mx.view(32, 12, 1024, 1), out=buf.view(32, 12, 1024, 1024))),
+        "fused_chain_softmax_S_plus_M": gbs(2 * nb + M.numel() * 4, lambda: ct.softmax(S, M, out=O)),
+    }
+    del buf, S, O, mx
+    # GPT-2 small non-GEMM forward ops on [8,1024,768] / [8,1024,3072] / [8,12,1024,1024]
+    g.manual_seed(6)
+    x = torch.randn(8, 1024, 768, device=dev, generator=g)
+    r = torch.randn(8, 1024, 768, device=dev, generator=g)
+    gam = 1 + 0.02 * torch.randn(768, device=dev, generator=g)
+    bet = 0.02 * torch.randn(768, device=dev, generator=g)
+    h = torch.randn(8, 1024, 3072, device=dev, generator=g)
+    a = torch.randn(8, 12, 1024, 1024, device=dev, generator=g)
+    ox, oh, oa = torch.empty_like(x), torch.empty_like(h), torch.empty_like(a)
+    res["gpt2_small_non_gemm"] = {
+        "residual_add_24MiB": gbs(3 * x.numel() * 4, lambda: ct.binary(ct.ADD, x, r, out=ox)),
+        "layernorm_24MiB": gbs(2 * x.numel() * 4, lambda: ct.layernorm(x, gam, bet, out=ox)),
+        "gelu_96MiB": gbs(2 * h.numel() * 4, lambda: ct.unary(ct.GELU_TANH, h, out=oh)),
+        "causal_softmax_384MiB": gbs(2 * a.numel() * 4, lambda: ct.softmax(a, None, True, out=oa)),
+    }
+    return res
+
+
 def cpu_baseline(sample_log2=26, reps=3):
     """The reference's CPU code on a bounded sample: n = 2^sample_log2 elements, the same five ops
     (gelu as the chain of reference primitives).  Every back-end the reference has for the op is

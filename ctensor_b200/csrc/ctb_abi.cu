@@ -739,6 +739,9 @@ int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream)
             if ((size_t)n > tmp_elems) tmp_elems = (size_t)n;
         }
     }
+    // the ticket region at the start of the shared workspace must stay zero between calls:
+    // intermediate sums never go there, even when no step of this call needs kernel scratch
+    if (kernel_ws < kTicketBytes) kernel_ws = kTicketBytes;
     kernel_ws = (kernel_ws + 255) / 256 * 256;
     const size_t tmp_bytes = (tmp_elems * eb + 255) / 256 * 256;
     void* ws = nullptr;
