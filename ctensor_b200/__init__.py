@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = [
     "ctb_reduce_ws", "ctb_reduce_dim_noalloc", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
     "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
+    "ctb_copy_into", "ctb_cat",
 ]
 
 
@@ -114,6 +115,8 @@ def lib() -> ctypes.CDLL:
     L.ctb_gather.argtypes = [vp, i32, vp, vp, vd, vd]
     L.ctb_accumulate_grad.argtypes = [vp, vp, vd]
     L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
+    L.ctb_copy_into.argtypes = [vp, vp, vd]
+    L.ctb_cat.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vd]
     L.ctb_adam_step.argtypes = [vp, vp, vd, vd] + [ctypes.c_double] * 4 + [i32, ctypes.c_double, i32, vd]
     L.ctb_binary_host.argtypes = [i32, vp, vp, vp, i32]
     L.ctb_unary_host.argtypes = [i32, vp, ctypes.c_double, vp, i32]
@@ -353,6 +356,32 @@ def accumulate_grad(grad, src):
     with _device_guard(g):
         check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
     return grad
+
+
+def copy_into(src, dst):
+    """dst[...] = src (broadcast allowed); dst may be any strided view."""
+    s, d = _as_dview(src), _as_dview(dst)
+    with _device_guard(d):
+        check(lib().ctb_copy_into(s.cview(), d.cview(), _stream_ptr(d)))
+    return dst
+
+
+def cat(tensors, dim: int = 0, out=None):
+    """cat_mp: concatenate along ``dim``."""
+    vs = [_as_dview(t) for t in tensors]
+    if out is None and vs:
+        shape = list(vs[0].shape)
+        if 0 <= dim < len(shape):
+            shape[dim] = sum(v.shape[dim] if len(v.shape) == len(shape) else 0 for v in vs)
+        out = _new_out(vs[0], tuple(shape))
+    cviews = [v.cview() for v in vs]
+    arr = (ctypes.POINTER(View) * max(1, len(cviews)))(*[ctypes.pointer(c) for c in cviews])
+    if not vs:
+        check(lib().ctb_cat(arr, 0, dim, None, None))       # raises "cat_mp: empty list"
+        return None
+    with _device_guard(vs[0]):
+        check(lib().ctb_cat(arr, len(cviews), dim, DView.of(out).cview(), _stream_ptr(vs[0])))
+    return out
 
 
 def sgd_step(param, grad, lr: float):

@@ -153,10 +153,13 @@ inline void* elem_ptr_mut(const ctb_view* v) {
 
 // Right-aligned broadcast of up to kMaxOperands inputs, then collapse.
 // Returns CTB_ERR_SHAPE if the shapes are not broadcastable (src/core/opsmp.cpp:19-28).
-int build_plan(const ctb_view* const* in, int nin, Plan* plan) {
+// `dst` (optional): the output is this strided view instead of a fresh contiguous buffer; it must
+// have the broadcast shape, and its strides take part in the collapse.
+int build_plan(const ctb_view* const* in, int nin, Plan* plan, const ctb_view* dst = nullptr) {
     int nd = 0;
     for (int i = 0; i < nin; ++i) nd = in[i]->ndim > nd ? in[i]->ndim : nd;
-    int64_t shape[CTB_MAX_DIMS], stride[kMaxOperands][CTB_MAX_DIMS];
+    if (dst && dst->ndim > nd) nd = dst->ndim;
+    int64_t shape[CTB_MAX_DIMS], stride[kMaxOperands][CTB_MAX_DIMS], ostride[CTB_MAX_DIMS];
     for (int d = 0; d < nd; ++d) {
         int64_t s = 1;
         for (int i = 0; i < nin; ++i) {
@@ -166,6 +169,12 @@ int build_plan(const ctb_view* const* in, int nin, Plan* plan) {
                 if (s != 1 && s != di) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
                 s = di;
             }
+        }
+        if (dst) {      // the destination fixes the extent; inputs may only broadcast into it
+            const int jd = d - (nd - dst->ndim);
+            const int64_t dd = jd < 0 ? 1 : dst->shape[jd];
+            if (s != 1 && s != dd) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+            s = dd;
         }
         shape[d] = s;
         for (int i = 0; i < nin; ++i) {
@@ -183,8 +192,17 @@ int build_plan(const ctb_view* const* in, int nin, Plan* plan) {
         }
         numel *= shape[d];
     }
+    if (dst) {
+        for (int d = 0; d < nd; ++d) {
+            const int j = d - (nd - dst->ndim);
+            const int64_t dd = j < 0 ? 1 : dst->shape[j];
+            if (dd != shape[d]) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+            ostride[d] = (j < 0 || dd == 1) ? 0 : dst->stride[j];
+        }
+    }
     plan->nin = nin;
     plan->numel = numel;
+    plan->out_strided = dst ? 1 : 0;
     // drop size-1 dims, merge neighbours
     int k = 0;
     for (int d = 0; d < nd; ++d) {
@@ -193,19 +211,23 @@ int build_plan(const ctb_view* const* in, int nin, Plan* plan) {
             bool merge = true;
             for (int i = 0; i < nin; ++i)
                 if (plan->stride[i][k - 1] != stride[i][d] * shape[d]) merge = false;
+            if (dst && plan->ostride[k - 1] != ostride[d] * shape[d]) merge = false;
             if (merge) {
                 plan->shape[k - 1] *= shape[d];
                 for (int i = 0; i < nin; ++i) plan->stride[i][k - 1] = stride[i][d];
+                if (dst) plan->ostride[k - 1] = ostride[d];
                 continue;
             }
         }
         plan->shape[k] = shape[d];
         for (int i = 0; i < nin; ++i) plan->stride[i][k] = stride[i][d];
+        if (dst) plan->ostride[k] = ostride[d];
         ++k;
     }
     if (k == 0) {
         plan->shape[0] = 1;
         for (int i = 0; i < nin; ++i) plan->stride[i][0] = 0;
+        if (dst) plan->ostride[0] = 0;
         k = 1;
     }
     plan->ndim = k;
@@ -777,6 +799,56 @@ int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream)
         return launch_binary(kOpAddFinite, grad->dtype, p, elem_ptr(grad), elem_ptr(&cur), elem_ptr_mut(grad), st);
     }
     return launch_accumulate_strided(grad->dtype, nd, tshape, tstride, cur.stride, elem_ptr_mut(grad), elem_ptr(&cur), st);
+}
+
+// ---- copies into existing tensors: copy_into, cat ----------------------------------------------------------
+int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream) {
+    int rc;
+    if ((rc = check_view(src, "copy: null input", "copy"))) return rc;
+    if ((rc = check_view(dst, "output: null view", "copy"))) return rc;
+    if (src->dtype != dst->dtype) return set_error(CTB_ERR_DTYPE, "copy: output dtype mismatch");
+    const ctb_view* in[1] = {src};
+    Plan p;
+    if ((rc = build_plan(in, 1, &p, dst))) return rc;
+    return launch_copy((int)dtype_bytes(src->dtype), p, elem_ptr(src), elem_ptr_mut(dst), (cudaStream_t)stream);
+}
+
+int ctb_cat(const ctb_view* const* inputs, int count, int dim, const ctb_view* out, void* stream) {
+    int rc;
+    if (!inputs || count <= 0) return set_error(CTB_ERR_ARG, "cat_mp: empty list");
+    for (int i = 0; i < count; ++i)
+        if ((rc = check_view(inputs[i], "cat_mp: null tensor", "cat_mp"))) return rc;
+    const int nd = inputs[0]->ndim;
+    if (dim < 0 || dim >= nd) return set_error(CTB_ERR_DIM, "cat_mp: dim out of range");
+    int64_t total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (inputs[i]->ndim != nd) return set_error(CTB_ERR_SHAPE, "cat_mp: ndim mismatch");
+        if (inputs[i]->dtype != inputs[0]->dtype) return set_error(CTB_ERR_DTYPE, "cat_mp: dtype mismatch");
+        for (int d = 0; d < nd; ++d)
+            if (d != dim && inputs[i]->shape[d] != inputs[0]->shape[d])
+                return set_error(CTB_ERR_SHAPE, "cat_mp: shape mismatch outside cat dim");
+        total += inputs[i]->shape[dim];
+    }
+    int64_t numel = total;
+    for (int d = 0; d < nd; ++d) if (d != dim) numel *= inputs[0]->shape[d];
+    if ((rc = check_out(out, numel, inputs[0]->dtype, "cat_mp"))) return rc;
+    if (out->ndim != nd) return set_error(CTB_ERR_SHAPE, "cat_mp: output has the wrong number of dims");
+    for (int d = 0; d < nd; ++d)
+        if (out->shape[d] != (d == dim ? total : inputs[0]->shape[d]))
+            return set_error(CTB_ERR_SHAPE, "cat_mp: output has the wrong shape");
+    // row-major strides of the output; each input lands in its slice along `dim`
+    int64_t ostride[CTB_MAX_DIMS], run = 1;
+    for (int d = nd - 1; d >= 0; --d) { ostride[d] = run; run *= out->shape[d]; }
+    int64_t at = 0;
+    for (int i = 0; i < count; ++i) {
+        ctb_view slice = *out;
+        for (int d = 0; d < nd; ++d) { slice.stride[d] = ostride[d]; slice.shape[d] = inputs[i]->shape[d]; }
+        slice.offset = out->offset + at * ostride[dim];
+        at += inputs[i]->shape[dim];
+        if (inputs[i]->shape[dim] == 0) continue;
+        if ((rc = ctb_copy_into(inputs[i], &slice, stream))) return rc;
+    }
+    return CTB_OK;
 }
 
 // ---- optimizer steps ---------------------------------------------------------------------------------

@@ -27,8 +27,9 @@ int current_device_info(DeviceInfo* info);
 // ---- iteration plan -------------------------------------------------------------------------
 // The host collapses (out, a, b) into at most CTB_MAX_DIMS joint dims (size-1 dims dropped,
 // adjacent dims merged when every operand allows it — the same folding idea as the reference's
-// TensorIterator, src/core/opsmp.cpp:76-126).  dims are ordered outer -> inner; the output is
-// always contiguous so its strides are implied.
+// TensorIterator, src/core/opsmp.cpp:76-126).  dims are ordered outer -> inner.  Operator results
+// are fresh contiguous tensors, so the output's strides are normally implied by the shape; a copy
+// into a slice of an existing tensor (cat) sets `out_strided` and gives them in `ostride`.
 constexpr int kMaxOperands = 3;
 struct Plan {
     int32_t ndim;                       // >= 1
@@ -36,6 +37,8 @@ struct Plan {
     int64_t numel;                      // output elements
     int64_t shape[CTB_MAX_DIMS];
     int64_t stride[kMaxOperands][CTB_MAX_DIMS];   // per input, elements, 0 = broadcast
+    int32_t out_strided;                // 0: the output is contiguous
+    int64_t ostride[CTB_MAX_DIMS];      // output strides when out_strided
 };
 
 // ---- vector access ----------------------------------------------------------------------------

@@ -291,20 +291,22 @@ ew_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__
 // ------------------------------------------------------------------------------------------------
 struct GatherArgs {
     DimSet dims;
-    int64_t stride[2][CTB_MAX_DIMS];
+    int64_t stride[3][CTB_MAX_DIMS];       // [0], [1] = inputs, [2] = output (OUT_STRIDED only)
     int64_t numel;
 };
 
-template <typename F, typename T, int NIN>
+template <typename F, typename T, int NIN, bool OUT_STRIDED>
 __global__ void __launch_bounds__(256)
 ew_gather_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
                  GatherArgs g, double scalar) {
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < g.numel; i += step) {
-        int64_t off[2] = {0, 0};
-        dimset_offsets<2>(g.dims, i, g.stride, off);
-        if (NIN == 2) out[i] = F::apply2(a[off[0]], b[off[1]]);
-        else out[i] = F::apply1(a[off[0]], scalar);
+        int64_t off[3] = {0, 0, 0};
+        if (OUT_STRIDED) dimset_offsets<3>(g.dims, i, g.stride, off);
+        else dimset_offsets<2>(g.dims, i, g.stride, off);
+        const int64_t o = OUT_STRIDED ? off[2] : i;
+        if (NIN == 2) out[o] = F::apply2(a[off[0]], b[off[1]]);
+        else out[o] = F::apply1(a[off[0]], scalar);
     }
 }
 
@@ -313,6 +315,7 @@ namespace {
 
 bool plan_is_flat(const Plan& p) {
     if (p.ndim != 1) return false;
+    if (p.out_strided && p.ostride[0] != 1 && p.shape[0] > 1) return false;
     for (int i = 0; i < p.nin; ++i)
         if (p.stride[i][0] != 0 && p.stride[i][0] != 1) return false;
     return true;
@@ -320,6 +323,7 @@ bool plan_is_flat(const Plan& p) {
 
 bool plan_is_rows(const Plan& p) {
     if (p.ndim < 2) return false;
+    if (p.out_strided && p.ostride[p.ndim - 1] != 1) return false;
     for (int i = 0; i < p.nin; ++i) {
         int64_t s = p.stride[i][p.ndim - 1];
         if (s != 0 && s != 1) return false;
@@ -377,7 +381,9 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
                 const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
             }
         int64_t out_stride[CTB_MAX_DIMS];
-        {
+        if (p.out_strided) {
+            for (int d = 0; d < nd - 1; ++d) out_stride[d] = p.ostride[d];
+        } else {
             int64_t st = p.shape[nd - 1];
             for (int d = nd - 2; d >= 0; --d) { out_stride[d] = st; st *= p.shape[d]; }
         }
@@ -393,6 +399,7 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
             const int d = order[k];
             oshape[k] = p.shape[d];
             g.stride[2][k] = out_stride[d];
+            if (out_stride[d] % RVEC != 0) aligned = false;
             rows *= p.shape[d];
             for (int i = 0; i < NIN; ++i) {
                 g.stride[i][k] = p.stride[i][d];
@@ -427,7 +434,12 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
     ga.numel = p.numel;
     int64_t blocks = ceil_div(p.numel, 256);
     if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
-    ew_gather_kernel<F, T, NIN><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
+    if (p.out_strided) {
+        for (int d = 0; d < p.ndim; ++d) ga.stride[2][d] = p.ostride[d];
+        ew_gather_kernel<F, T, NIN, true><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
+    } else {
+        ew_gather_kernel<F, T, NIN, false><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
+    }
     return cuda_error(cudaGetLastError(), "ew_gather launch");
 }
 

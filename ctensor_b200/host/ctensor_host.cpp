@@ -479,6 +479,35 @@ Tensor softmax(const Tensor& a, const Tensor& additive_mask) {
 }
 Tensor causal_softmax(const Tensor& a) { return softmax_impl(a, nullptr, 1); }
 
+// cat_mp, src/core/opsmp.cpp:717-804.
+Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
+    if (tensors.empty()) throw std::runtime_error("cat_mp: empty list");
+    for (const Tensor& t : tensors)
+        if (!t.impl) throw std::runtime_error("cat_mp: null tensor");
+    std::vector<size_t> out_shape = tensors[0].shape();
+    const size_t ndim = out_shape.size();
+    if (dim >= ndim) throw std::out_of_range("cat_mp: dim out of range");
+    size_t dim_sum = 0;
+    for (const Tensor& t : tensors) {
+        if (t.impl->ndim != ndim) throw std::runtime_error("cat_mp: ndim mismatch");
+        for (size_t i = 0; i < ndim; ++i)
+            if (i != dim && t.impl->shape[i] != out_shape[i]) throw std::runtime_error("cat_mp: shape mismatch outside cat dim");
+        dim_sum += t.impl->shape[dim];
+    }
+    out_shape[dim] = dim_sum;
+    ensure_device();
+    Tensor out(out_shape, tensors[0]._dtype(), false);
+    std::vector<ctb_view> views;
+    std::vector<const ctb_view*> ptrs;
+    views.reserve(tensors.size());
+    for (const Tensor& t : tensors) views.push_back(view_of(t, "cat_mp"));
+    for (const ctb_view& v : views) ptrs.push_back(&v);
+    const ctb_view vo = view_of(out, "cat_mp");
+    check(ctb_cat(ptrs.data(), (int)ptrs.size(), (int)dim, &vo, nullptr));
+    after_op();
+    return out;
+}
+
 Tensor log_softmax(const Tensor& a) {
     if (!a.impl) throw std::runtime_error("log_softmax: null input");
     ensure_device();

@@ -72,6 +72,8 @@ Tensor softmax(const Tensor& a);
 Tensor softmax(const Tensor& a, const Tensor& additive_mask);
 Tensor causal_softmax(const Tensor& a);
 Tensor log_softmax(const Tensor& a);                 // the chain inside Loss::CrossEntropy
+
+Tensor cat(const std::vector<Tensor>& tensors, size_t dim);
 Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps = 1e-5);
 
 // operators

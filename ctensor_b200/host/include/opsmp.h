@@ -38,6 +38,7 @@ inline Tensor softplus_mp(const Tensor& a) { return softplus(a); }
 inline Tensor tanh_mp(const Tensor& a) { return tanh(a); }
 inline Tensor sigmoid_mp(const Tensor& a) { return sigmoid(a); }
 inline Tensor Relu_mp(const Tensor& a) { return relu(a); }
+inline Tensor cat_mp(const std::vector<Tensor>& tensors, size_t dim) { return cat(tensors, dim); }
 
 namespace ctb_host { int last_dim_if_negative(const Tensor& t, int dim); }
 inline Tensor sum_mp(const Tensor& t, int dim = -1) { return sum(t, ctb_host::last_dim_if_negative(t, dim)); }

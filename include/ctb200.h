@@ -229,6 +229,15 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
  * Intermediate sums live in the library's per-device workspace (see ctb_reduce). */
 int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream);
 
+/* Copy `src` into the existing (possibly strided) view `dst` of the same shape and dtype; `src`
+ * may broadcast.  The building block of cat and of writes into slices. */
+int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream);
+
+/* cat_mp, src/core/opsmp.cpp:717-804: concatenate `count` views along `dim` into `out`
+ * (contiguous, the inputs' shape with the extents along `dim` added up).  All inputs have the
+ * same number of dims, dtype and extents outside `dim`; any strides.  One strided copy per input. */
+int ctb_cat(const ctb_view* const* inputs, int count, int dim, const ctb_view* out, void* stream);
+
 /* Optimizer steps, src/neuralnet/train_utils.h:50-188, in place on contiguous buffers.
  * ctb_sgd_step: param -= (float)lr * grad for CTB_F32 (:66-68); (T)(param - lr*grad) in double
  * for the other dtypes (:72-76).

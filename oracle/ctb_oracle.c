@@ -720,3 +720,41 @@ void orc_adam_step(float* theta, const float* grad, float* m, float* v, int64_t 
         theta[i] -= lr_t * m[i] / (sqrtf(v[i]) + (float)eps);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * cat_mp, src/core/opsmp.cpp:717-804 (its element-wise path, which also covers what the
+ * contiguous fast path does): out is contiguous with the inputs' shape and the extents along
+ * `dim` added up.  Returns the output element count, -1 for a malformed call.
+ * ---------------------------------------------------------------------------------------- */
+int64_t orc_cat(const orc_view* const* in, int count, int dim, void* out) {
+    if (count <= 0) return -1;
+    int nd = in[0]->ndim, dt = in[0]->dtype;
+    if (dim < 0 || dim >= nd) return -1;
+    int64_t oshape[ORC_MAX_DIMS], ostride[ORC_MAX_DIMS], total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (in[i]->ndim != nd || in[i]->dtype != dt) return -1;
+        for (int d = 0; d < nd; ++d)
+            if (d != dim && in[i]->shape[d] != in[0]->shape[d]) return -1;
+        total += in[i]->shape[dim];
+    }
+    for (int d = 0; d < nd; ++d) oshape[d] = d == dim ? total : in[0]->shape[d];
+    int64_t run = 1;
+    for (int d = nd - 1; d >= 0; --d) { ostride[d] = run; run *= oshape[d]; }
+    int64_t at = 0;
+    for (int i = 0; i < count; ++i) {
+        int64_t n = numel(in[i]);
+        for (int64_t j = 0; j < n; ++j) {
+            int64_t t = j, src = in[i]->offset, dst = 0;
+            for (int d = nd - 1; d >= 0; --d) {
+                int64_t c = t % in[i]->shape[d];
+                t /= in[i]->shape[d];
+                src += c * in[i]->stride[d];
+                dst += (c + (d == dim ? at : 0)) * ostride[d];
+            }
+            if (esize(dt) == 8) ((uint64_t*)out)[dst] = ((const uint64_t*)in[i]->base)[src];
+            else ((uint32_t*)out)[dst] = ((const uint32_t*)in[i]->base)[src];
+        }
+        at += in[i]->shape[dim];
+    }
+    return run;
+}

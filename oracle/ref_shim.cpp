@@ -402,6 +402,15 @@ int64_t ref_accumulate_grad(const RefView* target, const void* grad_init, const 
     });
 }
 
+// cat_mp (src/core/opsmp.cpp:717-804).
+int64_t ref_cat(const RefView* const* in, int count, int dim, void* out, int64_t cap) {
+    return guarded([&] {
+        std::vector<Tensor> ts;
+        for (int i = 0; i < count; ++i) ts.push_back(wrap(in[i]));
+        return emit(cat_mp(ts, (size_t)dim), out, cap);
+    });
+}
+
 // Optimizer steps, src/neuralnet/train_utils.h:50-188 (SGD, Adam, AdamW): `steps` calls of
 // step() on one fp32 parameter whose gradient buffer holds `grad` (the same gradient every
 // step).  The updated parameter is copied to `param_out`; Adam's moment vectors are private to

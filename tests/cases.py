@@ -2,7 +2,7 @@
 and the GPU tests.  Every case is a dict:
 
     name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
-    'accgrad'|'optim'), op, views (HostViews),
+    'accgrad'|'optim'|'cat'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -215,6 +215,15 @@ def all_cases():
     add(name="accgrad_i32", kind="accgrad", op=0, views=[HostView.contig(_rng(47).integers(-9, 9, (9,)).astype(np.int32)), Ai])
     add(name="accgrad_f64", kind="accgrad", op=0, views=[HostView.contig(_rng(48).standard_normal((6,))), Ad], exact=False)
 
+    # ---- cat: views = the inputs, dim = the cat dim ------------------------------------------------------------
+    add(name="cat_dim0", kind="cat", op=0, views=[A, A.narrow(0, 3, 11), B], dim=0)
+    add(name="cat_dim1", kind="cat", op=0, views=[A, C, A.narrow(1, 1, 5)], dim=1)
+    add(name="cat_transposed", kind="cat", op=0, views=[T, HostView.contig(_u(51, (48, 3)))], dim=1)
+    add(name="cat_perm4d_dim2", kind="cat", op=0, views=[P4, P4.narrow(2, 1, 2)], dim=2)
+    add(name="cat_i32", kind="cat", op=0, views=[Ai, Ai], dim=1)
+    add(name="cat_f64_single", kind="cat", op=0, views=[Ad.permute([1, 0])], dim=0)
+    add(name="cat_ragged_offset", kind="cat", op=0, views=[off, off.narrow(1, 2, 1), off.step(1, 3)], dim=1)
+
     # ---- optimizer steps: views = [parameter, gradient]; op = 0 SGD, 1 Adam, 2 AdamW; dim = number of steps ----
     w0 = HostView.contig(_n(49, (1003,), 0.5))
     gw = HostView.contig(_n(50, (1003,), 2.0))
@@ -252,6 +261,8 @@ def run_case(impl, case):
         return impl.gather(v[0], case["dim"], v[1])
     if k == "accgrad":
         return impl.accumulate_grad(v[0].numpy(), v[1])
+    if k == "cat":
+        return impl.cat(v, case["dim"])
     if k == "optim":
         return impl.optimizer_steps(case["op"], v[0].numpy(), v[1].numpy(), case["dim"], case["scalar"])
     raise ValueError(k)

@@ -149,6 +149,16 @@ int main() {
     ctb_host::accumulate_grad(bias_grad, Tensor::full({3}, std::nan("")));   // NaN contributions are skipped
     CHECK_NEAR(bias_grad[1], 3.0, 0.0);
 
+    Tensor c01 = cat({Tensor::from_vector({1, 2, 3, 4}, {2, 2}), Tensor::from_vector({5, 6}, {1, 2})}, 0);
+    CHECK(c01.shape()[0] == 3 && c01.shape()[1] == 2);
+    CHECK_NEAR(c01[2][1], 6.0, 0.0);
+    Tensor c1 = cat_mp({Tensor::from_vector({1, 2, 3, 4}, {2, 2}), Tensor::from_vector({5, 6}, {2, 1})}, 1);
+    CHECK(c1.shape()[1] == 3);
+    CHECK_NEAR(c1[0][2], 5.0, 0.0);
+    CHECK_NEAR(c1[1][0], 3.0, 0.0);
+    CHECK_THROWS(cat({Tensor::ones({2, 2}), Tensor::ones({3, 3})}, 0), std::runtime_error, "cat_mp: shape mismatch outside cat dim");
+    CHECK_THROWS(cat({}, 0), std::runtime_error, "cat_mp: empty list");
+
     // errors: the reference's exception types and texts
     CHECK_THROWS(Tensor::ones({2, 3}) + Tensor::ones({2, 2}), std::runtime_error, "Shape mismatch in binary op");
     CHECK_THROWS(add(Tensor(), a), std::runtime_error, "binary_op: null input");

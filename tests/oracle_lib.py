@@ -181,6 +181,8 @@ class Oracle:
         L.orc_gather.argtypes = [vp, ctypes.c_int, vp, ctypes.c_void_p]
         L.orc_accumulate_grad.restype = ctypes.c_int64
         L.orc_accumulate_grad.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int, vp]
+        L.orc_cat.restype = ctypes.c_int64
+        L.orc_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.orc_sgd_step.restype = None
         L.orc_sgd_step.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_double]
         L.orc_adam_step.restype = None
@@ -253,6 +255,16 @@ class Oracle:
         assert n == out.size, "oracle accumulate_grad failed"
         return out
 
+    def cat(self, views, dim: int) -> np.ndarray:
+        shape = list(views[0].shape)
+        shape[dim] = sum(v.shape[dim] for v in views)
+        out = np.empty(shape, NP_DTYPES[views[0].dtype])
+        cv = [v.cview() for v in views]
+        arr = (ctypes.POINTER(CView) * len(cv))(*[ctypes.pointer(c) for c in cv])
+        n = self.lib.orc_cat(arr, len(cv), dim, out.ctypes.data)
+        assert n == out.size, "oracle cat failed"
+        return out
+
     def optimizer_steps(self, kind: int, param: np.ndarray, grad: np.ndarray, steps: int, lr: float,
                         beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01) -> np.ndarray:
         """`steps` updates with the same gradient; kind 0 SGD, 1 Adam, 2 AdamW.  Returns the parameter."""
@@ -309,6 +321,8 @@ class Reference:
         L.ref_gather.argtypes = [vp, ctypes.c_int, vp, vd, i64]
         L.ref_accumulate_grad.restype = i64
         L.ref_accumulate_grad.argtypes = [vp, vd, vp, vd, i64]
+        L.ref_cat.restype = i64
+        L.ref_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, vd, i64]
         L.ref_optimizer_steps.restype = i64
         L.ref_optimizer_steps.argtypes = ([ctypes.c_int, vd, vd, i64, ctypes.c_int] + [ctypes.c_double] * 5 + [vd])
         L.ref_bench_step.restype = ctypes.c_double
@@ -377,6 +391,14 @@ class Reference:
         target = HostView.contig(np.zeros(g.shape, g.dtype))
         return self._check(self.lib.ref_accumulate_grad(target.cview(), g.ctypes.data, src.cview(),
                                                         out.ctypes.data, out.nbytes), out)
+
+    def cat(self, views, dim):
+        shape = list(views[0].shape)
+        shape[dim] = sum(v.shape[dim] for v in views)
+        out = np.empty(shape, NP_DTYPES[views[0].dtype])
+        cv = [v.cview() for v in views]
+        arr = (ctypes.POINTER(CView) * len(cv))(*[ctypes.pointer(c) for c in cv])
+        return self._check(self.lib.ref_cat(arr, len(cv), dim, out.ctypes.data, out.nbytes), out)
 
     def optimizer_steps(self, kind, param, grad, steps, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
         p = np.ascontiguousarray(param, np.float32)

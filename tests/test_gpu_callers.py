@@ -185,3 +185,34 @@ def test_optimizer_argument_checks(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.adam_step(p, p, p, p, 0.1, 0)
     assert e.value.code == 5
+
+
+def test_cat_matches_torch_and_copy_into_slices(ct):
+    a = torch.randn(300, 257, device="cuda")
+    b = torch.randn(300, 1023, device="cuda")
+    c = torch.randn(300, 4, device="cuda")
+    assert torch.equal(ct.cat([a, b, c], 1), torch.cat([a, b, c], 1))
+    assert torch.equal(ct.cat([a, a.flip(0).contiguous()], 0), torch.cat([a, a.flip(0)], 0))
+    big = torch.randn(8, 1024, 3072, device="cuda")
+    assert torch.equal(ct.cat([big, big], 2), torch.cat([big, big], 2))
+    p = torch.randn(16, 64, 12, 32, device="cuda").permute(0, 2, 1, 3)
+    assert torch.equal(ct.cat([p, p], 1), torch.cat([p, p], 1))
+    # copy_into: a strided destination, a broadcast source
+    dst = torch.zeros(64, 96, device="cuda")
+    ct.copy_into(torch.arange(32, dtype=torch.float32, device="cuda").reshape(1, 32), ct.DView.of(dst[:, 32:64]))
+    assert torch.equal(dst[:, 32:64], torch.arange(32, dtype=torch.float32, device="cuda").expand(64, 32))
+    assert float(dst[:, :32].abs().sum()) == 0 and float(dst[:, 64:].abs().sum()) == 0
+    ct.copy_into(a.t(), ct.DView.of(torch.empty(257, 300, device="cuda")))
+
+
+def test_cat_errors(ct):
+    a = torch.zeros(2, 3, device="cuda")
+    for bad, code, text in (([a, torch.zeros(2, 3, 1, device="cuda")], 2, "cat_mp: ndim mismatch"),
+                            ([a, torch.zeros(3, 4, device="cuda")], 2, "cat_mp: shape mismatch outside cat dim"),
+                            ([a, a.double()], 3, "cat_mp: dtype mismatch")):
+        with pytest.raises(ct.CtbError) as e:
+            ct.cat(bad, 0)
+        assert e.value.code == code and text in e.value.message
+    with pytest.raises(ct.CtbError) as e:
+        ct.cat([a], 2)
+    assert e.value.code == 4

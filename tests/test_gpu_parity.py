@@ -41,6 +41,8 @@ def run_gpu(ct, case):
     if k == "accgrad":
         grad = torch.from_numpy(case["views"][0].numpy()).cuda()
         return ct.accumulate_grad(grad, dv[1])
+    if k == "cat":
+        return ct.cat(dv, case["dim"])
     if k == "optim":
         p = torch.from_numpy(case["views"][0].numpy()).cuda()
         g = torch.from_numpy(case["views"][1].numpy()).cuda()
