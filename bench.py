@@ -395,6 +395,47 @@ def other_configs(ct, torch, dev):
     return res
 
 
+def profile_case(name: str):
+    """A few launches of one kernel family on a small case (inputs larger than L2, well under
+    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided`."""
+    import torch
+    import ctensor_b200 as ct
+    torch.manual_seed(0)
+    if name == "reductions":            # 4096 x 16384 fp32 = 256 MiB; dim 0 = column kernel, dim 1 = row kernel
+        X = torch.randn(4096, 16384, device="cuda")
+        for _ in range(2):
+            for op in (ct.VAR, ct.SUM, ct.ARGMAX, ct.MAX):
+                for dim in (0, 1):
+                    ct.reduce(op, X, dim)
+    elif name == "rows":                # softmax variants on [4,12,1024,1024] (192 MiB), LayerNorm on [65536,768]
+        C = torch.randn(4, 12, 1024, 1024, device="cuda")
+        O = torch.empty_like(C)
+        M = -torch.rand(1, 12, 1, 1024, device="cuda")
+        L = torch.randn(65536, 768, device="cuda")
+        LO = torch.empty_like(L)
+        g, b = torch.randn(768, device="cuda"), torch.randn(768, device="cuda")
+        for _ in range(2):
+            ct.softmax(C, out=O)
+            ct.softmax(C, M, out=O)
+            ct.softmax(C, None, True, out=O)
+            ct.log_softmax(C, out=O)
+            ct.layernorm(L, g, b, out=LO)
+    elif name == "strided":             # the permuted 4-d view at batch 4: S + M, contiguous(S), x - rowmax
+        buf = torch.randn(4, 1024, 12, 1024, device="cuda")
+        S = buf.permute(0, 2, 1, 3)
+        M = -torch.rand(1, 12, 1, 1024, device="cuda")
+        O = torch.empty(4, 12, 1024, 1024, device="cuda")
+        mx = torch.randn(4, 12, 1024, 1, device="cuda")
+        for _ in range(2):
+            ct.binary(ct.ADD, S, M, out=O)
+            ct.contiguous(S, out=O)
+            ct.binary(ct.SUB, O, mx, out=buf.view(4, 12, 1024, 1024))
+    else:
+        raise SystemExit(f"unknown profile case {name!r}")
+    torch.cuda.synchronize()
+    _emit({"profile_case": name, "status": "done"})
+
+
 def cpu_baseline(sample_log2=26, reps=3):
     """The reference's CPU code on a bounded sample: n = 2^sample_log2 elements, the same five ops
     (gelu as the chain of reference primitives).  Every back-end the reference has for the op is
@@ -506,7 +547,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
+    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided"],
+                    help="run a few launches of one kernel family on a small case and exit (for ncu)")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         bench_reference(args)
