@@ -45,6 +45,7 @@ namespace ctb {
 #define CTB_RED_COLS_CTAS_PER_SM 3         // register budget of the column kernel: at least this many CTAs per SM
 #endif
 
+constexpr int64_t kRowsWarpSmall = 2048;
 constexpr int64_t kRowsWarpMax = 8192;
 constexpr int kCounterSlots = kTicketSlots;           // uint32 tickets at the start of scratch
 constexpr size_t kCounterBytes = kTicketBytes;
@@ -530,9 +531,16 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
             c.splits = (int)ceil_div(g.rlen, chunk);
             return c;
         }
-        // a warp per row up to 8192 elements (no CTA barrier per row; a 512-thread CTA per 4096-element
-        // row measured 3.7 TB/s against the warp's 6.6), a CTA per row beyond
-        c.shape = g.rlen <= kRowsWarpMax ? SH_ROWS_WARP : SH_ROWS_BLOCK;
+        // A warp per line (no CTA barrier per line) when the lines are short, or when there are
+        // enough of them to fill the machine with warps and a 512-thread CTA would fit badly:
+        // lines up to 8192 elements (a CTA per 4096-element line measured 3.7 TB/s against the
+        // warp's 6.6) and longer lines that are not a whole number of CTA-wide batches
+        // ([40000,10000]: 7.1 against 5.1 TB/s).  A CTA per line otherwise.
+        const int64_t cta_batch = (int64_t)CTB_RED_BLOCK_THREADS * 4 * CTB_RED_UNROLL;
+        const bool many_lines = g.nout >= (int64_t)sm_count * 32;
+        const bool warp = g.rlen <= kRowsWarpSmall ||
+                          (many_lines && (g.rlen <= kRowsWarpMax || g.rlen % cta_batch != 0));
+        c.shape = warp ? SH_ROWS_WARP : SH_ROWS_BLOCK;
         return c;
     }
     // column case: innermost outer dim contiguous
