@@ -44,7 +44,7 @@ EXPORTED_SYMBOLS = [
     "ctb_reduce_ws", "ctb_reduce_dim_noalloc", "ctb_reduce_full_partial", "ctb_finalize_full", "ctb_softmax_lastdim",
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
     "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
-    "ctb_copy_into", "ctb_cat",
+    "ctb_copy_into", "ctb_cat", "ctb_channel_moments", "ctb_batchnorm_apply",
 ]
 
 
@@ -116,6 +116,8 @@ def lib() -> ctypes.CDLL:
     L.ctb_accumulate_grad.argtypes = [vp, vp, vd]
     L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
     L.ctb_copy_into.argtypes = [vp, vp, vd]
+    L.ctb_channel_moments.argtypes = [vp, vp, vp, vd]
+    L.ctb_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vp, vd]
     L.ctb_cat.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vd]
     L.ctb_adam_step.argtypes = [vp, vp, vd, vd] + [ctypes.c_double] * 4 + [i32, ctypes.c_double, i32, vd]
     L.ctb_binary_host.argtypes = [i32, vp, vp, vp, i32]
@@ -356,6 +358,28 @@ def accumulate_grad(grad, src):
     with _device_guard(g):
         check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
     return grad
+
+
+def channel_moments(x):
+    """Per-channel (dim 1) mean and biased variance of a contiguous x[N, C, ...]: (mean, var)."""
+    xv = _as_dview(x)
+    c = xv.shape[1] if len(xv.shape) > 1 else 0
+    mean, var = _new_out(xv, (c,)), _new_out(xv, (c,))
+    with _device_guard(xv):
+        check(lib().ctb_channel_moments(xv.cview(), DView.of(mean).cview(), DView.of(var).cview(), _stream_ptr(xv)))
+    return mean, var
+
+
+def batchnorm_apply(x, mean, var, gamma=None, beta=None, eps: float = 1e-5, out=None):
+    """((x - mean[c]) * (var[c] + eps)^-0.5) * gamma[c] + beta[c] for a contiguous x[N, C, ...]."""
+    xv = _as_dview(x)
+    opt = lambda t: None if t is None else _as_dview(t).cview()
+    if out is None:
+        out = _new_out(xv, xv.shape)
+    with _device_guard(xv):
+        check(lib().ctb_batchnorm_apply(xv.cview(), _as_dview(mean).cview(), _as_dview(var).cview(),
+                                        opt(gamma), opt(beta), float(eps), DView.of(out).cview(), _stream_ptr(xv)))
+    return out
 
 
 def copy_into(src, dst):

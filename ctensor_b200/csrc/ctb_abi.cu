@@ -801,6 +801,83 @@ int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream)
     return launch_accumulate_strided(grad->dtype, nd, tshape, tstride, cur.stride, elem_ptr_mut(grad), elem_ptr(&cur), st);
 }
 
+// ---- BatchNorm forward ---------------------------------------------------------------------------------
+namespace {
+
+// x[N, C, trailing...] contiguous fp32 -> (N, C, S)
+int batchnorm_geom(const ctb_view* x, int64_t* N, int64_t* C, int64_t* S, const char* who) {
+    int rc;
+    if ((rc = check_view(x, "batchnorm: null input", who))) return rc;
+    if (x->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "%s: only Float32 is supported", who);
+    if (x->ndim < 2) return set_error(CTB_ERR_SHAPE, "%s: input needs [batch, channels, ...]", who);
+    if (!view_contiguous(x)) return set_error(CTB_ERR_SHAPE, "%s: input must be contiguous", who);
+    *N = x->shape[0];
+    *C = x->shape[1];
+    *S = 1;
+    for (int d = 2; d < x->ndim; ++d) *S *= x->shape[d];
+    return CTB_OK;
+}
+
+// A per-channel parameter: C elements in any view whose other dims have extent 1.
+int channel_param(const ctb_view* v, int64_t C, const char* who, const float** ptr, int64_t* stride) {
+    int rc;
+    if ((rc = check_view(v, "batchnorm: null parameter", who))) return rc;
+    if (v->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "%s: parameters must be Float32", who);
+    if (view_numel(v) != C) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+    *stride = 0;
+    for (int d = 0; d < v->ndim; ++d) if (v->shape[d] == C && C > 1) *stride = v->stride[d];
+    *ptr = (const float*)elem_ptr(v);
+    return CTB_OK;
+}
+
+}  // namespace
+
+int ctb_channel_moments(const ctb_view* x, const ctb_view* mean, const ctb_view* var, void* stream) {
+    int rc;
+    int64_t N, C, S;
+    if ((rc = batchnorm_geom(x, &N, &C, &S, "channel_moments"))) return rc;
+    if ((rc = check_out(mean, C, CTB_F32, "channel_moments"))) return rc;
+    if ((rc = check_out(var, C, CTB_F32, "channel_moments"))) return rc;
+    if (N * S == 0) return set_error(CTB_ERR_SHAPE, "channel_moments: empty batch");
+    if (S == 1) {
+        // [N, C]: the statistics are column reductions; the column kernel reads whole rows
+        ctb_view x2 = *x;
+        x2.ndim = 2;
+        x2.shape[0] = N; x2.shape[1] = C;
+        x2.stride[0] = C; x2.stride[1] = 1;
+        if ((rc = ctb_reduce(CTB_MEAN, &x2, 0, mean, stream))) return rc;
+        return ctb_reduce(CTB_VAR, &x2, 0, var, stream);
+    }
+    DeviceInfo di;
+    if ((rc = current_device_info(&di))) return rc;
+    const size_t need = channel_moments_workspace_bytes(C, di.sm_count);
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(need, &ws))) return rc;
+    return launch_channel_moments((const float*)elem_ptr(x), (float*)elem_ptr_mut(mean), (float*)elem_ptr_mut(var),
+                                  N, C, S, ws, need, (cudaStream_t)stream);
+}
+
+int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view* var, const ctb_view* gamma,
+                        const ctb_view* beta, double eps, const ctb_view* out, void* stream) {
+    int rc;
+    int64_t N, C, S;
+    if ((rc = batchnorm_geom(x, &N, &C, &S, "batchnorm"))) return rc;
+    const float *pm, *pv, *pg = nullptr, *pb = nullptr;
+    int64_t sm, sv, sg = 0, sb = 0;
+    if ((rc = channel_param(mean, C, "batchnorm", &pm, &sm))) return rc;
+    if ((rc = channel_param(var, C, "batchnorm", &pv, &sv))) return rc;
+    if (gamma && (rc = channel_param(gamma, C, "batchnorm", &pg, &sg))) return rc;
+    if (beta && (rc = channel_param(beta, C, "batchnorm", &pb, &sb))) return rc;
+    if ((rc = check_out(out, N * C * S, CTB_F32, "batchnorm"))) return rc;
+    if (N * C * S == 0) return CTB_OK;
+    // 1/sqrt(var + eps) per channel lives behind the workspace's ticket region
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(kTicketBytes + (size_t)C * sizeof(float), &ws))) return rc;
+    return launch_batchnorm_apply((const float*)elem_ptr(x), pm, sm, pv, sv, pg, sg, pb, sb, eps,
+                                  (float*)((char*)ws + kTicketBytes), (float*)elem_ptr_mut(out), N, C, S,
+                                  (cudaStream_t)stream);
+}
+
 // ---- copies into existing tensors: copy_into, cat ----------------------------------------------------------
 int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream) {
     int rc;

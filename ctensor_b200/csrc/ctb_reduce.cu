@@ -591,7 +591,12 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
     uint32_t* tickets = (uint32_t*)ws;
     typename Pol::Acc* partials = (typename Pol::Acc*)((char*)ws + kCounterBytes);
     static_assert(sizeof(typename Pol::Acc) <= 16, "accumulator larger than the scratch slot");
-    switch (c.shape) {
+    Shape shape = c.shape;
+    // variance does three fp64 operations per element after the loads of a CTA-wide batch have
+    // landed; with a CTA per line that phase is not covered by loads, with a warp per line other
+    // warps' loads cover it ([16384,16384]: 6.1 against 5.4 TB/s) — if there are lines enough
+    if (shape == SH_ROWS_BLOCK && NeedsShift<Pol>::value && g.nout >= (int64_t)sm_count * 64) shape = SH_ROWS_WARP;
+    switch (shape) {
     case SH_ROWS_WARP: {
         // one warp per row, one pass per CTA (a persistent grid measured slower)
         int64_t blocks = ceil_div(g.nout, T / 32);

@@ -64,4 +64,12 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
                      const float* beta, int64_t bstride, double eps, float* out,
                      cudaStream_t stream);
 
+// BatchNorm forward pieces for a contiguous fp32 x[N, C, S] (ctb_norm.cu).
+size_t channel_moments_workspace_bytes(int64_t C, int sm_count);
+int launch_channel_moments(const float* x, float* mean, float* var, int64_t N, int64_t C, int64_t S,
+                           void* ws, size_t ws_bytes, cudaStream_t stream);
+int launch_batchnorm_apply(const float* x, const float* mean, int64_t mstride, const float* var, int64_t vstride,
+                           const float* gamma, int64_t gstride, const float* beta, int64_t bstride, double eps,
+                           float* rstd_scratch, float* out, int64_t N, int64_t C, int64_t S, cudaStream_t stream);
+
 }  // namespace ctb

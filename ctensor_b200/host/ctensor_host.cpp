@@ -508,6 +508,35 @@ Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
     return out;
 }
 
+// src/neuralnet/batchnorm/batchnorm.cpp:46-61 and :103-113.
+void channel_moments(const Tensor& x, Tensor& mean, Tensor& var) {
+    if (!x.impl) throw std::runtime_error("batchnorm: null input");
+    if (x.impl->ndim < 2) throw std::runtime_error("batchnorm: input needs [batch, channels, ...]");
+    ensure_device();
+    const Tensor xc = x.is_contiguous() ? x : x.contiguous();
+    mean = Tensor({x.impl->shape[1]}, x._dtype(), false);
+    var = Tensor({x.impl->shape[1]}, x._dtype(), false);
+    const ctb_view vx = view_of(xc, "batchnorm"), vm = view_of(mean, "batchnorm"), vv = view_of(var, "batchnorm");
+    check(ctb_channel_moments(&vx, &vm, &vv, nullptr));
+    after_op();
+}
+
+Tensor batch_norm_apply(const Tensor& x, const Tensor& mean, const Tensor& var, const Tensor& gamma,
+                        const Tensor& beta, double eps) {
+    if (!x.impl || !mean.impl || !var.impl) throw std::runtime_error("batchnorm: null input");
+    ensure_device();
+    const Tensor xc = x.is_contiguous() ? x : x.contiguous();
+    Tensor out(x.shape(), x._dtype(), false);
+    const ctb_view vx = view_of(xc, "batchnorm"), vm = view_of(mean, "batchnorm"), vv = view_of(var, "batchnorm"),
+                   vo = view_of(out, "batchnorm");
+    ctb_view vg, vb;
+    if (gamma.impl) vg = view_of(gamma, "batchnorm");
+    if (beta.impl) vb = view_of(beta, "batchnorm");
+    check(ctb_batchnorm_apply(&vx, &vm, &vv, gamma.impl ? &vg : nullptr, beta.impl ? &vb : nullptr, eps, &vo, nullptr));
+    after_op();
+    return out;
+}
+
 Tensor log_softmax(const Tensor& a) {
     if (!a.impl) throw std::runtime_error("log_softmax: null input");
     ensure_device();

@@ -74,6 +74,12 @@ Tensor causal_softmax(const Tensor& a);
 Tensor log_softmax(const Tensor& a);                 // the chain inside Loss::CrossEntropy
 
 Tensor cat(const std::vector<Tensor>& tensors, size_t dim);
+
+// BatchNorm::forward of the reference in two calls (its statistics block and its normalisation
+// block): x is a contiguous Float32 [N, C, ...]; mean/var/gamma/beta hold C elements.
+void channel_moments(const Tensor& x, Tensor& mean, Tensor& var);
+Tensor batch_norm_apply(const Tensor& x, const Tensor& mean, const Tensor& var, const Tensor& gamma,
+                        const Tensor& beta, double eps = 1e-5);
 Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps = 1e-5);
 
 // operators

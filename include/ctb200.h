@@ -209,6 +209,18 @@ int ctb_log_softmax_lastdim(const ctb_view* x, const ctb_view* mask, const ctb_v
 int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_view* beta,
                           double eps, const ctb_view* out, void* stream);
 
+/* BatchNorm forward, src/neuralnet/batchnorm/batchnorm.cpp:40-113, for a contiguous fp32
+ * x[N, C, ...].  ctb_channel_moments: per-channel mean and biased variance over every dim but
+ * dim 1 (:46-61; the reference permutes, copies and runs mean / sub / mul / mean).
+ * ctb_batchnorm_apply: y = ((x - mean[c]) * (var[c] + eps)^-0.5) * gamma[c] + beta[c] with every
+ * step rounded to fp32 and the scalar steps in double (:103-113); mean/var/gamma/beta hold C
+ * elements (any view whose other dims are 1, e.g. [C] or [1,C,1,1]); gamma/beta may be NULL.
+ * The running-statistics update (:63-86) is C scalar operations and stays with the caller. */
+int ctb_channel_moments(const ctb_view* x, const ctb_view* mean, const ctb_view* var, void* stream);
+int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view* var,
+                        const ctb_view* gamma, const ctb_view* beta, double eps,
+                        const ctb_view* out, void* stream);
+
 /* ---- callers either side of the path --------------------------------------------------------
  * Tensor::gather, src/core/tensor.cpp:344-428: out[i] = x[i with coordinate `dim` replaced by
  * index[i]].  `index` is CTB_I32 with x's number of dims and extents no larger than x's outside

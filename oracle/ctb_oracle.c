@@ -758,3 +758,44 @@ int64_t orc_cat(const orc_view* const* in, int count, int dim, void* out) {
     }
     return run;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * BatchNorm forward for a contiguous fp32 x[N, C, S], src/neuralnet/batchnorm/batchnorm.cpp.
+ * Statistics (:46-61): mean = mean(x over n, s); var = mean((x - mean)^2), both with the
+ * reference's mean = (float)((double)(float)sum * (1.0/count)) and fp32 element-wise steps.
+ * Normalisation (:103-113): y = ((x - mean) * pow_scalar(add_scalar(var, eps), -0.5)) * gamma + beta.
+ * ---------------------------------------------------------------------------------------- */
+void orc_channel_moments(const float* x, int64_t N, int64_t C, int64_t S, float* mean, float* var) {
+    double count = (double)(N * S), inv = 1.0 / count;
+    #pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < C; ++c) {
+        double acc = 0.0;
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t s = 0; s < S; ++s) acc += (double)x[(n * C + c) * S + s];
+        float mu = (float)((double)(float)acc * inv);
+        double acc2 = 0.0;
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t s = 0; s < S; ++s) {
+                float d = x[(n * C + c) * S + s] - mu;
+                acc2 += (double)(d * d);
+            }
+        mean[c] = mu;
+        var[c] = (float)((double)(float)acc2 * inv);
+    }
+}
+
+void orc_batchnorm_apply(const float* x, int64_t N, int64_t C, int64_t S, const float* mean, const float* var,
+                         const float* gamma, const float* beta, double eps, float* out) {
+    #pragma omp parallel for schedule(static)
+    for (int64_t line = 0; line < N * C; ++line) {
+        int64_t c = line % C;
+        float ve = (float)((double)var[c] + eps);
+        float rstd = (float)pow((double)ve, -0.5);
+        for (int64_t s = 0; s < S; ++s) {
+            float y = (x[line * S + s] - mean[c]) * rstd;
+            if (gamma) y = y * gamma[c];
+            if (beta) y = y + beta[c];
+            out[line * S + s] = y;
+        }
+    }
+}

@@ -402,6 +402,44 @@ int64_t ref_accumulate_grad(const RefView* target, const void* grad_init, const 
     });
 }
 
+// BatchNorm forward statistics and normalisation with the reference's own operator sequence
+// (src/neuralnet/batchnorm/batchnorm.cpp:40-61 and :103-113; the sums go through mean_mp, the
+// function the dispatcher picks on hosts without AVX-512 — its AVX-512 path throws for dim-wise
+// reductions).  x: contiguous [N, C, ...]; out_mean/out_var: C floats.
+int64_t ref_channel_moments(const RefView* x, float* out_mean, float* out_var) {
+    return guarded([&] {
+        Tensor input = wrap(x);
+        const size_t ndim = input.impl->ndim;
+        std::vector<size_t> perm(ndim);
+        perm[0] = 1;
+        perm[1] = 0;
+        for (size_t i = 2; i < ndim; ++i) perm[i] = i;
+        const size_t C = input.impl->shape[1], rest = input.numel() / C;
+        Tensor flat = input.permute(perm).reshape({C, rest});
+        Tensor mean_val = mean_mp(flat, 1);
+        Tensor diff = diff_mp(flat, mean_val.reshape({C, 1}));
+        Tensor var_val = mean_mp(mult_mp(diff, diff), 1);
+        std::memcpy(out_mean, mean_val.impl->data->data.get(), C * 4);
+        std::memcpy(out_var, var_val.impl->data->data.get(), C * 4);
+        return (int64_t)C;
+    });
+}
+
+int64_t ref_batchnorm_apply(const RefView* x, const RefView* mean, const RefView* var, const RefView* gamma,
+                            const RefView* beta, double eps, void* out, int64_t cap) {
+    return guarded([&] {
+        Tensor input = wrap(x);
+        std::vector<size_t> bshape(input.impl->ndim, 1);
+        bshape[1] = input.impl->shape[1];
+        Tensor x_centered = diff_mp(input, wrap(mean).reshape(bshape));
+        Tensor inv_std = pow_scalar_mp(add_scalar_mp(wrap(var).reshape(bshape), eps), -0.5);
+        Tensor y = mult_mp(x_centered, inv_std);
+        if (gamma) y = mult_mp(y, wrap(gamma).reshape(bshape));
+        if (beta) y = add_mp(y, wrap(beta).reshape(bshape));
+        return emit(y, out, cap);
+    });
+}
+
 // cat_mp (src/core/opsmp.cpp:717-804).
 int64_t ref_cat(const RefView* const* in, int count, int dim, void* out, int64_t cap) {
     return guarded([&] {

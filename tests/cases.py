@@ -2,7 +2,7 @@
 and the GPU tests.  Every case is a dict:
 
     name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
-    'accgrad'|'optim'|'cat'), op, views (HostViews),
+    'accgrad'|'optim'|'cat'|'bn_moments'|'bn_apply'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -224,6 +224,22 @@ def all_cases():
     add(name="cat_f64_single", kind="cat", op=0, views=[Ad.permute([1, 0])], dim=0)
     add(name="cat_ragged_offset", kind="cat", op=0, views=[off, off.narrow(1, 2, 1), off.step(1, 3)], dim=1)
 
+    # ---- BatchNorm forward: moments of x[N,C,...] (op 0 -> mean, 1 -> var) and the normalisation ------------------
+    bn4 = HostView.contig(_n(52, (6, 5, 7, 8), 2.0) + np.float32(0.75))
+    bn3 = HostView.contig(_n(53, (33, 12, 20)))
+    bn2 = HostView.contig(_n(54, (257, 36), 3.0))
+    for nm, v in (("4d", bn4), ("3d", bn3), ("2d", bn2)):
+        c = v.shape[1]
+        add(name=f"bn_mean_{nm}", kind="bn_moments", op=0, views=[v], exact=False)
+        add(name=f"bn_var_{nm}", kind="bn_moments", op=1, views=[v], exact=False)
+        mu = HostView.contig(_n(55, (c,), 0.3))
+        vr = HostView.contig(np.abs(_n(56, (c,))) + np.float32(0.1))
+        gm = HostView.contig((_n(57, (c,), 0.02) + 1).astype(np.float32))
+        bt = HostView.contig(_n(58, (c,), 0.02))
+        add(name=f"bn_apply_{nm}", kind="bn_apply", op=0, views=[v, mu, vr, gm, bt], scalar=1e-5)
+    add(name="bn_apply_4d_no_affine", kind="bn_apply", op=0,
+        views=[bn4, HostView.contig(_n(55, (5,), 0.3)), HostView.contig(np.abs(_n(56, (5,))) + np.float32(0.1))], scalar=1e-3)
+
     # ---- optimizer steps: views = [parameter, gradient]; op = 0 SGD, 1 Adam, 2 AdamW; dim = number of steps ----
     w0 = HostView.contig(_n(49, (1003,), 0.5))
     gw = HostView.contig(_n(50, (1003,), 2.0))
@@ -261,6 +277,11 @@ def run_case(impl, case):
         return impl.gather(v[0], case["dim"], v[1])
     if k == "accgrad":
         return impl.accumulate_grad(v[0].numpy(), v[1])
+    if k == "bn_moments":
+        return impl.channel_moments(v[0].numpy())[case["op"]]
+    if k == "bn_apply":
+        p = [t.numpy() for t in v[1:]] + [None] * (5 - len(v))
+        return impl.batchnorm_apply(v[0].numpy(), p[0], p[1], p[2], p[3], case["scalar"])
     if k == "cat":
         return impl.cat(v, case["dim"])
     if k == "optim":

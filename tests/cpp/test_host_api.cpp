@@ -159,6 +159,18 @@ int main() {
     CHECK_THROWS(cat({Tensor::ones({2, 2}), Tensor::ones({3, 3})}, 0), std::runtime_error, "cat_mp: shape mismatch outside cat dim");
     CHECK_THROWS(cat({}, 0), std::runtime_error, "cat_mp: empty list");
 
+    // BatchNorm forward pieces: x[N=2, C=2, S=2]
+    Tensor bx = Tensor::from_vector({1, 3, 10, 30, 5, 7, 50, 70}, {2, 2, 2});
+    Tensor bm, bv;
+    channel_moments(bx, bm, bv);
+    CHECK_NEAR(bm[0], 4.0, 1e-6);
+    CHECK_NEAR(bm[1], 40.0, 1e-5);
+    CHECK_NEAR(bv[0], 5.0, 1e-5);
+    CHECK_NEAR(bv[1], 500.0, 1e-3);
+    Tensor by = batch_norm_apply(bx, bm, bv, Tensor::full({2}, 2.0), Tensor::full({2}, 1.0), 0.0);
+    CHECK_NEAR(by[0][0][0], 2.0 * (1.0 - 4.0) / std::sqrt(5.0) + 1.0, 1e-5);
+    CHECK_NEAR(by[1][1][1], 2.0 * (70.0 - 40.0) / std::sqrt(500.0) + 1.0, 1e-5);
+
     // errors: the reference's exception types and texts
     CHECK_THROWS(Tensor::ones({2, 3}) + Tensor::ones({2, 2}), std::runtime_error, "Shape mismatch in binary op");
     CHECK_THROWS(add(Tensor(), a), std::runtime_error, "binary_op: null input");

@@ -181,6 +181,11 @@ class Oracle:
         L.orc_gather.argtypes = [vp, ctypes.c_int, vp, ctypes.c_void_p]
         L.orc_accumulate_grad.restype = ctypes.c_int64
         L.orc_accumulate_grad.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_int, vp]
+        L.orc_channel_moments.restype = None
+        L.orc_channel_moments.argtypes = [ctypes.c_void_p] + [ctypes.c_int64] * 3 + [ctypes.c_void_p] * 2
+        L.orc_batchnorm_apply.restype = None
+        L.orc_batchnorm_apply.argtypes = ([ctypes.c_void_p] + [ctypes.c_int64] * 3 + [ctypes.c_void_p] * 4 +
+                                          [ctypes.c_double, ctypes.c_void_p])
         L.orc_cat.restype = ctypes.c_int64
         L.orc_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.orc_sgd_step.restype = None
@@ -255,6 +260,32 @@ class Oracle:
         assert n == out.size, "oracle accumulate_grad failed"
         return out
 
+    @staticmethod
+    def _ncs(x: np.ndarray):
+        n, c = x.shape[0], x.shape[1]
+        return n, c, int(np.prod(x.shape[2:], dtype=np.int64)) if x.ndim > 2 else 1
+
+    def channel_moments(self, x: np.ndarray):
+        """x: contiguous fp32 [N, C, ...] -> (mean[C], var[C])."""
+        x = np.ascontiguousarray(x, np.float32)
+        n, c, s = self._ncs(x)
+        mean, var = np.empty(c, np.float32), np.empty(c, np.float32)
+        self.lib.orc_channel_moments(x.ctypes.data, n, c, s, mean.ctypes.data, var.ctypes.data)
+        return mean, var
+
+    def batchnorm_apply(self, x: np.ndarray, mean, var, gamma=None, beta=None, eps=1e-5) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        n, c, s = self._ncs(x)
+        out = np.empty_like(x)
+        ptr = lambda a: None if a is None else np.ascontiguousarray(a, np.float32).ctypes.data
+        keep = [np.ascontiguousarray(a, np.float32) for a in (mean, var)]
+        g = None if gamma is None else np.ascontiguousarray(gamma, np.float32)
+        b = None if beta is None else np.ascontiguousarray(beta, np.float32)
+        self.lib.orc_batchnorm_apply(x.ctypes.data, n, c, s, keep[0].ctypes.data, keep[1].ctypes.data,
+                                     None if g is None else g.ctypes.data, None if b is None else b.ctypes.data,
+                                     eps, out.ctypes.data)
+        return out
+
     def cat(self, views, dim: int) -> np.ndarray:
         shape = list(views[0].shape)
         shape[dim] = sum(v.shape[dim] for v in views)
@@ -321,6 +352,10 @@ class Reference:
         L.ref_gather.argtypes = [vp, ctypes.c_int, vp, vd, i64]
         L.ref_accumulate_grad.restype = i64
         L.ref_accumulate_grad.argtypes = [vp, vd, vp, vd, i64]
+        L.ref_channel_moments.restype = i64
+        L.ref_channel_moments.argtypes = [vp, vd, vd]
+        L.ref_batchnorm_apply.restype = i64
+        L.ref_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vd, i64]
         L.ref_cat.restype = i64
         L.ref_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, vd, i64]
         L.ref_optimizer_steps.restype = i64
@@ -391,6 +426,22 @@ class Reference:
         target = HostView.contig(np.zeros(g.shape, g.dtype))
         return self._check(self.lib.ref_accumulate_grad(target.cview(), g.ctypes.data, src.cview(),
                                                         out.ctypes.data, out.nbytes), out)
+
+    def channel_moments(self, x: np.ndarray):
+        hv = HostView.contig(np.ascontiguousarray(x, np.float32))
+        c = hv.shape[1]
+        mean, var = np.empty(c, np.float32), np.empty(c, np.float32)
+        n = self.lib.ref_channel_moments(hv.cview(), mean.ctypes.data, var.ctypes.data)
+        if n < 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return mean, var
+
+    def batchnorm_apply(self, x, mean, var, gamma=None, beta=None, eps=1e-5):
+        hv = HostView.contig(np.ascontiguousarray(x, np.float32))
+        hp = [None if a is None else HostView.contig(np.ascontiguousarray(a, np.float32)) for a in (mean, var, gamma, beta)]
+        out = np.empty(hv.shape, np.float32)
+        return self._check(self.lib.ref_batchnorm_apply(hv.cview(), _ptr(hp[0]), _ptr(hp[1]), _ptr(hp[2]), _ptr(hp[3]),
+                                                        eps, out.ctypes.data, out.nbytes), out)
 
     def cat(self, views, dim):
         shape = list(views[0].shape)

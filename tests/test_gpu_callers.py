@@ -216,3 +216,51 @@ def test_cat_errors(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.cat([a], 2)
     assert e.value.code == 4
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 28, 28), (32, 64, 7, 7), (16, 3, 33, 65), (4096, 512), (1000, 37),
+                                   (8, 20000, 16), (3, 5, 2, 2, 6)])
+def test_batchnorm_forward_shapes(ct, shape):
+    torch.manual_seed(len(shape) * 7 + shape[1])
+    x = torch.randn(*shape, device="cuda") * 1.5 + 0.5
+    c = shape[1]
+    dims = [d for d in range(len(shape)) if d != 1]
+    mean, var = ct.channel_moments(x)
+    xd = x.double()
+    assert torch.allclose(mean.double(), xd.mean(dims), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(var.double(), xd.var(dims, unbiased=False), rtol=1e-5, atol=1e-7)
+    gamma = 1 + 0.1 * torch.randn(c, device="cuda")
+    beta = 0.1 * torch.randn(c, device="cuda")
+    y = ct.batchnorm_apply(x, mean, var, gamma, beta, 1e-5)
+    bshape = [1, c] + [1] * (len(shape) - 2)
+    want = (xd - mean.double().view(bshape)) / torch.sqrt(var.double().view(bshape) + 1e-5) * gamma.double().view(bshape) + beta.double().view(bshape)
+    assert torch.allclose(y.double(), want, rtol=2e-5, atol=2e-6)
+    # parameters given as [1, C, 1, ...] views, no affine part
+    y2 = ct.batchnorm_apply(x, mean.view(bshape), var.view(bshape), None, None, 1e-5)
+    want2 = (xd - mean.double().view(bshape)) / torch.sqrt(var.double().view(bshape) + 1e-5)
+    assert torch.allclose(y2.double(), want2, rtol=2e-5, atol=2e-6)
+
+
+def test_batchnorm_matches_oracle_bitwise_on_apply(ct, oracle):
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((9, 6, 10, 12)).astype(np.float32)
+    mean = rng.standard_normal(6).astype(np.float32)
+    var = (np.abs(rng.standard_normal(6)) + 0.2).astype(np.float32)
+    g = rng.standard_normal(6).astype(np.float32)
+    b = rng.standard_normal(6).astype(np.float32)
+    got = ct.batchnorm_apply(*(torch.from_numpy(a).cuda() for a in (x, mean, var, g, b)), 1e-5)
+    ref = oracle.batchnorm_apply(x, mean, var, g, b, 1e-5)
+    np.testing.assert_allclose(got.cpu().numpy(), ref, rtol=1e-6, atol=0)      # pow() may differ in the last bit
+
+
+def test_batchnorm_argument_checks(ct):
+    x = torch.zeros(4, 3, 5, device="cuda")
+    with pytest.raises(ct.CtbError) as e:
+        ct.channel_moments(x.permute(0, 2, 1))
+    assert "contiguous" in e.value.message
+    with pytest.raises(ct.CtbError) as e:
+        ct.batchnorm_apply(x, torch.zeros(4, device="cuda"), torch.zeros(3, device="cuda"))
+    assert e.value.code == 2
+    with pytest.raises(ct.CtbError) as e:
+        ct.channel_moments(torch.zeros(4, device="cuda"))
+    assert e.value.code == 2

@@ -41,6 +41,11 @@ def run_gpu(ct, case):
     if k == "accgrad":
         grad = torch.from_numpy(case["views"][0].numpy()).cuda()
         return ct.accumulate_grad(grad, dv[1])
+    if k == "bn_moments":
+        return ct.channel_moments(dv[0])[case["op"]]
+    if k == "bn_apply":
+        p = dv[1:] + [None] * (5 - len(dv))
+        return ct.batchnorm_apply(dv[0], p[0], p[1], p[2], p[3], case["scalar"])
     if k == "cat":
         return ct.cat(dv, case["dim"])
     if k == "optim":
