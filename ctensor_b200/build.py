@@ -47,7 +47,7 @@ def build(force: bool = False, extra_flags=(), verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    subprocess.check_call([nvcc, "-shared", "-o", LIB, *objs])
+    subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB, *objs])
     return LIB
 
 
