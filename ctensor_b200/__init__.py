@@ -45,6 +45,7 @@ EXPORTED_SYMBOLS = [
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
     "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
     "ctb_copy_into", "ctb_cat", "ctb_channel_moments", "ctb_batchnorm_apply",
+    "ctb_matmul",
 ]
 
 
@@ -116,6 +117,7 @@ def lib() -> ctypes.CDLL:
     L.ctb_accumulate_grad.argtypes = [vp, vp, vd]
     L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
     L.ctb_copy_into.argtypes = [vp, vp, vd]
+    L.ctb_matmul.argtypes = [vp, vp, vp, vd]
     L.ctb_channel_moments.argtypes = [vp, vp, vp, vd]
     L.ctb_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vp, vd]
     L.ctb_cat.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vd]
@@ -358,6 +360,18 @@ def accumulate_grad(grad, src):
     with _device_guard(g):
         check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
     return grad
+
+
+def matmul(a, b, out=None):
+    """matmul_mp: 2-d operands, or 3-d with one leading batch dim."""
+    av, bv = _as_dview(a), _as_dview(b)
+    if out is None:
+        batch = max(av.shape[0] if len(av.shape) == 3 else 1, bv.shape[0] if len(bv.shape) == 3 else 1)
+        shape = (av.shape[-2], bv.shape[-1]) if len(av.shape) < 3 and len(bv.shape) < 3 else (batch, av.shape[-2], bv.shape[-1])
+        out = _new_out(av, shape)
+    with _device_guard(av):
+        check(lib().ctb_matmul(av.cview(), bv.cview(), DView.of(out).cview(), _stream_ptr(av)))
+    return out
 
 
 def channel_moments(x):

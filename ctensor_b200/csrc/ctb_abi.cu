@@ -878,6 +878,28 @@ int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view*
                                   (cudaStream_t)stream);
 }
 
+// ---- matmul ------------------------------------------------------------------------------------------
+int ctb_matmul(const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream) {
+    int rc;
+    if ((rc = check_view(a, "matmul: null input", "matmul"))) return rc;
+    if ((rc = check_view(b, "matmul: null input", "matmul"))) return rc;
+    if (a->ndim < 2 || b->ndim < 2) return set_error(CTB_ERR_SHAPE, "matmul_mp requires at least 2D tensors");
+    if (a->ndim > 3 || b->ndim > 3) return set_error(CTB_ERR_SHAPE, "matmul: at most one batch dim is supported");
+    if (a->dtype != b->dtype) return set_error(CTB_ERR_DTYPE, "matmul: operands must have the same dtype");
+    const int64_t K = a->shape[a->ndim - 1], M = a->shape[a->ndim - 2], N = b->shape[b->ndim - 1];
+    if (b->shape[b->ndim - 2] != K) return set_error(CTB_ERR_SHAPE, "matmul_mp shape mismatch");
+    const int64_t batch_a = a->ndim == 3 ? a->shape[0] : 1, batch_b = b->ndim == 3 ? b->shape[0] : 1;
+    const int64_t batch = batch_a > batch_b ? batch_a : batch_b;
+    if ((batch_a != batch && batch_a != 1) || (batch_b != batch && batch_b != 1))
+        return set_error(CTB_ERR_SHAPE, "matmul_mp shape mismatch");
+    if ((rc = check_out(out, batch * M * N, a->dtype, "matmul"))) return rc;
+    const int64_t sa = (a->ndim == 3 && batch_a > 1) ? a->stride[0] : 0;
+    const int64_t sb = (b->ndim == 3 && batch_b > 1) ? b->stride[0] : 0;
+    return launch_matmul(a->dtype, elem_ptr(a), elem_ptr(b), elem_ptr_mut(out), batch, M, N, K,
+                         a->stride[a->ndim - 2], a->stride[a->ndim - 1], sa,
+                         b->stride[b->ndim - 2], b->stride[b->ndim - 1], sb, (cudaStream_t)stream);
+}
+
 // ---- copies into existing tensors: copy_into, cat ----------------------------------------------------------
 int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream) {
     int rc;

@@ -166,5 +166,11 @@ int launch_adam(float* param, const float* grad, float* m, float* v, int64_t n, 
                 double beta2, double eps, int step, double weight_decay, int decoupled_decay,
                 cudaStream_t stream);
 
+// c[batch][M][N] (contiguous) = a x b with the given element strides; a batch stride of 0 repeats
+// that operand for every batch entry.
+int launch_matmul(int dtype, const void* a, const void* b, void* c, int64_t batch, int64_t M, int64_t N, int64_t K,
+                  int64_t a_m, int64_t a_k, int64_t a_batch, int64_t b_k, int64_t b_n, int64_t b_batch,
+                  cudaStream_t stream);
+
 struct ReducePlan;   // ctb_reduce.cuh
 }  // namespace ctb

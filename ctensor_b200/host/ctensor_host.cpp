@@ -479,6 +479,23 @@ Tensor softmax(const Tensor& a, const Tensor& additive_mask) {
 }
 Tensor causal_softmax(const Tensor& a) { return softmax_impl(a, nullptr, 1); }
 
+// matmul_mp, src/core/opsmp.cpp:460-482 (shape rules) — the product itself runs in ctb_matmul.
+Tensor matmul(const Tensor& a, const Tensor& b) {
+    if (!a.impl || !b.impl) throw std::runtime_error("matmul: null input");
+    if (a.impl->ndim < 2 || b.impl->ndim < 2) throw std::runtime_error("matmul_mp requires at least 2D tensors");
+    if (b.impl->shape[b.impl->ndim - 2] != a.impl->shape[a.impl->ndim - 1]) throw std::runtime_error("matmul_mp shape mismatch");
+    ensure_device();
+    std::vector<size_t> res_shape = a.shape();
+    res_shape.back() = b.impl->shape[b.impl->ndim - 1];
+    const bool req = a.requires_grad() || b.requires_grad();
+    Tensor out(res_shape, a._dtype(), req);
+    const ctb_view va = view_of(a, "matmul"), vb = view_of(b, "matmul"), vo = view_of(out, "matmul");
+    check(ctb_matmul(&va, &vb, &vo, nullptr));
+    after_op();
+    if (req) attach_grad(out, "matmul", {a, b}, 0.0);
+    return out;
+}
+
 // cat_mp, src/core/opsmp.cpp:717-804.
 Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
     if (tensors.empty()) throw std::runtime_error("cat_mp: empty list");

@@ -74,6 +74,7 @@ Tensor causal_softmax(const Tensor& a);
 Tensor log_softmax(const Tensor& a);                 // the chain inside Loss::CrossEntropy
 
 Tensor cat(const std::vector<Tensor>& tensors, size_t dim);
+Tensor matmul(const Tensor& a, const Tensor& b);     // the arithmetic of matmul_mp (fp32, k ascending)
 
 // BatchNorm::forward of the reference in two calls (its statistics block and its normalisation
 // block): x is a contiguous Float32 [N, C, ...]; mean/var/gamma/beta hold C elements.

@@ -38,6 +38,7 @@ inline Tensor softplus_mp(const Tensor& a) { return softplus(a); }
 inline Tensor tanh_mp(const Tensor& a) { return tanh(a); }
 inline Tensor sigmoid_mp(const Tensor& a) { return sigmoid(a); }
 inline Tensor Relu_mp(const Tensor& a) { return relu(a); }
+inline Tensor matmul_mp(const Tensor& a, const Tensor& b) { return matmul(a, b); }
 inline Tensor cat_mp(const std::vector<Tensor>& tensors, size_t dim) { return cat(tensors, dim); }
 
 namespace ctb_host { int last_dim_if_negative(const Tensor& t, int dim); }

@@ -241,6 +241,15 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
  * Intermediate sums live in the library's per-device workspace (see ctb_reduce). */
 int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream);
 
+/* matmul_mp, src/core/opsmp.cpp:460-558 (the reference's scalar back-end): out = a x b for 2-d
+ * operands or 3-d operands with one leading batch dim (an operand without it, or with batch
+ * extent 1, is reused for every batch entry); any strides; `out` contiguous [batch, M, N] (or
+ * [M, N]).  Float32 accumulates in fp32 with k ascending and no fused multiply-add — bit-identical
+ * to matmul_mp; other dtypes accumulate in double.  A plain shared-memory kernel: it exists so
+ * that callers of the operator path which also multiply matrices run on the device, not as a
+ * tuned GEMM (tensor cores would change the arithmetic). */
+int ctb_matmul(const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream);
+
 /* Copy `src` into the existing (possibly strided) view `dst` of the same shape and dtype; `src`
  * may broadcast.  The building block of cat and of writes into slices. */
 int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream);

@@ -799,3 +799,40 @@ void orc_batchnorm_apply(const float* x, int64_t N, int64_t C, int64_t S, const 
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * matmul_mp, src/core/opsmp.cpp:460-558: 2-d operands or 3-d with one leading batch dim.
+ * Float32: fp32 accumulation, k ascending, unfused (the reference's k blocks of 64 store and
+ * reload the fp32 partial sum: the same sequence).  Other dtypes: double products and sum.
+ * out: contiguous [batch, M, N].  Returns the element count or -1.
+ * ---------------------------------------------------------------------------------------- */
+int64_t orc_matmul(const orc_view* a, const orc_view* b, void* out) {
+    if (a->ndim < 2 || b->ndim < 2 || a->ndim > 3 || b->ndim > 3 || a->dtype != b->dtype) return -1;
+    int64_t K = a->shape[a->ndim - 1], M = a->shape[a->ndim - 2], N = b->shape[b->ndim - 1];
+    if (b->shape[b->ndim - 2] != K) return -1;
+    int64_t ba = a->ndim == 3 ? a->shape[0] : 1, bb = b->ndim == 3 ? b->shape[0] : 1;
+    int64_t batch = ba > bb ? ba : bb;
+    if ((ba != batch && ba != 1) || (bb != batch && bb != 1)) return -1;
+    int64_t sa = (a->ndim == 3 && ba > 1) ? a->stride[0] : 0, sb = (b->ndim == 3 && bb > 1) ? b->stride[0] : 0;
+    int64_t am = a->stride[a->ndim - 2], ak = a->stride[a->ndim - 1];
+    int64_t bk = b->stride[b->ndim - 2], bn = b->stride[b->ndim - 1];
+    int dt = a->dtype;
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t bi = 0; bi < batch; ++bi)
+        for (int64_t m = 0; m < M; ++m)
+            for (int64_t n = 0; n < N; ++n) {
+                int64_t ia = a->offset + bi * sa + m * am, ib = b->offset + bi * sb + n * bn;
+                if (dt == ORC_F32) {
+                    const float* pa = (const float*)a->base;
+                    const float* pb = (const float*)b->base;
+                    float sum = 0.0f;
+                    for (int64_t k = 0; k < K; ++k) sum += pa[ia + k * ak] * pb[ib + k * bk];
+                    ((float*)out)[(bi * M + m) * N + n] = sum;
+                } else {
+                    double sum = 0.0;
+                    for (int64_t k = 0; k < K; ++k) sum += rd(a->base, ia + k * ak, dt) * rd(b->base, ib + k * bk, dt);
+                    wr(out, (bi * M + m) * N + n, dt, sum);
+                }
+            }
+    return batch * M * N;
+}

@@ -440,6 +440,11 @@ int64_t ref_batchnorm_apply(const RefView* x, const RefView* mean, const RefView
     });
 }
 
+// matmul_mp (src/core/opsmp.cpp:460-558), the scalar back-end.
+int64_t ref_matmul(const RefView* a, const RefView* b, void* out, int64_t cap) {
+    return guarded([&] { return emit(matmul_mp(wrap(a), wrap(b)), out, cap); });
+}
+
 // cat_mp (src/core/opsmp.cpp:717-804).
 int64_t ref_cat(const RefView* const* in, int count, int dim, void* out, int64_t cap) {
     return guarded([&] {

@@ -2,7 +2,7 @@
 and the GPU tests.  Every case is a dict:
 
     name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
-    'accgrad'|'optim'|'cat'|'bn_moments'|'bn_apply'), op, views (HostViews),
+    'accgrad'|'optim'|'cat'|'bn_moments'|'bn_apply'|'matmul'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -224,6 +224,20 @@ def all_cases():
     add(name="cat_f64_single", kind="cat", op=0, views=[Ad.permute([1, 0])], dim=0)
     add(name="cat_ragged_offset", kind="cat", op=0, views=[off, off.narrow(1, 2, 1), off.step(1, 3)], dim=1)
 
+    # ---- matmul_mp (left operand carries the batch dim, as the reference's result shape does) ----------------------
+    ma = HostView.contig(_n(59, (70, 45)))
+    mb = HostView.contig(_n(60, (45, 33)))
+    add(name="matmul_2d", kind="matmul", op=0, views=[ma, mb])
+    add(name="matmul_2d_transposed_b", kind="matmul", op=0, views=[ma, HostView.contig(_n(61, (33, 45))).permute([1, 0])])
+    add(name="matmul_2d_transposed_a", kind="matmul", op=0, views=[HostView.contig(_n(62, (45, 70))).permute([1, 0]), mb])
+    add(name="matmul_3d", kind="matmul", op=0, views=[HostView.contig(_n(63, (5, 17, 130))), HostView.contig(_n(64, (5, 130, 9)))])
+    add(name="matmul_3d_shared_b", kind="matmul", op=0, views=[HostView.contig(_n(65, (4, 64, 64))), HostView.contig(_n(66, (64, 64)))])
+    add(name="matmul_long_k", kind="matmul", op=0, views=[HostView.contig(_n(67, (3, 1000))), HostView.contig(_n(68, (1000, 2)))])
+    add(name="matmul_special", kind="matmul", op=0,
+        views=[HostView.contig(SPECIAL_F32[:40].reshape(5, 8)), HostView.contig(SPECIAL_F32[5:45].reshape(8, 5))])
+    add(name="matmul_i32", kind="matmul", op=0, views=[Ai, HostView.contig(_rng(69).integers(-9, 9, (9, 4)).astype(np.int32))])
+    add(name="matmul_f64", kind="matmul", op=0, views=[Ad, HostView.contig(_rng(70).standard_normal((6, 7)))])
+
     # ---- BatchNorm forward: moments of x[N,C,...] (op 0 -> mean, 1 -> var) and the normalisation ------------------
     bn4 = HostView.contig(_n(52, (6, 5, 7, 8), 2.0) + np.float32(0.75))
     bn3 = HostView.contig(_n(53, (33, 12, 20)))
@@ -277,6 +291,8 @@ def run_case(impl, case):
         return impl.gather(v[0], case["dim"], v[1])
     if k == "accgrad":
         return impl.accumulate_grad(v[0].numpy(), v[1])
+    if k == "matmul":
+        return impl.matmul(v[0], v[1])
     if k == "bn_moments":
         return impl.channel_moments(v[0].numpy())[case["op"]]
     if k == "bn_apply":

@@ -159,6 +159,16 @@ int main() {
     CHECK_THROWS(cat({Tensor::ones({2, 2}), Tensor::ones({3, 3})}, 0), std::runtime_error, "cat_mp: shape mismatch outside cat dim");
     CHECK_THROWS(cat({}, 0), std::runtime_error, "cat_mp: empty list");
 
+    // Linear::forward (src/neuralnet/layer.cpp:32-37): matmul + bias
+    Tensor mx = Tensor::from_vector({1, 2, 3, 4, 5, 6}, {2, 3});
+    Tensor mw = Tensor::from_vector({1, 0, 0, 1, 1, 1}, {3, 2});
+    Tensor my = matmul_mp(mx, mw) + Tensor::from_vector({10, 20}, {1, 2});
+    CHECK_NEAR(my[0][0], 14.0, 0.0);
+    CHECK_NEAR(my[0][1], 25.0, 0.0);
+    CHECK_NEAR(my[1][0], 20.0, 0.0);
+    CHECK_NEAR(my[1][1], 31.0, 0.0);
+    CHECK_THROWS(matmul(mx, mx), std::runtime_error, "matmul_mp shape mismatch");
+
     // BatchNorm forward pieces: x[N=2, C=2, S=2]
     Tensor bx = Tensor::from_vector({1, 3, 10, 30, 5, 7, 50, 70}, {2, 2, 2});
     Tensor bm, bv;

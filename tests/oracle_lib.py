@@ -140,6 +140,11 @@ def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
     return tuple(out)
 
 
+def matmul_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
+    """Result shape of matmul_mp (the left operand's shape with the last extent replaced)."""
+    return tuple(a[:-1]) + (b[-1],)
+
+
 def reduced_shape(shape: Sequence[int], dim: int) -> tuple:
     if dim == -1:
         return (1,)
@@ -186,6 +191,8 @@ class Oracle:
         L.orc_batchnorm_apply.restype = None
         L.orc_batchnorm_apply.argtypes = ([ctypes.c_void_p] + [ctypes.c_int64] * 3 + [ctypes.c_void_p] * 4 +
                                           [ctypes.c_double, ctypes.c_void_p])
+        L.orc_matmul.restype = ctypes.c_int64
+        L.orc_matmul.argtypes = [vp, vp, ctypes.c_void_p]
         L.orc_cat.restype = ctypes.c_int64
         L.orc_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.orc_sgd_step.restype = None
@@ -258,6 +265,12 @@ class Oracle:
         shape = (ctypes.c_int64 * MAX_DIMS)(*out.shape)
         n = self.lib.orc_accumulate_grad(out.ctypes.data, shape, out.ndim, src.cview())
         assert n == out.size, "oracle accumulate_grad failed"
+        return out
+
+    def matmul(self, a: HostView, b: HostView) -> np.ndarray:
+        out = np.empty(matmul_shape(a.shape, b.shape), NP_DTYPES[a.dtype])
+        n = self.lib.orc_matmul(a.cview(), b.cview(), out.ctypes.data)
+        assert n == out.size, "oracle matmul failed"
         return out
 
     @staticmethod
@@ -356,6 +369,8 @@ class Reference:
         L.ref_channel_moments.argtypes = [vp, vd, vd]
         L.ref_batchnorm_apply.restype = i64
         L.ref_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vd, i64]
+        L.ref_matmul.restype = i64
+        L.ref_matmul.argtypes = [vp, vp, vd, i64]
         L.ref_cat.restype = i64
         L.ref_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, vd, i64]
         L.ref_optimizer_steps.restype = i64
@@ -426,6 +441,10 @@ class Reference:
         target = HostView.contig(np.zeros(g.shape, g.dtype))
         return self._check(self.lib.ref_accumulate_grad(target.cview(), g.ctypes.data, src.cview(),
                                                         out.ctypes.data, out.nbytes), out)
+
+    def matmul(self, a, b):
+        out = np.empty(matmul_shape(a.shape, b.shape), NP_DTYPES[a.dtype])
+        return self._check(self.lib.ref_matmul(a.cview(), b.cview(), out.ctypes.data, out.nbytes), out)
 
     def channel_moments(self, x: np.ndarray):
         hv = HostView.contig(np.ascontiguousarray(x, np.float32))

@@ -264,3 +264,25 @@ def test_batchnorm_argument_checks(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.channel_moments(torch.zeros(4, device="cuda"))
     assert e.value.code == 2
+
+
+def test_matmul_large_is_bit_identical_to_the_scalar_reference_order(ct, oracle):
+    rng = np.random.default_rng(21)
+    a = HostView.contig(rng.standard_normal((257, 770)).astype(np.float32))
+    b = HostView.contig(rng.standard_normal((770, 515)).astype(np.float32))
+    got = ct.matmul(to_device(a), to_device(b))
+    assert_bits_equal(got, oracle.matmul(a, b), "matmul 257x770x515")
+    # batched, the right operand shared and transposed
+    a3 = HostView.contig(rng.standard_normal((6, 100, 64)).astype(np.float32))
+    bt = HostView.contig(rng.standard_normal((48, 64)).astype(np.float32)).permute([1, 0])
+    assert_bits_equal(ct.matmul(to_device(a3), to_device(bt)), oracle.matmul(a3, bt), "batched matmul")
+
+
+def test_matmul_errors(ct):
+    x = torch.zeros(4, 5, device="cuda")
+    with pytest.raises(ct.CtbError) as e:
+        ct.matmul(x, x)
+    assert "matmul_mp shape mismatch" in e.value.message
+    with pytest.raises(ct.CtbError) as e:
+        ct.matmul(torch.zeros(5, device="cuda"), x, out=torch.zeros(4, device="cuda"))
+    assert "requires at least 2D" in e.value.message

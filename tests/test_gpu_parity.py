@@ -41,6 +41,8 @@ def run_gpu(ct, case):
     if k == "accgrad":
         grad = torch.from_numpy(case["views"][0].numpy()).cuda()
         return ct.accumulate_grad(grad, dv[1])
+    if k == "matmul":
+        return ct.matmul(dv[0], dv[1])
     if k == "bn_moments":
         return ct.channel_moments(dv[0])[case["op"]]
     if k == "bn_apply":
