@@ -45,7 +45,7 @@ EXPORTED_SYMBOLS = [
     "ctb_layernorm_lastdim", "ctb_binary_host", "ctb_unary_host", "ctb_reduce_host",
     "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
     "ctb_copy_into", "ctb_cat", "ctb_channel_moments", "ctb_batchnorm_apply",
-    "ctb_matmul",
+    "ctb_matmul", "ctb_optimizer_step",
 ]
 
 
@@ -57,6 +57,14 @@ class CtbError(RuntimeError):
         super().__init__(f"{STATUS_NAMES.get(code, code)}: {message}")
         self.code = code
         self.message = message
+
+
+class OptimizerHyper(ctypes.Structure):
+    """struct ctb_optimizer_hyper."""
+    _fields_ = [(n, ctypes.c_double) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "alpha")]
+
+
+(OPT_SGD, OPT_ADAM, OPT_ADAMW, OPT_ADAMAX, OPT_NADAM, OPT_RADAM, OPT_RMSPROP, OPT_ADAGRAD, OPT_LION) = range(9)
 
 
 class View(ctypes.Structure):
@@ -118,6 +126,7 @@ def lib() -> ctypes.CDLL:
     L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
     L.ctb_copy_into.argtypes = [vp, vp, vd]
     L.ctb_matmul.argtypes = [vp, vp, vp, vd]
+    L.ctb_optimizer_step.argtypes = [i32, vp, vp, vd, vd, ctypes.POINTER(OptimizerHyper), i32, vd]
     L.ctb_channel_moments.argtypes = [vp, vp, vp, vd]
     L.ctb_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vp, vd]
     L.ctb_cat.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vd]
@@ -439,6 +448,18 @@ def adam_step(param, grad, m, v, lr: float, step: int, beta1: float = 0.9, beta2
                                   float(beta2), float(eps), int(step),
                                   0.0 if weight_decay is None else float(weight_decay),
                                   0 if weight_decay is None else 1, _stream_ptr(p)))
+    return param
+
+
+def optimizer_step(kind: int, param, grad, state1, state2, step: int, lr: float, beta1: float = 0.9,
+                   beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0, alpha: float = 0.99):
+    """One in-place step of any of the reference's optimizers (OPT_* codes)."""
+    p, g = _as_dview(param), _as_dview(grad)
+    h = OptimizerHyper(lr, beta1, beta2, eps, weight_decay, alpha)
+    with _device_guard(p):
+        check(lib().ctb_optimizer_step(kind, p.cview(), g.cview(), None if state1 is None else state1.data_ptr(),
+                                       None if state2 is None else state2.data_ptr(), ctypes.byref(h), int(step),
+                                       _stream_ptr(p)))
     return param
 
 

@@ -979,6 +979,24 @@ int ctb_adam_step(const ctb_view* param, const ctb_view* grad, float* m, float* 
                        beta2, eps, step, weight_decay, decoupled_decay, (cudaStream_t)stream);
 }
 
+int ctb_optimizer_step(int kind, const ctb_view* param, const ctb_view* grad, float* state1, float* state2,
+                       const ctb_optimizer_hyper* hyper, int step, void* stream) {
+    if (!hyper) return set_error(CTB_ERR_NULL, "optimizer step: null hyper-parameters");
+    if (kind == CTB_OPT_SGD) return ctb_sgd_step(param, grad, hyper->lr, stream);
+    if (kind == CTB_OPT_ADAM || kind == CTB_OPT_ADAMW)
+        return ctb_adam_step(param, grad, state1, state2, hyper->lr, hyper->beta1, hyper->beta2, hyper->eps, step,
+                             hyper->weight_decay, kind == CTB_OPT_ADAMW, stream);
+    if (kind < 0 || kind >= CTB_OPTIMIZER_COUNT) return set_error(CTB_ERR_ARG, "optimizer step: unknown optimizer %d", kind);
+    int rc;
+    if ((rc = optimizer_operands(param, grad, "optimizer_step"))) return rc;
+    if (param->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "optimizer_step: only Float32 parameters are updated");
+    const bool two = kind == CTB_OPT_ADAMAX || kind == CTB_OPT_NADAM || kind == CTB_OPT_RADAM;
+    if (!state1 || (two && !state2)) return set_error(CTB_ERR_NULL, "optimizer_step: null state buffer");
+    if (step < 1) return set_error(CTB_ERR_ARG, "optimizer_step: the step count starts at 1");
+    return launch_optimizer(kind, (float*)elem_ptr_mut(param), (const float*)elem_ptr(grad), state1, state2,
+                            view_numel(param), *hyper, step, (cudaStream_t)stream);
+}
+
 // ---- host-buffer entry points --------------------------------------------------------------------------
 static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* b, double scalar,
                             const ctb_view* out, int device) {

@@ -172,5 +172,8 @@ int launch_matmul(int dtype, const void* a, const void* b, void* c, int64_t batc
                   int64_t a_m, int64_t a_k, int64_t a_batch, int64_t b_k, int64_t b_n, int64_t b_batch,
                   cudaStream_t stream);
 
+int launch_optimizer(int kind, float* param, const float* grad, float* state1, float* state2, int64_t n,
+                     const ctb_optimizer_hyper& hyper, int step, cudaStream_t stream);
+
 struct ReducePlan;   // ctb_reduce.cuh
 }  // namespace ctb

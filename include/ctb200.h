@@ -271,6 +271,23 @@ int ctb_adam_step(const ctb_view* param, const ctb_view* grad, float* m, float* 
                   double beta1, double beta2, double eps, int step, double weight_decay,
                   int decoupled_decay, void* stream);
 
+/* The other optimizers of src/neuralnet/train_utils.h (fp32 parameters, contiguous, in place):
+ * Adamax :190-239 (state1 = m, state2 = u), NAdam :241-291 (m, v), RAdam :293-355 (m, v),
+ * RMSprop :357-396 (state1 = v; hyper.alpha), Adagrad :398-437 (state1 = sum of squares),
+ * Lion :439-494 (state1 = m; hyper.weight_decay).  state buffers: device memory, param's element
+ * count, zero before the first step; state2 may be NULL where unused.  CTB_OPT_SGD / ADAM / ADAMW
+ * are routed to ctb_sgd_step / ctb_adam_step.  `step` is the 1-based step count. */
+enum ctb_optimizer {
+    CTB_OPT_SGD = 0, CTB_OPT_ADAM = 1, CTB_OPT_ADAMW = 2, CTB_OPT_ADAMAX = 3, CTB_OPT_NADAM = 4,
+    CTB_OPT_RADAM = 5, CTB_OPT_RMSPROP = 6, CTB_OPT_ADAGRAD = 7, CTB_OPT_LION = 8,
+    CTB_OPTIMIZER_COUNT
+};
+typedef struct ctb_optimizer_hyper {
+    double lr, beta1, beta2, eps, weight_decay, alpha;
+} ctb_optimizer_hyper;
+int ctb_optimizer_step(int kind, const ctb_view* param, const ctb_view* grad, float* state1,
+                       float* state2, const ctb_optimizer_hyper* hyper, int step, void* stream);
+
 /* ---- host-buffer entry points ---------------------------------------------------------------
  * Same semantics as ctb_binary / ctb_unary / ctb_reduce, but every view points to HOST memory
  * (pinned memory gives full PCIe speed).  Inputs are staged to `device`, the kernel runs there

@@ -836,3 +836,69 @@ int64_t orc_matmul(const orc_view* a, const orc_view* b, void* out) {
             }
     return batch * M * N;
 }
+
+/* The other optimizers of src/neuralnet/train_utils.h (fp32): kind 3 Adamax :190-239, 4 NAdam
+ * :241-291, 5 RAdam :293-355, 6 RMSprop :357-396, 7 Adagrad :398-437, 8 Lion :439-494.
+ * s1/s2 are the state vectors (m/u, m/v, m/v, v, sum_sq, m). */
+void orc_optimizer_step(int kind, float* theta, const float* grad, float* s1, float* s2, int64_t n,
+                        double lr, double beta1, double beta2, double eps, double weight_decay,
+                        double alpha, int t) {
+    double bc1 = 1.0 - pow(beta1, t), bc2 = 1.0 - pow(beta2, t);
+    if (kind == 3) {
+        float step_size = (float)(lr / bc1);
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i];
+            s1[i] = (float)beta1 * s1[i] + (1.0f - (float)beta1) * g;
+            float x = (float)beta2 * s2[i], y = fabsf(g);
+            s2[i] = (x < y) ? y : x;
+            theta[i] -= step_size * s1[i] / (s2[i] + (float)eps);
+        }
+    } else if (kind == 4) {
+        float step_size = (float)(lr * sqrt(bc2) / bc1);
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i];
+            s1[i] = (float)beta1 * s1[i] + (1.0f - (float)beta1) * g;
+            s2[i] = (float)beta2 * s2[i] + (1.0f - (float)beta2) * g * g;
+            float mn = (float)beta1 * s1[i] + (1.0f - (float)beta1) * g;
+            theta[i] -= step_size * mn / (sqrtf(s2[i]) + (float)eps);
+        }
+    } else if (kind == 5) {
+        float rho_inf = 2.0f / (1.0f - (float)beta2) - 1.0f;
+        float rho_t = rho_inf - 2.0f * t * pow(beta2, t) / (1.0f - pow(beta2, t));
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i];
+            s1[i] = (float)beta1 * s1[i] + (1.0f - (float)beta1) * g;
+            s2[i] = (float)beta2 * s2[i] + (1.0f - (float)beta2) * g * g;
+            float m_hat = s1[i] / (float)bc1;
+            if (rho_t > 4.0f) {
+                float v_hat = sqrtf(s2[i] / (float)bc2) + (float)eps;
+                float rect = sqrtf(((rho_t - 4.0f) * (rho_t - 2.0f) * rho_inf) / ((rho_inf - 4.0f) * (rho_inf - 2.0f) * rho_t));
+                theta[i] -= (float)lr * rect * m_hat / v_hat;
+            } else {
+                theta[i] -= (float)lr * m_hat;
+            }
+        }
+    } else if (kind == 6) {
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i];
+            s1[i] = (float)alpha * s1[i] + (1.0f - (float)alpha) * g * g;
+            theta[i] -= (float)lr * g / (sqrtf(s1[i]) + (float)eps);
+        }
+    } else if (kind == 7) {
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i];
+            s1[i] += g * g;
+            theta[i] -= (float)lr * g / (sqrtf(s1[i]) + (float)eps);
+        }
+    } else if (kind == 8) {
+        float b1 = (float)beta1, b2 = (float)beta2, lr_decay = (float)(lr * weight_decay), lr_f = (float)lr;
+        for (int64_t i = 0; i < n; ++i) {
+            float g = grad[i], m_t = s1[i];
+            if (weight_decay > 0) theta[i] -= lr_decay * theta[i];
+            float c_t = b1 * m_t + (1.0f - b1) * g;
+            float sign_ct = (c_t > 0.0f) ? 1.0f : ((c_t < 0.0f) ? -1.0f : 0.0f);
+            theta[i] -= lr_f * sign_ct;
+            s1[i] = b2 * m_t + (1.0f - b2) * g;
+        }
+    }
+}

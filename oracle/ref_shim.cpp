@@ -458,7 +458,8 @@ int64_t ref_cat(const RefView* const* in, int count, int dim, void* out, int64_t
 // step() on one fp32 parameter whose gradient buffer holds `grad` (the same gradient every
 // step).  The updated parameter is copied to `param_out`; Adam's moment vectors are private to
 // the reference's classes and are pinned through the parameter trajectory.
-// kind: 0 SGD, 1 Adam, 2 AdamW.
+// kind: 0 SGD, 1 Adam, 2 AdamW, 3 Adamax, 4 NAdam, 5 RAdam, 6 RMSprop (beta2 carries alpha),
+// 7 Adagrad, 8 Lion.
 int64_t ref_optimizer_steps(int kind, const float* param, const float* grad, int64_t n, int steps,
                             double lr, double beta1, double beta2, double eps, double weight_decay,
                             float* param_out) {
@@ -472,6 +473,12 @@ int64_t ref_optimizer_steps(int kind, const float* param, const float* grad, int
         if (kind == 0) opt.reset(new SGD(params, lr));
         else if (kind == 1) opt.reset(new Adam(params, lr, beta1, beta2, eps));
         else if (kind == 2) opt.reset(new AdamW(params, lr, beta1, beta2, eps, weight_decay));
+        else if (kind == 3) opt.reset(new Adamax(params, lr, beta1, beta2, eps));
+        else if (kind == 4) opt.reset(new NAdam(params, lr, beta1, beta2, eps));
+        else if (kind == 5) opt.reset(new RAdam(params, lr, beta1, beta2, eps));
+        else if (kind == 6) opt.reset(new RMSprop(params, lr, beta2 /* alpha */, eps));
+        else if (kind == 7) opt.reset(new Adagrad(params, lr, eps));
+        else if (kind == 8) opt.reset(new Lion(params, lr, beta1, beta2, weight_decay));
         else throw std::runtime_error("ref_optimizer_steps: unknown kind");
         for (int s = 0; s < steps; ++s) opt->step();
         std::memcpy(param_out, p.impl->data->data.get(), (size_t)n * 4);

@@ -254,12 +254,12 @@ def all_cases():
     add(name="bn_apply_4d_no_affine", kind="bn_apply", op=0,
         views=[bn4, HostView.contig(_n(55, (5,), 0.3)), HostView.contig(np.abs(_n(56, (5,))) + np.float32(0.1))], scalar=1e-3)
 
-    # ---- optimizer steps: views = [parameter, gradient]; op = 0 SGD, 1 Adam, 2 AdamW; dim = number of steps ----
+    # ---- optimizer steps: views = [parameter, gradient]; op = optimizer (0 SGD ... 8 Lion); dim = number of steps ----
     w0 = HostView.contig(_n(49, (1003,), 0.5))
     gw = HostView.contig(_n(50, (1003,), 2.0))
     gsp = SPECIAL_F32[np.isfinite(SPECIAL_F32)]
     wsp = HostView.contig(np.linspace(-2, 2, gsp.size).astype(np.float32))
-    for kind, nm in enumerate(("sgd", "adam", "adamw")):
+    for kind, nm in enumerate(("sgd", "adam", "adamw", "adamax", "nadam", "radam", "rmsprop", "adagrad", "lion")):
         add(name=f"optim_{nm}_1step", kind="optim", op=kind, views=[w0, gw], dim=1, scalar=0.01)
         add(name=f"optim_{nm}_7steps", kind="optim", op=kind, views=[w0, gw], dim=7, scalar=0.003)
         add(name=f"optim_{nm}_special_grads", kind="optim", op=kind, views=[wsp, HostView.contig(gsp)], dim=2, scalar=0.1)

@@ -200,6 +200,9 @@ class Oracle:
         L.orc_adam_step.restype = None
         L.orc_adam_step.argtypes = ([ctypes.c_void_p] * 4 + [ctypes.c_int64] + [ctypes.c_double] * 4 +
                                     [ctypes.c_int, ctypes.c_double, ctypes.c_int])
+        L.orc_optimizer_step.restype = None
+        L.orc_optimizer_step.argtypes = ([ctypes.c_int] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] +
+                                         [ctypes.c_double] * 6 + [ctypes.c_int])
         L.orc_unary_sweep_f32.restype = None
         L.orc_unary_sweep_f32.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_int64, ctypes.c_double, ctypes.c_void_p,
@@ -320,6 +323,11 @@ class Oracle:
             return p
         m = np.zeros(p.size, np.float32)
         v = np.zeros(p.size, np.float32)
+        if kind >= 3:
+            for t in range(1, steps + 1):
+                self.lib.orc_optimizer_step(kind, p.ctypes.data, g.ctypes.data, m.ctypes.data, v.ctypes.data, p.size,
+                                            lr, beta1, beta2, eps, weight_decay, beta2, t)
+            return p
         for t in range(1, steps + 1):
             self.lib.orc_adam_step(p.ctypes.data, g.ctypes.data, m.ctypes.data, v.ctypes.data, p.size, lr,
                                    beta1, beta2, eps, t, weight_decay, 1 if kind == 2 else 0)

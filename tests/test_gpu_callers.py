@@ -286,3 +286,49 @@ def test_matmul_errors(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.matmul(torch.zeros(5, device="cuda"), x, out=torch.zeros(4, device="cuda"))
     assert "requires at least 2D" in e.value.message
+
+
+def test_mlp_forward_loss_and_sgd_step_end_to_end(ct, oracle):
+    """The reference's MNIST recipe (test/train_mnist.cpp: Linear -> ReLU -> Linear ->
+    CrossEntropy, SGD) with every tensor operation on the device, against the same chain of
+    oracle calls: forward activations and the loss, then the gradient of the last layer
+    (softmax - onehot, bias gradient through accumulate_grad) and one SGD step."""
+    rng = np.random.default_rng(33)
+    B, D, H, C = 64, 784, 128, 10
+    x = HostView.contig(rng.uniform(0, 1, (B, D)).astype(np.float32))
+    w1 = HostView.contig((rng.standard_normal((D, H)) * 0.05).astype(np.float32))
+    b1 = HostView.contig(np.zeros((1, H), np.float32))
+    w2 = HostView.contig((rng.standard_normal((H, C)) * 0.05).astype(np.float32))
+    b2 = HostView.contig((rng.standard_normal((1, C)) * 0.01).astype(np.float32))
+    y = HostView.contig(rng.integers(0, C, (B, 1)).astype(np.int32))
+    hv = lambda a: HostView.contig(a)
+
+    # device
+    dx, dw1, db1, dw2, db2, dy = (to_device(v) for v in (x, w1, b1, w2, b2, y))
+    h = ct.unary(ct.RELU, ct.binary(ct.ADD, ct.matmul(dx, dw1), db1))
+    logits = ct.binary(ct.ADD, ct.matmul(h, dw2), db2)
+    logp = ct.log_softmax(logits)
+    loss = ct.reduce(ct.MEAN, ct.unary(ct.MUL_S, ct.gather(logp, 1, dy), -1.0), ct.DIM_FULL)
+    # oracle
+    oh = oracle.unary(ol.RELU, hv(oracle.binary(ol.ADD, hv(oracle.matmul(x, w1)), b1)))
+    ologits = oracle.binary(ol.ADD, hv(oracle.matmul(hv(oh), w2)), b2)
+    ologp = oracle.log_softmax(hv(ologits))
+    oloss = oracle.reduce(ol.MEAN, hv(oracle.unary(ol.MUL_S, hv(oracle.gather(hv(ologp), 1, y)), -1.0)), -1)
+    assert_bits_equal(h, oh, "hidden activations")
+    assert_bits_equal(logits, ologits, "logits")
+    assert_close(logp, ologp, RTOL, "log-probabilities")
+    assert_close(loss, oloss, RTOL, "loss")
+
+    # d loss / d logits = (softmax - onehot) / B ; bias gradient = its column sums ; SGD step on b2
+    onehot = torch.zeros(B, C, device="cuda")
+    onehot.scatter_(1, torch.from_numpy(y.numpy()).cuda().long(), 1.0)
+    dlogits = ct.unary(ct.MUL_S, ct.binary(ct.SUB, ct.softmax(logits), onehot), 1.0 / B)
+    gb2 = torch.zeros(1, C, device="cuda")
+    ct.accumulate_grad(gb2, dlogits)
+    new_b2 = torch.from_numpy(b2.numpy()).cuda()
+    ct.sgd_step(new_b2, gb2, 0.1)
+    od = oracle.unary(ol.MUL_S, hv(oracle.binary(ol.SUB, hv(oracle.softmax(hv(ologits))), hv(onehot.cpu().numpy()))), 1.0 / B)
+    ogb2 = oracle.accumulate_grad(np.zeros((1, C), np.float32), hv(od))
+    onew = oracle.optimizer_steps(0, b2.numpy(), ogb2, 1, 0.1)
+    np.testing.assert_allclose(gb2.cpu().numpy(), ogb2, rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(new_b2.cpu().numpy(), onew, rtol=1e-5, atol=1e-7)

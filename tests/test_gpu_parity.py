@@ -57,8 +57,10 @@ def run_gpu(ct, case):
         for t in range(1, case["dim"] + 1):
             if case["op"] == 0:
                 ct.sgd_step(p, g, case["scalar"])
-            else:
+            elif case["op"] <= 2:
                 ct.adam_step(p, g, m, v, case["scalar"], t, weight_decay=0.01 if case["op"] == 2 else None)
+            else:       # RMSprop's alpha travels in beta2, as in the golden generator
+                ct.optimizer_step(case["op"], p, g, m, v, t, case["scalar"], weight_decay=0.01, alpha=0.999)
         return p
     raise ValueError(k)
 
