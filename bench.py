@@ -392,12 +392,55 @@ def other_configs(ct, torch, dev):
         "gelu_96MiB": gbs(2 * h.numel() * 4, lambda: ct.unary(ct.GELU_TANH, h, out=oh)),
         "causal_softmax_384MiB": gbs(2 * a.numel() * 4, lambda: ct.softmax(a, None, True, out=oa)),
     }
+    del x, r, h, a, ox, oh, oa
+    # entry points for the callers either side of the path (algorithmic bytes: every operand once)
+    n = 1 << 28
+    p = torch.randn(n, device=dev, generator=g)
+    gr = torch.randn(n, device=dev, generator=g)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    G = gr.view(16384, 16384)
+    bias = torch.zeros(16384, device=dev)
+    xb = gr.view(128, 256, 64, 128)                      # BatchNorm input [N, C, H, W], 1 GiB
+    mean, var = ct.channel_moments(xb)
+    gam, bet = torch.ones(256, device=dev), torch.zeros(256, device=dev)
+    yb = m.view(128, 256, 64, 128)
+    logits = gr.view(32768, 8192)
+    lo = m.view(32768, 8192)
+    step = [0]
+
+    def adam():
+        step[0] += 1
+        ct.adam_step(p, gr, m, v, 1e-3, step[0])
+
+    callers = {
+        "sgd_step_1GiB": gbs(12 * n, lambda: ct.sgd_step(p, gr, 1e-3)),
+        "adam_step_1GiB": gbs(28 * n, adam),
+        "accumulate_grad_bias_16384x16384": gbs(4 * n + 8 * 16384, lambda: ct.accumulate_grad(bias, G)),
+        "accumulate_grad_same_shape_1GiB": gbs(12 * n, lambda: ct.accumulate_grad(p, gr)),
+        "batchnorm_moments_128x256x64x128": gbs(4 * n, lambda: ct.channel_moments(xb)),
+        "batchnorm_apply_128x256x64x128": gbs(8 * n, lambda: ct.batchnorm_apply(xb, mean, var, gam, bet, 1e-5, out=yb)),
+        "log_softmax_32768x8192": gbs(8 * n, lambda: ct.log_softmax(logits, out=lo)),
+        "cat_two_halves_1GiB": gbs(8 * n, lambda: ct.cat([gr.view(2, n // 2)[0].view(8192, -1), gr.view(2, n // 2)[1].view(8192, -1)], 1, out=m.view(8192, -1))),
+    }
+    a2 = torch.randn(4096, 4096, device=dev, generator=g)
+    c2 = torch.empty(4096, 4096, device=dev)
+    for _ in range(2):
+        ct.matmul(a2, a2, out=c2)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(3):
+        ct.matmul(a2, a2, out=c2)
+    t1.record()
+    torch.cuda.synchronize()
+    callers["matmul_4096^3_plain_fp32_TFLOPs"] = round(3 * 2 * 4096 ** 3 / t0.elapsed_time(t1) / 1e9, 1)
+    res["callers"] = callers
     return res
 
 
 def profile_case(name: str):
     """A few launches of one kernel family on a small case (inputs larger than L2, well under
-    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided`."""
+    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab`."""
     import torch
     import ctensor_b200 as ct
     torch.manual_seed(0)
@@ -420,6 +463,28 @@ def profile_case(name: str):
             ct.softmax(C, None, True, out=O)
             ct.log_softmax(C, out=O)
             ct.layernorm(L, g, b, out=LO)
+    elif name == "callers":             # optimizer, accumulate_grad, BatchNorm, gather on 2^26 elements
+        n = 1 << 26
+        p, gr = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        bias = torch.zeros(8192, device="cuda")
+        xb = gr.view(32, 256, 64, 128)
+        mean, var = ct.channel_moments(xb)
+        idx = torch.randint(0, 8192, (8192, 64), device="cuda", dtype=torch.int32)
+        for t in range(1, 3):
+            ct.adam_step(p, gr, m, v, 1e-3, t)
+            ct.sgd_step(p, gr, 1e-3)
+            ct.accumulate_grad(bias, gr.view(8192, 8192))
+            ct.channel_moments(xb)
+            ct.batchnorm_apply(xb, mean, var, None, None, 1e-5, out=m.view(32, 256, 64, 128))
+            ct.gather(gr.view(8192, 8192), 1, idx)
+    elif name == "vocab":               # vocabulary-sized rows: [2048, 50304] and [2048, 50257] logits
+        for cols in (50304, 50257):
+            L = torch.randn(2048, cols, device="cuda")
+            O = torch.empty_like(L)
+            for _ in range(2):
+                ct.log_softmax(L, out=O)
+                ct.softmax(L, out=O)
     elif name == "strided":             # the permuted 4-d view at batch 4: S + M, contiguous(S), x - rowmax
         buf = torch.randn(4, 1024, 12, 1024, device="cuda")
         S = buf.permute(0, 2, 1, 3)
@@ -547,7 +612,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
-    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided"],
+    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab"],
                     help="run a few launches of one kernel family on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:

@@ -332,3 +332,20 @@ def test_mlp_forward_loss_and_sgd_step_end_to_end(ct, oracle):
     onew = oracle.optimizer_steps(0, b2.numpy(), ogb2, 1, 0.1)
     np.testing.assert_allclose(gb2.cpu().numpy(), ogb2, rtol=1e-4, atol=1e-7)
     np.testing.assert_allclose(new_b2.cpu().numpy(), onew, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("cols", [8196, 12289, 16384, 30001, 50257, 65536, 100003, 250000])
+def test_softmax_long_rows_cluster_kernel(ct, oracle, cols):
+    """Rows beyond the register kernels: staged in the shared memory of a thread-block cluster
+    (up to 8 x 25600 columns), then the re-reading kernel; aligned and unaligned row starts."""
+    rng = np.random.default_rng(cols)
+    x = HostView.contig((rng.standard_normal((5, cols)) * 3).astype(np.float32))
+    np.testing.assert_allclose(ct.softmax(to_device(x)).cpu().numpy(), oracle.softmax(x), rtol=RTOL, atol=1e-12)
+    np.testing.assert_allclose(ct.log_softmax(to_device(x)).cpu().numpy(), oracle.log_softmax(x), rtol=RTOL, atol=1e-6)
+    if cols <= 30001:
+        m = HostView.contig(-rng.random((1, cols)).astype(np.float32))
+        np.testing.assert_allclose(ct.softmax(to_device(x), to_device(m)).cpu().numpy(), oracle.softmax(x, m), rtol=RTOL, atol=1e-12)
+        sq = HostView.contig(rng.standard_normal((2, 3, 8, cols)).astype(np.float32)[:, :, :, :])
+        got = ct.softmax(to_device(sq), None, causal=True).cpu().numpy()
+        ref = oracle.softmax(sq, None, causal=True)
+        np.testing.assert_allclose(got, ref, rtol=RTOL, atol=1e-12)
