@@ -840,6 +840,93 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
     }
 }
 
+// Rows of 8193 .. 32768 columns with 16-byte aligned starts: a thread-block cluster per row, every
+// CTA keeps 256 x NV x 4 columns in registers; the two fp64 row sums cross CTAs through
+// distributed shared memory (same scheme as softmax_rows_cluster_reg_kernel).
+template <int CS, int NV, int MODE>
+__global__ void __launch_bounds__(kClusterRowThreads)
+layernorm_rows_cluster_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
+                              const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
+                              RowIdx o, int64_t rows, int cols, double inv_cols, double eps) {
+    __shared__ double ssum[kClusterRowThreads / 32];
+    __shared__ double cta_s1, cta_s2;
+    constexpr int T = kClusterRowThreads;
+    const int tid = threadIdx.x;
+    const unsigned rank = cluster_rank();
+    const int64_t ridx = blockIdx.x / CS;
+    int64_t xo, mo, row;
+    row_offsets(o, ridx, &xo, &mo, &row);
+    const int c_lo = (int)rank * (T * NV * 4);
+    const float* xr = x + xo + c_lo;
+    const int live = cols - c_lo;                       // may be <= 0
+    float t[NV][4];
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * T + tid) * 4;
+        if (col < live) {
+            load_vec<4>(t[i], xr, col, cols);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s = __dadd_rn(s, (double)t[i][k]);
+        }
+    }
+    s = cta_sum_any(s, ssum);
+    if (tid == 0) cta_s1 = s;
+    cluster_barrier();
+    s = 0.0;
+#pragma unroll
+    for (unsigned r = 0; r < CS; ++r) s = __dadd_rn(s, cluster_peer_load(&cta_s1, r));
+    const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
+    double s2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * T + tid) * 4;
+        if (col < live) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                t[i][k] = __fsub_rn(t[i][k], mu);
+                s2 = __dadd_rn(s2, (double)__fmul_rn(t[i][k], t[i][k]));
+            }
+        }
+    }
+    s2 = cta_sum_any(s2, ssum);
+    if (tid == 0) cta_s2 = s2;
+    cluster_barrier();
+    s2 = 0.0;
+#pragma unroll
+    for (unsigned r = 0; r < CS; ++r) s2 = __dadd_rn(s2, cluster_peer_load(&cta_s2, r));
+    const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
+    const float ve = __double2float_rn(__dadd_rn((double)v, eps));
+    const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
+    float* orow = out + row * (int64_t)cols + c_lo;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * T + tid) * 4;
+        if (col < live) {
+            float r[4];
+            if (MODE == 1) {
+                float gv[4], bv[4];
+                load_vec<4>(gv, gamma + c_lo, col, cols);
+                load_vec<4>(bv, beta + c_lo, col, cols);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) r[k] = __fadd_rn(__fmul_rn(__fmul_rn(t[i][k], rstd), gv[k]), bv[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float y = __fmul_rn(t[i][k], rstd);
+                    if (MODE == 2) {
+                        if (gamma) y = __fmul_rn(y, gamma[(int64_t)(c_lo + col + k) * gstride]);
+                        if (beta) y = __fadd_rn(y, beta[(int64_t)(c_lo + col + k) * bstride]);
+                    }
+                    r[k] = y;
+                }
+            }
+            store_vec<4>(orow, col, r);
+        }
+    }
+    cluster_barrier();                                    // peers may still be reading cta_s2
+}
+
 __global__ void __launch_bounds__(256)
 layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
                            const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
@@ -1094,6 +1181,30 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     return cuda_error(cudaGetLastError(), "softmax launch");
 }
 
+namespace {
+
+template <int CS, int MODE>
+int launch_layernorm_cluster(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride, const float* beta,
+                             int64_t bstride, double inv, double eps, float* out, const RowIdx& o, cudaStream_t st) {
+    auto kernel = layernorm_rows_cluster_kernel<CS, 8, MODE>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(g.rows * CS));
+    cfg.blockDim = dim3(kClusterRowThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
+    return CTB_OK;
+}
+
+}  // namespace
+
 int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride,
                      const float* beta, int64_t bstride, double eps, float* out, cudaStream_t st) {
     if (g.rows == 0 || g.cols == 0) return CTB_OK;
@@ -1109,6 +1220,18 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
+    constexpr int64_t kClusterSpan = (int64_t)kClusterRowThreads * 8 * 4;      // columns per CTA
+    if (!launched && vec4 && g.cols <= 4 * kClusterSpan && g.rows * 4 < 0x7FFFFFFFll) {
+        const bool two = g.cols <= 2 * kClusterSpan;
+#define CTB_LN_CLUSTER(M)                                                                                               \
+        rc = two ? launch_layernorm_cluster<2, M>(g, x, gamma, gstride, beta, bstride, inv, eps, out, o, st)          \
+                 : launch_layernorm_cluster<4, M>(g, x, gamma, gstride, beta, bstride, inv, eps, out, o, st)
+        if (mode == 0) { CTB_LN_CLUSTER(0); }
+        else if (mode == 1) { CTB_LN_CLUSTER(1); }
+        else { CTB_LN_CLUSTER(2); }
+#undef CTB_LN_CLUSTER
+        return rc;
+    }
     if (!launched) {
         const int grid = rows_grid(g.rows, 1);
         layernorm_rows_long_kernel<<<grid, 256, 0, st>>>(x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps);

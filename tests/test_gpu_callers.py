@@ -349,3 +349,17 @@ def test_softmax_long_rows_cluster_kernel(ct, oracle, cols):
         got = ct.softmax(to_device(sq), None, causal=True).cpu().numpy()
         ref = oracle.softmax(sq, None, causal=True)
         np.testing.assert_allclose(got, ref, rtol=RTOL, atol=1e-12)
+
+
+@pytest.mark.parametrize("cols", [8196, 12288, 16384, 30000, 32768, 32772, 40001])
+def test_layernorm_long_rows(ct, oracle, cols):
+    """LayerNorm rows beyond the register kernels: cluster kernel up to 32768 aligned columns,
+    the re-reading kernel otherwise."""
+    rng = np.random.default_rng(cols)
+    x = HostView.contig((rng.standard_normal((7, cols)) * 2 + 0.3).astype(np.float32))
+    g = HostView.contig((1 + 0.02 * rng.standard_normal(cols)).astype(np.float32))
+    b = HostView.contig((0.02 * rng.standard_normal(cols)).astype(np.float32))
+    got = ct.layernorm(to_device(x), to_device(g), to_device(b), 1e-5).cpu().numpy()
+    np.testing.assert_allclose(got, oracle.layernorm(x, g, b, 1e-5), rtol=RTOL, atol=1e-6)
+    got = ct.layernorm(to_device(x), None, None, 1e-5).cpu().numpy()
+    np.testing.assert_allclose(got, oracle.layernorm(x, None, None, 1e-5), rtol=RTOL, atol=1e-6)
