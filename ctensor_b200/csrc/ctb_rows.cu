@@ -186,7 +186,7 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
         const int col = (i * GROUP + tid) * VEC;
         if (col < live) {
             load_vec<VEC>(t[i], xr, col, cols);
-            if (MODE == 0) {
+            if ((MODE & 7) == 0) {             // no mask, not causal (log-softmax included): one loop
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);
             }
@@ -195,7 +195,7 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int col = (i * GROUP + tid) * VEC;
-        if (MODE != 0 && col < live) {
+        if ((MODE & 7) != 0 && col < live) {
             if (has_mask) {
                 float mv[VEC];
                 if (m_inner) load_vec<VEC>(mv, mask + mo, col, cols);     // L1/L2 resident: short latency
