@@ -145,20 +145,24 @@ __device__ __forceinline__ float div_by_row(float e, float z, float r) {
     return out;
 }
 
-// Threads per CTA: 8 warp-rows, or 512 threads split into row groups of 128/256 threads.  (CTAs
-// that hold a single 4 KiB row each measured 2.4x slower than 8 rows per CTA: the kernel
+// Threads per CTA: 8 warp-rows; for row groups of 128/256 threads, 512 threads while a thread
+// holds at most 4 vectors and 256 threads when it holds more (measured: 2048 columns 6.1 against
+// 5.8 TB/s with 512, 4096 columns 6.7 against 6.3 and 8192 columns 6.4 against 5.2 with 256).
+// (CTAs that hold a single 4 KiB row each measured 2.4x slower than 8 rows per CTA: the kernel
 // becomes bound by CTA launch rate.)
-template <int GROUP> struct RowCta { static constexpr int kThreads = GROUP == 32 ? 256 : 512; };
+template <int GROUP, int NV> struct RowCta {
+    static constexpr int kThreads = GROUP == 32 ? 256 : (NV <= 4 ? 512 : 256);
+};
 
 // MODE bits (compile time, so the unrolled load loop has no run-time branch and all loads of a
 // row are in flight together): 1 = additive mask, 2 = the mask's last dim is contiguous
 // (else one value per row), 4 = causal, 8 = log-softmax: out = (t - m) - log((float)sum), the
 // chain of Loss::CrossEntropy (src/neuralnet/loss.cpp:97-104); not combined with causal.
 template <int GROUP, int VEC, int NV, int MODE>
-__global__ void __launch_bounds__(RowCta<GROUP>::kThreads)
+__global__ void __launch_bounds__(RowCta<GROUP, NV>::kThreads)
 softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
                     RowIdx o, int64_t rows, int cols, int64_t qlen) {
-    constexpr int THREADS = RowCta<GROUP>::kThreads;
+    constexpr int THREADS = RowCta<GROUP, NV>::kThreads;
     constexpr int GPC = THREADS / GROUP;                // rows per CTA
     constexpr bool has_mask = (MODE & 1) != 0, m_inner = (MODE & 2) != 0, causal = (MODE & 4) != 0;
     constexpr bool log_out = (MODE & 8) != 0;
@@ -769,11 +773,11 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
 // MODE (compile time): 0 = no scale/shift, 1 = gamma and beta are contiguous rows (vector
 // loads), 2 = general (either may be absent or strided).
 template <int GROUP, int VEC, int NV, int MODE>
-__global__ void __launch_bounds__(RowCta<GROUP>::kThreads)
+__global__ void __launch_bounds__(RowCta<GROUP, NV>::kThreads)
 layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
                       const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
                       RowIdx o, int64_t rows, int cols, double inv_cols, double eps) {
-    constexpr int THREADS = RowCta<GROUP>::kThreads;
+    constexpr int THREADS = RowCta<GROUP, NV>::kThreads;
     constexpr int GPC = THREADS / GROUP;
     __shared__ double ssum[THREADS / 32];
     const int tid = threadIdx.x % GROUP;
@@ -1026,8 +1030,8 @@ int rows_grid(int64_t rows, int groups_per_cta) {
     }
 #define CTB_ROWS_LAUNCH(MODES, KERNEL, G, V, N, ARGS)                                          \
     do {                                                                                       \
-        const int grid = rows_grid(g.rows, RowCta<G>::kThreads / G);                           \
-        const int thr = RowCta<G>::kThreads;                                                   \
+        const int grid = rows_grid(g.rows, RowCta<G, N>::kThreads / G);                        \
+        const int thr = RowCta<G, N>::kThreads;                                                \
         MODES(KERNEL, G, V, N, ARGS)                                                           \
     } while (0)
 
