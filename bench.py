@@ -63,7 +63,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -71,16 +71,28 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def wait_first_sample(self, timeout=5.0):
+        """nvidia-smi needs a moment to start on a fresh box: do not enter the timed region blind."""
+        t_end = time.monotonic() + timeout
+        while self.proc is not None and not self.rows and time.monotonic() < t_end:
+            time.sleep(0.01)
+
+    def samples_between(self, t0, t1):
+        return sum(1 for t, _ in self.rows if t0 <= t <= t1)
+
+    def stop(self, t0=None, t1=None):
+        """Statistics over the samples that arrived in [t0, t1] (host clock; every sample when
+        no window is given)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         sm, smax, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        rows = [r for t, r in self.rows if (t0 is None or t >= t0) and (t1 is None or t <= t1)]
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 smax = float(r[1])
@@ -156,23 +168,40 @@ def bench_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        run_step(ct, x, y, out)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+    for _ in range(args.warmup):
+        run_step(ct, x, y, out)
+    barrier()
+    if rank == 0:
+        sampler.wait_first_sample()
     barrier()
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS]
           for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_host0 = time.monotonic()
     e0.record()
     for k in range(args.steps):
         run_step(ct, x, y, out, ev[k])
     e1.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    t_host1 = time.monotonic()
+    clocks = None
+    if rank == 0:
+        window = "timed region"
+        if sampler.samples_between(t_host0, t_host1) < 3:
+            # a short timed region (few steps) gives the 20 ms sampler too little: keep the same
+            # kernels running, untimed, until there are samples under load
+            t_more = time.monotonic() + 0.6
+            while time.monotonic() < t_more:
+                run_step(ct, x, y, out)
+                torch.cuda.synchronize()
+            t_host1 = time.monotonic()
+            window = "timed region + 0.6 s of the same step, untimed"
+        clocks = sampler.stop(t_host0, t_host1)
+        clocks["window"] = window
+    barrier()
     ms_total = e0.elapsed_time(e1)
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if world > 1:
