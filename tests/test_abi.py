@@ -76,3 +76,31 @@ def test_no_cpu_fallback(L):
     assert np.all(o == 7.0)
     with pytest.raises(ct.CtbError):
         ct.check(st)
+
+
+def test_no_cpu_fallback_for_the_caller_side_entry_points(L):
+    """matmul, cat, accumulate_grad, gather, optimizer steps, BatchNorm and the fused rows also
+    refuse to run without a CUDA device and leave their outputs untouched."""
+    if L.ctb_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    a = np.ones((8, 8), np.float32)
+    o = np.full((8, 8), 7.0, np.float32)
+    idx = np.zeros((8, 1), np.int32)
+    oi = np.full((8, 1), 7.0, np.float32)
+    vi = ct.make_view(idx.ctypes.data, ct.I32, idx.shape, [1, 1])
+    va, vo = _host_view(a), _host_view(o)
+    views = (ctypes.POINTER(ct.View) * 1)(ctypes.pointer(va))
+    calls = [
+        lambda: L.ctb_matmul(va, va, vo, None),
+        lambda: L.ctb_cat(views, 1, 0, vo, None),
+        lambda: L.ctb_accumulate_grad(vo, va, None),
+        lambda: L.ctb_gather(va, 1, vi, _host_view(oi), None, None),
+        lambda: L.ctb_sgd_step(vo, va, 0.1, None),
+        lambda: L.ctb_softmax_lastdim(va, None, 0, vo, None),
+        lambda: L.ctb_log_softmax_lastdim(va, None, vo, None),
+        lambda: L.ctb_layernorm_lastdim(va, None, None, 1e-5, vo, None),
+        lambda: L.ctb_copy_into(va, vo, None),
+    ]
+    for i, call in enumerate(calls):
+        assert call() == 6, (i, L.ctb_last_error())
+    assert np.all(o == 7.0) and np.all(oi == 7.0)
