@@ -973,6 +973,7 @@ int ctb_adam_step(const ctb_view* param, const ctb_view* grad, float* m, float* 
     int rc;
     if ((rc = optimizer_operands(param, grad, "adam_step"))) return rc;
     if (param->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "adam_step: only Float32 parameters are updated");
+    if (view_numel(param) == 0) return CTB_OK;
     if (!m || !v) return set_error(CTB_ERR_NULL, "adam_step: null moment buffer");
     if (step < 1) return set_error(CTB_ERR_ARG, "adam_step: the step count starts at 1");
     return launch_adam((float*)elem_ptr_mut(param), (const float*)elem_ptr(grad), m, v, view_numel(param), lr, beta1,
@@ -991,6 +992,7 @@ int ctb_optimizer_step(int kind, const ctb_view* param, const ctb_view* grad, fl
     if ((rc = optimizer_operands(param, grad, "optimizer_step"))) return rc;
     if (param->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "optimizer_step: only Float32 parameters are updated");
     const bool two = kind == CTB_OPT_ADAMAX || kind == CTB_OPT_NADAM || kind == CTB_OPT_RADAM;
+    if (view_numel(param) == 0) return CTB_OK;
     if (!state1 || (two && !state2)) return set_error(CTB_ERR_NULL, "optimizer_step: null state buffer");
     if (step < 1) return set_error(CTB_ERR_ARG, "optimizer_step: the step count starts at 1");
     return launch_optimizer(kind, (float*)elem_ptr_mut(param), (const float*)elem_ptr(grad), state1, state2,

@@ -363,3 +363,29 @@ def test_layernorm_long_rows(ct, oracle, cols):
     np.testing.assert_allclose(got, oracle.layernorm(x, g, b, 1e-5), rtol=RTOL, atol=1e-6)
     got = ct.layernorm(to_device(x), None, None, 1e-5).cpu().numpy()
     np.testing.assert_allclose(got, oracle.layernorm(x, None, None, 1e-5), rtol=RTOL, atol=1e-6)
+
+
+def test_empty_and_degenerate_inputs(ct):
+    """Zero-sized tensors and extents of one go through the caller-side entry points without a
+    launch error and give the obvious results."""
+    dev = "cuda"
+    z = torch.zeros(0, 5, device=dev)
+    assert ct.log_softmax(z).shape == (0, 5)
+    assert ct.softmax(z).shape == (0, 5)
+    assert ct.cat([z, torch.ones(2, 5, device=dev)], 0).shape == (2, 5)
+    assert ct.cat([torch.ones(3, 0, device=dev), torch.ones(3, 2, device=dev)], 1).shape == (3, 2)
+    assert ct.gather(torch.ones(4, 3, device=dev), 1, torch.zeros(4, 0, dtype=torch.int32, device=dev)).shape == (4, 0)
+    g = torch.ones(5, device=dev)
+    ct.accumulate_grad(g, torch.zeros(0, 5, device=dev))            # nothing to add
+    assert torch.equal(g, torch.ones(5, device=dev))
+    k0 = ct.matmul(torch.ones(3, 0, device=dev), torch.ones(0, 4, device=dev))
+    assert k0.shape == (3, 4) and float(k0.abs().sum()) == 0.0      # empty sums are zero
+    one = torch.full((1, 1), 3.0, device=dev)
+    assert float(ct.softmax(one)) == 1.0 and float(ct.log_softmax(one)) == 0.0
+    assert float(ct.matmul(one, one)) == 9.0
+    p = torch.zeros(0, device=dev)
+    ct.sgd_step(p, p, 0.1)
+    ct.adam_step(p, p, p, p, 0.1, 1)
+    m, v = ct.channel_moments(torch.full((2, 3, 1), 5.0, device=dev))
+    assert torch.equal(m, torch.full((3,), 5.0, device=dev)) and float(v.abs().sum()) == 0.0
+    torch.cuda.synchronize()
