@@ -10,6 +10,7 @@ inline Tensor add_(const Tensor& a, const Tensor& b) { return add(a, b); }
 inline Tensor diff_(const Tensor& a, const Tensor& b) { return sub(a, b); }
 inline Tensor mult_(const Tensor& a, const Tensor& b) { return mul(a, b); }
 inline Tensor div_(const Tensor& a, const Tensor& b) { return div(a, b); }
+inline Tensor matmul_(const Tensor& a, const Tensor& b) { return matmul(a, b); }
 inline Tensor sub_afterscalar(double s, const Tensor& a) { return sub_scalar_rev(s, a); }
 inline Tensor mult_scalar(const Tensor& a, double s) { return mul_scalar(a, s); }
 inline Tensor scalar_div(double s, const Tensor& a) { return div_scalar_rev(s, a); }

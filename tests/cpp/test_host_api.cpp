@@ -168,6 +168,7 @@ int main() {
     CHECK_NEAR(my[1][0], 20.0, 0.0);
     CHECK_NEAR(my[1][1], 31.0, 0.0);
     CHECK_THROWS(matmul(mx, mx), std::runtime_error, "matmul_mp shape mismatch");
+    CHECK_NEAR(matmul_(mx, mw)[1][1], 11.0, 0.0);
 
     // BatchNorm forward pieces: x[N=2, C=2, S=2]
     Tensor bx = Tensor::from_vector({1, 3, 10, 30, 5, 7, 50, 70}, {2, 2, 2});
