@@ -41,6 +41,12 @@ namespace ctb {
 #ifndef CTB_RED_COLS_UNROLL
 #define CTB_RED_COLS_UNROLL 16             // row loads in flight per thread of the column kernel
 #endif
+#ifndef CTB_RED_BLOCK_THREADS_SHIFT
+#define CTB_RED_BLOCK_THREADS_SHIFT 512    // the same for variance: 128/256 gain 2-4 % at 16384 columns, lose 5 % at 32768
+#endif
+#ifndef CTB_RED_SHIFT_WARP_ROWS
+#define CTB_RED_SHIFT_WARP_ROWS 64         // variance: warp per line from this many lines per SM (32 and 16 measured slower)
+#endif
 #ifndef CTB_RED_COLS_CTAS_PER_SM
 #define CTB_RED_COLS_CTAS_PER_SM 3         // register budget of the column kernel: at least this many CTAs per SM
 #endif
@@ -241,11 +247,18 @@ __device__ __forceinline__ typename Pol::Acc block_reduce(typename Pol::Acc a, t
 // U vector loads issued back to back, then consumed.
 template <typename Pol, int VEC, int U>
 __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const float* __restrict__ line,
-                                                 int64_t j, int64_t stride, double shift) {
+                                                 int64_t j, int64_t stride, float shift_f) {
     using V = Vec<float, VEC>;
     V v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(line + j + u * stride));
+    // The line's shift value comes from a load of its own.  The empty volatile asm pins every use
+    // of it (starting with the conversion to double) behind the vector loads above; without it
+    // the conversion was scheduled first and each line waited for that one load before issuing
+    // the rest ([8192,16384] fp32 variance: over dim 0 6.33 -> 6.59 TB/s, over dim 1 5.40 -> 5.52).
+    float sf = shift_f;
+    if (NeedsShift<Pol>::value) asm volatile("" : "+f"(sf));
+    const double shift = (double)sf;
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -254,7 +267,7 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
 
 template <typename Pol, int VEC, int UNROLL>
 __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const float* __restrict__ line,
-                                                int64_t lo, int64_t hi, int tid, int nthr, double shift) {
+                                                int64_t lo, int64_t hi, int tid, int nthr, float shift) {
     const int64_t stride = (int64_t)nthr * VEC;
     int64_t j = lo + (int64_t)tid * VEC;
     // main loop: UNROLL loads in flight; the remainder keeps as many in flight as it has
@@ -273,7 +286,7 @@ __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const fl
     for (; j + VEC <= hi; j += stride) accumulate_batch<Pol, VEC, 1>(acc, line, j, stride, shift);
     if (VEC > 1) {   // ragged end of the line
         for (int k = 0; k < VEC; ++k)
-            if (j + k < hi) Pol::add(acc, line[j + k], j + k, shift);
+            if (j + k < hi) Pol::add(acc, line[j + k], j + k, (double)shift);
     }
 }
 
@@ -285,7 +298,7 @@ reduce_rows_warp_kernel(const float* __restrict__ a, void* out, OuterIdx o, int6
     const int64_t warps = (int64_t)gridDim.x * (THREADS / 32);
     for (int64_t row = (int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); row < nout; row += warps) {
         const float* line = a + outer_offset(o, row);
-        const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+        const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, lane, 32, shift);
         acc = warp_reduce<Pol>(acc);
@@ -300,7 +313,7 @@ reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int
     __shared__ typename Pol::Acc smem[THREADS / 32];
     for (int64_t row = blockIdx.x; row < nout; row += gridDim.x) {
         const float* line = a + outer_offset(o, row);
-        const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+        const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
         typename Pol::Acc acc = Pol::init();
         accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
         acc = block_reduce<Pol, THREADS>(acc, smem);
@@ -321,7 +334,7 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
     const int64_t row = blockIdx.y;
     const int splits = gridDim.x;
     const float* line = a + outer_offset(o, row);
-    const double shift = NeedsShift<Pol>::value ? (double)line[0] : 0.0;
+    const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
     const int64_t lo = (int64_t)blockIdx.x * chunk;
     int64_t hi = lo + chunk;
     if (hi > rlen) hi = rlen;
@@ -353,11 +366,18 @@ reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial
 // columns (VEC each), y walks rows.  grid = (column tiles, row splits, batch).
 template <typename Pol, int VEC, int U>
 __device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const float* __restrict__ q,
-                                           int64_t step, int64_t r, const double (&shift)[VEC]) {
+                                           int64_t step, int64_t r, const float (&shift_f)[VEC]) {
     using V = Vec<float, VEC>;
     V v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(q + u * step));
+    double shift[VEC];                   // uses pinned behind the loads, as in accumulate_batch
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        float sf = shift_f[k];
+        if (NeedsShift<Pol>::value) asm volatile("" : "+f"(sf));
+        shift[k] = (double)sf;
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -383,14 +403,14 @@ reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64
     if (r1 > rlen) r1 = rlen;
 
     Acc acc[VEC];
-    double shift[VEC];
+    float shift[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { acc[k] = Pol::init(); shift[k] = 0.0; }
+    for (int k = 0; k < VEC; ++k) { acc[k] = Pol::init(); shift[k] = 0.0f; }
     const bool active = col < ncols;     // ncols % VEC == 0 when VEC > 1
     if (active) {
         if (NeedsShift<Pol>::value) {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) shift[k] = (double)base[col + k];
+            for (int k = 0; k < VEC; ++k) shift[k] = base[col + k];
         }
         // CU row loads in flight; the remainder keeps as many in flight as it has (CU/2, ... 1)
         constexpr int CU = ColsUnroll<Pol>::value;
@@ -595,7 +615,7 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
     // variance does three fp64 operations per element after the loads of a CTA-wide batch have
     // landed; with a CTA per line that phase is not covered by loads, with a warp per line other
     // warps' loads cover it ([16384,16384]: 6.1 against 5.4 TB/s) — if there are lines enough
-    if (shape == SH_ROWS_BLOCK && NeedsShift<Pol>::value && g.nout >= (int64_t)sm_count * 64) shape = SH_ROWS_WARP;
+    if (shape == SH_ROWS_BLOCK && NeedsShift<Pol>::value && g.nout >= (int64_t)sm_count * CTB_RED_SHIFT_WARP_ROWS) shape = SH_ROWS_WARP;
     switch (shape) {
     case SH_ROWS_WARP: {
         // one warp per row, one pass per CTA (a persistent grid measured slower)
@@ -607,7 +627,7 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
         break;
     }
     case SH_ROWS_BLOCK: {
-        constexpr int TB = CTB_RED_BLOCK_THREADS;
+        constexpr int TB = NeedsShift<Pol>::value ? CTB_RED_BLOCK_THREADS_SHIFT : CTB_RED_BLOCK_THREADS;
         const unsigned grid = (unsigned)(g.nout < 0x7FFFFFFFll ? g.nout : 0x7FFFFFFFll);
         if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         else reduce_rows_block_kernel<Pol, 1, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
