@@ -300,14 +300,17 @@ def bench_ours(args):
                     s = (r % nslices) * m
                     fn(x[s:s + m], y[s:s + m], out[s:s + m])
                 torch.cuda.synchronize()
-                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a0.record()
-                for r in range(reps):
-                    s = (r % nslices) * m
-                    fn(x[s:s + m], y[s:s + m], out[s:s + m])
-                a1.record()
-                torch.cuda.synchronize()
-                res[name] = round(bpe * m * reps / a0.elapsed_time(a1) / 1e6, 1)
+                windows = []                 # median of three windows: one host hiccup in a
+                for _ in range(3):           # 1 ms window otherwise halves the figure
+                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a0.record()
+                    for r in range(reps):
+                        s = (r % nslices) * m
+                        fn(x[s:s + m], y[s:s + m], out[s:s + m])
+                    a1.record()
+                    torch.cuda.synchronize()
+                    windows.append(a0.elapsed_time(a1))
+                res[name] = round(bpe * m * reps / sorted(windows)[1] / 1e6, 1)
             sweep[f"2^{lg}"] = res
         del x, y, out
         try:
