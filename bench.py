@@ -600,6 +600,14 @@ def cpu_baseline(sample_log2=26, reps=3):
     else:
         impl = ol.Oracle()
         paths["oracle port (plain C + OpenMP)"] = None
+    # All the host threads this process may use.  torchrun exports OMP_NUM_THREADS=1 to its
+    # workers, which would time the reference's OpenMP loops on a single thread.
+    host_threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if kind == "reference":
+        impl.lib.ref_set_threads(host_threads)
+    else:
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(host_threads)
 
     def step(path):
         """Seconds for one step."""
@@ -620,7 +628,7 @@ def cpu_baseline(sample_log2=26, reps=3):
             results[name] = f"failed: {exc}"
     good = {k: v for k, v in results.items() if isinstance(v, float)}
     best_name = max(good, key=good.get)
-    threads = impl.lib.ref_max_threads() if kind == "reference" else (os.cpu_count() or 1)
+    threads = impl.lib.ref_max_threads() if kind == "reference" else host_threads
     return {"value": good[best_name], "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": f"n=2^{sample_log2} elements per tensor, the same 5 ops, best of {reps}; fastest back-end: {best_name}; "
                       "output allocation is inside every reference op and therefore inside its time",
