@@ -1,7 +1,7 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE — builds the real reference (CTensor src tree) as a shared library.
 #
-#   oracle/build_ref.sh [REFERENCE_ROOT]      (default REFERENCE_ROOT=/root/reference)
+#   oracle/build_ref.sh [REFERENCE_ROOT]      (REFERENCE_ROOT: the reference checkout; default below)
 #
 # Output: oracle/_ref/libctensor_ref.so  (+ oracle/_ref/BUILD_INFO.txt).  Nothing else is
 # written; no reference source is copied into the repository.
