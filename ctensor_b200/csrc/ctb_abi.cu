@@ -48,6 +48,9 @@ struct DeviceState {
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
+// The host-buffer entry points of one device share its staging buffer and its three streams:
+// one such call at a time per device (others wait here).
+std::mutex g_host_mu[kMaxDevices];
 }  // namespace
 
 int current_device_info(DeviceInfo* info) {
@@ -67,8 +70,12 @@ int current_device_info(DeviceInfo* info) {
 
 namespace {
 
-// Scratch that grows on demand and is zeroed when (re)allocated.
-int ensure_workspace(size_t bytes, void** out) {
+// Scratch that grows on demand.  The split kernels need the ticket region at its start to be
+// zero; a fresh allocation is cleared ON THE CALLER'S STREAM, so the clear is ordered before the
+// kernel that follows whatever kind of stream that is (a clear on the legacy default stream is
+// not ordered against non-blocking streams).  Growing frees the old buffer, which waits for
+// the device: work of other streams that still used it has finished by then.
+int ensure_workspace(size_t bytes, void** out, cudaStream_t st) {
     *out = nullptr;
     if (bytes == 0) return CTB_OK;
     DeviceInfo di;
@@ -82,7 +89,7 @@ int ensure_workspace(size_t bytes, void** out) {
         s.ws = nullptr;
         s.ws_bytes = 0;
         CTB_CUDA_TRY(cudaMalloc(&s.ws, want));
-        CTB_CUDA_TRY(cudaMemset(s.ws, 0, want));
+        CTB_CUDA_TRY(cudaMemsetAsync(s.ws, 0, kTicketBytes, st));
         s.ws_bytes = want;
     }
     *out = s.ws;
@@ -141,6 +148,30 @@ int check_out(const ctb_view* out, int64_t numel, int dtype, const char* who) {
     if (out->dtype != dtype) return set_error(CTB_ERR_DTYPE, "%s: output dtype mismatch", who);
     if (view_numel(out) != numel) return set_error(CTB_ERR_SHAPE, "%s: output has %lld elements, expected %lld", who, (long long)view_numel(out), (long long)numel);
     if (!view_contiguous(out)) return set_error(CTB_ERR_SHAPE, "%s: output must be contiguous", who);
+    return CTB_OK;
+}
+
+// The byte range of storage a view can touch: [lo, hi).
+void view_bytes(const ctb_view* v, const char** lo, const char** hi) {
+    const size_t es = dtype_bytes(v->dtype);
+    const int64_t span = view_span(v);
+    *lo = (const char*)v->base + (size_t)v->offset * es;
+    *hi = span > v->offset ? (const char*)v->base + (size_t)span * es : *lo;
+}
+
+// Every operator writes a FRESH tensor (src/core/opsmp.cpp:148,277,607); the kernels read inputs
+// through non-coherent loads and in another order than they write, so an output that overlaps an
+// input is refused instead of computed wrongly.
+int check_no_alias(const ctb_view* out, const ctb_view* const* in, int nin, const char* who) {
+    const char *olo, *ohi;
+    view_bytes(out, &olo, &ohi);
+    if (olo == ohi) return CTB_OK;
+    for (int i = 0; i < nin; ++i) {
+        if (!in[i] || !in[i]->base) continue;
+        const char *lo, *hi;
+        view_bytes(in[i], &lo, &hi);
+        if (lo < ohi && olo < hi) return set_error(CTB_ERR_ARG, "%s: the output overlaps an input", who);
+    }
     return CTB_OK;
 }
 
@@ -291,7 +322,10 @@ int reduce_out_check(int op, const ctb_view* a, int dim, const ctb_view* out) {
     int64_t nout = 1;
     if (dim != CTB_DIM_FULL)
         for (int d = 0; d < a->ndim; ++d) if (d != dim) nout *= a->shape[d];
-    return check_out(out, nout, op == CTB_ARGMAX ? CTB_I32 : a->dtype, "reduction");
+    int rc = check_out(out, nout, op == CTB_ARGMAX ? CTB_I32 : a->dtype, "reduction");
+    if (rc) return rc;
+    const ctb_view* in[1] = {a};
+    return check_no_alias(out, in, 1, "reduction");
 }
 
 int reduce_arg_check(int op, const ctb_view* a, int dim) {
@@ -310,11 +344,15 @@ int reduce_arg_check(int op, const ctb_view* a, int dim) {
 
 // Scratch needed by ctb_reduce for (a, dim): kernel scratch, plus a packed copy of the input
 // when a full reduction is asked of a non-dense view.
-size_t reduce_ws_need(const ctb_view* a, int dim, size_t* copy_bytes, bool want_partial = false) {
+// `op` < 0 = not known (the size query): the larger answer.  A dense but permuted view is
+// folded in memory order for sum/mean/var; max/min must see the elements in the view's own
+// order (which zero comes first decides the sign of a zero result), so they pack it first.
+size_t reduce_ws_need(int op, const ctb_view* a, int dim, size_t* copy_bytes, bool want_partial = false) {
     ReduceGeom g;
     *copy_bytes = 0;
     if (dim == CTB_DIM_FULL) {
-        if (!view_dense(a)) *copy_bytes = (((size_t)view_numel(a) * dtype_bytes(a->dtype)) + 255) / 256 * 256;
+        const bool order_matters = op < 0 || op == CTB_MAX || op == CTB_MIN;
+        if (!view_dense(a) || (order_matters && !view_contiguous(a))) *copy_bytes = (((size_t)view_numel(a) * dtype_bytes(a->dtype)) + 255) / 256 * 256;
         reduce_geom_full_dense(a, &g);
     } else {
         reduce_geom_dim(a, dim, &g);
@@ -332,7 +370,7 @@ int do_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, double* p
     ReduceGeom g;
     const void* src = elem_ptr(a);
     size_t copy_bytes = 0;
-    const size_t need = reduce_ws_need(a, dim, &copy_bytes, partial != nullptr);
+    const size_t need = reduce_ws_need(op, a, dim, &copy_bytes, partial != nullptr);
     if (need > ws_bytes || (need && !ws)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace of %zu bytes needed, %zu given", need, ws_bytes);
     if (need && !is_aligned(ws, 256)) return set_error(CTB_ERR_WORKSPACE, "reduction: workspace must be 256-byte aligned");
     if (dim == CTB_DIM_FULL) {
@@ -521,6 +559,7 @@ int ctb_binary(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out
     Plan p;
     if ((rc = build_plan(in, 2, &p))) return rc;
     if ((rc = check_out(out, p.numel, a->dtype, "binary_op"))) return rc;
+    if ((rc = check_no_alias(out, in, 2, "binary_op"))) return rc;
     return launch_binary(op, a->dtype, p, elem_ptr(a), elem_ptr(b), elem_ptr_mut(out), (cudaStream_t)stream);
 }
 
@@ -532,6 +571,7 @@ int ctb_unary(int op, const ctb_view* a, double scalar, const ctb_view* out, voi
     Plan p;
     if ((rc = build_plan(in, 1, &p))) return rc;
     if ((rc = check_out(out, p.numel, a->dtype, "unary_op"))) return rc;
+    if ((rc = check_no_alias(out, in, 1, "unary_op"))) return rc;
     return launch_unary(op, a->dtype, p, elem_ptr(a), scalar, elem_ptr_mut(out), (cudaStream_t)stream);
 }
 
@@ -542,6 +582,7 @@ int ctb_copy_strided(const ctb_view* src, const ctb_view* out, void* stream) {
     Plan p;
     if ((rc = build_plan(in, 1, &p))) return rc;
     if ((rc = check_out(out, p.numel, src->dtype, "copy"))) return rc;
+    if ((rc = check_no_alias(out, in, 1, "copy"))) return rc;
     return launch_copy((int)dtype_bytes(src->dtype), p, elem_ptr(src), elem_ptr_mut(out), (cudaStream_t)stream);
 }
 
@@ -549,7 +590,7 @@ size_t ctb_reduce_workspace_bytes(const ctb_view* a, int dim) {
     if (check_view(a, "reduction: null input", "reduction")) return 0;
     if (dim != CTB_DIM_FULL && (dim < 0 || dim >= a->ndim)) return 0;
     size_t copy_bytes;
-    return reduce_ws_need(a, dim, &copy_bytes);
+    return reduce_ws_need(-1, a, dim, &copy_bytes);
 }
 
 int ctb_reduce_ws(int op, const ctb_view* a, int dim, const ctb_view* out, void* workspace,
@@ -568,9 +609,9 @@ int ctb_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, void* st
     if ((rc = reduce_arg_check(op, a, dim))) return rc;
     if ((rc = reduce_out_check(op, a, dim, out))) return rc;
     size_t copy_bytes;
-    const size_t need = reduce_ws_need(a, dim, &copy_bytes);
+    const size_t need = reduce_ws_need(op, a, dim, &copy_bytes);
     void* ws = nullptr;
-    if ((rc = ensure_workspace(need, &ws))) return rc;
+    if ((rc = ensure_workspace(need, &ws, (cudaStream_t)stream))) return rc;
     return do_reduce(op, a, dim, out, nullptr, ws, need, (cudaStream_t)stream);
 }
 
@@ -593,9 +634,9 @@ int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* st
         return set_error(CTB_ERR_ARG, "reduction: fp64 partials exist for sum/mean/max/min only");
     if (a->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "reduction: fp64 partials need a Float32 input");
     size_t copy_bytes;
-    const size_t need = reduce_ws_need(a, CTB_DIM_FULL, &copy_bytes, true);
+    const size_t need = reduce_ws_need(op, a, CTB_DIM_FULL, &copy_bytes, true);
     void* ws = nullptr;
-    if ((rc = ensure_workspace(need, &ws))) return rc;
+    if ((rc = ensure_workspace(need, &ws, (cudaStream_t)stream))) return rc;
     return do_reduce(op, a, CTB_DIM_FULL, nullptr, partial, ws, need, (cudaStream_t)stream);
 }
 
@@ -615,6 +656,8 @@ static int softmax_entry(const ctb_view* x, const ctb_view* mask, int causal, in
     RowsGeom g;
     if ((rc = rows_geom(x, mask, &g, who))) return rc;
     if ((rc = check_out(out, g.rows * g.cols, CTB_F32, who))) return rc;
+    const ctb_view* ins[2] = {x, mask};
+    if ((rc = check_no_alias(out, ins, 2, who))) return rc;
     return launch_softmax(g, (const float*)elem_ptr(x), mask ? (const float*)elem_ptr(mask) : nullptr,
                           causal, log_out, (float*)elem_ptr_mut(out), (cudaStream_t)stream);
 }
@@ -644,6 +687,8 @@ int ctb_layernorm_lastdim(const ctb_view* x, const ctb_view* gamma, const ctb_vi
         st[i] = gb[i]->stride[gb[i]->ndim - 1];
     }
     if ((rc = check_out(out, g.rows * g.cols, CTB_F32, "layernorm"))) return rc;
+    const ctb_view* ins[3] = {x, gamma, beta};
+    if ((rc = check_no_alias(out, ins, 3, "layernorm"))) return rc;
     return launch_layernorm(g, (const float*)elem_ptr(x), gamma ? (const float*)elem_ptr(gamma) : nullptr, st[0],
                             beta ? (const float*)elem_ptr(beta) : nullptr, st[1], eps,
                             (float*)elem_ptr_mut(out), (cudaStream_t)stream);
@@ -767,7 +812,7 @@ int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream)
     kernel_ws = (kernel_ws + 255) / 256 * 256;
     const size_t tmp_bytes = (tmp_elems * eb + 255) / 256 * 256;
     void* ws = nullptr;
-    if (ngroups > 0 && (rc = ensure_workspace(kernel_ws + 2 * tmp_bytes, &ws))) return rc;
+    if (ngroups > 0 && (rc = ensure_workspace(kernel_ws + 2 * tmp_bytes, &ws, st))) return rc;
 
     const bool grad_dense = view_contiguous(grad);
     for (int gi = 0; gi < ngroups; ++gi) {
@@ -852,7 +897,7 @@ int ctb_channel_moments(const ctb_view* x, const ctb_view* mean, const ctb_view*
     if ((rc = current_device_info(&di))) return rc;
     const size_t need = channel_moments_workspace_bytes(C, di.sm_count);
     void* ws = nullptr;
-    if ((rc = ensure_workspace(need, &ws))) return rc;
+    if ((rc = ensure_workspace(need, &ws, (cudaStream_t)stream))) return rc;
     return launch_channel_moments((const float*)elem_ptr(x), (float*)elem_ptr_mut(mean), (float*)elem_ptr_mut(var),
                                   N, C, S, ws, need, (cudaStream_t)stream);
 }
@@ -872,7 +917,7 @@ int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view*
     if (N * C * S == 0) return CTB_OK;
     // 1/sqrt(var + eps) per channel lives behind the workspace's ticket region
     void* ws = nullptr;
-    if ((rc = ensure_workspace(kTicketBytes + (size_t)C * sizeof(float), &ws))) return rc;
+    if ((rc = ensure_workspace(kTicketBytes + (size_t)C * sizeof(float), &ws, (cudaStream_t)stream))) return rc;
     return launch_batchnorm_apply((const float*)elem_ptr(x), pm, sm, pv, sv, pg, sg, pb, sb, eps,
                                   (float*)((char*)ws + kTicketBytes), (float*)elem_ptr_mut(out), N, C, S,
                                   (cudaStream_t)stream);
@@ -1012,6 +1057,8 @@ static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* 
     if ((rc = build_plan(in, nin, &p))) return rc;
     if ((rc = check_out(out, p.numel, a->dtype, who))) return rc;
     if (p.numel == 0) return CTB_OK;
+    if (device < 0 || device >= kMaxDevices) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
+    std::lock_guard<std::mutex> host_lock(g_host_mu[device]);
     DeviceGuard guard(device);
     if (!guard.ok) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
     const size_t es = dtype_bytes(a->dtype);
@@ -1029,7 +1076,8 @@ static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* 
         const char* hb = nin == 2 ? (const char*)elem_ptr(b) : nullptr;
         char* ho = (char*)elem_ptr_mut(out);
         int64_t c = 0;
-        for (int64_t lo = 0; lo < p.numel; lo += chunk, ++c) {
+        // one chunk: upload -> kernel -> download on its stream
+        auto run_chunk = [&](int64_t lo, int64_t c) -> int {
             const int64_t n = p.numel - lo < chunk ? p.numel - lo : chunk;
             cudaStream_t st = streams[c % 3];
             char* base = stage + slot * (c % 3);
@@ -1041,13 +1089,19 @@ static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* 
             Plan cp = p;
             cp.numel = n;
             cp.shape[0] = n;
-            rc = nin == 2 ? launch_binary(op, a->dtype, cp, da, db, dout, st)
-                          : launch_unary(op, a->dtype, cp, da, scalar, dout, st);
-            if (rc) return rc;
+            int r = nin == 2 ? launch_binary(op, a->dtype, cp, da, db, dout, st)
+                             : launch_unary(op, a->dtype, cp, da, scalar, dout, st);
+            if (r) return r;
             CTB_CUDA_TRY(cudaMemcpyAsync(ho + (size_t)lo * es, dout, (size_t)n * es, cudaMemcpyDeviceToHost, st));
+            return CTB_OK;
+        };
+        for (int64_t lo = 0; lo < p.numel && !rc; lo += chunk, ++c) rc = run_chunk(lo, c);
+        // also on failure: no copy may still read or write the caller's buffers after the return
+        for (int i = 0; i < 3; ++i) {
+            const cudaError_t e = cudaStreamSynchronize(streams[i]);
+            if (e != cudaSuccess && !rc) rc = cuda_error(e, "host-buffer pipeline");
         }
-        for (int i = 0; i < 3; ++i) CTB_CUDA_TRY(cudaStreamSynchronize(streams[i]));
-        return CTB_OK;
+        return rc;
     }
     // general case: upload the touched storage spans, run once, download
     const size_t out_bytes = align_up((size_t)p.numel * es, 256);
@@ -1061,7 +1115,7 @@ static int host_elementwise(int nin, int op, const ctb_view* a, const ctb_view* 
     dout.base = stage + used;
     dout.offset = 0;
     rc = nin == 2 ? ctb_binary(op, &da, &db, &dout, st) : ctb_unary(op, &da, scalar, &dout, st);
-    if (rc) return rc;
+    if (rc) { cudaStreamSynchronize(st); return rc; }    // the uploads still read the caller's buffers
     CTB_CUDA_TRY(cudaMemcpyAsync(elem_ptr_mut(out), dout.base, (size_t)p.numel * es, cudaMemcpyDeviceToHost, st));
     CTB_CUDA_TRY(cudaStreamSynchronize(st));
     return CTB_OK;
@@ -1081,6 +1135,8 @@ int ctb_reduce_host(int op, const ctb_view* a, int dim, const ctb_view* out, int
     int rc;
     if ((rc = reduce_arg_check(op, a, dim))) return rc;
     if ((rc = reduce_out_check(op, a, dim, out))) return rc;
+    if (device < 0 || device >= kMaxDevices) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
+    std::lock_guard<std::mutex> host_lock(g_host_mu[device]);
     DeviceGuard guard(device);
     if (!guard.ok) return set_error(CTB_ERR_CUDA, "cannot select CUDA device %d", device);
     const size_t oes = dtype_bytes(out->dtype);
@@ -1095,7 +1151,7 @@ int ctb_reduce_host(int op, const ctb_view* a, int dim, const ctb_view* out, int
     if ((rc = upload_view(a, stage, &used, &da, st))) return rc;
     dout.base = stage + used;
     dout.offset = 0;
-    if ((rc = ctb_reduce(op, &da, dim, &dout, st))) return rc;
+    if ((rc = ctb_reduce(op, &da, dim, &dout, st))) { cudaStreamSynchronize(st); return rc; }
     CTB_CUDA_TRY(cudaMemcpyAsync(elem_ptr_mut(out), dout.base, (size_t)nout * oes, cudaMemcpyDeviceToHost, st));
     CTB_CUDA_TRY(cudaStreamSynchronize(st));
     return CTB_OK;

@@ -12,7 +12,8 @@
 //   cols       : an outer dim is contiguous (e.g. dim 0 of a row-major matrix) -> threads are
 //                coalesced along that dim and walk the reduce dim; row chunks are split over
 //                CTAs and combined by the same ticket scheme.
-//   generic    : any other geometry or dtype: one thread per output.
+//   generic    : any other geometry or dtype: a thread, a warp or a CTA chunk per output line,
+//                picked from the number and length of the lines.
 // Sums accumulate in fp64.  Every combine order is fixed by the launch geometry alone, so
 // results are identical from run to run.  No kernel waits on another block: the ticket is an
 // atomic counter that is read once, and the block that sees the last value does the combine.
@@ -68,19 +69,41 @@ template <typename VT> struct SumPol {
 };
 
 // std::max(acc, val) == (acc < val) ? val : acc — a NaN val never replaces acc
-// (src/core/opsmp.cpp:679-691).
+// (src/core/opsmp.cpp:679-691).  The reference walks the line in index order, so when the
+// extreme value is a zero and zeros of both signs are present it returns the FIRST zero of the
+// line (+0 and -0 compare equal, the earlier one stays).  A tree cannot know which zero came
+// first from the values alone, so the accumulator also carries z = 2*index + signbit of the
+// earliest zero seen (kNoZero when none); the finaliser takes the sign from z when m == 0.
+// Zeros are rare: the hot loops test a whole batch of loads for "any zero" with one predicate
+// chain and branch to note_zero() only then.
+constexpr int64_t kNoZero = 0x7FFFFFFFFFFFFFFFll;
 template <typename VT, bool IS_MAX> struct MinMaxPol {
-    struct Acc { VT m; };
+    struct Acc { VT m; int64_t z; };
     __device__ __forceinline__ static VT pick(VT acc, VT v) {
         if (IS_MAX) return (acc < v) ? v : acc;
         return (v < acc) ? v : acc;
     }
     __device__ __forceinline__ static Acc init() {
-        return {IS_MAX ? -(VT)INFINITY : (VT)INFINITY};
+        return {IS_MAX ? -(VT)INFINITY : (VT)INFINITY, kNoZero};
     }
     __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double) { a.m = pick(a.m, x); }
-    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) { return {pick(a.m, b.m)}; }
-    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) { return {__shfl_down_sync(0xffffffffu, a.m, off)}; }
+    __device__ __forceinline__ static void note_zero(Acc& a, VT x, int64_t idx) {
+        if (x == (VT)0) {
+            const int64_t key = 2 * idx + (signbit(x) ? 1 : 0);
+            if (key < a.z) a.z = key;
+        }
+    }
+    __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) {
+        return {pick(a.m, b.m), a.z < b.z ? a.z : b.z};
+    }
+    __device__ __forceinline__ static Acc shfl_down(const Acc& a, int off) {
+        return {__shfl_down_sync(0xffffffffu, a.m, off), __shfl_down_sync(0xffffffffu, a.z, off)};
+    }
+    // the extreme with the reference's sign rule for zeros applied
+    __device__ __forceinline__ static VT value(const Acc& a) {
+        if (a.m == (VT)0 && a.z != kNoZero) return (a.z & 1) ? -(VT)0 : (VT)0;
+        return a.m;
+    }
 };
 
 // Biased variance from two shifted moments in fp64: with d = x - shift (shift = first element of
@@ -145,8 +168,9 @@ template <typename T> struct Finalize {
     }
     template <typename VT, bool IS_MAX>
     __device__ __forceinline__ static void run_mm(const typename MinMaxPol<VT, IS_MAX>::Acc& a, void* out, int64_t oi, double* po) {
-        if (po) { po[oi] = (double)a.m; return; }
-        ((T*)out)[oi] = from_double<T>((double)a.m);
+        const VT m = MinMaxPol<VT, IS_MAX>::value(a);
+        if (po) { po[oi] = (double)m; return; }
+        ((T*)out)[oi] = from_double<T>((double)m);
     }
     template <typename VT>
     __device__ __forceinline__ static void run_var(const typename VarPol<VT>::Acc& a, int64_t n, void* out, int64_t oi) {
@@ -185,6 +209,17 @@ template <typename Pol> struct ColsUnroll { static constexpr int value = CTB_RED
 
 template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
 template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
+
+// Policies that must know where the zeros of a line are (max/min, see MinMaxPol).
+template <typename Pol> struct TracksZero { static constexpr bool value = false; };
+template <typename VT, bool M> struct TracksZero<MinMaxPol<VT, M>> { static constexpr bool value = true; };
+
+// One element through a policy on the scalar paths (ragged ends, the generic kernels).
+template <typename Pol, typename VT>
+__device__ __forceinline__ void add_element(typename Pol::Acc& acc, VT x, int64_t idx, double shift) {
+    Pol::add(acc, x, idx, shift);
+    if constexpr (TracksZero<Pol>::value) Pol::note_zero(acc, x, idx);
+}
 
 // ---- helpers -----------------------------------------------------------------------------------------
 struct OuterIdx {
@@ -263,6 +298,19 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
     for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
+    if constexpr (TracksZero<Pol>::value) {
+        bool any_zero = false;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
+        if (any_zero) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) Pol::note_zero(acc, v[u].v[k], j + u * stride + k);
+        }
+    }
 }
 
 template <typename Pol, int VEC, int UNROLL>
@@ -286,7 +334,7 @@ __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const fl
     for (; j + VEC <= hi; j += stride) accumulate_batch<Pol, VEC, 1>(acc, line, j, stride, shift);
     if (VEC > 1) {   // ragged end of the line
         for (int k = 0; k < VEC; ++k)
-            if (j + k < hi) Pol::add(acc, line[j + k], j + k, (double)shift);
+            if (j + k < hi) add_element<Pol>(acc, line[j + k], j + k, (double)shift);
     }
 }
 
@@ -382,6 +430,19 @@ __device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const 
     for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
+    if constexpr (TracksZero<Pol>::value) {
+        bool any_zero = false;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
+        if (any_zero) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) Pol::note_zero(acc[k], v[u].v[k], r + 8 * u);
+        }
+    }
 }
 
 template <typename Pol, int VEC>
@@ -474,8 +535,79 @@ reduce_generic_kernel(const T* __restrict__ a, void* out, OuterIdx o, int64_t no
         const T* line = a + outer_offset(o, i);
         const double shift = NeedsShift<Pol>::value && rlen > 0 ? to_double(line[0]) : 0.0;
         typename Pol::Acc acc = Pol::init();
-        for (int64_t k = 0; k < rlen; ++k) Pol::add(acc, to_double(line[k * rstride]), k, shift);
+        for (int64_t k = 0; k < rlen; ++k) add_element<Pol>(acc, to_double(line[k * rstride]), k, shift);
         Fin<T, Pol>::run(op, acc, rlen, out, i, nullptr);
+    }
+}
+
+// Generic lines, a warp per line: lanes stride over the line (coalesced when rstride == 1).
+template <typename Pol, typename T>
+__global__ void __launch_bounds__(256)
+reduce_generic_warp_kernel(const T* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen,
+                           int64_t rstride, int op) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * 8;
+    for (int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); i < nout; i += warps) {
+        const T* line = a + outer_offset(o, i);
+        const double shift = NeedsShift<Pol>::value ? to_double(line[0]) : 0.0;
+        typename Pol::Acc acc = Pol::init();
+        for (int64_t k = lane; k < rlen; k += 32) add_element<Pol>(acc, to_double(line[k * rstride]), k, shift);
+        acc = warp_reduce<Pol>(acc);
+        if (lane == 0) Fin<T, Pol>::run(op, acc, rlen, out, i, nullptr);
+    }
+}
+
+// Generic lines, few and long: grid = (splits, lines); a CTA folds elements [lo, hi) of its line,
+// four loads in flight per thread; with more than one split the partials are combined in index
+// order by the CTA that draws the line's last ticket (as in reduce_rows_split_kernel).
+template <typename Pol, typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+reduce_generic_split_kernel(const T* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen,
+                            int64_t rstride, int64_t chunk, int op, uint32_t* tickets,
+                            typename Pol::Acc* partials) {
+    __shared__ typename Pol::Acc smem[THREADS / 32];
+    __shared__ bool is_last;
+    const int splits = gridDim.x;
+    for (int64_t row = blockIdx.y; row < nout; row += gridDim.y) {
+        const T* line = a + outer_offset(o, row);
+        const double shift = NeedsShift<Pol>::value ? to_double(line[0]) : 0.0;
+        const int64_t lo = (int64_t)blockIdx.x * chunk;
+        int64_t hi = lo + chunk;
+        if (hi > rlen) hi = rlen;
+        typename Pol::Acc acc = Pol::init();
+        int64_t k = lo + threadIdx.x;
+        for (; k + 3 * THREADS < hi; k += 4 * THREADS) {
+            T v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = line[(k + u * THREADS) * rstride];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) add_element<Pol>(acc, to_double(v[u]), k + u * THREADS, shift);
+        }
+        for (; k < hi; k += THREADS) add_element<Pol>(acc, to_double(line[k * rstride]), k, shift);
+        acc = block_reduce<Pol, THREADS>(acc, smem);
+        if (splits == 1) {
+            if (threadIdx.x == 0) Fin<T, Pol>::run(op, acc, rlen, out, row, nullptr);
+            continue;
+        }
+        if (threadIdx.x == 0) {
+            partials[row * splits + blockIdx.x] = acc;
+            __threadfence();
+            const uint32_t t = atomicAdd(&tickets[row], 1u);
+            is_last = (t == (uint32_t)splits - 1);
+        }
+        __syncthreads();
+        if (is_last) {          // uniform across the CTA
+            __threadfence();
+            typename Pol::Acc c = Pol::init();
+            const typename Pol::Acc* p = partials + row * splits;
+            for (int i = threadIdx.x; i < splits; i += THREADS) c = Pol::combine(c, load_cg(p + i));
+            c = block_reduce<Pol, THREADS>(c, smem);
+            if (threadIdx.x == 0) {
+                Fin<T, Pol>::run(op, c, rlen, out, row, nullptr);
+                tickets[row] = 0;
+            }
+        }
+        __syncthreads();        // is_last and smem are reused by the next line
     }
 }
 
@@ -491,7 +623,7 @@ __global__ void finalize_full_kernel(int op, const double* partial, int64_t tota
 // ---- host side --------------------------------------------------------------------------------------------
 namespace {
 
-enum Shape { SH_ROWS_WARP, SH_ROWS_BLOCK, SH_ROWS_SPLIT, SH_COLS, SH_GENERIC };
+enum Shape { SH_ROWS_WARP, SH_ROWS_BLOCK, SH_ROWS_SPLIT, SH_COLS, SH_GENERIC, SH_GENERIC_WARP, SH_GENERIC_SPLIT };
 
 struct Choice {
     Shape shape;
@@ -533,10 +665,33 @@ int cols_splits_bound(int64_t tiles, int sm_count, int64_t rlen) {
     return s;
 }
 
+// Any dtype and geometry the Float32 fast paths do not take.  A thread per line when the lines
+// are short or plentiful enough to fill the machine that way; a CTA per line chunk when there are
+// few long lines (a full reduction of a Float64 or Int32 tensor is ONE line: a thread per line
+// would fold the whole tensor serially); a warp per line in between.
+constexpr int kGenericThreads = 256;
+void choose_generic(const ReduceGeom& g, int sm_count, Choice* c) {
+    c->shape = SH_GENERIC;
+    c->vec = 1;
+    c->splits = 1;
+    c->chunk = g.rlen;
+    if (g.nout == 0 || g.rlen < 64) return;
+    const int64_t resident_threads = (int64_t)sm_count * 2048;
+    if (g.nout >= resident_threads) return;
+    if (g.nout * 32 >= resident_threads || g.rlen < 4096) { c->shape = SH_GENERIC_WARP; return; }
+    c->shape = SH_GENERIC_SPLIT;
+    int64_t want = ceil_div((int64_t)sm_count * 8, g.nout);          // about 8 CTAs per SM in all
+    const int64_t max_splits = g.rlen / (4 * kGenericThreads);       // at least one unrolled pass each
+    if (want > max_splits) want = max_splits;
+    if (want > 4096) want = 4096;
+    if (want < 1 || g.nout > kCounterSlots) want = 1;
+    c->chunk = ceil_div(g.rlen, want);
+    c->splits = (int)ceil_div(g.rlen, c->chunk);
+}
+
 Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
     Choice c{};
-    c.shape = SH_GENERIC;
-    c.vec = 1;
+    choose_generic(g, sm_count, &c);
     if (dtype != CTB_F32 || g.nout == 0 || g.rlen == 0) return c;
     const bool base16 = a == nullptr || is_aligned(a, 16);
     if (g.rstride == 1 || g.rlen == 1) {
@@ -586,6 +741,7 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
 size_t scratch_bytes(const ReduceGeom& g, const Choice& c) {
     if (c.shape == SH_ROWS_SPLIT) return kCounterBytes + (size_t)g.nout * c.splits * 16;
     if (c.shape == SH_COLS && c.splits_bound > 1) return kCounterBytes + (size_t)c.batch * c.splits_bound * g.oshape[g.nouter - 1] * 16;
+    if (c.shape == SH_GENERIC_SPLIT && c.splits > 1) return kCounterBytes + (size_t)g.nout * c.splits * 16;
     return 0;
 }
 
@@ -657,27 +813,43 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
     return cuda_error(cudaGetLastError(), "reduce launch");
 }
 
-template <typename T>
-int launch_generic_t(int op, const ReduceGeom& g, const T* a, void* out, int sm_count, cudaStream_t st) {
-    int64_t blocks = ceil_div(g.nout, 256);
-    int64_t cap = (int64_t)sm_count * 8;
-    int grid = (int)(blocks < cap ? blocks : cap);
-    if (grid < 1) grid = 1;
+template <typename Pol, typename T>
+int launch_generic_pol(const Choice& c, int op, const ReduceGeom& g, const T* a, void* out, void* ws, int sm_count,
+                       cudaStream_t st) {
+    static_assert(sizeof(typename Pol::Acc) <= 16, "accumulator larger than the scratch slot");
     OuterIdx o = outer_of(g, g.nouter);
-    switch (op) {
-    case CTB_SUM: case CTB_MEAN: case kOpSumAccumulate:
-        reduce_generic_kernel<SumPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
-    case CTB_MAX:
-        reduce_generic_kernel<MinMaxPol<double, true>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
-    case CTB_MIN:
-        reduce_generic_kernel<MinMaxPol<double, false>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
-    case CTB_VAR:
-        reduce_generic_kernel<VarPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
-    case CTB_ARGMAX:
-        reduce_generic_kernel<ArgmaxPol<double>, T><<<grid, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op); break;
-    default: return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
+    const int64_t cap = (int64_t)sm_count * 8;
+    if (c.shape == SH_GENERIC_SPLIT) {
+        uint32_t* tickets = (uint32_t*)ws;
+        typename Pol::Acc* partials = (typename Pol::Acc*)((char*)ws + kCounterBytes);
+        dim3 grid((unsigned)c.splits, (unsigned)(g.nout < 65535 ? g.nout : 65535));
+        reduce_generic_split_kernel<Pol, T, kGenericThreads><<<grid, kGenericThreads, 0, st>>>(
+            a, out, o, g.nout, g.rlen, g.rstride, c.chunk, op, tickets, partials);
+    } else if (c.shape == SH_GENERIC_WARP) {
+        int64_t blocks = ceil_div(g.nout, 8);
+        if (blocks > cap * 4) blocks = cap * 4;
+        reduce_generic_warp_kernel<Pol, T><<<(unsigned)blocks, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op);
+    } else {
+        int64_t blocks = ceil_div(g.nout, 256);
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        reduce_generic_kernel<Pol, T><<<(unsigned)blocks, 256, 0, st>>>(a, out, o, g.nout, g.rlen, g.rstride, op);
     }
     return cuda_error(cudaGetLastError(), "reduce_generic launch");
+}
+
+template <typename T>
+int launch_generic_t(const Choice& c, int op, const ReduceGeom& g, const T* a, void* out, void* ws, int sm_count,
+                     cudaStream_t st) {
+    switch (op) {
+    case CTB_SUM: case CTB_MEAN: case kOpSumAccumulate:
+        return launch_generic_pol<SumPol<double>, T>(c, op, g, a, out, ws, sm_count, st);
+    case CTB_MAX: return launch_generic_pol<MinMaxPol<double, true>, T>(c, op, g, a, out, ws, sm_count, st);
+    case CTB_MIN: return launch_generic_pol<MinMaxPol<double, false>, T>(c, op, g, a, out, ws, sm_count, st);
+    case CTB_VAR: return launch_generic_pol<VarPol<double>, T>(c, op, g, a, out, ws, sm_count, st);
+    case CTB_ARGMAX: return launch_generic_pol<ArgmaxPol<double>, T>(c, op, g, a, out, ws, sm_count, st);
+    }
+    return set_error(CTB_ERR_ARG, "reduce: unknown operator code %d", op);
 }
 
 }  // namespace
@@ -713,11 +885,11 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
     if (need > ws_bytes || (need && !ws)) return set_error(CTB_ERR_WORKSPACE, "reduce: workspace of %zu bytes needed, %zu given", need, ws_bytes);
     if (need && !is_aligned(ws, 256)) return set_error(CTB_ERR_WORKSPACE, "reduce: workspace must be 256-byte aligned");
 
-    if (c.shape == SH_GENERIC) {
+    if (c.shape == SH_GENERIC || c.shape == SH_GENERIC_WARP || c.shape == SH_GENERIC_SPLIT) {
         switch (dtype) {
-        case CTB_F32: return launch_generic_t<float>(op, g, (const float*)a, out, di.sm_count, st);
-        case CTB_I32: return launch_generic_t<int32_t>(op, g, (const int32_t*)a, out, di.sm_count, st);
-        case CTB_F64: return launch_generic_t<double>(op, g, (const double*)a, out, di.sm_count, st);
+        case CTB_F32: return launch_generic_t<float>(c, op, g, (const float*)a, out, ws, di.sm_count, st);
+        case CTB_I32: return launch_generic_t<int32_t>(c, op, g, (const int32_t*)a, out, ws, di.sm_count, st);
+        case CTB_F64: return launch_generic_t<double>(c, op, g, (const double*)a, out, ws, di.sm_count, st);
         }
         return set_error(CTB_ERR_DTYPE, "reduce: unsupported dtype");
     }

@@ -15,7 +15,9 @@
 namespace {
 
 int g_device = 0;
-bool g_device_set = false;
+// The CUDA device is a per-thread setting: every host thread selects g_device before its first
+// operator (a process-wide flag would leave a second thread on device 0).
+thread_local int t_device_selected = -1;
 bool g_sync_after_op = true;
 ctb_host::GradFactory g_grad_factory;
 std::function<void(Tensor&)> g_backward;
@@ -31,11 +33,11 @@ std::function<void(Tensor&)> g_backward;
 inline void check(int status) { if (status != CTB_OK) raise(status); }
 
 void ensure_device() {
-    if (g_device_set) return;
+    if (t_device_selected == g_device) return;
     if (ctb_device_count() <= 0)
         throw std::runtime_error("ctensor_b200: no CUDA device (this library has no CPU fallback)");
     check(ctb_set_device(g_device));
-    g_device_set = true;
+    t_device_selected = g_device;
 }
 
 int dtype_code(DType dt, const char* who) {
@@ -129,6 +131,10 @@ Tensor reduce(int op, const char* name, const Tensor& a, int dim, bool grad) {
     if (!a.impl) throw std::runtime_error("reduction: null input");
     ensure_device();
     const int nd = (int)a.impl->ndim;
+    if (dim < -1) {                 // -1 is "everything"; other negative dims wrap (src/core/opsmp.cpp:598)
+        dim += nd;
+        if (dim < 0) throw std::out_of_range("reduction: dim out of range");
+    }
     std::vector<size_t> shape;
     if (dim >= 0 && dim < nd)
         for (int d = 0; d < nd; ++d) if (d != dim) shape.push_back(a.impl->shape[d]);
@@ -149,11 +155,11 @@ void set_device(int index) {
     if (ctb_device_count() <= index || index < 0) throw std::runtime_error("ctensor_b200: no such CUDA device");
     check(ctb_set_device(index));
     g_device = index;
-    g_device_set = true;
+    t_device_selected = index;
 }
 int device() { return g_device; }
 void set_sync_after_op(bool on) { g_sync_after_op = on; }
-void sync_for_host_access() { if (g_device_set) check(ctb_device_sync()); }
+void sync_for_host_access() { if (t_device_selected >= 0) check(ctb_device_sync()); }
 void set_grad_factory(GradFactory f) { g_grad_factory = std::move(f); }
 void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src) {
     if (!grad_buffer.impl) return;                      // as the reference: nothing to add to

@@ -18,7 +18,8 @@
  *  - Shapes and strides are in ELEMENTS, strides are non-negative, at most CTB_MAX_DIMS dims —
  *    the layout of the reference's Tensorimpl (src/core/tensor.h:322-358).
  *  - `out` views must be contiguous row-major (every reference op writes a fresh contiguous
- *    tensor: src/core/opsmp.cpp:148,277,607) and must not alias an input.
+ *    tensor: src/core/opsmp.cpp:148,277,607) and must not overlap an input: such a call is
+ *    refused with CTB_ERR_ARG (in-place entry points say so explicitly).
  *  - There is no CPU fallback: without a CUDA device every compute entry point fails with
  *    CTB_ERR_CUDA.
  */
@@ -144,9 +145,11 @@ int ctb_copy_strided(const ctb_view* src, const ctb_view* out, void* stream);
  * gives shape {1}).  dim == CTB_DIM_FULL: reduce everything to one element.  `out` has the
  * dtype of `a`, except CTB_ARGMAX which writes CTB_I32 and needs dim >= 0.
  * Accumulation is fp64 with a fixed combine order, so results are run-to-run identical.
- * Scratch memory for split reductions comes from a per-device workspace the library
- * allocates on first use (cudaMalloc) and keeps; calls on one device that share it must be
- * stream-ordered with respect to each other. */
+ * max/min return the zero the reference returns when the extreme is a zero of which both signs
+ * occur (the first in index order).  Scratch memory for split reductions comes from a
+ * per-device workspace the library allocates on first use (cudaMalloc) and keeps — a fresh
+ * workspace is cleared on `stream`; calls on one device that share it must be stream-ordered
+ * with respect to each other. */
 int ctb_reduce(int op, const ctb_view* a, int dim, const ctb_view* out, void* stream);
 
 /* Same, with caller-provided scratch (256-byte aligned device memory of at least
@@ -292,7 +295,9 @@ int ctb_optimizer_step(int kind, const ctb_view* param, const ctb_view* grad, fl
  * Same semantics as ctb_binary / ctb_unary / ctb_reduce, but every view points to HOST memory
  * (pinned memory gives full PCIe speed).  Inputs are staged to `device`, the kernel runs there
  * and the result is copied back before the call returns.  Contiguous same-shape inputs are
- * processed in chunks so that upload, kernel and download overlap. */
+ * processed in chunks so that upload, kernel and download overlap.  The calls of one device
+ * share its staging buffer and streams: they are serialised inside the library (a second host
+ * thread waits), and no copy is left in flight when a call returns, also when it fails. */
 int ctb_binary_host(int op, const ctb_view* a, const ctb_view* b, const ctb_view* out, int device);
 int ctb_unary_host(int op, const ctb_view* a, double scalar, const ctb_view* out, int device);
 int ctb_reduce_host(int op, const ctb_view* a, int dim, const ctb_view* out, int device);

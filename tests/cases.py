@@ -162,6 +162,28 @@ def all_cases():
                     exact=exact or v.dtype == ol.I32)
         if op in (ol.MAX, ol.MIN, ol.ARGMAX):
             add(name=f"red_{nm}_nan_rows", kind="reduce", op=op, views=[nan_rows], dim=1)
+    # zeros of both signs as the extreme value: the reference keeps the FIRST zero of a line in
+    # index order (std::max/min never replace an equal value), so the sign of a zero result depends
+    # on positions.  One input per kernel shape: short lines, long lines, column splits, very long
+    # lines (the split kernel), strided / other dtypes (the generic kernels).
+    def zeros_mix(seed, shape, sign):
+        pick = np.array([-0.0, 0.0, -1.5, -3.0], np.float32) * np.float32(sign)
+        return pick[_rng(seed).integers(0, 4, shape)]
+    for op, sign in ((ol.MAX, 1.0), (ol.MIN, -1.0)):
+        nm = ol.REDUCE_NAMES[op]
+        z2 = HostView.contig(zeros_mix(71, (33, 70), sign))
+        zlong = HostView.contig(zeros_mix(72, (3, 5000), sign))
+        ztall = HostView.contig(zeros_mix(73, (700, 36), sign))
+        zsplit = HostView.contig(zeros_mix(74, (2, 70000), sign))
+        zd = HostView.contig(zeros_mix(75, (9, 40), sign).astype(np.float64))
+        for vn, v, dims in (("2d", z2, (0, 1, -1)), ("long", zlong, (0, 1, -1)), ("tall", ztall, (0, 1, -1)),
+                            ("split", zsplit, (1, -1)), ("transposed", z2.permute([1, 0]), (0, 1, -1)),
+                            ("f64", zd, (0, 1, -1))):
+            for dim in dims:
+                add(name=f"red_{nm}_zeros_{vn}_d{dim}", kind="reduce", op=op, views=[v], dim=dim)
+        # relu output (+0 where the input was negative) joined with raw -0 inputs
+        add(name=f"red_{nm}_zeros_first_wins", kind="reduce", op=op, dim=1, views=[HostView.contig(np.array(
+            [[-0.0, 0.0, 0.0], [0.0, -0.0, -0.0], [-1.0 * sign, -0.0, 0.0], [0.0, -2.0 * sign, -0.0]], np.float32))])
     one = HostView.contig(np.array([4.25], np.float32))
     for op in (ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR):
         add(name=f"red_{ol.REDUCE_NAMES[op]}_single", kind="reduce", op=op, views=[one], dim=0, exact=True)

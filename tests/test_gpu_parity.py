@@ -165,6 +165,97 @@ def test_reduce_full_sizes(ct, oracle, op):
             assert_close(got, ref, RTOL, f"full n={n}")
 
 
+def _zeros_mix(seed, shape, sign, dtype=np.float32):
+    """Zeros of both signs among values on one side of zero: max (sign=+1) / min (sign=-1) is a zero
+    and its sign is the sign of the first zero of the line."""
+    pick = (np.array([-0.0, 0.0, -1.5, -3.0]) * sign).astype(dtype)
+    return pick[np.random.default_rng(seed).integers(0, 4, shape)]
+
+
+@pytest.mark.parametrize("shape,dim", [((2048, 4096), 0), ((2048, 4096), 1), ((4099, 1031), 0), ((4099, 1031), 1),
+                                       ((8, 300000), 1), ((300000, 8), 0), ((64, 20000), 1), ((3, 700, 1100), 1),
+                                       ((1 << 22,), 0), (((1 << 22) + 3,), -1), ((1500, 1500), -1)])
+@pytest.mark.parametrize("op", [ol.MAX, ol.MIN])
+def test_minmax_signed_zero_is_the_first_in_index_order(ct, oracle, shape, dim, op):
+    """Every reduction kernel shape on data whose extreme is a zero of either sign."""
+    x = HostView.contig(_zeros_mix(sum(shape), shape, 1.0 if op == ol.MAX else -1.0))
+    assert_bits_equal(ct.reduce(op, to_device(x), dim), oracle.reduce(op, x, dim), f"{shape} dim {dim}")
+    if len(shape) == 2:          # the transposed view: strided lines (generic kernels), permuted full reduction
+        t = x.permute([1, 0])
+        assert_bits_equal(ct.reduce(op, to_device(t), dim if dim < 0 else 1 - dim),
+                          oracle.reduce(op, t, dim if dim < 0 else 1 - dim), f"{shape}^T")
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.int32])
+@pytest.mark.parametrize("shape,dim", [(((1 << 22) + 5,), -1), ((1 << 20, 8), 0), ((8, 1 << 20), 1), ((3000, 700), 0),
+                                       ((3000, 700), 1), ((64, 50000), 1), ((70, 4, 30000), 2)])
+@pytest.mark.parametrize("op", [ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR, ol.ARGMAX])
+def test_reduce_other_dtypes_and_strided_shapes(ct, oracle, dtype, shape, dim, op):
+    """Float64 / Int32 tensors (and Float32 shapes outside the fast paths, below) go through the
+    generic kernels: a thread, a warp or a CTA chunk per line — a full reduction is one long line."""
+    if (op == ol.VAR and dtype == np.int32) or (op == ol.ARGMAX and dim < 0):
+        pytest.skip("not defined")
+    rng = np.random.default_rng(len(shape) * 7 + abs(dim))
+    raw = rng.standard_normal(shape) * 50
+    x = HostView.contig(raw.astype(dtype))
+    got = ct.reduce(op, to_device(x), dim)
+    ref = oracle.reduce(op, x, dim)
+    if op in (ol.MAX, ol.MIN, ol.ARGMAX) or dtype == np.int32 and op == ol.SUM:
+        assert_bits_equal(got, ref, f"{dtype.__name__} {shape} dim {dim}")
+    elif dtype == np.int32:      # mean of integers truncates: a last-bit difference of the fp64 sum can flip it
+        assert np.max(np.abs(got.cpu().numpy().astype(np.int64) - ref.astype(np.int64))) <= 1
+    else:
+        assert_close(got, ref, RTOL, f"{dtype.__name__} {shape} dim {dim}")
+
+
+@pytest.mark.parametrize("shape,dim", [((1 << 20, 8), 0), ((5000, 24), 0), ((40, 70001), 1)])
+@pytest.mark.parametrize("op", [ol.SUM, ol.MAX, ol.VAR, ol.ARGMAX])
+def test_reduce_f32_outside_the_fast_paths(ct, oracle, shape, dim, op):
+    """Fewer than 32 columns, or a strided reduce dim: Float32 lines the row / column kernels do not take."""
+    x = HostView.contig(np.random.default_rng(shape[1]).standard_normal(shape).astype(np.float32))
+    views = [x] if shape[1] < 32 else [HostView(x.buf, (shape[0], shape[1] // 2), (shape[1], 2), 1)]
+    for v in views:
+        got, ref = ct.reduce(op, to_device(v), dim), oracle.reduce(op, v, dim)
+        if op in (ol.MAX, ol.ARGMAX):
+            assert_bits_equal(got, ref, f"{shape} dim {dim}")
+        else:
+            assert_close(got, ref, RTOL, f"{shape} dim {dim}")
+
+
+def test_first_scratch_use_on_a_side_stream(ct, oracle):
+    """A reduction that makes the library (re)allocate its workspace, issued on a non-blocking side
+    stream: the clearing of the fresh workspace must be ordered before the kernel on THAT stream."""
+    buf = np.random.default_rng(77).standard_normal(1 << 27).astype(np.float32)
+    x = HostView(buf, (1 << 13, 1 << 13), (1 << 14, 2), 0)    # every other element: packed into the workspace first
+    d = to_device(x)
+    assert ct.reduce_workspace_bytes(d, -1) > (128 << 20)      # larger than any workspace an earlier test grew
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        got = ct.reduce(ct.SUM, d, -1)
+        again = ct.reduce(ct.SUM, d, -1)
+        cols = ct.reduce(ct.SUM, d, 0)                          # the ticket kernels on the same fresh workspace
+    side.synchronize()
+    assert_close(got, oracle.reduce(ol.SUM, x, -1), RTOL)
+    assert_bits_equal(again, got.cpu().numpy())
+    assert_close(cols, oracle.reduce(ol.SUM, x, 0), RTOL)
+
+
+def test_output_overlapping_an_input_is_refused(ct):
+    a = torch.zeros(64, 64, device="cuda")
+    b = torch.ones(64, 64, device="cuda")
+    for call in (lambda: ct.binary(ct.ADD, a, b, out=a), lambda: ct.unary(ct.EXP, a, out=a),
+                 lambda: ct.reduce(ct.SUM, a, 0, out=a.view(-1)[:64]), lambda: ct.softmax(a, out=a),
+                 lambda: ct.binary(ct.ADD, a, b, out=b.view(-1)[: 64 * 64].view(64, 64))):
+        with pytest.raises(ct.CtbError) as e:
+            call()
+        assert e.value.code == 5 and "overlaps an input" in e.value.message
+    # neighbours in one allocation do not overlap
+    buf = torch.zeros(2, 64, 64, device="cuda")
+    ct.binary(ct.ADD, buf[0], b, out=buf[1])
+    assert torch.all(buf[1] == 1)
+
+
 def test_argmax_ties_prefer_first_index(ct, oracle):
     x = np.zeros((64, 5000), np.float32)
     x[:, 1234] = 3.0

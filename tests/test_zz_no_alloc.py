@@ -35,6 +35,32 @@ def test_noalloc_reduction_matches_regular_entry_point(ct):
     assert np.array_equal(_bits(got), _bits(want))
 
 
+def test_noalloc_reduction_matches_the_cpu_oracle(ct, oracle):
+    """The entry point against the CPU restatement of the reference directly (not only against the
+    regular entry point): exact for max/min/argmax, 1e-5 relative for the sums; signed zeros included."""
+    import oracle_lib as ol
+    from oracle_lib import HostView
+    from gpu_util import to_device, assert_bits_equal, assert_close
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((4096, 640)).astype(np.float32)
+    x[rng.integers(0, 4096, 500), rng.integers(0, 640, 500)] = 0.0
+    x[rng.integers(0, 4096, 500), rng.integers(0, 640, 500)] = -0.0
+    z = np.minimum(x, 0.0).astype(np.float32)                      # column maxima are zeros of either sign
+    for arr in (x, z):
+        h = HostView.contig(arr)
+        d = to_device(h)
+        assert ct.reduce_workspace_bytes(d, 0) > 0
+        for op in (ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR, ol.ARGMAX):
+            ref = oracle.reduce(op, h, 0)
+            for call in range(2):
+                got = torch.empty(ref.shape, dtype=torch.int32 if op == ol.ARGMAX else torch.float32, device="cuda")
+                ct.reduce_dim_noalloc(op, d, 0, got)
+                if op in (ol.MAX, ol.MIN, ol.ARGMAX):
+                    assert_bits_equal(got, ref, f"op {op} call {call}")
+                else:
+                    assert_close(got, ref, 1e-5, f"op {op} call {call}")
+
+
 def test_noalloc_reduction_rejects_what_does_not_fit(ct):
     wide = torch.zeros(256, 131072, device="cuda")                  # needs ~6 MiB of partials
     assert ct.reduce_workspace_bytes(wide, 0) > ct.NOALLOC_SCRATCH_BYTES
