@@ -46,6 +46,8 @@ EXPORTED_SYMBOLS = [
     "ctb_log_softmax_lastdim", "ctb_gather", "ctb_accumulate_grad", "ctb_sgd_step", "ctb_adam_step",
     "ctb_copy_into", "ctb_cat", "ctb_channel_moments", "ctb_batchnorm_apply",
     "ctb_matmul", "ctb_optimizer_step",
+    "ctb_pool_alloc_managed", "ctb_pool_free_managed", "ctb_pool_trim", "ctb_pool_set_limit", "ctb_pool_stats",
+    "ctb_prefetch_managed",
 ]
 
 
@@ -65,6 +67,12 @@ class OptimizerHyper(ctypes.Structure):
 
 
 (OPT_SGD, OPT_ADAM, OPT_ADAMW, OPT_ADAMAX, OPT_NADAM, OPT_RADAM, OPT_RMSPROP, OPT_ADAGRAD, OPT_LION) = range(9)
+
+
+class PoolInfo(ctypes.Structure):
+    """struct ctb_pool_info."""
+    _fields_ = [("live_bytes", ctypes.c_size_t), ("cached_bytes", ctypes.c_size_t), ("cached_blocks", ctypes.c_size_t),
+                ("hits", ctypes.c_uint64), ("misses", ctypes.c_uint64), ("trims", ctypes.c_uint64)]
 
 
 class View(ctypes.Structure):
@@ -108,6 +116,14 @@ def lib() -> ctypes.CDLL:
     L.ctb_alloc.argtypes = [ctypes.POINTER(vd), ctypes.c_size_t, i32, vd]
     L.ctb_free.argtypes = [vd, vd]
     L.ctb_sync.argtypes = [vd]
+    L.ctb_alloc_managed.argtypes = [ctypes.POINTER(vd), ctypes.c_size_t, i32]
+    L.ctb_free_managed.argtypes = [vd]
+    L.ctb_pool_alloc_managed.argtypes = [ctypes.POINTER(vd), ctypes.c_size_t, i32, i32, vd]
+    L.ctb_pool_free_managed.argtypes = [vd]
+    L.ctb_pool_trim.argtypes = [i32]
+    L.ctb_pool_set_limit.argtypes = [i32, ctypes.c_size_t]
+    L.ctb_pool_stats.argtypes = [i32, ctypes.POINTER(PoolInfo)]
+    L.ctb_prefetch_managed.argtypes = [vd, ctypes.c_size_t, i32, vd]
     L.ctb_binary.argtypes = [i32, vp, vp, vp, vd]
     L.ctb_unary.argtypes = [i32, vp, ctypes.c_double, vp, vd]
     L.ctb_copy_strided.argtypes = [vp, vp, vd]

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libctb200.so")
-SOURCES = ["ctb_abi.cu", "ctb_elementwise.cu", "ctb_reduce.cu", "ctb_rows.cu", "ctb_index.cu", "ctb_optim.cu", "ctb_norm.cu", "ctb_matmul.cu"]
+SOURCES = ["ctb_abi.cu", "ctb_elementwise.cu", "ctb_reduce.cu", "ctb_rows.cu", "ctb_index.cu", "ctb_optim.cu", "ctb_norm.cu", "ctb_matmul.cu", "ctb_pool.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
@@ -69,6 +69,33 @@ def build_host(force: bool = False) -> str:
     return HOST_LIB
 
 
+def reference_root() -> str:
+    """Where the reference's sources are, for the steps that compile them as checkers: the
+    CTENSOR_REFERENCE environment variable, else a checkout named `reference` beside this
+    repository.  Empty when there is none (those steps are then skipped)."""
+    cand = os.environ.get("CTENSOR_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(PKG)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src", "core")) else ""
+
+
+GEN1_DIR = os.path.join(HOST_DIR, "gen1")
+GEN1_LIB = os.path.join(PKG, "libctensor_gen1.so")
+
+
+def build_gen1(force: bool = False) -> str:
+    """The first-generation host layer (tensor1.h / opsmp.h / ops1.h of the reference's root tree
+    over the C ABI): plain g++ like build_host."""
+    src = os.path.join(GEN1_DIR, "ctensor_gen1.cpp")
+    deps = [src, os.path.join(os.path.dirname(PKG), "include", "ctb200.h")]
+    deps += [os.path.join(GEN1_DIR, "include", f) for f in os.listdir(os.path.join(GEN1_DIR, "include"))]
+    if not force and os.path.exists(GEN1_LIB) and os.path.getmtime(GEN1_LIB) >= max(map(os.path.getmtime, deps)) \
+            and os.path.getmtime(GEN1_LIB) >= os.path.getmtime(LIB):
+        return GEN1_LIB
+    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-o", GEN1_LIB, src,
+                           "-I", GEN1_DIR, "-L", PKG, "-lctb200", "-Wl,-rpath,$ORIGIN"])
+    return GEN1_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
     print(build_host(force="--force" in sys.argv))
+    print(build_gen1(force="--force" in sys.argv))

@@ -18,6 +18,7 @@ int g_device = 0;
 // The CUDA device is a per-thread setting: every host thread selects g_device before its first
 // operator (a process-wide flag would leave a second thread on device 0).
 thread_local int t_device_selected = -1;
+thread_local std::vector<size_t> t_last_permutation;
 bool g_sync_after_op = true;
 ctb_host::GradFactory g_grad_factory;
 std::function<void(Tensor&)> g_backward;
@@ -33,11 +34,42 @@ std::function<void(Tensor&)> g_backward;
 inline void check(int status) { if (status != CTB_OK) raise(status); }
 
 void ensure_device() {
-    if (t_device_selected == g_device) return;
+    if (t_device_selected >= 0) return;
     if (ctb_device_count() <= 0)
         throw std::runtime_error("ctensor_b200: no CUDA device (this library has no CPU fallback)");
     check(ctb_set_device(g_device));
     t_device_selected = g_device;
+}
+
+// The GPU an operator on `t` runs on: the index of its Device(CUDA, i) tag
+// (src/core/device.h:5-25 of the reference); tensors tagged CPU or without an index live in
+// managed memory as well and use the default device.
+int device_index_of(const Device& d) { return (d.is_cuda() && d.index >= 0) ? d.index : g_device; }
+
+void use_device(int index) {
+    if (t_device_selected == index) return;
+    const int count = ctb_device_count();
+    if (count <= 0) throw std::runtime_error("ctensor_b200: no CUDA device (this library has no CPU fallback)");
+    if (index >= count) throw std::runtime_error("ctensor_b200: tensor is tagged with CUDA device " + std::to_string(index) +
+                                                 " but only " + std::to_string(count) + " are visible");
+    check(ctb_set_device(index));
+    t_device_selected = index;
+}
+void use_device_of(const Tensor& t) { use_device(device_index_of(t.device())); }
+
+// Operator results are overwritten by the kernel that produces them: their storage skips the
+// zero-fill that Storage::allocate otherwise promises (the reference's calloc).
+thread_local bool t_alloc_uninitialized = false;
+struct UninitializedScope {
+    bool prev;
+    UninitializedScope() : prev(t_alloc_uninitialized) { t_alloc_uninitialized = true; }
+    ~UninitializedScope() { t_alloc_uninitialized = prev; }
+};
+Tensor new_output(const std::vector<size_t>& shape, DType dt, const Device& dev) {
+    UninitializedScope scope;
+    Tensor out;
+    out.impl = std::make_shared<Tensorimpl>(shape, dt, false, Device(DeviceType::CUDA, device_index_of(dev)));
+    return out;
 }
 
 int dtype_code(DType dt, const char* who) {
@@ -78,7 +110,9 @@ ctb_view view_of_bits(const Tensor& t) {
     return v;
 }
 
-void after_op() { if (g_sync_after_op) check(ctb_device_sync()); }
+// All operators of the host layer are issued on the device's default stream: waiting for that
+// stream is enough (a device-wide wait would also wait for unrelated streams of the process).
+void after_op() { if (g_sync_after_op) check(ctb_sync(nullptr)); }
 
 void attach_grad(Tensor& out, const char* op, const std::vector<Tensor>& inputs, double scalar) {
     bool req = false;
@@ -104,11 +138,11 @@ std::vector<size_t> broadcast_shape(const Tensor& a, const Tensor& b) {
 Tensor binary(int op, const char* name, const Tensor& a, const Tensor& b, bool grad) {
     if (!a.impl || !b.impl) throw std::runtime_error("binary_op: null input");
     if (a.device() != b.device()) throw std::runtime_error(std::string(name) + ": tensors must be on same device");
-    ensure_device();
+    use_device_of(a);
     // two one-element operands give shape {1} whatever their rank (the reference's scalar
     // short-circuit, src/core/ops_dispatch.cpp:177-203)
     std::vector<size_t> shape = (a.numel() == 1 && b.numel() == 1) ? std::vector<size_t>{1} : broadcast_shape(a, b);
-    Tensor out(shape, a._dtype(), false);
+    Tensor out = new_output(shape, a._dtype(), a.device());
     const ctb_view va = view_of(a, name), vb = view_of(b, name), vo = view_of(out, name);
     check(ctb_binary(op, &va, &vb, &vo, nullptr));
     after_op();
@@ -118,8 +152,8 @@ Tensor binary(int op, const char* name, const Tensor& a, const Tensor& b, bool g
 
 Tensor unary(int op, const char* name, const Tensor& a, double scalar, bool grad) {
     if (!a.impl) throw std::runtime_error("unary_op: null input");
-    ensure_device();
-    Tensor out(a.shape(), a._dtype(), false);
+    use_device_of(a);
+    Tensor out = new_output(a.shape(), a._dtype(), a.device());
     const ctb_view va = view_of(a, name), vo = view_of(out, name);
     check(ctb_unary(op, &va, scalar, &vo, nullptr));
     after_op();
@@ -129,7 +163,7 @@ Tensor unary(int op, const char* name, const Tensor& a, double scalar, bool grad
 
 Tensor reduce(int op, const char* name, const Tensor& a, int dim, bool grad) {
     if (!a.impl) throw std::runtime_error("reduction: null input");
-    ensure_device();
+    use_device_of(a);
     const int nd = (int)a.impl->ndim;
     if (dim < -1) {                 // -1 is "everything"; other negative dims wrap (src/core/opsmp.cpp:598)
         dim += nd;
@@ -139,7 +173,7 @@ Tensor reduce(int op, const char* name, const Tensor& a, int dim, bool grad) {
     if (dim >= 0 && dim < nd)
         for (int d = 0; d < nd; ++d) if (d != dim) shape.push_back(a.impl->shape[d]);
     if (shape.empty()) shape.push_back(1);
-    Tensor out(shape, op == CTB_ARGMAX ? DType::Int32 : a._dtype(), false);
+    Tensor out = new_output(shape, op == CTB_ARGMAX ? DType::Int32 : a._dtype(), a.device());
     const ctb_view va = view_of(a, name), vo = view_of(out, name);
     check(ctb_reduce(op, &va, dim, &vo, nullptr));
     after_op();
@@ -160,11 +194,13 @@ void set_device(int index) {
 int device() { return g_device; }
 void set_sync_after_op(bool on) { g_sync_after_op = on; }
 void sync_for_host_access() { if (t_device_selected >= 0) check(ctb_device_sync()); }
+void trim_storage_pool() { check(ctb_pool_trim(-1)); }
+const std::vector<size_t>& last_permutation() { return t_last_permutation; }
 void set_grad_factory(GradFactory f) { g_grad_factory = std::move(f); }
 void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src) {
     if (!grad_buffer.impl) return;                      // as the reference: nothing to add to
     if (!grad_src.impl) throw std::runtime_error("accumulate_grad: null gradient");
-    ensure_device();
+    use_device_of(grad_buffer);
     const ctb_view vg = view_of(grad_buffer, "accumulate_grad"), vs = view_of(grad_src, "accumulate_grad");
     check(ctb_accumulate_grad(&vg, &vs, nullptr));
     after_op();
@@ -178,14 +214,19 @@ int last_dim_if_negative(const Tensor& t, int dim) {
 }  // namespace ctb_host
 
 // ---- storage: replaces Storage::allocate (src/core/tensor.cpp:18-39) --------------------------------
+// Managed memory from the library's size-bucketed pool (the reference's unfinished
+// CudaMemoryPool, src/core/tensor.h:253-289), resident on the GPU the Device tag names.
+// Zero-filled like the reference's calloc, except for operator results (new_output).
 std::shared_ptr<Storage> Storage::allocate(size_t n, DType dt, bool /*requires_grad*/, Device dev) {
     ensure_device();
+    const int index = device_index_of(dev);
     auto s = std::make_shared<Storage>();
     s->size = n;
-    s->device = dev;
+    s->device = Device(DeviceType::CUDA, index);
     void* p = nullptr;
-    check(ctb_alloc_managed(&p, n * dtype_size(dt), /*zero=*/1));   // zero-filled like calloc
-    s->data = std::shared_ptr<void>(p, [](void* q) { ctb_free_managed(q); });
+    if (index != t_device_selected) use_device(index);     // the clearing memset runs on that device's stream
+    check(ctb_pool_alloc_managed(&p, n * dtype_size(dt), t_alloc_uninitialized ? 0 : 1, index, nullptr));
+    s->data = std::shared_ptr<void>(p, [](void* q) { ctb_pool_free_managed(q); });
     return s;
 }
 
@@ -195,10 +236,28 @@ Tensor::Tensor(const std::vector<size_t>& shape_, DType dtype_, bool requires_gr
 
 Device Tensor::device() const { return impl ? impl->data->device : Device(DeviceType::CPU); }
 
+// A copy whose storage lives on `target` (src/core/tensor.h: Tensor::to).  The copy kernel runs
+// on the target GPU and reads the source through managed memory.
 Tensor Tensor::to(Device target) {
     if (!impl || device() == target) return *this;
-    Tensor out = clone();                      // storage is managed memory: reachable from both sides
-    out.impl->data->device = target;
+    if (target.is_cuda() && target.index >= ctb_device_count())
+        throw std::runtime_error("Tensor::to: no such CUDA device");
+    ctb_host::sync_for_host_access();          // work queued on the source's device is done
+    const int index = device_index_of(target);
+    use_device(index);
+    Tensor out = new_output(shape(), impl->dtype, Device(DeviceType::CUDA, index));
+    out.impl->requires_grad = impl->requires_grad;
+    const size_t es = dtype_size(impl->dtype);
+    if (es == 4 || es == 8) {
+        ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
+        check(ctb_copy_strided(&vs, &vo, nullptr));
+        check(ctb_sync(nullptr));
+    } else {
+        Tensor packed = contiguous();
+        ctb_host::sync_for_host_access();
+        std::memcpy(out.impl->data->data.get(), (const char*)packed.impl->data->data.get() + packed.impl->offset * es, numel() * es);
+    }
+    out.impl->data->device = target;            // keeps a CPU tag if that is what was asked for
     return out;
 }
 
@@ -216,7 +275,9 @@ bool Tensor::is_contiguous() const {
 
 Tensor Tensor::clone() const {
     if (!impl) return Tensor();
-    Tensor out(shape(), impl->dtype, impl->requires_grad);
+    use_device_of(*this);
+    Tensor out = new_output(shape(), impl->dtype, device());
+    out.impl->requires_grad = impl->requires_grad;
     const size_t es = dtype_size(impl->dtype);
     if (es == 4 || es == 8) {                   // strided gather on the GPU, bit copy
         ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
@@ -269,7 +330,10 @@ Tensor Tensor::permute(const std::vector<size_t>& dims) const {
     }
     Tensor out;
     out.impl = std::make_shared<Tensorimpl>(impl->data, impl->offset, shape, strides, impl->dtype, impl->requires_grad);
-    if (impl->requires_grad && g_grad_factory) out.impl->grad_fn = g_grad_factory("permute", {*this}, 0.0);
+    if (impl->requires_grad && g_grad_factory) {
+        t_last_permutation = dims;
+        out.impl->grad_fn = g_grad_factory("permute", {*this}, 0.0);
+    }
     return out;
 }
 
@@ -300,22 +364,25 @@ Tensor Tensor::gather(const Tensor& index, size_t dim) const {
     if (!impl) throw std::runtime_error("Gather on empty tensor");
     if (!index.impl) throw std::runtime_error("Gather with empty index");
     if (dim >= impl->ndim) throw std::out_of_range("Gather dimension out of range");
-    ensure_device();
-    Tensor out(index.shape(), impl->dtype, impl->requires_grad);
+    use_device_of(*this);
+    Tensor out = new_output(index.shape(), impl->dtype, device());
+    out.impl->requires_grad = impl->requires_grad;
     if (out.numel() == 0) return out;
     const ctb_view vx = view_of(*this, "gather"), vi = view_of(index, "gather"), vo = view_of(out, "gather");
-    // the kernel cannot throw: it raises a flag in managed memory that is read after the sync
-    void* flag_mem = nullptr;
-    check(ctb_alloc_managed(&flag_mem, sizeof(int32_t), 1));
-    const int rc = ctb_gather(&vx, (int)dim, &vi, &vo, (int32_t*)flag_mem, nullptr);
-    int32_t bad = 0;
-    if (rc == CTB_OK) {
-        ctb_host::sync_for_host_access();
-        bad = *(volatile int32_t*)flag_mem;
+    // the kernel cannot throw: it raises a flag in managed memory that is read after the wait
+    // (one flag per device, allocated on first use and kept)
+    static std::mutex flag_mu;
+    static int32_t* flags[64] = {};
+    int32_t* flag = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(flag_mu);
+        int32_t*& slot = flags[t_device_selected & 63];
+        if (!slot) check(ctb_alloc_managed((void**)&slot, sizeof(int32_t), 1));
+        flag = slot;
     }
-    ctb_free_managed(flag_mem);
-    check(rc);
-    if (bad) throw std::out_of_range("Gather index out of bounds");
+    check(ctb_gather(&vx, (int)dim, &vi, &vo, flag, nullptr));
+    check(ctb_sync(nullptr));
+    if (*(volatile int32_t*)flag) throw std::out_of_range("Gather index out of bounds");
     if (impl->requires_grad) attach_grad(out, "gather", {*this, index}, (double)dim);
     return out;
 }
@@ -456,7 +523,19 @@ Tensor relu(const Tensor& a) { return unary(CTB_RELU, "relu", a, 0.0, true); }
 Tensor gelu(const Tensor& a) { return unary(CTB_GELU_TANH, "gelu", a, 0.0, true); }
 
 Tensor sum(const Tensor& a, int dim) { return reduce(CTB_SUM, "sum", a, dim, true); }
-Tensor mean(const Tensor& a, int dim) { return reduce(CTB_MEAN, "mean", a, dim, true); }
+// mean = mul_scalar(sum, 1/N) in the reference (src/core/ops_dispatch.cpp:385-390).  The fused
+// kernel gives the same bits in one pass; when a gradient is wanted the two operators are
+// issued as the reference issues them, so the graph has the reference's two nodes.
+Tensor mean(const Tensor& a, int dim) {
+    if (a.impl && a.impl->requires_grad) {
+        Tensor s = sum(a, dim);
+        const int nd = (int)a.impl->ndim;
+        const int d = dim < -1 ? dim + nd : dim;
+        const double n = (d >= 0 && d < nd) ? (double)a.impl->shape[d] : (double)a.numel();
+        return mul_scalar(s, 1.0 / n);
+    }
+    return reduce(CTB_MEAN, "mean", a, dim, false);
+}
 Tensor max(const Tensor& a, int dim) { return reduce(CTB_MAX, "max", a, dim, false); }
 Tensor min(const Tensor& a, int dim) { return reduce(CTB_MIN, "min", a, dim, false); }
 Tensor var(const Tensor& a, int dim) { return reduce(CTB_VAR, "var", a, dim, false); }
@@ -469,8 +548,8 @@ Tensor argmax(const Tensor& a, int dim) {
 
 static Tensor softmax_impl(const Tensor& a, const Tensor* mask, int causal) {
     if (!a.impl) throw std::runtime_error("softmax: null input");
-    ensure_device();
-    Tensor out(a.shape(), a._dtype(), false);
+    use_device_of(a);
+    Tensor out = new_output(a.shape(), a._dtype(), a.device());
     const ctb_view va = view_of(a, "softmax"), vo = view_of(out, "softmax");
     ctb_view vm;
     if (mask) vm = view_of(*mask, "softmax");
@@ -490,11 +569,12 @@ Tensor matmul(const Tensor& a, const Tensor& b) {
     if (!a.impl || !b.impl) throw std::runtime_error("matmul: null input");
     if (a.impl->ndim < 2 || b.impl->ndim < 2) throw std::runtime_error("matmul_mp requires at least 2D tensors");
     if (b.impl->shape[b.impl->ndim - 2] != a.impl->shape[a.impl->ndim - 1]) throw std::runtime_error("matmul_mp shape mismatch");
-    ensure_device();
+    use_device_of(a);
     std::vector<size_t> res_shape = a.shape();
     res_shape.back() = b.impl->shape[b.impl->ndim - 1];
     const bool req = a.requires_grad() || b.requires_grad();
-    Tensor out(res_shape, a._dtype(), req);
+    Tensor out = new_output(res_shape, a._dtype(), a.device());
+    out.impl->requires_grad = req;
     const ctb_view va = view_of(a, "matmul"), vb = view_of(b, "matmul"), vo = view_of(out, "matmul");
     check(ctb_matmul(&va, &vb, &vo, nullptr));
     after_op();
@@ -518,8 +598,8 @@ Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
         dim_sum += t.impl->shape[dim];
     }
     out_shape[dim] = dim_sum;
-    ensure_device();
-    Tensor out(out_shape, tensors[0]._dtype(), false);
+    use_device_of(tensors[0]);
+    Tensor out = new_output(out_shape, tensors[0]._dtype(), tensors[0].device());
     std::vector<ctb_view> views;
     std::vector<const ctb_view*> ptrs;
     views.reserve(tensors.size());
@@ -535,10 +615,10 @@ Tensor cat(const std::vector<Tensor>& tensors, size_t dim) {
 void channel_moments(const Tensor& x, Tensor& mean, Tensor& var) {
     if (!x.impl) throw std::runtime_error("batchnorm: null input");
     if (x.impl->ndim < 2) throw std::runtime_error("batchnorm: input needs [batch, channels, ...]");
-    ensure_device();
+    use_device_of(x);
     const Tensor xc = x.is_contiguous() ? x : x.contiguous();
-    mean = Tensor({x.impl->shape[1]}, x._dtype(), false);
-    var = Tensor({x.impl->shape[1]}, x._dtype(), false);
+    mean = new_output({x.impl->shape[1]}, x._dtype(), x.device());
+    var = new_output({x.impl->shape[1]}, x._dtype(), x.device());
     const ctb_view vx = view_of(xc, "batchnorm"), vm = view_of(mean, "batchnorm"), vv = view_of(var, "batchnorm");
     check(ctb_channel_moments(&vx, &vm, &vv, nullptr));
     after_op();
@@ -547,9 +627,9 @@ void channel_moments(const Tensor& x, Tensor& mean, Tensor& var) {
 Tensor batch_norm_apply(const Tensor& x, const Tensor& mean, const Tensor& var, const Tensor& gamma,
                         const Tensor& beta, double eps) {
     if (!x.impl || !mean.impl || !var.impl) throw std::runtime_error("batchnorm: null input");
-    ensure_device();
+    use_device_of(x);
     const Tensor xc = x.is_contiguous() ? x : x.contiguous();
-    Tensor out(x.shape(), x._dtype(), false);
+    Tensor out = new_output(x.shape(), x._dtype(), x.device());
     const ctb_view vx = view_of(xc, "batchnorm"), vm = view_of(mean, "batchnorm"), vv = view_of(var, "batchnorm"),
                    vo = view_of(out, "batchnorm");
     ctb_view vg, vb;
@@ -562,8 +642,8 @@ Tensor batch_norm_apply(const Tensor& x, const Tensor& mean, const Tensor& var, 
 
 Tensor log_softmax(const Tensor& a) {
     if (!a.impl) throw std::runtime_error("log_softmax: null input");
-    ensure_device();
-    Tensor out(a.shape(), a._dtype(), false);
+    use_device_of(a);
+    Tensor out = new_output(a.shape(), a._dtype(), a.device());
     const ctb_view va = view_of(a, "log_softmax"), vo = view_of(out, "log_softmax");
     check(ctb_log_softmax_lastdim(&va, nullptr, &vo, nullptr));
     after_op();
@@ -572,8 +652,8 @@ Tensor log_softmax(const Tensor& a) {
 
 Tensor layer_norm(const Tensor& a, const Tensor& gamma, const Tensor& beta, double eps) {
     if (!a.impl) throw std::runtime_error("layernorm: null input");
-    ensure_device();
-    Tensor out(a.shape(), a._dtype(), false);
+    use_device_of(a);
+    Tensor out = new_output(a.shape(), a._dtype(), a.device());
     const ctb_view va = view_of(a, "layernorm"), vo = view_of(out, "layernorm");
     ctb_view vg, vb;
     if (gamma.impl) vg = view_of(gamma, "layernorm");

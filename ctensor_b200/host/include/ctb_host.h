@@ -20,6 +20,11 @@ int device();
 void set_sync_after_op(bool on);
 void sync_for_host_access();
 
+// Tensor storage comes from a pool of managed blocks (ctb_pool_alloc_managed): freed tensors
+// keep their memory cached for the next tensor of the same size.  This gives the cached blocks
+// back to the driver.
+void trim_storage_pool();
+
 // Autograd hook.  The reference attaches a GradFn node to every result whose inputs require
 // grad (src/core/ops_dispatch.cpp:159-167,247-255,312-315,378-381).  Those node classes belong
 // to the caller's autograd library, so it registers a factory once; `op` is the operator name
@@ -27,6 +32,9 @@ void sync_for_host_access();
 using GradFactory = std::function<std::shared_ptr<GradFn>(const std::string& op, const std::vector<Tensor>& inputs,
                                                           double scalar)>;
 void set_grad_factory(GradFactory f);
+// For op == "permute" the factory also needs the permutation: the one of the Tensor::permute call
+// that is asking for the node (valid during that factory call, per host thread).
+const std::vector<size_t>& last_permutation();
 
 // accumulate_grad of the reference's autograd (src/core/autograd.cpp:63-156) on the GPU:
 // `grad_buffer` (the tensor that wraps target.impl->grad) += grad_src, with the broadcast dims of

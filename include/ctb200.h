@@ -124,6 +124,33 @@ int ctb_sync(void* stream);
  * src/core/tensor.h:274).  Synchronous; `zero` != 0 clears the buffer. */
 int ctb_alloc_managed(void** ptr, size_t bytes, int zero);
 int ctb_free_managed(void* ptr);
+/* The pooled form of the above: what Storage::allocate should call for every operator result.
+ * The reference sketches it (a size-bucketed pool of managed blocks rounded to 512 bytes,
+ * src/core/tensor.h:253-289, behind Storage::allocate, src/core/tensor.cpp:18-39) but never
+ * finishes it.  ctb_pool_alloc_managed returns a block of at least `bytes` bytes of managed
+ * memory whose preferred location is `device`: a cached block of the same rounded size when one
+ * is free (no driver call, pages already resident in HBM), a new cudaMallocManaged block
+ * otherwise.  `zero` != 0 clears it on `stream` (only Tensor::zeros / fresh tensors promise
+ * zeros; operator outputs are overwritten anyway and skip the extra pass).
+ * ctb_pool_free_managed returns a block to its device's free list; it never waits for the
+ * device, so the caller's next use of the memory must be ordered after the last kernel that
+ * touched it (one stream per device gives that).  ctb_pool_trim frees the cached blocks of one
+ * device (-1: all); ctb_pool_set_limit bounds the idle bytes a device keeps (default 64 GiB). */
+typedef struct ctb_pool_info {
+    size_t   live_bytes;      /* handed out and not yet returned            */
+    size_t   cached_bytes;    /* idle in the free lists                     */
+    size_t   cached_blocks;
+    uint64_t hits, misses;    /* allocations served from / past the cache   */
+    uint64_t trims;           /* cached blocks given back to the driver     */
+} ctb_pool_info;
+int ctb_pool_alloc_managed(void** ptr, size_t bytes, int zero, int device, void* stream);
+int ctb_pool_free_managed(void* ptr);
+int ctb_pool_trim(int device);
+int ctb_pool_set_limit(int device, size_t cached_bytes);
+int ctb_pool_stats(int device, ctb_pool_info* info);
+/* Ask for the pages of a managed range to be moved to `device` ahead of the first kernel
+ * (advisory; a no-op where the platform cannot prefetch managed memory). */
+int ctb_prefetch_managed(void* ptr, size_t bytes, int device, void* stream);
 /* Select the CUDA device of the calling host thread / wait for all work on it. */
 int ctb_set_device(int index);
 int ctb_device_sync(void);

@@ -1,0 +1,64 @@
+#!/usr/bin/env bash
+# TEST INFRASTRUCTURE — builds tests/cpp/callers_program.cpp against the REFERENCE ITSELF, both
+# generations, as the CPU twins the GPU builds of the same program are compared with.
+#
+#   oracle/build_callers_ref.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
+#
+# Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref.
+#   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
+#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp
+#   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp
+# All sources are compiled where they lie (the second generation through the patched symlink
+# farm of ref_farm.sh); nothing is copied into the repository.
+set -euo pipefail
+REF="${1:-${CTENSOR_REFERENCE:-}}"
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+OUT="$HERE/_ref"
+PROGRAM="$HERE/../tests/cpp/callers_program.cpp"
+[ -n "$REF" ] || { echo "usage: build_callers_ref.sh REFERENCE_ROOT (or set CTENSOR_REFERENCE)" >&2; exit 2; }
+[ -d "$REF/src/core" ] || { echo "build_callers_ref: no reference at $REF" >&2; exit 3; }
+mkdir -p "$OUT"
+TMP="$(mktemp -d /tmp/ctcallers.XXXXXX)"
+trap 'rm -rf "$TMP"' EXIT
+. "$HERE/ref_farm.sh"
+make_ref_farm "$REF" "$TMP"
+CXX="${REF_CXX:-g++}"
+STD="-std=gnu++20 -w"
+mkdir -p "$TMP/obj2" "$TMP/obj1" "$TMP/src/neuralnet"
+for f in layer.cpp layer.h loss.cpp loss.h module.h; do ln -s "$REF/src/neuralnet/$f" "$TMP/src/neuralnet/$f"; done
+
+# ---- second generation ------------------------------------------------------------------------
+S="$TMP/src"
+INC2="-I$S -I$S/core -I$S/cpu/AVX2 -I$S/cpu/AVX512 -I$S/neuralnet"
+pids=()
+cc2() { $CXX $STD $2 $INC2 -c "$3" -o "$TMP/obj2/$1.o" & pids+=($!); }
+cc2 tensor       "-O2 -fopenmp"                 "$S/core/tensor.cpp"
+cc2 opsmp        "-O2 -fopenmp"                 "$S/core/opsmp.cpp"
+cc2 ops_dispatch "-O2 -fopenmp"                 "$S/core/ops_dispatch.cpp"
+cc2 autograd     "-O2 -fopenmp"                 "$S/core/autograd.cpp"
+cc2 avx2_f32     "-O3 -mavx2 -mfma -fopenmp"    "$S/cpu/AVX2/ops_avx2_f32.cpp"
+cc2 avx2_d64     "-O3 -mavx2 -mfma -fopenmp"    "$S/cpu/AVX2/ops_avx2_d64.cpp"
+cc2 avx512_f32   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_f32.cpp"
+cc2 avx512_d64   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_d64.cpp"
+cc2 layer        "-O2 -fopenmp"                 "$S/neuralnet/layer.cpp"
+cc2 loss         "-O2 -fopenmp"                 "$S/neuralnet/loss.cpp"
+cc2 program      "-O1"                          "$PROGRAM"
+for p in "${pids[@]}"; do wait "$p"; done
+$CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
+# The same program with the dispatcher's CPU feature probes answering "no" (a command-line macro
+# over __builtin_cpu_supports; the source is untouched): what the reference does on a host
+# without AVX2 / AVX-512, its scalar+OpenMP back-end everywhere.  On an AVX host the SIMD entries
+# throw for dim-wise reductions ("sum_avx512: only dim=-1", also inside accumulate_grad) and
+# multiply permuted matrices as if they were contiguous, so Linear and most backward passes
+# cannot run there; the scalar back-end honours strides and dims.
+$CXX $STD -O2 -fopenmp '-D__builtin_cpu_supports(x)=0' $INC2 -c "$S/core/ops_dispatch.cpp" -o "$TMP/obj2/ops_dispatch.o"
+$CXX -o "$OUT/callers_gen2_ref_scalar" "$TMP"/obj2/*.o -fopenmp
+
+# ---- first generation (root of the reference tree) -----------------------------------------------
+pids=()
+cc1() { $CXX $STD -O2 -fopenmp -DCTB_GEN1 -I"$REF" -c "$2" -o "$TMP/obj1/$1.o" & pids+=($!); }
+for f in tensor1 opsmp autograd layer loss data; do cc1 "$f" "$REF/$f.cpp"; done
+cc1 program "$PROGRAM"
+for p in "${pids[@]}"; do wait "$p"; done
+$CXX -o "$OUT/callers_gen1_ref" "$TMP"/obj1/*.o -fopenmp
+echo "built $OUT/callers_gen2_ref $OUT/callers_gen1_ref"

@@ -1,7 +1,7 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE — builds the real reference (CTensor src tree) as a shared library.
 #
-#   oracle/build_ref.sh [REFERENCE_ROOT]      (REFERENCE_ROOT: the reference checkout; default below)
+#   oracle/build_ref.sh REFERENCE_ROOT      (the reference checkout; or set CTENSOR_REFERENCE)
 #
 # Output: oracle/_ref/libctensor_ref.so  (+ oracle/_ref/BUILD_INFO.txt).  Nothing else is
 # written; no reference source is copied into the repository.
@@ -21,41 +21,22 @@
 # neither -O nor -fopenmp), which changes speed but not results (its arithmetic is plain
 # double-precision + - * / and libm calls).
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${CTENSOR_REFERENCE:-}}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
+[ -n "$REF" ] || { echo "usage: build_ref.sh REFERENCE_ROOT (or set CTENSOR_REFERENCE)" >&2; exit 2; }
 [ -d "$REF/src/core" ] || { echo "build_ref: no reference at $REF" >&2; exit 3; }
 mkdir -p "$OUT"
 TMP="$(mktemp -d /tmp/ctref.XXXXXX)"
 trap 'rm -rf "$TMP"' EXIT
-for d in core cpu/AVX2 cpu/AVX512; do
-  mkdir -p "$TMP/src/$d"
-  for f in "$REF/src/$d"/*.h "$REF/src/$d"/*.cpp; do
-    case "$(basename "$f")" in tensor.h|tensor.cpp) [ "$d" = core ] && continue ;; esac
-    ln -s "$f" "$TMP/src/$d/$(basename "$f")"
-  done
-done
-
-# spot 1: drop the CUDA pool block (from the "//Memory pool" marker up to the line before
-# "// STORAGE & INTERNAL IMPLEMENTATION")
-awk '
-  /^\/\/Memory pool/ {skip=1}
-  /^\/\/ STORAGE & INTERNAL IMPLEMENTATION/ {skip=0}
-  !skip {print}
-' "$REF/src/core/tensor.h" > "$TMP/src/core/tensor.h"
-# spot 2: drop "#include <cuda>" and the CUDA branch of Storage::allocate
-awk '
-  /^#include <cuda>/ {next}
-  /else if\(dev\.type == DeviceType::CUDA\)/ {print "    }"; skip=1; next}
-  skip && /^    }$/ {skip=0; next}
-  !skip {print}
-' "$REF/src/core/tensor.cpp" > "$TMP/src/core/tensor.cpp"
+. "$HERE/ref_farm.sh"
+make_ref_farm "$REF" "$TMP"
 
 S="$TMP/src"
 # the reference tree itself comes last: it only supplies header-only callers (the optimizers of
 # src/neuralnet/train_utils.h); "core/tensor.h" still resolves to the patched copy above
 INC="-I$S -I$S/core -I$S/cpu/AVX2 -I$S/cpu/AVX512 -I$REF/src"
-CXX="${REF_CXX:-g++}"   # the PATH g++ (13.3 in this image), not $CXX
+CXX="${REF_CXX:-g++}"   # the g++ on PATH, not $CXX
 STD="-std=gnu++20 -fPIC -w"
 CORE_FLAGS="-O2 -fopenmp"
 AVX2_FLAGS="-O3 -mavx2 -mfma -fopenmp"       # CMakeLists.txt:63

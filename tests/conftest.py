@@ -16,6 +16,7 @@ def pytest_configure(config):
     from ctensor_b200 import build as b
     b.build()
     b.build_host()
+    b.build_gen1()
 
 
 @pytest.fixture(scope="session")

@@ -1,0 +1,189 @@
+// One program, four builds: the reference's own callers of the operator path — autograd.cpp,
+// layer.cpp, loss.cpp, unchanged — driven through a Linear layer, two losses and a chain of
+// elementwise operators, forward and backward.
+//
+//   build                      tensor/operator layer                     callers
+//   callers_gen2_ref           the reference's src/core (CPU)            the reference's, unchanged
+//   callers_gen2_ref_scalar    the same, feature probes answering "no"   the reference's, unchanged
+//   callers_gen2_b200          ctensor_b200/host (GPU)                   the reference's, unchanged
+//   callers_gen1_ref           the reference's tensor1/opsmp (CPU)       the reference's, unchanged
+//   callers_gen1_b200          ctensor_b200/host/gen1 (GPU)              the reference's, unchanged
+//
+// It prints one "name count v0 v1 ..." line per result (loss values and every gradient).  The
+// tests compare the lines of a *_b200 build with those of the *_ref build.  A section that
+// throws prints "name unavailable <reason>".
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <exception>
+#include <string>
+#include <vector>
+
+#ifdef CTB_GEN1
+#include "tensor1.h"
+#include "opsmp.h"
+#include "autograd.h"
+#include "layer.h"
+#include "loss.h"
+#define DATA(t) ((t).impl->storage->data.get())
+#define GRAD(t) ((t).impl->storage->grad.get())
+#define F_EXP exp_mp
+#define F_LN ln_mp
+#define F_TANH tanh_mp
+#define F_RELU Relu_mp
+#define F_MEAN_ROWS(t) mean_mp((t), 1)
+// every dim folded in turn (flatten() would cut the graph: it attaches no backward node here)
+static Tensor sum_all(Tensor t) {
+    while (t.impl->ndim > 1) t = sum_mp(t, (int)t.impl->ndim - 1);
+    return sum_mp(t, 0);
+}
+#define F_SUM_ALL(t) sum_all(t)
+#else
+#include "core/tensor.h"
+#include "core/ops_dispatch.h"
+#include "core/autograd.h"
+#include "neuralnet/layer.h"
+#include "neuralnet/loss.h"
+#define DATA(t) ((t).impl->data->data.get())
+#define GRAD(t) ((t).impl->grad ? (t).impl->grad->data->data.get() : nullptr)
+#define F_EXP exp
+#define F_LN ln
+#define F_TANH tanh
+#define F_RELU relu
+#define F_MEAN_ROWS(t) mean((t), 1)
+// Everything summed as reshape-to-1-d + sum over dim 0: sum(t, -1) means "everything" on the
+// reference's SIMD back-ends and "the last dim" on its scalar one (src/core/opsmp.cpp:598), and a
+// dim-wise sum of a 2-d tensor cannot sit in a graph here — GradSum::backward
+// (src/core/autograd.cpp:369-373) hands the reduced gradient to accumulate_grad without
+// re-inserting the folded dim, which then reads past its end.
+#define F_SUM_ALL(t) sum((t).reshape({(t).numel()}), 0)
+#define CTB_NO_DIMWISE_SUM_BACKWARD 1
+#endif
+
+namespace {
+
+// a small deterministic generator (the same numbers in every build)
+struct Lcg {
+    uint64_t s;
+    explicit Lcg(uint64_t seed) : s(seed * 6364136223846793005ull + 1442695040888963407ull) {}
+    double next() {       // uniform in (-1, 1)
+        s = s * 6364136223846793005ull + 1442695040888963407ull;
+        return ((double)((s >> 11) & ((1ull << 53) - 1)) / (double)(1ull << 52)) - 1.0;
+    }
+};
+
+Tensor filled(const std::vector<size_t>& shape, uint64_t seed, double scale, bool requires_grad, double shift = 0.0) {
+    Tensor t(shape, DType::Float32, requires_grad);
+    Lcg g(seed);
+    const size_t n = t.numel();
+    for (size_t i = 0; i < n; ++i) write_scalar_at(DATA(t), i, DType::Float32, g.next() * scale + shift);
+    return t;
+}
+
+void print_values(const char* name, const void* p, size_t n) {
+    std::printf("%s %zu", name, n);
+    for (size_t i = 0; i < n; ++i) std::printf(" %.9g", read_scalar_at(p, i, DType::Float32));
+    std::printf("\n");
+}
+void print_data(const char* name, const Tensor& t) { print_values(name, DATA(t), t.numel()); }
+void print_grad(const char* name, const Tensor& t) {
+    const void* g = GRAD(t);
+    if (!g) { std::printf("%s unavailable no gradient buffer\n", name); return; }
+    print_values(name, g, t.numel());
+}
+
+template <typename F> void section(const char* name, F body) {
+    try {
+        body();
+    } catch (const std::exception& e) {
+        std::printf("%s unavailable %s\n", name, e.what());
+    }
+}
+
+}  // namespace
+
+int main() {
+    std::setvbuf(stdout, nullptr, _IOLBF, 1 << 16);      // a crash inside a caller loses no finished line
+    const size_t batch = 12, in_f = 16, out_f = 10;
+
+    // Linear -> MSE (layer.cpp: matmul + broadcast add; loss.cpp: sub, pow_scalar, full sum).
+    // The backward pass runs through the same loss spelled with operators: the reference's own
+    // GradMSE::backward writes numel(pred) values into the one-element gradient of the loss
+    // (loss.cpp, GradMSE::backward) and cannot be run for more than one element.
+    section("mse", [&] {
+        Linear lin((int)in_f, (int)out_f, true, DType::Float32);
+        lin.weight = filled({out_f, in_f}, 1, 0.5, true);
+        lin.bias = filled({out_f}, 2, 0.1, true);
+        Tensor x = filled({batch, in_f}, 3, 1.0, true);
+        Tensor target = filled({batch, out_f}, 4, 1.0, false);
+        Tensor y = lin.forward(x);
+        print_data("mse.forward", y);
+        print_data("mse.loss", Loss::MSE(y, target));
+        Tensor d = y - target;
+        Tensor loss = F_SUM_ALL(d * d) * (1.0 / (double)(batch * out_f));
+        print_data("mse.loss_from_operators", loss);
+        loss.backward();
+        print_grad("mse.grad_weight", lin.weight);
+        print_grad("mse.grad_bias", lin.bias);
+        print_grad("mse.grad_input", x);
+    });
+
+    // Linear -> CrossEntropy -> backward (loss.cpp: row max, sub, exp, row sum, ln, gather, mean)
+    section("ce", [&] {
+        Linear lin((int)in_f, (int)out_f, true, DType::Float32);
+        lin.weight = filled({out_f, in_f}, 5, 0.5, true);
+        lin.bias = filled({out_f}, 6, 0.1, true);
+        Tensor x = filled({batch, in_f}, 7, 1.0, true);
+        Tensor labels({batch, 1}, DType::Int32, false);
+        for (size_t i = 0; i < batch; ++i) write_scalar_at(DATA(labels), i, DType::Int32, (double)((i * 7 + 3) % out_f));
+        Tensor logits = lin.forward(x);
+        Tensor loss = Loss::CrossEntropy(logits, labels, "mean");
+        print_data("ce.loss", loss);
+        loss.backward();
+        print_grad("ce.grad_weight", lin.weight);
+        print_grad("ce.grad_bias", lin.bias);
+        print_grad("ce.grad_input", x);
+    });
+
+    // elementwise chain with broadcasting, through the autograd nodes of add/sub/mul/div,
+    // scalar ops, exp/ln/tanh/relu and a full sum: accumulate_grad folds the broadcast dims
+    section("chain", [&] {
+        Tensor a = filled({6, 8}, 8, 1.0, true);
+        Tensor b = filled({1, 8}, 9, 0.5, true, 1.5);          // in (1, 2): safe divisor, ln argument
+        Tensor c = filled({6, 1}, 10, 1.0, true);
+        Tensor u = (a * b + c) / b - a * 0.25;
+        Tensor v = F_TANH(u) + F_RELU(a) * F_EXP(c * 0.5) - F_LN(b);
+        Tensor total = F_SUM_ALL(v);
+        print_data("chain.value", total);
+        total.backward();
+        print_grad("chain.grad_a", a);
+        print_grad("chain.grad_b", b);
+        print_grad("chain.grad_c", c);
+    });
+
+    // the same kind of chain on same-shape operands (no broadcast folds, no ln): the part the
+    // reference's SIMD back-ends can run as well
+    section("plain", [&] {
+        Tensor a = filled({6, 8}, 12, 1.0, true);
+        Tensor b = filled({6, 8}, 13, 0.5, true, 1.5);
+        Tensor w = F_TANH(a * b + a / b) * F_RELU(a) + F_EXP(b * 0.5) - a * 0.125;
+        Tensor total = F_SUM_ALL(w);
+        print_data("plain.value", total);
+        total.backward();
+        print_grad("plain.grad_a", a);
+        print_grad("plain.grad_b", b);
+    });
+
+    // dim-wise mean through the graph (sum + mul_scalar nodes), then a full sum
+    section("rowmean", [&] {
+        Tensor a = filled({5, 7}, 11, 2.0, true);
+        Tensor m = F_MEAN_ROWS(a * a);
+        Tensor total = F_SUM_ALL(m);
+        print_data("rowmean.value", total);
+#ifndef CTB_NO_DIMWISE_SUM_BACKWARD
+        total.backward();
+        print_grad("rowmean.grad_a", a);
+#endif
+    });
+    return 0;
+}

@@ -10,8 +10,6 @@
 #include "ctb_host.h"
 #include "ops_dispatch.h"
 #include "opsmp.h"
-#include "ops1.h"
-#include "tensor1.h"
 
 static int g_checks = 0;
 #define CHECK(cond)                                                                  \
@@ -104,11 +102,11 @@ int main() {
     CHECK_NEAR((x > 0.25)[2], 1.0, 0.0);
     CHECK((x > 0.25)._dtype() == DType::Float32);        // comparisons answer in the input dtype
 
-    // legacy names (ops1.h / opsmp.h of the reference's root tree)
-    CHECK_NEAR(add_(a, b)[0][0], 5.0, 1e-6);
+    // the *_mp names of src/core/opsmp.h
+    CHECK_NEAR(add_mp(a, b)[0][0], 5.0, 1e-6);
     CHECK_NEAR(diff_mp(b, a)[0][0], 1.0, 1e-6);
-    CHECK_NEAR(mult_(a, b)[1][1], 6.0, 1e-6);
-    CHECK_NEAR(Relu_(x)[0], 0.0, 0.0);
+    CHECK_NEAR(mult_mp(a, b)[1][1], 6.0, 1e-6);
+    CHECK_NEAR(Relu_mp(x)[0], 0.0, 0.0);
     CHECK_NEAR(exp_mp(x)[1], 1.0, 0.0);
     CHECK_NEAR(mult_scalar_mp(a, 1.5)[0][0], 3.0, 1e-6);
 
@@ -168,7 +166,7 @@ int main() {
     CHECK_NEAR(my[1][0], 20.0, 0.0);
     CHECK_NEAR(my[1][1], 31.0, 0.0);
     CHECK_THROWS(matmul(mx, mx), std::runtime_error, "matmul_mp shape mismatch");
-    CHECK_NEAR(matmul_(mx, mw)[1][1], 11.0, 0.0);
+    CHECK_NEAR(matmul_mp(mx, mw)[1][1], 11.0, 0.0);
 
     // BatchNorm forward pieces: x[N=2, C=2, S=2]
     Tensor bx = Tensor::from_vector({1, 3, 10, 30, 5, 7, 50, 70}, {2, 2, 2});

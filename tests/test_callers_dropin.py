@@ -1,0 +1,154 @@
+"""The drop-in claim, tested: the reference's own callers of the operator path — autograd.cpp,
+layer.cpp, loss.cpp of both generations, UNCHANGED — compile and link against the B200 host
+layers (CPU test, where the reference sources exist), and the program they form
+(tests/cpp/callers_program.cpp: Linear -> losses -> backward, broadcast chains) gives on the GPU
+what the same program gives when it is linked against the reference itself (GPU test; golden lines
+in tests/golden/callers_*_ref.txt, made by tests/golden/make_callers_golden.py).
+
+Which reference build a line is compared with:
+  first generation   every line against callers_gen1_ref (the reference's root tree).
+  second generation  against callers_gen2_ref_scalar: the reference with its CPU feature probes
+                     answering "no", i.e. its scalar+OpenMP back-end, the only one that honours
+                     strides and dim-wise reductions.  As shipped on an AVX-512 host
+                     (callers_gen2_ref) the dispatcher multiplies the permuted weight matrix as if
+                     it were contiguous and throws "sum_avx512: only dim=-1" inside every backward
+                     pass that folds a broadcast dim.  Two lines depend on what dim = -1 means
+                     (everything on the SIMD back-ends and in the API documentation, the last dim
+                     on the scalar back-end): the loss values of Loss::MSE and Loss::CrossEntropy;
+                     they are checked against their definition, computed here with numpy.
+Tolerance 1e-5 relative (the operator path's fp32 tolerance; exp/ln/tanh are the reference's SIMD
+polynomial flavours on the GPU and libm on its scalar back-end, a difference of ~1e-7)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BUILT = os.path.join(ROOT, "tests", "cpp", "_built")
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+from ctensor_b200.build import reference_root      # noqa: E402
+
+REFERENCE = reference_root()
+RTOL, ATOL = 1e-5, 2e-7
+
+
+def parse(text):
+    """-> dict name -> np.ndarray | str (the reason of an 'unavailable' line)"""
+    out = {}
+    for line in text.splitlines():
+        w = line.split()
+        if len(w) >= 2 and w[1] == "unavailable":
+            out[w[0]] = " ".join(w[2:])
+        elif len(w) >= 2:
+            vals = np.array([float(x) for x in w[2:]], np.float64)
+            assert vals.size == int(w[1]), line[:80]
+            out[w[0]] = vals
+    return out
+
+
+def golden(name):
+    return parse(open(os.path.join(GOLDEN, name + ".txt")).read())
+
+
+def run_built(name):
+    exe = os.path.join(BUILT, name)
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} was not built (tests/cpp/build_callers.sh needs the reference sources)")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return parse(r.stdout)
+
+
+def assert_lines_match(got, want, names, what):
+    for n in names:
+        assert n in got, f"{what}: line {n} missing"
+        assert isinstance(got[n], np.ndarray), f"{what}: {n} unavailable on the GPU build: {got[n]}"
+        assert isinstance(want[n], np.ndarray), f"{what}: {n} unavailable in the reference build: {want[n]}"
+        np.testing.assert_allclose(got[n], want[n], rtol=RTOL, atol=ATOL, err_msg=f"{what}: {n}")
+
+
+# ---- CPU: the unchanged callers compile and link ----------------------------------------------------
+@pytest.mark.skipif(not REFERENCE, reason="no reference sources here (CTENSOR_REFERENCE, or a checkout beside the repository)")
+def test_unchanged_reference_callers_compile_and_link_against_the_host_layers():
+    from ctensor_b200 import build as b
+    b.build()
+    b.build_host()
+    b.build_gen1()
+    subprocess.check_call([os.path.join(ROOT, "tests", "cpp", "build_callers.sh"), REFERENCE])
+    for name in ("callers_gen2_b200", "callers_gen1_b200"):
+        assert os.path.exists(os.path.join(BUILT, name))
+
+
+def test_built_programs_refuse_to_run_without_a_gpu():
+    import ctensor_b200
+    if ctensor_b200.lib().ctb_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    for name in ("callers_gen2_b200", "callers_gen1_b200"):
+        exe = os.path.join(BUILT, name)
+        if not os.path.exists(exe):
+            pytest.skip("not built")
+        r = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+        assert "no CUDA device" in r.stdout + r.stderr          # every section reports it; nothing is computed
+
+
+def test_reference_twins_still_give_the_golden_lines():
+    """Where the reference twins were built (oracle/build_callers_ref.sh) they reproduce the committed lines."""
+    ran = 0
+    for name in ("callers_gen1_ref", "callers_gen2_ref", "callers_gen2_ref_scalar"):
+        exe = os.path.join(ROOT, "oracle", "_ref", name)
+        if not os.path.exists(exe):
+            continue
+        r = subprocess.run([exe], capture_output=True, text=True, timeout=120, cwd="/tmp")
+        assert r.returncode == 0
+        got, want = parse(r.stdout), golden(name)
+        assert got.keys() == want.keys()
+        for k, v in want.items():
+            if isinstance(v, np.ndarray):
+                np.testing.assert_allclose(got[k], v, rtol=1e-6, atol=1e-9, err_msg=f"{name}: {k}")
+        ran += 1
+    if not ran:
+        pytest.skip("oracle/_ref twins not built on this machine")
+
+
+# ---- known answers for the two lines whose meaning depends on dim = -1 -------------------------------------
+def _lcg(seed, n, scale, shift=0.0):
+    mask = (1 << 64) - 1
+    s = (seed * 6364136223846793005 + 1442695040888963407) & mask
+    out = np.empty(n)
+    for i in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & mask
+        out[i] = ((s >> 11) & ((1 << 53) - 1)) / float(1 << 52) - 1.0
+    return (out * scale + shift).astype(np.float32).astype(np.float64)
+
+
+def _known_losses():
+    batch, in_f, out_f = 12, 16, 10
+    y = _lcg(3, batch * in_f, 1.0).reshape(batch, in_f) @ _lcg(1, out_f * in_f, 0.5).reshape(out_f, in_f).T + _lcg(2, out_f, 0.1)
+    mse = np.mean((y - _lcg(4, batch * out_f, 1.0).reshape(batch, out_f)) ** 2)
+    logits = _lcg(7, batch * in_f, 1.0).reshape(batch, in_f) @ _lcg(5, out_f * in_f, 0.5).reshape(out_f, in_f).T + _lcg(6, out_f, 0.1)
+    logp = logits - logits.max(1, keepdims=True)
+    logp = logp - np.log(np.exp(logp).sum(1, keepdims=True))
+    labels = (np.arange(batch) * 7 + 3) % out_f
+    ce = -logp[np.arange(batch), labels].mean()
+    return mse, ce
+
+
+# ---- GPU: the programs run and agree with the reference builds -----------------------------------------------
+@pytest.mark.gpu
+def test_first_generation_callers_run_on_the_gpu_like_the_reference():
+    got, want = run_built("callers_gen1_b200"), golden("callers_gen1_ref")
+    assert_lines_match(got, want, [k for k, v in want.items() if isinstance(v, np.ndarray)], "gen 1")
+
+
+@pytest.mark.gpu
+def test_second_generation_callers_run_on_the_gpu_like_the_reference():
+    got, want = run_built("callers_gen2_b200"), golden("callers_gen2_ref_scalar")
+    dim_minus_one = {"mse.loss", "ce.loss"}
+    names = [k for k, v in want.items() if isinstance(v, np.ndarray) and k not in dim_minus_one]
+    assert len(names) >= 15
+    assert_lines_match(got, want, names, "gen 2")
+    mse, ce = _known_losses()
+    np.testing.assert_allclose(got["mse.loss"], [mse], rtol=RTOL, err_msg="Loss::MSE")
+    np.testing.assert_allclose(got["ce.loss"], [ce], rtol=RTOL, err_msg="Loss::CrossEntropy")
+    np.testing.assert_allclose(got["mse.loss_from_operators"], [mse], rtol=RTOL)

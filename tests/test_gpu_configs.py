@@ -1,10 +1,16 @@
-"""The benchmark configurations at their FULL sizes, checked through size-independent
-properties (the CPU oracle cannot cover 1.5 GiB tensors in seconds): a fused or strided kernel
-must agree with the same computation spelled as a chain of the primitive operators that the
-small-case tests have already pinned to the reference."""
+"""The benchmark configurations at their FULL sizes.  Two kinds of check: size-independent
+properties (a fused or strided kernel must agree with the same computation spelled as a chain of
+the primitive operators that the small-case tests have already pinned to the reference), and the
+CPU oracle itself on SAMPLES of the full-size result — rows, columns and windows that include the
+first and last tiles, the last split and the highest indices, so that an index error that only
+shows beyond 2^31 bytes or in the last row cannot pass on both sides."""
 import numpy as np
 import pytest
 import torch
+
+import oracle_lib as ol
+from oracle_lib import HostView
+from gpu_util import assert_bits_equal, assert_close
 
 pytestmark = pytest.mark.gpu
 RTOL = 1e-5
@@ -46,7 +52,30 @@ def test_config3_reductions_full_size(ct):
     del X
 
 
-def test_config4_permuted_softmax_chain_full_size(ct):
+def test_config3_reductions_full_size_against_the_oracle(ct, oracle):
+    """The oracle on 192 columns (dim 0) and 192 rows (dim 1) of the full-size X: the first and
+    last column tile / row, the rows of the last split, and a stretch in the middle."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2)
+    X = torch.randn(8192, 16384, device="cuda", generator=g)
+    X[8191, 16383] = 0.0
+    X[0, 16383] = -0.0
+    host = X.cpu().numpy()
+    whole = HostView.contig(host)
+    for dim, extent in ((0, 16384), (1, 8192)):
+        starts = (0, extent // 2 - 37, extent - 64)
+        for op in (ol.SUM, ol.MEAN, ol.VAR, ol.MAX, ol.MIN, ol.ARGMAX):
+            got = ct.reduce(op, X, dim).cpu().numpy()
+            for lo in starts:
+                ref = oracle.reduce(op, whole.narrow(1 - dim, lo, 64), dim)
+                if op in (ol.MAX, ol.MIN, ol.ARGMAX):
+                    assert_bits_equal(got[lo:lo + 64], ref, f"op {op} dim {dim} at {lo}")
+                else:
+                    assert_close(got[lo:lo + 64], ref, RTOL, f"op {op} dim {dim} at {lo}")
+    del X
+
+
+def test_config4_permuted_softmax_chain_full_size(ct, oracle):
     """S = permute(0,2,1,3) of a [32,1024,12,1024] buffer, M[1,12,1,1024]: S+M, then the chain
     max -> sub -> exp -> sum -> div along the last dim, fused and unfused."""
     g = torch.Generator(device="cuda")
@@ -72,9 +101,21 @@ def test_config4_permuted_softmax_chain_full_size(ct):
     assert differing < 1e-3                                     # the two differ only in rare last bits
     rows = ct.reduce(ct.SUM, fused, 3)
     assert float((rows - 1).abs().max()) < 1e-5
+    # the oracle on sampled rows [b, h, q, :] of S + M and of softmax(S + M), the last batch,
+    # head and row (the highest addresses of the 1.5 GiB buffer) among them
+    t = ct.binary(ct.ADD, S, M)
+    picks = [(0, 0, 0), (0, 11, 1023), (13, 5, 511), (31, 0, 0), (31, 11, 1022), (31, 11, 1023)]
+    x_rows = np.stack([buf[b, q, h, :].cpu().numpy() for b, h, q in picks])       # S[b,h,q,:] = buf[b,q,h,:]
+    m_rows = np.stack([M[0, h, 0, :].cpu().numpy() for b, h, q in picks])
+    hx, hm = HostView.contig(x_rows), HostView.contig(m_rows)
+    assert_bits_equal(np.stack([t[b, h, q].cpu().numpy() for b, h, q in picks]), oracle.binary(ol.ADD, hx, hm), "S+M rows")
+    assert_close(np.stack([fused[b, h, q].cpu().numpy() for b, h, q in picks]), oracle.softmax(hx, hm), RTOL,
+                 "softmax(S+M) rows")
+    assert_close(np.stack([chain[b, h, q].cpu().numpy() for b, h, q in picks]), oracle.softmax(hx, hm), RTOL,
+                 "unfused chain rows")
 
 
-def test_config5_gpt2_rows_full_size(ct):
+def test_config5_gpt2_rows_full_size(ct, oracle):
     """GPT-2 small non-GEMM ops on [8,1024,768] / [8,1024,3072] / [8,12,1024,1024]."""
     g = torch.Generator(device="cuda")
     g.manual_seed(6)
@@ -105,6 +146,53 @@ def test_config5_gpt2_rows_full_size(ct):
     by_mask = ct.softmax(s, mask)
     assert _bits_equal(by_flag, by_mask)
     assert float(by_flag[0, 0, 0, 1:].abs().max()) == 0.0
+    # the oracle on samples of every op: first / middle / last rows, windows and attention matrices
+    for lo in (0, 4000, 8 * 1024 - 16):
+        rows_h = HostView.contig(h.view(-1, 768)[lo:lo + 16].cpu().numpy())
+        xs = HostView.contig(x.view(-1, 768)[lo:lo + 16].cpu().numpy())
+        rs = HostView.contig(r.view(-1, 768)[lo:lo + 16].cpu().numpy())
+        assert_bits_equal(rows_h.numpy(), oracle.binary(ol.ADD, xs, rs), "residual add rows")
+        want = oracle.layernorm(rows_h, HostView.contig(gamma.cpu().numpy()), HostView.contig(beta.cpu().numpy()), 1e-5)
+        assert_close(fused.view(-1, 768)[lo:lo + 16].cpu().numpy(), want, RTOL, "layernorm rows")
+    ga = ct.unary(ct.GELU_TANH, a).view(-1)
+    for lo in (0, a.numel() // 2 - 777, a.numel() - (1 << 16)):
+        win = HostView.contig(a.view(-1)[lo:lo + (1 << 16)].cpu().numpy())
+        assert_bits_equal(ga[lo:lo + (1 << 16)].cpu().numpy(), oracle.unary(ol.GELU_TANH, win), "gelu window")
+    for b, hd in ((0, 0), (7, 11)):
+        mat = HostView.contig(s[b, hd].cpu().numpy().reshape(1, 1, 1024, 1024))
+        assert_close(by_flag[b, hd].cpu().numpy().reshape(1, 1, 1024, 1024), oracle.softmax(mat, None, causal=True), RTOL,
+                     "causal softmax matrix")
+
+
+def test_config2_sweep_full_size_against_the_oracle(ct, oracle):
+    """add, mul, exp, relu, gelu on 2^30-element tensors: three 2^20-element windows of every result
+    (start, an odd offset in the middle, the end) against the oracle, and the ragged tail of a
+    tensor of 2^30 + 5 elements."""
+    n = 1 << 30
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    x = torch.randn(n + 5, device="cuda", generator=g)
+    y = torch.randn(n + 5, device="cuda", generator=g)
+    w = 1 << 20
+    starts = (0, n // 2 - 12345, n - w)
+
+    def windows(t, lows):
+        return [HostView.contig(t[lo:lo + w].cpu().numpy()) for lo in lows]
+
+    for ragged in (False, True):
+        xs, ys = (x, y) if ragged else (x[:n], y[:n])
+        lows = (n + 5 - w,) if ragged else starts
+        xw, yw = windows(xs, lows), windows(ys, lows)
+        for op in (ol.ADD, ol.MUL):
+            out = ct.binary(op, xs, ys)
+            for lo, hx, hy in zip(lows, xw, yw):
+                assert_bits_equal(out[lo:lo + w].cpu().numpy(), oracle.binary(op, hx, hy), f"binary {op} at {lo}")
+            del out
+        for op in (ol.EXP, ol.RELU, ol.GELU_TANH):
+            out = ct.unary(op, xs)
+            for lo, hx in zip(lows, xw):
+                assert_bits_equal(out[lo:lo + w].cpu().numpy(), oracle.unary(op, hx), f"unary {op} at {lo}")
+            del out
 
 
 def test_dense_bit_pattern_blocks_fp32_unary(ct, oracle):
