@@ -226,6 +226,7 @@ std::shared_ptr<Storage> Storage::allocate(size_t n, DType dt, bool /*requires_g
     void* p = nullptr;
     if (index != t_device_selected) use_device(index);     // the clearing memset runs on that device's stream
     check(ctb_pool_alloc_managed(&p, n * dtype_size(dt), t_alloc_uninitialized ? 0 : 1, index, nullptr));
+    if (!t_alloc_uninitialized) check(ctb_sync(nullptr));   // the clearing is queued: the host may write right away
     s->data = std::shared_ptr<void>(p, [](void* q) { ctb_pool_free_managed(q); });
     return s;
 }
