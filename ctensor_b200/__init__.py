@@ -48,6 +48,7 @@ EXPORTED_SYMBOLS = [
     "ctb_matmul", "ctb_optimizer_step",
     "ctb_pool_alloc_managed", "ctb_pool_free_managed", "ctb_pool_trim", "ctb_pool_set_limit", "ctb_pool_stats",
     "ctb_prefetch_managed",
+    "ctb_div_backward", "ctb_tanh_backward", "ctb_cross_entropy", "ctb_cross_entropy_backward",
 ]
 
 
@@ -124,6 +125,10 @@ def lib() -> ctypes.CDLL:
     L.ctb_pool_set_limit.argtypes = [i32, ctypes.c_size_t]
     L.ctb_pool_stats.argtypes = [i32, ctypes.POINTER(PoolInfo)]
     L.ctb_prefetch_managed.argtypes = [vd, ctypes.c_size_t, i32, vd]
+    L.ctb_div_backward.argtypes = [vp, vp, vp, vp, vp, i32, vd]
+    L.ctb_tanh_backward.argtypes = [vp, vp, vp, i32, vd]
+    L.ctb_cross_entropy.argtypes = [vp, vp, i32, vp, vd, vd]
+    L.ctb_cross_entropy_backward.argtypes = [vp, vp, ctypes.c_double, vp, i32, vd, vd]
     L.ctb_binary.argtypes = [i32, vp, vp, vp, vd]
     L.ctb_unary.argtypes = [i32, vp, ctypes.c_double, vp, vd]
     L.ctb_copy_strided.argtypes = [vp, vp, vd]
@@ -385,6 +390,53 @@ def accumulate_grad(grad, src):
     with _device_guard(g):
         check(lib().ctb_accumulate_grad(g.cview(), s.cview(), _stream_ptr(g)))
     return grad
+
+
+def div_backward(grad, a, b, want_a=True, want_b=True, out_a=None, out_b=None, accumulate=False):
+    """ctb_div_backward: (grad / b, -((grad * a) / ((b * b) + 1e-6))) over the broadcast shape; with
+    ``accumulate`` the results are added into out_a / out_b (existing gradient buffers)."""
+    g, a, b = _as_dview(grad), _as_dview(a), _as_dview(b)
+    shape = broadcast_shape(g.shape, broadcast_shape(a.shape, b.shape))
+    if want_a and out_a is None:
+        out_a = _new_out(g, shape)
+    if want_b and out_b is None:
+        out_b = _new_out(g, shape)
+    with _device_guard(g):
+        check(lib().ctb_div_backward(g.cview(), a.cview(), b.cview(), DView.of(out_a).cview() if want_a else None,
+                                     DView.of(out_b).cview() if want_b else None, int(accumulate), _stream_ptr(g)))
+    return out_a, out_b
+
+
+def tanh_backward(grad, t, out=None, accumulate=False):
+    """ctb_tanh_backward: grad * (1 / (cosh t * cosh t))."""
+    g, t = _as_dview(grad), _as_dview(t)
+    if out is None:
+        out = _new_out(g, broadcast_shape(g.shape, t.shape))
+    with _device_guard(g):
+        check(lib().ctb_tanh_backward(g.cview(), t.cview(), DView.of(out).cview(), int(accumulate), _stream_ptr(g)))
+    return out
+
+
+def cross_entropy(logits, labels, mean=True, out=None, bad=None):
+    """ctb_cross_entropy: mean | sum over the rows of -(log_softmax(logits)[row, label])."""
+    x, lab = _as_dview(logits), _as_dview(labels)
+    if out is None:
+        out = _new_out(x, (1,))
+    with _device_guard(x):
+        check(lib().ctb_cross_entropy(x.cview(), lab.cview(), int(mean), DView.of(out).cview(),
+                                      None if bad is None else bad.data_ptr(), _stream_ptr(x)))
+    return out
+
+
+def cross_entropy_backward(logits, labels, grad_scale, out=None, accumulate=False, bad=None):
+    """ctb_cross_entropy_backward: (softmax(logits) - onehot(labels)) * grad_scale."""
+    x, lab = _as_dview(logits), _as_dview(labels)
+    if out is None:
+        out = _new_out(x, x.shape)
+    with _device_guard(x):
+        check(lib().ctb_cross_entropy_backward(x.cview(), lab.cview(), float(grad_scale), DView.of(out).cview(),
+                                               int(accumulate), None if bad is None else bad.data_ptr(), _stream_ptr(x)))
+    return out
 
 
 def matmul(a, b, out=None):

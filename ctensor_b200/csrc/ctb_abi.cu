@@ -13,6 +13,7 @@
 #include "ctb_common.cuh"
 #include "ctb_math.cuh"
 #include "ctb_reduce.cuh"
+#include "ctb_backward.cuh"
 
 namespace ctb {
 
@@ -921,6 +922,168 @@ int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view*
     return launch_batchnorm_apply((const float*)elem_ptr(x), pm, sm, pv, sv, pg, sg, pb, sb, eps,
                                   (float*)((char*)ws + kTicketBytes), (float*)elem_ptr_mut(out), N, C, S,
                                   (cudaStream_t)stream);
+}
+
+// ---- backward bodies, cross-entropy rows -----------------------------------------------------------------
+namespace {
+
+// Broadcast `ops` (null entries allowed) against the shape of `out`, which fixes every extent,
+// and collapse.  stride row k of the plan belongs to ops[k]; row 3 to `out`.
+int build_bwd_plan(const ctb_view* const* ops, const ctb_view* out, BwdPlan* plan) {
+    const int nd = out->ndim;
+    int64_t shape[CTB_MAX_DIMS], stride[4][CTB_MAX_DIMS];
+    for (int k = 0; k < 3; ++k)
+        if (ops[k] && ops[k]->ndim > nd) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+    for (int d = 0; d < nd; ++d) {
+        shape[d] = out->shape[d];
+        stride[3][d] = out->shape[d] == 1 ? 0 : out->stride[d];
+        for (int k = 0; k < 3; ++k) {
+            stride[k][d] = 0;
+            if (!ops[k]) continue;
+            const int j = d - (nd - ops[k]->ndim);
+            const int64_t e = j < 0 ? 1 : ops[k]->shape[j];
+            if (e != 1 && e != shape[d]) return set_error(CTB_ERR_SHAPE, "Shape mismatch in binary op");
+            stride[k][d] = (j < 0 || e == 1) ? 0 : ops[k]->stride[j];
+        }
+    }
+    plan->numel = 1;
+    int k = 0;
+    for (int d = 0; d < nd; ++d) {
+        plan->numel *= shape[d];
+        if (shape[d] == 1) continue;
+        bool merge = k > 0;
+        for (int q = 0; q < 4 && merge; ++q)
+            if (plan->stride[q][k - 1] != stride[q][d] * shape[d]) merge = false;
+        if (merge) {
+            plan->shape[k - 1] *= shape[d];
+            for (int q = 0; q < 4; ++q) plan->stride[q][k - 1] = stride[q][d];
+            continue;
+        }
+        plan->shape[k] = shape[d];
+        for (int q = 0; q < 4; ++q) plan->stride[q][k] = stride[q][d];
+        ++k;
+    }
+    if (k == 0) {
+        plan->shape[0] = 1;
+        for (int q = 0; q < 4; ++q) plan->stride[q][0] = 0;
+        k = 1;
+    }
+    plan->ndim = k;
+    plan->flat = k == 1 && plan->stride[3][0] == 1;
+    for (int q = 0; q < 3; ++q)
+        if (ops[q] && plan->stride[q][0] != 1) plan->flat = 0;
+    if (plan->numel == 1) plan->flat = 0;       // all strides collapse to 0: the strided kernel handles it
+    return CTB_OK;
+}
+
+int backward_chain_entry(int kind, const char* who, const ctb_view* grad, const ctb_view* x, const ctb_view* y,
+                         const ctb_view* out, int accumulate, void* stream) {
+    int rc;
+    if ((rc = check_view(grad, "backward: null gradient", who))) return rc;
+    if (x && (rc = check_view(x, "backward: null operand", who))) return rc;
+    if (y && (rc = check_view(y, "backward: null operand", who))) return rc;
+    if ((rc = check_view(out, "output: null view", who))) return rc;
+    const ctb_view* ops[3] = {grad, x, y};
+    for (int k = 0; k < 3; ++k)
+        if (ops[k] && ops[k]->dtype != out->dtype) return set_error(CTB_ERR_DTYPE, "%s: operands must have the same dtype", who);
+    if (!accumulate) {
+        if (!view_contiguous(out)) return set_error(CTB_ERR_SHAPE, "%s: output must be contiguous", who);
+        if ((rc = check_no_alias(out, ops, 3, who))) return rc;
+    }
+    BwdPlan plan;
+    if ((rc = build_bwd_plan(ops, out, &plan))) return rc;
+    return launch_backward_chain(kind, out->dtype, plan, elem_ptr(grad), x ? elem_ptr(x) : nullptr,
+                                 y ? elem_ptr(y) : nullptr, elem_ptr_mut(out), accumulate, (cudaStream_t)stream);
+}
+
+// logits [rows, classes] (classes contiguous), labels: `rows` Int32 values in a [rows] or [rows, 1] view
+int ce_geometry(const ctb_view* logits, const ctb_view* labels, const char* who, int64_t* rows, int64_t* classes,
+                int64_t* row_stride, int64_t* label_stride) {
+    int rc;
+    if ((rc = check_view(logits, "Loss::CrossEntropy: null tensor", who))) return rc;
+    if ((rc = check_view(labels, "Loss::CrossEntropy: null tensor", who))) return rc;
+    if (logits->ndim != 2) return set_error(CTB_ERR_SHAPE, "CrossEntropy: Pred must be 2D [Batch, Classes]");
+    if (logits->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "%s: only Float32 logits are supported", who);
+    if (labels->dtype != CTB_I32) return set_error(CTB_ERR_DTYPE, "Index tensor must be integer type");
+    *rows = logits->shape[0];
+    *classes = logits->shape[1];
+    if (*classes > 1 && logits->stride[1] != 1) return set_error(CTB_ERR_SHAPE, "%s: the class dim must be contiguous", who);
+    *row_stride = *rows > 1 ? logits->stride[0] : 0;
+    if (view_numel(labels) != *rows) return set_error(CTB_ERR_SHAPE, "%s: one label per row is expected", who);
+    *label_stride = 0;
+    for (int d = 0; d < labels->ndim; ++d)
+        if (labels->shape[d] == *rows && *rows > 1) *label_stride = labels->stride[d];
+    return CTB_OK;
+}
+
+}  // namespace
+
+int ctb_div_backward(const ctb_view* grad, const ctb_view* a, const ctb_view* b, const ctb_view* grad_a,
+                     const ctb_view* grad_b, int accumulate, void* stream) {
+    int rc;
+    if (!grad_a && !grad_b) return set_error(CTB_ERR_NULL, "div_backward: no output requested");
+    if (!b) return set_error(CTB_ERR_NULL, "backward: null operand");
+    if (grad_a && (rc = backward_chain_entry(kBwdDivA, "div_backward", grad, nullptr, b, grad_a, accumulate, stream))) return rc;
+    if (grad_b) {
+        if (!a) return set_error(CTB_ERR_NULL, "backward: null operand");
+        if ((rc = backward_chain_entry(kBwdDivB, "div_backward", grad, a, b, grad_b, accumulate, stream))) return rc;
+    }
+    return CTB_OK;
+}
+
+int ctb_tanh_backward(const ctb_view* grad, const ctb_view* t, const ctb_view* grad_t, int accumulate, void* stream) {
+    if (!t) return set_error(CTB_ERR_NULL, "backward: null operand");
+    return backward_chain_entry(kBwdTanh, "tanh_backward", grad, t, nullptr, grad_t, accumulate, stream);
+}
+
+int ctb_cross_entropy(const ctb_view* logits, const ctb_view* labels, int mean, const ctb_view* loss, int32_t* bad,
+                      void* stream) {
+    int rc;
+    int64_t rows, classes, row_stride, label_stride;
+    if ((rc = ce_geometry(logits, labels, "cross_entropy", &rows, &classes, &row_stride, &label_stride))) return rc;
+    if ((rc = check_out(loss, 1, CTB_F32, "cross_entropy"))) return rc;
+    if (rows == 0 || classes == 0) return set_error(CTB_ERR_SHAPE, "cross_entropy: empty batch");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (bad) CTB_CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(int32_t), st));
+    // scratch: [tickets | kernel scratch of the reduction | nll[rows]]
+    ctb_view nll;
+    memset(&nll, 0, sizeof nll);
+    nll.dtype = CTB_F32;
+    nll.ndim = 1;
+    nll.shape[0] = rows;
+    nll.stride[0] = 1;
+    ReduceGeom g;
+    reduce_geom_full_dense(&nll, &g);
+    size_t kernel_ws = reduce_workspace_bytes(g, CTB_F32);
+    if (kernel_ws < kTicketBytes) kernel_ws = kTicketBytes;
+    kernel_ws = (kernel_ws + 255) / 256 * 256;
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(kernel_ws + (size_t)rows * sizeof(float), &ws, st))) return rc;
+    float* nll_buf = (float*)((char*)ws + kernel_ws);
+    if ((rc = launch_ce_forward_rows((const float*)elem_ptr(logits), row_stride, (const int32_t*)elem_ptr(labels),
+                                     label_stride, rows, classes, nll_buf, bad, st))) return rc;
+    // mean(nll) / sum(nll) as the reduction operators compute them (fp64 accumulation, sum rounded
+    // to fp32, then times 1/rows in double and rounded: src/core/ops_dispatch.cpp:385-390)
+    return launch_reduce(mean ? CTB_MEAN : CTB_SUM, CTB_F32, g, nll_buf, elem_ptr_mut(loss), nullptr, ws, kernel_ws, st);
+}
+
+int ctb_cross_entropy_backward(const ctb_view* logits, const ctb_view* labels, double grad_scale,
+                               const ctb_view* grad_logits, int accumulate, int32_t* bad, void* stream) {
+    int rc;
+    int64_t rows, classes, row_stride, label_stride;
+    if ((rc = ce_geometry(logits, labels, "cross_entropy_backward", &rows, &classes, &row_stride, &label_stride))) return rc;
+    if ((rc = check_view(grad_logits, "output: null view", "cross_entropy_backward"))) return rc;
+    if (grad_logits->dtype != CTB_F32 || grad_logits->ndim != 2 || grad_logits->shape[0] != rows || grad_logits->shape[1] != classes)
+        return set_error(CTB_ERR_SHAPE, "cross_entropy_backward: the gradient must be Float32 [Batch, Classes]");
+    if (classes > 1 && grad_logits->stride[1] != 1) return set_error(CTB_ERR_SHAPE, "cross_entropy_backward: the class dim must be contiguous");
+    const ctb_view* ins[2] = {logits, labels};
+    if ((rc = check_no_alias(grad_logits, ins, 2, "cross_entropy_backward"))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (bad) CTB_CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(int32_t), st));
+    if (rows == 0 || classes == 0) return CTB_OK;
+    return launch_ce_backward_rows((const float*)elem_ptr(logits), row_stride, (const int32_t*)elem_ptr(labels), label_stride,
+                                   rows, classes, (float)grad_scale, (float*)elem_ptr_mut(grad_logits),
+                                   rows > 1 ? grad_logits->stride[0] : 0, accumulate, bad, st);
 }
 
 // ---- matmul ------------------------------------------------------------------------------------------

@@ -1,0 +1,288 @@
+// Backward bodies the reference spells as chains of elementwise operators, and the
+// cross-entropy rows of its loss module, each as one pass:
+//
+//   GradDiv::backward   src/core/autograd.cpp:188-202   da = g / b
+//                                                       db = -((g * a) / ((b * b) + 1e-6))
+//   GradTanh::backward  src/core/autograd.cpp:434-438   dt = g * (1 / (cosh t * cosh t))
+//   Loss::CrossEntropy  src/neuralnet/loss.cpp:90-118   loss = mean|sum over rows of
+//                                                       -(log_softmax(x)[row, label[row]])
+//   GradCrossEntropy    src/neuralnet/loss.cpp:319-370  dx = (softmax(x) - onehot(label)) * scale
+//
+// The elementwise chains keep the reference's rounding points: every operator result is rounded
+// to the tensor's dtype before the next one uses it, scalar steps are done in double and rounded
+// once.  On the CPU each of those steps is a pass over a fresh temporary (six operators and five
+// temporaries for db); here the operands are read once and the result is written — or added into
+// an existing gradient buffer, skipping NaN / infinite values as accumulate_grad does
+// (src/core/autograd.cpp:139-151) — once.
+#include "ctb_common.cuh"
+#include "ctb_math.cuh"
+#include "ctb_backward.cuh"
+
+namespace ctb {
+namespace {
+
+// ---- the three chains ------------------------------------------------------------------------------
+template <int KIND, typename T> struct BwdFn;
+template <typename T> struct BwdFn<kBwdDivA, T> {
+    __device__ __forceinline__ static T apply(T g, T, T b) { return BinaryFn<CTB_DIV, T>::apply(g, b); }
+};
+template <typename T> struct BwdFn<kBwdDivB, T> {
+    __device__ __forceinline__ static T apply(T g, T a, T b) {
+        const T num = BinaryFn<CTB_MUL, T>::apply(g, a);
+        const T den = BinaryFn<CTB_MUL, T>::apply(b, b);
+        const T den_safe = from_double<T>(__dadd_rn(to_double(den), 1e-6));      // add_scalar
+        const T res = BinaryFn<CTB_DIV, T>::apply(num, den_safe);
+        return from_double<T>(__dmul_rn(to_double(res), -1.0));                  // mul_scalar
+    }
+};
+template <typename T> struct BwdFn<kBwdTanh, T> {
+    __device__ __forceinline__ static T apply(T g, T t, T) {
+        const T c = from_double<T>(cosh(to_double(t)));
+        const T c2 = BinaryFn<CTB_MUL, T>::apply(c, c);
+        const T inv = from_double<T>(__ddiv_rn(1.0, to_double(c2)));             // div_scalar_rev
+        return BinaryFn<CTB_MUL, T>::apply(g, inv);
+    }
+};
+
+template <typename T, bool ACC> __device__ __forceinline__ T finish(T old, T v) {
+    return ACC ? BinaryFn<kOpAddFinite, T>::apply(old, v) : v;
+}
+
+// Every operand contiguous and of the result's shape: 128-bit accesses, one tile of
+// 256 threads x 2 vectors per CTA, all loads issued before the first use.
+template <int KIND, typename T, bool ACC, int VEC>
+__global__ void __launch_bounds__(256)
+bwd_flat_kernel(const T* __restrict__ g, const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, int64_t n) {
+    using V = Vec<T, VEC>;
+    constexpr int U = 2;
+    constexpr int64_t TILE = 256 * VEC * U;
+    const int64_t base = (int64_t)blockIdx.x * TILE + (int64_t)threadIdx.x * VEC;
+    constexpr bool NEED_Y = KIND != kBwdTanh;
+    if ((int64_t)(blockIdx.x + 1) * TILE <= n) {
+        V vg[U], vx[U], vy[U], vo[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t at = base + (int64_t)u * 256 * VEC;
+            vg[u] = ldg_stream(reinterpret_cast<const V*>(g + at));
+            if (KIND != kBwdDivA) vx[u] = ldg_stream(reinterpret_cast<const V*>(x + at));
+            if (NEED_Y) vy[u] = ldg_stream(reinterpret_cast<const V*>(y + at));
+            if (ACC) vo[u] = ldg_stream(reinterpret_cast<const V*>(out + at));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            V r;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
+                r.v[k] = finish<T, ACC>(ACC ? vo[u].v[k] : T(0),
+                                        BwdFn<KIND, T>::apply(vg[u].v[k], KIND != kBwdDivA ? vx[u].v[k] : T(0), NEED_Y ? vy[u].v[k] : T(0)));
+            stg_stream(reinterpret_cast<V*>(out + base + (int64_t)u * 256 * VEC), r);
+        }
+    } else {
+        for (int64_t i = (int64_t)blockIdx.x * TILE + threadIdx.x; i < n; i += 256)
+            out[i] = finish<T, ACC>(ACC ? out[i] : T(0),
+                                    BwdFn<KIND, T>::apply(g[i], KIND != kBwdDivA ? x[i] : T(0), NEED_Y ? y[i] : T(0)));
+    }
+}
+
+// Any strides / broadcasting: one multiplier-division chain per element.
+struct BwdIdx {
+    DimSet dims;
+    int64_t stride[4][CTB_MAX_DIMS];      // g, x, y, out
+    int64_t numel;
+};
+template <int KIND, typename T, bool ACC>
+__global__ void __launch_bounds__(256)
+bwd_strided_kernel(const T* __restrict__ g, const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, BwdIdx ix) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < ix.numel; i += step) {
+        int64_t off[4] = {0, 0, 0, 0};
+        dimset_offsets<4>(ix.dims, i, ix.stride, off);
+        const T v = BwdFn<KIND, T>::apply(g[off[0]], x ? x[off[1]] : T(0), y ? y[off[2]] : T(0));
+        out[off[3]] = finish<T, ACC>(ACC ? out[off[3]] : T(0), v);
+    }
+}
+
+template <int KIND, typename T>
+int launch_kind(const BwdPlan& p, const T* g, const T* x, const T* y, T* out, int accumulate, cudaStream_t st) {
+    if (p.numel == 0) return CTB_OK;
+    if (p.flat) {
+        constexpr int VEC = 16 / sizeof(T);
+        const bool aligned = is_aligned(g, 16) && is_aligned(out, 16) && (!x || is_aligned(x, 16)) && (!y || is_aligned(y, 16));
+        const int64_t tile = 256 * 2 * (aligned ? VEC : 1);
+        const unsigned grid = (unsigned)ceil_div(p.numel, tile);
+        if (aligned) {
+            if (accumulate) bwd_flat_kernel<KIND, T, true, VEC><<<grid, 256, 0, st>>>(g, x, y, out, p.numel);
+            else bwd_flat_kernel<KIND, T, false, VEC><<<grid, 256, 0, st>>>(g, x, y, out, p.numel);
+        } else {
+            if (accumulate) bwd_flat_kernel<KIND, T, true, 1><<<grid, 256, 0, st>>>(g, x, y, out, p.numel);
+            else bwd_flat_kernel<KIND, T, false, 1><<<grid, 256, 0, st>>>(g, x, y, out, p.numel);
+        }
+        return cuda_error(cudaGetLastError(), "backward chain launch");
+    }
+    BwdIdx ix{};
+    dimset_init(&ix.dims, p.ndim, p.shape);
+    ix.numel = p.numel;
+    for (int k = 0; k < 4; ++k)
+        for (int d = 0; d < p.ndim; ++d) ix.stride[k][d] = p.stride[k][d];
+    int64_t blocks = ceil_div(p.numel, 256);
+    if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
+    if (accumulate) bwd_strided_kernel<KIND, T, true><<<(unsigned)blocks, 256, 0, st>>>(g, x, y, out, ix);
+    else bwd_strided_kernel<KIND, T, false><<<(unsigned)blocks, 256, 0, st>>>(g, x, y, out, ix);
+    return cuda_error(cudaGetLastError(), "backward chain launch");
+}
+
+template <typename T>
+int launch_typed(int kind, const BwdPlan& p, const void* g, const void* x, const void* y, void* out, int accumulate,
+                 cudaStream_t st) {
+    switch (kind) {
+    case kBwdDivA: return launch_kind<kBwdDivA, T>(p, (const T*)g, (const T*)nullptr, (const T*)y, (T*)out, accumulate, st);
+    case kBwdDivB: return launch_kind<kBwdDivB, T>(p, (const T*)g, (const T*)x, (const T*)y, (T*)out, accumulate, st);
+    case kBwdTanh: return launch_kind<kBwdTanh, T>(p, (const T*)g, (const T*)x, (const T*)nullptr, (T*)out, accumulate, st);
+    }
+    return set_error(CTB_ERR_ARG, "backward chain: unknown kind %d", kind);
+}
+
+// ---- cross-entropy rows ---------------------------------------------------------------------------------
+// One warp per row up to 1024 classes, one 256-thread CTA per row beyond; the row is read from
+// global memory in each of the three sweeps (max, sum of exponentials, output) — after the first
+// sweep it is in L1/L2, so HBM sees it once.
+// THREADS = cooperating threads per row: 32 (a warp, shuffles only) or 256 (the CTA, through smem).
+template <int THREADS> __device__ __forceinline__ float row_max(float v, float* smem) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, off);
+        v = (v < o) ? o : v;
+    }
+    if (THREADS == 32) return v;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) smem[w] = v;
+    __syncthreads();
+    float r = smem[0];
+#pragma unroll
+    for (int i = 1; i < THREADS / 32; ++i) r = (r < smem[i]) ? smem[i] : r;
+    return r;
+}
+template <int THREADS> __device__ __forceinline__ double row_sum(double v, double* smem) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = __dadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if (THREADS == 32) return v;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) smem[w] = v;
+    __syncthreads();
+    double r = smem[0];
+#pragma unroll
+    for (int i = 1; i < THREADS / 32; ++i) r = __dadd_rn(r, smem[i]);
+    return r;
+}
+
+__device__ __forceinline__ int64_t resolve_label(int32_t label, int64_t classes, int32_t* bad) {
+    int64_t l = label;
+    if (l < 0) l += classes;                       // negative indices count from the end, as Tensor::gather's
+    if (l < 0 || l >= classes) {
+        if (bad) *bad = 1;
+        return -1;
+    }
+    return l;
+}
+
+// nll[row] = -((x[label] - max) - ln((float)sum exp(x - max))): the chain max -> sub -> exp -> sum ->
+// ln -> sub -> gather -> mul_scalar(-1) of Loss::CrossEntropy with the pinned exp / log flavours.
+template <int THREADS>
+__global__ void __launch_bounds__(256)
+ce_forward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
+                       int64_t label_stride, int64_t rows, int64_t classes, float* __restrict__ nll, int32_t* bad) {
+    __shared__ float smax[8];
+    __shared__ double ssum[8];
+    constexpr int RPB = THREADS == 32 ? 8 : 1;     // rows per CTA: 8 warps of one row each, or one CTA-wide row
+    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
+    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
+    if (row >= rows) return;                        // whole warps (or the whole CTA) leave together
+    const float* line = x + row * row_stride;
+    float m = -INFINITY;
+    for (int64_t c = t; c < classes; c += THREADS) { const float v = line[c]; m = (m < v) ? v : m; }
+    m = row_max<THREADS>(m, smax);
+    double z = 0.0;
+    for (int64_t c = t; c < classes; c += THREADS) z = __dadd_rn(z, (double)exp_cephes(__fsub_rn(line[c], m)));
+    z = row_sum<THREADS>(z, ssum);
+    if (t == 0) {
+        const int64_t l = resolve_label(labels[row * label_stride], classes, bad);
+        float out = 0.0f;
+        if (l >= 0) {
+            const float lz = log_cephes(__double2float_rn(z));
+            const float picked = __fsub_rn(__fsub_rn(line[l], m), lz);
+            out = __double2float_rn(__dmul_rn((double)picked, -1.0));
+        }
+        nll[row] = out;
+    }
+}
+
+// dx[row, c] = (exp(x - max) / sum - [c == label]) * scale (GradCrossEntropy::backward).
+template <int THREADS, bool ACC>
+__global__ void __launch_bounds__(256)
+ce_backward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
+                        int64_t label_stride, int64_t rows, int64_t classes, float scale, float* __restrict__ dx,
+                        int64_t dx_stride, int32_t* bad) {
+    __shared__ float smax[8];
+    __shared__ double ssum[8];
+    constexpr int RPB = THREADS == 32 ? 8 : 1;
+    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
+    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
+    if (row >= rows) return;
+    const float* line = x + row * row_stride;
+    float m = -1e9f;                                 // the reference's starting value (loss.cpp:345)
+    for (int64_t c = t; c < classes; c += THREADS) { const float v = line[c]; m = (v > m) ? v : m; }
+    m = row_max<THREADS>(m, smax);
+    double z = 0.0;
+    for (int64_t c = t; c < classes; c += THREADS) z = __dadd_rn(z, (double)expf(__fsub_rn(line[c], m)));
+    z = row_sum<THREADS>(z, ssum);
+    const float sum_exp = __double2float_rn(z);
+    const float inv = sum_exp > 1e-12f ? __fdiv_rn(1.0f, sum_exp) : 0.0f;
+    const int64_t l = resolve_label(labels[row * label_stride], classes, t == 0 ? bad : nullptr);
+    float* drow = dx + row * dx_stride;
+    for (int64_t c = t; c < classes; c += THREADS) {
+        float p = __fmul_rn(expf(__fsub_rn(line[c], m)), inv);
+        if (c == l) p = __fsub_rn(p, 1.0f);
+        const float v = __fmul_rn(p, scale);
+        drow[c] = ACC ? BinaryFn<kOpAddFinite, float>::apply(drow[c], v) : v;
+    }
+}
+
+}  // namespace
+
+int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, const void* x, const void* y, void* out,
+                          int accumulate, cudaStream_t st) {
+    switch (dtype) {
+    case CTB_F32: return launch_typed<float>(kind, p, g, x, y, out, accumulate, st);
+    case CTB_F64: return launch_typed<double>(kind, p, g, x, y, out, accumulate, st);
+    }
+    return set_error(CTB_ERR_DTYPE, "backward chain: only Float32 and Double64 gradients are supported");
+}
+
+int launch_ce_forward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
+                           int64_t classes, float* nll, int32_t* bad, cudaStream_t st) {
+    if (rows == 0) return CTB_OK;
+    if (classes <= 1024) ce_forward_rows_kernel<32><<<(unsigned)ceil_div(rows, 8), 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
+    else ce_forward_rows_kernel<256><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
+    return cuda_error(cudaGetLastError(), "cross-entropy rows launch");
+}
+
+int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
+                            int64_t classes, float scale, float* dx, int64_t dx_stride, int accumulate, int32_t* bad,
+                            cudaStream_t st) {
+    if (rows == 0) return CTB_OK;
+    const unsigned warp_grid = (unsigned)ceil_div(rows, 8);
+    if (classes <= 1024) {
+        if (accumulate) ce_backward_rows_kernel<32, true><<<warp_grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        else ce_backward_rows_kernel<32, false><<<warp_grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+    } else {
+        if (accumulate) ce_backward_rows_kernel<256, true><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        else ce_backward_rows_kernel<256, false><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+    }
+    return cuda_error(cudaGetLastError(), "cross-entropy backward launch");
+}
+
+}  // namespace ctb

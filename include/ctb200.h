@@ -271,6 +271,42 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
  * Intermediate sums live in the library's per-device workspace (see ctb_reduce). */
 int ctb_accumulate_grad(const ctb_view* grad, const ctb_view* src, void* stream);
 
+/* Backward bodies the reference spells as operator chains, one pass each.
+ * GradDiv::backward, src/core/autograd.cpp:188-202, for out = a / b with incoming gradient `grad`:
+ *   grad_a = grad / b                                   (div)
+ *   grad_b = -((grad * a) / ((b * b) + 1e-6))           (mul, mul, add_scalar, div, mul_scalar)
+ * GradTanh::backward, src/core/autograd.cpp:434-438, for out = tanh(t):
+ *   grad_t = grad * (1 / (cosh t * cosh t))             (cosh, mul, div_scalar_rev, mul)
+ * with the chain's rounding points kept (every operator result rounded to the dtype; cosh is the
+ * double-precision libm function rounded once, so tanh_backward agrees to ~1e-7).  a, b, t and
+ * grad broadcast against the output's shape; either of grad_a / grad_b may be NULL.
+ * accumulate == 0: the outputs are fresh contiguous tensors of the broadcast shape (feed them to
+ * ctb_accumulate_grad when a broadcast dim has to be folded).  accumulate != 0: the outputs are
+ * existing gradient buffers of that shape (any strides) and the result is ADDED into them, NaN /
+ * infinite values skipped, which is accumulate_grad's rule (src/core/autograd.cpp:139-151) —
+ * the whole backward step of a same-shape division is then two kernels.  Float32 / Double64. */
+int ctb_div_backward(const ctb_view* grad, const ctb_view* a, const ctb_view* b, const ctb_view* grad_a,
+                     const ctb_view* grad_b, int accumulate, void* stream);
+int ctb_tanh_backward(const ctb_view* grad, const ctb_view* t, const ctb_view* grad_t, int accumulate,
+                      void* stream);
+
+/* Loss::CrossEntropy, src/neuralnet/loss.cpp:90-118: logits [Batch, Classes] (Float32, classes
+ * contiguous), labels: one Int32 class index per row in a [Batch] or [Batch, 1] view (negative
+ * values count from the end, like Tensor::gather's indices).  loss (one Float32 element) =
+ * mean (mean != 0) or sum over the rows of -(log_softmax(logits)[row, label]) — the chain
+ * max -> sub -> exp -> sum -> ln -> sub -> gather -> mul_scalar(-1) -> mean in one pass over the
+ * logits plus a reduction of Batch values.  A label outside the row sets *bad (one int32 in device
+ * memory, may be NULL; cleared on `stream` first) and contributes 0; the reference throws there.
+ * GradCrossEntropy::backward, src/neuralnet/loss.cpp:319-370:
+ *   grad_logits[row, c] = (softmax(logits)[row, c] - (c == label[row])) * grad_scale
+ * where grad_scale is the loss's incoming gradient, already divided by Batch for the mean
+ * reduction (the reference does that division on the host, :337-340).  accumulate as above.
+ * Uses the library's per-device workspace (see ctb_reduce). */
+int ctb_cross_entropy(const ctb_view* logits, const ctb_view* labels, int mean, const ctb_view* loss,
+                      int32_t* bad, void* stream);
+int ctb_cross_entropy_backward(const ctb_view* logits, const ctb_view* labels, double grad_scale,
+                               const ctb_view* grad_logits, int accumulate, int32_t* bad, void* stream);
+
 /* matmul_mp, src/core/opsmp.cpp:460-558 (the reference's scalar back-end): out = a x b for 2-d
  * operands or 3-d operands with one leading batch dim (an operand without it, or with batch
  * extent 1, is reused for every batch entry); any strides; `out` contiguous [batch, M, N] (or

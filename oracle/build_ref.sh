@@ -55,6 +55,7 @@ cc avx2_f32      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_f32.cpp"
 cc avx2_d64      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_d64.cpp"
 cc avx512_f32    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_f32.cpp"
 cc avx512_d64    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_d64.cpp"
+cc loss          "$CORE_FLAGS"   "$REF/src/neuralnet/loss.cpp"      # GradCrossEntropy for the shim
 cc ref_shim      "$CORE_FLAGS"   "$HERE/ref_shim.cpp"
 for p in "${pids[@]}"; do wait "$p"; done
 

@@ -902,3 +902,37 @@ void orc_optimizer_step(int kind, float* theta, const float* grad, float* s1, fl
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * GradCrossEntropy::backward, src/neuralnet/loss.cpp:319-370, restated loop for loop:
+ * out[b, c] = (exp(x[b,c] - max_b) / sum_b - (c == label[b])) * scale, with the row maximum
+ * started at -1e9f, libm's single-precision exp, the row sum accumulated in fp32 in class order,
+ * one reciprocal per row (0 when the sum is <= 1e-12) and `scale` = grad_out (/ batch for the
+ * mean reduction) rounded to fp32.  x: contiguous fp32 [batch, classes]; labels: int32[batch].
+ * ---------------------------------------------------------------------------------------- */
+void orc_cross_entropy_backward(const float* x, const int32_t* labels, int64_t batch, int64_t classes, int mean,
+                                double grad_out, float* out) {
+    if (mean) grad_out /= (double)batch;
+    const float scale = (float)grad_out;
+#pragma omp parallel for
+    for (int64_t b = 0; b < batch; ++b) {
+        const float* row = x + b * classes;
+        float* g = out + b * classes;
+        float max_val = -1e9f;
+        for (int64_t c = 0; c < classes; ++c)
+            if (row[c] > max_val) max_val = row[c];
+        float sum_exp = 0.0f;
+        for (int64_t c = 0; c < classes; ++c) {
+            const float v = expf(row[c] - max_val);
+            g[c] = v;
+            sum_exp += v;
+        }
+        const int label = labels[b];
+        const float inv_sum = (sum_exp > 1e-12f) ? (1.0f / sum_exp) : 0.0f;
+        for (int64_t c = 0; c < classes; ++c) {
+            float prob = g[c] * inv_sum;
+            if ((int)c == label) prob -= 1.0f;
+            g[c] = prob * scale;
+        }
+    }
+}

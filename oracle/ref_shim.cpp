@@ -486,6 +486,72 @@ int64_t ref_optimizer_steps(int kind, const float* param, const float* grad, int
     });
 }
 
+// The reference's own backward nodes on same-shape operands (no broadcast fold, so that
+// accumulate_grad needs no dim-wise sum, which the dispatcher cannot do on AVX-512 hosts).
+// Each entry builds the node, gives the result tensor a gradient buffer holding `g`, calls the
+// node's backward and copies the operands' accumulated gradients out (they start at zero).
+namespace {
+Tensor owned_copy(const RefView* v, bool requires_grad) {
+    Tensor src = wrap(v);
+    Tensor t = src.contiguous().clone();
+    t.requires_grad_(requires_grad);
+    return t;
+}
+Tensor result_with_grad(const Tensor& like, const RefView* g) {
+    Tensor self(like.shape(), like._dtype(), true);
+    ensure_grad_buffer(self, true);
+    Tensor gv = wrap(g).contiguous();
+    std::memcpy(self.impl->grad->data->data.get(),
+                (const char*)gv.impl->data->data.get() + gv.impl->offset * dtype_size(gv._dtype()),
+                self.numel() * dtype_size(self._dtype()));
+    return self;
+}
+int64_t emit_grad(const Tensor& t, void* out, int64_t cap) {
+    if (!t.impl->grad) throw std::runtime_error("reference produced no gradient");
+    Tensor g;
+    g.impl = t.impl->grad;
+    return emit(g, out, cap);
+}
+}  // namespace
+
+// GradDiv::backward, src/core/autograd.cpp:188-202
+int64_t ref_div_backward(const RefView* g, const RefView* a, const RefView* b, void* out_a, void* out_b, int64_t cap) {
+    return guarded([&] {
+        Tensor ta = owned_copy(a, true), tb = owned_copy(b, true);
+        GradDiv node(ta, tb);
+        Tensor self = result_with_grad(ta, g);
+        node.backward(self);
+        emit_grad(ta, out_a, cap);
+        return emit_grad(tb, out_b, cap);
+    });
+}
+
+// GradTanh::backward, src/core/autograd.cpp:434-438
+int64_t ref_tanh_backward(const RefView* g, const RefView* t, void* out, int64_t cap) {
+    return guarded([&] {
+        Tensor tt = owned_copy(t, true);
+        GradTanh node(tt);
+        Tensor self = result_with_grad(tt, g);
+        node.backward(self);
+        return emit_grad(tt, out, cap);
+    });
+}
+
+// GradCrossEntropy::backward, src/neuralnet/loss.cpp:319-370.  `grad_out` is the loss's incoming
+// gradient (the node divides it by the batch size itself for reduction == "mean").
+int64_t ref_cross_entropy_backward(const RefView* logits, const RefView* labels, int mean, double grad_out, void* out,
+                                   int64_t cap) {
+    return guarded([&] {
+        Tensor pred = owned_copy(logits, true), target = owned_copy(labels, false);
+        GradCrossEntropy node(pred, target, mean ? "mean" : "sum");
+        Tensor self({1}, DType::Float32, true);
+        ensure_grad_buffer(self, true);
+        write_scalar_at(self.impl->grad->data->data.get(), 0, DType::Float32, grad_out);
+        node.backward(self);
+        return emit_grad(pred, out, cap);
+    });
+}
+
 // Wall time (seconds, std::chrono like the reference's own test/time_avx.cpp:11-24) of one
 // benchmark step on contiguous 1-d inputs of n elements: add, mul, exp, relu and the GELU
 // chain, each through the named back-end, results dropped as soon as they exist (the output

@@ -2,7 +2,7 @@
 and the GPU tests.  Every case is a dict:
 
     name, kind ('binary'|'unary'|'reduce'|'copy'|'softmax'|'layernorm'|'log_softmax'|'gather'|
-    'accgrad'|'optim'|'cat'|'bn_moments'|'bn_apply'|'matmul'), op, views (HostViews),
+    'accgrad'|'optim'|'cat'|'bn_moments'|'bn_apply'|'matmul'|'div_bwd'|'tanh_bwd'|'ce'|'ce_bwd'), op, views (HostViews),
     scalar, dim, causal, exact (bit-exact vs tolerance), path (reference back-end that defines it)
 
 Inputs are seeded; the golden file stores them anyway so it does not depend on numpy's RNG.
@@ -237,6 +237,43 @@ def all_cases():
     add(name="accgrad_i32", kind="accgrad", op=0, views=[HostView.contig(_rng(47).integers(-9, 9, (9,)).astype(np.int32)), Ai])
     add(name="accgrad_f64", kind="accgrad", op=0, views=[HostView.contig(_rng(48).standard_normal((6,))), Ad], exact=False)
 
+    # ---- backward bodies: views = [incoming gradient, forward operands...]; op 0 -> grad of a, 1 -> grad of b.
+    # Same-shape operands are pinned by the reference's own GradDiv / GradTanh nodes; the broadcast cases by
+    # the same operator chain spelled with the reference's back-end functions.
+    bg = HostView.contig(_n(76, (37, 53)))
+    ba = HostView.contig(_n(77, (37, 53), 2.0))
+    bb = HostView.contig(np.where(np.abs(_n(78, (37, 53))) < 0.05, np.float32(0.05), _n(78, (37, 53))).astype(np.float32))
+    brow = HostView.contig(_u(79, (1, 53), 0.5, 2.0))
+    bcol = HostView.contig(_u(80, (37, 1), -2.0, -0.5))
+    for which in (0, 1):
+        nm = "ab"[which]
+        add(name=f"divbwd_{nm}_same", kind="div_bwd", op=which, views=[bg, ba, bb], exact=True)
+        add(name=f"divbwd_{nm}_row_b", kind="div_bwd", op=which, views=[bg, ba, brow], exact=True)
+        add(name=f"divbwd_{nm}_col_a", kind="div_bwd", op=which, views=[bg, bcol, bb], exact=True)
+        add(name=f"divbwd_{nm}_transposed", kind="div_bwd", op=which,
+            views=[HostView.contig(_n(81, (53, 37))).permute([1, 0]), ba, bb], exact=True)
+        add(name=f"divbwd_{nm}_special", kind="div_bwd", op=which,
+            views=[HostView.contig(np.repeat(SPECIAL_F32, SPECIAL_F32.size).reshape(SPECIAL_F32.size, -1)),
+                   HostView.contig(SPECIAL_F32[::-1].copy()), HostView.contig(SPECIAL_F32)], exact=True)
+        add(name=f"divbwd_{nm}_f64", kind="div_bwd", op=which,
+            views=[HostView.contig(_rng(82).standard_normal((5, 6))), Ad, HostView.contig(_rng(83).standard_normal((6,)) + 3.0)], exact=True)
+    add(name="tanhbwd_same", kind="tanh_bwd", op=0, views=[bg, ba], exact=False)
+    add(name="tanhbwd_row", kind="tanh_bwd", op=0, views=[bg, brow], exact=False)
+    add(name="tanhbwd_large_arguments", kind="tanh_bwd", op=0,
+        views=[HostView.contig(np.ones(12, np.float32)), HostView.contig(np.array([0, 1e-3, 0.5, -0.5, 5, -5, 20, -20, 44, 60, 89, -100], np.float32))], exact=False)
+    # ---- cross-entropy rows: views = [logits [B,C], labels int32 [B,1]]; op 1 = mean, 0 = sum --------------------
+    ce_logits = HostView.contig(_n(84, (33, 10), 3.0))
+    ce_labels = HostView.contig(_rng(85).integers(0, 10, (33, 1)).astype(np.int32))
+    wide_logits = HostView.contig(_n(86, (7, 3000), 2.0))
+    wide_labels = HostView.contig(_rng(87).integers(0, 3000, (7, 1)).astype(np.int32))
+    for red, rn in ((1, "mean"), (0, "sum")):
+        add(name=f"ce_{rn}", kind="ce", op=red, views=[ce_logits, ce_labels], exact=False, path=ol.PATH_AVX512)
+        add(name=f"ce_{rn}_wide", kind="ce", op=red, views=[wide_logits, wide_labels], exact=False, path=ol.PATH_AVX512)
+        add(name=f"cebwd_{rn}", kind="ce_bwd", op=red, views=[ce_logits, ce_labels], scalar=1.0, exact=False)
+        add(name=f"cebwd_{rn}_wide", kind="ce_bwd", op=red, views=[wide_logits, wide_labels], scalar=0.37, exact=False)
+    add(name="ce_mean_row_slice", kind="ce", op=1, views=[HostView.contig(_n(88, (33, 16))).narrow(1, 3, 10), ce_labels], exact=False,
+        path=ol.PATH_AVX512)
+
     # ---- cat: views = the inputs, dim = the cat dim ------------------------------------------------------------
     add(name="cat_dim0", kind="cat", op=0, views=[A, A.narrow(0, 3, 11), B], dim=0)
     add(name="cat_dim1", kind="cat", op=0, views=[A, C, A.narrow(1, 1, 5)], dim=1)
@@ -322,6 +359,20 @@ def run_case(impl, case):
         return impl.batchnorm_apply(v[0].numpy(), p[0], p[1], p[2], p[3], case["scalar"])
     if k == "cat":
         return impl.cat(v, case["dim"])
+    if k == "div_bwd":
+        if is_ref:
+            if v[0].shape == v[1].shape == v[2].shape and v[0].dtype == ol.F32:     # the reference's own node
+                return impl.div_backward(v[0], v[1], v[2])[case["op"]]
+            return ol.Oracle.div_backward(impl, v[0], v[1], v[2])[case["op"]]     # its back-end functions, same chain
+        return impl.div_backward(v[0], v[1], v[2])[case["op"]]
+    if k == "tanh_bwd":
+        if is_ref and v[0].shape != v[1].shape:
+            return ol.Oracle.tanh_backward(impl, v[0], v[1])
+        return impl.tanh_backward(v[0], v[1])
+    if k == "ce":
+        return impl.cross_entropy(v[0], v[1], bool(case["op"]))
+    if k == "ce_bwd":
+        return impl.cross_entropy_backward(v[0], v[1], bool(case["op"]), case["scalar"])
     if k == "optim":
         return impl.optimizer_steps(case["op"], v[0].numpy(), v[1].numpy(), case["dim"], case["scalar"])
     raise ValueError(k)

@@ -38,7 +38,7 @@ def assert_bits_equal(got, ref: np.ndarray, what="", nan_payload_free=True):
                              f"got {got.reshape(-1)[i]!r} want {ref.reshape(-1)[i]!r}")
 
 
-def assert_close(got, ref: np.ndarray, rtol=1e-5, what=""):
+def assert_close(got, ref: np.ndarray, rtol=1e-5, what="", atol=0.0):
     got = got.detach().cpu().numpy() if isinstance(got, torch.Tensor) else got
     assert got.shape == ref.shape, f"{what}: shape {got.shape} != {ref.shape}"
-    np.testing.assert_allclose(got, ref, rtol=rtol, atol=0, err_msg=what, equal_nan=True)
+    np.testing.assert_allclose(got, ref, rtol=rtol, atol=atol, err_msg=what, equal_nan=True)

@@ -203,6 +203,9 @@ class Oracle:
         L.orc_optimizer_step.restype = None
         L.orc_optimizer_step.argtypes = ([ctypes.c_int] + [ctypes.c_void_p] * 4 + [ctypes.c_int64] +
                                          [ctypes.c_double] * 6 + [ctypes.c_int])
+        L.orc_cross_entropy_backward.restype = None
+        L.orc_cross_entropy_backward.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                                 ctypes.c_int, ctypes.c_double, ctypes.c_void_p]
         L.orc_unary_sweep_f32.restype = None
         L.orc_unary_sweep_f32.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                           ctypes.c_int64, ctypes.c_double, ctypes.c_void_p,
@@ -333,6 +336,40 @@ class Oracle:
                                    beta1, beta2, eps, t, weight_decay, 1 if kind == 2 else 0)
         return p
 
+    # ---- backward bodies and the cross-entropy rows: the reference's operator chains, spelled with
+    # ---- the primitives above (each pinned to the reference on its own) ----------------------------
+    def div_backward(self, g: HostView, a: HostView, b: HostView):
+        """GradDiv::backward, src/core/autograd.cpp:188-202 -> (g / b, -((g * a) / ((b * b) + 1e-6)))."""
+        c = HostView.contig
+        da = self.binary(DIV, g, b)
+        num, den = self.binary(MUL, g, a), self.binary(MUL, b, b)
+        den_safe = self.unary(ADD_S, c(den), 1e-6)
+        res = self.binary(DIV, c(num), c(den_safe))
+        return da, self.unary(MUL_S, c(res), -1.0)
+
+    def tanh_backward(self, g: HostView, t: HostView):
+        """GradTanh::backward, src/core/autograd.cpp:434-438: g * (1 / (cosh t * cosh t))."""
+        c = HostView.contig
+        ch = c(self.unary(COSH, t))
+        inv = self.unary(RDIV_S, c(self.binary(MUL, ch, ch)), 1.0)
+        return self.binary(MUL, g, c(inv))
+
+    def cross_entropy(self, logits: HostView, labels: HostView, mean: bool = True):
+        """Loss::CrossEntropy, src/neuralnet/loss.cpp:90-118: log-softmax chain, gather, * -1, mean | sum."""
+        c = HostView.contig
+        logp = c(self.log_softmax(logits))
+        idx = c(labels.numpy().reshape(-1, 1))
+        nll = self.unary(MUL_S, c(self.gather(logp, 1, idx)), -1.0)
+        return self.reduce(MEAN if mean else SUM, c(nll.reshape(-1)), -1)
+
+    def cross_entropy_backward(self, logits: HostView, labels: HostView, mean: bool = True, grad_out: float = 1.0):
+        x = np.ascontiguousarray(logits.numpy(), np.float32)
+        lab = np.ascontiguousarray(labels.numpy().reshape(-1), np.int32)
+        out = np.empty_like(x)
+        self.lib.orc_cross_entropy_backward(x.ctypes.data, lab.ctypes.data, x.shape[0], x.shape[1], int(mean),
+                                            float(grad_out), out.ctypes.data)
+        return out
+
     def sweep(self, op, start: int, step: int, count: int, scalar: float = 0.0):
         xin = np.empty(count, np.float32)
         out = np.empty(count, np.float32)
@@ -383,6 +420,12 @@ class Reference:
         L.ref_cat.argtypes = [ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int, vd, i64]
         L.ref_optimizer_steps.restype = i64
         L.ref_optimizer_steps.argtypes = ([ctypes.c_int, vd, vd, i64, ctypes.c_int] + [ctypes.c_double] * 5 + [vd])
+        L.ref_div_backward.restype = i64
+        L.ref_div_backward.argtypes = [vp, vp, vp, vd, vd, i64]
+        L.ref_tanh_backward.restype = i64
+        L.ref_tanh_backward.argtypes = [vp, vp, vd, i64]
+        L.ref_cross_entropy_backward.restype = i64
+        L.ref_cross_entropy_backward.argtypes = [vp, vp, ctypes.c_int, ctypes.c_double, vd, i64]
         L.ref_bench_step.restype = ctypes.c_double
         L.ref_bench_step.argtypes = [ctypes.c_int, vd, vd, i64]
         feats = L.ref_cpu_features()
@@ -484,6 +527,33 @@ class Reference:
         out = np.empty_like(p)
         return self._check(self.lib.ref_optimizer_steps(kind, p.ctypes.data, g.ctypes.data, p.size, steps, lr,
                                                         beta1, beta2, eps, weight_decay, out.ctypes.data), out)
+
+    def div_backward(self, g, a, b):
+        """The reference's own GradDiv node on same-shape operands -> (grad of a, grad of b)."""
+        oa, ob = np.empty(a.shape, NP_DTYPES[a.dtype]), np.empty(b.shape, NP_DTYPES[b.dtype])
+        self._check(self.lib.ref_div_backward(g.cview(), a.cview(), b.cview(), oa.ctypes.data, ob.ctypes.data, ob.nbytes), ob)
+        return oa, ob
+
+    def tanh_backward(self, g, t):
+        out = np.empty(t.shape, NP_DTYPES[t.dtype])
+        return self._check(self.lib.ref_tanh_backward(g.cview(), t.cview(), out.ctypes.data, out.nbytes), out)
+
+    def cross_entropy(self, logits, labels, mean=True):
+        """Loss::CrossEntropy's chain through the reference's own functions (its dispatcher throws
+        for the dim-wise max/sum on AVX-512 hosts, so the back-end functions are called directly)."""
+        c = HostView.contig
+        logp = c(self.log_softmax(logits))
+        nll = self.unary(MUL_S, c(self.gather(logp, 1, c(labels.numpy().reshape(-1, 1)))), -1.0)
+        flat = c(nll.reshape(-1))
+        total = self.reduce(SUM, flat, 0)
+        return self.unary(MUL_S, c(total), 1.0 / flat.numel) if mean else total
+
+    def cross_entropy_backward(self, logits, labels, mean=True, grad_out=1.0):
+        """The reference's own GradCrossEntropy node."""
+        out = np.empty(logits.shape, np.float32)
+        lab = HostView.contig(np.ascontiguousarray(labels.numpy().reshape(-1, 1), np.int32))
+        return self._check(self.lib.ref_cross_entropy_backward(logits.cview(), lab.cview(), int(mean), float(grad_out),
+                                                               out.ctypes.data, out.nbytes), out)
 
     def layernorm(self, x, gamma, beta, eps=1e-5):
         out = np.empty(x.shape, np.float32)

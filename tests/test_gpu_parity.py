@@ -50,6 +50,15 @@ def run_gpu(ct, case):
         return ct.batchnorm_apply(dv[0], p[0], p[1], p[2], p[3], case["scalar"])
     if k == "cat":
         return ct.cat(dv, case["dim"])
+    if k == "div_bwd":
+        return ct.div_backward(dv[0], dv[1], dv[2], want_a=case["op"] == 0, want_b=case["op"] == 1)[case["op"]]
+    if k == "tanh_bwd":
+        return ct.tanh_backward(dv[0], dv[1])
+    if k == "ce":
+        return ct.cross_entropy(dv[0], dv[1], bool(case["op"]))
+    if k == "ce_bwd":
+        batch = case["views"][0].shape[0]
+        return ct.cross_entropy_backward(dv[0], dv[1], case["scalar"] / (batch if case["op"] else 1))
     if k == "optim":
         p = torch.from_numpy(case["views"][0].numpy()).cuda()
         g = torch.from_numpy(case["views"][1].numpy()).cuda()
@@ -79,8 +88,10 @@ def test_case_vs_oracle_and_golden(ct, oracle, case):
         assert_bits_equal(got, ref, case["name"])
         assert C.digest(got) == gold["digest"], f"{case['name']}: differs from the reference's golden output"
     else:
-        assert_close(got, ref, RTOL, case["name"])
-        assert_close(got, gold["out"], RTOL, case["name"] + " (golden)")
+        # softmax(x) - 1 at the label cancels: an absolute floor of a few fp32 ulps of 1.0 for that kind
+        atol = 3e-7 * abs(case["scalar"]) if case["kind"] == "ce_bwd" else 0.0
+        assert_close(got, ref, RTOL, case["name"], atol)
+        assert_close(got, gold["out"], RTOL, case["name"] + " (golden)", atol)
 
 
 def test_causal_flag(ct, oracle):
@@ -254,6 +265,59 @@ def test_output_overlapping_an_input_is_refused(ct):
     buf = torch.zeros(2, 64, 64, device="cuda")
     ct.binary(ct.ADD, buf[0], b, out=buf[1])
     assert torch.all(buf[1] == 1)
+
+
+def test_backward_chains_accumulate_into_gradient_buffers(ct, oracle):
+    """accumulate = 1: the chain's result is added into an existing gradient buffer, NaN / infinite
+    contributions skipped (accumulate_grad's rule); strided buffers and 1 GiB operands included."""
+    rng = np.random.default_rng(21)
+    g = HostView.contig(rng.standard_normal((300, 257)).astype(np.float32))
+    a = HostView.contig(rng.standard_normal((300, 257)).astype(np.float32))
+    bnp = rng.standard_normal((300, 257)).astype(np.float32)
+    bnp[5, 7] = 0.0                                     # g / 0 -> inf: skipped
+    b = HostView.contig(bnp)
+    start_a = rng.standard_normal((300, 257)).astype(np.float32)
+    start_b = rng.standard_normal((300, 257)).astype(np.float32)
+    da, db = oracle.div_backward(g, a, b)
+    want_a = oracle.accumulate_grad(start_a, HostView.contig(da))
+    want_b = oracle.accumulate_grad(start_b, HostView.contig(db))
+    buf_a, buf_b = torch.from_numpy(start_a).cuda(), torch.from_numpy(start_b).cuda()
+    ct.div_backward(to_device(g), to_device(a), to_device(b), out_a=buf_a, out_b=buf_b, accumulate=True)
+    assert_bits_equal(buf_a, want_a, "grad_a += g / b")
+    assert_bits_equal(buf_b, want_b, "grad_b += chain")
+    assert buf_a[5, 7].item() == start_a[5, 7]
+    # a transposed gradient buffer (strided kernel)
+    tbuf = torch.from_numpy(np.ascontiguousarray(start_a.T)).cuda()
+    ct.tanh_backward(to_device(g), to_device(a), out=ct.DView.of(tbuf).permute([1, 0]), accumulate=True)
+    want_t = oracle.accumulate_grad(start_a, HostView.contig(oracle.tanh_backward(g, a)))
+    assert_close(tbuf.cpu().numpy().T, want_t, RTOL, "tanh backward into a transposed buffer", atol=1e-7)
+    # cross-entropy gradient added to an existing buffer
+    logits = HostView.contig(rng.standard_normal((64, 1500)).astype(np.float32) * 4)
+    labels = HostView.contig(rng.integers(0, 1500, (64, 1)).astype(np.int32))
+    start = rng.standard_normal((64, 1500)).astype(np.float32)
+    buf = torch.from_numpy(start).cuda()
+    ct.cross_entropy_backward(to_device(logits), to_device(labels), 1.0 / 64, out=buf, accumulate=True)
+    want = start + oracle.cross_entropy_backward(logits, labels, True, 1.0)
+    assert_close(buf, want, RTOL, "ce backward accumulate", atol=1e-6)
+    # a label outside the row raises the flag instead of a device-side error
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lab_bad = labels.numpy().copy()
+    lab_bad[3, 0] = 1500
+    ct.cross_entropy(to_device(logits), to_device(HostView.contig(lab_bad)), True, bad=bad)
+    assert bad.item() == 1
+    ct.cross_entropy(to_device(logits), to_device(labels), True, bad=bad)
+    assert bad.item() == 0
+
+
+@pytest.mark.parametrize("rows,classes", [(4096, 1000), (512, 50257), (65536, 10)])
+def test_cross_entropy_sizes(ct, oracle, rows, classes):
+    rng = np.random.default_rng(rows + classes)
+    logits = HostView.contig((rng.standard_normal((rows, classes)) * 3).astype(np.float32))
+    labels = HostView.contig(rng.integers(0, classes, (rows, 1)).astype(np.int32))
+    got = ct.cross_entropy(to_device(logits), to_device(labels), True)
+    assert_close(got, oracle.cross_entropy(logits, labels, True), RTOL, "loss")
+    grad = ct.cross_entropy_backward(to_device(logits), to_device(labels), 1.0 / rows)
+    assert_close(grad, oracle.cross_entropy_backward(logits, labels, True, 1.0), RTOL, "gradient", atol=3e-7 / rows)
 
 
 def test_argmax_ties_prefer_first_index(ct, oracle):
