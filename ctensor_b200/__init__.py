@@ -49,6 +49,8 @@ EXPORTED_SYMBOLS = [
     "ctb_pool_alloc_managed", "ctb_pool_free_managed", "ctb_pool_trim", "ctb_pool_set_limit", "ctb_pool_stats",
     "ctb_prefetch_managed",
     "ctb_div_backward", "ctb_tanh_backward", "ctb_cross_entropy", "ctb_cross_entropy_backward",
+    "ctb_shard_range", "ctb_comm_init_all", "ctb_comm_size", "ctb_comm_device", "ctb_comm_stream", "ctb_comm_sync",
+    "ctb_comm_destroy", "ctb_allreduce", "ctb_full_reduce_sharded",
 ]
 
 
@@ -125,6 +127,13 @@ def lib() -> ctypes.CDLL:
     L.ctb_pool_set_limit.argtypes = [i32, ctypes.c_size_t]
     L.ctb_pool_stats.argtypes = [i32, ctypes.POINTER(PoolInfo)]
     L.ctb_prefetch_managed.argtypes = [vd, ctypes.c_size_t, i32, vd]
+    L.ctb_shard_range.argtypes = [i64, i32, i32, ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    L.ctb_comm_init_all.argtypes = [i32, ctypes.POINTER(i32)]
+    L.ctb_comm_device.argtypes = [i32]
+    L.ctb_comm_stream.argtypes = [i32]
+    L.ctb_comm_stream.restype = vd
+    L.ctb_allreduce.argtypes = [ctypes.POINTER(vd), ctypes.c_size_t, i32, i32]
+    L.ctb_full_reduce_sharded.argtypes = [i32, ctypes.POINTER(vp), i64, ctypes.POINTER(vp)]
     L.ctb_div_backward.argtypes = [vp, vp, vp, vp, vp, i32, vd]
     L.ctb_tanh_backward.argtypes = [vp, vp, vp, i32, vd]
     L.ctb_cross_entropy.argtypes = [vp, vp, i32, vp, vd, vd]

@@ -220,6 +220,34 @@ int ctb_reduce_full_partial(int op, const ctb_view* a, double* partial, void* st
 int ctb_finalize_full(int op, const double* partial, int64_t total_count,
                       const ctb_view* out, void* stream);
 
+/* ---- several GPUs in one process -----------------------------------------------------------
+ * (No counterpart in the reference, which is CPU-only; its Device type, src/core/device.h:5-25,
+ * names a GPU by index and that is what the `devices` lists here hold.)
+ * The path shards along the leading dim: ctb_shard_range gives shard `index` of `parts` of a dim
+ * of `total` elements ([lo, hi), sizes differing by at most one).  Elementwise, broadcast and
+ * row-wise operators then run per shard with no communication.  ctb_comm_init_all builds one
+ * NCCL communicator over `ndev` GPUs (devices == NULL: GPUs 0..ndev-1; ndev <= 0: all visible)
+ * with one stream per GPU; NCCL is loaded at that moment (libnccl.so.2, or the library named by
+ * the environment variable CTB_NCCL_LIBRARY).  One communicator per process; calling it again
+ * replaces the communicator.
+ * ctb_allreduce: in-place all-reduce (op = CTB_SUM / CTB_MAX / CTB_MIN) of `count` elements at
+ * buffers[r] on the GPU of rank r, queued on the communicator's streams (ctb_comm_stream(r) lets
+ * the caller order its own kernels before it; ctb_comm_sync waits for all of them).
+ * ctb_full_reduce_sharded: shards[r] (on the GPU of rank r) are the leading-dim shards of one
+ * tensor; every GPU reduces its shard to an fp64 partial, ONE all-reduce of a double combines
+ * them, every GPU writes the result (outs[r], one element) with the reference's rounding —
+ * `total_count` is the element count mean divides by.  Returns when all GPUs are done. */
+int   ctb_shard_range(int64_t total, int parts, int index, int64_t* lo, int64_t* hi);
+int   ctb_comm_init_all(int ndev, const int* devices);
+int   ctb_comm_size(void);
+int   ctb_comm_device(int rank);
+void* ctb_comm_stream(int rank);
+int   ctb_comm_sync(void);
+int   ctb_comm_destroy(void);
+int   ctb_allreduce(void* const* buffers, size_t count, int dtype, int op);
+int   ctb_full_reduce_sharded(int op, const ctb_view* const* shards, int64_t total_count,
+                              const ctb_view* const* outs);
+
 /* ---- fused rows ----------------------------------------------------------------------------
  * Softmax over the last dim = the chain max -> sub -> exp -> sum -> div of
  * src/neuralnet/loss.cpp:97-101 in one pass over the rows.  `mask` (may be NULL) is first added

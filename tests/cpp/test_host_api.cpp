@@ -8,6 +8,7 @@
 #include <string>
 
 #include "ctb_host.h"
+#include "../../include/ctb200.h"
 #include "ops_dispatch.h"
 #include "opsmp.h"
 
@@ -198,6 +199,32 @@ int main() {
     Tensor z = mul_scalar(y, 2.0);
     CHECK(z.impl->grad_fn->op == "mul_scalar" && z.impl->grad_fn->scalar == 2.0);
     CHECK(!add(a, b).requires_grad() && !max(w).requires_grad());
+
+    // Device tags (src/core/device.h:5-25): a tensor lives on the GPU its tag names, results stay there
+    CHECK(a.device() == Device(DeviceType::CUDA, ctb_host::device()));
+    CHECK((a + b).device() == a.device());
+    CHECK(a.to(Device(DeviceType::CUDA, ctb_host::device())).impl == a.impl);        // already there: no copy
+    if (ctb_device_count() >= 2) {
+        Tensor far = a.to(Device(DeviceType::CUDA, 1));
+        CHECK(far.device() == Device(DeviceType::CUDA, 1));
+        Tensor far_sum = far + b.to(Device(DeviceType::CUDA, 1));
+        CHECK(far_sum.device() == Device(DeviceType::CUDA, 1));
+        CHECK_NEAR(far_sum[1][1], 5.0, 1e-6);
+        CHECK_NEAR(sum(far).item<double>(), 8.0, 1e-6);
+        CHECK_THROWS(far + b, std::runtime_error, "add: tensors must be on same device");
+    } else {
+        CHECK_THROWS(a.to(Device(DeviceType::CUDA, 1)), std::runtime_error, "Tensor::to: no such CUDA device");
+    }
+    // operator results reuse pooled storage: the second a + b takes the block the first one freed
+    const void* first = (a + b).impl->data->data.get();
+    const void* second = (a + b).impl->data->data.get();
+    CHECK(first == second);
+    // a mean that carries a gradient is the reference's two operators (sum, mul_scalar)
+    Tensor mw = mean(w, 1);
+    CHECK(mw.impl->grad_fn && mw.impl->grad_fn->op == "mul_scalar" && mw.impl->grad_fn->scalar == 0.5);
+    CHECK_NEAR(mw[0], 3.0, 1e-6);
+    CHECK(sum(t, -2).numel() == 2);                       // negative dims other than -1 wrap
+    CHECK_THROWS(sum(t, -5), std::out_of_range, "reduction: dim out of range");
 
     std::printf("ALL PASSED (%d checks)\n", g_checks);
     return 0;

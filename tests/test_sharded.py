@@ -97,3 +97,93 @@ def test_empty_shard_contributes_identity():
     t = torch.zeros(0)
     assert sharded.full_reduce(ct.MAX, t, 0, partial_fn=_host_partial,
                                finalize_fn=lambda op, p, n: p).item() == float("-inf")
+
+
+# ---- the C ABI's own multi-GPU entry points (single process) --------------------------------------------
+def test_c_abi_shard_ranges_match_the_python_ones():
+    import ctypes
+    L = ct.lib()
+    lo, hi = ctypes.c_int64(), ctypes.c_int64()
+    for n in (0, 1, 7, 8, 1000, 2 ** 31 + 5):
+        for parts in (1, 2, 3, 8):
+            for r in range(parts):
+                assert L.ctb_shard_range(n, parts, r, ctypes.byref(lo), ctypes.byref(hi)) == 0
+                assert (lo.value, hi.value) == sharded.shard_range(n, parts, r)
+    assert L.ctb_shard_range(10, 2, 2, ctypes.byref(lo), ctypes.byref(hi)) == 5
+    assert L.ctb_shard_range(10, 0, 0, ctypes.byref(lo), ctypes.byref(hi)) == 5
+    assert L.ctb_shard_range(10, 2, 0, None, ctypes.byref(hi)) == 1
+
+
+def test_c_abi_collectives_need_a_communicator_and_a_gpu():
+    import ctypes
+    L = ct.lib()
+    assert L.ctb_comm_size() == 0
+    bufs = (ctypes.c_void_p * 1)(None)
+    assert L.ctb_allreduce(bufs, 4, ct.F64, ct.SUM) == 5
+    assert b"no communicator" in L.ctb_last_error()
+    assert L.ctb_comm_sync() == 5
+    assert L.ctb_comm_destroy() == 0                       # nothing to destroy is not an error
+    if L.ctb_device_count() == 0:
+        assert L.ctb_comm_init_all(2, None) == 6           # CTB_ERR_CUDA: no CPU fallback
+        assert b"no CUDA device" in L.ctb_last_error()
+
+
+def _c_abi_sharded_reduce(ndev, oracle):
+    """ctb_comm_init_all over `ndev` GPUs; a tensor sharded along dim 0 across them."""
+    import ctypes
+    import oracle_lib as ol
+    from oracle_lib import HostView
+    L = ct.lib()
+    ct.check(L.ctb_comm_init_all(ndev, None))
+    try:
+        assert L.ctb_comm_size() == ndev
+        n = (1 << 22) + 11
+        x = (np.random.default_rng(8).standard_normal(n) * 2 + 0.1).astype(np.float32)
+        shards, outs = [], []
+        for r in range(ndev):
+            lo, hi = sharded.shard_range(n, ndev, r)
+            dev = L.ctb_comm_device(r)
+            shards.append(torch.from_numpy(x[lo:hi]).to(f"cuda:{dev}"))
+            outs.append(torch.empty(1, device=f"cuda:{dev}"))
+        torch.cuda.synchronize()
+        vp = ctypes.POINTER(ct.View)
+        for op in (ct.SUM, ct.MEAN, ct.MAX, ct.MIN):
+            sv = [ct.DView.of(s).cview() for s in shards]
+            ov = [ct.DView.of(o).cview() for o in outs]
+            ct.check(L.ctb_full_reduce_sharded(op, (vp * ndev)(*[ctypes.pointer(v) for v in sv]), n,
+                                               (vp * ndev)(*[ctypes.pointer(v) for v in ov])))
+            ref = oracle.reduce(op, HostView.contig(x), -1)
+            for o in outs:                                   # every GPU holds the same, correct value
+                if op in (ct.MAX, ct.MIN):
+                    assert o.cpu().numpy().view(np.uint32)[0] == ref.view(np.uint32)[0]
+                else:
+                    np.testing.assert_allclose(o.cpu().numpy(), ref, rtol=1e-5)
+            assert all(torch.equal(outs[0].cpu(), o.cpu()) for o in outs)
+        # a dim-0 reduction of row shards: fp64 partial rows, one all-reduce of 4096 doubles
+        m = x[: 1 << 22].reshape(-1, 4096)
+        parts = []
+        for r in range(ndev):
+            lo, hi = sharded.shard_range(m.shape[0], ndev, r)
+            dev = L.ctb_comm_device(r)
+            parts.append(torch.from_numpy(m[lo:hi].astype(np.float64).sum(0)).to(f"cuda:{dev}"))
+        torch.cuda.synchronize()
+        ptrs = (ctypes.c_void_p * ndev)(*[p.data_ptr() for p in parts])
+        ct.check(L.ctb_allreduce(ptrs, 4096, ct.F64, ct.SUM))
+        ct.check(L.ctb_comm_sync())
+        for p in parts:
+            np.testing.assert_allclose(p.cpu().numpy(), m.astype(np.float64).sum(0), rtol=1e-12)
+    finally:
+        ct.check(L.ctb_comm_destroy())
+    assert L.ctb_comm_size() == 0
+
+
+@pytest.mark.gpu
+def test_c_abi_sharded_full_reduce_on_one_gpu(oracle):
+    _c_abi_sharded_reduce(1, oracle)
+
+
+@pytest.mark.gpu
+def test_c_abi_sharded_full_reduce_on_all_gpus(oracle):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _c_abi_sharded_reduce(torch.cuda.device_count(), oracle)
