@@ -220,9 +220,9 @@ int main() {
     const void* second = (a + b).impl->data->data.get();
     CHECK(first == second);
     // a mean that carries a gradient is the reference's two operators (sum, mul_scalar)
-    Tensor mw = mean(w, 1);
-    CHECK(mw.impl->grad_fn && mw.impl->grad_fn->op == "mul_scalar" && mw.impl->grad_fn->scalar == 0.5);
-    CHECK_NEAR(mw[0], 3.0, 1e-6);
+    Tensor mean_w = mean(w, 1);
+    CHECK(mean_w.impl->grad_fn && mean_w.impl->grad_fn->op == "mul_scalar" && mean_w.impl->grad_fn->scalar == 0.5);
+    CHECK_NEAR(mean_w[0], 3.0, 1e-6);
     CHECK(sum(t, -2).numel() == 2);                       // negative dims other than -1 wrap
     CHECK_THROWS(sum(t, -5), std::out_of_range, "reduction: dim out of range");
 
