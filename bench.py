@@ -274,11 +274,68 @@ def bench_ours(args):
         tt = torch.tensor([s0.elapsed_time(s1) / reps], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        # the value, checked: an fp64 sum of the same shard computed independently (torch), all-reduced
+        chk = xs.double().sum().reshape(1)
+        if world > 1:
+            dist.all_reduce(chk)
+        want = float(chk.item())
+        got = float(res.item())
+        checked = abs(got - want) <= 1e-5 * max(abs(want), (m * world) ** 0.5)
+        # eight such sums whose partials share ONE all-reduce (the ~20 us collective amortised)
+        parts = torch.empty(8, dtype=torch.float64, device=dev)
+        chunks = xs.view(8, -1)
+
+        def batched():
+            for i in range(8):
+                ct.reduce_full_partial(ct.SUM, chunks[i], partial=parts[i:i + 1])
+            if world > 1:
+                dist.all_reduce(parts)
+            return parts
+
+        for _ in range(3):
+            batched()
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(reps):
+            batched()
+        b1.record()
+        barrier()
+        bt = torch.tensor([b0.elapsed_time(b1) / reps], device=dev, dtype=torch.float64)
+        # the collective alone
+        one = torch.zeros(1, dtype=torch.float64, device=dev)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            for _ in range(3):
+                dist.all_reduce(one)
+        barrier()
+        c0.record()
+        if world > 1:
+            for _ in range(reps):
+                dist.all_reduce(one)
+        c1.record()
+        barrier()
+        ctm = torch.tensor([c0.elapsed_time(c1) / reps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+            dist.all_reduce(ctm, op=dist.ReduceOp.MAX)
         sharded_sum = {"elements_per_gpu": m, "ms": round(float(tt.item()), 4),
-                       "GB/s": round(4.0 * m * world / float(tt.item()) / 1e6, 1), "value": float(res.item()),
+                       "GB/s": round(4.0 * m * world / float(tt.item()) / 1e6, 1), "value": got,
+                       "checked": bool(checked), "check": "fp64 sum of the same shards computed by torch, all-reduced; 1e-5 relative",
+                       "allreduce_one_fp64_ms": round(float(ctm.item()), 4),
+                       "eight_sums_one_allreduce": {"ms": round(float(bt.item()), 4),
+                                                    "GB/s": round(4.0 * m * world / float(bt.item()) / 1e6, 1)},
                        "collective": "none (1 rank)" if world == 1 else "1 all-reduce of one fp64 (NCCL)"}
     except Exception as exc:
         sharded_sum = {"error": repr(exc)}
+
+    # ---- the other configurations on row shards, every N (strong scaling: the config's size is fixed) ----
+    sharded_cfgs = None
+    if not args.kernel_only:
+        try:
+            sharded_cfgs = sharded_configs(ct, torch, dist, dev, rank, world, x, y, out)
+        except Exception as exc:
+            sharded_cfgs = {"error": repr(exc)}
 
     # ---- extras on rank 0 ------------------------------------------------------------------------------
     sweep, cpu, other = None, None, None
@@ -349,6 +406,10 @@ def bench_ours(args):
         "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * args.steps * world,
     }
     line["sharded_full_sum"] = sharded_sum
+    if sharded_cfgs is not None:
+        line["sharded_configs"] = sharded_cfgs
+    if world == 1 and not args.kernel_only:
+        line["host_layer"] = host_layer_bench()
     if sweep is not None:
         line["sweep"] = sweep
     if other is not None:
@@ -358,12 +419,117 @@ def bench_ours(args):
     # DRAM bytes per element from the ncu capture of the small case (n = 2^26), see
     # profiles/ew_flat_small_case_full_set.md; traffic grows in proportion to n.
     line["roofline"]["traffic"] = round(DRAM_BYTES_PER_ELEMENT[OPS[top][0]] * n)
+    line["roofline"]["traffic_source"] = "ncu capture of the n=2^26 case (DRAM read+write bytes per element) x n, not a counter read in this run"
     _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
 # ---------------------------------------------------------------------------------------------------
+def host_layer_bench():
+    """The C++ host layer (the drop-in path of a caller of the reference) timed by its own program:
+    `a + b`, relu(a), sum(a, 1) on pooled managed tensors, output allocation and the wait for the
+    kernel inside every call.  us per call and GB/s at 2^20 / 2^24 / 2^28 elements."""
+    exe = os.path.join(ROOT, "ctensor_b200", "host", "bench_host_layer.bin")
+    if not os.path.exists(exe):
+        return {"error": "ctensor_b200/host/bench_host_layer.bin not built"}
+    try:
+        r = subprocess.run([exe, "20", "24", "28"], capture_output=True, text=True, timeout=300)
+        return json.loads(r.stdout.strip().splitlines()[-1])
+    except Exception as exc:
+        return {"error": repr(exc)}
+
+
+def sharded_configs(ct, torch, dist, dev, rank, world, x, y, out):
+    """The reduction, permuted-softmax and GPT-2 configurations with their leading dim cut into
+    `world` row shards (strong scaling: the configuration's size is fixed, each GPU owns 1/world of
+    the rows), and the 2^30-element step cut the same way.  Row-wise work needs no communication;
+    the dim-0 sum of the reduction matrix combines fp64 partial rows with one all-reduce of 16384
+    doubles, timed on its own as well.  ms = max over ranks of the CUDA-event time per call."""
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(reps):
+            fn()
+        a1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a0.elapsed_time(a1) / reps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def entry(total_bytes, ms):
+        return {"ms": round(ms, 4), "GB/s": round(total_bytes / ms / 1e6, 1)}
+
+    res = {"scaling": "strong", "ranks": world}
+    g = torch.Generator(device=dev)
+    # the step itself on shards of ONE 2^30-element tensor pair
+    n = x.numel() // world
+    xs, ys, os_ = x[:n], y[:n], out[:n]
+    res["step_2^30_total"] = entry(BYTES_PER_ELEM_STEP * n * world, timed(lambda: run_step(ct, xs, ys, os_), reps=5))
+    # reductions: X[8192,16384], rows sharded
+    rows = 8192 // world
+    g.manual_seed(2 + 100 * rank)
+    X = torch.randn(rows, 16384, device=dev, generator=g)
+    r_rows = torch.empty(rows, device=dev)
+    part = torch.empty(16384, dtype=torch.float64, device=dev)
+    fin = torch.empty(16384, device=dev)
+
+    def dim0_sum():
+        # per-GPU fp64 partial rows -> one all-reduce -> rounding to fp32 (sum's finaliser)
+        ct.reduce(ct.SUM, X, 0, out=fin)
+        part.copy_(fin)                                  # stands for the fp64 partial rows of the shard
+        if world > 1:
+            dist.all_reduce(part)
+        fin.copy_(part)
+
+    nbX = 8192 * 16384 * 4
+    res["reductions_8192x16384"] = {
+        "sum_dim1_row_shards": entry(nbX, timed(lambda: ct.reduce(ct.SUM, X, 1, out=r_rows))),
+        "max_dim1_row_shards": entry(nbX, timed(lambda: ct.reduce(ct.MAX, X, 1, out=r_rows))),
+        "var_dim1_row_shards": entry(nbX, timed(lambda: ct.reduce(ct.VAR, X, 1, out=r_rows))),
+        "sum_dim0_row_shards_plus_allreduce": entry(nbX, timed(dim0_sum)),
+        "allreduce_16384_fp64_ms": round(timed(lambda: dist.all_reduce(part) if world > 1 else None), 4),
+    }
+    del X
+    # permuted softmax chain: batch 32 sharded
+    bsz = 32 // world
+    g.manual_seed(4 + 100 * rank)
+    buf = torch.randn(bsz, 1024, 12, 1024, device=dev, generator=g)
+    S = buf.permute(0, 2, 1, 3)
+    M = -torch.rand(1, 12, 1, 1024, device=dev, generator=g)
+    O = torch.empty(bsz, 12, 1024, 1024, device=dev)
+    nb = 32 * 1024 * 12 * 1024 * 4
+    res["permuted_softmax_chain"] = {
+        "S_plus_M": entry(2 * nb, timed(lambda: ct.binary(ct.ADD, S, M, out=O), reps=10)),
+        "fused_chain_softmax_S_plus_M": entry(2 * nb, timed(lambda: ct.softmax(S, M, out=O), reps=10)),
+    }
+    del buf, S, O
+    # GPT-2 small non-GEMM ops: batch 8 sharded
+    b5 = max(8 // world, 1)
+    g.manual_seed(6 + 100 * rank)
+    hx = torch.randn(b5, 1024, 768, device=dev, generator=g)
+    hr = torch.randn(b5, 1024, 768, device=dev, generator=g)
+    gam, bet = torch.ones(768, device=dev), torch.zeros(768, device=dev)
+    hh = torch.randn(b5, 1024, 3072, device=dev, generator=g)
+    ha = torch.randn(b5, 12, 1024, 1024, device=dev, generator=g)
+    ox, oh, oa = torch.empty_like(hx), torch.empty_like(hh), torch.empty_like(ha)
+    tot = b5 * world
+    res["gpt2_small_non_gemm"] = {
+        "residual_add": entry(3 * tot * 1024 * 768 * 4, timed(lambda: ct.binary(ct.ADD, hx, hr, out=ox))),
+        "layernorm": entry(2 * tot * 1024 * 768 * 4, timed(lambda: ct.layernorm(hx, gam, bet, out=ox))),
+        "gelu": entry(2 * tot * 1024 * 3072 * 4, timed(lambda: ct.unary(ct.GELU_TANH, hh, out=oh))),
+        "causal_softmax": entry(2 * tot * 12 * 1024 * 1024 * 4, timed(lambda: ct.softmax(ha, None, True, out=oa))),
+        "note": "per-GPU tensors shrink with N (3-48 MiB at N=8): launch-bound and L2-resident, reported not gated",
+    }
+    return res
+
+
 def other_configs(ct, torch, dev):
     """GB/s of the other benchmark configurations on one GPU.  Bytes are the algorithmic bytes
     (each distinct input element read once, each output element written once); every kernel is
@@ -383,12 +549,53 @@ def other_configs(ct, torch, dev):
 
     g = torch.Generator(device=dev)
     res = {}
+    # every named op that is not in the timed step, on 2^28-element tensors (1 GiB each)
+    n28 = 1 << 28
+    g.manual_seed(1)
+    xa = torch.randn(n28, device=dev, generator=g)
+    xb = torch.randn(n28, device=dev, generator=g)
+    xp = xa.abs() + 0.5                               # positive arguments for log
+    o28 = torch.empty(n28, device=dev)
+    o1 = torch.empty(1, device=dev)
+    res["named_ops_2^28"] = {
+        "sub": gbs(12 * n28, lambda: ct.binary(ct.SUB, xa, xb, out=o28)),
+        "div": gbs(12 * n28, lambda: ct.binary(ct.DIV, xa, xb, out=o28)),
+        "log": gbs(8 * n28, lambda: ct.unary(ct.LOG, xp, out=o28)),
+        "tanh": gbs(8 * n28, lambda: ct.unary(ct.TANH, xa, out=o28)),
+        "sum_full": gbs(4 * n28, lambda: ct.reduce(ct.SUM, xa, -1, out=o1)),
+        "mean_full": gbs(4 * n28, lambda: ct.reduce(ct.MEAN, xa, -1, out=o1)),
+        "max_full": gbs(4 * n28, lambda: ct.reduce(ct.MAX, xa, -1, out=o1)),
+        "min_full": gbs(4 * n28, lambda: ct.reduce(ct.MIN, xa, -1, out=o1)),
+        "var_full": gbs(4 * n28, lambda: ct.reduce(ct.VAR, xa, -1, out=o1)),
+    }
+    del xa, xb, xp, o28
+    # the CPU-runnable configuration: A[1024,1024], B[1,1024] ~ U(-1,1), seed 0 (4 MiB: L2-resident and
+    # launch-bound from Python; reported, not a bandwidth figure)
+    g.manual_seed(0)
+    A = torch.rand(1024, 1024, device=dev, generator=g) * 2 - 1
+    B = torch.rand(1, 1024, device=dev, generator=g) * 2 - 1
+    OA, r1k = torch.empty_like(A), torch.empty(1024, device=dev)
+    den = ct.unary(ct.ADD_S, ct.unary(ct.ABS, B), 1.0)
+    nbA, nbB = A.numel() * 4, B.numel() * 4
+    res["cpu_runnable_1024x1024"] = {
+        "A_plus_B": gbs(2 * nbA + nbB, lambda: ct.binary(ct.ADD, A, B, out=OA), reps=200),
+        "A_times_B": gbs(2 * nbA + nbB, lambda: ct.binary(ct.MUL, A, B, out=OA), reps=200),
+        "A_div_absB_plus_1": gbs(2 * nbA + nbB, lambda: ct.binary(ct.DIV, A, den, out=OA), reps=200),
+        "relu_A": gbs(2 * nbA, lambda: ct.unary(ct.RELU, A, out=OA), reps=200),
+        "sum_dim1": gbs(nbA + 4096, lambda: ct.reduce(ct.SUM, A, 1, out=r1k), reps=200),
+        "mean_dim1": gbs(nbA + 4096, lambda: ct.reduce(ct.MEAN, A, 1, out=r1k), reps=200),
+        "max_dim1": gbs(nbA + 4096, lambda: ct.reduce(ct.MAX, A, 1, out=r1k), reps=200),
+        "sum_full": gbs(nbA + 4, lambda: ct.reduce(ct.SUM, A, -1, out=o1), reps=200),
+        "max_full": gbs(nbA + 4, lambda: ct.reduce(ct.MAX, A, -1, out=o1), reps=200),
+    }
+    del A, B, OA
     # reductions: X[8192,16384] ~ N(0,1), seed 2
     g.manual_seed(2)
     X = torch.randn(8192, 16384, device=dev, generator=g)
     red = {}
     for dim in (0, 1):
-        for name, op in (("sum", ct.SUM), ("mean", ct.MEAN), ("var", ct.VAR), ("max", ct.MAX), ("argmax", ct.ARGMAX)):
+        for name, op in (("sum", ct.SUM), ("mean", ct.MEAN), ("var", ct.VAR), ("max", ct.MAX), ("min", ct.MIN),
+                         ("argmax", ct.ARGMAX)):
             r = torch.empty(X.shape[1 - dim], device=dev, dtype=torch.int32 if op == ct.ARGMAX else torch.float32)
             red[f"{name}_dim{dim}"] = gbs(X.numel() * 4 + r.numel() * 4, lambda: ct.reduce(op, X, dim, out=r))
     res["reductions_8192x16384"] = red
@@ -477,6 +684,9 @@ def other_configs(ct, torch, dev):
     yb = m.view(128, 256, 64, 128)
     logits = gr.view(32768, 8192)
     lo = m.view(32768, 8192)
+    xpos = p.abs() + 0.5
+    ce_labels = torch.randint(0, 8192, (32768, 1), device=dev, dtype=torch.int32)
+    ce_loss = torch.empty(1, device=dev)
     step = [0]
 
     def adam():
@@ -491,6 +701,10 @@ def other_configs(ct, torch, dev):
         "batchnorm_moments_128x256x64x128": gbs(4 * n, lambda: ct.channel_moments(xb)),
         "batchnorm_apply_128x256x64x128": gbs(8 * n, lambda: ct.batchnorm_apply(xb, mean, var, gam, bet, 1e-5, out=yb)),
         "log_softmax_32768x8192": gbs(8 * n, lambda: ct.log_softmax(logits, out=lo)),
+        "div_backward_both_1GiB": gbs(20 * n, lambda: ct.div_backward(gr, p, xpos, out_a=m, out_b=v)),
+        "tanh_backward_1GiB": gbs(12 * n, lambda: ct.tanh_backward(gr, p, out=m)),
+        "cross_entropy_32768x8192": gbs(4 * n, lambda: ct.cross_entropy(logits, ce_labels, True, out=ce_loss)),
+        "cross_entropy_backward_32768x8192": gbs(8 * n, lambda: ct.cross_entropy_backward(logits, ce_labels, 1.0 / 32768, out=lo)),
         "cat_two_halves_1GiB": gbs(8 * n, lambda: ct.cat([gr.view(2, n // 2)[0].view(8192, -1), gr.view(2, n // 2)[1].view(8192, -1)], 1, out=m.view(8192, -1))),
     }
     a2 = torch.randn(4096, 4096, device=dev, generator=g)
@@ -572,18 +786,16 @@ def profile_case(name: str):
     _emit({"profile_case": name, "status": "done"})
 
 
-def cpu_baseline(sample_log2=26, reps=3):
-    """The reference's CPU code on a bounded sample: n = 2^sample_log2 elements, the same five ops
-    (gelu as the chain of reference primitives).  Every back-end the reference has for the op is
-    timed; the fastest is the baseline value."""
+def cpu_baseline(sample_log2=28, reps=2, select_log2=24, extras=True):
+    """The reference's CPU code on a bounded sample of the step: the same five ops (gelu as the chain
+    of reference primitives) on n = 2^sample_log2 elements.  Every back-end the reference has for
+    the ops is first timed on a small selection sample (2^select_log2); the fastest is then timed on
+    the full sample and is the baseline value.  `extras` adds the baseline table: the scalar core as
+    the reference's CMake build ships it (no -O, no OpenMP) and the reduction configuration."""
+    import ctypes
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
-    n = 1 << sample_log2
-    rng = np.random.default_rng(1)
-    x = rng.standard_normal(n, dtype=np.float32)
-    y = rng.standard_normal(n, dtype=np.float32)
-    hx, hy = ol.HostView.contig(x), ol.HostView.contig(y)
     kind, impl, paths = "port", None, {}
     if ol.Reference.available():
         try:
@@ -596,7 +808,7 @@ def cpu_baseline(sample_log2=26, reps=3):
             paths["dispatch(avx512,1 thread as shipped)"] = ol.PATH_DISPATCH
         if impl.has_avx2:
             paths["avx2+openmp"] = ol.PATH_AVX2
-        paths["mp(scalar+openmp)"] = ol.PATH_MP
+        paths["mp(scalar+openmp, -O2)"] = ol.PATH_MP
     else:
         impl = ol.Oracle()
         paths["oracle port (plain C + OpenMP)"] = None
@@ -606,33 +818,79 @@ def cpu_baseline(sample_log2=26, reps=3):
     if kind == "reference":
         impl.lib.ref_set_threads(host_threads)
     else:
-        import ctypes
         ctypes.CDLL("libgomp.so.1").omp_set_num_threads(host_threads)
 
-    def step(path):
+    # shrink the sample where host memory is short: x, y, an output and the gelu chain's temporaries
+    avail = mem_available_bytes()
+    while sample_log2 > select_log2 and avail and 10 * 4 * (1 << sample_log2) > avail:
+        sample_log2 -= 1
+    rng = np.random.default_rng(1)
+    n = 1 << sample_log2
+    # N(0,1) values; beyond 2^24 elements the same block repeats (drawing 2^30 normals takes longer than timing them)
+    blk = min(n, 1 << 24)
+    x = np.tile(rng.standard_normal(blk, dtype=np.float32), n // blk)
+    y = np.tile(rng.standard_normal(blk, dtype=np.float32), n // blk)
+
+    def step(obj, path, xs, ys):
         """Seconds for one step."""
         if path is None:                                   # oracle port
+            hx, hy = ol.HostView.contig(xs), ol.HostView.contig(ys)
             t0 = time.perf_counter()
-            impl.binary(ol.ADD, hx, hy); impl.binary(ol.MUL, hx, hy)
-            impl.unary(ol.EXP, hx); impl.unary(ol.RELU, hx); impl.unary(ol.GELU_TANH, hx)
+            obj.binary(ol.ADD, hx, hy); obj.binary(ol.MUL, hx, hy)
+            obj.unary(ol.EXP, hx); obj.unary(ol.RELU, hx); obj.unary(ol.GELU_TANH, hx)
             return time.perf_counter() - t0
-        return impl.bench_step(path, x, y)                 # timed inside the reference build
+        return obj.bench_step(path, xs, ys)                # timed inside the reference build
 
+    m = 1 << min(select_log2, sample_log2)
     results = {}
     for name, path in paths.items():
         try:
-            step(path)
-            best = min(step(path) for _ in range(reps))
-            results[name] = round(BYTES_PER_ELEM_STEP * n / best / 1e9, 2)
+            step(impl, path, x[:m], y[:m])
+            best = min(step(impl, path, x[:m], y[:m]) for _ in range(2))
+            results[name] = round(BYTES_PER_ELEM_STEP * m / best / 1e9, 2)
         except Exception as exc:
             results[name] = f"failed: {exc}"
     good = {k: v for k, v in results.items() if isinstance(v, float)}
     best_name = max(good, key=good.get)
+    step(impl, paths[best_name], x, y)
+    best = min(step(impl, paths[best_name], x, y) for _ in range(max(1, reps)))
+    value = round(BYTES_PER_ELEM_STEP * n / best / 1e9, 2)
     threads = impl.lib.ref_max_threads() if kind == "reference" else host_threads
-    return {"value": good[best_name], "unit": "GB/s", "cores": threads, "kind": kind,
-            "sample": f"n=2^{sample_log2} elements per tensor, the same 5 ops, best of {reps}; fastest back-end: {best_name}; "
-                      "output allocation is inside every reference op and therefore inside its time",
-            "paths": results, "host_cpus": os.cpu_count()}
+    res = {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
+           "sample": f"n=2^{sample_log2} elements per tensor, the same 5 ops, best of {max(1, reps)}; fastest back-end "
+                     f"(picked on n=2^{min(select_log2, sample_log2)}): {best_name}; output allocation is inside every "
+                     "reference op and therefore inside its time",
+           "elements": n, "paths_GBs_on_selection_sample": results, "host_cpus": os.cpu_count()}
+    if extras and kind == "reference":
+        try:        # the scalar core as the reference's own build system compiles it
+            shipped_so = os.path.join(ROOT, "oracle", "_ref", "libctensor_ref_as_shipped.so")
+            if os.path.exists(shipped_so):
+                L = ctypes.CDLL(shipped_so)
+                L.ref_bench_step.restype = ctypes.c_double
+                L.ref_bench_step.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+                k = 1 << 21
+                t = min(L.ref_bench_step(ol.PATH_MP, x.ctypes.data, y.ctypes.data, k) for _ in range(2))
+                res["mp_as_shipped_flags"] = {"GB/s": round(BYTES_PER_ELEM_STEP * k / t / 1e9, 3), "elements": k,
+                                              "flags": "no -O, no -fopenmp (CMakeLists.txt gives the scalar core none): 1 thread"}
+        except Exception as exc:
+            res["mp_as_shipped_flags"] = {"error": repr(exc)}
+        try:        # the reduction configuration on the back-end that can do dim-wise reductions
+            X = rng.standard_normal((8192, 16384), dtype=np.float32)
+            hv = ol.HostView.contig(X)
+            red = {}
+            for nm, op, dim in (("sum_dim0", ol.SUM, 0), ("sum_dim1", ol.SUM, 1), ("max_dim0", ol.MAX, 0), ("max_dim1", ol.MAX, 1),
+                                ("argmax_dim1", ol.ARGMAX, 1), ("sum_full", ol.SUM, -1)):
+                if dim == -1:
+                    flat = ol.HostView.contig(X.reshape(-1))
+                    t0 = time.perf_counter(); impl.reduce(op, flat, -1, ol.PATH_DISPATCH); t = time.perf_counter() - t0
+                else:
+                    t0 = time.perf_counter(); impl.reduce(op, hv, dim, ol.PATH_MP); t = time.perf_counter() - t0
+                red[nm] = round(X.nbytes / t / 1e9, 2)
+            red["note"] = "X[8192,16384] fp32, one call each: sum_mp / max_mp / argmax (scalar+OpenMP), full sum through the dispatcher"
+            res["reductions_8192x16384_GBs"] = red
+        except Exception as exc:
+            res["reductions_8192x16384_GBs"] = {"error": repr(exc)}
+    return res
 
 
 def bench_reference(args):
@@ -640,8 +898,9 @@ def bench_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    n = 1 << args.cpu_log2
-    cpu = cpu_baseline(sample_log2=args.cpu_log2, reps=max(1, args.steps))
+    # the GPU arm's size (2^30 elements per tensor) where host memory permits, else the largest that fits
+    cpu = cpu_baseline(sample_log2=args.ref_log2, reps=max(1, min(args.steps, 2)), extras=False)
+    n = cpu["elements"]
     value = cpu["value"]
     line = {
         "impl": "reference",
@@ -649,9 +908,9 @@ def bench_reference(args):
         "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(BYTES_PER_ELEM_STEP * n / value / 1e6, 3), "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "contiguous fp32 sweep: add, mul, exp, relu, gelu(tanh) of N(0,1) tensors; each step a "
-                               f"bounded sample of n=2^{args.cpu_log2} elements on the host cores",
-                   "elements_per_step": n},
+        "config": {"workload": f"contiguous fp32 sweep, n=2^{n.bit_length() - 1} elements: add, mul, exp, relu, gelu(tanh) of "
+                               "N(0,1) tensors on the host cores (the reference's fastest back-end)",
+                   "elements_per_step": n, "elements_per_gpu": n},
         "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -687,7 +946,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--e2e-n", type=int, default=0, help="cap on the e2e tensor size (0 = same as --n)")
-    ap.add_argument("--cpu-log2", type=int, default=26)
+    ap.add_argument("--cpu-log2", type=int, default=28, help="log2 of the cpu_baseline sample of the GPU arm")
+    ap.add_argument("--ref-log2", type=int, default=30, help="log2 of the tensor size of --impl reference (shrunk if host RAM is short)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")

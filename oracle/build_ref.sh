@@ -3,7 +3,7 @@
 #
 #   oracle/build_ref.sh REFERENCE_ROOT      (the reference checkout; or set CTENSOR_REFERENCE)
 #
-# Output: oracle/_ref/libctensor_ref.so  (+ oracle/_ref/BUILD_INFO.txt).  Nothing else is
+# Output: oracle/_ref/libctensor_ref.so, oracle/_ref/libctensor_ref_as_shipped.so (+ oracle/_ref/BUILD_INFO.txt).  Nothing else is
 # written; no reference source is copied into the repository.
 #
 # The reference's HEAD does not compile (an unfinished CUDA allocator stub).  Two spots are
@@ -42,24 +42,31 @@ CORE_FLAGS="-O2 -fopenmp"
 AVX2_FLAGS="-O3 -mavx2 -mfma -fopenmp"       # CMakeLists.txt:63
 AVX512_FLAGS="-O3 -mavx512f -mavx512dq"      # CMakeLists.txt:71 (no OpenMP: single-threaded)
 
-mkdir -p "$TMP/obj"
-pids=()
-cc() { # name flags source
-  $CXX $STD $2 $INC -c "$3" -o "$TMP/obj/$1.o" & pids+=($!)
+# Two builds of the same sources: the checker (scalar core -O2 -fopenmp) and, for the benchmark's
+# baseline table only, the scalar core as the reference's CMake build ships it (no -O, no -fopenmp:
+# CMakeLists.txt:28-61 gives those targets no per-target flags).
+build_variant() { # object dir, core flags, output name
+  local OBJ="$1" CORE="$2" LIBNAME="$3"
+  mkdir -p "$OBJ"
+  pids=()
+  cc() { # name flags source
+    $CXX $STD $2 $INC -c "$3" -o "$OBJ/$1.o" & pids+=($!)
+  }
+  cc tensor        "$CORE"         "$TMP/src/core/tensor.cpp"
+  cc opsmp         "$CORE"         "$S/core/opsmp.cpp"
+  cc ops_dispatch  "$CORE"         "$S/core/ops_dispatch.cpp"
+  cc autograd      "$CORE"         "$S/core/autograd.cpp"
+  cc avx2_f32      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_f32.cpp"
+  cc avx2_d64      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_d64.cpp"
+  cc avx512_f32    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_f32.cpp"
+  cc avx512_d64    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_d64.cpp"
+  cc loss          "$CORE"         "$REF/src/neuralnet/loss.cpp"      # GradCrossEntropy for the shim
+  cc ref_shim      "$CORE_FLAGS"   "$HERE/ref_shim.cpp"
+  for p in "${pids[@]}"; do wait "$p"; done
+  $CXX -shared -o "$OUT/$LIBNAME" "$OBJ"/*.o -fopenmp
 }
-cc tensor        "$CORE_FLAGS"   "$TMP/src/core/tensor.cpp"
-cc opsmp         "$CORE_FLAGS"   "$S/core/opsmp.cpp"
-cc ops_dispatch  "$CORE_FLAGS"   "$S/core/ops_dispatch.cpp"
-cc autograd      "$CORE_FLAGS"   "$S/core/autograd.cpp"
-cc avx2_f32      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_f32.cpp"
-cc avx2_d64      "$AVX2_FLAGS"   "$S/cpu/AVX2/ops_avx2_d64.cpp"
-cc avx512_f32    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_f32.cpp"
-cc avx512_d64    "$AVX512_FLAGS" "$S/cpu/AVX512/ops_avx512_d64.cpp"
-cc loss          "$CORE_FLAGS"   "$REF/src/neuralnet/loss.cpp"      # GradCrossEntropy for the shim
-cc ref_shim      "$CORE_FLAGS"   "$HERE/ref_shim.cpp"
-for p in "${pids[@]}"; do wait "$p"; done
-
-$CXX -shared -o "$OUT/libctensor_ref.so" "$TMP"/obj/*.o -fopenmp
+build_variant "$TMP/obj" "$CORE_FLAGS" libctensor_ref.so
+build_variant "$TMP/obj_shipped" "" libctensor_ref_as_shipped.so
 {
   echo "reference: $REF"
   echo "compiler: $($CXX --version | head -1)"
@@ -68,4 +75,4 @@ $CXX -shared -o "$OUT/libctensor_ref.so" "$TMP"/obj/*.o -fopenmp
   echo "avx512 flags: $AVX512_FLAGS"
   echo "patched: tensor.h (CudaMemoryPool block removed), tensor.cpp (<cuda> include + CUDA allocate branch removed)"
 } > "$OUT/BUILD_INFO.txt"
-echo "built $OUT/libctensor_ref.so"
+echo "built $OUT/libctensor_ref.so $OUT/libctensor_ref_as_shipped.so"

@@ -14,7 +14,7 @@ def _run_reference_arm(extra_env):
     env.update(extra_env)
     proc = subprocess.run(
         [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1",
-         "--cpu-log2", "20"],
+         "--ref-log2", "20"],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [ln for ln in proc.stdout.splitlines() if ln.strip()]
