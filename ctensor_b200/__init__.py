@@ -411,8 +411,8 @@ def div_backward(grad, a, b, want_a=True, want_b=True, out_a=None, out_b=None, a
     if want_b and out_b is None:
         out_b = _new_out(g, shape)
     with _device_guard(g):
-        check(lib().ctb_div_backward(g.cview(), a.cview(), b.cview(), DView.of(out_a).cview() if want_a else None,
-                                     DView.of(out_b).cview() if want_b else None, int(accumulate), _stream_ptr(g)))
+        check(lib().ctb_div_backward(g.cview(), a.cview(), b.cview(), _as_dview(out_a).cview() if want_a else None,
+                                     _as_dview(out_b).cview() if want_b else None, int(accumulate), _stream_ptr(g)))
     return out_a, out_b
 
 
@@ -422,7 +422,7 @@ def tanh_backward(grad, t, out=None, accumulate=False):
     if out is None:
         out = _new_out(g, broadcast_shape(g.shape, t.shape))
     with _device_guard(g):
-        check(lib().ctb_tanh_backward(g.cview(), t.cview(), DView.of(out).cview(), int(accumulate), _stream_ptr(g)))
+        check(lib().ctb_tanh_backward(g.cview(), t.cview(), _as_dview(out).cview(), int(accumulate), _stream_ptr(g)))
     return out
 
 

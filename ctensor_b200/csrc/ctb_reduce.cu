@@ -39,6 +39,9 @@ namespace ctb {
 #ifndef CTB_RED_BLOCK_THREADS
 #define CTB_RED_BLOCK_THREADS 512          // one CTA per long row: 512 threads measured best on B200
 #endif
+#ifndef CTB_RED_BLOCK_UNROLL
+#define CTB_RED_BLOCK_UNROLL CTB_RED_UNROLL    // loads in flight per thread of the CTA-per-row kernel
+#endif
 #ifndef CTB_RED_COLS_UNROLL
 #define CTB_RED_COLS_UNROLL 16             // row loads in flight per thread of the column kernel
 #endif
@@ -79,9 +82,12 @@ template <typename VT> struct SumPol {
 constexpr int64_t kNoZero = 0x7FFFFFFFFFFFFFFFll;
 template <typename VT, bool IS_MAX> struct MinMaxPol {
     struct Acc { VT m; int64_t z; };
+    // One min/max instruction: it returns the operand that is not NaN (acc never is: it starts at
+    // an infinity), like the compare-and-keep above; which zero it returns for +0 against -0 does not
+    // matter, value() takes the sign of a zero result from z.
     __device__ __forceinline__ static VT pick(VT acc, VT v) {
-        if (IS_MAX) return (acc < v) ? v : acc;
-        return (v < acc) ? v : acc;
+        if (sizeof(VT) == 4) return IS_MAX ? (VT)fmaxf((float)acc, (float)v) : (VT)fminf((float)acc, (float)v);
+        return IS_MAX ? (VT)fmax((double)acc, (double)v) : (VT)fmin((double)acc, (double)v);
     }
     __device__ __forceinline__ static Acc init() {
         return {IS_MAX ? -(VT)INFINITY : (VT)INFINITY, kNoZero};
@@ -112,7 +118,13 @@ template <typename VT> struct VarPol {
     struct Acc { double s1, s2; };
     __device__ __forceinline__ static Acc init() { return {0.0, 0.0}; }
     __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double shift) {
+#ifdef CTB_VAR_F32_SUB
+        // the difference in the element's own precision (exact when x is within a factor 2 of the shift,
+        // else rounded to 2^-24 relative, far inside the 1e-5 contract): one fp64 operation fewer
+        double d = sizeof(VT) == 4 ? (double)__fsub_rn((float)x, (float)shift) : __dsub_rn((double)x, shift);
+#else
         double d = __dsub_rn((double)x, shift);
+#endif
         a.s1 = __dadd_rn(a.s1, d);
         a.s2 = fma(d, d, a.s2);
     }
@@ -206,6 +218,10 @@ template <typename T, typename VT> struct Fin<T, ArgmaxPol<VT>> {
 // Row loads kept in flight per thread by the column kernel: 16 measured best where the
 // per-element work is heavier (fp64 sums, variance, arg-reduction), 8 for plain max/min.
 template <typename Pol> struct ColsUnroll { static constexpr int value = CTB_RED_COLS_UNROLL; };
+#ifndef CTB_RED_COLS_UNROLL_MINMAX
+#define CTB_RED_COLS_UNROLL_MINMAX 8
+#endif
+template <typename VT, bool M> struct ColsUnroll<MinMaxPol<VT, M>> { static constexpr int value = CTB_RED_COLS_UNROLL_MINMAX; };
 
 template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
 template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
@@ -213,6 +229,17 @@ template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool val
 // Policies that must know where the zeros of a line are (max/min, see MinMaxPol).
 template <typename Pol> struct TracksZero { static constexpr bool value = false; };
 template <typename VT, bool M> struct TracksZero<MinMaxPol<VT, M>> { static constexpr bool value = true; };
+
+// The rare batch that holds a zero: re-read it (it is in L1) and note the zeros, out of line, so
+// that the hot loop keeps its register budget (inlined and unrolled, this path cost the split
+// kernel 38 registers and the column kernel spills).
+template <typename Pol>
+__device__ __noinline__ void note_zeros_strided(typename Pol::Acc* acc, const float* p, int64_t idx0, int64_t idx_step,
+                                                int64_t ptr_step, int batches, int vec, int acc_per_lane) {
+    for (int u = 0; u < batches; ++u)
+        for (int k = 0; k < vec; ++k)
+            Pol::note_zero(acc[acc_per_lane ? k : 0], p[u * ptr_step + k], idx0 + u * idx_step + (acc_per_lane ? 0 : k));
+}
 
 // One element through a policy on the scalar paths (ragged ends, the generic kernels).
 template <typename Pol, typename VT>
@@ -304,12 +331,7 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
-        if (any_zero) {
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) Pol::note_zero(acc, v[u].v[k], j + u * stride + k);
-        }
+        if (any_zero) note_zeros_strided<Pol>(&acc, line + j, j, stride, stride, U, VEC, 0);
     }
 }
 
@@ -363,7 +385,7 @@ reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int
         const float* line = a + outer_offset(o, row);
         const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
         typename Pol::Acc acc = Pol::init();
-        accumulate_line<Pol, VEC, CTB_RED_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
+        accumulate_line<Pol, VEC, CTB_RED_BLOCK_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
         acc = block_reduce<Pol, THREADS>(acc, smem);
         if (threadIdx.x == 0) Fin<float, Pol>::run(op, acc, rlen, out, row, nullptr);
     }
@@ -436,12 +458,7 @@ __device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const 
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
-        if (any_zero) {
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) Pol::note_zero(acc[k], v[u].v[k], r + 8 * u);
-        }
+        if (any_zero) note_zeros_strided<Pol>(acc, q, r, 8, step, U, VEC, 1);
     }
 }
 
@@ -711,7 +728,7 @@ Choice choose(const ReduceGeom& g, int dtype, const void* a, int sm_count) {
         // lines up to 8192 elements (a CTA per 4096-element line measured 3.7 TB/s against the
         // warp's 6.6) and longer lines that are not a whole number of CTA-wide batches
         // ([40000,10000]: 7.1 against 5.1 TB/s).  A CTA per line otherwise.
-        const int64_t cta_batch = (int64_t)CTB_RED_BLOCK_THREADS * 4 * CTB_RED_UNROLL;
+        const int64_t cta_batch = (int64_t)CTB_RED_BLOCK_THREADS * 4 * CTB_RED_BLOCK_UNROLL;
         const bool many_lines = g.nout >= (int64_t)sm_count * 32;
         const bool warp = g.rlen <= kRowsWarpSmall ||
                           (many_lines && (g.rlen <= kRowsWarpMax || g.rlen % cta_batch != 0));
