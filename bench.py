@@ -725,7 +725,7 @@ def other_configs(ct, torch, dev):
 
 def profile_case(name: str):
     """A few launches of one kernel family on a small case (inputs larger than L2, well under
-    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab`."""
+    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab|gelu`."""
     import torch
     import ctensor_b200 as ct
     torch.manual_seed(0)
@@ -735,6 +735,12 @@ def profile_case(name: str):
             for op in (ct.VAR, ct.SUM, ct.ARGMAX, ct.MAX):
                 for dim in (0, 1):
                     ct.reduce(op, X, dim)
+    elif name == "gelu":                # the elementwise tile kernel on 2^26 elements (256 MiB in, 256 MiB out)
+        x = torch.randn(1 << 26, device="cuda")
+        o = torch.empty_like(x)
+        for _ in range(3):
+            ct.unary(ct.GELU_TANH, x, out=o)
+            ct.unary(ct.EXP, x, out=o)
     elif name == "rows":                # softmax variants on [4,12,1024,1024] (192 MiB), LayerNorm on [65536,768]
         C = torch.randn(4, 12, 1024, 1024, device="cuda")
         O = torch.empty_like(C)
@@ -951,7 +957,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
-    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab"],
+    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab", "gelu"],
                     help="run a few launches of one kernel family on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:

@@ -32,6 +32,9 @@ def _newest_input() -> float:
 
 
 def build(force: bool = False, extra_flags=(), verbose: bool = False) -> str:
+    """CTB_NVCC_EXTRA (environment): extra nvcc flags, e.g. the -D knobs named in the kernels'
+    sources, for measurement builds (`CTB_NVCC_EXTRA=-DCTB_GELU_VARIANT=1 python -m ctensor_b200.build --force`)."""
+    extra_flags = tuple(extra_flags) + tuple(os.environ.get("CTB_NVCC_EXTRA", "").split())
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_input():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")

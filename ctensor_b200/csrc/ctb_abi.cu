@@ -1023,6 +1023,22 @@ int ctb_div_backward(const ctb_view* grad, const ctb_view* a, const ctb_view* b,
     int rc;
     if (!grad_a && !grad_b) return set_error(CTB_ERR_NULL, "div_backward: no output requested");
     if (!b) return set_error(CTB_ERR_NULL, "backward: null operand");
+    if (grad_a && grad_b && a && grad && !check_view(grad, "", "") && !check_view(a, "", "") && !check_view(b, "", "") &&
+        !check_view(grad_a, "", "") && !check_view(grad_b, "", "") && grad_a->dtype == grad_b->dtype) {
+        // every operand contiguous and of one shape: both gradients in a single pass
+        const ctb_view* opsa[3] = {grad, nullptr, b};
+        const ctb_view* opsb[3] = {grad, a, b};
+        BwdPlan pa, pb;
+        bool same = grad->dtype == grad_a->dtype && a->dtype == grad_a->dtype && b->dtype == grad_a->dtype;
+        if (same && !build_bwd_plan(opsa, grad_a, &pa) && !build_bwd_plan(opsb, grad_b, &pb) && pa.flat && pb.flat &&
+            pa.numel == pb.numel && (accumulate || (!check_no_alias(grad_a, opsb, 3, "div_backward") &&
+                                                    !check_no_alias(grad_b, opsb, 3, "div_backward")))) {
+            const ctb_view* outs[1] = {grad_a};
+            if (!check_no_alias(grad_b, outs, 1, "div_backward"))
+                return launch_div_backward_both(grad_a->dtype, pa.numel, elem_ptr(grad), elem_ptr(a), elem_ptr(b),
+                                                elem_ptr_mut(grad_a), elem_ptr_mut(grad_b), accumulate, (cudaStream_t)stream);
+        }
+    }
     if (grad_a && (rc = backward_chain_entry(kBwdDivA, "div_backward", grad, nullptr, b, grad_a, accumulate, stream))) return rc;
     if (grad_b) {
         if (!a) return set_error(CTB_ERR_NULL, "backward: null operand");

@@ -35,9 +35,15 @@ template <typename T> struct BwdFn<kBwdDivB, T> {
         return from_double<T>(__dmul_rn(to_double(res), -1.0));                  // mul_scalar
     }
 };
+// cosh: for Float32 the single-precision libm function — what the reference's SIMD back-ends call
+// (std::cosh on a float, src/cpu/AVX512/ops_avx512_f32.cpp:459-477); the double-precision one for
+// Double64.  Both are within a few ulp of the reference's result, far inside the 1e-5 contract.
+template <typename T> __device__ __forceinline__ T cosh_of(T t) { return from_double<T>(cosh(to_double(t))); }
+template <> __device__ __forceinline__ float cosh_of<float>(float t) { return coshf(t); }
+
 template <typename T> struct BwdFn<kBwdTanh, T> {
     __device__ __forceinline__ static T apply(T g, T t, T) {
-        const T c = from_double<T>(cosh(to_double(t)));
+        const T c = cosh_of<T>(t);
         const T c2 = BinaryFn<CTB_MUL, T>::apply(c, c);
         const T inv = from_double<T>(__ddiv_rn(1.0, to_double(c2)));             // div_scalar_rev
         return BinaryFn<CTB_MUL, T>::apply(g, inv);
@@ -81,6 +87,40 @@ bwd_flat_kernel(const T* __restrict__ g, const T* __restrict__ x, const T* __res
         for (int64_t i = (int64_t)blockIdx.x * TILE + threadIdx.x; i < n; i += 256)
             out[i] = finish<T, ACC>(ACC ? out[i] : T(0),
                                     BwdFn<KIND, T>::apply(g[i], KIND != kBwdDivA ? x[i] : T(0), NEED_Y ? y[i] : T(0)));
+    }
+}
+
+// Both gradients of a division in one pass over (g, a, b) when everything is contiguous: 20 bytes per
+// element instead of the 28 of two separate passes.
+template <typename T, bool ACC, int VEC>
+__global__ void __launch_bounds__(256)
+div_both_flat_kernel(const T* __restrict__ g, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ da,
+                     T* __restrict__ db, int64_t n) {
+    using V = Vec<T, VEC>;
+    constexpr int64_t TILE = 256 * VEC;
+    const int64_t base = (int64_t)blockIdx.x * TILE + (int64_t)threadIdx.x * VEC;
+    if ((int64_t)(blockIdx.x + 1) * TILE <= n) {
+        const V vg = ldg_stream(reinterpret_cast<const V*>(g + base));
+        const V va = ldg_stream(reinterpret_cast<const V*>(a + base));
+        const V vb = ldg_stream(reinterpret_cast<const V*>(b + base));
+        V oa, ob;
+        if (ACC) {
+            oa = ldg_stream(reinterpret_cast<const V*>(da + base));
+            ob = ldg_stream(reinterpret_cast<const V*>(db + base));
+        }
+        V ra, rb;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            ra.v[k] = finish<T, ACC>(ACC ? oa.v[k] : T(0), BwdFn<kBwdDivA, T>::apply(vg.v[k], T(0), vb.v[k]));
+            rb.v[k] = finish<T, ACC>(ACC ? ob.v[k] : T(0), BwdFn<kBwdDivB, T>::apply(vg.v[k], va.v[k], vb.v[k]));
+        }
+        stg_stream(reinterpret_cast<V*>(da + base), ra);
+        stg_stream(reinterpret_cast<V*>(db + base), rb);
+    } else {
+        for (int64_t i = (int64_t)blockIdx.x * TILE + threadIdx.x; i < n; i += 256) {
+            da[i] = finish<T, ACC>(ACC ? da[i] : T(0), BwdFn<kBwdDivA, T>::apply(g[i], T(0), b[i]));
+            db[i] = finish<T, ACC>(ACC ? db[i] : T(0), BwdFn<kBwdDivB, T>::apply(g[i], a[i], b[i]));
+        }
     }
 }
 
@@ -251,6 +291,102 @@ ce_backward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const i
     }
 }
 
+// ---- the same two row kernels with the row held in registers -------------------------------------------
+// NV values per thread, thread t owns columns t, t + THREADS, ...: the row is read from global
+// memory once and every exponential is evaluated once (the sweeping kernels above evaluate it twice
+// in the backward pass and read the row three times, from L1/L2).  Rows of up to THREADS * NV classes.
+template <int THREADS, int NV>
+__global__ void __launch_bounds__(256)
+ce_forward_rows_reg_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
+                           int64_t label_stride, int64_t rows, int64_t classes, float* __restrict__ nll, int32_t* bad) {
+    __shared__ float smax[8];
+    __shared__ double ssum[8];
+    constexpr int RPB = THREADS == 32 ? 8 : 1;
+    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
+    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
+    if (row >= rows) return;
+    const float* line = x + row * row_stride;
+    float v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int64_t c = (int64_t)i * THREADS + t;
+        v[i] = c < classes ? line[c] : -INFINITY;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) m = (m < v[i]) ? v[i] : m;
+    m = row_max<THREADS>(m, smax);
+    double z = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; i += 2) {
+        // exp_cephes2 evaluates two lanes with packed instructions, bit-identical to exp_cephes
+        const bool in0 = (int64_t)i * THREADS + t < classes, in1 = i + 1 < NV && (int64_t)(i + 1) * THREADS + t < classes;
+        const float2 e = exp_cephes2(make_float2(__fsub_rn(in0 ? v[i] : m, m), __fsub_rn(in1 ? v[i + 1 < NV ? i + 1 : i] : m, m)));
+        if (in0) z = __dadd_rn(z, (double)e.x);
+        if (in1) z = __dadd_rn(z, (double)e.y);
+    }
+    z = row_sum<THREADS>(z, ssum);
+    if (t == 0) {
+        const int64_t l = resolve_label(labels[row * label_stride], classes, bad);
+        float out = 0.0f;
+        if (l >= 0) {
+            const float lz = log_cephes(__double2float_rn(z));
+            const float picked = __fsub_rn(__fsub_rn(line[l], m), lz);
+            out = __double2float_rn(__dmul_rn((double)picked, -1.0));
+        }
+        nll[row] = out;
+    }
+}
+
+template <int THREADS, int NV, bool ACC>
+__global__ void __launch_bounds__(256)
+ce_backward_rows_reg_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
+                            int64_t label_stride, int64_t rows, int64_t classes, float scale, float* __restrict__ dx,
+                            int64_t dx_stride, int32_t* bad) {
+    __shared__ float smax[8];
+    __shared__ double ssum[8];
+    constexpr int RPB = THREADS == 32 ? 8 : 1;
+    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
+    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
+    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
+    if (row >= rows) return;
+    const float* line = x + row * row_stride;
+    float* drow = dx + row * dx_stride;
+    float v[NV], old[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int64_t c = (int64_t)i * THREADS + t;
+        v[i] = c < classes ? line[c] : -INFINITY;
+        if (ACC) old[i] = c < classes ? drow[c] : 0.0f;
+    }
+    float m = -1e9f;                                 // the reference's starting value (loss.cpp:345)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) m = (v[i] > m) ? v[i] : m;
+    m = row_max<THREADS>(m, smax);
+    double z = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const bool in = (int64_t)i * THREADS + t < classes;
+        v[i] = in ? expf(__fsub_rn(v[i], m)) : 0.0f;
+        z = __dadd_rn(z, (double)v[i]);
+    }
+    z = row_sum<THREADS>(z, ssum);
+    const float sum_exp = __double2float_rn(z);
+    const float inv = sum_exp > 1e-12f ? __fdiv_rn(1.0f, sum_exp) : 0.0f;
+    const int64_t l = resolve_label(labels[row * label_stride], classes, t == 0 ? bad : nullptr);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int64_t c = (int64_t)i * THREADS + t;
+        if (c < classes) {
+            float p = __fmul_rn(v[i], inv);
+            if (c == l) p = __fsub_rn(p, 1.0f);
+            const float g = __fmul_rn(p, scale);
+            drow[c] = ACC ? BinaryFn<kOpAddFinite, float>::apply(old[i], g) : g;
+        }
+    }
+}
+
 }  // namespace
 
 int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, const void* x, const void* y, void* out,
@@ -262,26 +398,86 @@ int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, 
     return set_error(CTB_ERR_DTYPE, "backward chain: only Float32 and Double64 gradients are supported");
 }
 
+// values per thread of the register-resident kernels for `classes` columns over `threads` threads (0: too long)
+static int ce_values_per_thread(int64_t classes, int threads) {
+    for (int nv = threads == 32 ? 2 : 8; nv <= 32; nv *= 2)
+        if (classes <= (int64_t)threads * nv) return nv;
+    return 0;
+}
+
+template <typename T>
+static int launch_div_both_t(int64_t n, const T* g, const T* a, const T* b, T* da, T* db, int accumulate, cudaStream_t st) {
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = is_aligned(g, 16) && is_aligned(a, 16) && is_aligned(b, 16) && is_aligned(da, 16) && is_aligned(db, 16);
+    const unsigned grid = (unsigned)ceil_div(n, 256 * (aligned ? VEC : 1));
+    if (aligned) {
+        if (accumulate) div_both_flat_kernel<T, true, VEC><<<grid, 256, 0, st>>>(g, a, b, da, db, n);
+        else div_both_flat_kernel<T, false, VEC><<<grid, 256, 0, st>>>(g, a, b, da, db, n);
+    } else {
+        if (accumulate) div_both_flat_kernel<T, true, 1><<<grid, 256, 0, st>>>(g, a, b, da, db, n);
+        else div_both_flat_kernel<T, false, 1><<<grid, 256, 0, st>>>(g, a, b, da, db, n);
+    }
+    return cuda_error(cudaGetLastError(), "div backward launch");
+}
+
+int launch_div_backward_both(int dtype, int64_t n, const void* g, const void* a, const void* b, void* da, void* db,
+                             int accumulate, cudaStream_t st) {
+    if (n == 0) return CTB_OK;
+    if (dtype == CTB_F32) return launch_div_both_t<float>(n, (const float*)g, (const float*)a, (const float*)b, (float*)da, (float*)db, accumulate, st);
+    if (dtype == CTB_F64) return launch_div_both_t<double>(n, (const double*)g, (const double*)a, (const double*)b, (double*)da, (double*)db, accumulate, st);
+    return set_error(CTB_ERR_DTYPE, "backward chain: only Float32 and Double64 gradients are supported");
+}
+
 int launch_ce_forward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
                            int64_t classes, float* nll, int32_t* bad, cudaStream_t st) {
     if (rows == 0) return CTB_OK;
-    if (classes <= 1024) ce_forward_rows_kernel<32><<<(unsigned)ceil_div(rows, 8), 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
-    else ce_forward_rows_kernel<256><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
+    const bool warp = classes <= 1024;
+    const unsigned grid = warp ? (unsigned)ceil_div(rows, 8) : (unsigned)rows;
+#define CTB_CE_FWD(THREADS, NV) ce_forward_rows_reg_kernel<THREADS, NV><<<grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad)
+    switch (ce_values_per_thread(classes, warp ? 32 : 256) * (warp ? 1 : 100)) {
+    case 2: CTB_CE_FWD(32, 2); break;
+    case 4: CTB_CE_FWD(32, 4); break;
+    case 8: CTB_CE_FWD(32, 8); break;
+    case 16: CTB_CE_FWD(32, 16); break;
+    case 32: CTB_CE_FWD(32, 32); break;
+    case 800: CTB_CE_FWD(256, 8); break;
+    case 1600: CTB_CE_FWD(256, 16); break;
+    case 3200: CTB_CE_FWD(256, 32); break;
+    default:    // rows longer than 8192 classes: sweeps over global memory
+        ce_forward_rows_kernel<256><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
+    }
+#undef CTB_CE_FWD
     return cuda_error(cudaGetLastError(), "cross-entropy rows launch");
+}
+
+template <bool ACC>
+static void launch_ce_backward_acc(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,
+                                   int64_t rows, int64_t classes, float scale, float* dx, int64_t dx_stride, int32_t* bad,
+                                   cudaStream_t st) {
+    const bool warp = classes <= 1024;
+    const unsigned grid = warp ? (unsigned)ceil_div(rows, 8) : (unsigned)rows;
+#define CTB_CE_BWD(THREADS, NV) ce_backward_rows_reg_kernel<THREADS, NV, ACC><<<grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad)
+    switch (ce_values_per_thread(classes, warp ? 32 : 256) * (warp ? 1 : 100)) {
+    case 2: CTB_CE_BWD(32, 2); break;
+    case 4: CTB_CE_BWD(32, 4); break;
+    case 8: CTB_CE_BWD(32, 8); break;
+    case 16: CTB_CE_BWD(32, 16); break;
+    case 32: CTB_CE_BWD(32, 32); break;
+    case 800: CTB_CE_BWD(256, 8); break;
+    case 1600: CTB_CE_BWD(256, 16); break;
+    case 3200: CTB_CE_BWD(256, 32); break;
+    default:
+        ce_backward_rows_kernel<256, ACC><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+    }
+#undef CTB_CE_BWD
 }
 
 int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
                             int64_t classes, float scale, float* dx, int64_t dx_stride, int accumulate, int32_t* bad,
                             cudaStream_t st) {
     if (rows == 0) return CTB_OK;
-    const unsigned warp_grid = (unsigned)ceil_div(rows, 8);
-    if (classes <= 1024) {
-        if (accumulate) ce_backward_rows_kernel<32, true><<<warp_grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-        else ce_backward_rows_kernel<32, false><<<warp_grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-    } else {
-        if (accumulate) ce_backward_rows_kernel<256, true><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-        else ce_backward_rows_kernel<256, false><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-    }
+    if (accumulate) launch_ce_backward_acc<true>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st);
+    else launch_ce_backward_acc<false>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st);
     return cuda_error(cudaGetLastError(), "cross-entropy backward launch");
 }
 

@@ -22,6 +22,10 @@ struct BwdPlan {
 int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, const void* x, const void* y,
                           void* out, int accumulate, cudaStream_t stream);
 
+// Both outputs of the division's backward step for contiguous same-shape operands of n elements.
+int launch_div_backward_both(int dtype, int64_t n, const void* g, const void* a, const void* b, void* da, void* db,
+                             int accumulate, cudaStream_t stream);
+
 // nll[row] for x[rows, classes] (row stride in elements, classes contiguous), labels[row * label_stride].
 int launch_ce_forward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,
                            int64_t rows, int64_t classes, float* nll, int32_t* bad, cudaStream_t stream);

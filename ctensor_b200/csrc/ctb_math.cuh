@@ -225,10 +225,68 @@ __device__ __forceinline__ float2 sigmoid_cephes2(float2 x) {
     return t;
 }
 
+// ---- exact reformulations of the GELU chain that were measured and rejected -------------------------
+// Build-time alternatives (-DCTB_GELU_VARIANT=1|2), kept so that their profiler counters can be
+// reproduced; both give the bits of the shipped chain for every one of the 2^32 inputs.
+//   1: the fp32 -> fp64 widening of the two scalar multiplies done with integer instructions
+//      instead of the conversion unit (two XU operations per element fewer, five ALU operations more)
+//   2: the division of tanh without the reciprocal unit: a magic-constant first guess and three
+//      Newton steps (one XU operation per element fewer, six fp32 operations more)
+#ifndef CTB_GELU_VARIANT
+#define CTB_GELU_VARIANT 0
+#endif
+// (float)((double)x * s) with the widening done by integer instructions.  Exact for normal x; zero,
+// denormal, infinite and NaN inputs give other doubles, which the GELU chain does not notice.
+__device__ __forceinline__ float mul_scalar_int_widen(float x, double s) {
+    const uint32_t b = __float_as_uint(x);
+    const uint32_t hi = (b & 0x80000000u) | (((b & 0x7fffffffu) >> 3) + 0x38000000u);
+    const uint32_t lo = b << 29;
+    return __double2float_rn(__dmul_rn(__hiloint2double((int)hi, (int)lo), s));
+}
+// tanh_cephes2 with the reciprocal of (e + 1) from an integer first guess and three Newton steps
+__device__ __forceinline__ float2 tanh_cephes2_no_rcp_unit(float2 x) {
+    const float2 e = exp_cephes2(__fmul2_rn(x, splat2(2.0f)), kTanhExpHi);
+    const float2 a = __fadd2_rn(e, splat2(-1.0f));
+    const float2 b = __fadd2_rn(e, splat2(1.0f));
+    const float2 nb = make_float2(-b.x, -b.y);
+    float2 r = make_float2(__uint_as_float(0x7EF311C7u - __float_as_uint(b.x)), __uint_as_float(0x7EF311C7u - __float_as_uint(b.y)));
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const float2 err = __ffma2_rn(nb, r, splat2(1.0f));
+        r = __ffma2_rn(r, err, r);
+    }
+    const float2 q = __fmul2_rn(a, r);
+    const float2 rem = __ffma2_rn(nb, q, a);
+    return __ffma2_rn(rem, r, q);
+}
+
 // The two double-precision scalar multiplies stay in double: an fp32 two-product emulation with a
 // near-tie check was bit-exact too but slower (it moves work from the conversion and fp64 pipes,
 // which otherwise idle, to the fp32 pipe, which is the busy one).
 __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
+#if CTB_GELU_VARIANT == 1
+    float2 u = __fmul2_rn(x, x);
+    u = __fmul2_rn(u, x);
+    u.x = mul_scalar_int_widen(u.x, 0.044715);
+    u.y = mul_scalar_int_widen(u.y, 0.044715);
+    u = __fadd2_rn(x, u);
+    u.x = mul_scalar_int_widen(u.x, 0.7978845608028654);
+    u.y = mul_scalar_int_widen(u.y, 0.7978845608028654);
+    float2 tv = tanh_cephes2(u);
+    tv = __fadd2_rn(tv, splat2(1.0f));
+    return __fmul2_rn(__fmul2_rn(x, splat2(0.5f)), tv);
+#elif CTB_GELU_VARIANT == 2
+    float2 u = __fmul2_rn(x, x);
+    u = __fmul2_rn(u, x);
+    u.x = mul_scalar_f32(u.x, 0.044715);
+    u.y = mul_scalar_f32(u.y, 0.044715);
+    u = __fadd2_rn(x, u);
+    u.x = mul_scalar_f32(u.x, 0.7978845608028654);
+    u.y = mul_scalar_f32(u.y, 0.7978845608028654);
+    float2 tv = tanh_cephes2_no_rcp_unit(u);
+    tv = __fadd2_rn(tv, splat2(1.0f));
+    return __fmul2_rn(__fmul2_rn(x, splat2(0.5f)), tv);
+#endif
     float2 u = __fmul2_rn(x, x);
     u = __fmul2_rn(u, x);
     u.x = mul_scalar_f32(u.x, 0.044715);

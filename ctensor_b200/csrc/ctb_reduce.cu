@@ -42,6 +42,9 @@ namespace ctb {
 #ifndef CTB_RED_BLOCK_UNROLL
 #define CTB_RED_BLOCK_UNROLL CTB_RED_UNROLL    // loads in flight per thread of the CTA-per-row kernel
 #endif
+#ifndef CTB_RED_BLOCK_PERSIST
+#define CTB_RED_BLOCK_PERSIST 0                // CTA-per-row kernel: CTAs per SM of a persistent grid (0: one CTA per row)
+#endif
 #ifndef CTB_RED_COLS_UNROLL
 #define CTB_RED_COLS_UNROLL 16             // row loads in flight per thread of the column kernel
 #endif
@@ -118,13 +121,10 @@ template <typename VT> struct VarPol {
     struct Acc { double s1, s2; };
     __device__ __forceinline__ static Acc init() { return {0.0, 0.0}; }
     __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double shift) {
-#ifdef CTB_VAR_F32_SUB
-        // the difference in the element's own precision (exact when x is within a factor 2 of the shift,
-        // else rounded to 2^-24 relative, far inside the 1e-5 contract): one fp64 operation fewer
-        double d = sizeof(VT) == 4 ? (double)__fsub_rn((float)x, (float)shift) : __dsub_rn((double)x, shift);
-#else
-        double d = __dsub_rn((double)x, shift);
-#endif
+        // Float32 elements: the difference in the element's own precision (exact when x is within a
+        // factor 2 of the shift, else rounded to 2^-24 relative: far inside the 1e-5 contract).  One
+        // fp64 operation fewer per element: [8192,16384] over dim 1 5.52 -> 5.72 TB/s, 2^28 elements 6.46 -> 6.66.
+        const double d = sizeof(VT) == 4 ? (double)__fsub_rn((float)x, (float)shift) : __dsub_rn((double)x, shift);
         a.s1 = __dadd_rn(a.s1, d);
         a.s2 = fma(d, d, a.s2);
     }
@@ -801,7 +801,9 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
     }
     case SH_ROWS_BLOCK: {
         constexpr int TB = NeedsShift<Pol>::value ? CTB_RED_BLOCK_THREADS_SHIFT : CTB_RED_BLOCK_THREADS;
-        const unsigned grid = (unsigned)(g.nout < 0x7FFFFFFFll ? g.nout : 0x7FFFFFFFll);
+        int64_t blocks = g.nout < 0x7FFFFFFFll ? g.nout : 0x7FFFFFFFll;
+        if (CTB_RED_BLOCK_PERSIST > 0 && blocks > (int64_t)sm_count * CTB_RED_BLOCK_PERSIST) blocks = (int64_t)sm_count * CTB_RED_BLOCK_PERSIST;
+        const unsigned grid = (unsigned)blocks;
         if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         else reduce_rows_block_kernel<Pol, 1, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
         break;
