@@ -21,6 +21,7 @@
 #include "ctb_math.cuh"
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 namespace ctb {
 
@@ -41,6 +42,9 @@ namespace ctb {
 #endif
 #ifndef CTB_RED_BLOCK_UNROLL
 #define CTB_RED_BLOCK_UNROLL CTB_RED_UNROLL    // loads in flight per thread of the CTA-per-row kernel
+#endif
+#ifndef CTB_RED_BLOCK_THREADS_MINMAX
+#define CTB_RED_BLOCK_THREADS_MINMAX CTB_RED_BLOCK_THREADS
 #endif
 #ifndef CTB_RED_BLOCK_PERSIST
 #define CTB_RED_BLOCK_PERSIST 0                // CTA-per-row kernel: CTAs per SM of a persistent grid (0: one CTA per row)
@@ -80,11 +84,14 @@ template <typename VT> struct SumPol {
 // line (+0 and -0 compare equal, the earlier one stays).  A tree cannot know which zero came
 // first from the values alone, so the accumulator also carries z = 2*index + signbit of the
 // earliest zero seen (kNoZero when none); the finaliser takes the sign from z when m == 0.
-// Zeros are rare: the hot loops test a whole batch of loads for "any zero" with one predicate
-// chain and branch to note_zero() only then.
-constexpr int64_t kNoZero = 0x7FFFFFFFFFFFFFFFll;
-template <typename VT, bool IS_MAX> struct MinMaxPol {
-    struct Acc { VT m; int64_t z; };
+// The hot loops pay one test per batch of loads for it: a thread walks its elements in index
+// order, so only the batch in which its running extreme BECOMES zero can hold the zero that
+// matters (m == 0 with z still unset); that batch is then re-read out of line (note_zeros_strided).
+// KEY: int64_t in general; int32_t where the reduced dim is shorter than 2^30 (the Float32 kernels pick
+// it at launch): the accumulator is then 8 bytes, like the arg-reduction's.
+template <typename VT, bool IS_MAX, typename KEY = int64_t> struct MinMaxPol {
+    struct Acc { VT m; KEY z; };
+    static constexpr KEY kNoZero = sizeof(KEY) == 8 ? (KEY)0x7FFFFFFFFFFFFFFFll : (KEY)0x7FFFFFFF;
     // One min/max instruction: it returns the operand that is not NaN (acc never is: it starts at
     // an infinity), like the compare-and-keep above; which zero it returns for +0 against -0 does not
     // matter, value() takes the sign of a zero result from z.
@@ -96,9 +103,11 @@ template <typename VT, bool IS_MAX> struct MinMaxPol {
         return {IS_MAX ? -(VT)INFINITY : (VT)INFINITY, kNoZero};
     }
     __device__ __forceinline__ static void add(Acc& a, VT x, int64_t, double) { a.m = pick(a.m, x); }
+    // the running extreme is a zero and no zero has been noted yet
+    __device__ __forceinline__ static bool became_zero(const Acc& a) { return a.m == (VT)0 && a.z == kNoZero; }
     __device__ __forceinline__ static void note_zero(Acc& a, VT x, int64_t idx) {
         if (x == (VT)0) {
-            const int64_t key = 2 * idx + (signbit(x) ? 1 : 0);
+            const KEY key = (KEY)(2 * idx + (signbit(x) ? 1 : 0));
             if (key < a.z) a.z = key;
         }
     }
@@ -127,6 +136,16 @@ template <typename VT> struct VarPol {
         const double d = sizeof(VT) == 4 ? (double)__fsub_rn((float)x, (float)shift) : __dsub_rn((double)x, shift);
         a.s1 = __dadd_rn(a.s1, d);
         a.s2 = fma(d, d, a.s2);
+    }
+    // Two neighbouring Float32 elements at once: their differences, the sum of the two and the sum of
+    // their squares in fp32 (each rounded to 2^-24 relative), then ONE widening and ONE fp64 addition
+    // per moment for the pair.  With s2 = sum d^2 the result's error is below 3e-7 * s2 / n, i.e.
+    // 3e-7 relative unless the line's first element lies many standard deviations from its mean.
+    __device__ __forceinline__ static void add2(Acc& a, float x0, float x1, double shift) {
+        const float sf = (float)shift;
+        const float d0 = __fsub_rn(x0, sf), d1 = __fsub_rn(x1, sf);
+        a.s1 = __dadd_rn(a.s1, (double)__fadd_rn(d0, d1));
+        a.s2 = __dadd_rn(a.s2, (double)__fmaf_rn(d1, d1, __fmul_rn(d0, d0)));
     }
     __device__ __forceinline__ static Acc combine(const Acc& a, const Acc& b) {
         return {__dadd_rn(a.s1, b.s1), __dadd_rn(a.s2, b.s2)};
@@ -178,9 +197,9 @@ template <typename T> struct Finalize {
         if (op == CTB_MEAN) s = from_double<T>(__dmul_rn(to_double(s), 1.0 / (double)n));
         ((T*)out)[oi] = s;
     }
-    template <typename VT, bool IS_MAX>
-    __device__ __forceinline__ static void run_mm(const typename MinMaxPol<VT, IS_MAX>::Acc& a, void* out, int64_t oi, double* po) {
-        const VT m = MinMaxPol<VT, IS_MAX>::value(a);
+    template <typename VT, bool IS_MAX, typename KEY>
+    __device__ __forceinline__ static void run_mm(const typename MinMaxPol<VT, IS_MAX, KEY>::Acc& a, void* out, int64_t oi, double* po) {
+        const VT m = MinMaxPol<VT, IS_MAX, KEY>::value(a);
         if (po) { po[oi] = (double)m; return; }
         ((T*)out)[oi] = from_double<T>((double)m);
     }
@@ -199,9 +218,9 @@ template <typename T, typename VT> struct Fin<T, SumPol<VT>> {
         Finalize<T>::template run<VT>(op, a, n, out, oi, po);
     }
 };
-template <typename T, typename VT, bool M> struct Fin<T, MinMaxPol<VT, M>> {
-    __device__ __forceinline__ static void run(int, const typename MinMaxPol<VT, M>::Acc& a, int64_t, void* out, int64_t oi, double* po) {
-        Finalize<T>::template run_mm<VT, M>(a, out, oi, po);
+template <typename T, typename VT, bool M, typename KEY> struct Fin<T, MinMaxPol<VT, M, KEY>> {
+    __device__ __forceinline__ static void run(int, const typename MinMaxPol<VT, M, KEY>::Acc& a, int64_t, void* out, int64_t oi, double* po) {
+        Finalize<T>::template run_mm<VT, M, KEY>(a, out, oi, po);
     }
 };
 template <typename T, typename VT> struct Fin<T, VarPol<VT>> {
@@ -221,14 +240,29 @@ template <typename Pol> struct ColsUnroll { static constexpr int value = CTB_RED
 #ifndef CTB_RED_COLS_UNROLL_MINMAX
 #define CTB_RED_COLS_UNROLL_MINMAX 8
 #endif
-template <typename VT, bool M> struct ColsUnroll<MinMaxPol<VT, M>> { static constexpr int value = CTB_RED_COLS_UNROLL_MINMAX; };
+template <typename VT, bool M, typename KEY> struct ColsUnroll<MinMaxPol<VT, M, KEY>> { static constexpr int value = CTB_RED_COLS_UNROLL_MINMAX; };
 
 template <typename Pol> struct NeedsShift { static constexpr bool value = false; };
 template <typename VT> struct NeedsShift<VarPol<VT>> { static constexpr bool value = true; };
 
+// Policies that take two neighbouring fp32 elements in one step (add2).
+template <typename Pol> struct TakesPairs { static constexpr bool value = false; };
+#ifdef CTB_VAR_PAIRS
+template <> struct TakesPairs<VarPol<float>> { static constexpr bool value = true; };
+#endif
+
+// Policies whose batches accumulate per vector lane (see accumulate_batch).
+template <typename Pol> struct LaneAccs { static constexpr bool value = false; };
+#ifdef CTB_LANE_ACCS_VAR
+template <> struct LaneAccs<VarPol<float>> { static constexpr bool value = true; };
+#endif
+#ifdef CTB_LANE_ACCS_SUM
+template <> struct LaneAccs<SumPol<float>> { static constexpr bool value = true; };
+#endif
+
 // Policies that must know where the zeros of a line are (max/min, see MinMaxPol).
 template <typename Pol> struct TracksZero { static constexpr bool value = false; };
-template <typename VT, bool M> struct TracksZero<MinMaxPol<VT, M>> { static constexpr bool value = true; };
+template <typename VT, bool M, typename KEY> struct TracksZero<MinMaxPol<VT, M, KEY>> { static constexpr bool value = true; };
 
 // The rare batch that holds a zero: re-read it (it is in L1) and note the zeros, out of line, so
 // that the hot loop keeps its register budget (inlined and unrolled, this path cost the split
@@ -245,7 +279,9 @@ __device__ __noinline__ void note_zeros_strided(typename Pol::Acc* acc, const fl
 template <typename Pol, typename VT>
 __device__ __forceinline__ void add_element(typename Pol::Acc& acc, VT x, int64_t idx, double shift) {
     Pol::add(acc, x, idx, shift);
-    if constexpr (TracksZero<Pol>::value) Pol::note_zero(acc, x, idx);
+    if constexpr (TracksZero<Pol>::value) {
+        if (Pol::became_zero(acc)) Pol::note_zero(acc, x, idx);
+    }
 }
 
 // ---- helpers -----------------------------------------------------------------------------------------
@@ -321,17 +357,31 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
     float sf = shift_f;
     if (NeedsShift<Pol>::value) asm volatile("" : "+f"(sf));
     const double shift = (double)sf;
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
-    if constexpr (TracksZero<Pol>::value) {
-        bool any_zero = false;
+    if constexpr (TakesPairs<Pol>::value && VEC % 2 == 0) {
 #pragma unroll
         for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
-        if (any_zero) note_zeros_strided<Pol>(&acc, line + j, j, stride, stride, U, VEC, 0);
+            for (int k = 0; k < VEC; k += 2) Pol::add2(acc, v[u].v[k], v[u].v[k + 1], shift);
+    } else if constexpr (LaneAccs<Pol>::value && VEC > 1 && U > 1) {
+        // one accumulator per vector lane inside the batch: VEC independent fp64 dependency chains of
+        // length U instead of one of length U * VEC, folded in lane order at the end of the batch
+        typename Pol::Acc part[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) part[k] = Pol::init();
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) Pol::add(part[k], v[u].v[k], j + u * stride + k, shift);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc = Pol::combine(acc, part[k]);
+    } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) Pol::add(acc, v[u].v[k], j + u * stride + k, shift);
+    }
+    if constexpr (TracksZero<Pol>::value) {
+        if (Pol::became_zero(acc)) note_zeros_strided<Pol>(&acc, line + j, j, stride, stride, U, VEC, 0);
     }
 }
 
@@ -453,12 +503,10 @@ __device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const 
 #pragma unroll
         for (int k = 0; k < VEC; ++k) Pol::add(acc[k], v[u].v[k], r + 8 * u, shift[k]);
     if constexpr (TracksZero<Pol>::value) {
-        bool any_zero = false;
+        bool became = false;
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) any_zero |= (v[u].v[k] == 0.0f);
-        if (any_zero) note_zeros_strided<Pol>(acc, q, r, 8, step, U, VEC, 1);
+        for (int k = 0; k < VEC; ++k) became |= Pol::became_zero(acc[k]);
+        if (became) note_zeros_strided<Pol>(acc, q, r, 8, step, U, VEC, 1);
     }
 }
 
@@ -800,12 +848,24 @@ int launch_fast(const Choice& c, const ReduceGeom& g, const float* a, void* out,
         break;
     }
     case SH_ROWS_BLOCK: {
-        constexpr int TB = NeedsShift<Pol>::value ? CTB_RED_BLOCK_THREADS_SHIFT : CTB_RED_BLOCK_THREADS;
         int64_t blocks = g.nout < 0x7FFFFFFFll ? g.nout : 0x7FFFFFFFll;
         if (CTB_RED_BLOCK_PERSIST > 0 && blocks > (int64_t)sm_count * CTB_RED_BLOCK_PERSIST) blocks = (int64_t)sm_count * CTB_RED_BLOCK_PERSIST;
         const unsigned grid = (unsigned)blocks;
-        if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
-        else reduce_rows_block_kernel<Pol, 1, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        auto launch = [&](auto tb) {
+            constexpr int TB = decltype(tb)::value;
+            if (c.vec == 4) reduce_rows_block_kernel<Pol, 4, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+            else reduce_rows_block_kernel<Pol, 1, TB><<<grid, TB, 0, st>>>(a, out, outer_of(g, g.nouter), g.nout, g.rlen, op);
+        };
+        if constexpr (NeedsShift<Pol>::value) {
+            launch(std::integral_constant<int, CTB_RED_BLOCK_THREADS_SHIFT>());
+        } else if constexpr (TracksZero<Pol>::value) {
+            // max / min: lines of up to two 256-thread batches run best with 256 threads ([8192,16384]:
+            // 6.62 against 6.27 TB/s), longer ones with 512 ([8192,32768]: 6.95 against 6.61)
+            if (g.rlen <= (int64_t)2 * 256 * 4 * CTB_RED_BLOCK_UNROLL) launch(std::integral_constant<int, 256>());
+            else launch(std::integral_constant<int, CTB_RED_BLOCK_THREADS_MINMAX>());
+        } else {
+            launch(std::integral_constant<int, CTB_RED_BLOCK_THREADS>());
+        }
         break;
     }
     case SH_ROWS_SPLIT: {
@@ -915,8 +975,12 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
     const float* fa = (const float*)a;
     switch (op) {
     case CTB_SUM: case CTB_MEAN: case kOpSumAccumulate: return launch_fast<SumPol<float>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
-    case CTB_MAX: return launch_fast<MinMaxPol<float, true>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
-    case CTB_MIN: return launch_fast<MinMaxPol<float, false>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_MAX:
+        if (g.rlen < (int64_t(1) << 30)) return launch_fast<MinMaxPol<float, true, int32_t>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+        return launch_fast<MinMaxPol<float, true>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+    case CTB_MIN:
+        if (g.rlen < (int64_t(1) << 30)) return launch_fast<MinMaxPol<float, false, int32_t>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
+        return launch_fast<MinMaxPol<float, false>>(c, g, fa, out, partial_out, ws, op, di.sm_count, st);
     case CTB_VAR: return launch_fast<VarPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);
     case CTB_ARGMAX: return launch_fast<ArgmaxPol<float>>(c, g, fa, out, nullptr, ws, op, di.sm_count, st);
     }
