@@ -343,7 +343,7 @@ __device__ __forceinline__ typename Pol::Acc block_reduce(typename Pol::Acc a, t
 // Accumulate elements [lo, hi) of one contiguous line; `nthr` cooperating threads, this one
 // has rank `tid`.  Vector loads when VEC > 1 (caller guarantees alignment of line + lo).
 // U vector loads issued back to back, then consumed.
-template <typename Pol, int VEC, int U>
+template <typename Pol, int VEC, int U, bool LANES = false>
 __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const float* __restrict__ line,
                                                  int64_t j, int64_t stride, float shift_f) {
     using V = Vec<float, VEC>;
@@ -362,7 +362,7 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
         for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int k = 0; k < VEC; k += 2) Pol::add2(acc, v[u].v[k], v[u].v[k + 1], shift);
-    } else if constexpr (LaneAccs<Pol>::value && VEC > 1 && U > 1) {
+    } else if constexpr (LANES && LaneAccs<Pol>::value && VEC > 1 && U > 1) {
         // one accumulator per vector lane inside the batch: VEC independent fp64 dependency chains of
         // length U instead of one of length U * VEC, folded in lane order at the end of the batch
         typename Pol::Acc part[VEC];
@@ -385,7 +385,7 @@ __device__ __forceinline__ void accumulate_batch(typename Pol::Acc& acc, const f
     }
 }
 
-template <typename Pol, int VEC, int UNROLL>
+template <typename Pol, int VEC, int UNROLL, bool LANES = false>
 __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const float* __restrict__ line,
                                                 int64_t lo, int64_t hi, int tid, int nthr, float shift) {
     const int64_t stride = (int64_t)nthr * VEC;
@@ -393,15 +393,15 @@ __device__ __forceinline__ void accumulate_line(typename Pol::Acc& acc, const fl
     // main loop: UNROLL loads in flight; the remainder keeps as many in flight as it has
     // (UNROLL/2, UNROLL/4, ... 1) instead of degrading to one load at a time
     for (; j + (UNROLL - 1) * stride + VEC <= hi; j += UNROLL * stride)
-        accumulate_batch<Pol, VEC, UNROLL>(acc, line, j, stride, shift);
+        accumulate_batch<Pol, VEC, UNROLL, LANES>(acc, line, j, stride, shift);
     if constexpr (UNROLL >= 16) {
-        if (j + 7 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 8>(acc, line, j, stride, shift); j += 8 * stride; }
+        if (j + 7 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 8, LANES>(acc, line, j, stride, shift); j += 8 * stride; }
     }
     if constexpr (UNROLL >= 8) {
-        if (j + 3 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 4>(acc, line, j, stride, shift); j += 4 * stride; }
+        if (j + 3 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 4, LANES>(acc, line, j, stride, shift); j += 4 * stride; }
     }
     if constexpr (UNROLL >= 4) {
-        if (j + 1 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 2>(acc, line, j, stride, shift); j += 2 * stride; }
+        if (j + 1 * stride + VEC <= hi) { accumulate_batch<Pol, VEC, 2, LANES>(acc, line, j, stride, shift); j += 2 * stride; }
     }
     for (; j + VEC <= hi; j += stride) accumulate_batch<Pol, VEC, 1>(acc, line, j, stride, shift);
     if (VEC > 1) {   // ragged end of the line
@@ -435,7 +435,7 @@ reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int
         const float* line = a + outer_offset(o, row);
         const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
         typename Pol::Acc acc = Pol::init();
-        accumulate_line<Pol, VEC, CTB_RED_BLOCK_UNROLL>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
+        accumulate_line<Pol, VEC, CTB_RED_BLOCK_UNROLL, true>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
         acc = block_reduce<Pol, THREADS>(acc, smem);
         if (threadIdx.x == 0) Fin<float, Pol>::run(op, acc, rlen, out, row, nullptr);
     }
