@@ -719,6 +719,38 @@ def other_configs(ct, torch, dev):
     t1.record()
     torch.cuda.synchronize()
     callers["matmul_4096^3_plain_fp32_TFLOPs"] = round(3 * 2 * 4096 ** 3 / t0.elapsed_time(t1) / 1e9, 1)
+    # the tensor-core entry point (tcgen05, TF32 products): b as the transposed view a Linear layer passes
+    try:
+        tc = {}
+        for size in (4096, 8192):
+            aa = torch.randn(size, size, device=dev, generator=g)
+            ww = torch.randn(size, size, device=dev, generator=g)
+            cc = torch.empty(size, size, device=dev)
+            bt = ct.DView.of(ww).permute([1, 0])
+            st = torch.zeros(1, dtype=torch.int32, device=dev)
+            for _ in range(3):
+                ct.matmul_tc(aa, bt, out=cc, status=st)
+            torch.cuda.synchronize()
+            if st.item() != 0:
+                raise RuntimeError(f"kernel status {st.item()}")
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(10):
+                ct.matmul_tc(aa, bt, out=cc)
+            t1.record()
+            torch.cuda.synchronize()
+            tc[f"{size}^3_TFLOPs"] = round(10 * 2 * size ** 3 / t0.elapsed_time(t1) / 1e9, 1)
+            del aa, ww, cc
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                pk = json.load(f)
+            tc["note"] = ("TF32 products; for scale: the measured cuBLAS bf16 peaks of this pool are "
+                          f"{pk.get('bf16_tflops')} (burst) / {pk.get('bf16_tflops_sustained')} (sustained) TFLOP/s, and TF32 runs at half the bf16 rate")
+        except Exception:
+            pass
+        callers["matmul_tensor_cores_tf32"] = tc
+    except Exception as exc:
+        callers["matmul_tensor_cores_tf32"] = {"error": repr(exc)}
     res["callers"] = callers
     return res
 

@@ -50,7 +50,7 @@ EXPORTED_SYMBOLS = [
     "ctb_prefetch_managed",
     "ctb_div_backward", "ctb_tanh_backward", "ctb_cross_entropy", "ctb_cross_entropy_backward",
     "ctb_shard_range", "ctb_comm_init_all", "ctb_comm_size", "ctb_comm_device", "ctb_comm_stream", "ctb_comm_sync",
-    "ctb_comm_destroy", "ctb_allreduce", "ctb_full_reduce_sharded",
+    "ctb_comm_destroy", "ctb_allreduce", "ctb_full_reduce_sharded", "ctb_matmul_tc",
 ]
 
 
@@ -156,6 +156,7 @@ def lib() -> ctypes.CDLL:
     L.ctb_sgd_step.argtypes = [vp, vp, ctypes.c_double, vd]
     L.ctb_copy_into.argtypes = [vp, vp, vd]
     L.ctb_matmul.argtypes = [vp, vp, vp, vd]
+    L.ctb_matmul_tc.argtypes = [vp, vp, vp, vd, vd]
     L.ctb_optimizer_step.argtypes = [i32, vp, vp, vd, vd, ctypes.POINTER(OptimizerHyper), i32, vd]
     L.ctb_channel_moments.argtypes = [vp, vp, vp, vd]
     L.ctb_batchnorm_apply.argtypes = [vp, vp, vp, vp, vp, ctypes.c_double, vp, vd]
@@ -457,6 +458,18 @@ def matmul(a, b, out=None):
         out = _new_out(av, shape)
     with _device_guard(av):
         check(lib().ctb_matmul(av.cview(), bv.cview(), DView.of(out).cview(), _stream_ptr(av)))
+    return out
+
+
+def matmul_tc(a, b, out=None, status=None):
+    """ctb_matmul_tc: the product on the tensor cores (TF32 products, fp32 accumulation).  `status`: an
+    int32 CUDA tensor of one element that is non-zero afterwards if the kernel gave up a wait."""
+    a, b = _as_dview(a), _as_dview(b)
+    if out is None:
+        out = _new_out(a, tuple(a.shape[:-1]) + (b.shape[-1],))
+    with _device_guard(a):
+        check(lib().ctb_matmul_tc(a.cview(), b.cview(), _as_dview(out).cview(),
+                                  None if status is None else status.data_ptr(), _stream_ptr(a)))
     return out
 
 

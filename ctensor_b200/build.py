@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libctb200.so")
-SOURCES = ["ctb_abi.cu", "ctb_elementwise.cu", "ctb_reduce.cu", "ctb_rows.cu", "ctb_index.cu", "ctb_optim.cu", "ctb_norm.cu", "ctb_matmul.cu", "ctb_pool.cu", "ctb_backward.cu", "ctb_comm.cu"]
+SOURCES = ["ctb_abi.cu", "ctb_elementwise.cu", "ctb_reduce.cu", "ctb_rows.cu", "ctb_index.cu", "ctb_optim.cu", "ctb_norm.cu", "ctb_matmul.cu", "ctb_pool.cu", "ctb_backward.cu", "ctb_comm.cu", "ctb_matmul_tc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",

@@ -1124,6 +1124,95 @@ int ctb_matmul(const ctb_view* a, const ctb_view* b, const ctb_view* out, void* 
                          b->stride[b->ndim - 2], b->stride[b->ndim - 1], sb, (cudaStream_t)stream);
 }
 
+// Tensor-core matmul: operands are brought to the layout the kernel's TMA loads need (unit stride
+// along K, rows 16-byte aligned) — directly when the views already have it, through a packed copy in
+// the library's workspace otherwise.
+int ctb_matmul_tc(const ctb_view* a, const ctb_view* b, const ctb_view* out, int32_t* status, void* stream) {
+    int rc;
+    if ((rc = check_view(a, "matmul: null input", "matmul_tc"))) return rc;
+    if ((rc = check_view(b, "matmul: null input", "matmul_tc"))) return rc;
+    if (a->ndim < 2 || b->ndim < 2) return set_error(CTB_ERR_SHAPE, "matmul_mp requires at least 2D tensors");
+    if (a->ndim > 3 || b->ndim > 3) return set_error(CTB_ERR_SHAPE, "matmul: at most one batch dim is supported");
+    if (a->dtype != CTB_F32 || b->dtype != CTB_F32) return set_error(CTB_ERR_DTYPE, "matmul_tc: only Float32 tensors are supported");
+    const int64_t K = a->shape[a->ndim - 1], M = a->shape[a->ndim - 2], N = b->shape[b->ndim - 1];
+    if (b->shape[b->ndim - 2] != K) return set_error(CTB_ERR_SHAPE, "matmul_mp shape mismatch");
+    const int64_t batch_a = a->ndim == 3 ? a->shape[0] : 1, batch_b = b->ndim == 3 ? b->shape[0] : 1;
+    const int64_t batch = batch_a > batch_b ? batch_a : batch_b;
+    if ((batch_a != batch && batch_a != 1) || (batch_b != batch && batch_b != 1))
+        return set_error(CTB_ERR_SHAPE, "matmul_mp shape mismatch");
+    if ((rc = check_out(out, batch * M * N, CTB_F32, "matmul_tc"))) return rc;
+    const ctb_view* ins[2] = {a, b};
+    if ((rc = check_no_alias(out, ins, 2, "matmul_tc"))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (batch * M * N == 0) return CTB_OK;
+    if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31))
+        return set_error(CTB_ERR_LIMIT, "matmul_tc: extents must be below 2^31");
+
+    // which operands can be used where they lie
+    const int64_t Kp = (K + 3) / 4 * 4;
+    auto usable = [&](const ctb_view* v, int row_dim, int k_dim, int64_t rows) {
+        const bool k_unit = K <= 1 || v->stride[k_dim] == 1;
+        const int64_t ld = v->stride[row_dim];
+        const bool ld_ok = rows <= 1 || (ld % 4 == 0 && ld >= K);
+        const bool batch_ok = v->ndim < 3 || v->shape[0] == 1 || v->stride[0] % 4 == 0;
+        return k_unit && ld_ok && batch_ok && is_aligned(elem_ptr(v), 16);
+    };
+    const bool a_direct = usable(a, a->ndim - 2, a->ndim - 1, M);
+    const bool b_direct = usable(b, b->ndim - 1, b->ndim - 2, N);      // b[K, N] seen as bt[N, K]: rows = N, k = dim -2
+    const size_t a_bytes = a_direct ? 0 : align_up((size_t)batch_a * M * Kp * 4, 256);
+    const size_t b_bytes = b_direct ? 0 : align_up((size_t)batch_b * N * Kp * 4, 256);
+    void* ws = nullptr;
+    if ((rc = ensure_workspace(kTicketBytes + 256 + a_bytes + b_bytes, &ws, st))) return rc;
+    int* err_word = (int*)((char*)ws + kTicketBytes);
+    float* a_pack = (float*)((char*)ws + kTicketBytes + 256);
+    float* b_pack = (float*)((char*)a_pack + a_bytes);
+    int* err = status ? status : err_word;
+    CTB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), st));
+
+    // packed copies: [batch, rows, Kp] with the pad columns zeroed (zeros add nothing to the products)
+    auto pack = [&](const ctb_view* v, bool transpose, int64_t nb, int64_t rows, float* dst) -> int {
+        if (Kp != K) CTB_CUDA_TRY(cudaMemsetAsync(dst, 0, (size_t)nb * rows * Kp * 4, st));
+        ctb_view src = *v;                       // as [nb, rows, K]
+        const int nd = v->ndim;
+        const int rd = transpose ? nd - 1 : nd - 2, kd = transpose ? nd - 2 : nd - 1;
+        src.ndim = 3;
+        src.shape[0] = nb;            src.stride[0] = (nd == 3 && v->shape[0] > 1) ? v->stride[0] : 0;
+        src.shape[1] = rows;          src.stride[1] = v->stride[rd];
+        src.shape[2] = K;             src.stride[2] = v->stride[kd];
+        ctb_view d = src;
+        d.base = dst;
+        d.offset = 0;
+        d.stride[0] = rows * Kp; d.stride[1] = Kp; d.stride[2] = 1;
+        if (K == 0) return CTB_OK;
+        return ctb_copy_into(&src, &d, stream);
+    };
+    if (!a_direct && (rc = pack(a, false, batch_a, M, a_pack))) return rc;
+    if (!b_direct && (rc = pack(b, true, batch_b, N, b_pack))) return rc;
+
+    for (int64_t i = 0; i < batch; ++i) {
+        const float* pa;
+        const float* pb;
+        int64_t lda, ldb;
+        if (a_direct) {
+            pa = (const float*)elem_ptr(a) + ((a->ndim == 3 && batch_a > 1) ? i * a->stride[0] : 0);
+            lda = M > 1 ? a->stride[a->ndim - 2] : Kp;
+        } else {
+            pa = a_pack + (batch_a > 1 ? i : 0) * M * Kp;
+            lda = Kp;
+        }
+        if (b_direct) {
+            pb = (const float*)elem_ptr(b) + ((b->ndim == 3 && batch_b > 1) ? i * b->stride[0] : 0);
+            ldb = N > 1 ? b->stride[b->ndim - 1] : Kp;
+        } else {
+            pb = b_pack + (batch_b > 1 ? i : 0) * N * Kp;
+            ldb = Kp;
+        }
+        float* pc = (float*)elem_ptr_mut(out) + i * M * N;
+        if ((rc = launch_matmul_tf32(pa, lda, pb, ldb, pc, N, M, N, K, err, st))) return rc;
+    }
+    return CTB_OK;
+}
+
 // ---- copies into existing tensors: copy_into, cat ----------------------------------------------------------
 int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream) {
     int rc;

@@ -172,6 +172,10 @@ int launch_matmul(int dtype, const void* a, const void* b, void* c, int64_t batc
                   int64_t a_m, int64_t a_k, int64_t a_batch, int64_t b_k, int64_t b_n, int64_t b_batch,
                   cudaStream_t stream);
 
+// Tensor-core product (ctb_matmul_tc.cu): c[M, N] = a[M, K] x bt[N, K]^T, fp32 in and out, TF32 products.
+int launch_matmul_tf32(const float* a, int64_t lda, const float* bt, int64_t ldb, float* c, int64_t ldc, int64_t M,
+                       int64_t N, int64_t K, int* error, cudaStream_t stream);
+
 int launch_optimizer(int kind, float* param, const float* grad, float* state1, float* state2, int64_t n,
                      const ctb_optimizer_hyper& hyper, int step, cudaStream_t stream);
 

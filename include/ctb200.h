@@ -344,6 +344,19 @@ int ctb_cross_entropy_backward(const ctb_view* logits, const ctb_view* labels, d
  * tuned GEMM (tensor cores would change the arithmetic). */
 int ctb_matmul(const ctb_view* a, const ctb_view* b, const ctb_view* out, void* stream);
 
+/* The same product on the tensor cores (tcgen05.mma, TF32 products, fp32 accumulation in tensor
+ * memory, operands staged by TMA): what the reference's SIMD GEMMs are to its scalar one
+ * (src/cpu/AVX2/ops_avx2_f32.cpp:650-775 against src/core/opsmp.cpp:460-558) — another summation
+ * order and rounding, many times the speed.  Float32 only; same shape rules as ctb_matmul.
+ * Tolerance: each product uses the upper 19 bits of its operands (10 mantissa bits), so
+ * |out - exact| <= 2^-9 * sum_k |a_ik * b_kj|.  Operands that TMA can read as they lie (unit
+ * stride along K — for b that means a transposed view of an [N, K] matrix, which is what
+ * Linear::forward passes — 16-byte aligned rows) are used in place; others are packed into the
+ * library's workspace first.  `status` (one int32 in device memory, may be NULL; cleared on
+ * `stream` first): non-zero afterwards if a bounded wait inside the kernel gave up, in which case
+ * `out` is not valid.  sm_100a only; one GPU. */
+int ctb_matmul_tc(const ctb_view* a, const ctb_view* b, const ctb_view* out, int32_t* status, void* stream);
+
 /* Copy `src` into the existing (possibly strided) view `dst` of the same shape and dtype; `src`
  * may broadcast.  The building block of cat and of writes into slices. */
 int ctb_copy_into(const ctb_view* src, const ctb_view* dst, void* stream);

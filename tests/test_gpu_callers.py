@@ -389,3 +389,46 @@ def test_empty_and_degenerate_inputs(ct):
     m, v = ct.channel_moments(torch.full((2, 3, 1), 5.0, device=dev))
     assert torch.equal(m, torch.full((3,), 5.0, device=dev)) and float(v.abs().sum()) == 0.0
     torch.cuda.synchronize()
+
+
+# ---- matmul on the tensor cores (tcgen05, TF32 products) ---------------------------------------------------
+@pytest.mark.parametrize("m,n,k,b_is_transposed_view", [
+    (128, 128, 32, True), (128, 128, 128, False), (256, 384, 64, True), (300, 200, 100, False), (300, 200, 100, True),
+    (1000, 1000, 1000, True), (77, 129, 513, False), (1, 130, 40, True), (4096, 512, 2048, True), (64, 64, 1, False)])
+def test_matmul_tensor_cores_within_the_tf32_tolerance(ct, oracle, m, n, k, b_is_transposed_view):
+    """|out - exact| <= 2^-9 * sum_k |a_ik b_kj|: every product is formed from the operands' upper 19 bits.
+    The exact value is the fp64 product; the reference's own fp32 GEMMs lie within 1e-6 of it."""
+    rng = np.random.default_rng(m * 7 + n * 3 + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    if b_is_transposed_view:                       # b = W^T for a weight matrix W[n, k]: what Linear::forward passes
+        w = rng.standard_normal((n, k)).astype(np.float32)
+        b_host = w.T
+        db = ct.DView.of(torch.from_numpy(w).cuda()).permute([1, 0])
+    else:
+        b_host = rng.standard_normal((k, n)).astype(np.float32)
+        db = torch.from_numpy(b_host).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ct.matmul_tc(torch.from_numpy(a).cuda(), db, status=status).cpu().numpy()
+    assert status.item() == 0, f"a wait inside the kernel gave up (code {status.item()})"
+    exact = a.astype(np.float64) @ b_host.astype(np.float64)
+    bound = 2.0 ** -9 * (np.abs(a).astype(np.float64) @ np.abs(b_host).astype(np.float64)) + 1e-30
+    assert got.shape == (m, n)
+    assert np.all(np.abs(got - exact) <= bound), float(np.max(np.abs(got - exact) / bound))
+    # and against the bit-exact CUDA-core entry point (== matmul_mp of the reference)
+    plain = ct.matmul(torch.from_numpy(a).cuda(), db).cpu().numpy()
+    assert np.all(np.abs(got - plain) <= bound + 1e-5 * np.abs(plain))
+
+
+def test_matmul_tensor_cores_batched_and_empty_k(ct):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((3, 130, 72)).astype(np.float32)
+    b = rng.standard_normal((72, 50)).astype(np.float32)              # shared by every batch entry
+    got = ct.matmul_tc(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()).cpu().numpy()
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    bound = 2.0 ** -9 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64))
+    assert np.all(np.abs(got - exact) <= bound)
+    z = ct.matmul_tc(torch.zeros(5, 0, device="cuda"), torch.zeros(0, 7, device="cuda"))
+    assert z.shape == (5, 7) and float(z.abs().max()) == 0.0
+    with pytest.raises(ct.CtbError) as e:
+        ct.matmul_tc(torch.zeros(4, 5, device="cuda"), torch.zeros(6, 7, device="cuda"))
+    assert e.value.message == "matmul_mp shape mismatch"
