@@ -41,7 +41,7 @@ constexpr int kStages = 4;
 constexpr int kUmmaK = 8;                                    // K of one tcgen05.mma, kind::tf32
 constexpr uint32_t kStageBytesA = kTileM * kTileK * 4, kStageBytesB = kTileN * kTileK * 4;
 constexpr uint32_t kTmemCols = 128;                          // fp32 accumulator columns (power of two >= 32)
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20;
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * (kStageBytesA + kStageBytesB) + 256;
 
 // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
@@ -116,6 +116,7 @@ matmul_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {                      // the whole warp allocates the accumulator's tensor-memory columns
+        __syncwarp();                     // .sync.aligned: lane 0 comes back from the barrier set-up first
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -167,7 +168,8 @@ matmul_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncwarp();
 
     // ---- epilogue: tensor memory -> registers -> global ---------------------------------------------
-    const bool have = num_kb > 0 && mbar_wait(accum, 0, abort_flag, error, 3) && !*abort_flag;
+    // warp-uniform: the tensor-memory loads below are .sync.aligned and must see the whole warp
+    const bool have = __all_sync(0xffffffffu, num_kb > 0 && mbar_wait(accum, 0, abort_flag, error, 3) && !*abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int64_t row = (int64_t)tile_m * kTileM + warp * 32 + lane;         // warp w reads accumulator lanes 32w..32w+31
 #pragma unroll 1
@@ -215,6 +217,7 @@ matmul_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (uint32_t it = 0; it < kSpinLimit && !mbar_try_wait(&full[kb % kStages], (kb / kStages) & 1); ++it) {}
     }
     __syncthreads();
+    __syncwarp();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
