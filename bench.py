@@ -687,6 +687,9 @@ def other_configs(ct, torch, dev):
     xpos = p.abs() + 0.5
     ce_labels = torch.randint(0, 8192, (32768, 1), device=dev, dtype=torch.int32)
     ce_loss = torch.empty(1, device=dev)
+    logits1k = gr[: 262144 * 1000].view(262144, 1000)
+    lo1k = m[: 262144 * 1000].view(262144, 1000)
+    labels1k = torch.randint(0, 1000, (262144, 1), device=dev, dtype=torch.int32)
     step = [0]
 
     def adam():
@@ -705,6 +708,8 @@ def other_configs(ct, torch, dev):
         "tanh_backward_1GiB": gbs(12 * n, lambda: ct.tanh_backward(gr, p, out=m)),
         "cross_entropy_32768x8192": gbs(4 * n, lambda: ct.cross_entropy(logits, ce_labels, True, out=ce_loss)),
         "cross_entropy_backward_32768x8192": gbs(8 * n, lambda: ct.cross_entropy_backward(logits, ce_labels, 1.0 / 32768, out=lo)),
+        "cross_entropy_262144x1000": gbs(4 * 262144 * 1000, lambda: ct.cross_entropy(logits1k, labels1k, True, out=ce_loss)),
+        "cross_entropy_backward_262144x1000": gbs(8 * 262144 * 1000, lambda: ct.cross_entropy_backward(logits1k, labels1k, 1.0 / 262144, out=lo1k)),
         "cat_two_halves_1GiB": gbs(8 * n, lambda: ct.cat([gr.view(2, n // 2)[0].view(8192, -1), gr.view(2, n // 2)[1].view(8192, -1)], 1, out=m.view(8192, -1))),
     }
     a2 = torch.randn(4096, 4096, device=dev, generator=g)
