@@ -762,7 +762,7 @@ def other_configs(ct, torch, dev):
 
 def profile_case(name: str):
     """A few launches of one kernel family on a small case (inputs larger than L2, well under
-    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab|gelu`."""
+    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab|gelu|matmul`."""
     import torch
     import ctensor_b200 as ct
     torch.manual_seed(0)
@@ -778,6 +778,12 @@ def profile_case(name: str):
         for _ in range(3):
             ct.unary(ct.GELU_TANH, x, out=o)
             ct.unary(ct.EXP, x, out=o)
+    elif name == "matmul":              # the tensor-core product on 2048^3 (b as a transposed view: no packing)
+        a = torch.randn(2048, 2048, device="cuda")
+        w = torch.randn(2048, 2048, device="cuda")
+        c = torch.empty(2048, 2048, device="cuda")
+        for _ in range(3):
+            ct.matmul_tc(a, ct.DView.of(w).permute([1, 0]), out=c)
     elif name == "rows":                # softmax variants on [4,12,1024,1024] (192 MiB), LayerNorm on [65536,768]
         C = torch.randn(4, 12, 1024, 1024, device="cuda")
         O = torch.empty_like(C)
@@ -994,7 +1000,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
-    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab", "gelu"],
+    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab", "gelu", "matmul"],
                     help="run a few launches of one kernel family on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:
