@@ -286,7 +286,7 @@ __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
     float2 tv = tanh_cephes2_no_rcp_unit(u);
     tv = __fadd2_rn(tv, splat2(1.0f));
     return __fmul2_rn(__fmul2_rn(x, splat2(0.5f)), tv);
-#endif
+#else
     float2 u = __fmul2_rn(x, x);
     u = __fmul2_rn(u, x);
     u.x = mul_scalar_f32(u.x, 0.044715);
@@ -298,6 +298,7 @@ __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
     t = __fadd2_rn(t, splat2(1.0f));
     const float2 h = __fmul2_rn(x, splat2(0.5f));
     return __fmul2_rn(h, t);
+#endif
 }
 
 // static_cast<int32_t>(double) as x86 cvttsd2si does it (write_scalar_at,
