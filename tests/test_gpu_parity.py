@@ -151,6 +151,29 @@ def test_bit_pattern_sweep(ct, oracle, op):
     assert_bits_equal(got, ref, ol.UNARY_NAMES[op])
 
 
+@pytest.mark.parametrize("op", [ol.EXP, ol.LOG, ol.TANH, ol.SIGMOID, ol.GELU_TANH])
+def test_packed_functions_equal_the_scalar_ones_on_every_fp32_pattern(ct, op):
+    """The contiguous kernel evaluates exp/log/tanh/sigmoid/gelu two lanes per instruction
+    (packed fp32x2 arithmetic); the strided kernels use the one-lane functions that
+    test_bit_pattern_sweep pins against the oracle.  Both must give the same bits for ALL 2^32
+    inputs: 32 blocks of 2^27 consecutive bit patterns, each once through a contiguous view and
+    once through a stride-2 view."""
+    m = 1 << 27
+    wide = torch.empty(2 * m, dtype=torch.float32, device="cuda")
+    for block in range(32):
+        lo = -(1 << 31) + block * m
+        x = torch.arange(lo, lo + m, dtype=torch.int64, device="cuda").to(torch.int32).view(torch.float32)
+        wide[::2] = x
+        packed = ct.unary(op, x)
+        scalar = ct.unary(op, ct.DView.of(wide[::2]))
+        same = torch.equal(packed.view(torch.int32), scalar.view(torch.int32))
+        if not same:
+            bad = (packed.view(torch.int32) != scalar.view(torch.int32)).nonzero()[:4].flatten().tolist()
+            raise AssertionError(f"{ol.UNARY_NAMES[op]}: block {block}, first differing patterns "
+                                 f"{[hex((lo + i) & 0xFFFFFFFF) for i in bad]}")
+        del packed, scalar, x
+
+
 @pytest.mark.parametrize("shape,dim", [((2048, 4096), 0), ((2048, 4096), 1), ((4099, 1031), 0), ((4099, 1031), 1),
                                        ((8, 300000), 1), ((300000, 8), 0), ((3, 700, 1100), 1), ((1 << 22,), 0)])
 @pytest.mark.parametrize("op", [ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.VAR, ol.ARGMAX])
