@@ -394,7 +394,11 @@ def test_empty_and_degenerate_inputs(ct):
 # ---- matmul on the tensor cores (tcgen05, TF32 products) ---------------------------------------------------
 @pytest.mark.parametrize("m,n,k,b_is_transposed_view", [
     (128, 128, 32, True), (128, 128, 128, False), (256, 384, 64, True), (300, 200, 100, False), (300, 200, 100, True),
-    (1000, 1000, 1000, True), (77, 129, 513, False), (1, 130, 40, True), (4096, 512, 2048, True), (64, 64, 1, False)])
+    (1000, 1000, 1000, True), (77, 129, 513, False), (1, 130, 40, True), (4096, 512, 2048, True), (64, 64, 1, False),
+    # enough tiles for the 256-wide tile to be chosen, ragged in every dim; several tiles per CTA (both
+    # accumulators reused, the load ring running across tile boundaries) for either tile width
+    (1300, 1800, 100, True), (1300, 1801, 72, False), (2048, 2048, 256, True), (4096, 4096, 96, True),
+    (80000, 100, 40, True), (5000, 129, 33, False)])
 def test_matmul_tensor_cores_within_the_tf32_tolerance(ct, oracle, m, n, k, b_is_transposed_view):
     """|out - exact| <= 2^-9 * sum_k |a_ik b_kj|: every product is formed from the operands' upper 19 bits.
     The exact value is the fp64 product; the reference's own fp32 GEMMs lie within 1e-6 of it."""
