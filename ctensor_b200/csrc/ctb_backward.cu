@@ -183,10 +183,11 @@ int launch_typed(int kind, const BwdPlan& p, const void* g, const void* x, const
 }
 
 // ---- cross-entropy rows ---------------------------------------------------------------------------------
-// One warp per row up to 1024 classes, one 256-thread CTA per row beyond; the row is read from
+// Rows of up to 8192 classes are served by the register-row kernel of ctb_rows.cu (one read of the
+// logits).  The kernels here take the longer rows: one 256-thread CTA per row, the row read from
 // global memory in each of the three sweeps (max, sum of exponentials, output) — after the first
 // sweep it is in L1/L2, so HBM sees it once.
-// THREADS = cooperating threads per row: 32 (a warp, shuffles only) or 256 (the CTA, through smem).
+// THREADS = cooperating threads per row: 256 (the CTA, through smem); 32 = a warp, shuffles only.
 template <int THREADS> __device__ __forceinline__ float row_max(float v, float* smem) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -291,102 +292,6 @@ ce_backward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const i
     }
 }
 
-// ---- the same two row kernels with the row held in registers -------------------------------------------
-// NV values per lane, lane t owns columns t, t + 32, ...: the row is read from global memory once and
-// every exponential is evaluated once (the sweeping kernels above evaluate it twice in the backward
-// pass and read the row three times, from L1/L2).  Used with a warp per row, up to 1024 classes.
-template <int THREADS, int NV>
-__global__ void __launch_bounds__(256)
-ce_forward_rows_reg_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
-                           int64_t label_stride, int64_t rows, int64_t classes, float* __restrict__ nll, int32_t* bad) {
-    __shared__ float smax[8];
-    __shared__ double ssum[8];
-    constexpr int RPB = THREADS == 32 ? 8 : 1;
-    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
-    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
-    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
-    if (row >= rows) return;
-    const float* line = x + row * row_stride;
-    float v[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int64_t c = (int64_t)i * THREADS + t;
-        v[i] = c < classes ? line[c] : -INFINITY;
-    }
-    float m = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) m = (m < v[i]) ? v[i] : m;
-    m = row_max<THREADS>(m, smax);
-    double z = 0.0;
-#pragma unroll
-    for (int i = 0; i < NV; i += 2) {
-        // exp_cephes2 evaluates two lanes with packed instructions, bit-identical to exp_cephes
-        const bool in0 = (int64_t)i * THREADS + t < classes, in1 = i + 1 < NV && (int64_t)(i + 1) * THREADS + t < classes;
-        const float2 e = exp_cephes2(make_float2(__fsub_rn(in0 ? v[i] : m, m), __fsub_rn(in1 ? v[i + 1 < NV ? i + 1 : i] : m, m)));
-        if (in0) z = __dadd_rn(z, (double)e.x);
-        if (in1) z = __dadd_rn(z, (double)e.y);
-    }
-    z = row_sum<THREADS>(z, ssum);
-    if (t == 0) {
-        const int64_t l = resolve_label(labels[row * label_stride], classes, bad);
-        float out = 0.0f;
-        if (l >= 0) {
-            const float lz = log_cephes(__double2float_rn(z));
-            const float picked = __fsub_rn(__fsub_rn(line[l], m), lz);
-            out = __double2float_rn(__dmul_rn((double)picked, -1.0));
-        }
-        nll[row] = out;
-    }
-}
-
-template <int THREADS, int NV, bool ACC>
-__global__ void __launch_bounds__(256)
-ce_backward_rows_reg_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
-                            int64_t label_stride, int64_t rows, int64_t classes, float scale, float* __restrict__ dx,
-                            int64_t dx_stride, int32_t* bad) {
-    __shared__ float smax[8];
-    __shared__ double ssum[8];
-    constexpr int RPB = THREADS == 32 ? 8 : 1;
-    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
-    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
-    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
-    if (row >= rows) return;
-    const float* line = x + row * row_stride;
-    float* drow = dx + row * dx_stride;
-    float v[NV], old[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int64_t c = (int64_t)i * THREADS + t;
-        v[i] = c < classes ? line[c] : -INFINITY;
-        if (ACC) old[i] = c < classes ? drow[c] : 0.0f;
-    }
-    float m = -1e9f;                                 // the reference's starting value (loss.cpp:345)
-#pragma unroll
-    for (int i = 0; i < NV; ++i) m = (v[i] > m) ? v[i] : m;
-    m = row_max<THREADS>(m, smax);
-    double z = 0.0;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const bool in = (int64_t)i * THREADS + t < classes;
-        v[i] = in ? expf(__fsub_rn(v[i], m)) : 0.0f;
-        z = __dadd_rn(z, (double)v[i]);
-    }
-    z = row_sum<THREADS>(z, ssum);
-    const float sum_exp = __double2float_rn(z);
-    const float inv = sum_exp > 1e-12f ? __fdiv_rn(1.0f, sum_exp) : 0.0f;
-    const int64_t l = resolve_label(labels[row * label_stride], classes, t == 0 ? bad : nullptr);
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int64_t c = (int64_t)i * THREADS + t;
-        if (c < classes) {
-            float p = __fmul_rn(v[i], inv);
-            if (c == l) p = __fsub_rn(p, 1.0f);
-            const float g = __fmul_rn(p, scale);
-            drow[c] = ACC ? BinaryFn<kOpAddFinite, float>::apply(old[i], g) : g;
-        }
-    }
-}
-
 }  // namespace
 
 int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, const void* x, const void* y, void* out,
@@ -396,13 +301,6 @@ int launch_backward_chain(int kind, int dtype, const BwdPlan& p, const void* g, 
     case CTB_F64: return launch_typed<double>(kind, p, g, x, y, out, accumulate, st);
     }
     return set_error(CTB_ERR_DTYPE, "backward chain: only Float32 and Double64 gradients are supported");
-}
-
-// values per thread of the register-resident kernels for `classes` columns over `threads` threads (0: too long)
-static int ce_values_per_thread(int64_t classes, int threads) {
-    for (int nv = threads == 32 ? 2 : 8; nv <= 32; nv *= 2)
-        if (classes <= (int64_t)threads * nv) return nv;
-    return 0;
 }
 
 template <typename T>
@@ -431,48 +329,19 @@ int launch_div_backward_both(int dtype, int64_t n, const void* g, const void* a,
 int launch_ce_forward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
                            int64_t classes, float* nll, int32_t* bad, cudaStream_t st) {
     if (rows == 0) return CTB_OK;
-    const bool warp = classes <= 1024;
-    const unsigned grid = warp ? (unsigned)ceil_div(rows, 8) : (unsigned)rows;
-#define CTB_CE_FWD(THREADS, NV) ce_forward_rows_reg_kernel<THREADS, NV><<<grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad)
-    switch (warp ? ce_values_per_thread(classes, 32) : 0) {
-    case 2: CTB_CE_FWD(32, 2); break;
-    case 4: CTB_CE_FWD(32, 4); break;
-    case 8: CTB_CE_FWD(32, 8); break;
-    case 16: CTB_CE_FWD(32, 16); break;
-    case 32: CTB_CE_FWD(32, 32); break;
-    default:    // more than 1024 classes: a CTA per row sweeping global memory (register-resident CTA-wide rows
-                // measured slower: 1.1 against 4.5 TB/s for the backward pass at 8192 classes)
+    if (!launch_ce_rows_registers(0, x, row_stride, labels, label_stride, rows, classes, 0.0f, nll, 0, bad, st))
         ce_forward_rows_kernel<256><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
-    }
-#undef CTB_CE_FWD
     return cuda_error(cudaGetLastError(), "cross-entropy rows launch");
-}
-
-template <bool ACC>
-static void launch_ce_backward_acc(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,
-                                   int64_t rows, int64_t classes, float scale, float* dx, int64_t dx_stride, int32_t* bad,
-                                   cudaStream_t st) {
-    const bool warp = classes <= 1024;
-    const unsigned grid = warp ? (unsigned)ceil_div(rows, 8) : (unsigned)rows;
-#define CTB_CE_BWD(THREADS, NV) ce_backward_rows_reg_kernel<THREADS, NV, ACC><<<grid, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad)
-    switch (warp ? ce_values_per_thread(classes, 32) : 0) {
-    case 2: CTB_CE_BWD(32, 2); break;
-    case 4: CTB_CE_BWD(32, 4); break;
-    case 8: CTB_CE_BWD(32, 8); break;
-    case 16: CTB_CE_BWD(32, 16); break;
-    case 32: CTB_CE_BWD(32, 32); break;
-    default:
-        ce_backward_rows_kernel<256, ACC><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-    }
-#undef CTB_CE_BWD
 }
 
 int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
                             int64_t classes, float scale, float* dx, int64_t dx_stride, int accumulate, int32_t* bad,
                             cudaStream_t st) {
     if (rows == 0) return CTB_OK;
-    if (accumulate) launch_ce_backward_acc<true>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st);
-    else launch_ce_backward_acc<false>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st);
+    if (!launch_ce_rows_registers(accumulate ? 2 : 1, x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st)) {
+        if (accumulate) ce_backward_rows_kernel<256, true><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        else ce_backward_rows_kernel<256, false><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+    }
     return cuda_error(cudaGetLastError(), "cross-entropy backward launch");
 }
 

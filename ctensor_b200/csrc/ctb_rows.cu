@@ -11,6 +11,7 @@
 // re-reading kernel.
 #include "ctb_reduce.cuh"
 #include "ctb_math.cuh"
+#include "ctb_backward.cuh"
 
 namespace ctb {
 
@@ -293,6 +294,109 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
             } else {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) r[k] = 0.0f;
+            }
+            store_vec<VEC>(orow, col, r);
+        }
+    }
+}
+
+// ---- cross-entropy rows ------------------------------------------------------------------------------------
+// Loss::CrossEntropy (src/neuralnet/loss.cpp:90-118) and GradCrossEntropy::backward (:319-370) on
+// the same row-in-registers scheme: the logits are read once, and either one value per row is
+// written (MODE 0: nll = -((x[label] - max) - ln((float)sum exp(x - max)))) or the gradient row
+// (MODE 1: dx = (exp(x - max) * (1 / sum) - [c == label]) * scale; MODE 2: the same added into dx,
+// NaN / infinite values skipped, which is accumulate_grad's rule, src/core/autograd.cpp:139-151).
+// Labels are one Int32 per row, negative values counting from the end like Tensor::gather's; a
+// label outside the row sets *bad and the row contributes 0 / no one-hot term.
+__device__ __forceinline__ int64_t ce_label(int32_t label, int64_t classes, int32_t* bad) {
+    int64_t l = label;
+    if (l < 0) l += classes;
+    if (l < 0 || l >= classes) {
+        if (bad) *bad = 1;
+        return -1;
+    }
+    return l;
+}
+
+template <int GROUP, int VEC, int NV, int MODE>
+__global__ void __launch_bounds__(RowCta<GROUP, NV>::kThreads)
+ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels, int64_t label_stride,
+               int64_t rows, int cols, float scale, float* __restrict__ out, int64_t out_stride, int32_t* bad) {
+    constexpr int THREADS = RowCta<GROUP, NV>::kThreads;
+    constexpr int GPC = THREADS / GROUP;
+    __shared__ float smax[THREADS / 32];
+    __shared__ double ssum[THREADS / 32];
+    const int tid = threadIdx.x % GROUP;
+    const int64_t row = (int64_t)blockIdx.x * GPC + threadIdx.x / GROUP;
+    if (row >= rows) return;                            // whole groups leave together
+    const float* xr = x + row * row_stride;
+    float t[NV][VEC];
+    // the backward pass starts its maximum at the reference's value (loss.cpp:345)
+    float m = MODE == 0 ? -INFINITY : -1e9f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            load_vec<VEC>(t[i], xr, col, cols);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) m = fmaxf(m, t[i][k]);
+        }
+    }
+    m = group_max<GROUP>(m, smax);
+    double z = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            if constexpr (VEC % 2 == 0) {
+#pragma unroll
+                for (int k = 0; k < VEC; k += 2) {
+                    const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
+                    t[i][k] = e.x;
+                    t[i][k + 1] = e.y;
+                    z = __dadd_rn(__dadd_rn(z, (double)e.x), (double)e.y);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
+                    z = __dadd_rn(z, (double)t[i][k]);
+                }
+            }
+        }
+    }
+    z = group_sum<GROUP>(z, ssum);
+    const float zf = __double2float_rn(z);
+    const int64_t l = ce_label(labels[row * label_stride], cols, tid == 0 ? bad : nullptr);
+    if constexpr (MODE == 0) {
+        if (tid == 0) {
+            float nll = 0.0f;
+            if (l >= 0) {
+                const float picked = __fsub_rn(__fsub_rn(xr[l], m), log_cephes(zf));
+                nll = __double2float_rn(__dmul_rn((double)picked, -1.0));
+            }
+            out[row] = nll;
+        }
+        return;
+    }
+    const float inv = zf > 1e-12f ? __fdiv_rn(1.0f, zf) : 0.0f;
+    float* orow = out + row * out_stride;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int col = (i * GROUP + tid) * VEC;
+        if (col < cols) {
+            float r[VEC];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                float p = __fmul_rn(t[i][k], inv);
+                if (col + k == l) p = __fsub_rn(p, 1.0f);
+                r[k] = __fmul_rn(p, scale);
+            }
+            if constexpr (MODE == 2) {
+                float old[VEC];
+                load_vec<VEC>(old, orow, col, cols);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) r[k] = BinaryFn<kOpAddFinite, float>::apply(old[k], r[k]);
             }
             store_vec<VEC>(orow, col, r);
         }
@@ -1028,6 +1132,12 @@ int rows_grid(int64_t rows, int groups_per_cta) {
     case 1: KERNEL<G, V, N, 1><<<grid, thr, 0, st>>> ARGS; break;                              \
     default: KERNEL<G, V, N, 2><<<grid, thr, 0, st>>> ARGS; break;                             \
     }
+#define CTB_MODES_CE(KERNEL, G, V, N, ARGS)                                                    \
+    switch (mode) {                                                                            \
+    case 0: KERNEL<G, V, N, 0><<<grid, thr, 0, st>>> ARGS; break;                              \
+    case 1: KERNEL<G, V, N, 1><<<grid, thr, 0, st>>> ARGS; break;                              \
+    default: KERNEL<G, V, N, 2><<<grid, thr, 0, st>>> ARGS; break;                             \
+    }
 #define CTB_ROWS_LAUNCH(MODES, KERNEL, G, V, N, ARGS)                                          \
     do {                                                                                       \
         const int grid = rows_grid(g.rows, RowCta<G, N>::kThreads / G);                        \
@@ -1241,6 +1351,21 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
         layernorm_rows_long_kernel<<<grid, 256, 0, st>>>(x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps);
     }
     return cuda_error(cudaGetLastError(), "layernorm launch");
+}
+
+// Cross-entropy rows that fit the register scheme (up to 8192 classes).  mode 0: out = nll[rows];
+// 1: out = dx; 2: out += dx.  Returns false, having launched nothing, for longer rows.
+bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,
+                              int64_t rows, int64_t classes, float scale, float* out, int64_t out_stride, int32_t* bad,
+                              cudaStream_t st) {
+    struct { int64_t rows, cols; } g{rows, classes};
+    bool vec4 = classes % 4 == 0 && is_aligned(x, 16) && row_stride % 4 == 0;
+    if (mode != 0) vec4 = vec4 && is_aligned(out, 16) && out_stride % 4 == 0;
+    bool launched = classes < 0x7FFFFFFFll && rows < 0x7FFFFFFFll;
+    if (launched)
+        CTB_ROWS_DISPATCH(CTB_MODES_CE, ce_rows_kernel,
+                          (x, row_stride, labels, label_stride, rows, (int)classes, scale, out, out_stride, bad));
+    return launched;
 }
 
 }  // namespace ctb
