@@ -219,7 +219,7 @@ def test_cat_errors(ct):
 
 
 @pytest.mark.parametrize("shape", [(64, 256, 28, 28), (32, 64, 7, 7), (16, 3, 33, 65), (4096, 512), (1000, 37),
-                                   (8, 20000, 16), (3, 5, 2, 2, 6)])
+                                   (8, 20000, 16), (3, 5, 2, 2, 6), (5, 7, 24), (3, 50, 8, 33)])
 def test_batchnorm_forward_shapes(ct, shape):
     torch.manual_seed(len(shape) * 7 + shape[1])
     x = torch.randn(*shape, device="cuda") * 1.5 + 0.5
