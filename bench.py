@@ -899,6 +899,18 @@ def cpu_baseline(sample_log2=28, reps=2, select_log2=24, extras=True):
             results[name] = round(BYTES_PER_ELEM_STEP * m / best / 1e9, 2)
         except Exception as exc:
             results[name] = f"failed: {exc}"
+    per_op = {}
+    if kind == "reference":         # each operator through each back-end (GB/s of its own algorithmic bytes)
+        for name, path in paths.items():
+            try:
+                impl.bench_ops(path, x[:m], y[:m])
+                runs = [impl.bench_ops(path, x[:m], y[:m]) for _ in range(2)]
+                if runs[0] is not None:
+                    best_t = [min(r[i] for r in runs) for i in range(5)]
+                    per_op[name] = {op: round(b * m / t / 1e9, 2)
+                                    for op, b, t in zip(("add", "mul", "exp", "relu", "gelu"), (12, 12, 8, 8, 8), best_t)}
+            except Exception as exc:
+                per_op[name] = f"failed: {exc}"
     good = {k: v for k, v in results.items() if isinstance(v, float)}
     best_name = max(good, key=good.get)
     step(impl, paths[best_name], x, y)
@@ -909,7 +921,8 @@ def cpu_baseline(sample_log2=28, reps=2, select_log2=24, extras=True):
            "sample": f"n=2^{sample_log2} elements per tensor, the same 5 ops, best of {max(1, reps)}; fastest back-end "
                      f"(picked on n=2^{min(select_log2, sample_log2)}): {best_name}; output allocation is inside every "
                      "reference op and therefore inside its time",
-           "elements": n, "paths_GBs_on_selection_sample": results, "host_cpus": os.cpu_count()}
+           "elements": n, "paths_GBs_on_selection_sample": results, "per_op_GBs_on_selection_sample": per_op,
+           "host_cpus": os.cpu_count()}
     if extras and kind == "reference":
         try:        # the scalar core as the reference's own build system compiles it
             shipped_so = os.path.join(ROOT, "oracle", "_ref", "libctensor_ref_as_shipped.so")

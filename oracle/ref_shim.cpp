@@ -578,4 +578,27 @@ double ref_bench_step(int path, const float* x, const float* y, int64_t n) {
     }
 }
 
+// The same five operators timed one by one: seconds[0..4] = add, mul, exp, relu, GELU chain.
+int ref_bench_ops(int path, const float* x, const float* y, int64_t n, double* seconds) {
+    RefView vx{}, vy{};
+    vx.base = (void*)x; vx.dtype = 0; vx.ndim = 1; vx.shape[0] = n; vx.stride[0] = 1;
+    vy = vx; vy.base = (void*)y;
+    try {
+        g_err.clear();
+        Tensor a = wrap(&vx), b = wrap(&vy);
+        const int tanh_path = (path == PATH_AVX2) ? PATH_AVX2 : PATH_AVX512;
+        using clk = std::chrono::high_resolution_clock;
+        auto lap = [&](int i, clk::time_point t0) { seconds[i] = std::chrono::duration<double>(clk::now() - t0).count(); };
+        { auto t0 = clk::now(); { Tensor r = do_binary(path, B_ADD, a, b); } lap(0, t0); }
+        { auto t0 = clk::now(); { Tensor r = do_binary(path, B_MUL, a, b); } lap(1, t0); }
+        { auto t0 = clk::now(); { Tensor r = do_unary(path, U_EXP, a, 0.0); } lap(2, t0); }
+        { auto t0 = clk::now(); { Tensor r = do_unary(path, U_RELU, a, 0.0); } lap(3, t0); }
+        { auto t0 = clk::now(); { Tensor r = gelu_chain(a, tanh_path); } lap(4, t0); }
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
 }  // extern "C"

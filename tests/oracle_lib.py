@@ -453,6 +453,18 @@ class Reference:
             raise RuntimeError(self.lib.ref_last_error().decode())
         return t
 
+    def bench_ops(self, path, x: np.ndarray, y: np.ndarray):
+        """Seconds for each of add, mul, exp, relu, gelu-chain (timed in C++); None if this build of the
+        reference library predates the entry point."""
+        if not hasattr(self.lib, "ref_bench_ops"):
+            return None
+        sec = (ctypes.c_double * 5)()
+        self.lib.ref_bench_ops.restype = ctypes.c_int
+        self.lib.ref_bench_ops.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        if self.lib.ref_bench_ops(path, x.ctypes.data, y.ctypes.data, x.size, ctypes.addressof(sec)) != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        return list(sec)
+
     def binary(self, op, a, b, path=PATH_MP):
         out = np.empty(broadcast_shape(a.shape, b.shape), NP_DTYPES[a.dtype])
         return self._check(self.lib.ref_binary(path, op, a.cview(), b.cview(), out.ctypes.data, out.nbytes), out)
