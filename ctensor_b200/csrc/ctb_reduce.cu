@@ -426,15 +426,33 @@ reduce_rows_warp_kernel(const float* __restrict__ a, void* out, OuterIdx o, int6
 }
 
 // ---- rows_block -----------------------------------------------------------------------------------------
+// Loads in flight per thread and resident CTAs per SM the CTA-per-row kernel is compiled for.
+// Variance: 4 loads in flight and a register budget that lets 5 CTAs of 256 threads share an SM
+// measured best ([8192,16384] over dim 1, same run: 5.19 TB/s with 8 loads and no budget, 6.04 with
+// 4 loads and no budget, 6.40 with 4 loads and 5 CTAs, 5.76 with 6 CTAs; rows of 32768 / 65536
+// elements 6.08 -> 6.78 / 6.36 -> 6.78): the heavier per-element work wants more rows in flight
+// per SM rather than more loads per thread.
+#ifndef CTB_RED_VAR_UNROLL
+#define CTB_RED_VAR_UNROLL 4
+#endif
+#ifndef CTB_RED_VAR_MINB
+#define CTB_RED_VAR_MINB 5
+#endif
+#ifndef CTB_RED_BLOCK_MINB
+#define CTB_RED_BLOCK_MINB 1
+#endif
+template <typename Pol> struct BlockShape { static constexpr int unroll = CTB_RED_BLOCK_UNROLL, min_ctas = CTB_RED_BLOCK_MINB; };
+template <typename VT> struct BlockShape<VarPol<VT>> { static constexpr int unroll = CTB_RED_VAR_UNROLL, min_ctas = CTB_RED_VAR_MINB; };
+
 template <typename Pol, int VEC, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, BlockShape<Pol>::min_ctas)
 reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int64_t nout, int64_t rlen, int op) {
     __shared__ typename Pol::Acc smem[THREADS / 32];
     for (int64_t row = blockIdx.x; row < nout; row += gridDim.x) {
         const float* line = a + outer_offset(o, row);
         const float shift = NeedsShift<Pol>::value ? line[0] : 0.0f;
         typename Pol::Acc acc = Pol::init();
-        accumulate_line<Pol, VEC, CTB_RED_BLOCK_UNROLL, true>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
+        accumulate_line<Pol, VEC, BlockShape<Pol>::unroll, true>(acc, line, 0, rlen, threadIdx.x, THREADS, shift);
         acc = block_reduce<Pol, THREADS>(acc, smem);
         if (threadIdx.x == 0) Fin<float, Pol>::run(op, acc, rlen, out, row, nullptr);
     }
