@@ -22,6 +22,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "ctb_common.cuh"
@@ -243,20 +244,30 @@ int ctb_full_reduce_sharded(int op, const ctb_view* const* shards, int64_t total
     ncclRedOp_t r;
     if (!nccl_op(op, &r)) return set_error(CTB_ERR_ARG, "reduction: sharded full reductions exist for sum/mean/max/min");
     DeviceRestore restore;
+    for (int i = 0; i < g_comm.n; ++i)
+        if (!shards[i] || !outs[i]) return set_error(CTB_ERR_NULL, "reduction: null input");
+    // an error after the first launch waits for what was queued before it returns: the caller's
+    // buffers are then no longer in use (the error text of the failing call is kept)
+    auto fail = [&](int code) {
+        const std::string text = ctb_last_error();
+        sync_all_locked();
+        return set_error(code, "%s", text.c_str());
+    };
     int rc;
     // 1. every GPU folds its shard to one fp64 partial, on its communicator stream
     for (int i = 0; i < g_comm.n; ++i) {
-        if (!shards[i] || !outs[i]) return set_error(CTB_ERR_NULL, "reduction: null input");
-        CTB_CUDA_TRY(cudaSetDevice(g_comm.devices[i]));
-        if ((rc = ctb_reduce_full_partial(op, shards[i], g_comm.partial[i], g_comm.streams[i]))) return rc;
+        const cudaError_t e = cudaSetDevice(g_comm.devices[i]);
+        if (e != cudaSuccess) return fail(cuda_error(e, "cudaSetDevice"));
+        if ((rc = ctb_reduce_full_partial(op, shards[i], g_comm.partial[i], g_comm.streams[i]))) return fail(rc);
     }
     // 2. one all-reduce of a double
     std::vector<void*> bufs(g_comm.partial.begin(), g_comm.partial.end());
-    if ((rc = allreduce_locked(bufs.data(), 1, ncclFloat64, r))) return rc;
+    if ((rc = allreduce_locked(bufs.data(), 1, ncclFloat64, r))) return fail(rc);
     // 3. the reference's rounding on every GPU
     for (int i = 0; i < g_comm.n; ++i) {
-        CTB_CUDA_TRY(cudaSetDevice(g_comm.devices[i]));
-        if ((rc = ctb_finalize_full(op, g_comm.partial[i], total_count, outs[i], g_comm.streams[i]))) return rc;
+        const cudaError_t e = cudaSetDevice(g_comm.devices[i]);
+        if (e != cudaSuccess) return fail(cuda_error(e, "cudaSetDevice"));
+        if ((rc = ctb_finalize_full(op, g_comm.partial[i], total_count, outs[i], g_comm.streams[i]))) return fail(rc);
     }
     return sync_all_locked();
 }
