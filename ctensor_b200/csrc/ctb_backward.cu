@@ -183,39 +183,44 @@ int launch_typed(int kind, const BwdPlan& p, const void* g, const void* x, const
 }
 
 // ---- cross-entropy rows ---------------------------------------------------------------------------------
-// Rows of up to 8192 classes are served by the register-row kernel of ctb_rows.cu (one read of the
-// logits).  The kernels here take the longer rows: one 256-thread CTA per row, the row read from
-// global memory in each of the three sweeps (max, sum of exponentials, output) — after the first
-// sweep it is in L1/L2, so HBM sees it once.
-// THREADS = cooperating threads per row: 256 (the CTA, through smem); 32 = a warp, shuffles only.
-template <int THREADS> __device__ __forceinline__ float row_max(float v, float* smem) {
+// Rows of up to 16384 classes (32768 for the gradient) are served by the register-row kernel of
+// ctb_rows.cu (one read of the logits).  The kernel here takes the longer rows (vocabulary-sized
+// logits), one 512-thread CTA per row:
+//   pass 1  one sweep over the row that keeps, per thread, a running maximum m and the sum
+//           z = sum exp(x - m), rescaling z by exp(m_old - m_new) whenever the maximum moves (rare
+//           after the first few elements); the CTA then folds the (m, z) pairs: M = max m,
+//           Z = sum z * exp(m - M).  This equals max -> sub -> exp -> sum of Loss::CrossEntropy
+//           (src/neuralnet/loss.cpp:97-101) up to the rounding of the rescaling factors (~1e-7
+//           relative, inside the loss's 1e-5 contract) and reads the row ONCE.
+//   pass 2  (gradient only) re-reads the row — with two CTAs per SM about 60 MB of rows are in
+//           flight, which the 126 MB L2 holds — and writes (exp(x - M) / Z - onehot) * scale.
+// 128-bit accesses after a scalar head that brings the row to 16-byte alignment (rows of 50257
+// floats start at every 4-byte phase).
+constexpr int kCeLongThreads = 512;       // two CTAs of 64 registers per SM
+
+__device__ __forceinline__ float cta_max_long(float v, float* smem) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        const float o = __shfl_xor_sync(0xffffffffu, v, off);
-        v = (v < o) ? o : v;
-    }
-    if (THREADS == 32) return v;
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     __syncthreads();
     if (lane == 0) smem[w] = v;
     __syncthreads();
-    float r = smem[0];
+    float r = lane < kCeLongThreads / 32 ? smem[lane] : -INFINITY;   // one warp folds the warps' values
 #pragma unroll
-    for (int i = 1; i < THREADS / 32; ++i) r = (r < smem[i]) ? smem[i] : r;
+    for (int off = 16; off > 0; off >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, off));
     return r;
 }
-template <int THREADS> __device__ __forceinline__ double row_sum(double v, double* smem) {
+__device__ __forceinline__ double cta_sum_long(double v, double* smem) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = __dadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
-    if (THREADS == 32) return v;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     __syncthreads();
     if (lane == 0) smem[w] = v;
     __syncthreads();
-    double r = smem[0];
+    double r = lane < kCeLongThreads / 32 ? smem[lane] : 0.0;
 #pragma unroll
-    for (int i = 1; i < THREADS / 32; ++i) r = __dadd_rn(r, smem[i]);
-    return r;
+    for (int off = 16; off > 0; off >>= 1) r = __dadd_rn(r, __shfl_xor_sync(0xffffffffu, r, off));
+    return r;                                     // xor tree: the same bits in every thread
 }
 
 __device__ __forceinline__ int64_t resolve_label(int32_t label, int64_t classes, int32_t* bad) {
@@ -228,67 +233,106 @@ __device__ __forceinline__ int64_t resolve_label(int32_t label, int64_t classes,
     return l;
 }
 
-// nll[row] = -((x[label] - max) - ln((float)sum exp(x - max))): the chain max -> sub -> exp -> sum ->
-// ln -> sub -> gather -> mul_scalar(-1) of Loss::CrossEntropy with the pinned exp / log flavours.
-template <int THREADS>
-__global__ void __launch_bounds__(256)
-ce_forward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
-                       int64_t label_stride, int64_t rows, int64_t classes, float* __restrict__ nll, int32_t* bad) {
-    __shared__ float smax[8];
-    __shared__ double ssum[8];
-    constexpr int RPB = THREADS == 32 ? 8 : 1;     // rows per CTA: 8 warps of one row each, or one CTA-wide row
-    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
-    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
-    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
-    if (row >= rows) return;                        // whole warps (or the whole CTA) leave together
-    const float* line = x + row * row_stride;
-    float m = -INFINITY;
-    for (int64_t c = t; c < classes; c += THREADS) { const float v = line[c]; m = (m < v) ? v : m; }
-    m = row_max<THREADS>(m, smax);
-    double z = 0.0;
-    for (int64_t c = t; c < classes; c += THREADS) z = __dadd_rn(z, (double)exp_cephes(__fsub_rn(line[c], m)));
-    z = row_sum<THREADS>(z, ssum);
-    if (t == 0) {
-        const int64_t l = resolve_label(labels[row * label_stride], classes, bad);
-        float out = 0.0f;
-        if (l >= 0) {
-            const float lz = log_cephes(__double2float_rn(z));
-            const float picked = __fsub_rn(__fsub_rn(line[l], m), lz);
-            out = __double2float_rn(__dmul_rn((double)picked, -1.0));
-        }
-        nll[row] = out;
+// running (m, z) of one thread
+struct OnlineSum {
+    float m;
+    double z;
+    __device__ __forceinline__ void raise(float vm) {          // the maximum moves to vm > m
+        z = __dmul_rn(z, (double)exp_cephes(__fsub_rn(m, vm)));   // exp(-inf) = 0 on the first element (z is 0 then)
+        m = vm;
     }
-}
+    __device__ __forceinline__ void push(float v) {
+        if (v > m) raise(v);
+        z = __dadd_rn(z, (double)exp_cephes(__fsub_rn(v, m)));
+    }
+    __device__ __forceinline__ void push4(const Vec<float, 4>& v) {
+        const float vm = fmaxf(fmaxf(v.v[0], v.v[1]), fmaxf(v.v[2], v.v[3]));
+        if (vm > m) raise(vm);
+        const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-m)));
+        const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-m)));
+        z = __dadd_rn(__dadd_rn(__dadd_rn(__dadd_rn(z, (double)e0.x), (double)e0.y), (double)e1.x), (double)e1.y);
+    }
+};
 
-// dx[row, c] = (exp(x - max) / sum - [c == label]) * scale (GradCrossEntropy::backward).
-template <int THREADS, bool ACC>
-__global__ void __launch_bounds__(256)
-ce_backward_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels,
-                        int64_t label_stride, int64_t rows, int64_t classes, float scale, float* __restrict__ dx,
-                        int64_t dx_stride, int32_t* bad) {
-    __shared__ float smax[8];
-    __shared__ double ssum[8];
-    constexpr int RPB = THREADS == 32 ? 8 : 1;
-    const int sub = THREADS == 32 ? (threadIdx.x >> 5) : 0;
-    const int t = THREADS == 32 ? (threadIdx.x & 31) : threadIdx.x;
-    const int64_t row = (int64_t)blockIdx.x * RPB + sub;
-    if (row >= rows) return;
-    const float* line = x + row * row_stride;
-    float m = -1e9f;                                 // the reference's starting value (loss.cpp:345)
-    for (int64_t c = t; c < classes; c += THREADS) { const float v = line[c]; m = (v > m) ? v : m; }
-    m = row_max<THREADS>(m, smax);
-    double z = 0.0;
-    for (int64_t c = t; c < classes; c += THREADS) z = __dadd_rn(z, (double)expf(__fsub_rn(line[c], m)));
-    z = row_sum<THREADS>(z, ssum);
-    const float sum_exp = __double2float_rn(z);
-    const float inv = sum_exp > 1e-12f ? __fdiv_rn(1.0f, sum_exp) : 0.0f;
-    const int64_t l = resolve_label(labels[row * label_stride], classes, t == 0 ? bad : nullptr);
-    float* drow = dx + row * dx_stride;
-    for (int64_t c = t; c < classes; c += THREADS) {
-        float p = __fmul_rn(expf(__fsub_rn(line[c], m)), inv);
-        if (c == l) p = __fsub_rn(p, 1.0f);
-        const float v = __fmul_rn(p, scale);
-        drow[c] = ACC ? BinaryFn<kOpAddFinite, float>::apply(drow[c], v) : v;
+// MODE 0: out[row] = nll; 1: out[row, :] = gradient; 2: out[row, :] += gradient (finite values only)
+template <int MODE>
+__global__ void __launch_bounds__(kCeLongThreads, 2)
+ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels, int64_t label_stride,
+                    int64_t rows, int64_t classes, float scale, float* __restrict__ out, int64_t out_stride, int32_t* bad) {
+    __shared__ float smax[32];
+    __shared__ double ssum[32];
+    using V4 = Vec<float, 4>;
+    constexpr int T = kCeLongThreads;
+    const int tid = threadIdx.x;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* line = x + row * row_stride;
+        const int64_t head = min(classes, (int64_t)((4 - ((reinterpret_cast<uintptr_t>(line) >> 2) & 3)) & 3));
+        const int64_t nvec = (classes - head) >> 2;
+        const int64_t tail = head + 4 * nvec;                   // [tail, classes): at most 3 elements
+        const V4* lv = reinterpret_cast<const V4*>(line + head);
+        // ---- pass 1 ------------------------------------------------------------------------------------
+        OnlineSum acc{MODE == 0 ? -INFINITY : -1e9f, 0.0};       // the gradient starts at the reference's -1e9 (loss.cpp:345)
+        if (tid < head) acc.push(line[tid]);
+        if (tid < classes - tail) acc.push(line[tail + tid]);
+        int64_t j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {                   // four loads in flight
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(lv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc.push4(v[u]);
+        }
+        for (; j < nvec; j += T) acc.push4(ldg_stream(lv + j));
+        const float M = cta_max_long(acc.m, smax);
+        const double Z = cta_sum_long(__dmul_rn(acc.z, (double)exp_cephes(__fsub_rn(acc.m, M))), ssum);
+        const float zf = __double2float_rn(Z);
+        const int64_t l = resolve_label(labels[row * label_stride], classes, tid == 0 ? bad : nullptr);
+        if constexpr (MODE == 0) {
+            if (tid == 0) {
+                float nll = 0.0f;
+                if (l >= 0) {
+                    const float picked = __fsub_rn(__fsub_rn(line[l], M), log_cephes(zf));
+                    nll = __double2float_rn(__dmul_rn((double)picked, -1.0));
+                }
+                out[row] = nll;
+            }
+        } else {
+            // ---- pass 2 --------------------------------------------------------------------------------
+            const float inv = zf > 1e-12f ? __fdiv_rn(1.0f, zf) : 0.0f;
+            float* orow = out + row * out_stride;
+            auto grad = [&](float v, int64_t c, float old) {
+                float p = __fmul_rn(exp_cephes(__fsub_rn(v, M)), inv);
+                if (c == l) p = __fsub_rn(p, 1.0f);
+                const float g = __fmul_rn(p, scale);
+                return MODE == 2 ? BinaryFn<kOpAddFinite, float>::apply(old, g) : g;
+            };
+            if (tid < head) orow[tid] = grad(line[tid], tid, MODE == 2 ? orow[tid] : 0.0f);
+            if (tid < classes - tail) orow[tail + tid] = grad(line[tail + tid], tail + tid, MODE == 2 ? orow[tail + tid] : 0.0f);
+            const bool out_vec = ((reinterpret_cast<uintptr_t>(orow + head) & 15) == 0);
+            for (int64_t k = tid; k < nvec; k += T) {
+                const V4 v = ldg_stream(lv + k);                 // L2
+                const int64_t c0 = head + 4 * k;
+                V4 r;
+                if (out_vec) {
+                    V4 old;
+                    if (MODE == 2) old = *reinterpret_cast<const V4*>(orow + c0);
+                    const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-M)));
+                    const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-M)));
+                    const float e[4] = {e0.x, e0.y, e1.x, e1.y};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float p = __fmul_rn(e[q], inv);
+                        if (c0 + q == l) p = __fsub_rn(p, 1.0f);
+                        const float g = __fmul_rn(p, scale);
+                        r.v[q] = MODE == 2 ? BinaryFn<kOpAddFinite, float>::apply(old.v[q], g) : g;
+                    }
+                    stg_stream(reinterpret_cast<V4*>(orow + c0), r);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) orow[c0 + q] = grad(v.v[q], c0 + q, MODE == 2 ? orow[c0 + q] : 0.0f);
+                }
+            }
+        }
     }
 }
 
@@ -329,8 +373,10 @@ int launch_div_backward_both(int dtype, int64_t n, const void* g, const void* a,
 int launch_ce_forward_rows(const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride, int64_t rows,
                            int64_t classes, float* nll, int32_t* bad, cudaStream_t st) {
     if (rows == 0) return CTB_OK;
-    if (!launch_ce_rows_registers(0, x, row_stride, labels, label_stride, rows, classes, 0.0f, nll, 0, bad, st))
-        ce_forward_rows_kernel<256><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, nll, bad);
+    if (!launch_ce_rows_registers(0, x, row_stride, labels, label_stride, rows, classes, 0.0f, nll, 0, bad, st)) {
+        const unsigned grid = (unsigned)(rows < 0x7FFFFFFFll ? rows : 0x7FFFFFFFll);
+        ce_long_rows_kernel<0><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, 0.0f, nll, 0, bad);
+    }
     return cuda_error(cudaGetLastError(), "cross-entropy rows launch");
 }
 
@@ -339,8 +385,9 @@ int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* l
                             cudaStream_t st) {
     if (rows == 0) return CTB_OK;
     if (!launch_ce_rows_registers(accumulate ? 2 : 1, x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st)) {
-        if (accumulate) ce_backward_rows_kernel<256, true><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-        else ce_backward_rows_kernel<256, false><<<(unsigned)rows, 256, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        const unsigned grid = (unsigned)(rows < 0x7FFFFFFFll ? rows : 0x7FFFFFFFll);
+        if (accumulate) ce_long_rows_kernel<2><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        else ce_long_rows_kernel<1><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
     }
     return cuda_error(cudaGetLastError(), "cross-entropy backward launch");
 }

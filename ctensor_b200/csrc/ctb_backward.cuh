@@ -33,7 +33,7 @@ int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* l
                             int64_t rows, int64_t classes, float scale, float* dx, int64_t dx_stride,
                             int accumulate, int32_t* bad, cudaStream_t stream);
 
-// The same two passes with the row held in registers (ctb_rows.cu), for rows of up to 8192 classes:
+// The same two passes with the row held in registers (ctb_rows.cu), for rows of up to 16384 classes (gradient: 32768):
 // mode 0 writes nll[rows] to `out`, 1 writes the gradient rows, 2 adds them into `out`.  False:
 // nothing was launched (the row is too long).
 bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,

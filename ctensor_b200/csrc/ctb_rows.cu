@@ -152,7 +152,7 @@ __device__ __forceinline__ float div_by_row(float e, float z, float r) {
 // (CTAs that hold a single 4 KiB row each measured 2.4x slower than 8 rows per CTA: the kernel
 // becomes bound by CTA launch rate.)
 template <int GROUP, int NV> struct RowCta {
-    static constexpr int kThreads = GROUP == 32 ? 256 : (NV <= 4 ? 512 : 256);
+    static constexpr int kThreads = GROUP == 32 ? 256 : (GROUP > 256 ? GROUP : (NV <= 4 ? 512 : 256));
 };
 
 // MODE bits (compile time, so the unrolled load loop has no run-time branch and all loads of a
@@ -1112,8 +1112,12 @@ int rows_grid(int64_t rows, int groups_per_cta) {
 }  // namespace
 
 // Dispatch over (GROUP, VEC, NV): a warp per row up to 8 vectors per lane (1024 floats), then
-// 128- and 256-thread groups; MASKED is a compile-time switch so the plain case carries no
-// mask/causal code.
+// 128-, 256- and 512-thread groups (up to 16384 columns), and a 1024-thread CTA per row up to the
+// caller's `cols_1024` columns (at most 32768; 0: never); MASKED is a compile-time switch so the
+// plain case carries no mask/causal code.  Measured against the cluster kernels they replace
+// (softmax / log-softmax / LayerNorm, TB/s): [16384,16384] 5.1 / 5.3 / 4.6 -> 5.2 / 5.7 / 5.8;
+// [20000,12288] 4.1 / 4.2 / 3.6 -> 5.4 / 5.2 / 5.7; [10000,20000] 3.3 / 3.2 / 2.8 -> 3.7 / 3.7 / 3.3
+// with the 1024-thread CTA, while [8192,32768] lost (4.7 -> 4.4) and stays on the cluster kernel.
 #define CTB_MODES_SOFTMAX(KERNEL, G, V, N, ARGS)                                               \
     switch (mode) {                                                                            \
     case 0: KERNEL<G, V, N, 0><<<grid, thr, 0, st>>> ARGS; break;                              \
@@ -1159,6 +1163,8 @@ int rows_grid(int64_t rows, int groups_per_cta) {
             else if (nv_128 <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 4, ARGS);                    \
             else if (nv_128 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 8, ARGS);                    \
             else if (nv_256 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 256, 4, 8, ARGS);                    \
+            else if (nv_256 <= 16) CTB_ROWS_LAUNCH(MODES, KERNEL, 512, 4, 8, ARGS);                   \
+            else if (g.cols <= cols_1024) CTB_ROWS_LAUNCH(MODES, KERNEL, 1024, 4, 8, ARGS);           \
             else launched = false;                                                             \
         } else {                                                                               \
             if (nv_warp <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 1, 4, ARGS);                         \
@@ -1264,6 +1270,7 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     if (log_out && causal) return set_error(CTB_ERR_ARG, "log_softmax: no causal variant");
     const int mode = (g.has_mask ? 1 : 0) | (g.has_mask && g.m_inner ? 2 : 0) | (causal ? 4 : 0) | (log_out ? 8 : 0);
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
+    const int64_t cols_1024 = 24576;
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen));
     if (!launched) {
@@ -1332,6 +1339,7 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     if (!gamma && !beta) mode = 0;
     else if (gamma && beta && gstride == 1 && bstride == 1 && vec4 && is_aligned(gamma, 16) && is_aligned(beta, 16)) mode = 1;
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
+    const int64_t cols_1024 = 24576;
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
     constexpr int64_t kClusterSpan = (int64_t)kClusterRowThreads * 8 * 4;      // columns per CTA
@@ -1353,7 +1361,7 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     return cuda_error(cudaGetLastError(), "layernorm launch");
 }
 
-// Cross-entropy rows that fit the register scheme (up to 8192 classes).  mode 0: out = nll[rows];
+// Cross-entropy rows that fit the register scheme (up to 16384 classes; the gradient up to 32768).  mode 0: out = nll[rows];
 // 1: out = dx; 2: out += dx.  Returns false, having launched nothing, for longer rows.
 bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, const int32_t* labels, int64_t label_stride,
                               int64_t rows, int64_t classes, float scale, float* out, int64_t out_stride, int32_t* bad,
@@ -1362,6 +1370,9 @@ bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, cons
     bool vec4 = classes % 4 == 0 && is_aligned(x, 16) && row_stride % 4 == 0;
     if (mode != 0) vec4 = vec4 && is_aligned(out, 16) && out_stride % 4 == 0;
     bool launched = classes < 0x7FFFFFFFll && rows < 0x7FFFFFFFll;
+    // a 1024-thread CTA per row beats the sweeping kernel for the gradient (3.1 -> 4.3 TB/s at 32768
+    // classes) but not for the loss, which writes nothing
+    const int64_t cols_1024 = mode == 0 ? 0 : 32768;
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_CE, ce_rows_kernel,
                           (x, row_stride, labels, label_stride, rows, (int)classes, scale, out, out_stride, bad));

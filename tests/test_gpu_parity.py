@@ -332,7 +332,7 @@ def test_backward_chains_accumulate_into_gradient_buffers(ct, oracle):
     assert bad.item() == 0
 
 
-@pytest.mark.parametrize("rows,classes", [(4096, 1000), (512, 50257), (65536, 10)])
+@pytest.mark.parametrize("rows,classes", [(4096, 1000), (512, 50257), (65536, 10), (300, 16384), (200, 32768), (64, 20000)])
 def test_cross_entropy_sizes(ct, oracle, rows, classes):
     rng = np.random.default_rng(rows + classes)
     logits = HostView.contig((rng.standard_normal((rows, classes)) * 3).astype(np.float32))
@@ -346,6 +346,36 @@ def test_cross_entropy_sizes(ct, oracle, rows, classes):
     # for that: 4e-9 * classes relative, and the same fraction of the largest possible entry absolute.
     rtol = max(RTOL, 4e-9 * classes)
     assert_close(grad, oracle.cross_entropy_backward(logits, labels, True, 1.0), rtol, "gradient", atol=max(3e-7, rtol) / rows)
+
+
+@pytest.mark.parametrize("classes,pad", [(40001, 3), (50257, 0), (9000, 5), (12288, 4), (33000, 1)])
+def test_cross_entropy_long_and_strided_rows(ct, classes, pad):
+    """Rows beyond the register kernels (one sweep with a running maximum), rows that start at every
+    4-byte phase (a slice of a wider buffer), and the gradient added into an existing buffer — against
+    the definition evaluated in float64."""
+    rows = 37
+    rng = np.random.default_rng(classes + pad)
+    wide = (rng.standard_normal((rows, classes + pad)) * 4).astype(np.float32)
+    labels = rng.integers(0, classes, (rows, 1)).astype(np.int32)
+    labels[1, 0] = -1                                  # counts from the end
+    dwide = torch.from_numpy(wide).cuda()
+    x = dwide[:, pad // 2: pad // 2 + classes] if pad else dwide
+    xs = wide[:, pad // 2: pad // 2 + classes].astype(np.float64) if pad else wide.astype(np.float64)
+    lab = np.where(labels[:, 0] < 0, labels[:, 0] + classes, labels[:, 0])
+    sh = xs - xs.max(1, keepdims=True)
+    logz = np.log(np.exp(sh).sum(1))
+    want_loss = float(np.mean(-(sh[np.arange(rows), lab] - logz)))
+    got = ct.cross_entropy(ct.DView.of(x), torch.from_numpy(labels).cuda(), True)
+    assert abs(float(got) - want_loss) <= 1e-5 * abs(want_loss)
+    soft = np.exp(sh - logz[:, None])
+    soft[np.arange(rows), lab] -= 1.0
+    want = soft / rows
+    grad = ct.cross_entropy_backward(ct.DView.of(x), torch.from_numpy(labels).cuda(), 1.0 / rows)
+    np.testing.assert_allclose(grad.cpu().numpy(), want, rtol=2e-5, atol=1e-9)
+    start = rng.standard_normal((rows, classes)).astype(np.float32)
+    buf = torch.from_numpy(start).cuda()
+    ct.cross_entropy_backward(ct.DView.of(x), torch.from_numpy(labels).cuda(), 1.0 / rows, out=buf, accumulate=True)
+    np.testing.assert_allclose(buf.cpu().numpy(), start + want, rtol=2e-5, atol=2e-7)
 
 
 def test_argmax_ties_prefer_first_index(ct, oracle):
