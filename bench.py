@@ -762,7 +762,7 @@ def other_configs(ct, torch, dev):
 
 def profile_case(name: str):
     """A few launches of one kernel family on a small case (inputs larger than L2, well under
-    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab|gelu|matmul`."""
+    1 GiB on the device), for profiler captures: `--profile-case reductions|rows|strided|callers|vocab|gelu|matmul|ce`."""
     import torch
     import ctensor_b200 as ct
     torch.manual_seed(0)
@@ -819,6 +819,16 @@ def profile_case(name: str):
             for _ in range(2):
                 ct.log_softmax(L, out=O)
                 ct.softmax(L, out=O)
+    elif name == "ce":                  # cross-entropy rows: [65536,1000] and [4096,16384] (registers), [2048,50257] (one sweep)
+        for rows, cols in ((65536, 1000), (4096, 16384), (2048, 50257)):
+            L = torch.randn(rows, cols, device="cuda")
+            G = torch.empty_like(L)
+            lab = torch.randint(0, cols, (rows, 1), device="cuda", dtype=torch.int32)
+            loss = torch.empty(1, device="cuda")
+            for _ in range(2):
+                ct.cross_entropy(L, lab, True, out=loss)
+                ct.cross_entropy_backward(L, lab, 1.0 / rows, out=G)
+            del L, G
     elif name == "strided":             # the permuted 4-d view at batch 4: S + M, contiguous(S), x - rowmax
         buf = torch.randn(4, 1024, 12, 1024, device="cuda")
         S = buf.permute(0, 2, 1, 3)
@@ -1013,7 +1023,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the timed steps (no e2e, sweep, cpu baseline, sharded sum): for profiler runs")
-    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab", "gelu", "matmul"],
+    ap.add_argument("--profile-case", default=None, choices=["reductions", "rows", "strided", "callers", "vocab", "gelu", "matmul", "ce"],
                     help="run a few launches of one kernel family on a small case and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:
