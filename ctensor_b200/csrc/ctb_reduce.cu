@@ -474,14 +474,21 @@ reduce_rows_block_kernel(const float* __restrict__ a, void* out, OuterIdx o, int
 #ifndef CTB_RED_SPLIT_VAR_LANES
 #define CTB_RED_SPLIT_VAR_LANES 1
 #endif
-template <typename Pol> struct SplitShape { static constexpr int unroll = CTB_RED_SPLIT_UNROLL; static constexpr bool lanes = false; };
-template <typename VT> struct SplitShape<VarPol<VT>> { static constexpr int unroll = CTB_RED_SPLIT_VAR_UNROLL; static constexpr bool lanes = CTB_RED_SPLIT_VAR_LANES != 0; };
+#ifndef CTB_RED_SPLIT_MINMAX_MINB
+#define CTB_RED_SPLIT_MINMAX_MINB 0
+#endif
+#ifndef CTB_RED_SPLIT_MINMAX_UNROLL
+#define CTB_RED_SPLIT_MINMAX_UNROLL CTB_RED_SPLIT_UNROLL
+#endif
+template <typename Pol> struct SplitShape { static constexpr int unroll = CTB_RED_SPLIT_UNROLL, min_ctas = 0; static constexpr bool lanes = false; };
+template <typename VT, bool M, typename KEY> struct SplitShape<MinMaxPol<VT, M, KEY>> { static constexpr int unroll = CTB_RED_SPLIT_MINMAX_UNROLL, min_ctas = CTB_RED_SPLIT_MINMAX_MINB; static constexpr bool lanes = false; };
+template <typename VT> struct SplitShape<VarPol<VT>> { static constexpr int unroll = CTB_RED_SPLIT_VAR_UNROLL, min_ctas = 0; static constexpr bool lanes = CTB_RED_SPLIT_VAR_LANES != 0; };
 
 // ---- rows_split -----------------------------------------------------------------------------------------
 // grid = (splits, nout).  Scratch: tickets[nout] (uint32, zero before and after), then
 // partials[nout][splits].
 template <typename Pol, int VEC, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, SplitShape<Pol>::min_ctas)
 reduce_rows_split_kernel(const float* __restrict__ a, void* out, double* partial_out, OuterIdx o,
                          int64_t rlen, int64_t chunk, int op, uint32_t* tickets,
                          typename Pol::Acc* partials) {
@@ -546,8 +553,14 @@ __device__ __forceinline__ void cols_batch(typename Pol::Acc (&acc)[VEC], const 
     }
 }
 
+#ifndef CTB_RED_COLS_MINMAX_CTAS
+#define CTB_RED_COLS_MINMAX_CTAS CTB_RED_COLS_CTAS_PER_SM
+#endif
+template <typename Pol> struct ColsCtas { static constexpr int value = CTB_RED_COLS_CTAS_PER_SM; };
+template <typename VT, bool M, typename KEY> struct ColsCtas<MinMaxPol<VT, M, KEY>> { static constexpr int value = CTB_RED_COLS_MINMAX_CTAS; };
+
 template <typename Pol, int VEC>
-__global__ void __launch_bounds__(256, CTB_RED_COLS_CTAS_PER_SM)
+__global__ void __launch_bounds__(256, ColsCtas<Pol>::value)
 reduce_cols_kernel(const float* __restrict__ a, void* out, OuterIdx batch, int64_t ncols, int64_t rlen,
                    int64_t rstride, int64_t rows_per_split, int op, uint32_t* tickets,
                    typename Pol::Acc* partials) {
