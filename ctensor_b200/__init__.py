@@ -224,7 +224,13 @@ class DView:
         return n
 
     def cview(self) -> View:
-        return make_view(self.buf.data_ptr(), self.dtype, self.shape, self.strides, self.offset)
+        """The C descriptor of this view; built once per DView (a view never changes), so a caller that
+        keeps its DViews pays the ctypes marshalling once, not per call."""
+        cv = self.__dict__.get("_cv")
+        if cv is None:
+            cv = make_view(self.buf.data_ptr(), self.dtype, self.shape, self.strides, self.offset)
+            self.__dict__["_cv"] = cv
+        return cv
 
     def permute(self, dims: Sequence[int]) -> "DView":
         return DView(self.buf, tuple(self.shape[d] for d in dims), tuple(self.strides[d] for d in dims), self.offset)
@@ -241,8 +247,24 @@ def _stream_ptr(x: DView) -> int:
     return torch.cuda.current_stream(x.buf.device).cuda_stream
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
 def _device_guard(x: DView):
-    return _torch().cuda.device(x.buf.device)
+    """Makes the tensor's device current for the call; free when it already is."""
+    cuda = _torch().cuda
+    dev = x.buf.device
+    if dev.type == "cuda" and dev.index == cuda.current_device():
+        return _NO_GUARD
+    return cuda.device(dev)
 
 
 def broadcast_shape(a: Sequence[int], b: Sequence[int]) -> tuple:
@@ -277,7 +299,7 @@ def binary(op: int, a, b, out=None):
     if out is None:
         out = _new_out(a, broadcast_shape(a.shape, b.shape))
     with _device_guard(a):
-        check(lib().ctb_binary(op, a.cview(), b.cview(), DView.of(out).cview(), _stream_ptr(a)))
+        check(lib().ctb_binary(op, a.cview(), b.cview(), _as_dview(out).cview(), _stream_ptr(a)))
     return out
 
 
@@ -286,7 +308,7 @@ def unary(op: int, a, scalar: float = 0.0, out=None):
     if out is None:
         out = _new_out(a, a.shape)
     with _device_guard(a):
-        check(lib().ctb_unary(op, a.cview(), float(scalar), DView.of(out).cview(), _stream_ptr(a)))
+        check(lib().ctb_unary(op, a.cview(), float(scalar), _as_dview(out).cview(), _stream_ptr(a)))
     return out
 
 
@@ -296,7 +318,7 @@ def contiguous(a, out=None):
     if out is None:
         out = _new_out(a, a.shape)
     with _device_guard(a):
-        check(lib().ctb_copy_strided(a.cview(), DView.of(out).cview(), _stream_ptr(a)))
+        check(lib().ctb_copy_strided(a.cview(), _as_dview(out).cview(), _stream_ptr(a)))
     return out
 
 
@@ -307,9 +329,9 @@ def reduce(op: int, a, dim: int = DIM_FULL, out=None, workspace=None):
         out = _new_out(a, reduced_shape(a.shape, dim), I32 if op == ARGMAX else None)
     with _device_guard(a):
         if workspace is None:
-            check(lib().ctb_reduce(op, a.cview(), dim, DView.of(out).cview(), _stream_ptr(a)))
+            check(lib().ctb_reduce(op, a.cview(), dim, _as_dview(out).cview(), _stream_ptr(a)))
         else:
-            check(lib().ctb_reduce_ws(op, a.cview(), dim, DView.of(out).cview(), workspace.data_ptr(),
+            check(lib().ctb_reduce_ws(op, a.cview(), dim, _as_dview(out).cview(), workspace.data_ptr(),
                                       workspace.numel() * workspace.element_size(), _stream_ptr(a)))
     return out
 
@@ -325,7 +347,7 @@ def reduce_dim_noalloc(op: int, a, dim: int, out):
     that array: keep them stream-ordered, and make the first call outside stream capture."""
     a = _as_dview(a)
     with _device_guard(a):
-        check(lib().ctb_reduce_dim_noalloc(op, a.cview(), dim, DView.of(out).cview(), _stream_ptr(a)))
+        check(lib().ctb_reduce_dim_noalloc(op, a.cview(), dim, _as_dview(out).cview(), _stream_ptr(a)))
     return out
 
 
@@ -349,7 +371,7 @@ def finalize_full(op: int, partial, total_count: int, out=None, dtype_code: int 
     if out is None:
         out = torch.empty(1, dtype=_torch_dtype(dtype_code), device=partial.device)
     with torch.cuda.device(partial.device):
-        check(lib().ctb_finalize_full(op, partial.data_ptr(), int(total_count), DView.of(out).cview(),
+        check(lib().ctb_finalize_full(op, partial.data_ptr(), int(total_count), _as_dview(out).cview(),
                                       torch.cuda.current_stream(partial.device).cuda_stream))
     return out
 
@@ -361,7 +383,7 @@ def softmax(x, mask=None, causal: bool = False, out=None):
         out = _new_out(x, x.shape)
     with _device_guard(x):
         check(lib().ctb_softmax_lastdim(x.cview(), None if m is None else m.cview(), int(causal),
-                                        DView.of(out).cview(), _stream_ptr(x)))
+                                        _as_dview(out).cview(), _stream_ptr(x)))
     return out
 
 
@@ -373,7 +395,7 @@ def log_softmax(x, mask=None, out=None):
         out = _new_out(x, x.shape)
     with _device_guard(x):
         check(lib().ctb_log_softmax_lastdim(x.cview(), None if m is None else m.cview(),
-                                            DView.of(out).cview(), _stream_ptr(x)))
+                                            _as_dview(out).cview(), _stream_ptr(x)))
     return out
 
 
@@ -386,7 +408,7 @@ def gather(x, dim: int, index, out=None):
         out = _new_out(x, idx.shape)
     bad = torch.zeros(1, dtype=torch.int32, device=x.buf.device)
     with _device_guard(x):
-        check(lib().ctb_gather(x.cview(), dim, idx.cview(), DView.of(out).cview(), bad.data_ptr(),
+        check(lib().ctb_gather(x.cview(), dim, idx.cview(), _as_dview(out).cview(), bad.data_ptr(),
                                _stream_ptr(x)))
     if int(bad.item()):
         raise CtbError(4, "Gather index out of bounds")
@@ -433,7 +455,7 @@ def cross_entropy(logits, labels, mean=True, out=None, bad=None):
     if out is None:
         out = _new_out(x, (1,))
     with _device_guard(x):
-        check(lib().ctb_cross_entropy(x.cview(), lab.cview(), int(mean), DView.of(out).cview(),
+        check(lib().ctb_cross_entropy(x.cview(), lab.cview(), int(mean), _as_dview(out).cview(),
                                       None if bad is None else bad.data_ptr(), _stream_ptr(x)))
     return out
 
@@ -444,7 +466,7 @@ def cross_entropy_backward(logits, labels, grad_scale, out=None, accumulate=Fals
     if out is None:
         out = _new_out(x, x.shape)
     with _device_guard(x):
-        check(lib().ctb_cross_entropy_backward(x.cview(), lab.cview(), float(grad_scale), DView.of(out).cview(),
+        check(lib().ctb_cross_entropy_backward(x.cview(), lab.cview(), float(grad_scale), _as_dview(out).cview(),
                                                int(accumulate), None if bad is None else bad.data_ptr(), _stream_ptr(x)))
     return out
 
@@ -457,7 +479,7 @@ def matmul(a, b, out=None):
         shape = (av.shape[-2], bv.shape[-1]) if len(av.shape) < 3 and len(bv.shape) < 3 else (batch, av.shape[-2], bv.shape[-1])
         out = _new_out(av, shape)
     with _device_guard(av):
-        check(lib().ctb_matmul(av.cview(), bv.cview(), DView.of(out).cview(), _stream_ptr(av)))
+        check(lib().ctb_matmul(av.cview(), bv.cview(), _as_dview(out).cview(), _stream_ptr(av)))
     return out
 
 
@@ -491,7 +513,7 @@ def batchnorm_apply(x, mean, var, gamma=None, beta=None, eps: float = 1e-5, out=
         out = _new_out(xv, xv.shape)
     with _device_guard(xv):
         check(lib().ctb_batchnorm_apply(xv.cview(), _as_dview(mean).cview(), _as_dview(var).cview(),
-                                        opt(gamma), opt(beta), float(eps), DView.of(out).cview(), _stream_ptr(xv)))
+                                        opt(gamma), opt(beta), float(eps), _as_dview(out).cview(), _stream_ptr(xv)))
     return out
 
 
@@ -517,7 +539,7 @@ def cat(tensors, dim: int = 0, out=None):
         check(lib().ctb_cat(arr, 0, dim, None, None))       # raises "cat_mp: empty list"
         return None
     with _device_guard(vs[0]):
-        check(lib().ctb_cat(arr, len(cviews), dim, DView.of(out).cview(), _stream_ptr(vs[0])))
+        check(lib().ctb_cat(arr, len(cviews), dim, _as_dview(out).cview(), _stream_ptr(vs[0])))
     return out
 
 
@@ -562,7 +584,7 @@ def layernorm(x, gamma=None, beta=None, eps: float = 1e-5, out=None):
     with _device_guard(x):
         check(lib().ctb_layernorm_lastdim(x.cview(), None if g is None else g.cview(),
                                           None if b is None else b.cview(), float(eps),
-                                          DView.of(out).cview(), _stream_ptr(x)))
+                                          _as_dview(out).cview(), _stream_ptr(x)))
     return out
 
 
