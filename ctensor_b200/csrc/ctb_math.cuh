@@ -225,15 +225,23 @@ __device__ __forceinline__ float2 sigmoid_cephes2(float2 x) {
     return t;
 }
 
-// ---- exact reformulations of the GELU chain that were measured and rejected -------------------------
-// Build-time alternatives (-DCTB_GELU_VARIANT=1|2), kept so that their profiler counters can be
-// reproduced; both give the bits of the shipped chain for every one of the 2^32 inputs.
-//   1: the fp32 -> fp64 widening of the two scalar multiplies done with integer instructions
-//      instead of the conversion unit (two XU operations per element fewer, five ALU operations more)
-//   2: the division of tanh without the reciprocal unit: a magic-constant first guess and three
-//      Newton steps (one XU operation per element fewer, six fp32 operations more)
+// ---- exact formulations of the GELU chain -----------------------------------------------------------
+// The chain has two scalar multiplies that the reference evaluates in double,
+// (float)((double)x * s).  Done with conversion instructions they cost four operations per element
+// on the conversion / special-function (XU) pipe, which — with the reciprocal of tanh — is the pipe
+// that bounds the kernel.  Build-time choice (-DCTB_GELU_VARIANT=n); every variant gives the same
+// bits for every one of the 2^32 inputs:
+//   0: conversion instructions (5 XU operations per element, 28.4 instructions)
+//   1: the fp32 -> fp64 widenings done with integer instructions (3 XU, 36 instructions): no faster
+//   2: the division of tanh from an integer first guess and three Newton steps instead of the
+//      reciprocal unit (4 XU, 30 instructions): no faster
+//   3: variant 1 on magnitudes — every step up to the argument of tanh is odd in x and rounds
+//      symmetrically, so the widenings need no sign handling (three integer instructions each) and
+//      the sign is put back once (3 XU, ~33 instructions): 3-6 % faster than 0, the more so when the
+//      SM clock is held down by the power cap.  This is what ships.
+//   4: 3 and 2 together (2 XU operations per element)
 #ifndef CTB_GELU_VARIANT
-#define CTB_GELU_VARIANT 0
+#define CTB_GELU_VARIANT 3
 #endif
 // (float)((double)x * s) with the widening done by integer instructions.  Exact for normal x; zero,
 // denormal, infinite and NaN inputs give other doubles, which the GELU chain does not notice.
@@ -242,6 +250,11 @@ __device__ __forceinline__ float mul_scalar_int_widen(float x, double s) {
     const uint32_t hi = (b & 0x80000000u) | (((b & 0x7fffffffu) >> 3) + 0x38000000u);
     const uint32_t lo = b << 29;
     return __double2float_rn(__dmul_rn(__hiloint2double((int)hi, (int)lo), s));
+}
+// The same for x >= 0 (no sign to carry): three integer instructions.
+__device__ __forceinline__ float mul_scalar_int_widen_pos(float x, double s) {
+    const uint32_t b = __float_as_uint(x);
+    return __double2float_rn(__dmul_rn(__hiloint2double((int)((b >> 3) + 0x38000000u), (int)(b << 29)), s));
 }
 // tanh_cephes2 with the reciprocal of (e + 1) from an integer first guess and three Newton steps
 __device__ __forceinline__ float2 tanh_cephes2_no_rcp_unit(float2 x) {
@@ -260,9 +273,8 @@ __device__ __forceinline__ float2 tanh_cephes2_no_rcp_unit(float2 x) {
     return __ffma2_rn(rem, r, q);
 }
 
-// The two double-precision scalar multiplies stay in double: an fp32 two-product emulation with a
-// near-tie check was bit-exact too but slower (it moves work from the conversion and fp64 pipes,
-// which otherwise idle, to the fp32 pipe, which is the busy one).
+// The two scalar multiplies stay double-precision multiplies: an fp32 two-product emulation with a
+// near-tie check was bit-exact too but slower (more fp32 instructions than it saves elsewhere).
 __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
 #if CTB_GELU_VARIANT == 1
     float2 u = __fmul2_rn(x, x);
@@ -273,6 +285,21 @@ __device__ __forceinline__ float2 gelu_tanh_chain2(float2 x) {
     u.x = mul_scalar_int_widen(u.x, 0.7978845608028654);
     u.y = mul_scalar_int_widen(u.y, 0.7978845608028654);
     float2 tv = tanh_cephes2(u);
+    tv = __fadd2_rn(tv, splat2(1.0f));
+    return __fmul2_rn(__fmul2_rn(x, splat2(0.5f)), tv);
+#elif CTB_GELU_VARIANT == 3 || CTB_GELU_VARIANT == 4
+    const float2 ax = make_float2(fabsf(x.x), fabsf(x.y));
+    float2 u = __fmul2_rn(__fmul2_rn(x, x), ax);
+    u.x = mul_scalar_int_widen_pos(u.x, 0.044715);
+    u.y = mul_scalar_int_widen_pos(u.y, 0.044715);
+    u = __fadd2_rn(ax, u);
+    u.x = __uint_as_float(__float_as_uint(mul_scalar_int_widen_pos(u.x, 0.7978845608028654)) | (__float_as_uint(x.x) & 0x80000000u));
+    u.y = __uint_as_float(__float_as_uint(mul_scalar_int_widen_pos(u.y, 0.7978845608028654)) | (__float_as_uint(x.y) & 0x80000000u));
+#if CTB_GELU_VARIANT == 4
+    float2 tv = tanh_cephes2_no_rcp_unit(u);
+#else
+    float2 tv = tanh_cephes2(u);
+#endif
     tv = __fadd2_rn(tv, splat2(1.0f));
     return __fmul2_rn(__fmul2_rn(x, splat2(0.5f)), tv);
 #elif CTB_GELU_VARIANT == 2
