@@ -126,12 +126,17 @@ __device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
 // exp_cephes for two lanes: clamp, fx and floor per lane; range reduction and polynomial packed.
 // `hi` may lower the upper clamp for callers that saturate earlier (tanh).
 __device__ __forceinline__ float2 exp_cephes2(float2 v, float hi = kExpHi) {
-    float x0 = v.x, x1 = v.y, f0, f1;
-    int32_t p0, p1;
-    exp_cephes_front(x0, f0, p0, hi);
-    exp_cephes_front(x1, f1, p1, hi);
+    // the front end of exp_cephes_front, lane for lane, with the three arithmetic steps packed:
+    // fx, the round-down add that takes floor(fx), and MAGIC - r (as fma(r, -1, MAGIC): the same
+    // single rounding of the same exact value)
+    const float x0 = fmaxf(fminf(v.x, hi), -kExpHi), x1 = fmaxf(fminf(v.y, hi), -kExpHi);
+    const float MAGIC = 12582912.0f;
+    const float2 fx = __ffma2_rn(make_float2(x0, x1), splat2(1.44269504088896341f), splat2(0.5f));
+    const float2 r = __fadd2_rd(fx, splat2(MAGIC));
+    const int32_t p0 = (__float_as_int(r.x) - (0x4B400000 - 127)) << 23;
+    const int32_t p1 = (__float_as_int(r.y) - (0x4B400000 - 127)) << 23;
+    const float2 nfx = __ffma2_rn(r, splat2(-1.0f), splat2(MAGIC));
     float2 x = make_float2(x0, x1);
-    const float2 nfx = make_float2(f0, f1);
     x = __ffma2_rn(nfx, splat2(0.693359375f), x);
     x = __ffma2_rn(nfx, splat2(-2.12194440e-4f), x);
     const float2 z = __fmul2_rn(x, x);
@@ -236,7 +241,7 @@ __device__ __forceinline__ float2 sigmoid_cephes2(float2 x) {
 //   2: the division of tanh from an integer first guess and three Newton steps instead of the
 //      reciprocal unit (4 XU, 30 instructions): no faster
 //   3: variant 1 on magnitudes — every step up to the argument of tanh is odd in x and rounds
-//      symmetrically, so the widenings need no sign handling (three integer instructions each) and
+//      symmetrically, so the widenings need no sign handling (two integer instructions each) and
 //      the sign is put back once (3 XU, ~33 instructions): 3-6 % faster than 0, the more so when the
 //      SM clock is held down by the power cap.  This is what ships.
 //   4: 3 and 2 together (2 XU operations per element)
@@ -251,10 +256,14 @@ __device__ __forceinline__ float mul_scalar_int_widen(float x, double s) {
     const uint32_t lo = b << 29;
     return __double2float_rn(__dmul_rn(__hiloint2double((int)hi, (int)lo), s));
 }
-// The same for x >= 0 (no sign to carry): three integer instructions.
+// The same for x >= 0 (no sign to carry) in two integer instructions: the bits of x shifted into a
+// double's layout WITHOUT re-biasing the exponent are the double x * 2^-896 — exactly, for zero and
+// denormal x too (m * 2^-149 becomes the denormal double m * 2^-1045) — and the scalar carries the
+// factor 2^896 instead (an exact scaling of both operands: the product and its rounding are those
+// of (double)x * s).  Infinite and NaN inputs give finite values, which the GELU chain does not notice.
 __device__ __forceinline__ float mul_scalar_int_widen_pos(float x, double s) {
     const uint32_t b = __float_as_uint(x);
-    return __double2float_rn(__dmul_rn(__hiloint2double((int)((b >> 3) + 0x38000000u), (int)(b << 29)), s));
+    return __double2float_rn(__dmul_rn(__hiloint2double((int)(b >> 3), (int)(b << 29)), s * 0x1p896));
 }
 // tanh_cephes2 with the reciprocal of (e + 1) from an integer first guess and three Newton steps
 __device__ __forceinline__ float2 tanh_cephes2_no_rcp_unit(float2 x) {
