@@ -95,11 +95,14 @@ def build_gen1(force: bool = False) -> str:
     src = os.path.join(GEN1_DIR, "ctensor_gen1.cpp")
     deps = [src, os.path.join(os.path.dirname(PKG), "include", "ctb200.h")]
     deps += [os.path.join(GEN1_DIR, "include", f) for f in os.listdir(os.path.join(GEN1_DIR, "include"))]
+    # the optimizer vocabulary and classes are shared with the second-generation layer
+    shared = os.path.join(HOST_DIR, "include")
+    deps += [os.path.join(shared, f) for f in ("ctb_optimizer.h", "optimizer_classes.h")]
     if not force and os.path.exists(GEN1_LIB) and os.path.getmtime(GEN1_LIB) >= max(map(os.path.getmtime, deps)) \
             and os.path.getmtime(GEN1_LIB) >= os.path.getmtime(LIB):
         return GEN1_LIB
     subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-o", GEN1_LIB, src,
-                           "-I", GEN1_DIR, "-L", PKG, "-lctb200", "-Wl,-rpath,$ORIGIN"])
+                           "-I", GEN1_DIR, "-I", shared, "-L", PKG, "-lctb200", "-Wl,-rpath,$ORIGIN"])
     return GEN1_LIB
 
 

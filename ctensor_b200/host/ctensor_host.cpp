@@ -206,6 +206,60 @@ void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src) {
     after_op();
 }
 
+bool has_grad(const Tensor& param) {
+    return param.impl && param.impl->grad && param.impl->grad->data && param.impl->grad->data->data;
+}
+void* storage_key(const Tensor& param) { return param.impl ? param.impl->data->data.get() : nullptr; }
+
+std::shared_ptr<float> optimizer_state(const Tensor& param) {
+    if (!param.impl) throw std::runtime_error("optimizer: null parameter");
+    use_device_of(param);
+    void* p = nullptr;
+    check(ctb_alloc(&p, param.numel() * sizeof(float), /*zero=*/1, nullptr));
+    const int index = device_index_of(param.device());
+    return std::shared_ptr<float>((float*)p, [index](float* q) {
+        // the block goes back to the pool of the GPU it came from; a failure here (process exit
+        // after the CUDA context is gone) is not reportable from a deleter
+        if (ctb_set_device(index) == CTB_OK) ctb_free(q, nullptr);
+        t_device_selected = index;
+    });
+}
+
+void optimizer_step(OptimizerKind kind, Tensor& param, float* state1, float* state2, const OptimizerHyper& hyper, int step) {
+    if (!has_grad(param)) return;
+    use_device_of(param);
+    Tensor g;
+    g.impl = param.impl->grad;
+    const ctb_view vp = view_of(param, "optimizer"), vg = view_of(g, "optimizer");
+    ctb_optimizer_hyper h;
+    h.lr = hyper.lr; h.beta1 = hyper.beta1; h.beta2 = hyper.beta2; h.eps = hyper.eps;
+    h.weight_decay = hyper.weight_decay; h.alpha = hyper.alpha;
+    check(ctb_optimizer_step((int)kind, &vp, &vg, state1, state2, &h, step, nullptr));
+    after_op();
+}
+
+void zero_grad(Tensor& param) {
+    if (!has_grad(param)) return;
+    Tensor g;
+    g.impl = param.impl->grad;
+    use_device_of(g);
+    // one zero element, broadcast over the buffer by the copy kernel (bits, so any 4- or 8-byte dtype)
+    static thread_local std::vector<std::shared_ptr<void>> zeros;        // per device
+    const int index = device_index_of(g.device());
+    if ((int)zeros.size() <= index) zeros.resize(index + 1);
+    if (!zeros[index]) {
+        void* z = nullptr;
+        check(ctb_alloc(&z, 8, /*zero=*/1, nullptr));
+        zeros[index] = std::shared_ptr<void>(z, [](void*) {});           // lives as long as the thread's context
+    }
+    ctb_view vg = view_of_bits(g), vz = vg;
+    vz.base = zeros[index].get();
+    vz.offset = 0;
+    for (int d = 0; d < vz.ndim; ++d) vz.stride[d] = 0;
+    check(ctb_copy_into(&vz, &vg, nullptr));
+    after_op();
+}
+
 void set_backward_entry(std::function<void(Tensor&)> f) { g_backward = std::move(f); }
 int last_dim_if_negative(const Tensor& t, int dim) {
     if (!t.impl) throw std::runtime_error("reduction: null input");

@@ -162,6 +162,51 @@ void set_device(int index) {
 int device() { return g_device; }
 void sync_for_host_access() { if (t_device_selected >= 0) check(ctb_device_sync()); }
 void set_grad_factory(GradFactory f) { g_grad_factory = std::move(f); }
+bool has_grad(const Tensor& param) { return param.impl && param.impl->storage && param.impl->storage->grad; }
+void* storage_key(const Tensor& param) { return param.impl && param.impl->storage ? param.impl->storage->data.get() : nullptr; }
+
+std::shared_ptr<float> optimizer_state(const Tensor& param) {
+    if (!param.impl) throw std::runtime_error("optimizer: null parameter");
+    ensure_device();
+    void* p = nullptr;
+    check(ctb_alloc(&p, param.numel() * sizeof(float), /*zero=*/1, nullptr));
+    return std::shared_ptr<float>((float*)p, [](float* q) { ctb_free(q, nullptr); });
+}
+
+namespace {
+// The gradient buffer as a view: the parameter's own geometry over impl->storage->grad.
+ctb_view grad_view_of(const Tensor& param) {
+    ctb_view v = view_of(param);
+    v.base = param.impl->storage->grad.get();
+    return v;
+}
+}  // namespace
+
+void optimizer_step(ctb_opt::Kind kind, Tensor& param, float* state1, float* state2, const ctb_opt::Hyper& hyper, int step) {
+    if (!has_grad(param)) return;
+    ensure_device();
+    const ctb_view vp = view_of(param), vg = grad_view_of(param);
+    ctb_optimizer_hyper h;
+    h.lr = hyper.lr; h.beta1 = hyper.beta1; h.beta2 = hyper.beta2; h.eps = hyper.eps;
+    h.weight_decay = hyper.weight_decay; h.alpha = hyper.alpha;
+    check(ctb_optimizer_step((int)kind, &vp, &vg, state1, state2, &h, step, nullptr));
+    after_op();
+}
+
+void zero_grad(Tensor& param) {
+    if (!has_grad(param)) return;
+    ensure_device();
+    // one zero element broadcast over the buffer by the copy kernel
+    static thread_local void* zero = nullptr;
+    if (!zero) check(ctb_alloc(&zero, 8, /*zero=*/1, nullptr));
+    ctb_view vg = grad_view_of(param), vz = vg;
+    vz.base = zero;
+    vz.offset = 0;
+    for (int d = 0; d < vz.ndim; ++d) vz.stride[d] = 0;
+    check(ctb_copy_into(&vz, &vg, nullptr));
+    after_op();
+}
+
 void set_backward_entry(std::function<void(Tensor&)> f) { g_backward = std::move(f); }
 }  // namespace ctb_gen1
 

@@ -4,6 +4,7 @@
 #include <memory>
 #include <string>
 #include <vector>
+#include "ctb_optimizer.h"
 #include "tensor1.h"
 
 namespace ctb_gen1 {
@@ -30,5 +31,17 @@ void set_grad_factory(GradFactory f);
 // The entry point behind Tensor::backward() (the reference's tensor1.cpp:471-475 calls the free
 // function backward(Tensor&) of autograd.cpp).
 void set_backward_entry(std::function<void(Tensor&)> f);
+
+// ---- optimizer steps: what this layer's train_utils.h is built on -----------------------------------------
+// One fused in-place update of `param` from its gradient buffer (impl->storage->grad) on the GPU,
+// with the arithmetic of the reference's optimizer classes (root train_utils.h:48-540).  Nothing
+// happens when the parameter has no gradient buffer.  `step` is the 1-based step count; state
+// vectors: numel fp32 zeros in device memory (optimizer_state), null where the optimizer has none.
+bool has_grad(const Tensor& param);
+void* storage_key(const Tensor& param);
+std::shared_ptr<float> optimizer_state(const Tensor& param);
+void optimizer_step(ctb_opt::Kind kind, Tensor& param, float* state1, float* state2, const ctb_opt::Hyper& hyper, int step);
+// Clears the gradient buffer on the GPU (Optimizer::zero_grad, root train_utils.h:37-44).
+void zero_grad(Tensor& param);
 
 }  // namespace ctb_gen1

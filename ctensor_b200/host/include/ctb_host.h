@@ -4,6 +4,7 @@
 #include <memory>
 #include <string>
 #include <vector>
+#include "ctb_optimizer.h"
 #include "tensor.h"
 
 namespace ctb_host {
@@ -41,6 +42,23 @@ const std::vector<size_t>& last_permutation();
 // grad_src summed first and NaN/Inf contributions skipped.  The autograd library calls this in
 // place of its host loop.
 void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src);
+
+// ---- optimizer steps: what the host layer's train_utils.h is built on ----------------------------------
+// One fused in-place update of `param` from its gradient buffer on the GPU, with the arithmetic of
+// the reference's optimizer classes (src/neuralnet/train_utils.h:50-494), expression for expression.
+// Nothing happens when the parameter has no gradient buffer (the reference's own check).
+using OptimizerKind = ctb_opt::Kind;
+using OptimizerHyper = ctb_opt::Hyper;
+// Whether the parameter has a gradient buffer, and the address its optimizer state is filed under
+// (the parameter's storage, like the reference's `states` maps).
+bool has_grad(const Tensor& param);
+void* storage_key(const Tensor& param);
+// A per-parameter state vector (moments): numel fp32 zeros in device memory on the parameter's GPU.
+std::shared_ptr<float> optimizer_state(const Tensor& param);
+// `step` is the 1-based step count; state1 / state2 as the optimizer needs them (null where unused).
+void optimizer_step(OptimizerKind kind, Tensor& param, float* state1, float* state2, const OptimizerHyper& hyper, int step);
+// Clears the parameter's gradient buffer on the GPU (Optimizer::zero_grad, :37-46).
+void zero_grad(Tensor& param);
 
 // Hook behind Tensor::backward(); the autograd library installs its backward(root) here.
 void set_backward_entry(std::function<void(Tensor&)> f);

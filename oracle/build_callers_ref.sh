@@ -42,7 +42,9 @@ cc2 avx512_f32   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_f32.cp
 cc2 avx512_d64   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_d64.cpp"
 cc2 layer        "-O2 -fopenmp"                 "$S/neuralnet/layer.cpp"
 cc2 loss         "-O2 -fopenmp"                 "$S/neuralnet/loss.cpp"
-cc2 program      "-O1"                          "$PROGRAM"
+# the program also includes the reference's train_utils.h (optimizers), whose own includes reach into
+# the data-loader and dashboard headers: the real tree is the last include path for those
+$CXX $STD -O1 $INC2 -I"$REF/src" -c "$PROGRAM" -o "$TMP/obj2/program.o" & pids+=($!)
 for p in "${pids[@]}"; do wait "$p"; done
 $CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
 # The same program with the dispatcher's CPU feature probes answering "no" (a command-line macro

@@ -32,7 +32,8 @@ LINK="-L$PKG -lctb200 -Wl,-rpath,\$ORIGIN/../../../ctensor_b200"
 # ---- second generation: src/core + src/neuralnet --------------------------------------------------
 G2="$TMP/gen2/src"
 mkdir -p "$G2/core" "$G2/neuralnet"
-for f in tensor.h device.h ops_dispatch.h opsmp.h ctb_host.h; do ln -s "$PKG/host/include/$f" "$G2/core/$f"; done
+for f in tensor.h device.h ops_dispatch.h opsmp.h ctb_host.h ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G2/core/$f"; done
+ln -s "$PKG/host/include/train_utils.h" "$G2/neuralnet/train_utils.h"      # replaces the reference's (optimizers, StepLR)
 for f in autograd.h autograd.cpp; do ln -s "$REF/src/core/$f" "$G2/core/$f"; done                        # unchanged
 for f in layer.h layer.cpp loss.h loss.cpp module.h; do ln -s "$REF/src/neuralnet/$f" "$G2/neuralnet/$f"; done   # unchanged
 ln -s "$PKG/host/glue/autograd_glue.cpp" "$G2/core/autograd_glue.cpp"
@@ -44,7 +45,8 @@ $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/callers_gen2_b200" \
 if [ -f "$PKG/libctensor_gen1.so" ]; then
   G1="$TMP/gen1"
   mkdir -p "$G1"
-  for f in tensor1.h opsmp.h ops1.h ctb_gen1.h; do ln -s "$PKG/host/gen1/include/$f" "$G1/$f"; done
+  for f in tensor1.h opsmp.h ops1.h ctb_gen1.h train_utils.h; do ln -s "$PKG/host/gen1/include/$f" "$G1/$f"; done
+  for f in ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G1/$f"; done
   for f in autograd.h autograd.cpp layer.h layer.cpp loss.h loss.cpp module.h; do ln -s "$REF/$f" "$G1/$f"; done   # unchanged
   ln -s "$PKG/host/gen1/autograd_glue_gen1.cpp" "$G1/autograd_glue_gen1.cpp"
   $CXX $FLAGS -DCTB_GEN1 -I"$G1" -o "$OUT/callers_gen1_b200" \

@@ -1,6 +1,7 @@
 // One program, four builds: the reference's own callers of the operator path — autograd.cpp,
 // layer.cpp, loss.cpp, unchanged — driven through a Linear layer, two losses and a chain of
-// elementwise operators, forward and backward.
+// elementwise operators, forward and backward, and — with the optimizer classes of train_utils.h —
+// through three training steps per optimizer.
 //
 //   build                      tensor/operator layer                     callers
 //   callers_gen2_ref           the reference's src/core (CPU)            the reference's, unchanged
@@ -15,8 +16,12 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 #include <exception>
+#include <iomanip>          // the reference's train_utils.h uses std::setprecision without including it
+#include <iostream>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #ifdef CTB_GEN1
@@ -25,6 +30,7 @@
 #include "autograd.h"
 #include "layer.h"
 #include "loss.h"
+#include "train_utils.h"
 #define DATA(t) ((t).impl->storage->data.get())
 #define GRAD(t) ((t).impl->storage->grad.get())
 #define F_EXP exp_mp
@@ -44,6 +50,7 @@ static Tensor sum_all(Tensor t) {
 #include "core/autograd.h"
 #include "neuralnet/layer.h"
 #include "neuralnet/loss.h"
+#include "neuralnet/train_utils.h"
 #define DATA(t) ((t).impl->data->data.get())
 #define GRAD(t) ((t).impl->grad ? (t).impl->grad->data->data.get() : nullptr)
 #define F_EXP exp
@@ -185,5 +192,39 @@ int main() {
         print_grad("rowmean.grad_a", a);
 #endif
     });
+    // Three training steps of Linear -> CrossEntropy with each optimizer class of train_utils.h:
+    // zero_grad, forward, backward, step — the loop a user of the reference writes.  In the *_b200
+    // builds the classes are the host layer's (one fused kernel per parameter and step).
+    auto train = [&](const char* name, auto make_optimizer) {
+        section(name, [&] {
+            Linear lin((int)in_f, (int)out_f, true, DType::Float32);
+            lin.weight = filled({out_f, in_f}, 21, 0.5, true);
+            lin.bias = filled({out_f}, 22, 0.1, true);
+            Tensor x = filled({batch, in_f}, 23, 1.0, false);
+            Tensor labels({batch, 1}, DType::Int32, false);
+            for (size_t i = 0; i < batch; ++i) write_scalar_at(DATA(labels), i, DType::Int32, (double)((i * 3 + 1) % out_f));
+            std::vector<Tensor*> params = {&lin.weight, &lin.bias};
+            auto opt = make_optimizer(params);
+            std::string tag(name);
+            for (int it = 0; it < 3; ++it) {
+                opt.zero_grad();
+                Tensor loss = Loss::CrossEntropy(lin.forward(x), labels, "mean");
+                if (it == 2) print_data((tag + ".loss").c_str(), loss);
+                loss.backward();
+                opt.step();
+            }
+            print_data((tag + ".weight").c_str(), lin.weight);
+            print_data((tag + ".bias").c_str(), lin.bias);
+        });
+    };
+    train("optim_sgd", [](std::vector<Tensor*>& p) { return SGD(p, 0.1); });
+    train("optim_adam", [](std::vector<Tensor*>& p) { return Adam(p, 0.01); });
+    train("optim_adamw", [](std::vector<Tensor*>& p) { return AdamW(p, 0.01, 0.9, 0.999, 1e-8, 0.05); });
+    train("optim_adamax", [](std::vector<Tensor*>& p) { return Adamax(p, 0.01); });
+    train("optim_nadam", [](std::vector<Tensor*>& p) { return NAdam(p, 0.01); });
+    train("optim_radam", [](std::vector<Tensor*>& p) { return RAdam(p, 0.01); });
+    train("optim_rmsprop", [](std::vector<Tensor*>& p) { return RMSprop(p, 0.01); });
+    train("optim_adagrad", [](std::vector<Tensor*>& p) { return Adagrad(p, 0.05); });
+    train("optim_lion", [](std::vector<Tensor*>& p) { return Lion(p, 0.01, 0.9, 0.99, 0.05); });
     return 0;
 }

@@ -138,17 +138,22 @@ def _known_losses():
 @pytest.mark.gpu
 def test_first_generation_callers_run_on_the_gpu_like_the_reference():
     got, want = run_built("callers_gen1_b200"), golden("callers_gen1_ref")
-    assert_lines_match(got, want, [k for k, v in want.items() if isinstance(v, np.ndarray)], "gen 1")
+    names = [k for k, v in want.items() if isinstance(v, np.ndarray)]
+    assert sum(k.startswith("optim_") for k in names) == 27          # loss, weight, bias of nine optimizers
+    assert_lines_match(got, want, names, "gen 1")
 
 
 @pytest.mark.gpu
 def test_second_generation_callers_run_on_the_gpu_like_the_reference():
     got, want = run_built("callers_gen2_b200"), golden("callers_gen2_ref_scalar")
-    dim_minus_one = {"mse.loss", "ce.loss"}
+    # (the loss lines of the optimizer sections are CrossEntropy values too: same dim = -1 question)
+    dim_minus_one = {"mse.loss", "ce.loss"} | {k for k in want if k.startswith("optim_") and k.endswith(".loss")}
     names = [k for k, v in want.items() if isinstance(v, np.ndarray) and k not in dim_minus_one]
-    assert len(names) >= 15
+    assert len(names) >= 15 + 18                            # + weight and bias after three steps of nine optimizers
     assert_lines_match(got, want, names, "gen 2")
     mse, ce = _known_losses()
     np.testing.assert_allclose(got["mse.loss"], [mse], rtol=RTOL, err_msg="Loss::MSE")
     np.testing.assert_allclose(got["ce.loss"], [ce], rtol=RTOL, err_msg="Loss::CrossEntropy")
     np.testing.assert_allclose(got["mse.loss_from_operators"], [mse], rtol=RTOL)
+    for k in sorted(dim_minus_one):
+        assert isinstance(got[k], np.ndarray) and got[k].size == 1 and np.isfinite(got[k][0]) and 0.0 < got[k][0] < 5.0, k
