@@ -95,9 +95,17 @@ inline Tensor operator*(const Tensor& a, const Tensor& b) { return mul(a, b); }
 inline Tensor operator*(const Tensor& a, double s) { return mul_scalar(a, s); }
 inline Tensor operator*(double s, const Tensor& a) { return mul_scalar(a, s); }
 inline Tensor operator/(const Tensor& a, const Tensor& b) { return div(a, b); }
-// The reference's header routes Tensor / double to sub_scalar (src/core/ops_dispatch.h:84, a
-// typo there); this library divides.
+// The reference's header routes Tensor / double to sub_scalar (src/core/ops_dispatch.h:84, a typo
+// there) and callers are compiled against it: the input gradient of its BatchNorm
+// (src/neuralnet/batchnorm/batchnorm.cpp:186, `inv_std / M`) is what that typo makes of it.  A
+// drop-in gives the callers the numbers they get from the reference, so the operator does the same
+// here; define CTB_SCALAR_DIVISION_DIVIDES to get a division (div_scalar is the named function
+// for it either way).
+#ifdef CTB_SCALAR_DIVISION_DIVIDES
 inline Tensor operator/(const Tensor& a, double s) { return div_scalar(a, s); }
+#else
+inline Tensor operator/(const Tensor& a, double s) { return sub_scalar(a, s); }
+#endif
 inline Tensor operator/(double s, const Tensor& a) { return div_scalar_rev(s, a); }
 inline Tensor operator^(const Tensor& a, const Tensor& b) { return pow(a, b); }
 inline Tensor operator^(const Tensor& a, double s) { return pow_scalar(a, s); }

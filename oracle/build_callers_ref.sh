@@ -6,7 +6,7 @@
 #
 # Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref.
 #   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
-#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp
+#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, batchnorm/batchnorm.cpp
 #   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp
 # All sources are compiled where they lie (the second generation through the patched symlink
 # farm of ref_farm.sh); nothing is copied into the repository.
@@ -26,6 +26,8 @@ CXX="${REF_CXX:-g++}"
 STD="-std=gnu++20 -w"
 mkdir -p "$TMP/obj2" "$TMP/obj1" "$TMP/src/neuralnet"
 for f in layer.cpp layer.h loss.cpp loss.h module.h; do ln -s "$REF/src/neuralnet/$f" "$TMP/src/neuralnet/$f"; done
+mkdir -p "$TMP/src/neuralnet/batchnorm"
+for f in batchnorm.cpp batchnorm.h; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$TMP/src/neuralnet/batchnorm/$f"; done
 
 # ---- second generation ------------------------------------------------------------------------
 S="$TMP/src"
@@ -42,6 +44,7 @@ cc2 avx512_f32   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_f32.cp
 cc2 avx512_d64   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_d64.cpp"
 cc2 layer        "-O2 -fopenmp"                 "$S/neuralnet/layer.cpp"
 cc2 loss         "-O2 -fopenmp"                 "$S/neuralnet/loss.cpp"
+cc2 batchnorm    "-O2 -fopenmp"                 "$S/neuralnet/batchnorm/batchnorm.cpp"
 # the program also includes the reference's train_utils.h (optimizers), whose own includes reach into
 # the data-loader and dashboard headers: the real tree is the last include path for those
 $CXX $STD -O1 $INC2 -I"$REF/src" -c "$PROGRAM" -o "$TMP/obj2/program.o" & pids+=($!)

@@ -36,10 +36,12 @@ for f in tensor.h device.h ops_dispatch.h opsmp.h ctb_host.h ctb_optimizer.h opt
 ln -s "$PKG/host/include/train_utils.h" "$G2/neuralnet/train_utils.h"      # replaces the reference's (optimizers, StepLR)
 for f in autograd.h autograd.cpp; do ln -s "$REF/src/core/$f" "$G2/core/$f"; done                        # unchanged
 for f in layer.h layer.cpp loss.h loss.cpp module.h; do ln -s "$REF/src/neuralnet/$f" "$G2/neuralnet/$f"; done   # unchanged
+mkdir -p "$G2/neuralnet/batchnorm"
+for f in batchnorm.h batchnorm.cpp; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$G2/neuralnet/batchnorm/$f"; done      # unchanged
 ln -s "$PKG/host/glue/autograd_glue.cpp" "$G2/core/autograd_glue.cpp"
 $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/callers_gen2_b200" \
     "$HERE/callers_program.cpp" "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" \
-    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" -lctensor_host $LINK
+    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" -lctensor_host $LINK
 
 # ---- first generation: the root of the reference tree ----------------------------------------------
 if [ -f "$PKG/libctensor_gen1.so" ]; then

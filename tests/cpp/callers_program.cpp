@@ -51,6 +51,8 @@ static Tensor sum_all(Tensor t) {
 #include "neuralnet/layer.h"
 #include "neuralnet/loss.h"
 #include "neuralnet/train_utils.h"
+#include "neuralnet/batchnorm/batchnorm.h"
+#define CTB_HAVE_BATCHNORM 1
 #define DATA(t) ((t).impl->data->data.get())
 #define GRAD(t) ((t).impl->grad ? (t).impl->grad->data->data.get() : nullptr)
 #define F_EXP exp
@@ -192,6 +194,30 @@ int main() {
         print_grad("rowmean.grad_a", a);
 #endif
     });
+#ifdef CTB_HAVE_BATCHNORM
+    // BatchNorm (src/neuralnet/batchnorm/batchnorm.cpp, unchanged): training-mode forward over
+    // x[N, C, H, W] (permute, reshape, mean, sub, mul, pow_scalar, broadcasts), its backward node,
+    // the running statistics, and the inference-mode forward
+    section("bn", [&] {
+        BatchNorm bn(3);
+        bn.gamma = filled({3}, 31, 0.5, true, 1.0);
+        bn.beta = filled({3}, 32, 0.1, true);
+        Tensor x = filled({4, 3, 5, 5}, 33, 1.0, true);
+        Tensor y = bn.forward(x);
+        print_data("bn.forward", y);
+        print_data("bn.running_mean", bn.running_mean);
+        print_data("bn.running_var", bn.running_var);
+        Tensor total = F_SUM_ALL(y * y);
+        print_data("bn.value", total);
+        total.backward();
+        print_grad("bn.grad_x", x);
+        print_grad("bn.grad_gamma", bn.gamma);
+        print_grad("bn.grad_beta", bn.beta);
+        bn.eval();
+        print_data("bn.eval_forward", bn.forward(x));
+    });
+#endif
+
     // Three training steps of Linear -> CrossEntropy with each optimizer class of train_utils.h:
     // zero_grad, forward, backward, step — the loop a user of the reference writes.  In the *_b200
     // builds the classes are the host layer's (one fused kernel per parameter and step).

@@ -46,7 +46,8 @@ int main() {
     CHECK_NEAR((b - a)[1][1], 1.0, 1e-5);
     CHECK_NEAR((a * b)[0][1], 6.0, 1e-5);
     CHECK_NEAR((a / b)[1][0], 2.0 / 3.0, 1e-5);
-    CHECK_NEAR((a / 4.0)[0][0], 0.5, 1e-6);
+    CHECK_NEAR(div_scalar(a, 4.0)[0][0], 0.5, 1e-6);
+    CHECK_NEAR((a / 4.0)[0][0], 2.0 - 4.0, 1e-6);          // Tensor / double is sub_scalar, as in the reference's header (ops_dispatch.h:84)
     CHECK_NEAR((1.0 - a)[0][0], -1.0, 1e-6);
 
     // reductions (test/test_ops.cpp:113-128): dim = -1 reduces everything to shape {1}
@@ -113,7 +114,7 @@ int main() {
 
     // integer semantics (test/test_ops.cpp:203-213): truncation
     Tensor i3 = Tensor::from_vector({3, 5}, {2}, DType::Int32);
-    CHECK((int)double((i3 / 2.0)[0]) == 1 && (int)double((i3 / 2.0)[1]) == 2);
+    CHECK((int)double(div_scalar(i3, 2.0)[0]) == 1 && (int)double(div_scalar(i3, 2.0)[1]) == 2);
     CHECK((int)double(Tensor::from_vector({1.5, 2.5}, {2}).astype(DType::Int32)[1]) == 2);
 
     // fused rows
