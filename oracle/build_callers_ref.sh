@@ -6,8 +6,9 @@
 #
 # Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref.
 #   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
-#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, batchnorm/batchnorm.cpp
-#   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp
+#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp
+#   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp,
+#          batchnorm.cpp, Relu.cpp
 # All sources are compiled where they lie (the second generation through the patched symlink
 # farm of ref_farm.sh); nothing is copied into the repository.
 set -euo pipefail
@@ -25,7 +26,7 @@ make_ref_farm "$REF" "$TMP"
 CXX="${REF_CXX:-g++}"
 STD="-std=gnu++20 -w"
 mkdir -p "$TMP/obj2" "$TMP/obj1" "$TMP/src/neuralnet"
-for f in layer.cpp layer.h loss.cpp loss.h module.h; do ln -s "$REF/src/neuralnet/$f" "$TMP/src/neuralnet/$f"; done
+for f in layer.cpp layer.h loss.cpp loss.h module.h Relu.cpp Relu.h; do ln -s "$REF/src/neuralnet/$f" "$TMP/src/neuralnet/$f"; done
 mkdir -p "$TMP/src/neuralnet/batchnorm"
 for f in batchnorm.cpp batchnorm.h; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$TMP/src/neuralnet/batchnorm/$f"; done
 
@@ -45,6 +46,7 @@ cc2 avx512_d64   "-O3 -mavx512f -mavx512dq"     "$S/cpu/AVX512/ops_avx512_d64.cp
 cc2 layer        "-O2 -fopenmp"                 "$S/neuralnet/layer.cpp"
 cc2 loss         "-O2 -fopenmp"                 "$S/neuralnet/loss.cpp"
 cc2 batchnorm    "-O2 -fopenmp"                 "$S/neuralnet/batchnorm/batchnorm.cpp"
+cc2 relu         "-O2 -fopenmp"                 "$S/neuralnet/Relu.cpp"
 # the program also includes the reference's train_utils.h (optimizers), whose own includes reach into
 # the data-loader and dashboard headers: the real tree is the last include path for those
 $CXX $STD -O1 $INC2 -I"$REF/src" -c "$PROGRAM" -o "$TMP/obj2/program.o" & pids+=($!)
@@ -62,7 +64,7 @@ $CXX -o "$OUT/callers_gen2_ref_scalar" "$TMP"/obj2/*.o -fopenmp
 # ---- first generation (root of the reference tree) -----------------------------------------------
 pids=()
 cc1() { $CXX $STD -O2 -fopenmp -DCTB_GEN1 -I"$REF" -c "$2" -o "$TMP/obj1/$1.o" & pids+=($!); }
-for f in tensor1 opsmp autograd layer loss data; do cc1 "$f" "$REF/$f.cpp"; done
+for f in tensor1 opsmp autograd layer loss data batchnorm Relu; do cc1 "$f" "$REF/$f.cpp"; done
 cc1 program "$PROGRAM"
 for p in "${pids[@]}"; do wait "$p"; done
 $CXX -o "$OUT/callers_gen1_ref" "$TMP"/obj1/*.o -fopenmp

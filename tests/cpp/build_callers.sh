@@ -1,6 +1,7 @@
 #!/usr/bin/env bash
 # Builds tests/cpp/callers_program.cpp against the B200 host layers together with the
-# reference's own callers of the operator path — autograd.cpp, layer.cpp, loss.cpp — UNCHANGED:
+# reference's own callers of the operator path — autograd.cpp, layer.cpp, loss.cpp, batchnorm.cpp,
+# Relu.cpp — UNCHANGED:
 # the proof that the host layers are drop-in replacements for the reference's tensor/operator files.
 #
 #   tests/cpp/build_callers.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
@@ -35,13 +36,13 @@ mkdir -p "$G2/core" "$G2/neuralnet"
 for f in tensor.h device.h ops_dispatch.h opsmp.h ctb_host.h ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G2/core/$f"; done
 ln -s "$PKG/host/include/train_utils.h" "$G2/neuralnet/train_utils.h"      # replaces the reference's (optimizers, StepLR)
 for f in autograd.h autograd.cpp; do ln -s "$REF/src/core/$f" "$G2/core/$f"; done                        # unchanged
-for f in layer.h layer.cpp loss.h loss.cpp module.h; do ln -s "$REF/src/neuralnet/$f" "$G2/neuralnet/$f"; done   # unchanged
+for f in layer.h layer.cpp loss.h loss.cpp module.h Relu.h Relu.cpp; do ln -s "$REF/src/neuralnet/$f" "$G2/neuralnet/$f"; done   # unchanged
 mkdir -p "$G2/neuralnet/batchnorm"
 for f in batchnorm.h batchnorm.cpp; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$G2/neuralnet/batchnorm/$f"; done      # unchanged
 ln -s "$PKG/host/glue/autograd_glue.cpp" "$G2/core/autograd_glue.cpp"
 $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/callers_gen2_b200" \
     "$HERE/callers_program.cpp" "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" \
-    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" -lctensor_host $LINK
+    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" "$G2/neuralnet/Relu.cpp" -lctensor_host $LINK
 
 # ---- first generation: the root of the reference tree ----------------------------------------------
 if [ -f "$PKG/libctensor_gen1.so" ]; then
@@ -49,10 +50,10 @@ if [ -f "$PKG/libctensor_gen1.so" ]; then
   mkdir -p "$G1"
   for f in tensor1.h opsmp.h ops1.h ctb_gen1.h train_utils.h; do ln -s "$PKG/host/gen1/include/$f" "$G1/$f"; done
   for f in ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G1/$f"; done
-  for f in autograd.h autograd.cpp layer.h layer.cpp loss.h loss.cpp module.h; do ln -s "$REF/$f" "$G1/$f"; done   # unchanged
+  for f in autograd.h autograd.cpp layer.h layer.cpp loss.h loss.cpp module.h batchnorm.h batchnorm.cpp Relu.h Relu.cpp; do ln -s "$REF/$f" "$G1/$f"; done   # unchanged
   ln -s "$PKG/host/gen1/autograd_glue_gen1.cpp" "$G1/autograd_glue_gen1.cpp"
   $CXX $FLAGS -DCTB_GEN1 -I"$G1" -o "$OUT/callers_gen1_b200" \
       "$HERE/callers_program.cpp" "$G1/autograd.cpp" "$G1/autograd_glue_gen1.cpp" "$G1/layer.cpp" "$G1/loss.cpp" \
-      -lctensor_gen1 $LINK
+      "$G1/batchnorm.cpp" "$G1/Relu.cpp" -lctensor_gen1 $LINK
 fi
 echo "built $(ls "$OUT" | tr '\n' ' ')"

@@ -1,7 +1,8 @@
 // One program, four builds: the reference's own callers of the operator path — autograd.cpp,
 // layer.cpp, loss.cpp, unchanged — driven through a Linear layer, two losses and a chain of
 // elementwise operators, forward and backward, and — with the optimizer classes of train_utils.h —
-// through three training steps per optimizer.
+// through three training steps per optimizer; plus the reference's BatchNorm and activation modules
+// (batchnorm.cpp, Relu.cpp), unchanged as well.
 //
 //   build                      tensor/operator layer                     callers
 //   callers_gen2_ref           the reference's src/core (CPU)            the reference's, unchanged
@@ -31,6 +32,9 @@
 #include "layer.h"
 #include "loss.h"
 #include "train_utils.h"
+#include "batchnorm.h"
+#include "Relu.h"
+#define CTB_HAVE_BATCHNORM 1
 #define DATA(t) ((t).impl->storage->data.get())
 #define GRAD(t) ((t).impl->storage->grad.get())
 #define F_EXP exp_mp
@@ -52,6 +56,7 @@ static Tensor sum_all(Tensor t) {
 #include "neuralnet/loss.h"
 #include "neuralnet/train_utils.h"
 #include "neuralnet/batchnorm/batchnorm.h"
+#include "neuralnet/Relu.h"
 #define CTB_HAVE_BATCHNORM 1
 #define DATA(t) ((t).impl->data->data.get())
 #define GRAD(t) ((t).impl->grad ? (t).impl->grad->data->data.get() : nullptr)
@@ -217,6 +222,27 @@ int main() {
         print_data("bn.eval_forward", bn.forward(x));
     });
 #endif
+
+    // The activation modules of Relu.cpp (unchanged): Relu, LeakyRelu and PRelu with their own
+    // backward nodes (host loops over the storage the operators produced)
+    section("act", [&] {
+        Tensor x = filled({6, 8}, 41, 2.0, true);
+        Relu relu_module;
+        print_data("act.relu", relu_module.forward(x));
+        Tensor leaky = LeakyRelu(x, 0.1);
+        print_data("act.leaky", leaky);
+        Tensor total = F_SUM_ALL(leaky * leaky);
+        total.backward();
+        print_grad("act.leaky_grad_x", x);
+        Tensor z = filled({6, 8}, 42, 2.0, true);
+        PRelu prelu(1, 0.25);
+        Tensor pz = prelu.forward(z);
+        print_data("act.prelu", pz);
+        Tensor total2 = F_SUM_ALL(pz * pz);
+        total2.backward();
+        print_grad("act.prelu_grad_x", z);
+        print_grad("act.prelu_grad_weight", prelu.weight);
+    });
 
     // Three training steps of Linear -> CrossEntropy with each optimizer class of train_utils.h:
     // zero_grad, forward, backward, step — the loop a user of the reference writes.  In the *_b200
