@@ -44,6 +44,14 @@ $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/callers_gen2_b200" \
     "$HERE/callers_program.cpp" "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" \
     "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" "$G2/neuralnet/Relu.cpp" -lctensor_host $LINK
 
+# The convolution and pooling modules are not part of the operator path (their loops run on the
+# host, over the managed storage); they must still COMPILE against the replaced headers.
+mkdir -p "$G2/neuralnet/conv" "$G2/neuralnet/pooling"
+for d in conv pooling; do for f in $d.h $d.cpp; do ln -s "$REF/src/neuralnet/$d/$f" "$G2/neuralnet/$d/$f"; done; done
+for d in conv pooling; do
+  $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -c "$G2/neuralnet/$d/$d.cpp" -o "$TMP/$d.o"
+done
+
 # ---- first generation: the root of the reference tree ----------------------------------------------
 if [ -f "$PKG/libctensor_gen1.so" ]; then
   G1="$TMP/gen1"
