@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libctb200.so")
 MAX_DIMS = 8
 
 # dtypes (reference DType numbering)
-F32, I32, F64 = 0, 1, 2
+F32, I32, F64, U8, U16, U32, U64, I8, I16, I64, BOOL = range(11)        # the reference's DType numbering
 # binary operators
 ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE, POW = range(11)
 # unary operators
@@ -185,14 +185,27 @@ def _torch():
 def _dtype_code(t) -> int:
     torch = _torch()
     try:
-        return {torch.float32: F32, torch.int32: I32, torch.float64: F64}[t.dtype]
+        return _TORCH_CODES[t.dtype] if _TORCH_CODES else _torch_codes()[t.dtype]
     except KeyError:
         raise CtbError(3, f"unsupported dtype {t.dtype}")
 
 
-def _torch_dtype(code: int):
+_TORCH_CODES: dict = {}
+
+
+def _torch_codes() -> dict:
+    """torch dtype -> element-type code (the reference's DType numbering)."""
     torch = _torch()
-    return {F32: torch.float32, I32: torch.int32, F64: torch.float64}[code]
+    _TORCH_CODES.update({torch.float32: F32, torch.int32: I32, torch.float64: F64, torch.uint8: U8, torch.int8: I8,
+                         torch.int16: I16, torch.int64: I64, torch.bool: BOOL})
+    for name, code in (("uint16", U16), ("uint32", U32), ("uint64", U64)):      # copy-only types; newer torch has them
+        if hasattr(torch, name):
+            _TORCH_CODES[getattr(torch, name)] = code
+    return _TORCH_CODES
+
+
+def _torch_dtype(code: int):
+    return {v: k for k, v in _torch_codes().items()}[code]
 
 
 @dataclass

@@ -97,8 +97,16 @@ int ensure_workspace(size_t bytes, void** out, cudaStream_t st) {
     return CTB_OK;
 }
 
-size_t dtype_bytes(int dt) { return dt == CTB_F64 ? 8 : 4; }
-bool dtype_ok(int dt) { return dt == CTB_F32 || dt == CTB_I32 || dt == CTB_F64; }
+size_t dtype_bytes(int dt) {
+    switch (dt) {
+    case CTB_F64: case CTB_U64: case CTB_I64: return 8;
+    case CTB_U16: case CTB_I16: return 2;
+    case CTB_U8: case CTB_I8: case CTB_BOOL: return 1;
+    }
+    return 4;
+}
+// A dtype the library knows; what a given operator accepts is decided where it is launched.
+bool dtype_ok(int dt) { return dt >= CTB_F32 && dt <= CTB_BOOL; }
 
 int64_t view_numel(const ctb_view* v) {
     int64_t n = 1;
@@ -333,7 +341,7 @@ int reduce_arg_check(int op, const ctb_view* a, int dim) {
     int rc = check_view(a, "reduction: null input", "reduction");
     if (rc) return rc;
     if (op < 0 || op >= CTB_REDUCE_OP_COUNT) return set_error(CTB_ERR_ARG, "reduction: unknown operator code %d", op);
-    if (op == CTB_VAR && a->dtype == CTB_I32)
+    if (op == CTB_VAR && a->dtype != CTB_F32 && a->dtype != CTB_F64)
         return set_error(CTB_ERR_DTYPE, "var: not defined for integer tensors");
     if (op == CTB_ARGMAX) {
         if (dim < 0 || dim >= a->ndim) return set_error(CTB_ERR_DIM, "argmax: dim out of range");

@@ -334,6 +334,26 @@ bool plan_is_rows(const Plan& p) {
     return true;
 }
 
+// The general strided kernel alone: what the element types outside Float32 / Int32 / Double64 use
+// (the reference serves them through its type-erased scalar loop as well).
+template <typename F, typename T, int NIN>
+int launch_gather_shape(const Plan& p, const T* a, const T* b, T* out, double scalar, cudaStream_t st) {
+    GatherArgs ga{};
+    dimset_init(&ga.dims, p.ndim, p.shape);
+    for (int d = 0; d < p.ndim; ++d)
+        for (int i = 0; i < NIN; ++i) ga.stride[i][d] = p.stride[i][d];
+    ga.numel = p.numel;
+    int64_t blocks = ceil_div(p.numel, 256);
+    if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
+    if (p.out_strided) {
+        for (int d = 0; d < p.ndim; ++d) ga.stride[2][d] = p.ostride[d];
+        ew_gather_kernel<F, T, NIN, true><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
+    } else {
+        ew_gather_kernel<F, T, NIN, false><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
+    }
+    return cuda_error(cudaGetLastError(), "ew_gather launch");
+}
+
 template <typename F, typename T, int NIN>
 int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, cudaStream_t st) {
     constexpr int THREADS = CTB_EW_THREADS;
@@ -427,20 +447,7 @@ int launch_shapes(const Plan& p, const T* a, const T* b, T* out, double scalar, 
         }
     }
 
-    GatherArgs ga{};
-    dimset_init(&ga.dims, p.ndim, p.shape);
-    for (int d = 0; d < p.ndim; ++d)
-        for (int i = 0; i < NIN; ++i) ga.stride[i][d] = p.stride[i][d];
-    ga.numel = p.numel;
-    int64_t blocks = ceil_div(p.numel, 256);
-    if (blocks > 0x7FFFFFFFll) blocks = 0x7FFFFFFFll;
-    if (p.out_strided) {
-        for (int d = 0; d < p.ndim; ++d) ga.stride[2][d] = p.ostride[d];
-        ew_gather_kernel<F, T, NIN, true><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
-    } else {
-        ew_gather_kernel<F, T, NIN, false><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, ga, scalar);
-    }
-    return cuda_error(cudaGetLastError(), "ew_gather launch");
+    return launch_gather_shape<F, T, NIN>(p, a, b, out, scalar, st);
 }
 
 template <int OP>
@@ -449,6 +456,9 @@ int launch_binary_dt(int dtype, const Plan& p, const void* a, const void* b, voi
     case CTB_F32: return launch_shapes<BinAdapter<OP, float>, float, 2>(p, (const float*)a, (const float*)b, (float*)out, 0.0, st);
     case CTB_I32: return launch_shapes<BinAdapter<OP, int32_t>, int32_t, 2>(p, (const int32_t*)a, (const int32_t*)b, (int32_t*)out, 0.0, st);
     case CTB_F64: return launch_shapes<BinAdapter<OP, double>, double, 2>(p, (const double*)a, (const double*)b, (double*)out, 0.0, st);
+#define CTB_NARROW(CODE, T) case CODE: return launch_gather_shape<BinAdapter<OP, T>, T, 2>(p, (const T*)a, (const T*)b, (T*)out, 0.0, st);
+    CTB_NARROW(CTB_U8, uint8_t) CTB_NARROW(CTB_I8, int8_t) CTB_NARROW(CTB_I16, int16_t) CTB_NARROW(CTB_I64, int64_t) CTB_NARROW(CTB_BOOL, bool)
+#undef CTB_NARROW
     }
     return set_error(CTB_ERR_DTYPE, "binary op: unsupported dtype or op not registered");
 }
@@ -459,6 +469,9 @@ int launch_unary_dt(int dtype, const Plan& p, const void* a, double s, void* out
     case CTB_F32: return launch_shapes<UnAdapter<OP, float>, float, 1>(p, (const float*)a, nullptr, (float*)out, s, st);
     case CTB_I32: return launch_shapes<UnAdapter<OP, int32_t>, int32_t, 1>(p, (const int32_t*)a, nullptr, (int32_t*)out, s, st);
     case CTB_F64: return launch_shapes<UnAdapter<OP, double>, double, 1>(p, (const double*)a, nullptr, (double*)out, s, st);
+#define CTB_NARROW(CODE, T) case CODE: return launch_gather_shape<UnAdapter<OP, T>, T, 1>(p, (const T*)a, nullptr, (T*)out, s, st);
+    CTB_NARROW(CTB_U8, uint8_t) CTB_NARROW(CTB_I8, int8_t) CTB_NARROW(CTB_I16, int16_t) CTB_NARROW(CTB_I64, int64_t) CTB_NARROW(CTB_BOOL, bool)
+#undef CTB_NARROW
     }
     return set_error(CTB_ERR_DTYPE, "unary op: unsupported dtype");
 }
@@ -501,6 +514,10 @@ int launch_copy(int elem_bytes, const Plan& p, const void* a, void* out, cudaStr
         return launch_shapes<CopyAdapter<uint32_t>, uint32_t, 1>(p, (const uint32_t*)a, nullptr, (uint32_t*)out, 0.0, st);
     if (elem_bytes == 8)
         return launch_shapes<CopyAdapter<uint64_t>, uint64_t, 1>(p, (const uint64_t*)a, nullptr, (uint64_t*)out, 0.0, st);
+    if (elem_bytes == 1)
+        return launch_gather_shape<CopyAdapter<uint8_t>, uint8_t, 1>(p, (const uint8_t*)a, nullptr, (uint8_t*)out, 0.0, st);
+    if (elem_bytes == 2)
+        return launch_gather_shape<CopyAdapter<uint16_t>, uint16_t, 1>(p, (const uint16_t*)a, nullptr, (uint16_t*)out, 0.0, st);
     return set_error(CTB_ERR_DTYPE, "copy: unsupported element size %d", elem_bytes);
 }
 

@@ -349,6 +349,16 @@ template <typename T> __device__ __forceinline__ T from_double(double v);
 template <> __device__ __forceinline__ float from_double<float>(double v) { return __double2float_rn(v); }
 template <> __device__ __forceinline__ double from_double<double>(double v) { return v; }
 template <> __device__ __forceinline__ int32_t from_double<int32_t>(double v) { return d2i_x86(v); }
+// The narrow integer types as x86 compiles static_cast<T>(double) (write_scalar_at,
+// src/core/tensor.h:79-83): a 32-bit truncating conversion whose low bits are stored; Int64 through
+// the 64-bit conversion (INT64_MIN for NaN / out of range); Bool is value != 0.
+template <> __device__ __forceinline__ uint8_t from_double<uint8_t>(double v) { return (uint8_t)d2i_x86(v); }
+template <> __device__ __forceinline__ int8_t from_double<int8_t>(double v) { return (int8_t)d2i_x86(v); }
+template <> __device__ __forceinline__ int16_t from_double<int16_t>(double v) { return (int16_t)d2i_x86(v); }
+template <> __device__ __forceinline__ int64_t from_double<int64_t>(double v) {
+    return (v >= -9223372036854775808.0 && v < 9223372036854775808.0) ? __double2ll_rz(v) : INT64_MIN;
+}
+template <> __device__ __forceinline__ bool from_double<bool>(double v) { return v != 0.0; }
 
 // ---- binary functors: out = (T) op((double)a, (double)b), src/core/opsmp.cpp:198,249-252 --------
 // For fp32 the four arithmetic ops are evaluated directly in fp32: the double-precision result

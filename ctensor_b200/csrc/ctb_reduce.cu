@@ -1018,6 +1018,12 @@ int launch_reduce(int op, int dtype, const ReduceGeom& g, const void* a, void* o
         case CTB_F32: return launch_generic_t<float>(c, op, g, (const float*)a, out, ws, di.sm_count, st);
         case CTB_I32: return launch_generic_t<int32_t>(c, op, g, (const int32_t*)a, out, ws, di.sm_count, st);
         case CTB_F64: return launch_generic_t<double>(c, op, g, (const double*)a, out, ws, di.sm_count, st);
+        // the element types the reference reduces through double on its scalar back-end only
+        case CTB_U8: return launch_generic_t<uint8_t>(c, op, g, (const uint8_t*)a, out, ws, di.sm_count, st);
+        case CTB_I8: return launch_generic_t<int8_t>(c, op, g, (const int8_t*)a, out, ws, di.sm_count, st);
+        case CTB_I16: return launch_generic_t<int16_t>(c, op, g, (const int16_t*)a, out, ws, di.sm_count, st);
+        case CTB_I64: return launch_generic_t<int64_t>(c, op, g, (const int64_t*)a, out, ws, di.sm_count, st);
+        case CTB_BOOL: return launch_generic_t<bool>(c, op, g, (const bool*)a, out, ws, di.sm_count, st);
         }
         return set_error(CTB_ERR_DTYPE, "reduce: unsupported dtype");
     }
@@ -1084,6 +1090,11 @@ int launch_finalize_full(int op, int dtype, const double* partial, int64_t total
     case CTB_F32: finalize_full_kernel<float><<<1, 32, 0, st>>>(op, partial, total, (float*)out); break;
     case CTB_I32: finalize_full_kernel<int32_t><<<1, 32, 0, st>>>(op, partial, total, (int32_t*)out); break;
     case CTB_F64: finalize_full_kernel<double><<<1, 32, 0, st>>>(op, partial, total, (double*)out); break;
+    case CTB_U8: finalize_full_kernel<uint8_t><<<1, 32, 0, st>>>(op, partial, total, (uint8_t*)out); break;
+    case CTB_I8: finalize_full_kernel<int8_t><<<1, 32, 0, st>>>(op, partial, total, (int8_t*)out); break;
+    case CTB_I16: finalize_full_kernel<int16_t><<<1, 32, 0, st>>>(op, partial, total, (int16_t*)out); break;
+    case CTB_I64: finalize_full_kernel<int64_t><<<1, 32, 0, st>>>(op, partial, total, (int64_t*)out); break;
+    case CTB_BOOL: finalize_full_kernel<bool><<<1, 32, 0, st>>>(op, partial, total, (bool*)out); break;
     default: return set_error(CTB_ERR_DTYPE, "finalize: unsupported dtype");
     }
     return cuda_error(cudaGetLastError(), "finalize launch");

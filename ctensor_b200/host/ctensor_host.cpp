@@ -72,11 +72,18 @@ Tensor new_output(const std::vector<size_t>& shape, DType dt, const Device& dev)
     return out;
 }
 
+// Element types beyond Float32 / Int32 / Double64 are served by the reference's scalar back-end
+// only (the *_mp names); its dispatcher refuses them (src/core/ops_dispatch.cpp:206-209).
+thread_local bool t_scalar_back_end = false;
+
 int dtype_code(DType dt, const char* who) {
     switch (dt) {
     case DType::Float32: return CTB_F32;
     case DType::Int32: return CTB_I32;
     case DType::Double64: return CTB_F64;
+    case DType::UInt8: case DType::Int8: case DType::Int16: case DType::Int64: case DType::Bool:
+        if (t_scalar_back_end) return (int)dt;              // the C ABI keeps the reference's numbering
+        [[fallthrough]];
     default: throw std::runtime_error(std::string(who) + ": unsupported dtype or op not registered");
     }
 }
@@ -101,7 +108,8 @@ ctb_view view_of_bits(const Tensor& t) {
     std::memset(&v, 0, sizeof v);
     v.base = t.impl->data->data.get();
     v.offset = (int64_t)t.impl->offset;
-    v.dtype = dtype_size(t.impl->dtype) == 8 ? CTB_F64 : CTB_F32;
+    const size_t es = dtype_size(t.impl->dtype);
+    v.dtype = es == 8 ? CTB_F64 : es == 4 ? CTB_F32 : es == 2 ? CTB_U16 : CTB_U8;
     v.ndim = (int32_t)t.impl->ndim;
     for (size_t i = 0; i < t.impl->ndim; ++i) {
         v.shape[i] = (int64_t)t.impl->shape[i];
@@ -185,6 +193,9 @@ Tensor reduce(int op, const char* name, const Tensor& a, int dim, bool grad) {
 
 // ---- runtime knobs ------------------------------------------------------------------------------
 namespace ctb_host {
+ScalarBackEndScope::ScalarBackEndScope() : prev_(t_scalar_back_end) { t_scalar_back_end = true; }
+ScalarBackEndScope::~ScalarBackEndScope() { t_scalar_back_end = prev_; }
+
 void set_device(int index) {
     if (ctb_device_count() <= index || index < 0) throw std::runtime_error("ctensor_b200: no such CUDA device");
     check(ctb_set_device(index));
@@ -302,16 +313,9 @@ Tensor Tensor::to(Device target) {
     use_device(index);
     Tensor out = new_output(shape(), impl->dtype, Device(DeviceType::CUDA, index));
     out.impl->requires_grad = impl->requires_grad;
-    const size_t es = dtype_size(impl->dtype);
-    if (es == 4 || es == 8) {
-        ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
-        check(ctb_copy_strided(&vs, &vo, nullptr));
-        check(ctb_sync(nullptr));
-    } else {
-        Tensor packed = contiguous();
-        ctb_host::sync_for_host_access();
-        std::memcpy(out.impl->data->data.get(), (const char*)packed.impl->data->data.get() + packed.impl->offset * es, numel() * es);
-    }
+    ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
+    check(ctb_copy_strided(&vs, &vo, nullptr));
+    check(ctb_sync(nullptr));
     out.impl->data->device = target;            // keeps a CPU tag if that is what was asked for
     return out;
 }
@@ -333,22 +337,9 @@ Tensor Tensor::clone() const {
     use_device_of(*this);
     Tensor out = new_output(shape(), impl->dtype, device());
     out.impl->requires_grad = impl->requires_grad;
-    const size_t es = dtype_size(impl->dtype);
-    if (es == 4 || es == 8) {                   // strided gather on the GPU, bit copy
-        ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);
-        check(ctb_copy_strided(&vs, &vo, nullptr));
-        after_op();
-    } else {                                    // 1- and 2-byte element types: host gather
-        ctb_host::sync_for_host_access();
-        const size_t n = numel(), nd = impl->ndim;
-        const char* src = (const char*)impl->data->data.get();
-        char* dst = (char*)out.impl->data->data.get();
-        for (size_t i = 0; i < n; ++i) {
-            size_t t = i, off = impl->offset;
-            for (size_t d = nd; d-- > 0;) { off += (t % impl->shape[d]) * impl->strides[d]; t /= impl->shape[d]; }
-            std::memcpy(dst + i * es, src + off * es, es);
-        }
-    }
+    ctb_view vs = view_of_bits(*this), vo = view_of_bits(out);      // strided gather on the GPU, bit copy
+    check(ctb_copy_strided(&vs, &vo, nullptr));
+    after_op();
     return out;
 }
 

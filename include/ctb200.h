@@ -36,8 +36,19 @@ extern "C" {
 #define CTB_MAX_DIMS 8
 #define CTB_ABI_VERSION 1
 
-/* Element types; numbering follows the reference's DType enum (src/core/tensor.h:23-25). */
-enum ctb_dtype { CTB_F32 = 0, CTB_I32 = 1, CTB_F64 = 2 };
+/* Element types; numbering follows the reference's DType enum (src/core/tensor.h:23-25).
+ * Float32, Int32 and Double64 run on every kernel shape.  The other integer types and Bool are
+ * what the reference's scalar back-end handles through double (read_scalar_at / write_scalar_at,
+ * src/core/tensor.h:54-86; its dispatcher refuses them, src/core/ops_dispatch.cpp:206-209):
+ * ctb_binary, ctb_unary (the operators evaluated in double), ctb_reduce and the copies accept
+ * UInt8, Int8, Int16, Int64 and Bool on the general strided kernels, with the stores of x86
+ * static_cast (8- and 16-bit types: the low bits of the truncated 32-bit integer; Int64:
+ * INT64_MIN outside its range; Bool: value != 0).  UInt16, UInt32 and UInt64 can only be copied:
+ * the reference itself cannot store them (write_scalar_at has no case for them). */
+enum ctb_dtype {
+    CTB_F32 = 0, CTB_I32 = 1, CTB_F64 = 2, CTB_U8 = 3, CTB_U16 = 4, CTB_U32 = 5, CTB_U64 = 6,
+    CTB_I8 = 7, CTB_I16 = 8, CTB_I64 = 9, CTB_BOOL = 10
+};
 
 enum ctb_status {
     CTB_OK = 0,

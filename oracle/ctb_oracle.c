@@ -27,7 +27,7 @@
 typedef struct orc_view {       /* same layout as struct ctb_view (include/ctb200.h) */
     void*   base;
     int64_t offset;
-    int32_t dtype;              /* 0 f32, 1 i32, 2 f64 */
+    int32_t dtype;              /* the reference's DType numbering: 0 f32, 1 i32, 2 f64, 3 u8, 4 u16, 5 u32, 6 u64, 7 i8, 8 i16, 9 i64, 10 bool */
     int32_t ndim;
     int64_t shape[ORC_MAX_DIMS];
     int64_t stride[ORC_MAX_DIMS];
@@ -56,11 +56,35 @@ static inline int32_t d2i_x86(double v) {
     if (!(v > -2147483649.0 && v < 2147483648.0)) return INT32_MIN;
     return (int32_t)v;
 }
-static inline size_t esize(int dt) { return dt == ORC_F64 ? 8 : 4; }
+/* Element sizes, type-erased loads and stores: dtype_size / read_scalar_at / write_scalar_at,
+ * src/core/tensor.h:30-86.  The stores are x86's static_cast<T>(double): the narrow integer types
+ * take the low bits of the 32-bit truncating conversion, Int64 the 64-bit one (INT64_MIN outside
+ * its range), Bool is value != 0; UInt16 / UInt32 / UInt64 have no store in the reference (a
+ * result of such a type keeps the zeros it was allocated with). */
+enum { ORC_U8 = 3, ORC_U16 = 4, ORC_U32 = 5, ORC_U64 = 6, ORC_I8 = 7, ORC_I16 = 8, ORC_I64 = 9, ORC_BOOL = 10 };
+static inline size_t esize(int dt) {
+    switch (dt) {
+    case ORC_F64: case ORC_U64: case ORC_I64: return 8;
+    case ORC_U16: case ORC_I16: return 2;
+    case ORC_U8: case ORC_I8: case ORC_BOOL: return 1;
+    default: return 4;
+    }
+}
+static inline int64_t d2ll_x86(double v) {
+    return (v >= -9223372036854775808.0 && v < 9223372036854775808.0) ? (int64_t)v : INT64_MIN;
+}
 static inline double rd(const void* p, int64_t i, int dt) {
     switch (dt) {
     case ORC_F32: return (double)((const float*)p)[i];
     case ORC_I32: return (double)((const int32_t*)p)[i];
+    case ORC_U8:  return (double)((const uint8_t*)p)[i];
+    case ORC_U16: return (double)((const uint16_t*)p)[i];
+    case ORC_U32: return (double)((const uint32_t*)p)[i];
+    case ORC_U64: return (double)((const uint64_t*)p)[i];
+    case ORC_I8:  return (double)((const int8_t*)p)[i];
+    case ORC_I16: return (double)((const int16_t*)p)[i];
+    case ORC_I64: return (double)((const int64_t*)p)[i];
+    case ORC_BOOL: return ((const uint8_t*)p)[i] ? 1.0 : 0.0;
     default:      return ((const double*)p)[i];
     }
 }
@@ -68,6 +92,12 @@ static inline void wr(void* p, int64_t i, int dt, double v) {
     switch (dt) {
     case ORC_F32: ((float*)p)[i] = (float)v; break;
     case ORC_I32: ((int32_t*)p)[i] = d2i_x86(v); break;
+    case ORC_U8:  ((uint8_t*)p)[i] = (uint8_t)d2i_x86(v); break;
+    case ORC_I8:  ((int8_t*)p)[i] = (int8_t)d2i_x86(v); break;
+    case ORC_I16: ((int16_t*)p)[i] = (int16_t)d2i_x86(v); break;
+    case ORC_I64: ((int64_t*)p)[i] = d2ll_x86(v); break;
+    case ORC_BOOL: ((uint8_t*)p)[i] = v != 0.0; break;
+    case ORC_U16: case ORC_U32: case ORC_U64: break;
     default:      ((double*)p)[i] = v; break;
     }
 }
@@ -354,7 +384,10 @@ int64_t orc_contiguous(const orc_view* a, void* out) {
 static inline double round_dt(double v, int dt) {
     if (dt == ORC_F32) return (double)(float)v;
     if (dt == ORC_I32) return (double)d2i_x86(v);
-    return v;
+    if (dt == ORC_F64) return v;
+    uint64_t slot = 0;                    /* the other types: through their own store and load */
+    wr(&slot, 0, dt, v);
+    return rd(&slot, 0, dt);
 }
 
 /* element offset of flattened logical index i (used by the full reductions) */
@@ -623,8 +656,7 @@ int64_t orc_gather(const orc_view* x, int dim, const orc_view* index, void* out)
         if (idx < 0) idx += x->shape[dim];
         if (idx < 0 || idx >= x->shape[dim]) return -2;
         xoff += idx * x->stride[dim];
-        if (esize(x->dtype) == 8) ((uint64_t*)out)[i] = ((const uint64_t*)x->base)[xoff];
-        else ((uint32_t*)out)[i] = ((const uint32_t*)x->base)[xoff];
+        memcpy((char*)out + (size_t)i * esize(x->dtype), (const char*)x->base + (size_t)xoff * esize(x->dtype), esize(x->dtype));
     }
     return n;
 }
@@ -751,8 +783,7 @@ int64_t orc_cat(const orc_view* const* in, int count, int dim, void* out) {
                 src += c * in[i]->stride[d];
                 dst += (c + (d == dim ? at : 0)) * ostride[d];
             }
-            if (esize(dt) == 8) ((uint64_t*)out)[dst] = ((const uint64_t*)in[i]->base)[src];
-            else ((uint32_t*)out)[dst] = ((const uint32_t*)in[i]->base)[src];
+            memcpy((char*)out + (size_t)dst * esize(dt), (const char*)in[i]->base + (size_t)src * esize(dt), esize(dt));
         }
         at += in[i]->shape[dim];
     }

@@ -135,6 +135,47 @@ def all_cases():
         add(name=f"un_{nm}_f64", kind="unary", op=op, views=[Ad], scalar=2.5)
     add(name="un_mul_s_i32_overflow", kind="unary", op=ol.MUL_S, views=[edge_a], scalar=3.0)
 
+    # ---- the other integer types and Bool: served by the reference's scalar back-end through double
+    # (read_scalar_at / write_scalar_at); results stored with x86's static_cast.  Values stay inside
+    # the types' ranges except in the *_wrap cases (the low bits of the truncated 32-bit integer).
+    narrow = {
+        "u8": (np.uint8, _rng(101).integers(0, 200, (6, 11)), _rng(102).integers(1, 12, (11,))),
+        "i8": (np.int8, _rng(103).integers(-60, 60, (6, 11)), _rng(104).integers(1, 9, (11,))),
+        "i16": (np.int16, _rng(105).integers(-3000, 3000, (6, 11)), _rng(106).integers(1, 90, (11,))),
+        "i64": (np.int64, _rng(107).integers(-10**12, 10**12, (6, 11)), _rng(108).integers(1, 10**6, (11,))),
+        "bool": (np.bool_, _rng(109).integers(0, 2, (6, 11)), _rng(110).integers(0, 2, (11,))),
+    }
+    for tn, (npdt, av, bv) in narrow.items():
+        An, Bn = HostView.contig(av.astype(npdt)), HostView.contig(bv.astype(npdt))
+        bin_ops = (ol.ADD, ol.SUB, ol.MUL, ol.LT, ol.LE, ol.GT, ol.GE, ol.EQ, ol.NE) + (() if tn == "bool" else (ol.DIV,))
+        for op in bin_ops:
+            if tn in ("u8", "i8") and op == ol.MUL:
+                continue                                    # products leave the range: see *_wrap below
+            add(name=f"bin_{ol.BINARY_NAMES[op]}_{tn}", kind="binary", op=op, views=[An, Bn])
+        for op in (ol.ADD_S, ol.MUL_S, ol.DIV_S, ol.RSUB_S, ol.GT_S, ol.ABS, ol.RELU):
+            if tn == "bool" and op not in (ol.GT_S, ol.ABS, ol.RELU):
+                continue
+            add(name=f"un_{ol.UNARY_NAMES[op]}_{tn}", kind="unary", op=op, views=[An], scalar=0.5 if op == ol.MUL_S else 2.0)
+        add(name=f"un_add_s_{tn}_transposed", kind="unary", op=ol.ADD_S, views=[An.permute([1, 0])], scalar=1.0)
+        add(name=f"copy_{tn}_transposed", kind="copy", op=0, views=[An.permute([1, 0])])
+        for op in (ol.SUM, ol.MEAN, ol.MAX, ol.MIN, ol.ARGMAX):
+            if tn in ("u8", "i8") and op == ol.SUM:
+                continue
+            for dim in (0, 1) + (() if op == ol.ARGMAX else (-1,)):
+                if tn in ("u8", "i8", "bool") and op in (ol.SUM, ol.MEAN) and dim == -1:
+                    continue
+                add(name=f"red_{ol.REDUCE_NAMES[op]}_{tn}_d{dim}", kind="reduce", op=op, views=[An], dim=dim)
+    wrap_a = HostView.contig(np.array([200, 100, 255, 7, 0, 128], np.uint8))
+    wrap_b = HostView.contig(np.array([100, 100, 255, 40, 0, 2], np.uint8))
+    for op in (ol.ADD, ol.MUL, ol.SUB):
+        add(name=f"bin_{ol.BINARY_NAMES[op]}_u8_wrap", kind="binary", op=op, views=[wrap_a, wrap_b])
+    add(name="red_sum_u8_wrap_d0", kind="reduce", op=ol.SUM, dim=0, views=[HostView.contig(np.full((9, 4), 100, np.uint8))])
+    add(name="un_mul_s_i64_out_of_range", kind="unary", op=ol.MUL_S, scalar=1e10,
+        views=[HostView.contig(np.array([10**12, -10**12, 5, 0], np.int64))])
+    for tn, npdt in (("u16", np.uint16), ("u32", np.uint32), ("u64", np.uint64)):      # copied, never computed
+        add(name=f"copy_{tn}_transposed", kind="copy", op=0,
+            views=[HostView.contig(_rng(111).integers(0, 60000, (5, 7)).astype(npdt)).permute([1, 0])])
+
     # ---- strided copy -----------------------------------------------------------------------------------
     for nm, v in (("perm4d", P4), ("transposed", T), ("offset", off), ("stepped", stepped),
                   ("i32", HostView.contig(Ai.numpy()).permute([1, 0])), ("f64", Ad.permute([1, 0])),

@@ -117,6 +117,21 @@ int main() {
     CHECK((int)double(div_scalar(i3, 2.0)[0]) == 1 && (int)double(div_scalar(i3, 2.0)[1]) == 2);
     CHECK((int)double(Tensor::from_vector({1.5, 2.5}, {2}).astype(DType::Int32)[1]) == 2);
 
+    // element types of the reference's scalar back-end: served under the *_mp names (through double,
+    // stored like x86's static_cast), refused under the dispatcher's names like the reference does
+    Tensor u8a = Tensor::from_vector({200, 100, 7, 0}, {2, 2}, DType::UInt8);
+    Tensor u8b = Tensor::from_vector({100, 100, 2, 0}, {2, 2}, DType::UInt8);
+    Tensor u8s = add_mp(u8a, u8b);
+    CHECK(u8s._dtype() == DType::UInt8 && (int)double(u8s[0][0]) == 44 && (int)double(u8s[0][1]) == 200);   // 300 -> 44
+    CHECK((int)double(div_mp(u8a, Tensor::from_vector({3, 3, 3, 3}, {2, 2}, DType::UInt8))[1][0]) == 2);
+    Tensor i64 = Tensor::from_vector({1e12, -3.0}, {2}, DType::Int64);
+    CHECK(double(mult_scalar_mp(i64, 2.0)[0]) == 2e12 && double(abs_mp(i64)[1]) == 3.0);
+    CHECK((int)double(sum_mp(Tensor::from_vector({1, 2, 3, 4, 5, 6}, {2, 3}, DType::Int16), 1)[1]) == 15);
+    CHECK(double(u8a.permute({1, 0}).contiguous()[0][1]) == 7.0);
+    CHECK_THROWS(add(u8a, u8b), std::runtime_error, "add: unsupported dtype or op not registered");
+    CHECK_THROWS(add_mp(Tensor::from_vector({1, 2}, {2}, DType::UInt16), Tensor::from_vector({1, 2}, {2}, DType::UInt16)),
+                 std::runtime_error, "add: unsupported dtype or op not registered");
+
     // fused rows
     Tensor sm = softmax(Tensor::from_vector({1, 2, 3, 1, 1, 1}, {2, 3}));
     CHECK_NEAR(double(sm[0][0]) + double(sm[0][1]) + double(sm[0][2]), 1.0, 1e-6);

@@ -23,9 +23,10 @@ ORACLE_SO = os.path.join(ORACLE_DIR, "libctb_oracle.so")
 REF_SO = os.path.join(ORACLE_DIR, "_ref", "libctensor_ref.so")
 
 MAX_DIMS = 8
-F32, I32, F64 = 0, 1, 2
-NP_DTYPES = {F32: np.float32, I32: np.int32, F64: np.float64}
-DT_OF = {np.dtype(np.float32): F32, np.dtype(np.int32): I32, np.dtype(np.float64): F64}
+F32, I32, F64, U8, U16, U32, U64, I8, I16, I64, BOOL = range(11)       # the reference's DType numbering
+NP_DTYPES = {F32: np.float32, I32: np.int32, F64: np.float64, U8: np.uint8, U16: np.uint16, U32: np.uint32,
+             U64: np.uint64, I8: np.int8, I16: np.int16, I64: np.int64, BOOL: np.bool_}
+DT_OF = {np.dtype(v): k for k, v in NP_DTYPES.items()}
 
 # operator codes (include/ctb200.h)
 ADD, SUB, MUL, DIV, LT, LE, GT, GE, EQ, NE, POW = range(11)
