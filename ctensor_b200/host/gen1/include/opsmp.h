@@ -13,96 +13,64 @@
 #include <vector>
 #include "tensor1.h"
 
-Tensor add_mp(const Tensor& a, const Tensor& b);
-Tensor diff_mp(const Tensor& a, const Tensor& b);
-Tensor mult_mp(const Tensor& a, const Tensor& b);
-Tensor div_mp(const Tensor& a, const Tensor& b);
-Tensor pow_mp(const Tensor& a, const Tensor& b);
-Tensor matmul_mp(const Tensor& A, const Tensor& B);
+// The names are kept in lists (one list per signature) that expand to the declarations and, further
+// down, to the operator overloads that forward to them.
 
-Tensor add_scalar_mp(const Tensor& a, double scalar);
-Tensor sub_scalar_mp(const Tensor& a, double scalar);
-Tensor sub_afterscalar_mp(double scalar, const Tensor& a);
-Tensor mult_scalar_mp(const Tensor& a, double scalar);
-Tensor div_scalar_mp(const Tensor& a, double scalar);
-Tensor scalar_div_mp(double scalar, const Tensor& a);
-Tensor pow_scalar_mp(const Tensor& a, double scalar);
-Tensor scalar_pow_mp(double scalar, const Tensor& a);
+// Tensor f(const Tensor&, const Tensor&)
+#define CTB_GEN1_TENSOR_TENSOR(X) \
+    X(add_mp) X(diff_mp) X(mult_mp) X(div_mp) X(pow_mp) X(matmul_mp) \
+    X(lt_mp) X(le_mp) X(gt_mp) X(ge_mp) X(eq_mp) X(ne_mp)
+// Tensor f(const Tensor&, double)
+#define CTB_GEN1_TENSOR_SCALAR(X) \
+    X(add_scalar_mp) X(sub_scalar_mp) X(mult_scalar_mp) X(div_scalar_mp) X(pow_scalar_mp) \
+    X(lt_mp) X(le_mp) X(gt_mp) X(ge_mp) X(eq_mp) X(neq_mp)
+// Tensor f(double, const Tensor&)
+#define CTB_GEN1_SCALAR_TENSOR(X) X(sub_afterscalar_mp) X(scalar_div_mp) X(scalar_pow_mp)
+// Tensor f(const Tensor&)
+#define CTB_GEN1_UNARY(X) \
+    X(abs_mp) X(ln_mp) X(exp_mp) X(sqrt_mp) X(sin_mp) X(asin_mp) X(cos_mp) X(acos_mp) X(tan_mp) X(atan_mp) \
+    X(tanh_mp) X(sinh_mp) X(cosh_mp) X(sigmoid_mp) X(Relu_mp) X(softplus_mp)
+// Tensor f(const Tensor&, int dim = -1): -1 is the last dim
+#define CTB_GEN1_REDUCTIONS(X) X(sum_mp) X(mean_mp) X(max_mp) X(min_mp)
 
-Tensor abs_mp(const Tensor& a);
-Tensor ln_mp(const Tensor& a);
-Tensor exp_mp(const Tensor& a);
-Tensor sqrt_mp(const Tensor& a);
-Tensor sin_mp(const Tensor& a);
-Tensor asin_mp(const Tensor& a);
-Tensor cos_mp(const Tensor& a);
-Tensor acos_mp(const Tensor& a);
-Tensor tan_mp(const Tensor& a);
-Tensor atan_mp(const Tensor& a);
-Tensor tanh_mp(const Tensor& a);
-Tensor sinh_mp(const Tensor& a);
-Tensor cosh_mp(const Tensor& a);
-Tensor sigmoid_mp(const Tensor& a);
-Tensor Relu_mp(const Tensor& a);
-Tensor softplus_mp(const Tensor& a);
-
-Tensor sum_mp(const Tensor& t, int dim = -1);
-Tensor mean_mp(const Tensor& t, int dim = -1);
-Tensor max_mp(const Tensor& t, int dim = -1);
-Tensor min_mp(const Tensor& t, int dim = -1);
-
-Tensor lt_mp(const Tensor& a, double b);
-Tensor le_mp(const Tensor& a, double b);
-Tensor gt_mp(const Tensor& a, double b);
-Tensor ge_mp(const Tensor& a, double b);
-Tensor eq_mp(const Tensor& a, double b);
-Tensor neq_mp(const Tensor& a, double b);
-Tensor lt_mp(const Tensor& a, const Tensor& b);
-Tensor le_mp(const Tensor& a, const Tensor& b);
-Tensor gt_mp(const Tensor& a, const Tensor& b);
-Tensor ge_mp(const Tensor& a, const Tensor& b);
-Tensor eq_mp(const Tensor& a, const Tensor& b);
-Tensor ne_mp(const Tensor& a, const Tensor& b);
-
+#define CTB_X(name) Tensor name(const Tensor& a, const Tensor& b);
+CTB_GEN1_TENSOR_TENSOR(CTB_X)
+#undef CTB_X
+#define CTB_X(name) Tensor name(const Tensor& a, double scalar);
+CTB_GEN1_TENSOR_SCALAR(CTB_X)
+#undef CTB_X
+#define CTB_X(name) Tensor name(double scalar, const Tensor& a);
+CTB_GEN1_SCALAR_TENSOR(CTB_X)
+#undef CTB_X
+#define CTB_X(name) Tensor name(const Tensor& a);
+CTB_GEN1_UNARY(CTB_X)
+#undef CTB_X
+#define CTB_X(name) Tensor name(const Tensor& t, int dim = -1);
+CTB_GEN1_REDUCTIONS(CTB_X)
+#undef CTB_X
 Tensor cat_mp(const std::vector<Tensor>& tensors, size_t dim);
 
-inline Tensor operator+(const Tensor& a, const Tensor& b) { return add_mp(a, b); }
-inline Tensor operator+(const Tensor& a, double s) { return add_scalar_mp(a, s); }
-inline Tensor operator+(double s, const Tensor& a) { return add_scalar_mp(a, s); }
-inline Tensor operator-(const Tensor& a, const Tensor& b) { return diff_mp(a, b); }
-inline Tensor operator-(const Tensor& a, double s) { return sub_scalar_mp(a, s); }
-inline Tensor operator-(double s, const Tensor& a) { return sub_afterscalar_mp(s, a); }
+// ---- operators: symbol, tensor-tensor function, tensor-scalar function, scalar-tensor function -------------
+#define CTB_GEN1_ARITHMETIC(X)                                          \
+    X(+, add_mp, add_scalar_mp(a, s), add_scalar_mp(a, s))               \
+    X(-, diff_mp, sub_scalar_mp(a, s), sub_afterscalar_mp(s, a))         \
+    X(*, mult_mp, mult_scalar_mp(a, s), mult_scalar_mp(a, s))            \
+    X(/, div_mp, div_scalar_mp(a, s), scalar_div_mp(s, a))               \
+    X(^, pow_mp, pow_scalar_mp(a, s), scalar_pow_mp(s, a))
+#define CTB_X(op, tt, ts, st)                                                                     \
+    inline Tensor operator op(const Tensor& a, const Tensor& b) { return tt(a, b); }               \
+    inline Tensor operator op(const Tensor& a, double s) { return ts; }                            \
+    inline Tensor operator op(double s, const Tensor& a) { return st; }                            \
+    inline Tensor& operator op##=(Tensor& a, const Tensor& b) { a = tt(a, b); return a; }          \
+    inline Tensor& operator op##=(Tensor& a, double s) { a = ts; return a; }
+CTB_GEN1_ARITHMETIC(CTB_X)
+#undef CTB_X
 inline Tensor operator-(const Tensor& a) { return mult_scalar_mp(a, -1.0); }
-inline Tensor operator*(const Tensor& a, const Tensor& b) { return mult_mp(a, b); }
-inline Tensor operator*(const Tensor& a, double s) { return mult_scalar_mp(a, s); }
-inline Tensor operator*(double s, const Tensor& a) { return mult_scalar_mp(a, s); }
-inline Tensor operator/(const Tensor& a, const Tensor& b) { return div_mp(a, b); }
-inline Tensor operator/(const Tensor& a, double s) { return div_scalar_mp(a, s); }
-inline Tensor operator/(double s, const Tensor& a) { return scalar_div_mp(s, a); }
-inline Tensor operator^(const Tensor& a, const Tensor& b) { return pow_mp(a, b); }
-inline Tensor operator^(const Tensor& a, double s) { return pow_scalar_mp(a, s); }
-inline Tensor operator^(double s, const Tensor& a) { return scalar_pow_mp(s, a); }
 
-inline Tensor& operator+=(Tensor& a, const Tensor& b) { a = add_mp(a, b); return a; }
-inline Tensor& operator+=(Tensor& a, double s) { a = add_scalar_mp(a, s); return a; }
-inline Tensor& operator-=(Tensor& a, const Tensor& b) { a = diff_mp(a, b); return a; }
-inline Tensor& operator-=(Tensor& a, double s) { a = sub_scalar_mp(a, s); return a; }
-inline Tensor& operator*=(Tensor& a, const Tensor& b) { a = mult_mp(a, b); return a; }
-inline Tensor& operator*=(Tensor& a, double s) { a = mult_scalar_mp(a, s); return a; }
-inline Tensor& operator/=(Tensor& a, const Tensor& b) { a = div_mp(a, b); return a; }
-inline Tensor& operator/=(Tensor& a, double s) { a = div_scalar_mp(a, s); return a; }
-inline Tensor& operator^=(Tensor& a, const Tensor& b) { a = pow_mp(a, b); return a; }
-inline Tensor& operator^=(Tensor& a, double s) { a = pow_scalar_mp(a, s); return a; }
-
-inline Tensor operator<(const Tensor& a, double b) { return lt_mp(a, b); }
-inline Tensor operator<=(const Tensor& a, double b) { return le_mp(a, b); }
-inline Tensor operator>(const Tensor& a, double b) { return gt_mp(a, b); }
-inline Tensor operator>=(const Tensor& a, double b) { return ge_mp(a, b); }
-inline Tensor operator==(const Tensor& a, double b) { return eq_mp(a, b); }
-inline Tensor operator!=(const Tensor& a, double b) { return neq_mp(a, b); }
-inline Tensor operator<(const Tensor& a, const Tensor& b) { return lt_mp(a, b); }
-inline Tensor operator<=(const Tensor& a, const Tensor& b) { return le_mp(a, b); }
-inline Tensor operator>(const Tensor& a, const Tensor& b) { return gt_mp(a, b); }
-inline Tensor operator>=(const Tensor& a, const Tensor& b) { return ge_mp(a, b); }
-inline Tensor operator==(const Tensor& a, const Tensor& b) { return eq_mp(a, b); }
-inline Tensor operator!=(const Tensor& a, const Tensor& b) { return ne_mp(a, b); }
+// comparisons: symbol, tensor-tensor function, tensor-scalar function
+#define CTB_GEN1_COMPARISONS(X) X(<, lt_mp, lt_mp) X(<=, le_mp, le_mp) X(>, gt_mp, gt_mp) X(>=, ge_mp, ge_mp) X(==, eq_mp, eq_mp) X(!=, ne_mp, neq_mp)
+#define CTB_X(op, tt, ts)                                                                          \
+    inline Tensor operator op(const Tensor& a, const Tensor& b) { return tt(a, b); }               \
+    inline Tensor operator op(const Tensor& a, double b) { return ts(a, b); }
+CTB_GEN1_COMPARISONS(CTB_X)
+#undef CTB_X
