@@ -112,7 +112,10 @@ int ctb_pool_alloc_managed(void** ptr, size_t bytes, int zero, int device, void*
     }
     if (zero) {
         const cudaError_t e = cudaMemsetAsync(p, 0, bytes ? bytes : 1, (cudaStream_t)stream);
-        if (e != cudaSuccess) return cuda_error(e, "cudaMemsetAsync");
+        if (e != cudaSuccess) {
+            ctb_pool_free_managed(p);         // the block stays accounted for: back onto its free list
+            return cuda_error(e, "cudaMemsetAsync");
+        }
     }
     *ptr = p;
     return CTB_OK;
