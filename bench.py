@@ -435,9 +435,48 @@ def host_layer_bench():
         return {"error": "ctensor_b200/host/bench_host_layer.bin not built"}
     try:
         r = subprocess.run([exe, "20", "24", "28"], capture_output=True, text=True, timeout=300)
-        return json.loads(r.stdout.strip().splitlines()[-1])
+        res = json.loads(r.stdout.strip().splitlines()[-1])
     except Exception as exc:
         return {"error": repr(exc)}
+    res["train_step"] = train_step_bench()
+    return res
+
+
+def train_step_bench():
+    """A training step as a user of the reference writes it (two Linear layers, relu, CrossEntropy,
+    backward, SGD from train_utils.h; tests/cpp/train_step_program.cpp), ms per step:
+      drop_in       the reference's autograd.cpp / layer.cpp / loss.cpp unchanged over the host layer —
+                    their host loops (accumulate_grad, the memset of ensure_grad_buffer, the loop of
+                    GradCrossEntropy) pull every gradient buffer across PCIe and back
+      three_edits   the three bodies replaced by calls of the host layer, as the integration notes describe
+      three_edits_tensor_cores   the same with matmul on the tensor cores (TF32 products)
+      reference_cpu the same program linked with the reference itself (scalar back-end, host cores)
+    The programs are built where the reference's sources are; absent binaries are reported as such."""
+    built = os.path.join(ROOT, "tests", "cpp", "_built")
+    runs = {"drop_in": (os.path.join(built, "train_step_gen2_b200"), {}),
+            "three_edits": (os.path.join(built, "train_step_gen2_b200_edited"), {}),
+            "three_edits_tensor_cores": (os.path.join(built, "train_step_gen2_b200_edited"), {"CTB_HOST_MATMUL_TENSOR_CORES": "1"}),
+            "reference_cpu": (os.path.join(ROOT, "oracle", "_ref", "train_step_gen2_ref_scalar"), {})}
+    out = {}
+    for shape_name, argv in (("batch512_1024x1024x16", ["512", "1024", "1024", "16"]),
+                             ("batch4096_4096x4096x1000", ["4096", "4096", "4096", "1000"])):
+        row = {}
+        for name, (exe, env) in runs.items():
+            if name == "reference_cpu" and shape_name != "batch512_1024x1024x16":
+                continue                                    # minutes per step on the host cores
+            if not os.path.exists(exe):
+                row[name] = "not built"
+                continue
+            try:
+                steps = "3" if name == "reference_cpu" else "10"
+                r = subprocess.run([exe] + argv + [steps], capture_output=True, text=True, timeout=300,
+                                   env=dict(os.environ, **env))
+                d = json.loads(r.stdout.strip().splitlines()[-1])
+                row[name] = {k: d[k] for k in ("ms_per_step", "forward_ms", "loss_ms", "backward_ms", "optimizer_ms") if k in d}
+            except Exception as exc:
+                row[name] = {"error": repr(exc)}
+        out[shape_name] = row
+    return out
 
 
 def sharded_configs(ct, torch, dist, dev, rank, world, x, y, out):

@@ -39,16 +39,21 @@ matmul_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, floa
     for (int i = 0; i < kMicro; ++i)
 #pragma unroll
         for (int j = 0; j < kMicro; ++j) acc[i][j] = 0.0f;
+    const bool a_walks_m = g.a_k != 1 && g.a_m == 1, b_walks_k = g.b_n != 1 && g.b_k == 1;
     for (int64_t k0 = 0; k0 < g.K; k0 += kTileK) {
         // 64 x 16 elements of A and 16 x 64 of B, four per thread each; zero beyond the edges
         // (the zero products leave the in-range sums unchanged)
+        // Consecutive threads walk the operand's contiguous dim, whichever it is: k for a row-major
+        // A, m for a transposed view of one (what the backward pass of a product multiplies by);
+        // n for a row-major B, k for a transposed view (the weight of a Linear layer).  The order
+        // of the sum over k does not depend on it.
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const int e = threadIdx.x + r * 256;
-            const int am = e >> 4, ak = e & 15;                 // A: consecutive threads walk k
+            const int am = a_walks_m ? (e & 63) : (e >> 4), ak = a_walks_m ? (e >> 6) : (e & 15);
             const int64_t m = m0 + am, k = k0 + ak;
             sa[ak][am] = (m < g.M && k < g.K) ? ab[m * g.a_m + k * g.a_k] : 0.0f;
-            const int bk = e >> 6, bn = e & 63;                 // B: consecutive threads walk n
+            const int bk = b_walks_k ? (e & 15) : (e >> 6), bn = b_walks_k ? (e >> 4) : (e & 63);
             const int64_t kk = k0 + bk, n = n0 + bn;
             sb[bk][bn] = (kk < g.K && n < g.N) ? bb[kk * g.b_k + n * g.b_n] : 0.0f;
         }

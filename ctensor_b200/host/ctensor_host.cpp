@@ -20,6 +20,16 @@ int g_device = 0;
 thread_local int t_device_selected = -1;
 thread_local std::vector<size_t> t_last_permutation;
 bool g_sync_after_op = true;
+// matmul on the tensor cores (TF32 products): -1 = not decided yet (the environment variable
+// CTB_HOST_MATMUL_TENSOR_CORES=1 switches it on for programs that cannot call the setter)
+int g_matmul_tc = -1;
+bool matmul_on_tensor_cores() {
+    if (g_matmul_tc < 0) {
+        const char* e = std::getenv("CTB_HOST_MATMUL_TENSOR_CORES");
+        g_matmul_tc = (e && *e == '1') ? 1 : 0;
+    }
+    return g_matmul_tc == 1;
+}
 ctb_host::GradFactory g_grad_factory;
 std::function<void(Tensor&)> g_backward;
 
@@ -204,6 +214,7 @@ void set_device(int index) {
 }
 int device() { return g_device; }
 void set_sync_after_op(bool on) { g_sync_after_op = on; }
+void set_matmul_tensor_cores(bool on) { g_matmul_tc = on ? 1 : 0; }
 void sync_for_host_access() { if (t_device_selected >= 0) check(ctb_device_sync()); }
 void trim_storage_pool() { check(ctb_pool_trim(-1)); }
 const std::vector<size_t>& last_permutation() { return t_last_permutation; }
@@ -215,6 +226,66 @@ void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src) {
     const ctb_view vg = view_of(grad_buffer, "accumulate_grad"), vs = view_of(grad_src, "accumulate_grad");
     check(ctb_accumulate_grad(&vg, &vs, nullptr));
     after_op();
+}
+
+namespace {
+// One int32 per device the kernels raise for a label outside its row (managed: the host reads it).
+int32_t* bad_label_flag(int index) {
+    static thread_local std::vector<std::shared_ptr<void>> flags;
+    if ((int)flags.size() <= index) flags.resize(index + 1);
+    if (!flags[index]) {
+        void* p = nullptr;
+        check(ctb_alloc_managed(&p, sizeof(int32_t), /*zero=*/1));
+        flags[index] = std::shared_ptr<void>(p, [](void*) {});
+    }
+    return (int32_t*)flags[index].get();
+}
+std::vector<size_t> broadcast_of(const Tensor& a, const Tensor& b) { return broadcast_shape(a, b); }
+}  // namespace
+
+Tensor cross_entropy(const Tensor& logits, const Tensor& labels, bool mean) {
+    if (!logits.impl || !labels.impl) throw std::runtime_error("cross_entropy: null input");
+    use_device_of(logits);
+    Tensor loss = new_output({1}, DType::Float32, logits.device());
+    int32_t* bad = bad_label_flag(device_index_of(logits.device()));
+    const ctb_view vx = view_of(logits, "cross_entropy"), vl = view_of(labels, "cross_entropy"), vo = view_of(loss, "cross_entropy");
+    check(ctb_cross_entropy(&vx, &vl, mean ? 1 : 0, &vo, bad, nullptr));
+    check(ctb_sync(nullptr));
+    if (*bad) throw std::out_of_range("Gather index out of bounds");
+    return loss;
+}
+
+Tensor cross_entropy_backward(const Tensor& logits, const Tensor& labels, double grad_scale) {
+    if (!logits.impl || !labels.impl) throw std::runtime_error("cross_entropy_backward: null input");
+    use_device_of(logits);
+    Tensor grad = new_output(logits.shape(), DType::Float32, logits.device());
+    const ctb_view vx = view_of(logits, "cross_entropy_backward"), vl = view_of(labels, "cross_entropy_backward"),
+                   vg = view_of(grad, "cross_entropy_backward");
+    check(ctb_cross_entropy_backward(&vx, &vl, grad_scale, &vg, /*accumulate=*/0, nullptr, nullptr));
+    after_op();
+    return grad;
+}
+
+void div_backward(const Tensor& grad, const Tensor& a, const Tensor& b, Tensor* grad_a, Tensor* grad_b) {
+    if (!grad.impl || !a.impl || !b.impl) throw std::runtime_error("div_backward: null input");
+    use_device_of(grad);
+    const std::vector<size_t> shape = broadcast_of(a, b);
+    ctb_view va_out, vb_out;
+    if (grad_a) { *grad_a = new_output(shape, grad._dtype(), grad.device()); va_out = view_of(*grad_a, "div_backward"); }
+    if (grad_b) { *grad_b = new_output(shape, grad._dtype(), grad.device()); vb_out = view_of(*grad_b, "div_backward"); }
+    const ctb_view vg = view_of(grad, "div_backward"), va = view_of(a, "div_backward"), vb = view_of(b, "div_backward");
+    check(ctb_div_backward(&vg, &va, &vb, grad_a ? &va_out : nullptr, grad_b ? &vb_out : nullptr, /*accumulate=*/0, nullptr));
+    after_op();
+}
+
+Tensor tanh_backward(const Tensor& grad, const Tensor& t) {
+    if (!grad.impl || !t.impl) throw std::runtime_error("tanh_backward: null input");
+    use_device_of(grad);
+    Tensor out = new_output(broadcast_of(grad, t), grad._dtype(), grad.device());
+    const ctb_view vg = view_of(grad, "tanh_backward"), vt = view_of(t, "tanh_backward"), vo = view_of(out, "tanh_backward");
+    check(ctb_tanh_backward(&vg, &vt, &vo, /*accumulate=*/0, nullptr));
+    after_op();
+    return out;
 }
 
 bool has_grad(const Tensor& param) {
@@ -622,8 +693,30 @@ Tensor matmul(const Tensor& a, const Tensor& b) {
     Tensor out = new_output(res_shape, a._dtype(), a.device());
     out.impl->requires_grad = req;
     const ctb_view va = view_of(a, "matmul"), vb = view_of(b, "matmul"), vo = view_of(out, "matmul");
-    check(ctb_matmul(&va, &vb, &vo, nullptr));
-    after_op();
+    if (matmul_on_tensor_cores() && a._dtype() == DType::Float32) {
+        // A wait inside the kernel that gave up is reported through a status word.  Reading it on the
+        // host moves its (managed) page across PCIe and back, so it is looked at on the first call
+        // and on every 64th: enough to stop a program whose products have started to fail.
+        static thread_local std::vector<std::shared_ptr<void>> status;          // one int32 per device
+        static thread_local unsigned calls = 0;
+        const int index = device_index_of(a.device());
+        if ((int)status.size() <= index) status.resize(index + 1);
+        const bool look = (calls++ % 64) == 0;
+        if (look && !status[index]) {
+            void* p = nullptr;
+            check(ctb_alloc_managed(&p, sizeof(int32_t), /*zero=*/1));
+            status[index] = std::shared_ptr<void>(p, [](void*) {});
+        }
+        check(ctb_matmul_tc(&va, &vb, &vo, look ? (int32_t*)status[index].get() : nullptr, nullptr));
+        after_op();
+        if (look) {
+            check(ctb_sync(nullptr));
+            if (*(const int32_t*)status[index].get() != 0) throw std::runtime_error("matmul: the tensor-core kernel gave up a wait");
+        }
+    } else {
+        check(ctb_matmul(&va, &vb, &vo, nullptr));
+        after_op();
+    }
     if (req) attach_grad(out, "matmul", {a, b}, 0.0);
     return out;
 }

@@ -21,6 +21,13 @@ int device();
 void set_sync_after_op(bool on);
 void sync_for_host_access();
 
+// matmul / matmul_mp reproduce the reference's scalar product bit for bit (ctb_matmul, CUDA cores).
+// Switched on, Float32 products run on the tensor cores instead (ctb_matmul_tc: TF32 products, fp32
+// accumulation, |error| <= 2^-9 * sum |a_ik b_kj|) — the trade the reference's own SIMD GEMMs make
+// against its scalar one, at 30 times the speed.  Off by default; the environment variable
+// CTB_HOST_MATMUL_TENSOR_CORES=1 switches it on without a code change.
+void set_matmul_tensor_cores(bool on);
+
 // Tensor storage comes from a pool of managed blocks (ctb_pool_alloc_managed): freed tensors
 // keep their memory cached for the next tensor of the same size.  This gives the cached blocks
 // back to the driver.
@@ -42,6 +49,23 @@ const std::vector<size_t>& last_permutation();
 // grad_src summed first and NaN/Inf contributions skipped.  The autograd library calls this in
 // place of its host loop.
 void accumulate_grad(Tensor& grad_buffer, const Tensor& grad_src);
+
+// ---- fused bodies for the autograd and loss libraries --------------------------------------------------
+// What the reference spells as chains of operators or as host loops, as one kernel each (the C ABI's
+// ctb_cross_entropy, ctb_cross_entropy_backward, ctb_div_backward, ctb_tanh_backward).  Results are
+// fresh tensors; hand them to accumulate_grad as the reference's bodies do with theirs.
+//   cross_entropy           Loss::CrossEntropy's value (src/neuralnet/loss.cpp:90-118): logits [B, C],
+//                           labels Int32 [B] or [B, 1]; mean or sum over the rows; a label outside
+//                           its row throws std::out_of_range like the reference's gather
+//   cross_entropy_backward  GradCrossEntropy::backward (:319-370): (softmax - onehot) * grad_scale,
+//                           grad_scale = the loss's incoming gradient (divided by B for "mean")
+//   div_backward            GradDiv::backward (src/core/autograd.cpp:188-202): both gradients of a / b
+//                           in the broadcast shape of the result (either pointer may be null)
+//   tanh_backward           GradTanh::backward (:434-438)
+Tensor cross_entropy(const Tensor& logits, const Tensor& labels, bool mean = true);
+Tensor cross_entropy_backward(const Tensor& logits, const Tensor& labels, double grad_scale);
+void div_backward(const Tensor& grad, const Tensor& a, const Tensor& b, Tensor* grad_a, Tensor* grad_b);
+Tensor tanh_backward(const Tensor& grad, const Tensor& t);
 
 // ---- optimizer steps: what the host layer's train_utils.h is built on ----------------------------------
 // One fused in-place update of `param` from its gradient buffer on the GPU, with the arithmetic of

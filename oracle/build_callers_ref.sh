@@ -60,6 +60,10 @@ $CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
 # cannot run there; the scalar back-end honours strides and dims.
 $CXX $STD -O2 -fopenmp '-D__builtin_cpu_supports(x)=0' $INC2 -c "$S/core/ops_dispatch.cpp" -o "$TMP/obj2/ops_dispatch.o"
 $CXX -o "$OUT/callers_gen2_ref_scalar" "$TMP"/obj2/*.o -fopenmp
+# the timed training step (tests/cpp/train_step_program.cpp) on the same scalar back-end
+$CXX $STD -O1 $INC2 -I"$REF/src" -c "$HERE/../tests/cpp/train_step_program.cpp" -o "$TMP/train_step.o"
+rm -f "$TMP/obj2/program.o"
+$CXX -o "$OUT/train_step_gen2_ref_scalar" "$TMP"/obj2/*.o "$TMP/train_step.o" -fopenmp
 
 # ---- first generation (root of the reference tree) -----------------------------------------------
 pids=()

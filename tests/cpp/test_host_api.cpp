@@ -246,6 +246,60 @@ int main() {
     CHECK(sum(t, -2).numel() == 2);                       // negative dims other than -1 wrap
     CHECK_THROWS(sum(t, -5), std::out_of_range, "reduction: dim out of range");
 
+    // the fused bodies for the loss and autograd libraries: one kernel each, same numbers as the chains
+    {
+        Tensor logits = Tensor::from_vector({1.0, 2.0, 0.5, -1.0, 0.0, 3.0}, {2, 3});
+        Tensor labels = Tensor::from_vector({1, 2}, {2, 1}, DType::Int32);
+        const double l0 = -(2.0 - std::log(std::exp(1.0) + std::exp(2.0) + std::exp(0.5)));
+        const double l1 = -(3.0 - std::log(std::exp(-1.0) + std::exp(0.0) + std::exp(3.0)));
+        CHECK_NEAR(ctb_host::cross_entropy(logits, labels, true)[0], (l0 + l1) / 2, 1e-6);
+        CHECK_NEAR(ctb_host::cross_entropy(logits, labels, false)[0], l0 + l1, 1e-6);
+        Tensor g = ctb_host::cross_entropy_backward(logits, labels, 0.5);
+        const double z0 = std::exp(1.0) + std::exp(2.0) + std::exp(0.5);
+        CHECK(g.shape() == logits.shape());
+        CHECK_NEAR(g[0][0], 0.5 * std::exp(1.0) / z0, 1e-6);
+        CHECK_NEAR(g[0][1], 0.5 * (std::exp(2.0) / z0 - 1.0), 1e-6);
+        CHECK_NEAR(double(g[1][0]) + double(g[1][1]) + double(g[1][2]), 0.0, 1e-6);
+        Tensor wrong = Tensor::from_vector({1, 3}, {2, 1}, DType::Int32);
+        CHECK_THROWS(ctb_host::cross_entropy(logits, wrong, true), std::out_of_range, "Gather index out of bounds");
+
+        Tensor up = Tensor::from_vector({1.0, 2.0, 3.0, 4.0}, {2, 2}), num = Tensor::from_vector({2.0, 4.0, 6.0, 8.0}, {2, 2});
+        Tensor den = Tensor::from_vector({2.0, 4.0}, {1, 2});                     // broadcast over the rows
+        Tensor ga, gb;
+        ctb_host::div_backward(up, num, den, &ga, &gb);
+        CHECK(ga.shape() == std::vector<size_t>({2, 2}) && gb.shape() == std::vector<size_t>({2, 2}));
+        CHECK_NEAR(ga[1][1], 4.0 / 4.0, 1e-6);                                      // grad / b
+        CHECK_NEAR(gb[1][0], -3.0 * 6.0 / 4.0, 1e-6);                              // -grad * a / b^2
+        ctb_host::div_backward(up, num, den, nullptr, &gb);                        // either side alone
+        CHECK_NEAR(gb[0][1], -2.0 * 4.0 / 16.0, 1e-6);
+        Tensor th = ctb_host::tanh_backward(up, num);
+        CHECK_NEAR(th[0][0], 1.0 * (1.0 - std::tanh(2.0) * std::tanh(2.0)), 1e-6);
+    }
+    // matmul on the tensor cores when asked for: TF32 products, the same shapes and the same backward node
+    {
+        const size_t M = 96, K = 200, N = 72;
+        std::vector<double> av(M * K), bv(N * K);
+        for (size_t i = 0; i < av.size(); ++i) av[i] = double((i * 37) % 101) / 64.0 - 0.75;
+        for (size_t i = 0; i < bv.size(); ++i) bv[i] = double((i * 53) % 89) / 32.0 - 1.25;
+        Tensor ma = Tensor::from_vector(av, {M, K}), mb = Tensor::from_vector(bv, {N, K}, DType::Float32, true);
+        Tensor exact = matmul(ma, mb.permute({1, 0}));
+        ctb_host::set_matmul_tensor_cores(true);
+        Tensor fast = matmul(ma, mb.permute({1, 0}));
+        ctb_host::set_matmul_tensor_cores(false);
+        CHECK(fast.shape() == exact.shape() && fast.requires_grad() && fast.impl->grad_fn && fast.impl->grad_fn->op == "matmul");
+        double worst = 0.0, bound = 0.0;
+        for (size_t i : {size_t(0), M / 2, M - 1})
+            for (size_t j : {size_t(0), N / 3, N - 1}) {
+                double mag = 0.0;
+                for (size_t k = 0; k < K; ++k) mag += std::fabs(av[i * K + k] * bv[j * K + k]);
+                worst = std::fmax(worst, std::fabs(double(fast[i][j]) - double(exact[i][j])));
+                bound = std::fmax(bound, mag / 512.0);
+            }
+        CHECK(worst <= bound);
+        Tensor again = matmul(ma, mb.permute({1, 0}));                                       // switched off again: the exact kernel
+        CHECK(double(again[M - 1][N - 1]) == double(exact[M - 1][N - 1]));
+    }
+
     std::printf("ALL PASSED (%d checks)\n", g_checks);
     return 0;
 }

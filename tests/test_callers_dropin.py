@@ -157,3 +157,49 @@ def test_second_generation_callers_run_on_the_gpu_like_the_reference():
     np.testing.assert_allclose(got["mse.loss_from_operators"], [mse], rtol=RTOL)
     for k in sorted(dim_minus_one):
         assert isinstance(got[k], np.ndarray) and got[k].size == 1 and np.isfinite(got[k][0]) and 0.0 < got[k][0] < 5.0, k
+
+
+# ---- the timed training step: same numbers with and without the integration edits ----------------------------
+def _train_step_known_losses(batch, features, hidden, classes, steps, lr=0.05):
+    """tests/cpp/train_step_program.cpp in numpy (fp64): two warm-up steps + `steps` steps of plain SGD on
+    Linear -> relu -> Linear -> mean cross entropy; -> (loss of the first step, loss of the last step)."""
+    w1, b1 = _lcg(1, hidden * features, 0.05).reshape(hidden, features), _lcg(2, hidden, 0.01)
+    w2, b2 = _lcg(3, classes * hidden, 0.05).reshape(classes, hidden), _lcg(4, classes, 0.01)
+    x = _lcg(5, batch * features, 1.0).reshape(batch, features)
+    labels, rows = (np.arange(batch) * 5 + 1) % classes, np.arange(batch)
+    losses = []
+    for _ in range(steps + 2):
+        h = x @ w1.T + b1
+        a = np.maximum(h, 0)
+        z = a @ w2.T + b2
+        logp = z - z.max(1, keepdims=True)
+        logp = logp - np.log(np.exp(logp).sum(1, keepdims=True))
+        losses.append(-logp[rows, labels].mean())
+        g = np.exp(logp)
+        g[rows, labels] -= 1
+        g /= batch
+        gh = (g @ w2) * (h > 0)
+        w2, b2 = w2 - lr * (g.T @ a), b2 - lr * g.sum(0)
+        w1, b1 = w1 - lr * (gh.T @ x), b1 - lr * gh.sum(0)
+    return losses[0], losses[-1]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("exe,env,rtol", [
+    ("train_step_gen2_b200", {}, 2e-5),                       # the reference's callers unchanged
+    ("train_step_gen2_b200_edited", {}, 2e-5),                # the three bodies replaced by host-layer calls
+    ("train_step_gen2_b200_edited", {"CTB_HOST_MATMUL_TENSOR_CORES": "1"}, 5e-3),      # TF32 products
+])
+def test_training_step_follows_the_definition(exe, env, rtol):
+    import json
+    path = os.path.join(BUILT, exe)
+    if not os.path.exists(path):
+        pytest.skip(f"{path} was not built (tests/cpp/build_callers.sh needs the reference sources)")
+    shape = (64, 128, 128, 16, 5)
+    r = subprocess.run([path] + [str(v) for v in shape], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, **env))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    got = json.loads(r.stdout.strip().splitlines()[-1])
+    first, last = _train_step_known_losses(*shape)
+    np.testing.assert_allclose([got["loss_first"], got["loss_last"]], [first, last], rtol=rtol)
+    assert last < first
