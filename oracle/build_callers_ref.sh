@@ -6,7 +6,8 @@
 #
 # Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref.
 #   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
-#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp
+#          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp,
+#          dropout/dropout.cpp, norm/norm.cpp
 #   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp,
 #          batchnorm.cpp, Relu.cpp
 # All sources are compiled where they lie (the second generation through the patched symlink
@@ -25,10 +26,15 @@ trap 'rm -rf "$TMP"' EXIT
 make_ref_farm "$REF" "$TMP"
 CXX="${REF_CXX:-g++}"
 STD="-std=gnu++20 -w"
-mkdir -p "$TMP/obj2" "$TMP/obj1" "$TMP/src/neuralnet"
-for f in layer.cpp layer.h loss.cpp loss.h module.h Relu.cpp Relu.h; do ln -s "$REF/src/neuralnet/$f" "$TMP/src/neuralnet/$f"; done
-mkdir -p "$TMP/src/neuralnet/batchnorm"
-for f in batchnorm.cpp batchnorm.h; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$TMP/src/neuralnet/batchnorm/$f"; done
+mkdir -p "$TMP/obj2" "$TMP/obj1"
+# The callers' side of the tree — src/neuralnet, src/dashboard, the umbrella headers core.h and
+# neuralnet.h — file by file as symbolic links, so that every "core/tensor.h" they ask for is the
+# farm's patched one (a link to a whole directory would lead back into the real tree).
+(cd "$REF/src" && find neuralnet dashboard -type f \( -name '*.h' -o -name '*.cpp' \)) | while read -r f; do
+  mkdir -p "$TMP/src/$(dirname "$f")"
+  ln -s "$REF/src/$f" "$TMP/src/$f"
+done
+for f in core.h neuralnet.h; do ln -s "$REF/src/$f" "$TMP/src/$f"; done
 
 # ---- second generation ------------------------------------------------------------------------
 S="$TMP/src"
@@ -47,9 +53,9 @@ cc2 layer        "-O2 -fopenmp"                 "$S/neuralnet/layer.cpp"
 cc2 loss         "-O2 -fopenmp"                 "$S/neuralnet/loss.cpp"
 cc2 batchnorm    "-O2 -fopenmp"                 "$S/neuralnet/batchnorm/batchnorm.cpp"
 cc2 relu         "-O2 -fopenmp"                 "$S/neuralnet/Relu.cpp"
-# the program also includes the reference's train_utils.h (optimizers), whose own includes reach into
-# the data-loader and dashboard headers: the real tree is the last include path for those
-$CXX $STD -O1 $INC2 -I"$REF/src" -c "$PROGRAM" -o "$TMP/obj2/program.o" & pids+=($!)
+cc2 dropout      "-O2 -fopenmp"                 "$S/neuralnet/dropout/dropout.cpp"
+cc2 norm         "-O2 -fopenmp"                 "$S/neuralnet/norm/norm.cpp"
+$CXX $STD -O1 $INC2 -c "$PROGRAM" -o "$TMP/obj2/program.o" & pids+=($!)
 for p in "${pids[@]}"; do wait "$p"; done
 $CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
 # The same program with the dispatcher's CPU feature probes answering "no" (a command-line macro
@@ -61,7 +67,7 @@ $CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
 $CXX $STD -O2 -fopenmp '-D__builtin_cpu_supports(x)=0' $INC2 -c "$S/core/ops_dispatch.cpp" -o "$TMP/obj2/ops_dispatch.o"
 $CXX -o "$OUT/callers_gen2_ref_scalar" "$TMP"/obj2/*.o -fopenmp
 # the timed training step (tests/cpp/train_step_program.cpp) on the same scalar back-end
-$CXX $STD -O1 $INC2 -I"$REF/src" -c "$HERE/../tests/cpp/train_step_program.cpp" -o "$TMP/train_step.o"
+$CXX $STD -O1 $INC2 -c "$HERE/../tests/cpp/train_step_program.cpp" -o "$TMP/train_step.o"
 rm -f "$TMP/obj2/program.o"
 $CXX -o "$OUT/train_step_gen2_ref_scalar" "$TMP"/obj2/*.o "$TMP/train_step.o" -fopenmp
 

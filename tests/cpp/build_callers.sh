@@ -1,7 +1,7 @@
 #!/usr/bin/env bash
 # Builds tests/cpp/callers_program.cpp against the B200 host layers together with the
 # reference's own callers of the operator path — autograd.cpp, layer.cpp, loss.cpp, batchnorm.cpp,
-# Relu.cpp — UNCHANGED:
+# Relu.cpp, dropout.cpp, norm.cpp, metrics.h (with the umbrella headers core.h / neuralnet.h) — UNCHANGED:
 # the proof that the host layers are drop-in replacements for the reference's tensor/operator files.
 #
 #   tests/cpp/build_callers.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
@@ -32,17 +32,24 @@ LINK="-L$PKG -lctb200 -Wl,-rpath,\$ORIGIN/../../../ctensor_b200"
 
 # ---- second generation: src/core + src/neuralnet --------------------------------------------------
 G2="$TMP/gen2/src"
-mkdir -p "$G2/core" "$G2/neuralnet"
+mkdir -p "$G2/core"
 for f in tensor.h device.h ops_dispatch.h opsmp.h ctb_host.h ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G2/core/$f"; done
+# the callers' side, unchanged: autograd, the headers of src/core that only build on tensor.h (the
+# Ops:: declarations, the dtype switch macro, the image readers' declarations), the umbrella headers,
+# and src/neuralnet + src/dashboard file by file (a link to a whole directory would lead a quoted
+# #include back into the real tree, to the reference's own tensor.h)
+for f in autograd.h autograd.cpp ops.h dispatch.h data.h; do ln -s "$REF/src/core/$f" "$G2/core/$f"; done
+for f in core.h neuralnet.h; do ln -s "$REF/src/$f" "$G2/$f"; done
+(cd "$REF/src" && find neuralnet dashboard -type f \( -name '*.h' -o -name '*.cpp' \)) | while read -r f; do
+  mkdir -p "$G2/$(dirname "$f")"
+  [ "$f" = neuralnet/train_utils.h ] || ln -s "$REF/src/$f" "$G2/$f"
+done
 ln -s "$PKG/host/include/train_utils.h" "$G2/neuralnet/train_utils.h"      # replaces the reference's (optimizers, StepLR)
-for f in autograd.h autograd.cpp; do ln -s "$REF/src/core/$f" "$G2/core/$f"; done                        # unchanged
-for f in layer.h layer.cpp loss.h loss.cpp module.h Relu.h Relu.cpp; do ln -s "$REF/src/neuralnet/$f" "$G2/neuralnet/$f"; done   # unchanged
-mkdir -p "$G2/neuralnet/batchnorm"
-for f in batchnorm.h batchnorm.cpp; do ln -s "$REF/src/neuralnet/batchnorm/$f" "$G2/neuralnet/batchnorm/$f"; done      # unchanged
 ln -s "$PKG/host/glue/autograd_glue.cpp" "$G2/core/autograd_glue.cpp"
 $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/callers_gen2_b200" \
     "$HERE/callers_program.cpp" "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" \
-    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" "$G2/neuralnet/Relu.cpp" -lctensor_host $LINK
+    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss.cpp" "$G2/neuralnet/batchnorm/batchnorm.cpp" "$G2/neuralnet/Relu.cpp" \
+    "$G2/neuralnet/dropout/dropout.cpp" "$G2/neuralnet/norm/norm.cpp" -lctensor_host $LINK
 
 # the timed training step (bench.py runs it for its `host_layer.train_step` key)
 $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200" \
@@ -99,13 +106,14 @@ $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200
     "$HERE/train_step_program.cpp" "$G2/core/autograd_edited.cpp" "$G2/core/autograd_glue.cpp" \
     "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss_edited.cpp" -lctensor_host $LINK
 
-# The convolution and pooling modules are not part of the operator path (their loops run on the
-# host, over the managed storage); they must still COMPILE against the replaced headers.
-mkdir -p "$G2/neuralnet/conv" "$G2/neuralnet/pooling"
-for d in conv pooling; do for f in $d.h $d.cpp; do ln -s "$REF/src/neuralnet/$d/$f" "$G2/neuralnet/$d/$f"; done; done
-for d in conv pooling; do
-  $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -c "$G2/neuralnet/$d/$d.cpp" -o "$TMP/$d.o"
+# The convolution and pooling modules and the checkpoint reader/writer are not part of the operator
+# path (their loops run on the host, over the managed storage); they must still COMPILE against the
+# replaced headers, and so must a unit that includes the whole of nn.h (every header of the tree).
+for f in conv/conv pooling/pooling check; do
+  $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -c "$G2/neuralnet/$f.cpp" -o "$TMP/$(basename $f).o"
 done
+printf '#include <iomanip>\n#include "neuralnet/nn.h"\nint main() { return 0; }\n' > "$TMP/everything.cpp"
+$CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -c "$TMP/everything.cpp" -o "$TMP/everything.o"
 
 # ---- first generation: the root of the reference tree ----------------------------------------------
 if [ -f "$PKG/libctensor_gen1.so" ]; then

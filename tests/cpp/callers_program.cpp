@@ -2,7 +2,9 @@
 // layer.cpp, loss.cpp, unchanged — driven through a Linear layer, two losses and a chain of
 // elementwise operators, forward and backward, and — with the optimizer classes of train_utils.h —
 // through three training steps per optimizer; plus the reference's BatchNorm and activation modules
-// (batchnorm.cpp, Relu.cpp), unchanged as well.
+// (batchnorm.cpp, Relu.cpp), unchanged as well; in the second generation also its Dropout module,
+// its norm functions and its metrics (dropout.cpp, norm.cpp, metrics.h through the umbrella headers
+// core.h and neuralnet.h).
 //
 //   build                      tensor/operator layer                     callers
 //   callers_gen2_ref           the reference's src/core (CPU)            the reference's, unchanged
@@ -21,6 +23,7 @@
 #include <exception>
 #include <iomanip>          // the reference's train_utils.h uses std::setprecision without including it
 #include <iostream>
+#include <limits>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -57,6 +60,9 @@ static Tensor sum_all(Tensor t) {
 #include "neuralnet/train_utils.h"
 #include "neuralnet/batchnorm/batchnorm.h"
 #include "neuralnet/Relu.h"
+#include "neuralnet/dropout/dropout.h"
+#include "neuralnet/norm/norm.h"          // includes core.h: every header of src/core
+#include "neuralnet/metrics.h"            // includes neuralnet.h: every header of src/neuralnet
 #define CTB_HAVE_BATCHNORM 1
 #define DATA(t) ((t).impl->data->data.get())
 #define GRAD(t) ((t).impl->grad ? (t).impl->grad->data->data.get() : nullptr)
@@ -105,6 +111,8 @@ void print_grad(const char* name, const Tensor& t) {
     if (!g) { std::printf("%s unavailable no gradient buffer\n", name); return; }
     print_values(name, g, t.numel());
 }
+
+void print_number(const char* name, double v) { std::printf("%s 1 %.9g\n", name, v); }
 
 template <typename F> void section(const char* name, F body) {
     try {
@@ -243,6 +251,70 @@ int main() {
         print_grad("act.prelu_grad_x", z);
         print_grad("act.prelu_grad_weight", prelu.weight);
     });
+
+#ifndef CTB_GEN1
+    // Dropout (src/neuralnet/dropout/dropout.cpp, unchanged): the mask is drawn on the host from a
+    // generator with a fixed seed, so every build draws the same one; forward = input * mask * scale
+    // through the operators, GradDropout::backward the same on the gradient; identity after eval()
+    section("dropout", [&] {
+        Dropout drop(0.3);
+        Tensor x = filled({6, 8}, 51, 1.0, true);
+        Tensor y = drop.forward(x);
+        print_data("dropout.forward", y);
+        Tensor total = F_SUM_ALL(y * y);
+        print_data("dropout.value", total);
+        total.backward();
+        print_grad("dropout.grad_x", x);
+        drop.eval();
+        print_data("dropout.eval_forward", drop.forward(x));
+    });
+
+    // The norm functions (src/neuralnet/norm/norm.cpp, unchanged): abs, pow_scalar, sum / max / min
+    // over a dim, sqrt, the comparison against zero, unsqueeze for keepdim, and the global forms
+    section("norm", [&] {
+        Tensor x = filled({5, 7}, 52, 2.0, false);
+        for (size_t i = 0; i < x.numel(); i += 4) write_scalar_at(DATA(x), i, DType::Float32, 0.0);   // zeros for the count
+        const double inf = std::numeric_limits<double>::infinity();
+        print_data("norm.l1_rows", norm(x, 1.0, 1));
+        print_data("norm.l2_cols", norm(x, 2.0, 0));
+        print_data("norm.max_rows", norm(x, inf, 1));
+        print_data("norm.min_cols", norm(x, -inf, 0));
+        print_data("norm.count_rows", norm(x, 0.0, 1));
+        print_data("norm.l3_rows_keepdim", norm(x, 3.0, 1, true));
+        print_data("norm.l2_negative_dim", norm(x, 2.0, -2));         // wraps to dim 0
+        print_data("norm.l2_global", norm(x, 2.0));
+        print_data("norm.l1_global", norm(x, 1.0));
+        print_data("norm.l3_global", norm(x, 3.0));
+        print_data("norm.infinity_global", infinity_norm(x));
+        print_data("norm.zero_cols", zero_norm(x, 0));
+    });
+
+    // The metrics of src/neuralnet/metrics.h (header-only, unchanged): argmax, comparisons, astype,
+    // full sums and means, item<float>()
+    section("metrics", [&] {
+        Tensor logits = filled({12, 10}, 53, 1.0, false);
+        Tensor labels({12, 1}, DType::Int32, false);
+        for (size_t i = 0; i < 12; ++i) {       // half of the labels are the row's argmax, half are not
+            size_t best = 0;
+            for (size_t c = 1; c < 10; ++c)
+                if (read_scalar_at(DATA(logits), i * 10 + c, DType::Float32) > read_scalar_at(DATA(logits), i * 10 + best, DType::Float32)) best = c;
+            write_scalar_at(DATA(labels), i, DType::Int32, (double)(i % 2 ? best : (best + 3) % 10));
+        }
+        print_number("metrics.accuracy", (double)torch::metrics::accuracy(logits, labels));
+        print_number("metrics.accuracy_score", torch::metrics::accuracy_score(logits, labels));
+        Tensor scores = filled({16, 1}, 54, 0.5, false, 0.5);
+        Tensor truth({16, 1}, DType::Float32, false);
+        for (size_t i = 0; i < 16; ++i) write_scalar_at(DATA(truth), i, DType::Float32, (double)((i * 5 + 1) % 3 == 0));
+        print_number("metrics.binary_accuracy", torch::metrics::binary_accuracy(scores, truth));
+        print_number("metrics.precision", torch::metrics::precision_score(scores, truth));
+        print_number("metrics.recall", torch::metrics::recall_score(scores, truth));
+        print_number("metrics.f1", torch::metrics::f1_score(scores, truth, 0.4f));
+        Tensor predicted = filled({24}, 55, 1.0, false), wanted = filled({24}, 56, 1.0, false);
+        print_number("metrics.mse", torch::metrics::mean_squared_error(predicted, wanted));
+        print_number("metrics.mae", torch::metrics::mean_absolute_error(predicted, wanted));
+        print_number("metrics.r2", torch::metrics::r2_score(predicted, wanted));
+    });
+#endif
 
     // Three training steps of Linear -> CrossEntropy with each optimizer class of train_utils.h:
     // zero_grad, forward, backward, step — the loop a user of the reference writes.  In the *_b200

@@ -1,5 +1,6 @@
 """The drop-in claim, tested: the reference's own callers of the operator path — autograd.cpp,
-layer.cpp, loss.cpp of both generations, UNCHANGED — compile and link against the B200 host
+layer.cpp, loss.cpp, batchnorm.cpp, Relu.cpp of both generations and, in the second, dropout.cpp,
+norm.cpp and metrics.h behind the umbrella headers, UNCHANGED — compile and link against the B200 host
 layers (CPU test, where the reference sources exist), and the program they form
 (tests/cpp/callers_program.cpp: Linear -> losses -> backward, broadcast chains) gives on the GPU
 what the same program gives when it is linked against the reference itself (GPU test; golden lines
@@ -150,6 +151,9 @@ def test_second_generation_callers_run_on_the_gpu_like_the_reference():
     dim_minus_one = {"mse.loss", "ce.loss"} | {k for k in want if k.startswith("optim_") and k.endswith(".loss")}
     names = [k for k, v in want.items() if isinstance(v, np.ndarray) and k not in dim_minus_one]
     assert len(names) >= 15 + 18                            # + weight and bias after three steps of nine optimizers
+    for line in ("dropout.forward", "dropout.grad_x", "dropout.eval_forward", "norm.l2_cols", "norm.l3_rows_keepdim",
+                 "norm.l2_global", "norm.zero_cols", "metrics.accuracy", "metrics.f1", "metrics.r2"):
+        assert line in names, line                          # dropout.cpp, norm.cpp, metrics.h ran in the reference build
     assert_lines_match(got, want, names, "gen 2")
     mse, ce = _known_losses()
     np.testing.assert_allclose(got["mse.loss"], [mse], rtol=RTOL, err_msg="Loss::MSE")
