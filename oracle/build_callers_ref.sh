@@ -9,7 +9,7 @@
 #          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp,
 #          dropout/dropout.cpp, norm/norm.cpp
 #   gen 1: the reference's root tensor1.cpp, opsmp.cpp, autograd.cpp, layer.cpp, loss.cpp, data.cpp,
-#          batchnorm.cpp, Relu.cpp
+#          batchnorm.cpp, Relu.cpp, dropout.cpp
 # All sources are compiled where they lie (the second generation through the patched symlink
 # farm of ref_farm.sh); nothing is copied into the repository.
 set -euo pipefail
@@ -74,7 +74,7 @@ $CXX -o "$OUT/train_step_gen2_ref_scalar" "$TMP"/obj2/*.o "$TMP/train_step.o" -f
 # ---- first generation (root of the reference tree) -----------------------------------------------
 pids=()
 cc1() { $CXX $STD -O2 -fopenmp -DCTB_GEN1 -I"$REF" -c "$2" -o "$TMP/obj1/$1.o" & pids+=($!); }
-for f in tensor1 opsmp autograd layer loss data batchnorm Relu; do cc1 "$f" "$REF/$f.cpp"; done
+for f in tensor1 opsmp autograd layer loss data batchnorm Relu dropout; do cc1 "$f" "$REF/$f.cpp"; done
 cc1 program "$PROGRAM"
 for p in "${pids[@]}"; do wait "$p"; done
 $CXX -o "$OUT/callers_gen1_ref" "$TMP"/obj1/*.o -fopenmp

@@ -121,10 +121,12 @@ if [ -f "$PKG/libctensor_gen1.so" ]; then
   mkdir -p "$G1"
   for f in tensor1.h opsmp.h ops1.h ctb_gen1.h train_utils.h; do ln -s "$PKG/host/gen1/include/$f" "$G1/$f"; done
   for f in ctb_optimizer.h optimizer_classes.h; do ln -s "$PKG/host/include/$f" "$G1/$f"; done
-  for f in autograd.h autograd.cpp layer.h layer.cpp loss.h loss.cpp module.h batchnorm.h batchnorm.cpp Relu.h Relu.cpp; do ln -s "$REF/$f" "$G1/$f"; done   # unchanged
+  for f in autograd.h autograd.cpp layer.h layer.cpp loss.h loss.cpp module.h batchnorm.h batchnorm.cpp Relu.h Relu.cpp \
+           dropout.h dropout.cpp pooling.h pooling.cpp check.h check.cpp; do ln -s "$REF/$f" "$G1/$f"; done   # unchanged
   ln -s "$PKG/host/gen1/autograd_glue_gen1.cpp" "$G1/autograd_glue_gen1.cpp"
   $CXX $FLAGS -DCTB_GEN1 -I"$G1" -o "$OUT/callers_gen1_b200" \
       "$HERE/callers_program.cpp" "$G1/autograd.cpp" "$G1/autograd_glue_gen1.cpp" "$G1/layer.cpp" "$G1/loss.cpp" \
-      "$G1/batchnorm.cpp" "$G1/Relu.cpp" -lctensor_gen1 $LINK
+      "$G1/batchnorm.cpp" "$G1/Relu.cpp" "$G1/dropout.cpp" -lctensor_gen1 $LINK
+  for f in pooling check; do $CXX $FLAGS -DCTB_GEN1 -I"$G1" -c "$G1/$f.cpp" -o "$TMP/gen1_$f.o"; done      # compile only
 fi
 echo "built $(ls "$OUT" | tr '\n' ' ')"

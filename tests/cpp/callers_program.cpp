@@ -2,8 +2,8 @@
 // layer.cpp, loss.cpp, unchanged — driven through a Linear layer, two losses and a chain of
 // elementwise operators, forward and backward, and — with the optimizer classes of train_utils.h —
 // through three training steps per optimizer; plus the reference's BatchNorm and activation modules
-// (batchnorm.cpp, Relu.cpp), unchanged as well; in the second generation also its Dropout module,
-// its norm functions and its metrics (dropout.cpp, norm.cpp, metrics.h through the umbrella headers
+// and its Dropout module (batchnorm.cpp, Relu.cpp, dropout.cpp), unchanged as well; in the second
+// generation also its norm functions and its metrics (dropout.cpp, norm.cpp, metrics.h through the umbrella headers
 // core.h and neuralnet.h).
 //
 //   build                      tensor/operator layer                     callers
@@ -37,6 +37,7 @@
 #include "train_utils.h"
 #include "batchnorm.h"
 #include "Relu.h"
+#include "dropout.h"
 #define CTB_HAVE_BATCHNORM 1
 #define DATA(t) ((t).impl->storage->data.get())
 #define GRAD(t) ((t).impl->storage->grad.get())
@@ -252,8 +253,7 @@ int main() {
         print_grad("act.prelu_grad_weight", prelu.weight);
     });
 
-#ifndef CTB_GEN1
-    // Dropout (src/neuralnet/dropout/dropout.cpp, unchanged): the mask is drawn on the host from a
+    // Dropout (src/neuralnet/dropout/dropout.cpp, root dropout.cpp, unchanged): the mask is drawn on the host from a
     // generator with a fixed seed, so every build draws the same one; forward = input * mask * scale
     // through the operators, GradDropout::backward the same on the gradient; identity after eval()
     section("dropout", [&] {
@@ -269,6 +269,7 @@ int main() {
         print_data("dropout.eval_forward", drop.forward(x));
     });
 
+#ifndef CTB_GEN1
     // The norm functions (src/neuralnet/norm/norm.cpp, unchanged): abs, pow_scalar, sum / max / min
     // over a dim, sqrt, the comparison against zero, unsqueeze for keepdim, and the global forms
     section("norm", [&] {

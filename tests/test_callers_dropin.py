@@ -141,6 +141,7 @@ def test_first_generation_callers_run_on_the_gpu_like_the_reference():
     got, want = run_built("callers_gen1_b200"), golden("callers_gen1_ref")
     names = [k for k, v in want.items() if isinstance(v, np.ndarray)]
     assert sum(k.startswith("optim_") for k in names) == 27          # loss, weight, bias of nine optimizers
+    assert sum(k.startswith("dropout.") for k in names) == 4         # root dropout.cpp ran in the reference build
     assert_lines_match(got, want, names, "gen 1")
 
 
