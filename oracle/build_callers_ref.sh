@@ -4,7 +4,8 @@
 #
 #   oracle/build_callers_ref.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
 #
-# Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref.
+# Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref,
+# train_step_gen2_ref_scalar, verify_gen1_ref.
 #   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
 #          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp,
 #          dropout/dropout.cpp, norm/norm.cpp
@@ -76,6 +77,12 @@ pids=()
 cc1() { $CXX $STD -O2 -fopenmp -DCTB_GEN1 -I"$REF" -c "$2" -o "$TMP/obj1/$1.o" & pids+=($!); }
 for f in tensor1 opsmp autograd layer loss data batchnorm Relu dropout; do cc1 "$f" "$REF/$f.cpp"; done
 cc1 program "$PROGRAM"
+$CXX $STD -O2 -fopenmp -I"$REF" -c "$REF/ops1.cpp" -o "$TMP/ops1.o" & pids+=($!)
+$CXX $STD -O1 -fopenmp -I"$REF" -c "$REF/verify.cpp" -o "$TMP/verify.o" & pids+=($!)
 for p in "${pids[@]}"; do wait "$p"; done
 $CXX -o "$OUT/callers_gen1_ref" "$TMP"/obj1/*.o -fopenmp
+# the reference's own gradient checks of the first generation (root verify.cpp: losses and one backward
+# pass per operator, printed), linked with the reference's tensor1 / opsmp / ops1 / autograd / loss
+rm -f "$TMP/obj1/program.o"
+$CXX -o "$OUT/verify_gen1_ref" "$TMP"/obj1/*.o "$TMP/ops1.o" "$TMP/verify.o" -fopenmp
 echo "built $OUT/callers_gen2_ref $OUT/callers_gen1_ref"

@@ -6,7 +6,8 @@
 #
 #   tests/cpp/build_callers.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
 #
-# Outputs: tests/cpp/_built/callers_gen2_b200, tests/cpp/_built/callers_gen1_b200.
+# Outputs: tests/cpp/_built/callers_gen2_b200, callers_gen1_b200, train_step_gen2_b200(_edited),
+# reference_test_tensor_b200, reference_test_ops_b200, reference_verify_gen1_b200.
 #
 # What a maintainer of the reference does is: replace tensor.h / device.h / ops_dispatch.h /
 # opsmp.h (second generation) or tensor1.h / opsmp.h / ops1.h (first generation) by the headers
@@ -106,6 +107,13 @@ $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200
     "$HERE/train_step_program.cpp" "$G2/core/autograd_edited.cpp" "$G2/core/autograd_glue.cpp" \
     "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss_edited.cpp" -lctensor_host $LINK
 
+# The reference's own unit tests of the tensor type and the operator dispatcher (test/test.cpp,
+# test/test_ops.cpp: known answers for creation, indexing, views, gather, arithmetic, matmul, reductions,
+# broadcasting, astype, a backward pass), unchanged: they exit non-zero on the first failed assertion.
+$CXX $FLAGS -I"$G2" -I"$G2/core" -o "$OUT/reference_test_tensor_b200" "$REF/test/test.cpp" -lctensor_host $LINK
+$CXX $FLAGS -I"$G2" -I"$G2/core" -o "$OUT/reference_test_ops_b200" "$REF/test/test_ops.cpp" \
+    "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" -lctensor_host $LINK
+
 # The convolution and pooling modules and the checkpoint reader/writer are not part of the operator
 # path (their loops run on the host, over the managed storage); they must still COMPILE against the
 # replaced headers, and so must a unit that includes the whole of nn.h (every header of the tree).
@@ -127,6 +135,11 @@ if [ -f "$PKG/libctensor_gen1.so" ]; then
   $CXX $FLAGS -DCTB_GEN1 -I"$G1" -o "$OUT/callers_gen1_b200" \
       "$HERE/callers_program.cpp" "$G1/autograd.cpp" "$G1/autograd_glue_gen1.cpp" "$G1/layer.cpp" "$G1/loss.cpp" \
       "$G1/batchnorm.cpp" "$G1/Relu.cpp" "$G1/dropout.cpp" -lctensor_gen1 $LINK
+  # the reference's own gradient checks of this generation (root verify.cpp), unchanged; its printed
+  # output is compared with what the same file prints when linked with the reference
+  ln -s "$REF/verify.cpp" "$G1/verify.cpp"
+  $CXX $FLAGS -DCTB_GEN1 -I"$G1" -o "$OUT/reference_verify_gen1_b200" "$G1/verify.cpp" "$G1/autograd.cpp" \
+      "$G1/autograd_glue_gen1.cpp" "$G1/loss.cpp" -lctensor_gen1 $LINK
   for f in pooling check; do $CXX $FLAGS -DCTB_GEN1 -I"$G1" -c "$G1/$f.cpp" -o "$TMP/gen1_$f.o"; done      # compile only
 fi
 echo "built $(ls "$OUT" | tr '\n' ' ')"

@@ -1,6 +1,7 @@
 """Generate tests/golden/callers_gen1_ref.txt, callers_gen2_ref.txt and callers_gen2_ref_scalar.txt: the output of
 tests/cpp/callers_program.cpp built against the REFERENCE ITSELF (oracle/build_callers_ref.sh
-builds oracle/_ref/callers_gen{1,2}_ref from the reference's own sources first).
+builds oracle/_ref/callers_gen{1,2}_ref from the reference's own sources first) — and
+verify_gen1_ref.txt: what the reference's own root verify.cpp prints when linked with the reference.
 
     oracle/build_callers_ref.sh <reference root> && python tests/golden/make_callers_golden.py
 
@@ -16,7 +17,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 
 def main():
-    for name in ("callers_gen1_ref", "callers_gen2_ref", "callers_gen2_ref_scalar"):
+    for name in ("callers_gen1_ref", "callers_gen2_ref", "callers_gen2_ref_scalar", "verify_gen1_ref"):
         exe = os.path.join(ROOT, "oracle", "_ref", name)
         out = subprocess.run([exe], capture_output=True, text=True, check=True, cwd="/tmp").stdout
         path = os.path.join(HERE, f"{name}.txt")

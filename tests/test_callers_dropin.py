@@ -208,3 +208,45 @@ def test_training_step_follows_the_definition(exe, env, rtol):
     first, last = _train_step_known_losses(*shape)
     np.testing.assert_allclose([got["loss_first"], got["loss_last"]], [first, last], rtol=rtol)
     assert last < first
+
+
+# ---- the reference's own unit tests, unchanged, over the host layer ----------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("exe,last_line", [
+    ("reference_test_tensor_b200", "All Tests Passed!"),                       # test/test.cpp
+    ("reference_test_ops_b200", "All tests completed successfully."),          # test/test_ops.cpp
+])
+def test_reference_unit_tests_pass_over_the_host_layer(exe, last_line):
+    path = os.path.join(BUILT, exe)
+    if not os.path.exists(path):
+        pytest.skip(f"{path} was not built (tests/cpp/build_callers.sh needs the reference sources)")
+    r = subprocess.run([path], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.strip().splitlines()[-1] == last_line
+    assert "Skipped" not in r.stdout and "Skipping" not in r.stdout           # broadcasting and the gradient check ran
+
+
+_NUMBER = r"[-+]?(?:\d+\.?\d*|\.\d+)(?:[eE][-+]?\d+)?"
+
+
+def _text_and_numbers(text):
+    """-> (the text with every number replaced by '#', the numbers)"""
+    import re
+    return re.sub(_NUMBER, "#", text), [float(x) for x in re.findall(_NUMBER, text)]
+
+
+@pytest.mark.gpu
+def test_first_generation_gradient_checks_print_what_the_reference_prints():
+    """The reference's root verify.cpp (Huber / MAE / CrossEntropy / MSE losses and one backward pass per
+    operator through ops1.h, printed), unchanged over the first-generation host layer, against the same
+    file linked with the reference (tests/golden/verify_gen1_ref.txt): same text, numbers equal to the
+    printed precision."""
+    path = os.path.join(BUILT, "reference_verify_gen1_b200")
+    if not os.path.exists(path):
+        pytest.skip(f"{path} was not built (tests/cpp/build_callers.sh needs the reference sources)")
+    r = subprocess.run([path], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    got_text, got = _text_and_numbers(r.stdout)
+    want_text, want = _text_and_numbers(open(os.path.join(GOLDEN, "verify_gen1_ref.txt")).read())
+    assert got_text == want_text
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
