@@ -413,10 +413,14 @@ def log_softmax(x, mask=None, out=None):
 
 
 def gather(x, dim: int, index, out=None):
-    """Tensor::gather: out[i] = x[i with coordinate ``dim`` replaced by index[i]] (index: int32).
+    """Tensor::gather: out[i] = x[i with coordinate ``dim`` replaced by index[i]]; the index may hold
+    any integer dtype (src/core/tensor.cpp:352-356 of the reference refuses the floating ones: so does
+    this binding; the library itself also takes them, as the first generation's gather does).
     Raises CtbError(CTB_ERR_DIM) with the reference's text when an index is out of bounds."""
     torch = _torch()
     x, idx = _as_dview(x), _as_dview(index)
+    if idx.dtype in (F32, F64):
+        raise CtbError(3, "Index tensor must be integer type")
     if out is None:
         out = _new_out(x, idx.shape)
     bad = torch.zeros(1, dtype=torch.int32, device=x.buf.device)

@@ -710,7 +710,7 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
     if ((rc = check_view(index, "Gather with empty index", "gather"))) return rc;
     if (dim < 0 || dim >= x->ndim) return set_error(CTB_ERR_DIM, "Gather dimension out of range");
     if (x->ndim != index->ndim) return set_error(CTB_ERR_SHAPE, "Input and index must have same number of dimensions");
-    if (index->dtype != CTB_I32) return set_error(CTB_ERR_DTYPE, "Index tensor must be integer type");
+    if (!dtype_ok(index->dtype)) return set_error(CTB_ERR_DTYPE, "gather: unsupported index dtype");
     for (int d = 0; d < x->ndim; ++d)
         if (d != dim && index->shape[d] > x->shape[d])
             return set_error(CTB_ERR_SHAPE, "Index shape dimension mismatch with input");
@@ -718,7 +718,7 @@ int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view
     if (bad) CTB_CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(int32_t), (cudaStream_t)stream));
     if (view_numel(index) == 0) return CTB_OK;
     return launch_gather((int)dtype_bytes(x->dtype), x->ndim, index->shape, x->stride, index->stride, dim,
-                         x->shape[dim], elem_ptr(x), (const int32_t*)elem_ptr(index), elem_ptr_mut(out), bad,
+                         x->shape[dim], elem_ptr(x), elem_ptr(index), index->dtype, elem_ptr_mut(out), bad,
                          (cudaStream_t)stream);
 }
 

@@ -154,8 +154,8 @@ int launch_unary(int op, int dtype, const Plan& plan, const void* a, double scal
 int launch_copy(int elem_bytes, const Plan& plan, const void* a, void* out, cudaStream_t stream);
 // out[i] = x[i with coordinate `dim` replaced by index[i]]; shapes/strides have `ndim` entries.
 int launch_gather(int elem_bytes, int ndim, const int64_t* ishape, const int64_t* xstride, const int64_t* istride,
-                  int dim, int64_t gsize, const void* x, const int32_t* index, void* out, int32_t* bad,
-                  cudaStream_t stream);
+                  int dim, int64_t gsize, const void* x, const void* index, int index_dtype, void* out, int32_t* bad,
+                  cudaStream_t st);
 // grad[...] += src[...] (finite values only) over `shape`, any strides.
 int launch_accumulate_strided(int dtype, int ndim, const int64_t* shape, const int64_t* gstride,
                               const int64_t* sstride, void* grad, const void* src, cudaStream_t stream);

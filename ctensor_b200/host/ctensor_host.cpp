@@ -481,10 +481,15 @@ Tensor Tensor::gather(const Tensor& index, size_t dim) const {
     if (!impl) throw std::runtime_error("Gather on empty tensor");
     if (!index.impl) throw std::runtime_error("Gather with empty index");
     if (dim >= impl->ndim) throw std::out_of_range("Gather dimension out of range");
+    if (impl->ndim != index.impl->ndim) throw std::runtime_error("Input and index must have same number of dimensions");
+    const DType index_dtype = index._dtype();            // any integer dtype (src/core/tensor.cpp:352-356)
+    if (index_dtype == DType::Float32 || index_dtype == DType::Double64 || index_dtype == DType::Float16)
+        throw std::runtime_error("Index tensor must be integer type");
     use_device_of(*this);
     Tensor out = new_output(index.shape(), impl->dtype, device());
     out.impl->requires_grad = impl->requires_grad;
     if (out.numel() == 0) return out;
+    ctb_host::ScalarBackEndScope every_dtype;           // values are moved, indices read through double: any dtype
     const ctb_view vx = view_of(*this, "gather"), vi = view_of(index, "gather"), vo = view_of(out, "gather");
     // the kernel cannot throw: it raises a flag in managed memory that is read after the wait
     // (one flag per device, allocated on first use and kept)

@@ -495,14 +495,14 @@ void Tensor::print_shape() const {
 }
 
 // out[i] = input[i with coordinate `dim` replaced by index[i]] (tensor1.cpp:478-565).  The index
-// tensor may hold any dtype there (values pass through double); here it must be Int32, which is
-// what the callers' data loaders produce.  No backward node, as in the reference.
+// tensor may hold any dtype (its values pass through double and are truncated, :548-549), e.g. the
+// Float32 one-hot targets the reference's verify.cpp hands to Loss::CrossEntropy.  No backward
+// node, as in the reference.
 Tensor Tensor::gather(const Tensor& index, size_t dim) const {
     if (!impl || !index.impl) throw std::runtime_error("gather: input or index tensor is empty");
     if (impl->ndim != index.impl->ndim) throw std::runtime_error("gather: input and index must have same number of dimensions");
     for (size_t i = 0; i < impl->ndim; ++i)
         if (i != dim && impl->shape[i] != index.impl->shape[i]) throw std::runtime_error("gather: shape mismatch");
-    if (index._dtype() != DType::Int32) throw std::runtime_error("gather: the index tensor must be Int32");
     ensure_device();
     Tensor out = new_output(index.shape(), _dtype(), impl->requires_grad);
     if (out.numel() == 0) return out;

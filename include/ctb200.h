@@ -292,9 +292,11 @@ int ctb_batchnorm_apply(const ctb_view* x, const ctb_view* mean, const ctb_view*
 
 /* ---- callers either side of the path --------------------------------------------------------
  * Tensor::gather, src/core/tensor.cpp:344-428: out[i] = x[i with coordinate `dim` replaced by
- * index[i]].  `index` is CTB_I32 with x's number of dims and extents no larger than x's outside
- * `dim`; `out` is contiguous with index's shape and x's dtype.  Negative indices count from the
- * end.  The reference throws "Gather index out of bounds"; a kernel cannot, so such an element
+ * index[i]].  `index` has x's number of dims and extents no larger than x's outside `dim`; it may
+ * hold any dtype — the reference reads an index through double and truncates it (:385-386; it
+ * refuses the floating types at :352-356, the first generation's tensor1.cpp:548-549 takes them
+ * too; that check is the caller's).  `out` is contiguous with index's shape and x's dtype, any of
+ * the eleven.  Negative indices count from the end.  The reference throws "Gather index out of bounds"; a kernel cannot, so such an element
  * is written as 0 and *bad (one int32 in device memory, may be NULL; cleared on `stream` first)
  * is set to 1 for the caller to test after synchronising. */
 int ctb_gather(const ctb_view* x, int dim, const ctb_view* index, const ctb_view* out,

@@ -154,6 +154,8 @@ int main() {
     CHECK_NEAR(picked[0][0], double(lsm[0][2]), 0.0);
     CHECK_NEAR(picked[1][0], double(lsm[1][0]), 0.0);
     CHECK_NEAR(mean(picked * -1.0).item<double>(), -(double(lsm[0][2]) + double(lsm[1][0])) / 2, 1e-6);
+    CHECK_NEAR(lsm.gather(Tensor::from_vector({2, 0}, {2, 1}, DType::Int64), 1)[0][0], double(lsm[0][2]), 0.0);     // any integer index dtype
+    CHECK_NEAR(lsm.gather(Tensor::from_vector({1, 2}, {2, 1}, DType::UInt8), 1)[1][0], double(lsm[1][2]), 0.0);
     CHECK_THROWS(lsm.gather(Tensor::from_vector({3, 0}, {2, 1}, DType::Int32), 1), std::out_of_range, "Gather index out of bounds");
     CHECK_THROWS(lsm.gather(tgt, 2), std::out_of_range, "Gather dimension out of range");
     CHECK_THROWS(lsm.gather(Tensor::from_vector({0, 0}, {2, 1}), 1), std::runtime_error, "Index tensor must be integer type");

@@ -73,6 +73,19 @@ def test_gather_out_of_bounds_is_reported(ct):
     assert "Index shape dimension mismatch" in e.value.message
 
 
+@pytest.mark.parametrize("index_dtype", ["int64", "int16", "uint8", "int8"])
+@pytest.mark.parametrize("x_dtype", ["float32", "float64", "int16", "uint8", "int64"])
+def test_gather_any_integer_index_and_element_size(ct, index_dtype, x_dtype):
+    """The reference reads indices through double from any integer dtype (src/core/tensor.cpp:385-386) and
+    moves elements of any size."""
+    torch.manual_seed(11)
+    x = (torch.randn(64, 100, device="cuda") * 50).to(getattr(torch, x_dtype))
+    idx = torch.randint(0, 100, (64, 37), device="cuda").to(getattr(torch, index_dtype))
+    got = ct.gather(x.t(), 0, idx.t().contiguous())          # a strided source as well
+    assert torch.equal(got, torch.gather(x.t(), 0, idx.t().long()))
+    assert torch.equal(ct.gather(x, 1, idx), torch.gather(x, 1, idx.long()))
+
+
 def test_gather_large_matches_torch(ct):
     x = torch.randn(4096, 512, device="cuda")
     idx = torch.randint(0, 512, (4096, 64), device="cuda", dtype=torch.int32)
