@@ -439,7 +439,30 @@ def host_layer_bench():
     except Exception as exc:
         return {"error": repr(exc)}
     res["train_step"] = train_step_bench()
+    res["reference_time_avx"] = reference_timing_program()
     return res
+
+
+def reference_timing_program():
+    """The reference's own timing program (test/time_avx.cpp: 100 x add_mp, then 100 x add, of two
+    1000 x 1000 tensors), built unchanged over the host layer and against the reference itself; seconds
+    for the 100 calls as the program prints them."""
+    import re
+    out = {}
+    for name, exe in (("b200", os.path.join(ROOT, "tests", "cpp", "_built", "reference_time_avx_b200")),
+                      ("reference_cpu", os.path.join(ROOT, "oracle", "_ref", "time_avx_gen2_ref"))):
+        if not os.path.exists(exe):
+            out[name] = "not built"
+            continue
+        try:
+            subprocess.run([exe], capture_output=True, text=True, timeout=120)          # first run: page faults, pool
+            r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+            t = re.findall(r"100 (\w+) additions of 1000x1000 tensors: ([-+.eE0-9]+) seconds", r.stdout)
+            out[name] = ({("add_mp_100_calls_s" if k == "Scalar" else "add_100_calls_s"): float(v) for k, v in t}
+                         or {"error": (r.stdout + r.stderr)[-200:]})
+        except Exception as exc:
+            out[name] = {"error": repr(exc)}
+    return out
 
 
 def train_step_bench():

@@ -5,7 +5,7 @@
 #   oracle/build_callers_ref.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
 #
 # Outputs (only into oracle/_ref/): callers_gen2_ref, callers_gen2_ref_scalar, callers_gen1_ref,
-# train_step_gen2_ref_scalar, verify_gen1_ref.
+# train_step_gen2_ref_scalar, time_avx_gen2_ref, verify_gen1_ref.
 #   gen 2: the reference's src/core (tensor, opsmp, ops_dispatch, autograd, both SIMD back-ends,
 #          shipped per-target flags) + src/neuralnet/layer.cpp, loss.cpp, Relu.cpp, batchnorm/batchnorm.cpp,
 #          dropout/dropout.cpp, norm/norm.cpp
@@ -67,6 +67,10 @@ $CXX -o "$OUT/callers_gen2_ref" "$TMP"/obj2/*.o -fopenmp
 # cannot run there; the scalar back-end honours strides and dims.
 $CXX $STD -O2 -fopenmp '-D__builtin_cpu_supports(x)=0' $INC2 -c "$S/core/ops_dispatch.cpp" -o "$TMP/obj2/ops_dispatch.o"
 $CXX -o "$OUT/callers_gen2_ref_scalar" "$TMP"/obj2/*.o -fopenmp
+# the reference's own timing program (test/time_avx.cpp) as shipped: SIMD dispatcher against add_mp
+$CXX $STD -O2 -fopenmp $INC2 -c "$REF/test/time_avx.cpp" -o "$TMP/time_avx.o"
+$CXX $STD -O2 -fopenmp $INC2 -c "$S/core/ops_dispatch.cpp" -o "$TMP/ops_dispatch_simd.o"
+$CXX -o "$OUT/time_avx_gen2_ref" $(ls "$TMP"/obj2/*.o | grep -v -e program.o -e ops_dispatch.o) "$TMP/ops_dispatch_simd.o" "$TMP/time_avx.o" -fopenmp
 # the timed training step (tests/cpp/train_step_program.cpp) on the same scalar back-end
 $CXX $STD -O1 $INC2 -c "$HERE/../tests/cpp/train_step_program.cpp" -o "$TMP/train_step.o"
 rm -f "$TMP/obj2/program.o"

@@ -7,7 +7,7 @@
 #   tests/cpp/build_callers.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
 #
 # Outputs: tests/cpp/_built/callers_gen2_b200, callers_gen1_b200, train_step_gen2_b200(_edited),
-# reference_test_tensor_b200, reference_test_ops_b200, reference_verify_gen1_b200.
+# reference_test_tensor_b200, reference_test_ops_b200, reference_time_avx_b200, reference_verify_gen1_b200.
 #
 # What a maintainer of the reference does is: replace tensor.h / device.h / ops_dispatch.h /
 # opsmp.h (second generation) or tensor1.h / opsmp.h / ops1.h (first generation) by the headers
@@ -113,6 +113,10 @@ $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200
 $CXX $FLAGS -I"$G2" -I"$G2/core" -o "$OUT/reference_test_tensor_b200" "$REF/test/test.cpp" -lctensor_host $LINK
 $CXX $FLAGS -I"$G2" -I"$G2/core" -o "$OUT/reference_test_ops_b200" "$REF/test/test_ops.cpp" \
     "$G2/core/autograd.cpp" "$G2/core/autograd_glue.cpp" -lctensor_host $LINK
+
+# The reference's own timing program (test/time_avx.cpp: 100 x add_mp and 100 x add of two 1000 x 1000
+# tensors), unchanged; bench.py runs it beside the same file linked with the reference.
+$CXX $FLAGS -I"$G2" -I"$G2/core" -o "$OUT/reference_time_avx_b200" "$REF/test/time_avx.cpp" -lctensor_host $LINK
 
 # The convolution and pooling modules and the checkpoint reader/writer are not part of the operator
 # path (their loops run on the host, over the managed storage); they must still COMPILE against the
