@@ -462,6 +462,9 @@ def reference_timing_program():
                          or {"error": (r.stdout + r.stderr)[-200:]})
         except Exception as exc:
             out[name] = {"error": repr(exc)}
+    out["note"] = ("the program times its first loop (add_mp) from a cold start: on the GPU build that loop contains the "
+                   "one-time load of the elementwise kernel module (about 0.1 s, measured: first call 100 ms, later calls "
+                   "13 us); the second loop (add) is the steady state")
     return out
 
 
