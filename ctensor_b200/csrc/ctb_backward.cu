@@ -250,7 +250,9 @@ struct OnlineSum {
         if (vm > m) raise(vm);
         const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-m)));
         const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-m)));
-        z = __dadd_rn(__dadd_rn(__dadd_rn(__dadd_rn(z, (double)e0.x), (double)e0.y), (double)e1.x), (double)e1.y);
+        // the four terms of a vector (each in (0, 1]) meet in fp32 first: one widening per vector
+        const float2 s = __fadd2_rn(e0, e1);
+        z = __dadd_rn(z, (double)__fadd_rn(s.x, s.y));
     }
 };
 

@@ -318,6 +318,13 @@ __device__ __forceinline__ int64_t ce_label(int32_t label, int64_t classes, int3
     return l;
 }
 
+#ifndef CTB_CE_LOSS_F32_PARTIALS
+#define CTB_CE_LOSS_F32_PARTIALS 1
+#endif
+#ifndef CTB_CE_LOSS_WARP_ROWS_16
+#define CTB_CE_LOSS_WARP_ROWS_16 1
+#endif
+
 template <int GROUP, int VEC, int NV, int MODE>
 __global__ void __launch_bounds__(RowCta<GROUP, NV>::kThreads)
 ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels, int64_t label_stride,
@@ -344,6 +351,11 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
     }
     m = group_max<GROUP>(m, smax);
     double z = 0.0;
+    // The loss pass is bound by instruction issue (one exponential per 4 bytes read): a thread's own
+    // terms (at most NV * VEC of them, each in (0, 1]) are summed in two fp32 lanes and widened once;
+    // the gradient pass keeps the fp64 sum per term.
+    constexpr bool kF32Partials = CTB_CE_LOSS_F32_PARTIALS && MODE == 0 && VEC % 2 == 0;
+    float2 zz = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int col = (i * GROUP + tid) * VEC;
@@ -354,7 +366,8 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
                     const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
                     t[i][k] = e.x;
                     t[i][k + 1] = e.y;
-                    z = __dadd_rn(__dadd_rn(z, (double)e.x), (double)e.y);
+                    if constexpr (kF32Partials) zz = __fadd2_rn(zz, e);
+                    else z = __dadd_rn(__dadd_rn(z, (double)e.x), (double)e.y);
                 }
             } else {
 #pragma unroll
@@ -365,6 +378,7 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
             }
         }
     }
+    if constexpr (kF32Partials) z = __dadd_rn((double)zz.x, (double)zz.y);
     z = group_sum<GROUP>(z, ssum);
     const float zf = __double2float_rn(z);
     const int64_t l = ce_label(labels[row * label_stride], cols, tid == 0 ? bad : nullptr);
@@ -1373,6 +1387,16 @@ bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, cons
     // a 1024-thread CTA per row beats the sweeping kernel for the gradient (3.1 -> 4.3 TB/s at 32768
     // classes) but not for the loss, which writes nothing
     const int64_t cols_1024 = mode == 0 ? 0 : 32768;
+#if CTB_CE_LOSS_WARP_ROWS_16
+    // The loss pass, bound by instruction issue, pays for the group's barriers by the element: rows
+    // of 1025 .. 2048 classes stay with one warp per row (16 vectors per lane) instead of 128 threads.
+    if (launched && mode == 0 && vec4 && classes > 1024 && classes <= 2048) {
+        const int grid = rows_grid(g.rows, RowCta<32, 16>::kThreads / 32);
+        ce_rows_kernel<32, 4, 16, 0><<<grid, RowCta<32, 16>::kThreads, 0, st>>>(x, row_stride, labels, label_stride, rows,
+                                                                              (int)classes, scale, out, out_stride, bad);
+        return true;
+    }
+#endif
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_CE, ce_rows_kernel,
                           (x, row_stride, labels, label_stride, rows, (int)classes, scale, out, out_stride, bad));
