@@ -321,9 +321,6 @@ __device__ __forceinline__ int64_t ce_label(int32_t label, int64_t classes, int3
 #ifndef CTB_CE_LOSS_F32_PARTIALS
 #define CTB_CE_LOSS_F32_PARTIALS 1
 #endif
-#ifndef CTB_CE_LOSS_WARP_ROWS_16
-#define CTB_CE_LOSS_WARP_ROWS_16 1
-#endif
 
 template <int GROUP, int VEC, int NV, int MODE>
 __global__ void __launch_bounds__(RowCta<GROUP, NV>::kThreads)
@@ -1163,7 +1160,11 @@ int rows_grid(int64_t rows, int groups_per_cta) {
         MODES(KERNEL, G, V, N, ARGS)                                                           \
     } while (0)
 
-#define CTB_ROWS_DISPATCH(MODES, KERNEL, ARGS)                                                        \
+// W16: CTB_ROWS_W16_ON keeps rows of 1025 .. 2048 columns with one warp per row (16 vectors per lane),
+// CTB_ROWS_W16_OFF hands them to the 128-thread groups (and instantiates nothing).
+#define CTB_ROWS_W16_ON(MODES, KERNEL, ARGS) else if (nv_warp <= 16) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 16, ARGS);
+#define CTB_ROWS_W16_OFF(MODES, KERNEL, ARGS)
+#define CTB_ROWS_DISPATCH(MODES, KERNEL, ARGS, W16)                                                        \
     do {                                                                                       \
         const int64_t per_v = vec4 ? 4 : 1;                                                    \
         const int64_t nv_warp = ceil_div(g.cols, 32 * per_v);                                  \
@@ -1174,6 +1175,7 @@ int rows_grid(int64_t rows, int groups_per_cta) {
             else if (nv_warp <= 2) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 2, ARGS);                    \
             else if (nv_warp <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 4, ARGS);                    \
             else if (nv_warp <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 32, 4, 8, ARGS);                    \
+            W16(MODES, KERNEL, ARGS)                                                           \
             else if (nv_128 <= 4) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 4, ARGS);                    \
             else if (nv_128 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 128, 4, 8, ARGS);                    \
             else if (nv_256 <= 8) CTB_ROWS_LAUNCH(MODES, KERNEL, 256, 4, 8, ARGS);                    \
@@ -1286,7 +1288,7 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
     const int64_t cols_1024 = 24576;
     if (launched)
-        CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen));
+        CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen), CTB_ROWS_W16_OFF);
     if (!launched) {
         const int grid = rows_grid(g.rows, 1);
         const size_t row_bytes = ((size_t)g.cols * sizeof(float) + 15) / 16 * 16;
@@ -1355,7 +1357,7 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
     const int64_t cols_1024 = 24576;
     if (launched)
-        CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
+        CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps), CTB_ROWS_W16_OFF);
     constexpr int64_t kClusterSpan = (int64_t)kClusterRowThreads * 8 * 4;      // columns per CTA
     if (!launched && vec4 && g.cols <= 4 * kClusterSpan && g.rows * 4 < 0x7FFFFFFFll) {
         const bool two = g.cols <= 2 * kClusterSpan;
@@ -1387,19 +1389,13 @@ bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, cons
     // a 1024-thread CTA per row beats the sweeping kernel for the gradient (3.1 -> 4.3 TB/s at 32768
     // classes) but not for the loss, which writes nothing
     const int64_t cols_1024 = mode == 0 ? 0 : 32768;
-#if CTB_CE_LOSS_WARP_ROWS_16
-    // The loss pass, bound by instruction issue, pays for the group's barriers by the element: rows
-    // of 1025 .. 2048 classes stay with one warp per row (16 vectors per lane) instead of 128 threads.
-    if (launched && mode == 0 && vec4 && classes > 1024 && classes <= 2048) {
-        const int grid = rows_grid(g.rows, RowCta<32, 16>::kThreads / 32);
-        ce_rows_kernel<32, 4, 16, 0><<<grid, RowCta<32, 16>::kThreads, 0, st>>>(x, row_stride, labels, label_stride, rows,
-                                                                              (int)classes, scale, out, out_stride, bad);
-        return true;
-    }
-#endif
+    // Rows of 1025 .. 2048 classes stay with one warp per row (16 vectors per lane) instead of 128
+    // threads: the loss pass, bound by instruction issue, pays for a group's barriers by the element
+    // (3.8 -> 5.4 TB/s at 2048 classes), and the gradient gains 7-10 %; softmax and LayerNorm
+    // measured slower that way at 1280 .. 2048 columns and keep the 128-thread groups.
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_CE, ce_rows_kernel,
-                          (x, row_stride, labels, label_stride, rows, (int)classes, scale, out, out_stride, bad));
+                          (x, row_stride, labels, label_stride, rows, (int)classes, scale, out, out_stride, bad), CTB_ROWS_W16_ON);
     return launched;
 }
 

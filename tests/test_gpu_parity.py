@@ -332,7 +332,8 @@ def test_backward_chains_accumulate_into_gradient_buffers(ct, oracle):
     assert bad.item() == 0
 
 
-@pytest.mark.parametrize("rows,classes", [(4096, 1000), (512, 50257), (65536, 10), (300, 16384), (200, 32768), (64, 20000)])
+@pytest.mark.parametrize("rows,classes", [(4096, 1000), (512, 50257), (65536, 10), (300, 16384), (200, 32768), (64, 20000),
+                                          (2048, 2048), (1000, 1028), (777, 1536), (500, 2044), (300, 4096), (300, 8192)])
 def test_cross_entropy_sizes(ct, oracle, rows, classes):
     rng = np.random.default_rng(rows + classes)
     logits = HostView.contig((rng.standard_normal((rows, classes)) * 3).astype(np.float32))
