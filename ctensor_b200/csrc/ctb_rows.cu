@@ -881,6 +881,145 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// Long rows without a mask, vectorised: one 512-thread CTA per row sweeps the row three times —
+// maximum; exponentials (each computed once, written unnormalised, summed); division — with the
+// second and third sweep served by L2 (a row of 50257 floats is 200 KB; two CTAs per SM keep 60 MB
+// in flight).  Log-softmax writes nothing in the second sweep and reads x a third time.  The
+// kernels that keep the row on chip across a cluster serialise load, reductions and store per row
+// with two resident CTAs per SM; here every sweep is a plain stream with four vectors in flight.
+// Rows whose start is not 16-byte aligned are peeled (at most three elements at either end); a row
+// whose input and output start at different 16-byte phases is walked element by element.
+#ifndef CTB_SOFTMAX_SWEEP
+#define CTB_SOFTMAX_SWEEP 1
+#endif
+#ifndef CTB_SOFTMAX_COLS_1024
+#define CTB_SOFTMAX_COLS_1024 0
+#endif
+#ifndef CTB_CE_GRAD_COLS_1024
+#define CTB_CE_GRAD_COLS_1024 0
+#endif
+#ifndef CTB_SOFTMAX_SWEEP_WIDE_COLS
+#define CTB_SOFTMAX_SWEEP_WIDE_COLS 57344
+#endif
+
+// T = 512 (two CTAs per SM) or 1024 (one: half as many rows in flight, for rows so long that the
+// rows of 296 CTAs, input and output, no longer fit in L2 together).
+template <bool LOG, int T>
+__global__ void __launch_bounds__(T, 1024 / T)
+softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int64_t rows, int64_t cols) {
+    __shared__ float smax[T / 32];
+    __shared__ double ssum[T / 32];
+    using V4 = Vec<float, 4>;
+    const int tid = threadIdx.x;
+    for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
+        int64_t xo, mo, row;
+        row_offsets(o, ridx, &xo, &mo, &row);
+        const float* xr = x + xo;
+        float* orow = out + row * cols;
+        const bool same_phase = ((reinterpret_cast<uintptr_t>(xr) ^ reinterpret_cast<uintptr_t>(orow)) & 15) == 0;
+        const int64_t head = same_phase ? min(cols, (int64_t)((4 - ((reinterpret_cast<uintptr_t>(xr) >> 2) & 3)) & 3)) : cols;
+        const int64_t nvec = (cols - head) >> 2;
+        const int64_t tail = head + 4 * nvec;                   // [0, head) and [tail, cols): element by element
+        const V4* xv = reinterpret_cast<const V4*>(xr + head);
+        V4* ov = reinterpret_cast<V4*>(orow + head);
+        // ---- sweep 1: the maximum -------------------------------------------------------------------
+        float m = -INFINITY;
+        for (int64_t c = tid; c < head; c += T) m = fmaxf(m, xr[c]);
+        for (int64_t c = tail + tid; c < cols; c += T) m = fmaxf(m, xr[c]);
+        int64_t j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) m = fmaxf(fmaxf(m, fmaxf(v[u].v[0], v[u].v[1])), fmaxf(v[u].v[2], v[u].v[3]));
+        }
+        for (; j < nvec; j += T) {
+            const V4 v = ldg_stream(xv + j);
+            m = fmaxf(fmaxf(m, fmaxf(v.v[0], v.v[1])), fmaxf(v.v[2], v.v[3]));
+        }
+        m = cta_max_any(m, smax);
+        // ---- sweep 2: exponentials and their sum (from L2) ------------------------------------------------
+        double z = 0.0;
+        auto scalar_exp = [&](int64_t c) {
+            const float e = exp_cephes(__fsub_rn(xr[c], m));
+            if (!LOG) orow[c] = e;
+            z = __dadd_rn(z, (double)e);
+        };
+        for (int64_t c = tid; c < head; c += T) scalar_exp(c);
+        for (int64_t c = tail + tid; c < cols; c += T) scalar_exp(c);
+        auto vector_exp = [&](const V4& v, int64_t k) {
+            const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-m)));
+            const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-m)));
+            if (!LOG) {
+                V4 e;
+                e.v[0] = e0.x, e.v[1] = e0.y, e.v[2] = e1.x, e.v[3] = e1.y;
+                stg_stream(ov + k, e);
+            }
+            const float2 s = __fadd2_rn(e0, e1);               // four terms in (0, 1] meet in fp32: one widening per vector
+            z = __dadd_rn(z, (double)__fadd_rn(s.x, s.y));
+        };
+        j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) vector_exp(v[u], j + u * T);
+        }
+        for (; j < nvec; j += T) vector_exp(ldg_stream(xv + j), j);
+        z = cta_sum_any(z, ssum);
+        const float zf = __double2float_rn(z);
+        // ---- sweep 3: the result (every thread re-reads what it wrote itself) ------------------------------
+        if constexpr (LOG) {
+            const float lz = log_cephes(zf);
+            auto fin = [&](float v) { return __fsub_rn(__fsub_rn(v, m), lz); };
+            for (int64_t c = tid; c < head; c += T) orow[c] = fin(xr[c]);
+            for (int64_t c = tail + tid; c < cols; c += T) orow[c] = fin(xr[c]);
+            j = tid;
+            for (; j + 3 * T < nvec; j += 4 * T) {
+                V4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) v[u].v[q] = fin(v[u].v[q]);
+                    stg_stream(ov + j + u * T, v[u]);
+                }
+            }
+            for (; j < nvec; j += T) {
+                V4 v = ldg_stream(xv + j);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v.v[q] = fin(v.v[q]);
+                stg_stream(ov + j, v);
+            }
+        } else {
+            const float rz = row_reciprocal(zf);
+            for (int64_t c = tid; c < head; c += T) orow[c] = div_by_row(orow[c], zf, rz);
+            for (int64_t c = tail + tid; c < cols; c += T) orow[c] = div_by_row(orow[c], zf, rz);
+            j = tid;
+            for (; j + 3 * T < nvec; j += 4 * T) {
+                V4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(ov + j + u * T);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) v[u].v[q] = div_by_row(v[u].v[q], zf, rz);
+                    stg_stream(ov + j + u * T, v[u]);
+                }
+            }
+            for (; j < nvec; j += T) {
+                V4 v = ldg_stream(ov + j);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v.v[q] = div_by_row(v.v[q], zf, rz);
+                stg_stream(ov + j, v);
+            }
+        }
+    }
+}
+
 // ---- layernorm -------------------------------------------------------------------------------------------
 // mu = mean(x); d = x - mu; v = mean(d*d); r = (v + eps)^-0.5; y = d*r*gamma + beta, with
 // mean(.) = (float)((double)(float)sum_fp64 * (1.0/cols)) and the scalar steps in double,
@@ -959,123 +1098,121 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
     }
 }
 
-// Rows of 8193 .. 32768 columns with 16-byte aligned starts: a thread-block cluster per row, every
-// CTA keeps 256 x NV x 4 columns in registers; the two fp64 row sums cross CTAs through
-// distributed shared memory (same scheme as softmax_rows_cluster_reg_kernel).
-template <int CS, int NV, int MODE>
-__global__ void __launch_bounds__(kClusterRowThreads)
-layernorm_rows_cluster_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
-                              const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
-                              RowIdx o, int64_t rows, int cols, double inv_cols, double eps) {
-    __shared__ double ssum[kClusterRowThreads / 32];
-    __shared__ double cta_s1, cta_s2;
-    constexpr int T = kClusterRowThreads;
+// Rows beyond the register kernels: one 512-thread CTA per row sweeps x three times — sum; squared
+// deviations; result — the second and third sweep served by L2, the output written once (the
+// arithmetic of layernorm_rows_kernel; rows are peeled to 16-byte alignment like the softmax
+// sweeps).  Measured against the cluster-of-CTAs kernel it replaced (TB/s): [8192,32768] 4.2 -> 4.9;
+// rows that kernel could not take went through a scalar loop: [5341,50257] 1.3 -> 3.7,
+// [1000,262145] 1.0 -> 2.5; against the 1024-thread register CTA: [13000,20000] 3.4 -> 4.2.
+#ifndef CTB_LAYERNORM_COLS_1024
+#define CTB_LAYERNORM_COLS_1024 0
+#endif
+__global__ void __launch_bounds__(512, 2)
+layernorm_rows_sweep_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
+                            const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
+                            RowIdx o, int64_t rows, int64_t cols, double inv_cols, double eps) {
+    __shared__ double ssum[16];
+    using V4 = Vec<float, 4>;
+    constexpr int T = 512;
     const int tid = threadIdx.x;
-    const unsigned rank = cluster_rank();
-    const int64_t ridx = blockIdx.x / CS;
-    int64_t xo, mo, row;
-    row_offsets(o, ridx, &xo, &mo, &row);
-    const int c_lo = (int)rank * (T * NV * 4);
-    const float* xr = x + xo + c_lo;
-    const int live = cols - c_lo;                       // may be <= 0
-    float t[NV][4];
-    double s = 0.0;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int col = (i * T + tid) * 4;
-        if (col < live) {
-            load_vec<4>(t[i], xr, col, cols);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) s = __dadd_rn(s, (double)t[i][k]);
-        }
-    }
-    s = cta_sum_any(s, ssum);
-    if (tid == 0) cta_s1 = s;
-    cluster_barrier();
-    s = 0.0;
-#pragma unroll
-    for (unsigned r = 0; r < CS; ++r) s = __dadd_rn(s, cluster_peer_load(&cta_s1, r));
-    const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
-    double s2 = 0.0;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int col = (i * T + tid) * 4;
-        if (col < live) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                t[i][k] = __fsub_rn(t[i][k], mu);
-                s2 = __dadd_rn(s2, (double)__fmul_rn(t[i][k], t[i][k]));
-            }
-        }
-    }
-    s2 = cta_sum_any(s2, ssum);
-    if (tid == 0) cta_s2 = s2;
-    cluster_barrier();
-    s2 = 0.0;
-#pragma unroll
-    for (unsigned r = 0; r < CS; ++r) s2 = __dadd_rn(s2, cluster_peer_load(&cta_s2, r));
-    const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
-    const float ve = __double2float_rn(__dadd_rn((double)v, eps));
-    const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
-    float* orow = out + row * (int64_t)cols + c_lo;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int col = (i * T + tid) * 4;
-        if (col < live) {
-            float r[4];
-            if (MODE == 1) {
-                float gv[4], bv[4];
-                load_vec<4>(gv, gamma + c_lo, col, cols);
-                load_vec<4>(bv, beta + c_lo, col, cols);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) r[k] = __fadd_rn(__fmul_rn(__fmul_rn(t[i][k], rstd), gv[k]), bv[k]);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float y = __fmul_rn(t[i][k], rstd);
-                    if (MODE == 2) {
-                        if (gamma) y = __fmul_rn(y, gamma[(int64_t)(c_lo + col + k) * gstride]);
-                        if (beta) y = __fadd_rn(y, beta[(int64_t)(c_lo + col + k) * bstride]);
-                    }
-                    r[k] = y;
-                }
-            }
-            store_vec<4>(orow, col, r);
-        }
-    }
-    cluster_barrier();                                    // peers may still be reading cta_s2
-}
-
-__global__ void __launch_bounds__(256)
-layernorm_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ gamma, int64_t gstride,
-                           const float* __restrict__ beta, int64_t bstride, float* __restrict__ out,
-                           RowIdx o, int64_t rows, int64_t cols, double inv_cols, double eps) {
-    __shared__ double ssum[8];
     for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
         int64_t xo, mo, row;
         row_offsets(o, ridx, &xo, &mo, &row);
         const float* xr = x + xo;
-        double s = 0.0;
-        for (int64_t c = threadIdx.x; c < cols; c += 256) s = __dadd_rn(s, (double)xr[c]);
-        s = cta_sum256(s, ssum);
-        const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
-        double s2 = 0.0;
         float* orow = out + row * cols;
-        for (int64_t c = threadIdx.x; c < cols; c += 256) {
-            float d = __fsub_rn(xr[c], mu);
-            orow[c] = d;
-            s2 = __dadd_rn(s2, (double)__fmul_rn(d, d));
+        const bool same_phase = ((reinterpret_cast<uintptr_t>(xr) ^ reinterpret_cast<uintptr_t>(orow)) & 15) == 0;
+        const int64_t head = same_phase ? min(cols, (int64_t)((4 - ((reinterpret_cast<uintptr_t>(xr) >> 2) & 3)) & 3)) : cols;
+        const int64_t nvec = (cols - head) >> 2;
+        const int64_t tail = head + 4 * nvec;
+        const V4* xv = reinterpret_cast<const V4*>(xr + head);
+        V4* ov = reinterpret_cast<V4*>(orow + head);
+        // ---- sweep 1: the mean ----------------------------------------------------------------------------
+        double s = 0.0;
+        for (int64_t c = tid; c < head; c += T) s = __dadd_rn(s, (double)xr[c]);
+        for (int64_t c = tail + tid; c < cols; c += T) s = __dadd_rn(s, (double)xr[c]);
+        int64_t j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) s = __dadd_rn(s, (double)v[u].v[q]);
         }
-        s2 = cta_sum256(s2, ssum);
-        const float v = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
-        const float ve = __double2float_rn(__dadd_rn((double)v, eps));
+        for (; j < nvec; j += T) {
+            const V4 v = ldg_stream(xv + j);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) s = __dadd_rn(s, (double)v.v[q]);
+        }
+        s = cta_sum_any(s, ssum);
+        const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
+        // ---- sweep 2: the variance (from L2) -------------------------------------------------------------
+        double s2 = 0.0;
+        auto dev2 = [&](float v) {
+            const float d = __fsub_rn(v, mu);
+            s2 = __dadd_rn(s2, (double)__fmul_rn(d, d));
+        };
+        for (int64_t c = tid; c < head; c += T) dev2(xr[c]);
+        for (int64_t c = tail + tid; c < cols; c += T) dev2(xr[c]);
+        j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) dev2(v[u].v[q]);
+        }
+        for (; j < nvec; j += T) {
+            const V4 v = ldg_stream(xv + j);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dev2(v.v[q]);
+        }
+        s2 = cta_sum_any(s2, ssum);
+        const float var = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
+        const float ve = __double2float_rn(__dadd_rn((double)var, eps));
         const float rstd = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn((double)ve)));
-        for (int64_t c = threadIdx.x; c < cols; c += 256) {
-            float y = __fmul_rn(orow[c], rstd);
+        // ---- sweep 3: the result ---------------------------------------------------------------------------
+        auto fin = [&](float v, int64_t c) {
+            float y = __fmul_rn(__fsub_rn(v, mu), rstd);
             if (gamma) y = __fmul_rn(y, gamma[c * gstride]);
             if (beta) y = __fadd_rn(y, beta[c * bstride]);
-            orow[c] = y;
+            return y;
+        };
+        for (int64_t c = tid; c < head; c += T) orow[c] = fin(xr[c], c);
+        for (int64_t c = tail + tid; c < cols; c += T) orow[c] = fin(xr[c], c);
+        const bool gvec = (!gamma || (gstride == 1 && (reinterpret_cast<uintptr_t>(gamma + head) & 15) == 0)) &&
+                          (!beta || (bstride == 1 && (reinterpret_cast<uintptr_t>(beta + head) & 15) == 0));
+        auto vector_fin = [&](V4 v, int64_t k) {
+            const int64_t c0 = head + 4 * k;
+            if (gvec) {
+                V4 gv, bv;
+                if (gamma) gv = *reinterpret_cast<const V4*>(gamma + c0);
+                if (beta) bv = *reinterpret_cast<const V4*>(beta + c0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float y = __fmul_rn(__fsub_rn(v.v[q], mu), rstd);
+                    if (gamma) y = __fmul_rn(y, gv.v[q]);
+                    if (beta) y = __fadd_rn(y, bv.v[q]);
+                    v.v[q] = y;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v.v[q] = fin(v.v[q], c0 + q);
+            }
+            stg_stream(ov + k, v);
+        };
+        j = tid;
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) vector_fin(v[u], j + u * T);
         }
+        for (; j < nvec; j += T) vector_fin(ldg_stream(xv + j), j);
     }
 }
 
@@ -1127,8 +1264,9 @@ int rows_grid(int64_t rows, int groups_per_cta) {
 // caller's `cols_1024` columns (at most 32768; 0: never); MASKED is a compile-time switch so the
 // plain case carries no mask/causal code.  Measured against the cluster kernels they replace
 // (softmax / log-softmax / LayerNorm, TB/s): [16384,16384] 5.1 / 5.3 / 4.6 -> 5.2 / 5.7 / 5.8;
-// [20000,12288] 4.1 / 4.2 / 3.6 -> 5.4 / 5.2 / 5.7; [10000,20000] 3.3 / 3.2 / 2.8 -> 3.7 / 3.7 / 3.3
-// with the 1024-thread CTA, while [8192,32768] lost (4.7 -> 4.4) and stays on the cluster kernel.
+// [20000,12288] 4.1 / 4.2 / 3.6 -> 5.4 / 5.2 / 5.7.  The 1024-thread CTA ([10000,20000]: 3.7 / 3.7 /
+// 3.3) lost to the three-sweep kernels (4.2 / 4.6 / 4.2) and now serves masked and causal rows and
+// the accumulating cross-entropy gradient only.
 #define CTB_MODES_SOFTMAX(KERNEL, G, V, N, ARGS)                                               \
     switch (mode) {                                                                            \
     case 0: KERNEL<G, V, N, 0><<<grid, thr, 0, st>>> ARGS; break;                              \
@@ -1286,7 +1424,7 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     if (log_out && causal) return set_error(CTB_ERR_ARG, "log_softmax: no causal variant");
     const int mode = (g.has_mask ? 1 : 0) | (g.has_mask && g.m_inner ? 2 : 0) | (causal ? 4 : 0) | (log_out ? 8 : 0);
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
-    const int64_t cols_1024 = 24576;
+    const int64_t cols_1024 = (g.has_mask || causal) ? 24576 : CTB_SOFTMAX_COLS_1024;       // plain rows: the sweeps
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen), CTB_ROWS_W16_OFF);
     if (!launched) {
@@ -1296,7 +1434,20 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
         // measured best ([5341,50257]: 3.1 / 3.7 / 3.2 TB/s with 2 / 4 / 8 CTAs)
         const int cs = g.cols <= 25600 ? 2 : (g.cols <= 51200 ? 4 : 8);
         const int64_t chunk = ceil_div(ceil_div(g.cols, cs), 4) * 4;
-        if (vec4 && !g.has_mask && !causal && try_softmax_cluster_reg(g, x, log_out, out, o, st, &rc)) {
+        // measured, [rows, cols] of 1 GiB, softmax / log-softmax in TB/s, sweeps against the cluster kernels:
+        // 25000: 4.4 / 4.9 against 3.8 / 3.7; 32768: 4.9 / 5.2 against 4.7 / 4.7; 50257: 4.2 / 4.4 against
+        // 3.6 / 3.7; 65536: 4.0 / 4.0 against 3.9 / 3.9; 131072: 3.1 / 3.6 against 3.5 / 3.5; 262145 (beyond
+        // the clusters' reach): 2.5 / 3.1 against 0.8 / 1.1
+        const bool cluster_reach = chunk * 4 <= 100 * 1024;
+        if (CTB_SOFTMAX_SWEEP && !g.has_mask && !causal && (log_out || g.cols <= 98304 || !cluster_reach)) {
+            if (g.cols <= CTB_SOFTMAX_SWEEP_WIDE_COLS) {
+                if (log_out) softmax_rows_sweep_kernel<true, 512><<<grid, 512, 0, st>>>(x, out, o, g.rows, g.cols);
+                else softmax_rows_sweep_kernel<false, 512><<<grid, 512, 0, st>>>(x, out, o, g.rows, g.cols);
+            } else {
+                if (log_out) softmax_rows_sweep_kernel<true, 1024><<<grid, 1024, 0, st>>>(x, out, o, g.rows, g.cols);
+                else softmax_rows_sweep_kernel<false, 1024><<<grid, 1024, 0, st>>>(x, out, o, g.rows, g.cols);
+            }
+        } else if (vec4 && !g.has_mask && !causal && try_softmax_cluster_reg(g, x, log_out, out, o, st, &rc)) {
             if (rc) return rc;
         } else if (g.cols < 0x7FFFFFFFll && chunk * 4 <= 100 * 1024 && g.rows * cs < 0x7FFFFFFFll) {
             rc = launch_softmax_cluster(cs, (int)chunk, g, x, mask, causal, log_out, out, o, st);
@@ -1318,30 +1469,6 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
     return cuda_error(cudaGetLastError(), "softmax launch");
 }
 
-namespace {
-
-template <int CS, int MODE>
-int launch_layernorm_cluster(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride, const float* beta,
-                             int64_t bstride, double inv, double eps, float* out, const RowIdx& o, cudaStream_t st) {
-    auto kernel = layernorm_rows_cluster_kernel<CS, 8, MODE>;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(g.rows * CS));
-    cfg.blockDim = dim3(kClusterRowThreads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps));
-    return CTB_OK;
-}
-
-}  // namespace
-
 int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int64_t gstride,
                      const float* beta, int64_t bstride, double eps, float* out, cudaStream_t st) {
     if (g.rows == 0 || g.cols == 0) return CTB_OK;
@@ -1355,24 +1482,12 @@ int launch_layernorm(const RowsGeom& g, const float* x, const float* gamma, int6
     if (!gamma && !beta) mode = 0;
     else if (gamma && beta && gstride == 1 && bstride == 1 && vec4 && is_aligned(gamma, 16) && is_aligned(beta, 16)) mode = 1;
     bool launched = g.cols < 0x7FFFFFFFll && g.rows < 0x7FFFFFFFll;   // else: the grid-stride long-row kernel
-    const int64_t cols_1024 = 24576;
+    const int64_t cols_1024 = CTB_LAYERNORM_COLS_1024;
     if (launched)
         CTB_ROWS_DISPATCH(CTB_MODES_LAYERNORM, layernorm_rows_kernel, (x, gamma, gstride, beta, bstride, out, o, g.rows, (int)g.cols, inv, eps), CTB_ROWS_W16_OFF);
-    constexpr int64_t kClusterSpan = (int64_t)kClusterRowThreads * 8 * 4;      // columns per CTA
-    if (!launched && vec4 && g.cols <= 4 * kClusterSpan && g.rows * 4 < 0x7FFFFFFFll) {
-        const bool two = g.cols <= 2 * kClusterSpan;
-#define CTB_LN_CLUSTER(M)                                                                                               \
-        rc = two ? launch_layernorm_cluster<2, M>(g, x, gamma, gstride, beta, bstride, inv, eps, out, o, st)          \
-                 : launch_layernorm_cluster<4, M>(g, x, gamma, gstride, beta, bstride, inv, eps, out, o, st)
-        if (mode == 0) { CTB_LN_CLUSTER(0); }
-        else if (mode == 1) { CTB_LN_CLUSTER(1); }
-        else { CTB_LN_CLUSTER(2); }
-#undef CTB_LN_CLUSTER
-        return rc;
-    }
     if (!launched) {
         const int grid = rows_grid(g.rows, 1);
-        layernorm_rows_long_kernel<<<grid, 256, 0, st>>>(x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps);
+        layernorm_rows_sweep_kernel<<<grid, 512, 0, st>>>(x, gamma, gstride, beta, bstride, out, o, g.rows, g.cols, inv, eps);
     }
     return cuda_error(cudaGetLastError(), "layernorm launch");
 }
@@ -1386,9 +1501,10 @@ bool launch_ce_rows_registers(int mode, const float* x, int64_t row_stride, cons
     bool vec4 = classes % 4 == 0 && is_aligned(x, 16) && row_stride % 4 == 0;
     if (mode != 0) vec4 = vec4 && is_aligned(out, 16) && out_stride % 4 == 0;
     bool launched = classes < 0x7FFFFFFFll && rows < 0x7FFFFFFFll;
-    // a 1024-thread CTA per row beats the sweeping kernel for the gradient (3.1 -> 4.3 TB/s at 32768
-    // classes) but not for the loss, which writes nothing
-    const int64_t cols_1024 = mode == 0 ? 0 : 32768;
+    // a 1024-thread CTA per row beats the two-sweep kernel for the accumulating gradient (3.1 -> 4.3
+    // TB/s at 32768 classes) but neither the three-sweep one of the plain gradient (4.7) nor the
+    // loss pass, which writes nothing
+    const int64_t cols_1024 = mode == 0 ? 0 : (mode == 1 ? CTB_CE_GRAD_COLS_1024 : 32768);
     // Rows of 1025 .. 2048 classes stay with one warp per row (16 vectors per lane) instead of 128
     // threads: the loss pass, bound by instruction issue, pays for a group's barriers by the element
     // (3.8 -> 5.4 TB/s at 2048 classes), and the gradient gains 7-10 %; softmax and LayerNorm

@@ -349,8 +349,9 @@ def test_mlp_forward_loss_and_sgd_step_end_to_end(ct, oracle):
 
 @pytest.mark.parametrize("cols", [8196, 12289, 16384, 30001, 50257, 65536, 100003, 250000])
 def test_softmax_long_rows_cluster_kernel(ct, oracle, cols):
-    """Rows beyond the register kernels: staged in the shared memory of a thread-block cluster
-    (up to 8 x 25600 columns), then the re-reading kernel; aligned and unaligned row starts."""
+    """Rows beyond the register kernels, aligned and unaligned row starts: plain rows through the
+    three-sweep kernels (512 threads, 1024 beyond 57344 columns), masked and causal ones staged in the
+    shared memory of a thread-block cluster; softmax of 98305 .. 204800 columns on the clusters too."""
     rng = np.random.default_rng(cols)
     x = HostView.contig((rng.standard_normal((5, cols)) * 3).astype(np.float32))
     np.testing.assert_allclose(ct.softmax(to_device(x)).cpu().numpy(), oracle.softmax(x), rtol=RTOL, atol=1e-12)
@@ -364,10 +365,9 @@ def test_softmax_long_rows_cluster_kernel(ct, oracle, cols):
         np.testing.assert_allclose(got, ref, rtol=RTOL, atol=1e-12)
 
 
-@pytest.mark.parametrize("cols", [8196, 12288, 16384, 30000, 32768, 32772, 40001])
+@pytest.mark.parametrize("cols", [8196, 12288, 16384, 16388, 30000, 32768, 32772, 40001, 50257, 131075])
 def test_layernorm_long_rows(ct, oracle, cols):
-    """LayerNorm rows beyond the register kernels: cluster kernel up to 32768 aligned columns,
-    the re-reading kernel otherwise."""
+    """LayerNorm rows beyond the register kernels: the three-sweep kernel, aligned and unaligned rows."""
     rng = np.random.default_rng(cols)
     x = HostView.contig((rng.standard_normal((7, cols)) * 2 + 0.3).astype(np.float32))
     g = HostView.contig((1 + 0.02 * rng.standard_normal(cols)).astype(np.float32))
