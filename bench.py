@@ -887,9 +887,11 @@ def profile_case(name: str):
         for cols in (50304, 50257):
             L = torch.randn(2048, cols, device="cuda")
             O = torch.empty_like(L)
+            gamma, beta = torch.randn(cols, device="cuda"), torch.randn(cols, device="cuda")
             for _ in range(2):
                 ct.log_softmax(L, out=O)
                 ct.softmax(L, out=O)
+                ct.layernorm(L, gamma, beta, out=O)
     elif name == "ce":                  # cross-entropy rows: [65536,1000] and [4096,16384] (registers), [2048,50257] (one sweep)
         for rows, cols in ((65536, 1000), (4096, 16384), (2048, 50257)):
             L = torch.randn(rows, cols, device="cuda")

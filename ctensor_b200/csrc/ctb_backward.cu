@@ -16,6 +16,7 @@
 // (src/core/autograd.cpp:139-151) — once.
 #include "ctb_common.cuh"
 #include "ctb_math.cuh"
+#include "ctb_sweep.cuh"
 #include "ctb_backward.cuh"
 
 namespace ctb {
@@ -288,18 +289,10 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             float mx = -1e9f;                                   // the reference's starting value (loss.cpp:345)
             if (tid < head) mx = fmaxf(mx, line[tid]);
             if (tid < classes - tail) mx = fmaxf(mx, line[tail + tid]);
-            int64_t j = tid;
-            for (; j + 3 * T < nvec; j += 4 * T) {
-                V4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(lv + j + u * T);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) mx = fmaxf(fmaxf(mx, fmaxf(v[u].v[0], v[u].v[1])), fmaxf(v[u].v[2], v[u].v[3]));
-            }
-            for (; j < nvec; j += T) {
-                const V4 v = ldg_stream(lv + j);
+            auto load_x = [&](int64_t k) { return ldg_stream(lv + k); };
+            sweep_vectors<T>(nvec, tid, load_x, [&](const V4& v, int64_t) {
                 mx = fmaxf(fmaxf(mx, fmaxf(v.v[0], v.v[1])), fmaxf(v.v[2], v.v[3]));
-            }
+            });
             const float M = cta_max_long(mx, smax);
             double z = 0.0;
             auto scalar_exp = [&](int64_t c) {
@@ -323,15 +316,7 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
                 const float2 s2 = __fadd2_rn(e0, e1);
                 z = __dadd_rn(z, (double)__fadd_rn(s2.x, s2.y));
             };
-            j = tid;
-            for (; j + 3 * T < nvec; j += 4 * T) {
-                V4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(lv + j + u * T);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) vector_exp(v[u], j + u * T);
-            }
-            for (; j < nvec; j += T) vector_exp(ldg_stream(lv + j), j);
+            sweep_vectors<T>(nvec, tid, load_x, vector_exp);
             const float zf = __double2float_rn(cta_sum_long(z, ssum));
             const int64_t l = resolve_label(labels[row * label_stride], classes, tid == 0 ? bad : nullptr);
             const float inv = zf > 1e-12f ? __fdiv_rn(1.0f, zf) : 0.0f;
@@ -342,24 +327,20 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             };
             if (tid < head) orow[tid] = fin(orow[tid], tid);
             if (tid < classes - tail) orow[tail + tid] = fin(orow[tail + tid], tail + tid);
-            auto vector_fin = [&](int64_t k) {
-                const int64_t c0 = head + 4 * k;
-                if (out_vec) {
-                    V4 v = ldg_stream(ov + k);
+            if (out_vec) {
+                sweep_vectors<T>(nvec, tid, [&](int64_t k) { return ldg_stream(ov + k); }, [&](V4 v, int64_t k) {
+                    const int64_t c0 = head + 4 * k;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) v.v[q] = fin(v.v[q], c0 + q);
                     stg_stream(ov + k, v);
-                } else {
+                });
+            } else {
+                for (int64_t k = tid; k < nvec; k += T) {
+                    const int64_t c0 = head + 4 * k;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) orow[c0 + q] = fin(orow[c0 + q], c0 + q);
                 }
-            };
-            j = tid;
-            for (; j + 3 * T < nvec; j += 4 * T) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) vector_fin(j + u * T);
             }
-            for (; j < nvec; j += T) vector_fin(j);
             continue;
         }
         // ---- pass 1 ------------------------------------------------------------------------------------

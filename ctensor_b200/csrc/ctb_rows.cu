@@ -11,6 +11,7 @@
 // re-reading kernel.
 #include "ctb_reduce.cuh"
 #include "ctb_math.cuh"
+#include "ctb_sweep.cuh"
 #include "ctb_backward.cuh"
 
 namespace ctb {
@@ -904,6 +905,8 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
 
 // T = 512 (two CTAs per SM) or 1024 (one: half as many rows in flight, for rows so long that the
 // rows of 296 CTAs, input and output, no longer fit in L2 together).
+// (Issuing the next step's loads before consuming the current step's vectors — sweep_vectors'
+// PIPELINED — measured within noise here, unlike in the cross-entropy gradient; the plain form is used.)
 template <bool LOG, int T>
 __global__ void __launch_bounds__(T, 1024 / T)
 softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int64_t rows, int64_t cols) {
@@ -926,18 +929,10 @@ softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int
         float m = -INFINITY;
         for (int64_t c = tid; c < head; c += T) m = fmaxf(m, xr[c]);
         for (int64_t c = tail + tid; c < cols; c += T) m = fmaxf(m, xr[c]);
-        int64_t j = tid;
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) m = fmaxf(fmaxf(m, fmaxf(v[u].v[0], v[u].v[1])), fmaxf(v[u].v[2], v[u].v[3]));
-        }
-        for (; j < nvec; j += T) {
-            const V4 v = ldg_stream(xv + j);
+        auto load_x = [&](int64_t k) { return ldg_stream(xv + k); };
+        sweep_vectors<T, false>(nvec, tid, load_x, [&](const V4& v, int64_t) {
             m = fmaxf(fmaxf(m, fmaxf(v.v[0], v.v[1])), fmaxf(v.v[2], v.v[3]));
-        }
+        });
         m = cta_max_any(m, smax);
         // ---- sweep 2: exponentials and their sum (from L2) ------------------------------------------------
         double z = 0.0;
@@ -959,15 +954,7 @@ softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int
             const float2 s = __fadd2_rn(e0, e1);               // four terms in (0, 1] meet in fp32: one widening per vector
             z = __dadd_rn(z, (double)__fadd_rn(s.x, s.y));
         };
-        j = tid;
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) vector_exp(v[u], j + u * T);
-        }
-        for (; j < nvec; j += T) vector_exp(ldg_stream(xv + j), j);
+        sweep_vectors<T, false>(nvec, tid, load_x, vector_exp);
         z = cta_sum_any(z, ssum);
         const float zf = __double2float_rn(z);
         // ---- sweep 3: the result (every thread re-reads what it wrote itself) ------------------------------
@@ -976,46 +963,20 @@ softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int
             auto fin = [&](float v) { return __fsub_rn(__fsub_rn(v, m), lz); };
             for (int64_t c = tid; c < head; c += T) orow[c] = fin(xr[c]);
             for (int64_t c = tail + tid; c < cols; c += T) orow[c] = fin(xr[c]);
-            j = tid;
-            for (; j + 3 * T < nvec; j += 4 * T) {
-                V4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) v[u].v[q] = fin(v[u].v[q]);
-                    stg_stream(ov + j + u * T, v[u]);
-                }
-            }
-            for (; j < nvec; j += T) {
-                V4 v = ldg_stream(xv + j);
+            sweep_vectors<T, false>(nvec, tid, load_x, [&](V4 v, int64_t k) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) v.v[q] = fin(v.v[q]);
-                stg_stream(ov + j, v);
-            }
+                stg_stream(ov + k, v);
+            });
         } else {
             const float rz = row_reciprocal(zf);
             for (int64_t c = tid; c < head; c += T) orow[c] = div_by_row(orow[c], zf, rz);
             for (int64_t c = tail + tid; c < cols; c += T) orow[c] = div_by_row(orow[c], zf, rz);
-            j = tid;
-            for (; j + 3 * T < nvec; j += 4 * T) {
-                V4 v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = ldg_stream(ov + j + u * T);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) v[u].v[q] = div_by_row(v[u].v[q], zf, rz);
-                    stg_stream(ov + j + u * T, v[u]);
-                }
-            }
-            for (; j < nvec; j += T) {
-                V4 v = ldg_stream(ov + j);
+            sweep_vectors<T, false>(nvec, tid, [&](int64_t k) { return ldg_stream(ov + k); }, [&](V4 v, int64_t k) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) v.v[q] = div_by_row(v.v[q], zf, rz);
-                stg_stream(ov + j, v);
-            }
+                stg_stream(ov + k, v);
+            });
         }
     }
 }
@@ -1126,50 +1087,30 @@ layernorm_rows_sweep_kernel(const float* __restrict__ x, const float* __restrict
         const int64_t tail = head + 4 * nvec;
         const V4* xv = reinterpret_cast<const V4*>(xr + head);
         V4* ov = reinterpret_cast<V4*>(orow + head);
-        // ---- sweep 1: the mean ----------------------------------------------------------------------------
-        double s = 0.0;
-        for (int64_t c = tid; c < head; c += T) s = __dadd_rn(s, (double)xr[c]);
-        for (int64_t c = tail + tid; c < cols; c += T) s = __dadd_rn(s, (double)xr[c]);
-        int64_t j = tid;
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
+        // ---- sweep 1: the mean (four independent fp64 chains per thread, one per vector lane) ------------------
+        auto load_x = [&](int64_t k) { return ldg_stream(xv + k); };
+        double sl[4] = {0.0, 0.0, 0.0, 0.0};
+        for (int64_t c = tid; c < head; c += T) sl[0] = __dadd_rn(sl[0], (double)xr[c]);
+        for (int64_t c = tail + tid; c < cols; c += T) sl[1] = __dadd_rn(sl[1], (double)xr[c]);
+        sweep_vectors<T, false>(nvec, tid, load_x, [&](const V4& v, int64_t) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) s = __dadd_rn(s, (double)v[u].v[q]);
-        }
-        for (; j < nvec; j += T) {
-            const V4 v = ldg_stream(xv + j);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) s = __dadd_rn(s, (double)v.v[q]);
-        }
-        s = cta_sum_any(s, ssum);
+            for (int q = 0; q < 4; ++q) sl[q] = __dadd_rn(sl[q], (double)v.v[q]);
+        });
+        const double s = cta_sum_any(__dadd_rn(__dadd_rn(sl[0], sl[1]), __dadd_rn(sl[2], sl[3])), ssum);
         const float mu = __double2float_rn(__dmul_rn((double)__double2float_rn(s), inv_cols));
         // ---- sweep 2: the variance (from L2) -------------------------------------------------------------
-        double s2 = 0.0;
-        auto dev2 = [&](float v) {
+        double vl[4] = {0.0, 0.0, 0.0, 0.0};
+        auto dev2 = [&](float v, int lane) {
             const float d = __fsub_rn(v, mu);
-            s2 = __dadd_rn(s2, (double)__fmul_rn(d, d));
+            vl[lane] = __dadd_rn(vl[lane], (double)__fmul_rn(d, d));
         };
-        for (int64_t c = tid; c < head; c += T) dev2(xr[c]);
-        for (int64_t c = tail + tid; c < cols; c += T) dev2(xr[c]);
-        j = tid;
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
+        for (int64_t c = tid; c < head; c += T) dev2(xr[c], 0);
+        for (int64_t c = tail + tid; c < cols; c += T) dev2(xr[c], 1);
+        sweep_vectors<T, false>(nvec, tid, load_x, [&](const V4& v, int64_t) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) dev2(v[u].v[q]);
-        }
-        for (; j < nvec; j += T) {
-            const V4 v = ldg_stream(xv + j);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) dev2(v.v[q]);
-        }
+            for (int q = 0; q < 4; ++q) dev2(v.v[q], q);
+        });
+        double s2 = __dadd_rn(__dadd_rn(vl[0], vl[1]), __dadd_rn(vl[2], vl[3]));
         s2 = cta_sum_any(s2, ssum);
         const float var = __double2float_rn(__dmul_rn((double)__double2float_rn(s2), inv_cols));
         const float ve = __double2float_rn(__dadd_rn((double)var, eps));
@@ -1204,15 +1145,7 @@ layernorm_rows_sweep_kernel(const float* __restrict__ x, const float* __restrict
             }
             stg_stream(ov + k, v);
         };
-        j = tid;
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ldg_stream(xv + j + u * T);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) vector_fin(v[u], j + u * T);
-        }
-        for (; j < nvec; j += T) vector_fin(ldg_stream(xv + j), j);
+        sweep_vectors<T, false>(nvec, tid, load_x, vector_fin);
     }
 }
 

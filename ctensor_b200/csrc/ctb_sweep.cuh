@@ -1,0 +1,46 @@
+// One sweep of a long row's 128-bit vectors by the T threads of a CTA, four loads in flight per
+// thread.  PIPELINED issues the four loads of the next step before the four vectors of the current
+// step are consumed, so a thread has loads in flight while it computes (a row of 50257 floats gives
+// a thread of 512 six steps per sweep).  Measured: +3 .. 10 % in the cross-entropy gradient
+// ([8192,32768] 4.7 -> 5.1 TB/s), within noise in the softmax and LayerNorm sweeps, which use the
+// plain form and its smaller register footprint.
+#pragma once
+#include "ctb_common.cuh"
+
+namespace ctb {
+
+// load(k) -> Vec<float, 4> number k of the row; body(v, k) consumes it.  Thread `tid` takes the
+// vectors tid, tid + T, tid + 2T, ... in ascending order.  PIPELINED = false keeps four loads in
+// flight without the second buffer (for bodies that need the registers themselves).
+template <int T, bool PIPELINED = true, typename Load, typename Body>
+__device__ __forceinline__ void sweep_vectors(int64_t nvec, int tid, Load load, Body body) {
+    using V4 = Vec<float, 4>;
+    int64_t j = tid;
+    if constexpr (!PIPELINED) {
+        for (; j + 3 * T < nvec; j += 4 * T) {
+            V4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = load(j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) body(v[u], j + u * T);
+        }
+    } else if (j + 3 * T < nvec) {
+        V4 cur[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cur[u] = load(j + u * T);
+        for (j += 4 * T; j + 3 * T < nvec; j += 4 * T) {
+            V4 nxt[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) nxt[u] = load(j + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) body(cur[u], j - 4 * T + u * T);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) body(cur[u], j - 4 * T + u * T);
+    }
+    for (; j < nvec; j += T) body(load(j), j);
+}
+
+}  // namespace ctb
