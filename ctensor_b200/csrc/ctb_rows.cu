@@ -1065,6 +1065,9 @@ layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gam
 // sweeps).  Measured against the cluster-of-CTAs kernel it replaced (TB/s): [8192,32768] 4.2 -> 4.9;
 // rows that kernel could not take went through a scalar loop: [5341,50257] 1.3 -> 3.7,
 // [1000,262145] 1.0 -> 2.5; against the 1024-thread register CTA: [13000,20000] 3.4 -> 4.2.
+// (Two sweeps — both moments about the row's first element in fp64, then the result — measured
+// slower up to 65536 columns, 3.3 against 3.7 TB/s at 50257: four fp64 operations per element cost
+// more than the sweep through L2 they save.)
 #ifndef CTB_LAYERNORM_COLS_1024
 #define CTB_LAYERNORM_COLS_1024 0
 #endif
