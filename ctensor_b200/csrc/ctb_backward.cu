@@ -237,26 +237,52 @@ __device__ __forceinline__ int64_t resolve_label(int32_t label, int64_t classes,
     return l;
 }
 
-// running (m, z) of one thread
+// running (m, z) of one thread.  GRAD: the exponential lets a NaN argument through
+// (exp_nan_through).  Otherwise (the loss, which follows the operator chain max -> sub -> exp ->
+// sum): a NaN logit is ignored by the maximum and its term is the clamped exponential of NaN,
+// whatever the maximum — such terms are counted apart (`nan_terms`), outside the rescaling.
+template <bool GRAD>
 struct OnlineSum {
     float m;
     double z;
+    int nan_terms;
     __device__ __forceinline__ void raise(float vm) {          // the maximum moves to vm > m
         z = __dmul_rn(z, (double)exp_cephes(__fsub_rn(m, vm)));   // exp(-inf) = 0 on the first element (z is 0 then)
         m = vm;
     }
     __device__ __forceinline__ void push(float v) {
+        if (!GRAD && v != v) {
+            ++nan_terms;
+            return;
+        }
         if (v > m) raise(v);
-        z = __dadd_rn(z, (double)exp_cephes(__fsub_rn(v, m)));
+        const float d = __fsub_rn(v, m);
+        z = __dadd_rn(z, (double)(GRAD ? exp_nan_through(d) : exp_cephes(d)));
     }
     __device__ __forceinline__ void push4(const Vec<float, 4>& v) {
+        if (!GRAD) {
+            const float probe = __fadd_rn(__fadd_rn(v.v[0], v.v[1]), __fadd_rn(v.v[2], v.v[3]));
+            if (probe != probe) {                               // rare: a NaN among the four (or inf - inf)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) push(v.v[q]);
+                return;
+            }
+        }
         const float vm = fmaxf(fmaxf(v.v[0], v.v[1]), fmaxf(v.v[2], v.v[3]));
         if (vm > m) raise(vm);
-        const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-m)));
-        const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-m)));
+        const float2 d0 = __fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-m));
+        const float2 d1 = __fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-m));
+        const float2 e0 = GRAD ? exp_nan_through2(d0) : exp_cephes2(d0);
+        const float2 e1 = GRAD ? exp_nan_through2(d1) : exp_cephes2(d1);
         // the four terms of a vector (each in (0, 1]) meet in fp32 first: one widening per vector
         const float2 s = __fadd2_rn(e0, e1);
         z = __dadd_rn(z, (double)__fadd_rn(s.x, s.y));
+    }
+    // this thread's share of the row sum under the row maximum M
+    __device__ __forceinline__ double under(float M) const {
+        double r = __dmul_rn(z, (double)exp_cephes(__fsub_rn(m, M)));
+        if (!GRAD && nan_terms) r = __dadd_rn(r, __dmul_rn((double)nan_terms, (double)exp_cephes(__int_as_float(0x7fc00000))));
+        return r;
     }
 };
 
@@ -296,15 +322,15 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             const float M = cta_max_long(mx, smax);
             double z = 0.0;
             auto scalar_exp = [&](int64_t c) {
-                const float e = exp_cephes(__fsub_rn(line[c], M));
+                const float e = exp_nan_through(__fsub_rn(line[c], M));
                 orow[c] = e;
                 z = __dadd_rn(z, (double)e);
             };
             if (tid < head) scalar_exp(tid);
             if (tid < classes - tail) scalar_exp(tail + tid);
             auto vector_exp = [&](const V4& v, int64_t k) {
-                const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-M)));
-                const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-M)));
+                const float2 e0 = exp_nan_through2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-M)));
+                const float2 e1 = exp_nan_through2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-M)));
                 if (out_vec) {
                     V4 e;
                     e.v[0] = e0.x, e.v[1] = e0.y, e.v[2] = e1.x, e.v[3] = e1.y;
@@ -344,7 +370,7 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             continue;
         }
         // ---- pass 1 ------------------------------------------------------------------------------------
-        OnlineSum acc{MODE == 0 ? -INFINITY : -1e9f, 0.0};       // the gradient starts at the reference's -1e9 (loss.cpp:345)
+        OnlineSum<MODE != 0> acc{MODE == 0 ? -INFINITY : -1e9f, 0.0, 0};       // the gradient starts at the reference's -1e9 (loss.cpp:345)
         if (tid < head) acc.push(line[tid]);
         if (tid < classes - tail) acc.push(line[tail + tid]);
         int64_t j = tid;
@@ -357,7 +383,7 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
         }
         for (; j < nvec; j += T) acc.push4(ldg_stream(lv + j));
         const float M = cta_max_long(acc.m, smax);
-        const double Z = cta_sum_long(__dmul_rn(acc.z, (double)exp_cephes(__fsub_rn(acc.m, M))), ssum);
+        const double Z = cta_sum_long(acc.under(M), ssum);
         const float zf = __double2float_rn(Z);
         const int64_t l = resolve_label(labels[row * label_stride], classes, tid == 0 ? bad : nullptr);
         if constexpr (MODE == 0) {
@@ -374,7 +400,7 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             const float inv = zf > 1e-12f ? __fdiv_rn(1.0f, zf) : 0.0f;
             float* orow = out + row * out_stride;
             auto grad = [&](float v, int64_t c, float old) {
-                float p = __fmul_rn(exp_cephes(__fsub_rn(v, M)), inv);
+                float p = __fmul_rn(exp_nan_through(__fsub_rn(v, M)), inv);
                 if (c == l) p = __fsub_rn(p, 1.0f);
                 const float g = __fmul_rn(p, scale);
                 return MODE == 2 ? BinaryFn<kOpAddFinite, float>::apply(old, g) : g;
@@ -389,8 +415,8 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
                 if (out_vec) {
                     V4 old;
                     if (MODE == 2) old = *reinterpret_cast<const V4*>(orow + c0);
-                    const float2 e0 = exp_cephes2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-M)));
-                    const float2 e1 = exp_cephes2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-M)));
+                    const float2 e0 = exp_nan_through2(__fadd2_rn(make_float2(v.v[0], v.v[1]), splat2(-M)));
+                    const float2 e1 = exp_nan_through2(__fadd2_rn(make_float2(v.v[2], v.v[3]), splat2(-M)));
                     const float e[4] = {e0.x, e0.y, e1.x, e1.y};
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {

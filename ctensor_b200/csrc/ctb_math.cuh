@@ -151,6 +151,20 @@ __device__ __forceinline__ float2 exp_cephes2(float2 v, float hi = kExpHi) {
     return __fmul2_rn(y, make_float2(__int_as_float(p0), __int_as_float(p1)));
 }
 
+// The exponential as GradCrossEntropy::backward takes it (std::exp, src/neuralnet/loss.cpp:351): a
+// NaN argument — a NaN logit, or inf - inf under an infinite row maximum — gives NaN, where the
+// operator exp above clamps it to its upper bound.  Arguments there are <= 0 otherwise.
+__device__ __forceinline__ float exp_nan_through(float d) {
+    const float e = exp_cephes(d);
+    return d != d ? d : e;
+}
+__device__ __forceinline__ float2 exp_nan_through2(float2 d) {
+    float2 e = exp_cephes2(d);
+    e.x = d.x != d.x ? d.x : e.x;
+    e.y = d.y != d.y ? d.y : e.y;
+    return e;
+}
+
 // Reciprocal estimate refined by one Newton step, for b in [1, 2^26].
 __device__ __forceinline__ float2 rcp_newton2(float2 b, float2 nb) {
     float2 r;

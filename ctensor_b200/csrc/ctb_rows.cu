@@ -139,7 +139,13 @@ __device__ __forceinline__ float row_reciprocal(float z) {
     const float err = fmaf(-z, r, 1.0f);
     return fmaf(r, err, r);
 }
+// r = row_reciprocal(z) is a usable reciprocal only for a normal z below 2^126: beyond that (a row
+// whose exponentials hit the clamp, e.g. inf - inf = NaN arguments: each term 2.4e38), for an
+// infinite or NaN sum and for a subnormal one the estimate is 0, NaN or infinite, and the row is
+// divided by IEEE division — e / inf = 0, e / NaN = NaN, as the reference's div gives.
+__device__ __forceinline__ bool reciprocal_usable(float r) { return r > 0.0f && r < INFINITY; }
 __device__ __forceinline__ float div_by_row(float e, float z, float r) {
+    if (!reciprocal_usable(r)) return __fdiv_rn(e, z);
     const float q = __fmul_rn(e, r);
     const float rem = fmaf(-z, q, e);
     float out = fmaf(rem, r, q);
@@ -283,7 +289,10 @@ softmax_rows_kernel(const float* __restrict__ x, const float* __restrict__ mask,
                         r[k + 1] = res.y;
                         smallest = fminf(smallest, fminf(e.x, e.y));
                     }
-                    if (smallest < 1e-30f) {            // rare: a quotient may be subnormal (or e == 0)
+                    if (!reciprocal_usable(rz)) {       // the row's sum is huge, infinite, NaN or subnormal
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) r[k] = __fdiv_rn(t[i][k], zf);
+                    } else if (smallest < 1e-30f) {     // rare: a quotient may be subnormal (or e == 0)
 #pragma unroll
                         for (int k = 0; k < VEC; ++k)
                             if (t[i][k] < 1e-30f) r[k] = (t[i][k] == 0.0f) ? 0.0f : __fdiv_rn(t[i][k], zf);
@@ -361,7 +370,8 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
             if constexpr (VEC % 2 == 0) {
 #pragma unroll
                 for (int k = 0; k < VEC; k += 2) {
-                    const float2 e = exp_cephes2(__fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m)));
+                    const float2 sh = __fadd2_rn(make_float2(t[i][k], t[i][k + 1]), splat2(-m));
+                    const float2 e = MODE == 0 ? exp_cephes2(sh) : exp_nan_through2(sh);
                     t[i][k] = e.x;
                     t[i][k + 1] = e.y;
                     if constexpr (kF32Partials) zz = __fadd2_rn(zz, e);
@@ -370,7 +380,7 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
             } else {
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) {
-                    t[i][k] = exp_cephes(__fsub_rn(t[i][k], m));
+                    t[i][k] = MODE == 0 ? exp_cephes(__fsub_rn(t[i][k], m)) : exp_nan_through(__fsub_rn(t[i][k], m));
                     z = __dadd_rn(z, (double)t[i][k]);
                 }
             }
@@ -654,7 +664,10 @@ softmax_rows_cluster_reg_kernel(const float* __restrict__ x, float* __restrict__
                     r[k + 1] = res.y;
                     smallest = fminf(smallest, fminf(e.x, e.y));
                 }
-                if (smallest < 1e-30f) {                // rare: a quotient may be subnormal (or e == 0)
+                if (!reciprocal_usable(rz)) {           // the row's sum is huge, infinite, NaN or subnormal
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) r[k] = __fdiv_rn(t[i][k], zf);
+                } else if (smallest < 1e-30f) {         // rare: a quotient may be subnormal (or e == 0)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         if (t[i][k] < 1e-30f) r[k] = (t[i][k] == 0.0f) ? 0.0f : __fdiv_rn(t[i][k], zf);
@@ -816,7 +829,10 @@ softmax_rows_cluster_kernel(const float* __restrict__ x, const float* __restrict
                         r.v[k + 1] = res.y;
                         smallest = fminf(smallest, fminf(e.x, e.y));
                     }
-                    if (smallest < 1e-30f) {
+                    if (!reciprocal_usable(rz)) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) r.v[k] = __fdiv_rn(v.v[k], zf);
+                    } else if (smallest < 1e-30f) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             if (v.v[k] < 1e-30f) r.v[k] = (v.v[k] == 0.0f) ? 0.0f : __fdiv_rn(v.v[k], zf);

@@ -449,3 +449,63 @@ def test_matmul_tensor_cores_batched_and_empty_k(ct):
     with pytest.raises(ct.CtbError) as e:
         ct.matmul_tc(torch.zeros(4, 5, device="cuda"), torch.zeros(6, 7, device="cuda"))
     assert e.value.message == "matmul_mp shape mismatch"
+
+
+@pytest.mark.parametrize("cols", [1000, 2048, 12288, 20000, 50257])
+def test_rows_with_special_values_follow_the_reference_chain(ct, oracle, cols):
+    """+inf, -inf, NaN and huge entries inside rows, for every row-kernel family (warp rows, thread
+    groups, the three-sweep kernels): what the reference's chain of operators gives (max ignores a
+    NaN, inf - inf is NaN, the exponential clamps its argument), element for element."""
+    rng = np.random.default_rng(cols)
+    x = (rng.standard_normal((8, cols)) * 3).astype(np.float32)
+    x[1, cols // 3] = np.inf
+    x[2, 5::7] = -np.inf
+    x[3, cols // 2] = np.nan
+    x[4, :] = 1e30
+    x[5, :] = -np.inf
+    x[6, 0] = np.inf
+    x[6, cols - 1] = np.inf
+    x[7, ::2] = 3e38
+    hx = HostView.contig(x)
+    with np.errstate(all="ignore"):
+        want_sm, want_lsm = oracle.softmax(hx), oracle.log_softmax(hx)
+    got_sm = ct.softmax(to_device(hx)).cpu().numpy()
+    got_lsm = ct.log_softmax(to_device(hx)).cpu().numpy()
+    np.testing.assert_allclose(got_sm, want_sm, rtol=RTOL, atol=1e-12, equal_nan=True)
+    np.testing.assert_allclose(got_lsm, want_lsm, rtol=RTOL, atol=1e-6, equal_nan=True)
+    # the masked kernels (thread-block clusters for the long rows) on the same rows
+    m = HostView.contig(-rng.random((1, cols)).astype(np.float32))
+    with np.errstate(all="ignore"):
+        want_masked = oracle.softmax(hx, m)
+    np.testing.assert_allclose(ct.softmax(to_device(hx), to_device(m)).cpu().numpy(), want_masked, rtol=RTOL, atol=1e-12, equal_nan=True)
+
+
+@pytest.mark.parametrize("cols", [1000, 2048, 12288, 20000, 50257])
+def test_layernorm_and_cross_entropy_rows_with_special_values(ct, oracle, cols):
+    """The same kinds of rows through LayerNorm and the cross-entropy kernels (register rows, the
+    one-sweep loss, the three-sweep gradient)."""
+    rng = np.random.default_rng(cols + 1)
+    x = (rng.standard_normal((6, cols)) * 3).astype(np.float32)
+    x[1, cols // 3] = np.inf
+    x[2, 5::7] = -np.inf
+    x[3, cols // 2] = np.nan
+    x[4, :] = 1e30
+    x[5, ::2] = 3e38
+    hx = HostView.contig(x)
+    g = HostView.contig((1 + 0.02 * rng.standard_normal(cols)).astype(np.float32))
+    b = HostView.contig((0.02 * rng.standard_normal(cols)).astype(np.float32))
+    with np.errstate(all="ignore"):
+        want = oracle.layernorm(hx, g, b, 1e-5)
+    got = ct.layernorm(to_device(hx), to_device(g), to_device(b), 1e-5).cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=1e-6, equal_nan=True)
+    labels = rng.integers(0, cols, (6, 1)).astype(np.int32)
+    for row in range(6):                     # row by row: a NaN loss of one row would hide the others in the mean
+        hr = HostView.contig(np.ascontiguousarray(x[row:row + 1]))
+        hl = HostView.contig(np.ascontiguousarray(labels[row:row + 1]))
+        with np.errstate(all="ignore"):
+            want_loss = oracle.cross_entropy(hr, hl, True)
+            want_grad = oracle.cross_entropy_backward(hr, hl, True, 1.0)
+        got_loss = ct.cross_entropy(to_device(hr), to_device(hl), True).cpu().numpy()
+        got_grad = ct.cross_entropy_backward(to_device(hr), to_device(hl), 1.0).cpu().numpy()
+        np.testing.assert_allclose(got_loss, want_loss, rtol=RTOL, atol=1e-6, equal_nan=True, err_msg=f"loss of row {row}")
+        np.testing.assert_allclose(got_grad, want_grad, rtol=max(RTOL, 4e-9 * cols), atol=1e-6, equal_nan=True, err_msg=f"gradient of row {row}")
