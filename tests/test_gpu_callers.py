@@ -509,3 +509,28 @@ def test_layernorm_and_cross_entropy_rows_with_special_values(ct, oracle, cols):
         got_grad = ct.cross_entropy_backward(to_device(hr), to_device(hl), 1.0).cpu().numpy()
         np.testing.assert_allclose(got_loss, want_loss, rtol=RTOL, atol=1e-6, equal_nan=True, err_msg=f"loss of row {row}")
         np.testing.assert_allclose(got_grad, want_grad, rtol=max(RTOL, 4e-9 * cols), atol=1e-6, equal_nan=True, err_msg=f"gradient of row {row}")
+
+
+@pytest.mark.parametrize("cols,pad,shift", [(20000, 3, 1), (50257, 0, 0), (50257, 5, 2), (17000, 4, 0), (70001, 1, 1), (33000, 2, 1)])
+def test_long_rows_of_a_wider_buffer(ct, cols, pad, shift):
+    """The three-sweep kernels on rows cut out of a wider buffer: input rows start at every 4-byte phase,
+    and at a 16-byte phase that differs from the output row's (walked element by element) — softmax,
+    log-softmax and LayerNorm against the definitions evaluated in float64."""
+    rows = 11
+    rng = np.random.default_rng(cols + pad + shift)
+    wide = (rng.standard_normal((rows, cols + pad)) * 3 + 0.5).astype(np.float32)
+    x = torch.from_numpy(wide).cuda()[:, shift:shift + cols]
+    xs = wide[:, shift:shift + cols].astype(np.float64)
+    sh = xs - xs.max(1, keepdims=True)
+    logz = np.log(np.exp(sh).sum(1, keepdims=True))
+    np.testing.assert_allclose(ct.softmax(ct.DView.of(x)).cpu().numpy(), np.exp(sh - logz), rtol=2e-5, atol=1e-12)
+    np.testing.assert_allclose(ct.log_softmax(ct.DView.of(x)).cpu().numpy(), sh - logz, rtol=2e-5, atol=2e-6)
+    gamma = (1 + 0.02 * rng.standard_normal(cols)).astype(np.float32)
+    beta = (0.02 * rng.standard_normal(cols)).astype(np.float32)
+    mu = xs.mean(1, keepdims=True)
+    var = ((xs - mu) ** 2).mean(1, keepdims=True)
+    want = (xs - mu) / np.sqrt(var + 1e-5) * gamma + beta
+    got = ct.layernorm(ct.DView.of(x), torch.from_numpy(gamma).cuda(), torch.from_numpy(beta).cuda(), 1e-5)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-5, atol=2e-6)
+    got = ct.layernorm(ct.DView.of(x), None, None, 1e-5)
+    np.testing.assert_allclose(got.cpu().numpy(), (xs - mu) / np.sqrt(var + 1e-5), rtol=2e-5, atol=2e-6)
