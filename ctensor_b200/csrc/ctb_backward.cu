@@ -197,6 +197,9 @@ int launch_typed(int kind, const BwdPlan& p, const void* g, const void* x, const
 //           flight, which the 126 MB L2 holds — and writes (exp(x - M) / Z - onehot) * scale.
 // 128-bit accesses after a scalar head that brings the row to 16-byte alignment (rows of 50257
 // floats start at every 4-byte phase).
+#ifndef CTB_CE_SWEEP1_LOADS
+#define CTB_CE_SWEEP1_LOADS 8
+#endif
 #ifndef CTB_CE_GRAD_SWEEP
 #define CTB_CE_GRAD_SWEEP 1
 #endif
@@ -316,7 +319,7 @@ ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32
             if (tid < head) mx = fmaxf(mx, line[tid]);
             if (tid < classes - tail) mx = fmaxf(mx, line[tail + tid]);
             auto load_x = [&](int64_t k) { return ldg_stream(lv + k); };
-            sweep_vectors<T>(nvec, tid, load_x, [&](const V4& v, int64_t) {
+            sweep_vectors<T, false, CTB_CE_SWEEP1_LOADS>(nvec, tid, load_x, [&](const V4& v, int64_t) {
                 mx = fmaxf(fmaxf(mx, fmaxf(v.v[0], v.v[1])), fmaxf(v.v[2], v.v[3]));
             });
             const float M = cta_max_long(mx, smax);

@@ -909,6 +909,10 @@ softmax_rows_long_kernel(const float* __restrict__ x, const float* __restrict__ 
 #ifndef CTB_SOFTMAX_SWEEP
 #define CTB_SOFTMAX_SWEEP 1
 #endif
+// vectors in flight per thread in the first sweep, the one that comes from HBM (8 against 4: +1 .. 5 %)
+#ifndef CTB_SWEEP1_LOADS
+#define CTB_SWEEP1_LOADS 8
+#endif
 #ifndef CTB_SOFTMAX_COLS_1024
 #define CTB_SOFTMAX_COLS_1024 0
 #endif
@@ -946,7 +950,7 @@ softmax_rows_sweep_kernel(const float* __restrict__ x, float* out, RowIdx o, int
         for (int64_t c = tid; c < head; c += T) m = fmaxf(m, xr[c]);
         for (int64_t c = tail + tid; c < cols; c += T) m = fmaxf(m, xr[c]);
         auto load_x = [&](int64_t k) { return ldg_stream(xv + k); };
-        sweep_vectors<T, false>(nvec, tid, load_x, [&](const V4& v, int64_t) {
+        sweep_vectors<T, false, CTB_SWEEP1_LOADS>(nvec, tid, load_x, [&](const V4& v, int64_t) {
             m = fmaxf(fmaxf(m, fmaxf(v.v[0], v.v[1])), fmaxf(v.v[2], v.v[3]));
         });
         m = cta_max_any(m, smax);
@@ -1111,7 +1115,7 @@ layernorm_rows_sweep_kernel(const float* __restrict__ x, const float* __restrict
         double sl[4] = {0.0, 0.0, 0.0, 0.0};
         for (int64_t c = tid; c < head; c += T) sl[0] = __dadd_rn(sl[0], (double)xr[c]);
         for (int64_t c = tail + tid; c < cols; c += T) sl[1] = __dadd_rn(sl[1], (double)xr[c]);
-        sweep_vectors<T, false>(nvec, tid, load_x, [&](const V4& v, int64_t) {
+        sweep_vectors<T, false, CTB_SWEEP1_LOADS>(nvec, tid, load_x, [&](const V4& v, int64_t) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) sl[q] = __dadd_rn(sl[q], (double)v.v[q]);
         });

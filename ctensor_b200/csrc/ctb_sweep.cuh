@@ -10,35 +10,35 @@
 namespace ctb {
 
 // load(k) -> Vec<float, 4> number k of the row; body(v, k) consumes it.  Thread `tid` takes the
-// vectors tid, tid + T, tid + 2T, ... in ascending order.  PIPELINED = false keeps four loads in
+// vectors tid, tid + T, tid + 2T, ... in ascending order.  PIPELINED = false keeps U loads in
 // flight without the second buffer (for bodies that need the registers themselves).
-template <int T, bool PIPELINED = true, typename Load, typename Body>
+template <int T, bool PIPELINED = true, int U = 4, typename Load, typename Body>
 __device__ __forceinline__ void sweep_vectors(int64_t nvec, int tid, Load load, Body body) {
     using V4 = Vec<float, 4>;
     int64_t j = tid;
     if constexpr (!PIPELINED) {
-        for (; j + 3 * T < nvec; j += 4 * T) {
-            V4 v[4];
+        for (; j + (U - 1) * T < nvec; j += U * T) {
+            V4 v[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = load(j + u * T);
+            for (int u = 0; u < U; ++u) v[u] = load(j + u * T);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) body(v[u], j + u * T);
+            for (int u = 0; u < U; ++u) body(v[u], j + u * T);
         }
-    } else if (j + 3 * T < nvec) {
-        V4 cur[4];
+    } else if (j + (U - 1) * T < nvec) {
+        V4 cur[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) cur[u] = load(j + u * T);
-        for (j += 4 * T; j + 3 * T < nvec; j += 4 * T) {
-            V4 nxt[4];
+        for (int u = 0; u < U; ++u) cur[u] = load(j + u * T);
+        for (j += U * T; j + (U - 1) * T < nvec; j += U * T) {
+            V4 nxt[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) nxt[u] = load(j + u * T);
+            for (int u = 0; u < U; ++u) nxt[u] = load(j + u * T);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) body(cur[u], j - 4 * T + u * T);
+            for (int u = 0; u < U; ++u) body(cur[u], j - U * T + u * T);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
+            for (int u = 0; u < U; ++u) cur[u] = nxt[u];
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) body(cur[u], j - 4 * T + u * T);
+        for (int u = 0; u < U; ++u) body(cur[u], j - U * T + u * T);
     }
     for (; j < nvec; j += T) body(load(j), j);
 }
