@@ -476,12 +476,14 @@ def train_step_bench():
                     GradCrossEntropy) pull every gradient buffer across PCIe and back
       three_edits   the three bodies replaced by calls of the host layer, as the integration notes describe
       three_edits_tensor_cores   the same with matmul on the tensor cores (TF32 products)
+      four_edits_tensor_cores    the same with the body of Loss::CrossEntropy replaced by one host-layer call as well
       reference_cpu the same program linked with the reference itself (scalar back-end, host cores)
     The programs are built where the reference's sources are; absent binaries are reported as such."""
     built = os.path.join(ROOT, "tests", "cpp", "_built")
     runs = {"drop_in": (os.path.join(built, "train_step_gen2_b200"), {}),
             "three_edits": (os.path.join(built, "train_step_gen2_b200_edited"), {}),
             "three_edits_tensor_cores": (os.path.join(built, "train_step_gen2_b200_edited"), {"CTB_HOST_MATMUL_TENSOR_CORES": "1"}),
+            "four_edits_tensor_cores": (os.path.join(built, "train_step_gen2_b200_edited4"), {"CTB_HOST_MATMUL_TENSOR_CORES": "1"}),
             "reference_cpu": (os.path.join(ROOT, "oracle", "_ref", "train_step_gen2_ref_scalar"), {})}
     out = {}
     for shape_name, argv in (("batch512_1024x1024x16", ["512", "1024", "1024", "16"]),

@@ -6,7 +6,7 @@
 #
 #   tests/cpp/build_callers.sh REFERENCE_ROOT      (or set CTENSOR_REFERENCE)
 #
-# Outputs: tests/cpp/_built/callers_gen2_b200, callers_gen1_b200, train_step_gen2_b200(_edited),
+# Outputs: tests/cpp/_built/callers_gen2_b200, callers_gen1_b200, train_step_gen2_b200(_edited, _edited4),
 # reference_test_tensor_b200, reference_test_ops_b200, reference_time_avx_b200, reference_verify_gen1_b200.
 #
 # What a maintainer of the reference does is: replace tensor.h / device.h / ops_dispatch.h /
@@ -106,6 +106,29 @@ grep -q "^// void GradCrossEntropy::backward" "$G2/neuralnet/loss_edited.cpp" ||
 $CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200_edited" \
     "$HERE/train_step_program.cpp" "$G2/core/autograd_edited.cpp" "$G2/core/autograd_glue.cpp" \
     "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss_edited.cpp" -lctensor_host $LINK
+
+# A fourth edit, optional: the body of Loss::CrossEntropy (src/neuralnet/loss.cpp:90-118, eleven operators
+# and a host read of the reduced value) becomes one call of the host layer, the backward node attached as
+# the reference attaches it.
+awk '/^Tensor Loss::CrossEntropy\(const Tensor& pred_, const Tensor& target_, std::string reduction\) \{/ { skip = 1 } { if (skip) print "// " $0; else print } skip && /^}/ { skip = 0 }' \
+    "$G2/neuralnet/loss_edited.cpp" > "$G2/neuralnet/loss_edited4.cpp"
+cat >> "$G2/neuralnet/loss_edited4.cpp" <<'EOF'
+
+Tensor Loss::CrossEntropy(const Tensor& pred_, const Tensor& target_, std::string reduction) {
+    if (!pred_.impl || !target_.impl) throw std::runtime_error("Loss::CrossEntropy: null tensor");
+    if (pred_.impl->ndim != 2) throw std::runtime_error("CrossEntropy: Pred must be 2D [Batch, Classes]");
+    Tensor result = ctb_host::cross_entropy(pred_, target_, reduction == "mean");
+    if (pred_.requires_grad()) {
+        result.impl->requires_grad = true;
+        result.impl->grad_fn = std::make_shared<GradCrossEntropy>(pred_, target_, reduction);
+    }
+    return result;
+}
+EOF
+grep -q "^// Tensor Loss::CrossEntropy" "$G2/neuralnet/loss_edited4.cpp" || { echo "build_callers: Loss::CrossEntropy not found in loss.cpp" >&2; exit 4; }
+$CXX $FLAGS -I"$G2" -I"$G2/core" -I"$G2/neuralnet" -o "$OUT/train_step_gen2_b200_edited4" \
+    "$HERE/train_step_program.cpp" "$G2/core/autograd_edited.cpp" "$G2/core/autograd_glue.cpp" \
+    "$G2/neuralnet/layer.cpp" "$G2/neuralnet/loss_edited4.cpp" -lctensor_host $LINK
 
 # The reference's own unit tests of the tensor type and the operator dispatcher (test/test.cpp,
 # test/test_ops.cpp: known answers for creation, indexing, views, gather, arithmetic, matmul, reductions,

@@ -194,6 +194,7 @@ def _train_step_known_losses(batch, features, hidden, classes, steps, lr=0.05):
     ("train_step_gen2_b200", {}, 2e-5),                       # the reference's callers unchanged
     ("train_step_gen2_b200_edited", {}, 2e-5),                # the three bodies replaced by host-layer calls
     ("train_step_gen2_b200_edited", {"CTB_HOST_MATMUL_TENSOR_CORES": "1"}, 5e-3),      # TF32 products
+    ("train_step_gen2_b200_edited4", {}, 2e-5),               # + Loss::CrossEntropy's body as one host-layer call
 ])
 def test_training_step_follows_the_definition(exe, env, rtol):
     import json
