@@ -534,3 +534,29 @@ def test_long_rows_of_a_wider_buffer(ct, cols, pad, shift):
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-5, atol=2e-6)
     got = ct.layernorm(ct.DView.of(x), None, None, 1e-5)
     np.testing.assert_allclose(got.cpu().numpy(), (xs - mu) / np.sqrt(var + 1e-5), rtol=2e-5, atol=2e-6)
+
+
+def test_batchnorm_with_special_values_follows_the_reference_chain(ct, oracle):
+    """Channels that hold +inf, -inf, NaN or huge values: moments and normalised output as the
+    reference's operator chain gives them (NaN and inf propagate through the sums; the other channels
+    are untouched)."""
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((6, 7, 5, 8)).astype(np.float32)
+    x[1, 1, 2, 3] = np.inf
+    x[2, 2, 0, 0] = -np.inf
+    x[3, 3, 4, 7] = np.nan
+    x[:, 4] = 1e30
+    x[0, 5, 1, 1] = 3e38
+    x[5, 5, 1, 1] = 3e38
+    with np.errstate(all="ignore"):
+        want_mean, want_var = oracle.channel_moments(x)
+    mean, var = ct.channel_moments(torch.from_numpy(x).cuda())
+    np.testing.assert_allclose(mean.cpu().numpy().ravel(), np.asarray(want_mean).ravel(), rtol=RTOL, atol=1e-6, equal_nan=True)
+    np.testing.assert_allclose(var.cpu().numpy().ravel(), np.asarray(want_var).ravel(), rtol=RTOL, atol=1e-6, equal_nan=True)
+    g = rng.standard_normal(7).astype(np.float32)
+    b = rng.standard_normal(7).astype(np.float32)
+    m_in, v_in = np.asarray(want_mean, np.float32).ravel(), np.asarray(want_var, np.float32).ravel()
+    with np.errstate(all="ignore"):
+        want = oracle.batchnorm_apply(x, m_in, v_in, g, b, 1e-5)
+    got = ct.batchnorm_apply(*(torch.from_numpy(a).cuda() for a in (x, m_in, v_in, g, b)), 1e-5)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-6, atol=0, equal_nan=True)
