@@ -200,9 +200,6 @@ int launch_typed(int kind, const BwdPlan& p, const void* g, const void* x, const
 #ifndef CTB_CE_SWEEP1_LOADS
 #define CTB_CE_SWEEP1_LOADS 8
 #endif
-#ifndef CTB_CE_GRAD_SWEEP
-#define CTB_CE_GRAD_SWEEP 1
-#endif
 constexpr int kCeLongThreads = 512;       // two CTAs of 64 registers per SM
 
 __device__ __forceinline__ float cta_max_long(float v, float* smem) {
@@ -289,8 +286,8 @@ struct OnlineSum {
     }
 };
 
-// MODE 0: out[row] = nll; 1: out[row, :] = gradient; 2: out[row, :] += gradient (finite values only);
-// 3: as 1, in three sweeps that use the output row as scratch
+// MODE 0: out[row] = nll; 2: out[row, :] += gradient (finite values only), two sweeps;
+// 3: out[row, :] = gradient, in three sweeps that use the output row as scratch
 template <int MODE>
 __global__ void __launch_bounds__(kCeLongThreads, 2)
 ce_long_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* __restrict__ labels, int64_t label_stride,
@@ -489,8 +486,7 @@ int launch_ce_backward_rows(const float* x, int64_t row_stride, const int32_t* l
     if (!launch_ce_rows_registers(accumulate ? 2 : 1, x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad, st)) {
         const unsigned grid = (unsigned)(rows < 0x7FFFFFFFll ? rows : 0x7FFFFFFFll);
         if (accumulate) ce_long_rows_kernel<2><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-        else if (CTB_CE_GRAD_SWEEP) ce_long_rows_kernel<3><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
-        else ce_long_rows_kernel<1><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
+        else ce_long_rows_kernel<3><<<grid, kCeLongThreads, 0, st>>>(x, row_stride, labels, label_stride, rows, classes, scale, dx, dx_stride, bad);
     }
     return cuda_error(cudaGetLastError(), "cross-entropy backward launch");
 }

@@ -425,14 +425,7 @@ ce_rows_kernel(const float* __restrict__ x, int64_t row_stride, const int32_t* _
     }
 }
 
-// Rows of 8193 .. ~57000 columns (vocabulary-sized logits): the row is staged in shared memory,
-// so x (and the mask) are read once from HBM and the result is written once.  One 1024-thread CTA
-// per row; the dynamic shared memory holds the row, which also decides how many CTAs share an SM.
-// VEC4: row starts and lengths allow 128-bit accesses.
-constexpr int kSmemRowThreads = 1024;
-constexpr size_t kSmemRowMaxBytes = 227 * 1024 - 2048;      // dynamic shared memory a CTA may ask for, less the static part
-constexpr int kSmemRowUnroll = 4;
-
+// CTA-wide reductions for the long-row kernels (any block size).
 __device__ __forceinline__ float cta_max_any(float v, float* smem) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
@@ -454,95 +447,6 @@ __device__ __forceinline__ double cta_sum_any(double v, double* smem) {
     double r = smem[0];
     for (int i = 1; i < nw; ++i) r = __dadd_rn(r, smem[i]);
     return r;
-}
-
-template <bool VEC4>
-__global__ void __launch_bounds__(kSmemRowThreads)
-softmax_rows_smem_kernel(const float* __restrict__ x, const float* __restrict__ mask, float* __restrict__ out,
-                         RowIdx o, int64_t rows, int cols, int64_t qlen, int m_inner, int has_mask, int causal,
-                         int log_out) {
-    extern __shared__ __align__(16) float srow[];
-    __shared__ float smax[kSmemRowThreads / 32];
-    __shared__ double ssum[kSmemRowThreads / 32];
-    constexpr int W = VEC4 ? 4 : 1;
-    using V = Vec<float, W>;
-    const int tid = threadIdx.x;
-    const int stride = kSmemRowThreads * W;
-    for (int64_t ridx = blockIdx.x; ridx < rows; ridx += gridDim.x) {
-        int64_t xo, mo, row;
-        row_offsets(o, ridx, &xo, &mo, &row);
-        const float* xr = x + xo;
-        const float* mr = has_mask ? mask + mo : nullptr;
-        const float m0 = (has_mask && !m_inner) ? mr[0] : 0.0f;
-        const int live = causal ? (int)min((int64_t)cols, row % qlen + 1) : cols;
-        // pass 1: HBM -> shared memory (t = x + mask), running maximum; kSmemRowUnroll loads in flight
-        float m = -INFINITY;
-        int c = tid * W;
-        for (; c + (kSmemRowUnroll - 1) * stride < live; c += kSmemRowUnroll * stride) {
-            V v[kSmemRowUnroll];
-#pragma unroll
-            for (int u = 0; u < kSmemRowUnroll; ++u) v[u] = ldg_stream(reinterpret_cast<const V*>(xr + c + u * stride));
-#pragma unroll
-            for (int u = 0; u < kSmemRowUnroll; ++u) {
-                const int cc = c + u * stride;
-#pragma unroll
-                for (int k = 0; k < W; ++k) {
-                    float t = v[u].v[k];
-                    if (has_mask) t = __fadd_rn(t, m_inner ? mr[cc + k] : m0);
-                    if (causal && cc + k >= live) t = -INFINITY;
-                    v[u].v[k] = t;
-                    m = fmaxf(m, t);
-                }
-                *reinterpret_cast<V*>(srow + cc) = v[u];
-            }
-        }
-        for (; c < live; c += stride) {
-            V v = ldg_stream(reinterpret_cast<const V*>(xr + c));
-#pragma unroll
-            for (int k = 0; k < W; ++k) {
-                float t = v.v[k];
-                if (has_mask) t = __fadd_rn(t, m_inner ? mr[c + k] : m0);
-                if (causal && c + k >= live) t = -INFINITY;
-                v.v[k] = t;
-                m = fmaxf(m, t);
-            }
-            *reinterpret_cast<V*>(srow + c) = v;
-        }
-        m = cta_max_any(m, smax);
-        // pass 2: exponentials (kept in shared memory; log-softmax keeps the shifted input), fp64 sum
-        double z = 0.0;
-        for (c = tid * W; c < live; c += stride) {
-            V v = *reinterpret_cast<const V*>(srow + c);
-#pragma unroll
-            for (int k = 0; k < W; ++k) {
-                const float sh = __fsub_rn(v.v[k], m);
-                const float e = exp_cephes(sh);
-                v.v[k] = log_out ? sh : e;
-                z = __dadd_rn(z, (double)e);
-            }
-            *reinterpret_cast<V*>(srow + c) = v;
-        }
-        z = cta_sum_any(z, ssum);
-        const float zf = __double2float_rn(z);
-        const float rz = row_reciprocal(zf);
-        const float lz = log_out ? log_cephes(zf) : 0.0f;
-        // pass 3: shared memory -> HBM
-        float* orow = out + row * (int64_t)cols;
-        for (c = tid * W; c < cols; c += stride) {
-            V r;
-            if (c < live) {
-                const V v = *reinterpret_cast<const V*>(srow + c);
-#pragma unroll
-                for (int k = 0; k < W; ++k)
-                    r.v[k] = log_out ? __fsub_rn(v.v[k], lz) : ((causal && c + k >= live) ? 0.0f : div_by_row(v.v[k], zf, rz));
-            } else {
-#pragma unroll
-                for (int k = 0; k < W; ++k) r.v[k] = 0.0f;
-            }
-            stg_stream(reinterpret_cast<V*>(orow + c), r);
-        }
-        __syncthreads();                     // the row buffer is reused by the next row
-    }
 }
 
 // Rows too long for one CTA's registers, spread over a thread-block cluster: each of the CS CTAs
@@ -1385,7 +1289,6 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
         CTB_ROWS_DISPATCH(CTB_MODES_SOFTMAX, softmax_rows_kernel, (x, mask, out, o, g.rows, (int)g.cols, g.qlen), CTB_ROWS_W16_OFF);
     if (!launched) {
         const int grid = rows_grid(g.rows, 1);
-        const size_t row_bytes = ((size_t)g.cols * sizeof(float) + 15) / 16 * 16;
         // clusters of 2 / 4 / 8 CTAs: about 8K - 12.5K columns (32 - 50 KiB of shared memory) per CTA
         // measured best ([5341,50257]: 3.1 / 3.7 / 3.2 TB/s with 2 / 4 / 8 CTAs)
         const int cs = g.cols <= 25600 ? 2 : (g.cols <= 51200 ? 4 : 8);
@@ -1408,16 +1311,6 @@ int launch_softmax(const RowsGeom& g, const float* x, const float* mask, int cau
         } else if (g.cols < 0x7FFFFFFFll && chunk * 4 <= 100 * 1024 && g.rows * cs < 0x7FFFFFFFll) {
             rc = launch_softmax_cluster(cs, (int)chunk, g, x, mask, causal, log_out, out, o, st);
             if (rc) return rc;
-        } else if (g.cols < 0x7FFFFFFFll && row_bytes <= kSmemRowMaxBytes) {
-            // the row fits in shared memory: one pass over HBM
-            // (the attribute belongs to the current device's context: set per launch, it is cheap)
-            if (vec4) {
-                CTB_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_smem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemRowMaxBytes));
-                softmax_rows_smem_kernel<true><<<grid, kSmemRowThreads, row_bytes, st>>>(x, mask, out, o, g.rows, (int)g.cols, g.qlen, g.m_inner, g.has_mask, causal, log_out);
-            } else {
-                CTB_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_smem_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemRowMaxBytes));
-                softmax_rows_smem_kernel<false><<<grid, kSmemRowThreads, row_bytes, st>>>(x, mask, out, o, g.rows, (int)g.cols, g.qlen, g.m_inner, g.has_mask, causal, log_out);
-            }
         } else {
             softmax_rows_long_kernel<<<grid, 256, 0, st>>>(x, mask, out, o, g.rows, g.cols, g.qlen, g.m_inner, g.has_mask, causal, log_out);
         }
