@@ -785,6 +785,21 @@ def other_configs(ct, torch, dev):
         "cross_entropy_backward_262144x1000": gbs(8 * 262144 * 1000, lambda: ct.cross_entropy_backward(logits1k, labels1k, 1.0 / 262144, out=lo1k)),
         "cat_two_halves_1GiB": gbs(8 * n, lambda: ct.cat([gr.view(2, n // 2)[0].view(8192, -1), gr.view(2, n // 2)[1].view(8192, -1)], 1, out=m.view(8192, -1))),
     }
+    # vocabulary-sized rows ([5341, 50257] = 1 GiB; rows start at every 4-byte phase): the three-sweep kernels
+    vrows, vcols = 5341, 50257
+    vx = torch.randn(vrows, vcols, device=dev, generator=g)
+    vo = torch.empty_like(vx)
+    vg, vb = torch.randn(vcols, device=dev, generator=g), torch.randn(vcols, device=dev, generator=g)
+    vlab = torch.randint(0, vcols, (vrows, 1), device=dev, generator=g).to(torch.int32)
+    nv = vrows * vcols
+    callers["vocabulary_rows_5341x50257"] = {
+        "softmax": gbs(8 * nv, lambda: ct.softmax(vx, out=vo)),
+        "log_softmax": gbs(8 * nv, lambda: ct.log_softmax(vx, out=vo)),
+        "layernorm": gbs(8 * nv, lambda: ct.layernorm(vx, vg, vb, out=vo)),
+        "cross_entropy": gbs(4 * nv, lambda: ct.cross_entropy(vx, vlab, True, out=ce_loss)),
+        "cross_entropy_backward": gbs(8 * nv, lambda: ct.cross_entropy_backward(vx, vlab, 1.0 / vrows, out=vo)),
+    }
+    del vx, vo
     a2 = torch.randn(4096, 4096, device=dev, generator=g)
     c2 = torch.empty(4096, 4096, device=dev)
     for _ in range(2):
